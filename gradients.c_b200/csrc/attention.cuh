@@ -1,0 +1,21 @@
+// Internal interface between the attention entry points (attention.cu) and the tensor-core
+// flash kernels (attention_flash.cu).
+#pragma once
+#include "common.cuh"
+
+struct gdb_flash_args {
+    const void *q, *k, *v, *grad_out;
+    const int *cu;
+    void *out_or_dq;   // forward: out; backward: dQ
+    void *dk, *dv;     // backward only
+    float *stats;      // [N, Hq, 3] (row max, exp-sum, D); may be NULL in forward
+    int n_tokens, batch, hq, hkv, dh;
+    int causal, window, prefix, max_seqlen;
+    float scale;
+    uint32_t dtype;
+};
+
+// Both return GD_ERR_UNSUPPORTED when the configuration is outside the fast path; the caller
+// then runs the general kernels.
+gd_status gdb_flash_varlen_forward(gd_backend *be, const gdb_flash_args *a);
+gd_status gdb_flash_varlen_backward(gd_backend *be, const gdb_flash_args *a, bool have_forward_stats);

@@ -1,0 +1,243 @@
+// Shared definitions of the B200 backend: the opaque backend/buffer structs, view -> device
+// pointer resolution with byte-range checks (the CUDA counterpart of
+// gd_metal_byte_range_valid, reference src/backends/metal/backend_metal.m:340-352), storage
+// dtype conversion helpers and launch bookkeeping.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <string.h>
+#include <stdio.h>
+
+#include "../../include/gd_backend_b200.h"
+
+#define GDB_SM_COUNT_DEFAULT 148
+
+struct gdb_tmap_cache;  // tcgen05 GEMM tensor-map cache (gemm_tcgen05.cu)
+struct gdb_dp_state;    // NCCL state (dp.cu)
+
+struct gd_backend {
+    int device;
+    int sm_count;
+    cudaStream_t stream;
+    uint64_t launches;
+    int gemm_mode;            // 0 auto, 1 portable, 2 tcgen05 required
+    char last_error[256];
+    // private workspace (split-K partials, reductions, attention scratch); created once at
+    // create_default so no allocation happens while a step is being enqueued.
+    unsigned char *ws;
+    size_t ws_bytes;
+    int *err_flag;            // device int: set by kernels whose bounded waits gave up
+    int *err_flag_host;       // pinned mirror
+    float *rope_table;        // cos/sin table [512][32][2] for head_dim 64, theta 10000
+    unsigned char *l2_flush;  // >L2 scratch for gdb200_flush_l2
+    size_t l2_flush_bytes;
+    gdb_tmap_cache *tmaps;
+    gdb_dp_state *dp;
+};
+
+enum { GDB_BUF_DEVICE = 0, GDB_BUF_MANAGED = 1 };
+
+struct gd_backend_buffer {
+    gd_backend *backend;
+    unsigned char *dptr;   // device address (equals hptr for managed buffers)
+    void *hptr;            // address reported by gd_backend_buffer_host_ptr
+    size_t nbytes;
+    size_t reserve_bytes;  // size of the host address reservation when kind == DEVICE
+    int kind;
+};
+
+static inline gd_status gdb_fail(gd_backend *be, cudaError_t e, const char *what)
+{
+    if (be != NULL) {
+        snprintf(be->last_error, sizeof(be->last_error), "%s: %s", what, cudaGetErrorString(e));
+    }
+    return e == cudaErrorMemoryAllocation ? GD_ERR_OUT_OF_MEMORY : GD_ERR_INTERNAL;
+}
+
+// Check the launch that was just issued; counts it.
+static inline gd_status gdb_launched(gd_backend *be, const char *what)
+{
+    cudaError_t e = cudaGetLastError();
+    be->launches += 1U;
+    if (e != cudaSuccess) {
+        return gdb_fail(be, e, what);
+    }
+    return GD_OK;
+}
+
+static inline size_t gdb_dtype_size(uint32_t dtype)
+{
+    switch (dtype) {
+    case GDB_DTYPE_F16: case GDB_DTYPE_BF16: case GDB_DTYPE_U16: return 2U;
+    case GDB_DTYPE_F32: case GDB_DTYPE_I32: return 4U;
+    case GDB_DTYPE_U8: return 1U;
+    default: return 0U;
+    }
+}
+
+static inline bool gdb_range_ok(const gd_backend_buffer *b, size_t offset, size_t nbytes)
+{
+    return b != NULL && b->dptr != NULL && offset <= b->nbytes && nbytes <= b->nbytes - offset;
+}
+
+// Resolve a contiguous tensor view to a device pointer; NULL when the view is invalid.
+static inline void *gdb_tv_ptr(const gd_backend_tensor_view *v, uint32_t dtype)
+{
+    size_t es;
+    if (v == NULL || v->buffer == NULL || v->dtype != dtype) {
+        return NULL;
+    }
+    es = gdb_dtype_size(dtype);
+    if (es == 0U || v->count > SIZE_MAX / es || !gdb_range_ok(v->buffer, v->offset, v->count * es)) {
+        return NULL;
+    }
+    if ((v->offset % es) != 0U) {
+        return NULL;
+    }
+    return v->buffer->dptr + v->offset;
+}
+
+static inline void *gdb_raw_ptr(gd_backend_buffer *b, size_t offset, size_t nbytes)
+{
+    return gdb_range_ok(b, offset, nbytes) ? (void *)(b->dptr + offset) : NULL;
+}
+
+static inline bool gdb_same_shape(const gd_backend_tensor_view *a, const gd_backend_tensor_view *b)
+{
+    if (a->rank != b->rank || a->count != b->count || a->rank > 8U) {
+        return false;
+    }
+    for (uint32_t i = 0; i < a->rank; ++i) {
+        if (a->shape[i] != b->shape[i]) {
+            return false;
+        }
+    }
+    return true;
+}
+
+static inline bool gdb_is_float_dtype(uint32_t dt)
+{
+    return dt == GDB_DTYPE_F16 || dt == GDB_DTYPE_BF16 || dt == GDB_DTYPE_F32;
+}
+
+static inline unsigned gdb_grid_for(size_t work_items, unsigned threads, const gd_backend *be, unsigned waves)
+{
+    size_t blocks = (work_items + threads - 1U) / threads;
+    size_t cap = (size_t)(be != NULL && be->sm_count > 0 ? be->sm_count : GDB_SM_COUNT_DEFAULT) * waves;
+    if (blocks > cap) {
+        blocks = cap;
+    }
+    return blocks == 0U ? 1U : (unsigned)blocks;
+}
+
+#ifdef __CUDACC__
+// ---- storage <-> float conversion ----
+template <typename T> struct gdb_io;
+template <> struct gdb_io<__half> {
+    static __device__ __forceinline__ float ld(const __half *p, size_t i) { return __half2float(p[i]); }
+    static __device__ __forceinline__ void st(__half *p, size_t i, float v) { p[i] = __float2half_rn(v); }
+    static __device__ __forceinline__ float rnd(float v) { return __half2float(__float2half_rn(v)); }
+    static __device__ __forceinline__ float up(unsigned short bits) { return __half2float(__ushort_as_half(bits)); }
+    static __device__ __forceinline__ unsigned short down(float v) { return __half_as_ushort(__float2half_rn(v)); }
+};
+template <> struct gdb_io<__nv_bfloat16> {
+    static __device__ __forceinline__ float ld(const __nv_bfloat16 *p, size_t i) { return __bfloat162float(p[i]); }
+    static __device__ __forceinline__ void st(__nv_bfloat16 *p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    static __device__ __forceinline__ float up(unsigned short bits) { return __uint_as_float(((unsigned)bits) << 16); }
+    static __device__ __forceinline__ unsigned short down(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
+};
+template <> struct gdb_io<float> {
+    static __device__ __forceinline__ float ld(const float *p, size_t i) { return p[i]; }
+    static __device__ __forceinline__ void st(float *p, size_t i, float v) { p[i] = v; }
+    static __device__ __forceinline__ float rnd(float v) { return v; }
+};
+
+// 8 x 16-bit values held in one 16-byte vector.
+template <typename T> struct gdb_vec8 {
+    uint4 raw;
+    __device__ __forceinline__ float get(int i) const
+    {
+        const unsigned w = (&raw.x)[i >> 1];
+        return gdb_io<T>::up((unsigned short)((i & 1) ? (w >> 16) : (w & 0xffffU)));
+    }
+    __device__ __forceinline__ void set(int i, float v)
+    {
+        unsigned *w = &(&raw.x)[i >> 1];
+        const unsigned b = gdb_io<T>::down(v);
+        *w = (i & 1) ? ((*w & 0x0000ffffU) | (b << 16)) : ((*w & 0xffff0000U) | b);
+    }
+};
+
+__device__ __forceinline__ float gdb_warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v += __shfl_xor_sync(0xffffffffU, v, o);
+    }
+    return v;
+}
+__device__ __forceinline__ float gdb_warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffU, v, o));
+    }
+    return v;
+}
+// Block-wide sum for blocks of up to 1024 threads; `sh` must hold 33 floats.
+__device__ __forceinline__ float gdb_block_sum(float v, float *sh)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = gdb_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? sh[lane] : 0.0f;
+        t = gdb_warp_sum(t);
+        if (lane == 0) sh[32] = t;
+    }
+    __syncthreads();
+    return sh[32];
+}
+__device__ __forceinline__ float gdb_block_max(float v, float *sh)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = gdb_warp_max(v);
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? sh[lane] : -3.402823466e38f;
+        t = gdb_warp_max(t);
+        if (lane == 0) sh[32] = t;
+    }
+    __syncthreads();
+    return sh[32];
+}
+
+__device__ __forceinline__ uint64_t gdb_splitmix64(uint64_t x)
+{
+    x += 0x9E3779B97F4A7C15ULL;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBULL;
+    return x ^ (x >> 31);
+}
+#endif  // __CUDACC__
+
+// ---- entry points implemented in other translation units and shared internally ----
+gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb,
+                            const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
+                            const gd_backend_vector_view *bias, const gd_backend_matrix_view *y);
+// tcgen05 path: returns GD_ERR_UNSUPPORTED when the shape/alignment cannot use it.
+gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype,
+                           const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
+                           void *c, size_t ldc_bytes, const void *bias,
+                           uint32_t M, uint32_t N, uint32_t K);
+void gdb_tmap_cache_destroy(gd_backend *be);
+void gdb_dp_destroy(gd_backend *be);

@@ -1,0 +1,368 @@
+// Dense contraction entry points (matmul / matmul_nt / matmul_tn / linear / batched variants /
+// reduce_rows) and the portable tiled kernel used for shapes the tcgen05 path cannot take
+// (ragged sizes, strides that are not 16-byte multiples, F32 operands).
+//
+// Reference semantics: src/core/backend.h:187-223; F16 storage with FP32 accumulation and one
+// rounding at the store; gd_backend_linear adds the bias in FP32 before that rounding
+// (src/ops/_shared/gemm/metal_gemm_common.h:124-133); reduce_rows accumulates in FP32 and
+// rounds once (src/ops/linear/metal_linear.metal:33-52).
+#include "common.cuh"
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+// C[m, n] = sum_k A(m, k) * B(k, n) (+ bias[n]); A(m,k) = a[m*sam + k*sak], B(k,n) = b[k*sbk + n*sbn]
+// (element strides), C row-major with leading dimension ldc. 256 threads, 4x4 outputs each.
+template <typename T>
+__global__ void gemm_portable_kernel(const T *__restrict__ a, size_t sam, size_t sak,
+                                     const T *__restrict__ b, size_t sbk, size_t sbn,
+                                     T *__restrict__ c, size_t ldc, const T *__restrict__ bias,
+                                     unsigned M, unsigned N, unsigned K,
+                                     size_t batch_a, size_t batch_b, size_t batch_c)
+{
+    __shared__ float as[TK][TM + 4];
+    __shared__ float bs[TK][TN + 4];
+    a += (size_t)blockIdx.z * batch_a;
+    b += (size_t)blockIdx.z * batch_b;
+    c += (size_t)blockIdx.z * batch_c;
+    const unsigned m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+    const unsigned tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4] = {};
+    for (unsigned k0 = 0; k0 < K; k0 += TK) {
+        // A tile: TM x TK = 1024 elements, 4 per thread. Pick the loop order that walks the
+        // unit-stride dimension fastest across adjacent threads.
+        for (unsigned e = threadIdx.x; e < TM * TK; e += 256) {
+            unsigned mm, kk;
+            if (sak == 1) {
+                kk = e % TK;
+                mm = e / TK;
+            } else {
+                mm = e % TM;
+                kk = e / TM;
+            }
+            const unsigned gm = m0 + mm, gk = k0 + kk;
+            as[kk][mm] = (gm < M && gk < K) ? gdb_io<T>::ld(a, (size_t)gm * sam + (size_t)gk * sak) : 0.0f;
+        }
+        for (unsigned e = threadIdx.x; e < TN * TK; e += 256) {
+            unsigned nn, kk;
+            if (sbk == 1) {
+                kk = e % TK;
+                nn = e / TK;
+            } else {
+                nn = e % TN;
+                kk = e / TN;
+            }
+            const unsigned gn = n0 + nn, gk = k0 + kk;
+            bs[kk][nn] = (gn < N && gk < K) ? gdb_io<T>::ld(b, (size_t)gk * sbk + (size_t)gn * sbn) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                av[i] = as[kk][ty * 4 + i];
+                bv[i] = bs[kk][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned gm = m0 + ty * 4 + i;
+        if (gm >= M) {
+            continue;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned gn = n0 + tx * 4 + j;
+            if (gn < N) {
+                const float bv = bias != nullptr ? gdb_io<T>::ld(bias, gn) : 0.0f;
+                gdb_io<T>::st(c, (size_t)gm * ldc + gn, acc[i][j] + bv);
+            }
+        }
+    }
+}
+
+// reduce_rows stage 1: block (cb, rb) sums its row chunk for 256 columns into ws[rb, c].
+template <typename T>
+__global__ void reduce_rows_stage_kernel(const T *x, size_t ld, float *partial, size_t rows, size_t cols, size_t chunk)
+{
+    const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t r0 = (size_t)blockIdx.y * chunk;
+    size_t r1 = r0 + chunk;
+    if (r1 > rows) {
+        r1 = rows;
+    }
+    if (c >= cols) {
+        return;
+    }
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    size_t r = r0;
+    for (; r + 4 <= r1; r += 4) {
+        a0 += gdb_io<T>::ld(x, (r + 0) * ld + c);
+        a1 += gdb_io<T>::ld(x, (r + 1) * ld + c);
+        a2 += gdb_io<T>::ld(x, (r + 2) * ld + c);
+        a3 += gdb_io<T>::ld(x, (r + 3) * ld + c);
+    }
+    for (; r < r1; ++r) {
+        a0 += gdb_io<T>::ld(x, r * ld + c);
+    }
+    partial[(size_t)blockIdx.y * cols + c] = (a0 + a1) + (a2 + a3);
+}
+template <typename T>
+__global__ void reduce_rows_final_kernel(const float *partial, T *y, size_t blocks, size_t cols)
+{
+    const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) {
+        return;
+    }
+    float s = 0.0f;
+    for (size_t b = 0; b < blocks; ++b) {
+        s += partial[b * cols + c];
+    }
+    gdb_io<T>::st(y, c, s);
+}
+
+bool mv_ok(const gd_backend_matrix_view *v, size_t es)
+{
+    if (v == NULL || v->buffer == NULL || v->rows == 0U || v->cols == 0U || es == 0U) {
+        return false;
+    }
+    if (v->row_bytes < (size_t)v->cols * es || (v->row_bytes % es) != 0U || (v->offset % es) != 0U) {
+        return false;
+    }
+    const size_t span = (size_t)(v->rows - 1U) * v->row_bytes + (size_t)v->cols * es;
+    return gdb_range_ok(v->buffer, v->offset, span);
+}
+
+template <typename T>
+void launch_portable(gd_backend *be, int ta, int tb, const void *a, size_t lda, const void *b, size_t ldb,
+                     void *c, size_t ldc, const void *bias, unsigned M, unsigned N, unsigned K,
+                     unsigned batch, size_t ba, size_t bb, size_t bc)
+{
+    // lda/ldb/ldc in elements. ta: A stored [K, M]; tb: B stored [N, K].
+    const size_t sam = ta ? 1 : lda, sak = ta ? lda : 1;
+    const size_t sbk = tb ? 1 : ldb, sbn = tb ? ldb : 1;
+    dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, batch);
+    gemm_portable_kernel<T><<<grid, 256, 0, be->stream>>>((const T *)a, sam, sak, (const T *)b, sbk, sbn, (T *)c, ldc,
+                                                           (const T *)bias, M, N, K, ba, bb, bc);
+}
+
+}  // namespace
+
+// x: [M, K] (or [K, M] when ta), w: [K, N] (or [N, K] when tb), y: [M, N].
+gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb, const gd_backend_matrix_view *x,
+                            const gd_backend_matrix_view *w, const gd_backend_vector_view *bias,
+                            const gd_backend_matrix_view *y)
+{
+    if (be == NULL || x == NULL || w == NULL || y == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = y->dtype;
+    const size_t es = gdb_dtype_size(dt);
+    if (x->dtype != dt || w->dtype != dt) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (!gdb_is_float_dtype(dt)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (!mv_ok(x, es) || !mv_ok(w, es) || !mv_ok(y, es)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t M = y->rows, N = y->cols;
+    const uint32_t K = ta ? x->rows : x->cols;
+    if ((ta ? x->cols : x->rows) != M || (tb ? w->rows : w->cols) != N || (tb ? w->cols : w->rows) != K) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const void *bp = NULL;
+    if (bias != NULL) {
+        if (bias->buffer == NULL || bias->dtype != dt || bias->length != N || (bias->offset % es) != 0U ||
+            !gdb_range_ok(bias->buffer, bias->offset, (size_t)N * es)) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+        bp = bias->buffer->dptr + bias->offset;
+    }
+    const void *ap = x->buffer->dptr + x->offset;
+    const void *wp = w->buffer->dptr + w->offset;
+    void *cp = y->buffer->dptr + y->offset;
+    if (be->gemm_mode != 1 && dt != GDB_DTYPE_F32) {
+        gd_status st = gdb_gemm_tcgen05(be, ta, tb, dt, ap, x->row_bytes, wp, w->row_bytes, cp, y->row_bytes, bp, M, N, K);
+        if (st != GD_ERR_UNSUPPORTED) {
+            return st;
+        }
+        if (be->gemm_mode == 2) {
+            return GD_ERR_UNSUPPORTED;
+        }
+    } else if (be->gemm_mode == 2) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (dt == GDB_DTYPE_F16) {
+        launch_portable<__half>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0);
+    } else if (dt == GDB_DTYPE_BF16) {
+        launch_portable<__nv_bfloat16>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0);
+    } else {
+        launch_portable<float>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0);
+    }
+    return gdb_launched(be, "gemm_portable");
+}
+
+namespace {
+
+bool bv_ok(const gd_backend_batched_matrix_view *v, size_t es)
+{
+    if (v == NULL || v->buffer == NULL || v->rows == 0U || v->cols == 0U || v->batch_rank > GD_BACKEND_MAX_BATCH_DIMS ||
+        v->row_bytes < (size_t)v->cols * es || (v->row_bytes % es) != 0U || (v->offset % es) != 0U) {
+        return false;
+    }
+    size_t max_off = (size_t)(v->rows - 1U) * v->row_bytes + (size_t)v->cols * es;
+    for (uint32_t d = 0; d < v->batch_rank; ++d) {
+        if (v->batch_shape[d] == 0U || (v->batch_strides[d] % es) != 0U) {
+            return false;
+        }
+        max_off += (size_t)(v->batch_shape[d] - 1U) * v->batch_strides[d];
+    }
+    return gdb_range_ok(v->buffer, v->offset, max_off);
+}
+
+// Batched contraction with numpy-style broadcast over the batch dims of the output view.
+// batch_strides are byte strides; a stride of 0 broadcasts that operand.
+gd_status batched_dispatch(gd_backend *be, int ta, int tb, const gd_backend_batched_matrix_view *x,
+                           const gd_backend_batched_matrix_view *w, const gd_backend_batched_matrix_view *y)
+{
+    if (be == NULL || x == NULL || w == NULL || y == NULL || x->dtype != y->dtype || w->dtype != y->dtype) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = y->dtype;
+    const size_t es = gdb_dtype_size(dt);
+    if (!gdb_is_float_dtype(dt)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (!bv_ok(x, es) || !bv_ok(w, es) || !bv_ok(y, es) || x->batch_rank != y->batch_rank || w->batch_rank != y->batch_rank) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t M = y->rows, N = y->cols, K = ta ? x->rows : x->cols;
+    if ((ta ? x->cols : x->rows) != M || (tb ? w->rows : w->cols) != N || (tb ? w->cols : w->rows) != K) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    size_t total = 1;
+    for (uint32_t d = 0; d < y->batch_rank; ++d) {
+        total *= y->batch_shape[d];
+    }
+    if (total == 0U || total != y->batch_count) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    for (size_t bi = 0; bi < total; ++bi) {
+        size_t rem = bi, xo = 0, wo = 0, yo = 0;
+        for (int d = (int)y->batch_rank - 1; d >= 0; --d) {
+            const size_t idx = rem % y->batch_shape[d];
+            rem /= y->batch_shape[d];
+            xo += (x->batch_shape[d] == 1U ? 0U : idx) * x->batch_strides[d];
+            wo += (w->batch_shape[d] == 1U ? 0U : idx) * w->batch_strides[d];
+            yo += idx * y->batch_strides[d];
+        }
+        gd_backend_matrix_view xv = {x->buffer, x->offset + xo, x->rows, x->cols, x->row_bytes, dt};
+        gd_backend_matrix_view wv = {w->buffer, w->offset + wo, w->rows, w->cols, w->row_bytes, dt};
+        gd_backend_matrix_view yv = {y->buffer, y->offset + yo, y->rows, y->cols, y->row_bytes, dt};
+        gd_status st = gdb_gemm_dispatch(be, ta, tb, &xv, &wv, NULL, &yv);
+        if (st != GD_OK) {
+            return st;
+        }
+    }
+    return GD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+gd_status gd_backend_matmul(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_matrix_view *y)
+{
+    return gdb_gemm_dispatch(be, 0, 0, x, w, NULL, y);
+}
+gd_status gd_backend_matmul_nt(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_matrix_view *y)
+{
+    return gdb_gemm_dispatch(be, 0, 1, x, w, NULL, y);
+}
+gd_status gd_backend_matmul_tn(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_matrix_view *y)
+{
+    return gdb_gemm_dispatch(be, 1, 0, x, w, NULL, y);
+}
+gd_status gd_backend_linear(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_vector_view *bias, const gd_backend_matrix_view *y)
+{
+    return gdb_gemm_dispatch(be, 0, 0, x, w, bias, y);
+}
+gd_status gd_backend_batched_matmul(gd_backend *be, const gd_backend_batched_matrix_view *x, const gd_backend_batched_matrix_view *w, const gd_backend_batched_matrix_view *y)
+{
+    return batched_dispatch(be, 0, 0, x, w, y);
+}
+gd_status gd_backend_batched_matmul_nt(gd_backend *be, const gd_backend_batched_matrix_view *x, const gd_backend_batched_matrix_view *w, const gd_backend_batched_matrix_view *y)
+{
+    return batched_dispatch(be, 0, 1, x, w, y);
+}
+gd_status gd_backend_batched_matmul_tn(gd_backend *be, const gd_backend_batched_matrix_view *x, const gd_backend_batched_matrix_view *w, const gd_backend_batched_matrix_view *y)
+{
+    return batched_dispatch(be, 1, 0, x, w, y);
+}
+
+gd_status gd_backend_reduce_rows(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_vector_view *y)
+{
+    if (be == NULL || x == NULL || y == NULL || y->buffer == NULL || x->dtype != y->dtype || y->length != x->cols) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = x->dtype;
+    const size_t es = gdb_dtype_size(dt);
+    if (!gdb_is_float_dtype(dt)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (!mv_ok(x, es) || (y->offset % es) != 0U || !gdb_range_ok(y->buffer, y->offset, (size_t)y->length * es)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const size_t rows = x->rows, cols = x->cols, ld = x->row_bytes / es;
+    const unsigned col_blocks = (unsigned)((cols + 255U) / 256U);
+    size_t blocks = ((size_t)be->sm_count * 8U + col_blocks - 1U) / col_blocks;
+    if (blocks > (rows + 31U) / 32U) {
+        blocks = (rows + 31U) / 32U;
+    }
+    if (blocks * cols * sizeof(float) > be->ws_bytes) {
+        blocks = be->ws_bytes / (cols * sizeof(float));
+    }
+    if (blocks == 0U) {
+        return GD_ERR_OUT_OF_MEMORY;
+    }
+    const size_t chunk = (rows + blocks - 1U) / blocks;
+    blocks = (rows + chunk - 1U) / chunk;
+    const void *xp = x->buffer->dptr + x->offset;
+    void *yp = y->buffer->dptr + y->offset;
+    float *ws = (float *)be->ws;
+    dim3 grid(col_blocks, (unsigned)blocks);
+    if (dt == GDB_DTYPE_F16) {
+        reduce_rows_stage_kernel<__half><<<grid, 256, 0, be->stream>>>((const __half *)xp, ld, ws, rows, cols, chunk);
+    } else if (dt == GDB_DTYPE_BF16) {
+        reduce_rows_stage_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((const __nv_bfloat16 *)xp, ld, ws, rows, cols, chunk);
+    } else {
+        reduce_rows_stage_kernel<float><<<grid, 256, 0, be->stream>>>((const float *)xp, ld, ws, rows, cols, chunk);
+    }
+    gd_status st = gdb_launched(be, "reduce_rows stage");
+    if (st != GD_OK) {
+        return st;
+    }
+    if (dt == GDB_DTYPE_F16) {
+        reduce_rows_final_kernel<__half><<<col_blocks, 256, 0, be->stream>>>(ws, (__half *)yp, blocks, cols);
+    } else if (dt == GDB_DTYPE_BF16) {
+        reduce_rows_final_kernel<__nv_bfloat16><<<col_blocks, 256, 0, be->stream>>>(ws, (__nv_bfloat16 *)yp, blocks, cols);
+    } else {
+        reduce_rows_final_kernel<float><<<col_blocks, 256, 0, be->stream>>>(ws, (float *)yp, blocks, cols);
+    }
+    return gdb_launched(be, "reduce_rows final");
+}
+
+}  // extern "C"

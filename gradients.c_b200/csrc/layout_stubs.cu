@@ -1,0 +1,116 @@
+// Slice copies used by concat / split (multi-prompt prefill gathers last rows through
+// gd_backend_concat_to_full) and the entries that are off the gpt_lm path, which answer
+// GD_ERR_UNSUPPORTED exactly like the reference's null backend
+// (src/backends/null/backend_null.c). Slice semantics: src/core/backend.h:579-615.
+#include "common.cuh"
+
+namespace {
+
+// TO_FULL: full[o, off + a, r] = slice[o, a, r]; else slice[...] = full[...].
+template <typename U, bool TO_FULL>
+__global__ void slice_copy_kernel(const U *src, U *dst, size_t count, size_t slice_span, size_t full_span, size_t lead)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const size_t o = i / slice_span, r = i - o * slice_span;
+        const size_t f = o * full_span + lead + r;
+        if (TO_FULL) {
+            dst[f] = src[i];
+        } else {
+            dst[i] = src[f];
+        }
+    }
+}
+
+template <bool TO_FULL>
+gd_status slice_copy(gd_backend *be, const gd_backend_tensor_view *slice, const gd_backend_tensor_view *full,
+                     uint64_t count, uint64_t inner, uint64_t slice_axis, uint64_t full_axis, uint64_t axis_offset)
+{
+    if (be == NULL || slice == NULL || full == NULL || slice->dtype != full->dtype || inner == 0U || slice_axis == 0U ||
+        full_axis == 0U || axis_offset > full_axis || slice_axis > full_axis - axis_offset || slice->count != count ||
+        (count % (slice_axis * inner)) != 0U) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const size_t es = gdb_dtype_size(slice->dtype);
+    if (es == 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const size_t outer = count / (slice_axis * inner);
+    if (full->count != outer * full_axis * inner) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    void *sp = gdb_tv_ptr(slice, slice->dtype), *fp = gdb_tv_ptr(full, full->dtype);
+    if (sp == NULL || fp == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (count == 0U) {
+        return GD_OK;
+    }
+    const size_t ss = slice_axis * inner, fs = full_axis * inner, lead = axis_offset * inner;
+    const unsigned grid = gdb_grid_for(count, 256, be, 8);
+    const void *src = TO_FULL ? sp : fp;
+    void *dst = TO_FULL ? fp : sp;
+    if (es == 1U) {
+        slice_copy_kernel<unsigned char, TO_FULL><<<grid, 256, 0, be->stream>>>((const unsigned char *)src, (unsigned char *)dst, count, ss, fs, lead);
+    } else if (es == 2U) {
+        slice_copy_kernel<unsigned short, TO_FULL><<<grid, 256, 0, be->stream>>>((const unsigned short *)src, (unsigned short *)dst, count, ss, fs, lead);
+    } else {
+        slice_copy_kernel<unsigned, TO_FULL><<<grid, 256, 0, be->stream>>>((const unsigned *)src, (unsigned *)dst, count, ss, fs, lead);
+    }
+    return gdb_launched(be, "slice_copy");
+}
+
+}  // namespace
+
+#define TV const gd_backend_tensor_view *
+#define UNSUPPORTED_BODY { return GD_ERR_UNSUPPORTED; }
+
+extern "C" {
+
+gd_status gd_backend_concat_to_full(gd_backend *be, TV src, TV dst, const gd_backend_concat_args *a)
+{
+    return a == NULL ? GD_ERR_INVALID_ARGUMENT : slice_copy<true>(be, src, dst, a->count, a->inner, a->slice_axis, a->full_axis, a->axis_offset);
+}
+gd_status gd_backend_concat_from_full(gd_backend *be, TV src, TV dst, const gd_backend_concat_args *a)
+{
+    return a == NULL ? GD_ERR_INVALID_ARGUMENT : slice_copy<false>(be, dst, src, a->count, a->inner, a->slice_axis, a->full_axis, a->axis_offset);
+}
+gd_status gd_backend_split_from_full(gd_backend *be, TV full, TV slice, const gd_backend_split_args *a)
+{
+    return a == NULL ? GD_ERR_INVALID_ARGUMENT : slice_copy<false>(be, slice, full, a->count, a->inner, a->slice_axis, a->full_axis, a->axis_offset);
+}
+gd_status gd_backend_split_to_full(gd_backend *be, TV slice, TV full, const gd_backend_split_args *a)
+{
+    return a == NULL ? GD_ERR_INVALID_ARGUMENT : slice_copy<true>(be, slice, full, a->count, a->inner, a->slice_axis, a->full_axis, a->axis_offset);
+}
+
+gd_status gd_backend_permute(gd_backend *, TV, TV, const gd_backend_permute_args *) UNSUPPORTED_BODY
+gd_status gd_backend_mul(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_sub(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_sigmoid(gd_backend *, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_sigmoid_backward(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_tanh(gd_backend *, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_tanh_backward(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_reduce_contiguous(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_reduce_axis(gd_backend *, TV, TV, uint32_t, float) UNSUPPORTED_BODY
+gd_status gd_backend_broadcast_axis(gd_backend *, TV, TV, uint32_t, float) UNSUPPORTED_BODY
+gd_status gd_backend_broadcast_to(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_broadcast_scalar(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_reduce_broadcast(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_sigmoid_backward_from_output(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_tanh_backward_from_output(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_mul_backward_direct(gd_backend *, TV, TV, TV, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_mul_reduce_suffix(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
+gd_status gd_backend_mse_forward(gd_backend *, TV, TV, TV, uint64_t, float) UNSUPPORTED_BODY
+gd_status gd_backend_mse_backward(gd_backend *, TV, TV, TV, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_huber_forward(gd_backend *, TV, TV, TV, uint64_t, float, float) UNSUPPORTED_BODY
+gd_status gd_backend_huber_backward(gd_backend *, TV, TV, TV, TV, TV, float, float) UNSUPPORTED_BODY
+gd_status gd_backend_powlu_forward(gd_backend *, TV, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_powlu_backward(gd_backend *, TV, TV, TV, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_powlu_split_forward(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_powlu_split_backward(gd_backend *, TV, TV, TV, float) UNSUPPORTED_BODY
+gd_status gd_backend_minimax_m3_index_topk(gd_backend *, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY
+gd_status gd_backend_minimax_m3_sparse_attention(gd_backend *, TV, TV, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY
+gd_status gd_backend_minimax_m3_sparse_attention_backward(gd_backend *, TV, TV, TV, TV, TV, TV, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY
+
+}  // extern "C"

@@ -1,0 +1,374 @@
+// RMSNorm forward / backward / weight-gradient kernels (HBM-bound, one warp per row).
+//
+// Reference arithmetic: src/ops/rms_norm/metal_rms_norm.metal:29-608
+//   inv  = rsqrt(mean(x^2) + eps)                         (:59)
+//   out  = x * w * inv                                    (:64)
+//   dx   = inv * g * w - x * inv^3 / cols * sum(g * w * x) (:249-262)
+//   dw   = sum_rows g * x * inv, via FP32 partials [row_blocks, cols] (:414-447, :554-580)
+// The simdgroup counts in gd_backend_rms_norm_args describe the Metal launch and are ignored.
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROWS_PER_BLOCK = 4;  // 4 warps per block, one row each
+
+template <typename T> struct row_loader {
+    // Row sum of f(x) with 16-byte loads when the row allows it.
+    static __device__ __forceinline__ bool vec_ok(const T *row, size_t cols)
+    {
+        return sizeof(T) == 2 && (cols % 8U) == 0U && ((uintptr_t)row % 16U) == 0U;
+    }
+};
+
+// MODE 0: out only; MODE 1: out + inv; MODE 2: inv only.
+template <typename T, int MODE>
+__global__ void rms_fwd_kernel(const T *x, const T *w, T *out, float *inv_out, size_t rows, size_t cols, float eps)
+{
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+    if (row >= rows) {
+        return;
+    }
+    const T *xr = x + row * cols;
+    float ss = 0.0f;
+    bool vec = false;
+    if constexpr (sizeof(T) == 2) {
+        vec = (cols % 8U) == 0U && ((uintptr_t)xr % 16U) == 0U &&
+              (MODE == 2 || (((uintptr_t)(out + row * cols) | (uintptr_t)w) % 16U) == 0U);
+        if (vec) {
+            const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+            for (size_t v = lane; v < cols / 8U; v += 32) {
+                gdb_vec8<T> a;
+                a.raw = xv[v];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float f = a.get(e);
+                    ss += f * f;
+                }
+            }
+        }
+    }
+    if (!vec) {
+        for (size_t c = lane; c < cols; c += 32) {
+            const float f = gdb_io<T>::ld(xr, c);
+            ss += f * f;
+        }
+    }
+    ss = gdb_warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)cols + eps);
+    if (MODE != 0 && lane == 0) {
+        inv_out[row] = inv;
+    }
+    if (MODE == 2) {
+        return;
+    }
+    T *orow = out + row * cols;
+    if constexpr (sizeof(T) == 2) {
+        if (vec) {
+            const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+            const uint4 *wv = reinterpret_cast<const uint4 *>(w);
+            uint4 *ov = reinterpret_cast<uint4 *>(orow);
+            for (size_t v = lane; v < cols / 8U; v += 32) {
+                gdb_vec8<T> a, b;
+                a.raw = xv[v];
+                b.raw = __ldg(&wv[v]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    a.set(e, a.get(e) * b.get(e) * inv);
+                }
+                ov[v] = a.raw;
+            }
+            return;
+        }
+    }
+    for (size_t c = lane; c < cols; c += 32) {
+        gdb_io<T>::st(orow, c, gdb_io<T>::ld(xr, c) * gdb_io<T>::ld(w, c) * inv);
+    }
+}
+
+// STATS true: inv read from inv_in; false: recomputed from x.
+template <typename T, bool STATS>
+__global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, const T *g, T *dx, size_t rows, size_t cols, float eps)
+{
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+    if (row >= rows) {
+        return;
+    }
+    const T *xr = x + row * cols, *gr = g + row * cols;
+    T *dr = dx + row * cols;
+    float a = 0.0f, ss = 0.0f;
+    bool vec = false;
+    if constexpr (sizeof(T) == 2) {
+        vec = (cols % 8U) == 0U && (((uintptr_t)xr | (uintptr_t)gr | (uintptr_t)dr | (uintptr_t)w) % 16U) == 0U;
+        if (vec) {
+            const uint4 *xv = reinterpret_cast<const uint4 *>(xr), *gv = reinterpret_cast<const uint4 *>(gr);
+            const uint4 *wv = reinterpret_cast<const uint4 *>(w);
+            for (size_t v = lane; v < cols / 8U; v += 32) {
+                gdb_vec8<T> xa, ga, wa;
+                xa.raw = xv[v];
+                ga.raw = gv[v];
+                wa.raw = __ldg(&wv[v]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float xf = xa.get(e);
+                    a += ga.get(e) * wa.get(e) * xf;
+                    ss += xf * xf;
+                }
+            }
+        }
+    }
+    if (!vec) {
+        for (size_t c = lane; c < cols; c += 32) {
+            const float xf = gdb_io<T>::ld(xr, c);
+            a += gdb_io<T>::ld(gr, c) * gdb_io<T>::ld(w, c) * xf;
+            ss += xf * xf;
+        }
+    }
+    a = gdb_warp_sum(a);
+    float inv;
+    if (STATS) {
+        inv = inv_in[row];
+    } else {
+        ss = gdb_warp_sum(ss);
+        inv = rsqrtf(ss / (float)cols + eps);
+    }
+    const float k = inv * inv * inv / (float)cols;
+    if constexpr (sizeof(T) == 2) {
+        if (vec) {
+            const uint4 *xv = reinterpret_cast<const uint4 *>(xr), *gv = reinterpret_cast<const uint4 *>(gr);
+            const uint4 *wv = reinterpret_cast<const uint4 *>(w);
+            uint4 *dv = reinterpret_cast<uint4 *>(dr);
+            for (size_t v = lane; v < cols / 8U; v += 32) {
+                gdb_vec8<T> xa, ga, wa;
+                xa.raw = xv[v];
+                ga.raw = gv[v];
+                wa.raw = __ldg(&wv[v]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    ga.set(e, inv * ga.get(e) * wa.get(e) - xa.get(e) * k * a);
+                }
+                dv[v] = ga.raw;
+            }
+            return;
+        }
+    }
+    for (size_t c = lane; c < cols; c += 32) {
+        gdb_io<T>::st(dr, c, inv * gdb_io<T>::ld(gr, c) * gdb_io<T>::ld(w, c) - gdb_io<T>::ld(xr, c) * k * a);
+    }
+}
+
+// Stage 1 of dw: block (cb, rb) sums rows [rb*chunk, rb*chunk+chunk) of columns
+// [cb*256, cb*256+256) into partial[rb, c]; thread t owns column cb*256+t, 4 rows in flight.
+template <typename T>
+__global__ void rms_wgrad_stage_kernel(const T *x, const float *inv, const T *g, float *partial,
+                                       size_t rows, size_t cols, size_t chunk)
+{
+    const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t r0 = (size_t)blockIdx.y * chunk;
+    size_t r1 = r0 + chunk;
+    if (r1 > rows) {
+        r1 = rows;
+    }
+    if (c >= cols) {
+        return;
+    }
+    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+    size_t r = r0;
+    for (; r + 4 <= r1; r += 4) {
+        acc0 += gdb_io<T>::ld(g, (r + 0) * cols + c) * gdb_io<T>::ld(x, (r + 0) * cols + c) * __ldg(&inv[r + 0]);
+        acc1 += gdb_io<T>::ld(g, (r + 1) * cols + c) * gdb_io<T>::ld(x, (r + 1) * cols + c) * __ldg(&inv[r + 1]);
+        acc2 += gdb_io<T>::ld(g, (r + 2) * cols + c) * gdb_io<T>::ld(x, (r + 2) * cols + c) * __ldg(&inv[r + 2]);
+        acc3 += gdb_io<T>::ld(g, (r + 3) * cols + c) * gdb_io<T>::ld(x, (r + 3) * cols + c) * __ldg(&inv[r + 3]);
+    }
+    for (; r < r1; ++r) {
+        acc0 += gdb_io<T>::ld(g, r * cols + c) * gdb_io<T>::ld(x, r * cols + c) * __ldg(&inv[r]);
+    }
+    partial[(size_t)blockIdx.y * cols + c] = (acc0 + acc1) + (acc2 + acc3);
+}
+
+template <typename T>
+__global__ void rms_wgrad_reduce_kernel(const float *partial, T *dw, size_t blocks, size_t cols)
+{
+    const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) {
+        return;
+    }
+    float s = 0.0f;
+    for (size_t b = 0; b < blocks; ++b) {
+        s += partial[b * cols + c];
+    }
+    gdb_io<T>::st(dw, c, s);
+}
+
+bool args_ok(const gd_backend_rms_norm_args *a)
+{
+    return a != NULL && a->rows > 0U && a->cols > 0U && a->rows <= SIZE_MAX / a->cols && a->eps >= 0.0f;
+}
+
+template <typename T, int MODE>
+gd_status fwd_launch(gd_backend *be, const void *x, const void *w, void *out, float *inv, const gd_backend_rms_norm_args *a)
+{
+    const unsigned grid = (unsigned)((a->rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
+    rms_fwd_kernel<T, MODE><<<grid, 32 * ROWS_PER_BLOCK, 0, be->stream>>>((const T *)x, (const T *)w, (T *)out, inv, a->rows, a->cols, a->eps);
+    return gdb_launched(be, "rms_norm_forward");
+}
+
+template <int MODE>
+gd_status fwd_dispatch(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                       const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv_rms,
+                       const gd_backend_rms_norm_args *a)
+{
+    if (be == NULL || x == NULL || !args_ok(a) || x->count != a->rows * a->cols) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (!gdb_is_float_dtype(x->dtype)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const void *xp = gdb_tv_ptr(x, x->dtype), *wp = NULL;
+    void *op = NULL;
+    float *ip = NULL;
+    if (MODE != 2) {
+        if (weight == NULL || out == NULL || weight->count != a->cols || out->count != x->count) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+        wp = gdb_tv_ptr(weight, x->dtype);
+        op = gdb_tv_ptr(out, x->dtype);
+        if (wp == NULL || op == NULL) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+    }
+    if (MODE != 0) {
+        if (inv_rms == NULL || inv_rms->count != a->rows) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+        ip = (float *)gdb_tv_ptr(inv_rms, GDB_DTYPE_F32);
+        if (ip == NULL) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+    }
+    if (xp == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (x->dtype == GDB_DTYPE_F16) {
+        return fwd_launch<__half, MODE>(be, xp, wp, op, ip, a);
+    }
+    if (x->dtype == GDB_DTYPE_BF16) {
+        return fwd_launch<__nv_bfloat16, MODE>(be, xp, wp, op, ip, a);
+    }
+    return fwd_launch<float, MODE>(be, xp, wp, op, ip, a);
+}
+
+template <bool STATS>
+gd_status bwd_dispatch(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                       const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
+                       const gd_backend_tensor_view *grad_x, const gd_backend_rms_norm_args *a)
+{
+    if (be == NULL || x == NULL || weight == NULL || grad_out == NULL || grad_x == NULL || !args_ok(a) ||
+        x->count != a->rows * a->cols || weight->count != a->cols || grad_out->count != x->count ||
+        grad_x->count != x->count || (STATS && (inv_rms == NULL || inv_rms->count != a->rows))) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (!gdb_is_float_dtype(x->dtype)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const void *xp = gdb_tv_ptr(x, x->dtype), *wp = gdb_tv_ptr(weight, x->dtype), *gp = gdb_tv_ptr(grad_out, x->dtype);
+    void *dp = gdb_tv_ptr(grad_x, x->dtype);
+    const float *ip = STATS ? (const float *)gdb_tv_ptr(inv_rms, GDB_DTYPE_F32) : NULL;
+    if (xp == NULL || wp == NULL || gp == NULL || dp == NULL || (STATS && ip == NULL)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const unsigned grid = (unsigned)((a->rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
+    const unsigned threads = 32 * ROWS_PER_BLOCK;
+    if (x->dtype == GDB_DTYPE_F16) {
+        rms_bwd_kernel<__half, STATS><<<grid, threads, 0, be->stream>>>((const __half *)xp, (const __half *)wp, ip, (const __half *)gp, (__half *)dp, a->rows, a->cols, a->eps);
+    } else if (x->dtype == GDB_DTYPE_BF16) {
+        rms_bwd_kernel<__nv_bfloat16, STATS><<<grid, threads, 0, be->stream>>>((const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip, (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, a->rows, a->cols, a->eps);
+    } else {
+        rms_bwd_kernel<float, STATS><<<grid, threads, 0, be->stream>>>((const float *)xp, (const float *)wp, ip, (const float *)gp, (float *)dp, a->rows, a->cols, a->eps);
+    }
+    return gdb_launched(be, "rms_norm_backward");
+}
+
+}  // namespace
+
+extern "C" {
+
+gd_status gd_backend_rms_norm_forward(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight, const gd_backend_tensor_view *out, const gd_backend_rms_norm_args *args)
+{
+    return fwd_dispatch<0>(be, x, weight, out, NULL, args);
+}
+
+gd_status gd_backend_rms_norm_forward_stats(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight, const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv_rms, const gd_backend_rms_norm_args *args)
+{
+    return fwd_dispatch<1>(be, x, weight, out, inv_rms, args);
+}
+
+gd_status gd_backend_rms_norm_inv(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *inv_rms, const gd_backend_rms_norm_args *args)
+{
+    return fwd_dispatch<2>(be, x, NULL, NULL, inv_rms, args);
+}
+
+gd_status gd_backend_rms_norm_backward(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *grad_x, const gd_backend_rms_norm_args *args)
+{
+    return bwd_dispatch<false>(be, x, weight, NULL, grad_out, grad_x, args);
+}
+
+gd_status gd_backend_rms_norm_backward_stats(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight, const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *grad_x, const gd_backend_rms_norm_args *args)
+{
+    return bwd_dispatch<true>(be, x, weight, inv_rms, grad_out, grad_x, args);
+}
+
+// The caller provides partial [row_blocks, cols] F32; its content is private to the backend.
+// This implementation uses min(row_blocks, enough blocks for ~4 waves) row chunks.
+gd_status gd_backend_rms_norm_weight_backward_stats(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *grad_weight, const gd_backend_tensor_view *partial, const gd_backend_rms_norm_args *a)
+{
+    if (be == NULL || x == NULL || inv_rms == NULL || grad_out == NULL || grad_weight == NULL || partial == NULL ||
+        !args_ok(a) || a->row_blocks == 0U || x->count != a->rows * a->cols || grad_out->count != x->count ||
+        inv_rms->count != a->rows || grad_weight->count != a->cols || partial->count < a->row_blocks * a->cols) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (!gdb_is_float_dtype(x->dtype)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const void *xp = gdb_tv_ptr(x, x->dtype), *gp = gdb_tv_ptr(grad_out, x->dtype);
+    const float *ip = (const float *)gdb_tv_ptr(inv_rms, GDB_DTYPE_F32);
+    float *pp = (float *)gdb_tv_ptr(partial, GDB_DTYPE_F32);
+    void *dw = gdb_tv_ptr(grad_weight, x->dtype);
+    if (xp == NULL || gp == NULL || ip == NULL || pp == NULL || dw == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const unsigned col_blocks = (unsigned)((a->cols + 255U) / 256U);
+    size_t blocks = a->row_blocks;
+    const size_t want = ((size_t)be->sm_count * 8U + col_blocks - 1U) / col_blocks;
+    if (blocks > want) {
+        blocks = want;
+    }
+    if (blocks > 65535U) {
+        blocks = 65535U;
+    }
+    const size_t chunk = (a->rows + blocks - 1U) / blocks;
+    blocks = (a->rows + chunk - 1U) / chunk;
+    dim3 grid(col_blocks, (unsigned)blocks);
+    if (x->dtype == GDB_DTYPE_F16) {
+        rms_wgrad_stage_kernel<__half><<<grid, 256, 0, be->stream>>>((const __half *)xp, ip, (const __half *)gp, pp, a->rows, a->cols, chunk);
+    } else if (x->dtype == GDB_DTYPE_BF16) {
+        rms_wgrad_stage_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((const __nv_bfloat16 *)xp, ip, (const __nv_bfloat16 *)gp, pp, a->rows, a->cols, chunk);
+    } else {
+        rms_wgrad_stage_kernel<float><<<grid, 256, 0, be->stream>>>((const float *)xp, ip, (const float *)gp, pp, a->rows, a->cols, chunk);
+    }
+    gd_status st = gdb_launched(be, "rms_norm_wgrad_stage");
+    if (st != GD_OK) {
+        return st;
+    }
+    if (x->dtype == GDB_DTYPE_F16) {
+        rms_wgrad_reduce_kernel<__half><<<col_blocks, 256, 0, be->stream>>>(pp, (__half *)dw, blocks, a->cols);
+    } else if (x->dtype == GDB_DTYPE_BF16) {
+        rms_wgrad_reduce_kernel<__nv_bfloat16><<<col_blocks, 256, 0, be->stream>>>(pp, (__nv_bfloat16 *)dw, blocks, a->cols);
+    } else {
+        rms_wgrad_reduce_kernel<float><<<col_blocks, 256, 0, be->stream>>>(pp, (float *)dw, blocks, a->cols);
+    }
+    return gdb_launched(be, "rms_norm_wgrad_reduce");
+}
+
+}  // extern "C"

@@ -1,0 +1,384 @@
+/*
+ * gd_backend_b200.h - C ABI of the B200 (sm_100a) CUDA backend for gradients.c.
+ *
+ * The shared library libgd_backend_b200.so defines every global symbol that the
+ * gradients.c host runtime binds at its backend boundary (reference:
+ * src/core/backend.h:144-791 and src/core/backend_generated.h:6-43, 109 functions).
+ * The reference selects a backend at link time (one set of gd_backend_* symbols per
+ * build, Makefile:57-73), so linking libgradients.a against this library instead of
+ * src/backends/null/ is the whole integration.
+ *
+ * Struct layouts below are binary-compatible with the reference's view/descriptor
+ * structs (src/core/backend.h:21-140,301-305,321-325,528-537,579-639,671-689); the
+ * field order is part of the ABI. If the reference's own header is already included
+ * (GD_CORE_BACKEND_H defined) the type section is skipped and only the additive
+ * gdb200_* entry points are declared.
+ *
+ * Conventions shared by all entries (reference: src/core/backend.h and the behaviour of
+ * src/backends/metal/backend_metal.m:340-394,534-897):
+ *   - first argument is the backend handle; return value is a gd_status code
+ *     (include/gradients/status.h:8-19); arguments are validated and byte ranges are
+ *     checked against the buffer size; nothing aborts.
+ *   - `offset` fields are byte offsets into `buffer`; matrix views carry `row_bytes`.
+ *   - dtype codes are gd_dtype values (include/gradients/tensor.h:49-57).
+ *   - all work is enqueued on one in-order CUDA stream; gd_backend_flush waits for it.
+ *   - entries that are off the gpt_lm train/decode path return GD_ERR_UNSUPPORTED, as
+ *     the reference's null backend does (src/backends/null/backend_null.c).
+ */
+#ifndef GD_BACKEND_B200_H
+#define GD_BACKEND_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef GD_CORE_BACKEND_H /* reference header not present: declare the ABI ourselves */
+
+#ifndef GRADIENTS_STATUS_H
+/* include/gradients/status.h:8-19 */
+typedef enum gd_status {
+    GD_OK = 0,
+    GD_ERR_INVALID_ARGUMENT = -1,
+    GD_ERR_OUT_OF_MEMORY = -2,
+    GD_ERR_FROZEN = -3,
+    GD_ERR_BUSY = -4,
+    GD_ERR_BAD_STATE = -5,
+    GD_ERR_UNSUPPORTED = -6,
+    GD_ERR_INTERNAL = -7,
+    GD_ERR_NOT_IMPLEMENTED = -8,
+    GD_ERR_IO = -9
+} gd_status;
+#endif
+
+/* gd_dtype codes travel as uint32_t (include/gradients/tensor.h:49-57). */
+enum {
+    GDB_DTYPE_F16 = 1,
+    GDB_DTYPE_BF16 = 2,
+    GDB_DTYPE_F32 = 3,
+    GDB_DTYPE_I32 = 4,
+    GDB_DTYPE_U8 = 5,
+    GDB_DTYPE_U16 = 6
+};
+
+typedef struct gd_backend gd_backend;               /* opaque, src/core/backend.h:10 */
+typedef struct gd_backend_buffer gd_backend_buffer; /* opaque, src/core/backend.h:11 */
+typedef struct gd_backend_fence { void *handle; } gd_backend_fence; /* :13-15 */
+
+/* src/core/backend.h:17-19 has only the Metal kind; this backend reports 2. */
+typedef enum gd_backend_kind { GD_BACKEND_METAL = 1, GD_BACKEND_CUDA_B200 = 2 } gd_backend_kind;
+
+/* ---- views (src/core/backend.h:21-50,132-140) ---- */
+typedef struct gd_backend_matrix_view {
+    gd_backend_buffer *buffer;
+    size_t offset;
+    uint32_t rows, cols;
+    size_t row_bytes;
+    uint32_t dtype;
+} gd_backend_matrix_view;
+
+#define GD_BACKEND_MAX_BATCH_DIMS 6U
+typedef struct gd_backend_batched_matrix_view {
+    gd_backend_buffer *buffer;
+    size_t offset;
+    uint32_t rows, cols;
+    size_t row_bytes;
+    uint32_t dtype;
+    uint32_t batch_rank, batch_count;
+    uint32_t batch_shape[GD_BACKEND_MAX_BATCH_DIMS];
+    size_t batch_strides[GD_BACKEND_MAX_BATCH_DIMS];
+} gd_backend_batched_matrix_view;
+
+typedef struct gd_backend_vector_view {
+    gd_backend_buffer *buffer;
+    size_t offset;
+    uint32_t length;
+    uint32_t dtype;
+} gd_backend_vector_view;
+
+typedef struct gd_backend_tensor_view {
+    gd_backend_buffer *buffer;
+    size_t offset;
+    size_t count;
+    uint32_t dtype;
+    uint32_t rank;
+    int64_t shape[8];
+    int64_t strides[8];
+} gd_backend_tensor_view;
+
+/* ---- optimizer / AMP descriptors (src/core/backend.h:52-130) ---- */
+typedef struct gd_backend_adamw_desc {
+    gd_backend_buffer *param_buffer;      size_t param_offset;
+    gd_backend_buffer *master_buffer;     size_t master_offset;     /* optional FP32 masters */
+    gd_backend_buffer *grad_buffer;       size_t grad_offset;
+    gd_backend_buffer *grad_scale_buffer; size_t grad_scale_offset; /* optional F32 multiplier */
+    gd_backend_buffer *found_inf_buffer;  size_t found_inf_offset;  /* optional I32 skip flag */
+    gd_backend_buffer *m_buffer;          size_t m_offset;
+    gd_backend_buffer *v_buffer;          size_t v_offset;
+    gd_backend_buffer *state_f32_buffer;  /* optional device scalar state */
+    size_t beta1_power_offset, beta2_power_offset, step_scale_offset, decay_scale_offset, eps_scaled_offset;
+    gd_backend_buffer *state_i32_buffer;  /* optional device step counters */
+    size_t param_step_offset, optimizer_step_offset;
+    size_t count;
+    uint32_t param_dtype, grad_dtype;
+    uint32_t has_master, has_grad_scale, has_found_inf, has_device_state;
+    uint32_t bias_correction, update_optimizer_step;
+    float lr, beta1, beta2, eps, weight_decay, bias_correction1, bias_correction2;
+} gd_backend_adamw_desc;
+
+typedef struct gd_backend_amp_state_desc {
+    gd_backend_buffer *scale_buffer; size_t scale_offset; /* F32[2]: scale, 1/scale */
+    gd_backend_buffer *flags_buffer; size_t flags_offset; /* I32[3]: growth_tracker, found_inf, last_found_inf */
+    float growth_factor, backoff_factor, min_scale, max_scale;
+    uint32_t growth_interval;
+} gd_backend_amp_state_desc;
+
+typedef struct gd_backend_amp_unscale_desc {
+    gd_backend_buffer *grad_buffer; size_t grad_offset;
+    size_t count;
+    uint32_t grad_dtype;
+    gd_backend_buffer *inv_scale_buffer; size_t inv_scale_offset;
+    gd_backend_buffer *found_inf_buffer; size_t found_inf_offset;
+} gd_backend_amp_unscale_desc;
+
+typedef struct gd_backend_grad_norm_desc {
+    gd_backend_buffer *grad_buffer; size_t grad_offset;
+    size_t count;
+    uint32_t grad_dtype;
+    gd_backend_buffer *partial_buffer; size_t partial_offset; size_t partial_count;
+    gd_backend_buffer *grad_scale_buffer; size_t grad_scale_offset;
+    gd_backend_buffer *found_inf_buffer; size_t found_inf_offset;
+    uint32_t has_found_inf;
+} gd_backend_grad_norm_desc;
+
+/* ---- per-op argument blocks ---- */
+typedef struct gd_backend_embedding_args { uint64_t ids_count, vocab, dim; } gd_backend_embedding_args; /* :301-305 */
+typedef struct gd_backend_rope_args { float theta; uint32_t n_dims; uint32_t interleaved; } gd_backend_rope_args; /* :321-325 */
+typedef struct gd_backend_rms_norm_args { /* :528-537 */
+    uint64_t rows, cols, row_blocks;
+    float eps;
+    uint32_t simdgroups, wgrad_simdgroups, wgrad_row_block, reserved0;
+} gd_backend_rms_norm_args;
+typedef struct gd_backend_concat_args { uint64_t count, inner, slice_axis, full_axis, axis_offset; } gd_backend_concat_args; /* :579-585 */
+typedef struct gd_backend_split_args { uint64_t count, inner, slice_axis, full_axis, axis_offset; } gd_backend_split_args;   /* :598-604 */
+typedef struct gd_backend_permute_args { /* :617-624 */
+    uint64_t count, inner;
+    uint32_t rank, active_rank;
+    uint32_t axes[8];
+    uint32_t reserved0;
+} gd_backend_permute_args;
+typedef struct gd_backend_minimax_m3_sparse_args { /* :632-639 */
+    float scale;
+    uint32_t block_size, topk, init_blocks, local_blocks, max_seqlen;
+} gd_backend_minimax_m3_sparse_args;
+typedef struct gd_backend_sdpa_varlen_args { /* :671-678 */
+    float scale;
+    uint32_t causal, sliding_window, prefix_len, max_seqlen, use_forward_stats;
+} gd_backend_sdpa_varlen_args;
+typedef struct gd_backend_sdpa_decode_args { /* :680-685 */
+    float scale;
+    uint32_t sliding_window, prefix_len;
+    int32_t cache_pos;
+} gd_backend_sdpa_decode_args;
+typedef struct gd_backend_kv_cache_append_args { int32_t cache_pos; } gd_backend_kv_cache_append_args; /* :687-689 */
+
+#define GDB_TV const gd_backend_tensor_view *
+#define GDB_MV const gd_backend_matrix_view *
+#define GDB_BV const gd_backend_batched_matrix_view *
+#define GDB_VV const gd_backend_vector_view *
+
+/* ---- lifecycle, buffers, stream scope, fences (src/core/backend.h:144-158,788-791) ---- */
+gd_status gd_backend_create_default(gd_backend **out_backend);
+void gd_backend_destroy(gd_backend *backend);
+gd_backend_kind gd_backend_kind_query(const gd_backend *backend);
+const char *gd_backend_name(const gd_backend *backend);
+gd_status gd_backend_buffer_create(gd_backend *backend, size_t nbytes, gd_backend_buffer **out_buffer);
+void gd_backend_buffer_destroy(gd_backend_buffer *buffer);
+size_t gd_backend_buffer_nbytes(const gd_backend_buffer *buffer);
+void *gd_backend_buffer_host_ptr(gd_backend_buffer *buffer);
+bool gd_backend_buffer_is_host_visible(const gd_backend_buffer *buffer);
+gd_status gd_backend_scope_begin(gd_backend *backend);
+gd_status gd_backend_flush(gd_backend *backend);
+gd_status gd_backend_record_fence(gd_backend *backend, gd_backend_fence *out_fence);
+void gd_backend_fence_destroy(gd_backend_fence *fence);
+bool gd_backend_fence_is_complete(gd_backend_fence *fence);
+gd_status gd_backend_fence_wait(gd_backend_fence *fence);
+
+/* ---- transfers and initialisers (:160-185) ---- */
+gd_status gd_backend_upload(gd_backend *backend, gd_backend_buffer *buffer, size_t offset, const void *src, size_t nbytes);
+gd_status gd_backend_download(gd_backend *backend, gd_backend_buffer *buffer, size_t offset, void *dst, size_t nbytes);
+gd_status gd_backend_fill(gd_backend *backend, gd_backend_buffer *buffer, size_t offset, size_t count, size_t elem_size, uint32_t pattern);
+gd_status gd_backend_rand_uniform(gd_backend *backend, gd_backend_buffer *buffer, size_t offset, size_t count, uint32_t dtype, uint64_t seed, float low, float high);
+
+/* ---- dense contractions (:187-223). matmul: y = x w; _nt: y = x w^T (w stored [y.cols, x.cols]);
+ * _tn: y = x^T w (x stored [inner, y.rows]); linear: y = x w + bias (bias added in FP32 before the
+ * single rounding); reduce_rows: y[c] = sum_r x[r,c]. F16/BF16 storage, FP32 accumulation. ---- */
+gd_status gd_backend_matmul(gd_backend *backend, GDB_MV x, GDB_MV w, GDB_MV y);
+gd_status gd_backend_matmul_nt(gd_backend *backend, GDB_MV x, GDB_MV w, GDB_MV y);
+gd_status gd_backend_matmul_tn(gd_backend *backend, GDB_MV x, GDB_MV w, GDB_MV y);
+gd_status gd_backend_batched_matmul(gd_backend *backend, GDB_BV x, GDB_BV w, GDB_BV y);
+gd_status gd_backend_batched_matmul_nt(gd_backend *backend, GDB_BV x, GDB_BV w, GDB_BV y);
+gd_status gd_backend_batched_matmul_tn(gd_backend *backend, GDB_BV x, GDB_BV w, GDB_BV y);
+gd_status gd_backend_linear(gd_backend *backend, GDB_MV x, GDB_MV w, GDB_VV bias, GDB_MV y);
+gd_status gd_backend_reduce_rows(gd_backend *backend, GDB_MV x, GDB_VV y);
+
+/* ---- gradient plumbing (:224-240): dst += src (F16 rounds every add); dst = src * scale ---- */
+gd_status gd_backend_accumulate(gd_backend *backend, gd_backend_buffer *dst_buffer, size_t dst_offset, gd_backend_buffer *src_buffer, size_t src_offset, size_t count, uint32_t dtype);
+gd_status gd_backend_scale(gd_backend *backend, gd_backend_buffer *dst_buffer, size_t dst_offset, gd_backend_buffer *src_buffer, size_t src_offset, size_t count, uint32_t dtype, float scale);
+
+/* ---- elementwise, generated group (src/core/backend_generated.h:6-43) ---- */
+gd_status gd_backend_relu(gd_backend *backend, GDB_TV x, GDB_TV y);
+gd_status gd_backend_relu_backward(gd_backend *backend, GDB_TV x, GDB_TV grad_out, GDB_TV grad_x);
+gd_status gd_backend_add(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV out);
+gd_status gd_backend_mul(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV out);
+gd_status gd_backend_sub(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV out);
+gd_status gd_backend_sigmoid(gd_backend *backend, GDB_TV x, GDB_TV y);
+gd_status gd_backend_sigmoid_backward(gd_backend *backend, GDB_TV x, GDB_TV grad_out, GDB_TV grad_x);
+gd_status gd_backend_tanh(gd_backend *backend, GDB_TV x, GDB_TV y);
+gd_status gd_backend_tanh_backward(gd_backend *backend, GDB_TV x, GDB_TV grad_out, GDB_TV grad_x);
+
+/* ---- dropout (:273-299): keep iff top 24 bits of splitmix64(seed+i) >= ceil(p*2^24) ---- */
+gd_status gd_backend_dropout_forward(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV mask, float p, uint64_t seed);
+gd_status gd_backend_dropout_add_forward(gd_backend *backend, GDB_TV residual, GDB_TV x, GDB_TV y, GDB_TV mask, float p, uint64_t seed);
+gd_status gd_backend_dropout_backward(gd_backend *backend, GDB_TV grad_out, GDB_TV grad_x, float p, uint64_t seed);
+gd_status gd_backend_dropout_backward_mask(gd_backend *backend, GDB_TV mask, GDB_TV grad_out, GDB_TV grad_x, float scale);
+
+/* ---- embedding (:307-319): invalid ids give NaN rows forward and are skipped backward ---- */
+gd_status gd_backend_embedding_forward(gd_backend *backend, GDB_TV table, GDB_TV ids, GDB_TV out, const gd_backend_embedding_args *args);
+gd_status gd_backend_embedding_backward(gd_backend *backend, GDB_TV grad_out, GDB_TV ids, GDB_TV grad_table, GDB_TV scratch, const gd_backend_embedding_args *args);
+
+/* ---- rotary embedding (:327-358) ---- */
+gd_status gd_backend_rope(gd_backend *backend, GDB_TV x, GDB_TV pos_ids, GDB_TV out, const gd_backend_rope_args *args);
+gd_status gd_backend_rope_backward(gd_backend *backend, GDB_TV grad_out, GDB_TV pos_ids, GDB_TV grad_x, const gd_backend_rope_args *args);
+gd_status gd_backend_qkv_split_rope_forward(gd_backend *backend, GDB_TV qkv, GDB_TV pos_ids, GDB_TV q, GDB_TV k, GDB_TV v, uint32_t n_heads, uint32_t head_dim, const gd_backend_rope_args *args);
+gd_status gd_backend_qkv_split_rope_backward(gd_backend *backend, GDB_TV grad_q, GDB_TV grad_k, GDB_TV grad_v, GDB_TV pos_ids, GDB_TV grad_qkv, uint32_t n_heads, uint32_t head_dim, const gd_backend_rope_args *args);
+
+/* ---- gated MLP (:509-526): out = x1 * silu(x2); split form takes x12 = [x1 | x2] ---- */
+gd_status gd_backend_swiglu_forward(gd_backend *backend, GDB_TV x1, GDB_TV x2, GDB_TV out);
+gd_status gd_backend_swiglu_backward(gd_backend *backend, GDB_TV x1, GDB_TV x2, GDB_TV grad_out, GDB_TV grad_x1, GDB_TV grad_x2);
+gd_status gd_backend_swiglu_split_forward(gd_backend *backend, GDB_TV x12, GDB_TV out);
+gd_status gd_backend_swiglu_split_backward(gd_backend *backend, GDB_TV x12, GDB_TV grad_out, GDB_TV grad_x12);
+
+/* ---- RMSNorm (:539-577) ---- */
+gd_status gd_backend_rms_norm_forward(gd_backend *backend, GDB_TV x, GDB_TV weight, GDB_TV out, const gd_backend_rms_norm_args *args);
+gd_status gd_backend_rms_norm_forward_stats(gd_backend *backend, GDB_TV x, GDB_TV weight, GDB_TV out, GDB_TV inv_rms, const gd_backend_rms_norm_args *args);
+gd_status gd_backend_rms_norm_inv(gd_backend *backend, GDB_TV x, GDB_TV inv_rms, const gd_backend_rms_norm_args *args);
+gd_status gd_backend_rms_norm_backward(gd_backend *backend, GDB_TV x, GDB_TV weight, GDB_TV grad_out, GDB_TV grad_x, const gd_backend_rms_norm_args *args);
+gd_status gd_backend_rms_norm_backward_stats(gd_backend *backend, GDB_TV x, GDB_TV weight, GDB_TV inv_rms, GDB_TV grad_out, GDB_TV grad_x, const gd_backend_rms_norm_args *args);
+gd_status gd_backend_rms_norm_weight_backward_stats(gd_backend *backend, GDB_TV x, GDB_TV inv_rms, GDB_TV grad_out, GDB_TV grad_weight, GDB_TV partial, const gd_backend_rms_norm_args *args);
+
+/* ---- attention and KV cache (:691-750) ---- */
+gd_status gd_backend_sdpa_varlen(gd_backend *backend, GDB_TV q, GDB_TV k, GDB_TV v, GDB_TV cu_seqlens, GDB_TV out, GDB_TV stats, const gd_backend_sdpa_varlen_args *args);
+gd_status gd_backend_sdpa_varlen_backward(gd_backend *backend, GDB_TV grad_out, GDB_TV q, GDB_TV k, GDB_TV v, GDB_TV cu_seqlens, GDB_TV grad_q, GDB_TV grad_k, GDB_TV grad_v, GDB_TV stats, const gd_backend_sdpa_varlen_args *args);
+gd_status gd_backend_sdpa_decode(gd_backend *backend, GDB_TV q, GDB_TV k_cache, GDB_TV v_cache, GDB_TV cache_pos, GDB_TV out, const gd_backend_sdpa_decode_args *args);
+gd_status gd_backend_sdpa_decode_at(gd_backend *backend, GDB_TV q, GDB_TV k_cache, GDB_TV v_cache, GDB_TV out, const gd_backend_sdpa_decode_args *args);
+gd_status gd_backend_sdpa_decode_positions(gd_backend *backend, GDB_TV q, GDB_TV k_cache, GDB_TV v_cache, GDB_TV cache_pos, GDB_TV out, const gd_backend_sdpa_decode_args *args);
+gd_status gd_backend_kv_cache_append_at(gd_backend *backend, GDB_TV k_cache, GDB_TV v_cache, GDB_TV k_new, GDB_TV v_new, const gd_backend_kv_cache_append_args *args);
+gd_status gd_backend_kv_cache_append_positions(gd_backend *backend, GDB_TV k_cache, GDB_TV v_cache, GDB_TV cache_pos, GDB_TV k_new, GDB_TV v_new, const gd_backend_kv_cache_append_args *args);
+gd_status gd_backend_kv_cache_append_packed(gd_backend *backend, GDB_TV k_cache, GDB_TV v_cache, GDB_TV cache_pos, GDB_TV cu_seqlens, GDB_TV k_new, GDB_TV v_new, const gd_backend_kv_cache_append_args *args);
+
+/* ---- losses (:381-450) ---- */
+gd_status gd_backend_cross_entropy_loss(gd_backend *backend, GDB_TV logits, GDB_TV targets, GDB_TV row_loss);
+gd_status gd_backend_cross_entropy_loss_stats(gd_backend *backend, GDB_TV logits, GDB_TV targets, GDB_TV row_loss, GDB_TV row_max, GDB_TV row_inv_sum);
+gd_status gd_backend_cross_entropy_backward(gd_backend *backend, GDB_TV logits, GDB_TV targets, GDB_TV grad_loss, GDB_TV grad_logits, float scale);
+gd_status gd_backend_cross_entropy_backward_stats(gd_backend *backend, GDB_TV logits, GDB_TV targets, GDB_TV row_max, GDB_TV row_inv_sum, GDB_TV grad_loss, GDB_TV grad_logits, float scale);
+gd_status gd_backend_lm_cross_entropy_online_update(gd_backend *backend, GDB_TV logits_chunk, GDB_TV bias_chunk, GDB_TV targets, GDB_TV row_loss, GDB_TV row_max, GDB_TV row_inv_sum, uint64_t class_start, uint64_t total_classes, float logits_softcap);
+gd_status gd_backend_lm_cross_entropy_finalize(gd_backend *backend, GDB_TV targets, GDB_TV row_loss, GDB_TV row_max, GDB_TV row_inv_sum, GDB_TV row_valid, uint64_t total_classes, int32_t ignore_index);
+gd_status gd_backend_lm_cross_entropy_reduce_normalize(gd_backend *backend, GDB_TV row_loss, GDB_TV row_valid, GDB_TV loss, GDB_TV inv_valid_count);
+gd_status gd_backend_lm_cross_entropy_backward_chunk(gd_backend *backend, GDB_TV logits_chunk, GDB_TV bias_chunk, GDB_TV targets, GDB_TV row_max, GDB_TV row_inv_sum, GDB_TV grad_loss, GDB_TV inv_valid_count, GDB_TV grad_logits_chunk, uint64_t class_start, uint64_t total_classes, float scale, float logits_softcap, int32_t ignore_index);
+
+/* ---- AMP loss scaling, gradient clipping, AdamW (:752-786) ---- */
+gd_status gd_backend_amp_begin_step(gd_backend *backend, const gd_backend_amp_state_desc *desc);
+gd_status gd_backend_amp_finish_step(gd_backend *backend, const gd_backend_amp_state_desc *desc);
+gd_status gd_backend_amp_fill_scale(gd_backend *backend, gd_backend_buffer *dst_buffer, size_t dst_offset, size_t count, uint32_t dtype, gd_backend_buffer *scale_buffer, size_t scale_offset);
+gd_status gd_backend_amp_scale(gd_backend *backend, gd_backend_buffer *dst_buffer, size_t dst_offset, gd_backend_buffer *src_buffer, size_t src_offset, size_t count, uint32_t dtype, gd_backend_buffer *scale_buffer, size_t scale_offset);
+gd_status gd_backend_amp_unscale(gd_backend *backend, const gd_backend_amp_unscale_desc *desc);
+gd_status gd_backend_amp_unscale_batch(gd_backend *backend, const gd_backend_amp_unscale_desc *descs, uint32_t desc_count);
+gd_status gd_backend_grad_clip_scale(gd_backend *backend, const gd_backend_grad_norm_desc *descs, uint32_t desc_count, gd_backend_buffer *scale_buffer, size_t scale_offset, float max_norm, float eps);
+gd_status gd_backend_adamw(gd_backend *backend, const gd_backend_adamw_desc *desc);
+gd_status gd_backend_adamw_batch(gd_backend *backend, const gd_backend_adamw_desc *descs, uint32_t desc_count);
+
+/* ---- layout copies (:587-630); concat_to_full is used by multi-prompt prefill ---- */
+gd_status gd_backend_concat_to_full(gd_backend *backend, GDB_TV src, GDB_TV dst, const gd_backend_concat_args *args);
+gd_status gd_backend_concat_from_full(gd_backend *backend, GDB_TV src, GDB_TV dst, const gd_backend_concat_args *args);
+gd_status gd_backend_split_from_full(gd_backend *backend, GDB_TV full, GDB_TV slice, const gd_backend_split_args *args);
+gd_status gd_backend_split_to_full(gd_backend *backend, GDB_TV slice, GDB_TV full, const gd_backend_split_args *args);
+gd_status gd_backend_permute(gd_backend *backend, GDB_TV src, GDB_TV dst, const gd_backend_permute_args *args);
+
+/* ---- entries off the gpt_lm path: always GD_ERR_UNSUPPORTED (as src/backends/null/backend_null.c) ---- */
+gd_status gd_backend_reduce_contiguous(gd_backend *backend, GDB_TV src, GDB_TV dst, float scale);
+gd_status gd_backend_reduce_axis(gd_backend *backend, GDB_TV src, GDB_TV dst, uint32_t axis, float scale);
+gd_status gd_backend_broadcast_axis(gd_backend *backend, GDB_TV src, GDB_TV dst, uint32_t axis, float scale);
+gd_status gd_backend_broadcast_to(gd_backend *backend, GDB_TV src, GDB_TV dst, float scale);
+gd_status gd_backend_broadcast_scalar(gd_backend *backend, GDB_TV src, GDB_TV dst, float scale);
+gd_status gd_backend_reduce_broadcast(gd_backend *backend, GDB_TV src, GDB_TV dst, float scale);
+gd_status gd_backend_sigmoid_backward_from_output(gd_backend *backend, GDB_TV sigmoid_out, GDB_TV grad_out, GDB_TV grad_x);
+gd_status gd_backend_tanh_backward_from_output(gd_backend *backend, GDB_TV tanh_out, GDB_TV grad_out, GDB_TV grad_x);
+gd_status gd_backend_mul_backward_direct(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV grad_out, GDB_TV grad_x, GDB_TV grad_y);
+gd_status gd_backend_mul_reduce_suffix(gd_backend *backend, GDB_TV grad_out, GDB_TV other, GDB_TV dst);
+gd_status gd_backend_mse_forward(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV out, uint64_t chunk_size, float scale);
+gd_status gd_backend_mse_backward(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV grad_out, GDB_TV grad_x, GDB_TV grad_y, float scale);
+gd_status gd_backend_huber_forward(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV out, uint64_t chunk_size, float scale, float delta);
+gd_status gd_backend_huber_backward(gd_backend *backend, GDB_TV x, GDB_TV y, GDB_TV grad_out, GDB_TV grad_x, GDB_TV grad_y, float scale, float delta);
+gd_status gd_backend_powlu_forward(gd_backend *backend, GDB_TV x1, GDB_TV x2, GDB_TV out, float m);
+gd_status gd_backend_powlu_backward(gd_backend *backend, GDB_TV x1, GDB_TV x2, GDB_TV grad_out, GDB_TV grad_x1, GDB_TV grad_x2, float m);
+gd_status gd_backend_powlu_split_forward(gd_backend *backend, GDB_TV x12, GDB_TV out, float m);
+gd_status gd_backend_powlu_split_backward(gd_backend *backend, GDB_TV x12, GDB_TV grad_out, GDB_TV grad_x12, float m);
+gd_status gd_backend_minimax_m3_index_topk(gd_backend *backend, GDB_TV index_q, GDB_TV index_k, GDB_TV cu_seqlens, GDB_TV topk_idx, const gd_backend_minimax_m3_sparse_args *args);
+gd_status gd_backend_minimax_m3_sparse_attention(gd_backend *backend, GDB_TV q, GDB_TV k, GDB_TV v, GDB_TV cu_seqlens, GDB_TV topk_idx, GDB_TV out, const gd_backend_minimax_m3_sparse_args *args);
+gd_status gd_backend_minimax_m3_sparse_attention_backward(gd_backend *backend, GDB_TV grad_out, GDB_TV q, GDB_TV k, GDB_TV v, GDB_TV cu_seqlens, GDB_TV topk_idx, GDB_TV grad_q, GDB_TV grad_k, GDB_TV grad_v, GDB_TV stats, const gd_backend_minimax_m3_sparse_args *args);
+
+#undef GDB_TV
+#undef GDB_MV
+#undef GDB_BV
+#undef GDB_VV
+
+#endif /* !GD_CORE_BACKEND_H */
+
+/* ==================================================================================
+ * Additive entry points (no counterpart in the reference). The reference ABI links and
+ * runs without them; they exist for measurement, data parallelism and foreign-function
+ * callers that cannot hold the opaque structs.
+ * ================================================================================== */
+
+/* Raw device address of byte `offset` of a buffer (for ctypes/FFI tests and NCCL staging). */
+void *gdb200_buffer_device_ptr(gd_backend_buffer *buffer, size_t offset);
+/* The CUDA stream (cudaStream_t) every entry of this backend enqueues on. */
+void *gdb200_stream(gd_backend *backend);
+/* CUDA device ordinal the backend was created on (GD_CUDA_DEVICE, else LOCAL_RANK, else 0). */
+int gdb200_device(const gd_backend *backend);
+/* Number of kernel launches issued by this backend since creation (all entries). */
+uint64_t gdb200_launch_count(const gd_backend *backend);
+/* Last CUDA error string seen by the backend ("" if none); storage owned by the backend. */
+const char *gdb200_last_error(const gd_backend *backend);
+/* Select the GEMM implementation: 0 = automatic (tcgen05 when the shape/alignment allows,
+ * else the portable tiled kernel), 1 = force the portable kernel, 2 = require tcgen05 and
+ * fail with GD_ERR_UNSUPPORTED when it cannot run. Returns the previous value. */
+int gdb200_set_gemm_mode(gd_backend *backend, int mode);
+/* Event pair timing helper: records an event on the backend stream and returns an opaque
+ * handle; gdb200_event_elapsed_ms synchronises on `stop` and returns milliseconds. */
+void *gdb200_event_record(gd_backend *backend);
+float gdb200_event_elapsed_ms(void *start, void *stop);
+void gdb200_event_destroy(void *event);
+/* Write `nbytes` of zeros-then-ones pattern over a private >L2 buffer to evict L2. */
+gd_status gdb200_flush_l2(gd_backend *backend);
+
+/* Data-parallel gradient exchange (the reference has no collective; one process per GPU).
+ * id_bytes is the 128-byte ncclUniqueId produced by gdb200_dp_unique_id on rank 0. */
+gd_status gdb200_dp_unique_id(void *id_bytes_128);
+gd_status gdb200_dp_init(gd_backend *backend, const void *id_bytes_128, int rank, int world);
+/* In-place sum all-reduce of `count` elements of dtype (F16/BF16/F32) on the comm stream,
+ * ordered after everything already enqueued on the compute stream. */
+gd_status gdb200_dp_all_reduce(gd_backend *backend, gd_backend_buffer *buffer, size_t offset, size_t count, uint32_t dtype);
+/* Make the compute stream wait for all outstanding all-reduces. */
+gd_status gdb200_dp_join(gd_backend *backend);
+void gdb200_dp_shutdown(gd_backend *backend);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GD_BACKEND_B200_H */
