@@ -1,0 +1,389 @@
+"""gpt_lm: the decoder-only transformer of the reference's examples/gpt_lm, expressed over the
+op capsules of ops.py, with its training step and KV-cache prefill/decode.
+
+Follows examples/gpt_lm/gpt_lm_shared.c: gpt_block_forward :602-749, gpt_lm_forward :751-823,
+gpt_block_prefill_cached :825, gpt_block_decode_cached :961, dropout site seeds :724,747,788,
+parameter init :196-218,296-344 (normal, std 0.02, residual projections 0.02/sqrt(2L), norms 1,
+biases 0), weight-decay groups examples/gpt_lm/main.c:3374-3378, and the training step order
+of src/train/trainer.c:75-223. Model dimensions are run-time values here (the reference fixes
+them at compile time, gpt_lm_shared.h:10-28).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+
+from . import abi, ops
+from .abi import F16, BF16, F32, I32
+from .optim import AdamW, AdamwConfig, AmpConfig, AmpScaler, gd_backward_amp
+from .runtime import Context, Tensor
+
+MASK64 = (1 << 64) - 1
+GPT_DROPOUT_EMBED = 0x9E3779B97F4A7C15
+GPT_DROPOUT_ATTN = 0xBF58476D1CE4E5B9
+GPT_DROPOUT_MLP = 0x94D049BB133111EB
+GPT_DEFAULT_SEED = 0x6750746C6D5EED00
+
+
+def splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & MASK64
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & MASK64
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & MASK64
+    return x ^ (x >> 31)
+
+
+@dataclass
+class GptConfig:
+    vocab_size: int = 2048
+    context_length: int = 512
+    d_model: int = 512
+    n_layers: int = 3
+    n_heads: int = 8
+    head_dim: int = 64
+    mlp_hidden: int = 1024          # reference: 2 * d_model (gpt_lm_shared.h:28)
+    tied_lm_head: bool = True       # reference ties the LM head to the embedding (gpt_lm_shared.c:393-396)
+    dropout_p: float = 0.05
+    logits_softcap: float = 30.0
+    sdpa_window: int = 256
+    rms_eps: float = 1.0e-5
+    pad_token_id: int = -1          # ignore_index passed to the loss
+    dtype: int = F16
+    dropout_seed: int = GPT_DEFAULT_SEED
+    rope_theta: float = 10000.0
+
+    @staticmethod
+    def reference_default() -> "GptConfig":
+        return GptConfig()
+
+    @staticmethod
+    def baseline() -> "GptConfig":
+        """The benchmark configuration: SwiGLU hidden 1536, untied biased LM head, dropout 0.1,
+        no sliding window."""
+        return GptConfig(mlp_hidden=1536, tied_lm_head=False, dropout_p=0.1, sdpa_window=0)
+
+    @staticmethod
+    def scaled() -> "GptConfig":
+        return GptConfig(vocab_size=32768, context_length=2048, d_model=2048, n_layers=24, n_heads=16, head_dim=128,
+                         mlp_hidden=5632, tied_lm_head=False, dropout_p=0.1, sdpa_window=0, dtype=BF16)
+
+
+def param_specs(cfg: GptConfig) -> list[tuple[str, tuple[int, ...], str]]:
+    """(name, shape, kind) in registration order; kind is one of normal / residual / ones / zeros."""
+    d, f = cfg.d_model, cfg.mlp_hidden
+    specs = [("token_embedding", (cfg.vocab_size, d), "normal")]
+    for i in range(cfg.n_layers):
+        p = f"blocks.{i}."
+        specs += [
+            (p + "attn_norm_w", (d,), "ones"),
+            (p + "qkv_proj.weight", (3 * d, d), "normal"), (p + "qkv_proj.bias", (3 * d,), "zeros"),
+            (p + "attn_proj.weight", (d, d), "residual"), (p + "attn_proj.bias", (d,), "zeros"),
+            (p + "mlp_norm_w", (d,), "ones"),
+            (p + "up_gate.weight", (2 * f, d), "normal"), (p + "up_gate.bias", (2 * f,), "zeros"),
+            (p + "down_proj.weight", (f, d), "residual"), (p + "down_proj.bias", (d,), "zeros"),
+        ]
+    specs.append(("final_norm_w", (d,), "ones"))
+    if not cfg.tied_lm_head:
+        specs.append(("lm_head.weight", (cfg.vocab_size, d), "normal"))
+    specs.append(("lm_head_bias", (cfg.vocab_size,), "zeros"))
+    return specs
+
+
+def init_params(cfg: GptConfig, seed: int = 0, residual_scaled: bool = True) -> dict[str, np.ndarray]:
+    """Host-side initial weights as float32 arrays already rounded to the storage dtype grid."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name, shape, kind in param_specs(cfg):
+        if kind == "ones":
+            a = np.ones(shape, dtype=np.float32)
+        elif kind == "zeros":
+            a = np.zeros(shape, dtype=np.float32)
+        else:
+            std = 0.02 / math.sqrt(2.0 * cfg.n_layers) if (kind == "residual" and residual_scaled) else 0.02
+            a = (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
+        out[name] = round_to_storage(a, cfg.dtype)
+    return out
+
+
+def round_to_storage(a: np.ndarray, dtype: int) -> np.ndarray:
+    if dtype == F16:
+        return a.astype(np.float16).astype(np.float32)
+    if dtype == BF16:
+        from .runtime import bf16_bits_from_f32, f32_from_bf16_bits
+        return f32_from_bf16_bits(bf16_bits_from_f32(a)).reshape(a.shape)
+    return a.astype(np.float32)
+
+
+@dataclass
+class Batch:
+    """One packed training batch on the host: token ids, next-token targets (ignored rows hold
+    pad_token_id or -1), positions restarting per segment, and cu_seqlens."""
+    input_ids: np.ndarray
+    targets: np.ndarray
+    positions: np.ndarray
+    cu_seqlens: np.ndarray
+    real_tokens: int = 0
+
+    @property
+    def h2d_bytes(self) -> int:
+        return int(self.input_ids.nbytes + self.targets.nbytes + self.positions.nbytes + self.cu_seqlens.nbytes)
+
+
+def synthetic_batch(cfg: GptConfig, n_seqs: int, min_len: int, max_len: int, seed: int, pad_to: int = 0) -> Batch:
+    """Packed sequences with lengths uniform in [min_len, max_len] and ids uniform over the
+    vocabulary. The target of the last token of every sequence is ignored (-1). When pad_to > 0
+    the stream is padded with one fully ignored segment up to a multiple of pad_to rows
+    (the reference rejects token counts that are not a multiple of the context length,
+    gpt_lm_shared.c:776)."""
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(min_len, max_len + 1, size=n_seqs)
+    ids, tgt, pos, cu = [], [], [], [0]
+    for n in lens:
+        n = int(n)
+        s = rng.integers(0, cfg.vocab_size, size=n, dtype=np.int64).astype(np.int32)
+        t = np.empty(n, dtype=np.int32)
+        t[:-1] = s[1:]
+        t[-1] = -1
+        ids.append(s)
+        tgt.append(t)
+        pos.append(np.arange(n, dtype=np.int32))
+        cu.append(cu[-1] + n)
+    real = cu[-1]
+    if pad_to > 0 and real % pad_to != 0:
+        pad = pad_to - real % pad_to
+        while pad > 0:  # padding segments never exceed the context length
+            n = min(pad, cfg.context_length)
+            ids.append(np.zeros(n, dtype=np.int32))
+            tgt.append(np.full(n, -1, dtype=np.int32))
+            pos.append(np.arange(n, dtype=np.int32))
+            cu.append(cu[-1] + n)
+            pad -= n
+    return Batch(np.concatenate(ids), np.concatenate(tgt), np.concatenate(pos), np.asarray(cu, dtype=np.int32), real)
+
+
+class GptLm:
+    def __init__(self, ctx: Context, cfg: GptConfig, host_params: Optional[dict[str, np.ndarray]] = None, seed: int = 0):
+        assert cfg.n_heads * cfg.head_dim == cfg.d_model
+        self.ctx, self.cfg = ctx, cfg
+        self.training = True
+        host_params = host_params if host_params is not None else init_params(cfg, seed)
+        self.params: dict[str, Tensor] = {}
+        self.weight_decay_mask: dict[str, bool] = {}
+        for name, shape, _ in param_specs(cfg):
+            t = ctx.from_numpy(ctx.params, cfg.dtype, host_params[name].reshape(shape), name)
+            t.requires_grad = True
+            t.is_leaf = True
+            self.params[name] = t
+            self.weight_decay_mask[name] = not (name.endswith("norm_w") or name.endswith("bias"))
+        self.k_cache: list[Tensor] = []
+        self.v_cache: list[Tensor] = []
+
+    # ---- parameters ----
+    def param_list(self) -> list[Tensor]:
+        return list(self.params.values())
+
+    def lm_head_weight(self) -> Tensor:
+        return self.params["token_embedding"] if self.cfg.tied_lm_head else self.params["lm_head.weight"]
+
+    def n_params(self) -> int:
+        return sum(t.count for t in self.params.values())
+
+    def make_optimizer(self, config: AdamwConfig) -> AdamW:
+        names = list(self.params.keys())
+        wds = [config.weight_decay if self.weight_decay_mask[n] else 0.0 for n in names]
+        return AdamW(self.ctx, [self.params[n] for n in names], config, wds)
+
+    # ---- forward ----
+    def _site_seed(self, site: int, layer: int, step: int) -> int:
+        return splitmix64((self.cfg.dropout_seed ^ site ^ ((layer << 32) & MASK64) ^ step) & MASK64)
+
+    def block_forward(self, i: int, x: Tensor, positions: Tensor, cu_seqlens: Tensor, step: int) -> Tensor:
+        ctx, cfg, p = self.ctx, self.cfg, self.params
+        pre = f"blocks.{i}."
+        normed = ops.gd_rms_norm(ctx, x, p[pre + "attn_norm_w"], cfg.rms_eps)
+        qkv = ops.gd_linear_transposed_weight(ctx, normed, p[pre + "qkv_proj.weight"], p[pre + "qkv_proj.bias"])
+        q, k, v = ops.gd_qkv_split_rope(ctx, qkv, positions, cfg.n_heads, cfg.head_dim, cfg.rope_theta)
+        attn = ops.gd_sdpa_varlen(ctx, q, k, v, cu_seqlens, causal=True, sliding_window=cfg.sdpa_window,
+                                  max_seqlen=cfg.context_length)
+        attn_flat = attn.reshape((attn.shape[0], cfg.d_model))
+        attn_flat.requires_grad = attn.requires_grad
+        if attn.requires_grad:
+            def reshape_backward():
+                if attn_flat.grad is not None:
+                    ctx.accumulate_grad(attn, attn_flat.grad.reshape(attn.shape))
+            ctx.record(reshape_backward)
+        proj = ops.gd_linear_transposed_weight(ctx, attn_flat, p[pre + "attn_proj.weight"], p[pre + "attn_proj.bias"])
+        resid = ops.gd_dropout_add(ctx, x, proj, cfg.dropout_p, self.training, self._site_seed(GPT_DROPOUT_ATTN, i, step))
+        normed2 = ops.gd_rms_norm(ctx, resid, p[pre + "mlp_norm_w"], cfg.rms_eps)
+        up_gate = ops.gd_linear_transposed_weight(ctx, normed2, p[pre + "up_gate.weight"], p[pre + "up_gate.bias"])
+        mlp = ops.gd_swiglu_split_linear(ctx, up_gate, p[pre + "down_proj.weight"], p[pre + "down_proj.bias"])
+        return ops.gd_dropout_add(ctx, resid, mlp, cfg.dropout_p, self.training, self._site_seed(GPT_DROPOUT_MLP, i, step))
+
+    def forward(self, input_ids: Tensor, target_ids: Tensor, positions: Tensor, cu_seqlens: Tensor, step: int) -> Tensor:
+        """gpt_lm_forward: returns the scalar F32 mean loss tensor."""
+        ctx, cfg, p = self.ctx, self.cfg, self.params
+        x = ops.gd_embedding(ctx, p["token_embedding"], input_ids)
+        x = ops.gd_dropout(ctx, x, cfg.dropout_p, self.training, splitmix64((cfg.dropout_seed ^ GPT_DROPOUT_EMBED ^ step) & MASK64))
+        for i in range(cfg.n_layers):
+            x = self.block_forward(i, x, positions, cu_seqlens, step)
+        final = ops.gd_rms_norm(ctx, x, p["final_norm_w"], cfg.rms_eps)
+        return ops.gd_lm_cross_entropy_softcapped_bias_ignore(ctx, final, self.lm_head_weight(), p["lm_head_bias"], target_ids,
+                                                              cfg.logits_softcap, cfg.pad_token_id)
+
+    def upload_batch(self, batch: Batch):
+        ctx = self.ctx
+        return (ctx.from_numpy(ctx.data, I32, batch.input_ids, "input_ids"),
+                ctx.from_numpy(ctx.data, I32, batch.targets, "targets"),
+                ctx.from_numpy(ctx.data, I32, batch.positions, "positions"),
+                ctx.from_numpy(ctx.data, I32, batch.cu_seqlens, "cu_seqlens"))
+
+    # ---- KV-cache generation ----
+    def alloc_kv_cache(self, batch: int, capacity: int) -> None:
+        cfg, ctx = self.cfg, self.ctx
+        self.k_cache = [ctx.zeros(ctx.state, cfg.dtype, (batch, capacity, cfg.n_heads, cfg.head_dim), f"k_cache.{i}") for i in range(cfg.n_layers)]
+        self.v_cache = [ctx.zeros(ctx.state, cfg.dtype, (batch, capacity, cfg.n_heads, cfg.head_dim), f"v_cache.{i}") for i in range(cfg.n_layers)]
+
+    def _mlp_infer(self, pre: str, resid: Tensor) -> Tensor:
+        ctx, cfg, p = self.ctx, self.cfg, self.params
+        normed2 = ops.gd_rms_norm(ctx, resid, p[pre + "mlp_norm_w"], cfg.rms_eps)
+        up_gate = ops.gd_linear_transposed_weight(ctx, normed2, p[pre + "up_gate.weight"], p[pre + "up_gate.bias"])
+        mlp = ops.gd_swiglu_split_linear(ctx, up_gate, p[pre + "down_proj.weight"], p[pre + "down_proj.bias"])
+        return ops.gd_add(ctx, resid, mlp)
+
+    def prefill_last_logits(self, input_ids: Tensor, positions: Tensor, cu_seqlens: Tensor, cache_pos: Tensor,
+                            last_rows: np.ndarray) -> Tensor:
+        """Packed prefill that fills the caches and returns logits [B, V] of the last row of each prompt
+        (gpt_lm_shared.c:1117-1202)."""
+        ctx, cfg, p = self.ctx, self.cfg, self.params
+        prev = ctx.grad_enabled
+        ctx.grad_enabled = False
+        try:
+            x = ops.gd_embedding(ctx, p["token_embedding"], input_ids)
+            for i in range(cfg.n_layers):
+                pre = f"blocks.{i}."
+                normed = ops.gd_rms_norm(ctx, x, p[pre + "attn_norm_w"], cfg.rms_eps)
+                qkv = ops.gd_linear_transposed_weight(ctx, normed, p[pre + "qkv_proj.weight"], p[pre + "qkv_proj.bias"])
+                q, k, v = ops.gd_qkv_split_rope(ctx, qkv, positions, cfg.n_heads, cfg.head_dim, cfg.rope_theta)
+                ops.gd_kv_cache_append_packed(ctx, self.k_cache[i], self.v_cache[i], cache_pos, cu_seqlens, k, v)
+                attn = ops.gd_sdpa_varlen(ctx, q, k, v, cu_seqlens, causal=True, sliding_window=cfg.sdpa_window, max_seqlen=cfg.context_length)
+                proj = ops.gd_linear_transposed_weight(ctx, attn.reshape((attn.shape[0], cfg.d_model)), p[pre + "attn_proj.weight"], p[pre + "attn_proj.bias"])
+                resid = ops.gd_add(ctx, x, proj)
+                x = self._mlp_infer(pre, resid)
+            # gather the last row of each prompt: slice + concat_to_full per prompt
+            b = len(last_rows)
+            gathered = ctx.scratch_empty(cfg.dtype, (b, cfg.d_model), "last_rows")
+            for j, r in enumerate(last_rows):
+                args = abi.ConcatArgs(cfg.d_model, cfg.d_model, 1, b, j)
+                src = x.rows(int(r), 1)
+                ctx.check(ctx.lib.gd_backend_concat_to_full(ctx.backend, ops._tvp(src), ops._tvp(gathered), ops.byref(args)), "concat_to_full")
+            final = ops.gd_rms_norm(ctx, gathered, p["final_norm_w"], cfg.rms_eps)
+            return ops.gd_linear_transposed_weight(ctx, final, self.lm_head_weight(), p["lm_head_bias"])
+        finally:
+            ctx.grad_enabled = prev
+
+    def decode_logits(self, input_ids: Tensor, positions: Tensor, cache_pos: Tensor) -> Tensor:
+        """One decode step for B sequences: ids [B], positions [B], cache_pos [B] -> logits [B, V]
+        (gpt_lm_shared.c:961-1115,1204-1246)."""
+        ctx, cfg, p = self.ctx, self.cfg, self.params
+        prev = ctx.grad_enabled
+        ctx.grad_enabled = False
+        try:
+            b = input_ids.count
+            x = ops.gd_embedding(ctx, p["token_embedding"], input_ids)
+            for i in range(cfg.n_layers):
+                pre = f"blocks.{i}."
+                normed = ops.gd_rms_norm(ctx, x, p[pre + "attn_norm_w"], cfg.rms_eps)
+                qkv = ops.gd_linear_transposed_weight(ctx, normed, p[pre + "qkv_proj.weight"], p[pre + "qkv_proj.bias"])
+                q, k, v = ops.gd_qkv_split_rope(ctx, qkv, positions, cfg.n_heads, cfg.head_dim, cfg.rope_theta)
+                shape4 = (b, 1, cfg.n_heads, cfg.head_dim)
+                ops.gd_kv_cache_append_positions(ctx, self.k_cache[i], self.v_cache[i], cache_pos, k.reshape(shape4), v.reshape(shape4))
+                attn = ops.gd_sdpa_decode_positions(ctx, q.reshape(shape4), self.k_cache[i], self.v_cache[i], cache_pos,
+                                                    sliding_window=cfg.sdpa_window)
+                proj = ops.gd_linear_transposed_weight(ctx, attn.reshape((b, cfg.d_model)), p[pre + "attn_proj.weight"], p[pre + "attn_proj.bias"])
+                resid = ops.gd_add(ctx, x, proj)
+                x = self._mlp_infer(pre, resid)
+            final = ops.gd_rms_norm(ctx, x, p["final_norm_w"], cfg.rms_eps)
+            return ops.gd_linear_transposed_weight(ctx, final, self.lm_head_weight(), p["lm_head_bias"])
+        finally:
+            ctx.grad_enabled = prev
+
+
+@dataclass
+class TrainConfig:
+    lr: float = 3.0e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1.0e-8
+    weight_decay: float = 1.0e-4
+    grad_clip_norm: float = 1.0
+    amp: AmpConfig = field(default_factory=AmpConfig)
+
+    @staticmethod
+    def baseline() -> "TrainConfig":
+        return TrainConfig(weight_decay=0.1, amp=AmpConfig(init_scale=65536.0))
+
+
+class Trainer:
+    """gd_train_batch: begin_step -> loss_fn -> backward_amp -> optimizer step -> end_step."""
+
+    def __init__(self, model: GptLm, cfg: TrainConfig, dp=None):
+        self.model, self.cfg, self.ctx = model, cfg, model.ctx
+        self.optimizer = model.make_optimizer(AdamwConfig(cfg.lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, True))
+        self.scaler = AmpScaler(self.ctx, cfg.amp)
+        self.global_step = 0
+        self.dp = dp
+
+    def train_batch(self, batch: Batch, lr: Optional[float] = None) -> Tensor:
+        ctx, model = self.ctx, self.model
+        ctx.begin_step()
+        self.optimizer.zero_grad()
+        ids, tgt, pos, cu = model.upload_batch(batch)
+        loss = model.forward(ids, tgt, pos, cu, self.global_step + 1)
+        gd_backward_amp(ctx, loss, self.scaler)
+        inv_override = None
+        if self.dp is not None:
+            inv_override = self.dp.reduce_gradients(self.optimizer, self.scaler)
+        self.optimizer.step_amp_clip_lr(self.scaler, self.cfg.lr if lr is None else lr, self.cfg.grad_clip_norm, inv_override)
+        ctx.end_step()
+        self.global_step += 1
+        return loss
+
+
+def greedy_generate(model: GptLm, prompts: np.ndarray, new_tokens: int, capacity: int) -> np.ndarray:
+    """Batched greedy KV-cache generation: packed prefill, then `new_tokens` decode steps with
+    host argmax (first maximum wins, soft cap applied on the host as gpt_lm_shared.c:1322,1388-1398)."""
+    ctx, cfg = model.ctx, model.cfg
+    b, plen = prompts.shape
+    model.alloc_kv_cache(b, capacity)
+    out = np.zeros((b, new_tokens), dtype=np.int32)
+    ctx.begin_step()
+    ids = ctx.from_numpy(ctx.data, I32, prompts.reshape(-1).astype(np.int32))
+    pos = ctx.from_numpy(ctx.data, I32, np.tile(np.arange(plen, dtype=np.int32), b))
+    cu = ctx.from_numpy(ctx.data, I32, (np.arange(b + 1, dtype=np.int32) * plen))
+    cpos = ctx.from_numpy(ctx.data, I32, np.zeros(b, dtype=np.int32))
+    logits = model.prefill_last_logits(ids, pos, cu, cpos, np.arange(b) * plen + plen - 1)
+    ctx.end_step()
+    nxt = host_argmax(logits.read_f32(), cfg.logits_softcap)
+    for t in range(new_tokens):
+        out[:, t] = nxt
+        if t == new_tokens - 1:
+            break
+        ctx.begin_step()
+        cur = plen + t
+        ids = ctx.from_numpy(ctx.data, I32, nxt.astype(np.int32))
+        pos = ctx.from_numpy(ctx.data, I32, np.full(b, cur, dtype=np.int32))
+        cpos = ctx.from_numpy(ctx.data, I32, np.full(b, cur, dtype=np.int32))
+        logits = model.decode_logits(ids, pos, cpos)
+        ctx.end_step()
+        nxt = host_argmax(logits.read_f32(), cfg.logits_softcap)
+    return out
+
+
+def host_argmax(logits: np.ndarray, softcap: float) -> np.ndarray:
+    x = logits.astype(np.float32)
+    if softcap > 0.0:
+        x = np.float32(softcap) * np.tanh(x / np.float32(softcap))
+    x = np.where(np.isfinite(x), x, -np.inf)
+    return np.argmax(x, axis=1).astype(np.int32)  # numpy argmax returns the first maximum

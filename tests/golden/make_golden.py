@@ -1,0 +1,210 @@
+"""Generates the committed golden fixtures under tests/golden/ from the REFERENCE's own code.
+
+Run in a container that has the reference tree (default /root/reference) and after
+`python -c "import __graft_entry__ as g; g.build()"` (which builds oracle/_ref/ref_harness.so):
+
+    python tests/golden/make_golden.py [--ref /root/reference]
+
+Sources of truth (nothing is re-derived from this repository's oracle):
+  * CPU reference functions that the reference's C tests carry (tests/test_sdpa_varlen.c:122-371,
+    599-677; tests/test_lm_cross_entropy.c:141-296; tests/test_rope.c:67-103;
+    tests/test_rms_norm.c:56-105), compiled from the reference tree into oracle/_ref/ref_harness.so,
+    on the tests' own deterministic pattern inputs and case shapes.
+  * The reference-side functions of the reference's PyTorch oracle scripts, imported from the
+    reference tree: src/ops/rms_norm/{fwd,bwd}.py (make_inputs, reference), src/ops/dropout/fwd.py
+    (case_input, dropout_mask, ref_dropout). src/ops/linear/{fwd,bwd}.py compute their reference
+    inline in run_case (fwd.py:147-156, bwd.py:171-190); those lines are transcribed here.
+  * Closed-form expectations of tests/test_optim.c:197-211,228-229,293,313,363-372 and the
+    schedule points of tests/test_optim.c:50-61.
+The fixtures are small .npz files; tests/test_oracle_golden.py checks oracle/ against them on CPU
+and tests/test_gpu_golden.py checks the CUDA backend against them on a B200.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import cref  # noqa: E402
+
+
+def load_script(ref: str, rel: str, name: str):
+    sys.path.insert(0, ref)
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ref, rel))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def sdpa_cases(h: cref.RefHarness) -> dict:
+    out = {}
+    # (name, N, Hq, Hkv, Dh, cu, window, prefix): the shapes of tests/test_sdpa_varlen.c:373-597
+    cases = [("n5_gqa_dh4", 5, 2, 1, 4, [0, 2, 5], 0, 0),
+             ("n160_dh64_w8_p4", 160, 2, 1, 64, [0, 64, 160], 8, 4),
+             ("n160_dh64_w8_p0", 160, 2, 1, 64, [0, 64, 160], 8, 0),
+             ("n520_dh64_w32", 520, 1, 1, 64, [0, 520], 32, 0),
+             ("n96_dh64_causal", 96, 4, 2, 64, [0, 17, 40, 96], 0, 0)]
+    for name, n, hq, hkv, dh, cu, win, pre in cases:
+        cu = np.asarray(cu, dtype=np.int32)
+        q = h.fill_tokens(n * hq * dh, -0.2)
+        k = h.fill_tokens(n * hkv * dh, 0.1)
+        v = h.fill_tokens(n * hkv * dh, -0.05)
+        go = h.fill_tokens(n * hq * dh, 0.02)
+        scale = float(np.float32(1.0 / np.sqrt(np.float64(dh))))
+        fwd = h.varlen_fwd(q, k, v, cu, hq, hkv, dh, scale, 1, win, pre)
+        dq, dk, dv = h.varlen_bwd(go, q, k, v, cu, hq, hkv, dh, scale, 1, win, pre)
+        out[name] = dict(q=q.reshape(n, hq, dh), k=k.reshape(n, hkv, dh), v=v.reshape(n, hkv, dh), go=go.reshape(n, hq, dh),
+                         cu=cu, window=win, prefix=pre, scale=np.float32(scale), out=fwd, dq=dq, dk=dk, dv=dv)
+    # decode (tests/test_sdpa_varlen.c:679-719 shape family): B1 Tq2 Tmax5 and a windowed Tq1 case
+    for name, b, tq, tmax, hq, hkv, dh, pos, win, pre in [("decode_b1_tq2", 1, 2, 5, 2, 1, 4, 2, 0, 0),
+                                                         ("decode_b2_tq1_w3", 2, 1, 9, 4, 2, 64, 6, 3, 0)]:
+        q = h.fill_tokens(b * tq * hq * dh, -0.1)
+        k = h.fill_tokens(b * tmax * hkv * dh, 0.07)
+        v = h.fill_tokens(b * tmax * hkv * dh, -0.03)
+        scale = float(np.float32(1.0 / np.sqrt(np.float64(dh))))
+        o = h.decode(q, k, v, pos, b, tq, tmax, hq, hkv, dh, scale, win, pre)
+        out[name] = dict(q=q.reshape(b, tq, hq, dh), k=k.reshape(b, tmax, hkv, dh), v=v.reshape(b, tmax, hkv, dh),
+                         cache_pos=np.int32(pos), window=win, prefix=pre, scale=np.float32(scale), out=o)
+    return out
+
+
+def lmce_cases(h: cref.RefHarness) -> dict:
+    out = {}
+    base = np.array([3, 17, 31, 0, 8, 22], dtype=np.int32)
+    ign = np.array([3, -1, 31, 0, -1, 22], dtype=np.int32)
+    for name, targets, cap, bias in [("cap0_nobias", base, 0.0, False), ("cap075_bias", base, 0.75, True),
+                                     ("cap30_bias_ignore", ign, 30.0, True), ("cap075_nobias_ignore", ign, 0.75, False)]:
+        r = h.lmce_case(targets, cap, bias)
+        out[name] = dict(hidden=r["hidden"], weight=r["weight"], bias=r["bias"], targets=targets, cap=np.float32(cap),
+                         has_bias=np.int32(bias), loss=np.float32(r["loss"]), dh=r["dh"], dw=r["dw"], db=r["db"])
+    return out
+
+
+def rope_rms_cases(h: cref.RefHarness) -> dict:
+    out = {}
+    rng = np.random.default_rng(7)
+    for name, shape, n_dims, inter in [("rope_half_full", (6, 2, 8), 8, False), ("rope_interleaved_tail", (5, 3, 10), 6, True),
+                                       ("rope_dh64", (37, 2, 64), 64, False)]:
+        x = rng.standard_normal(shape).astype(np.float32)
+        pos = (np.arange(shape[0]) * 3 % 11).astype(np.int32)
+        out[name] = dict(x=x, pos=pos, n_dims=np.int32(n_dims), interleaved=np.int32(inter), theta=np.float32(10000.0),
+                         fwd=h.rope(x, pos, 10000.0, n_dims, inter, 1.0), bwd=h.rope(x, pos, 10000.0, n_dims, inter, -1.0))
+    for name, rows, cols in [("rms_7x24", 7, 24), ("rms_33x512", 33, 512)]:
+        x = (rng.standard_normal((rows, cols)) * 0.5).astype(np.float32)
+        w = (rng.standard_normal(cols) * 0.25 + 1.0).astype(np.float32)
+        g = (rng.standard_normal((rows, cols)) * 0.25).astype(np.float32)
+        o, dx, dw = h.rms(x, w, g, 1.0e-5)
+        out[name] = dict(x=x, w=w, g=g, eps=np.float32(1.0e-5), out=o, dx=dx, dw=dw)
+    return out
+
+
+def script_cases(ref: str) -> dict:
+    out = {}
+    fwd = load_script(ref, "src/ops/rms_norm/fwd.py", "ref_rms_fwd")
+    bwd = load_script(ref, "src/ops/rms_norm/bwd.py", "ref_rms_bwd")
+    for case in fwd.cases():
+        x, w = fwd.make_inputs(case)
+        out["py_rms_fwd_" + case.name] = dict(x=x.numpy(), w=w.numpy(), eps=np.float32(case.eps), is_f16=np.int32(case.dtype == "f16"),
+                                              y=fwd.reference(case, x, w).numpy())
+    for case in bwd.cases():
+        x, w, g = bwd.make_inputs(case)
+        dx, dw = bwd.reference(case, x, w, g)
+        out["py_rms_bwd_" + case.name] = dict(x=x.numpy(), w=w.numpy(), g=g.numpy(), eps=np.float32(case.eps),
+                                              is_f16=np.int32(case.dtype == "f16"), dx=dx.numpy(), dw=dw.numpy())
+    dr = load_script(ref, "src/ops/dropout/fwd.py", "ref_dropout_fwd")
+    for case in dr.make_cases():
+        if not case.training:
+            continue
+        x = dr.case_input(case)
+        y = dr.ref_dropout(x, case)
+        mask = dr.dropout_mask(case.shape, case.p, case.seed).numpy().astype(np.uint8)
+        out["py_dropout_" + case.name] = dict(x=x.float().numpy(), p=np.float32(case.p), seed=np.uint64(case.seed),
+                                              is_f16=np.int32(case.dtype == "f16"), y=y.float().numpy(), mask=mask)
+    # linear forward / backward: reference lines transcribed (src/ops/linear/fwd.py:147-156, bwd.py:171-190)
+    for m, k, n, has_bias in [(4, 7, 6, True), (4, 7, 6, False), (64, 128, 96, True)]:
+        seed = 3000 + m * 3 + k * 5 + n * 7 + (11 if has_bias else 0)
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        x = (torch.randn(m, k, generator=gen, dtype=torch.float32) * 0.04).to(torch.float16)
+        w = (torch.randn(k, n, generator=gen, dtype=torch.float32) * 0.04).to(torch.float16)
+        b = (torch.randn(n, generator=gen, dtype=torch.float32) * 0.04).to(torch.float16)
+        ref = x.float() @ w.float()
+        if has_bias:
+            ref = ref + b.float()
+        ref = ref.to(torch.float16).float()
+        gy = (torch.randn(m, n, generator=gen, dtype=torch.float32) * 0.04).to(torch.float16)
+        dx = (gy.float() @ w.float().t()).to(torch.float16).float()
+        dw = (x.float().t() @ gy.float()).to(torch.float16).float()
+        db = gy.float().sum(dim=0).to(torch.float16).float()
+        out[f"py_linear_m{m}k{k}n{n}_{'bias' if has_bias else 'nobias'}"] = dict(
+            x=x.float().numpy(), w=w.float().numpy(), b=b.float().numpy(), has_bias=np.int32(has_bias), y=ref.numpy(),
+            gy=gy.float().numpy(), dx=dx.numpy(), dw=dw.numpy(), db=db.numpy())
+    return out
+
+
+def optim_cases() -> dict:
+    """Closed-form expectations restated from tests/test_optim.c (the test computes them inline)."""
+    f = np.float32
+    out = {}
+    # first AdamW step (test_optim.c:197-211,228-229): p0 = {1,2,3}, g0 = {0.1,-0.2,0.3}
+    p0, g0 = np.array([1, 2, 3], dtype=f), np.array([0.1, -0.2, 0.3], dtype=f)
+    lr, eps, wd = f(1.0e-2), f(1.0e-8), f(0.1)
+    m, v = g0, g0 * g0
+    upd = m / (np.sqrt(v, dtype=f) + eps)
+    out["adamw_first_step"] = dict(p0=p0, g0=g0, lr=lr, eps=eps, wd=wd, beta1=f(0.9), beta2=f(0.999),
+                                   want_f16=(p0 - lr * (upd + wd * p0)).astype(np.float16).view(np.uint16))
+    # clip case (test_optim.c:363-372): p0 = {1,2}, g0 = {3,4}, max_norm 0.5, lr 0.1, beta 0, eps 1, wd 0
+    p0, g0 = np.array([1, 2], dtype=f), np.array([3, 4], dtype=f)
+    clip = f(0.5) / (f(5.0) + f(1.0e-6))
+    cg = g0 * clip
+    want = p0 - f(0.1) * (cg / (np.abs(cg) + f(1.0)))
+    out["adamw_clip_step"] = dict(p0=p0, g0=g0, max_norm=f(0.5), lr=f(0.1), want_f16=want.astype(np.float16).view(np.uint16),
+                                  norm=f(5.0))
+    # lr schedule points (test_optim.c:50-61): max 1e-3, min 1e-4, warmup 10, total 110
+    steps = np.array([0, 5, 10, 60, 110, 500], dtype=np.int64)
+    vals = []
+    for s in steps:
+        if s < 10:
+            vals.append(1.0e-3 * s / 10)
+        else:
+            pr = min(1.0, (s - 10) / 100)
+            vals.append(1.0e-4 + 0.5 * (1.0e-3 - 1.0e-4) * (1.0 + np.cos(np.pi * pr)))
+    out["lr_schedule"] = dict(steps=steps, max_lr=f(1.0e-3), min_lr=f(1.0e-4), warmup=np.int64(10), total=np.int64(110),
+                              values=np.array(vals, dtype=f))
+    return out
+
+
+def save(group: str, cases: dict) -> None:
+    flat = {}
+    for cname, fields in cases.items():
+        for fname, val in fields.items():
+            flat[f"{cname}/{fname}"] = np.asarray(val)
+    path = os.path.join(HERE, group + ".npz")
+    np.savez_compressed(path, **flat)
+    print(f"{path}: {len(cases)} cases, {os.path.getsize(path)} bytes")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    if not cref.harness_available():
+        raise SystemExit("oracle/_ref/ref_harness.so is missing: run __graft_entry__.build() where the reference tree exists")
+    h = cref.RefHarness()
+    save("ref_ctest_sdpa", sdpa_cases(h))
+    save("ref_ctest_lmce", lmce_cases(h))
+    save("ref_ctest_rope_rms", rope_rms_cases(h))
+    save("ref_py_scripts", script_cases(args.ref))
+    save("ref_ctest_optim", optim_cases())
+
+
+if __name__ == "__main__":
+    main()
