@@ -1,0 +1,412 @@
+"""GPU parity: every backend entry on the gpt_lm path, called through the C ABI, against the CPU
+oracle on the same seeded inputs. Integer / mask / copy work is bit-exact; floating-point work
+is within gpu_util.TOL of the FP32 oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import BF16, F16, F32, I32, U8, abi, close, dev, host, pkg, rnd_np, storage_name
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+ops = pkg.ops
+byref = C.byref
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+def t32(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))
+
+
+# ------------------------------------------------------------------ memory primitives
+def test_fill_scale_accumulate_rand(step):
+    ctx = step
+    x = rnd_np(rng(0).standard_normal(1000 + 7).astype(np.float32), F16)
+    y = rnd_np(rng(1).standard_normal(1000 + 7).astype(np.float32), F16)
+    dx, dy = dev(ctx, x, F16), dev(ctx, y, F16)
+    ctx.check(ctx.lib.gd_backend_accumulate(ctx.backend, dx.buffer, dx.offset, dy.buffer, dy.offset, dx.count, F16), "acc")
+    assert np.array_equal(host(dx), rnd_np(x + y, F16))                      # one rounding per add: exact
+    out = ctx.scratch_empty(F16, x.shape)
+    ctx.check(ctx.lib.gd_backend_scale(ctx.backend, out.buffer, out.offset, dy.buffer, dy.offset, dy.count, F16, 0.375), "scale")
+    assert np.array_equal(host(out), rnd_np(y * np.float32(0.375), F16))
+    ctx.check(ctx.lib.gd_backend_scale(ctx.backend, out.buffer, out.offset, dy.buffer, dy.offset, dy.count, F16, 1.0), "scale1")
+    assert np.array_equal(host(out), y)
+    f = ctx.scratch_empty(F32, (33,))
+    ctx.fill(f, 0xFF800000)
+    assert np.all(np.isneginf(host(f)))
+    r = ctx.scratch_empty(F32, (4096,))
+    ctx.check(ctx.lib.gd_backend_rand_uniform(ctx.backend, r.buffer, r.offset, r.count, F32, 1234, -0.5, 1.5), "rand")
+    assert np.array_equal(host(r), O.rand_uniform(4096, 1234, -0.5, 1.5))    # integer hash + FP32 affine: exact
+
+
+@pytest.mark.parametrize("shape,bshape", [((64, 1536), (1536,)), ((5, 7), (7,)), ((3, 4, 6), (3, 4, 6)), ((3, 4, 6), (4, 1))])
+def test_add_broadcast(step, shape, bshape):
+    ctx = step
+    x = rnd_np(rng(2).standard_normal(shape).astype(np.float32), F16)
+    y = rnd_np(rng(3).standard_normal(bshape).astype(np.float32), F16)
+    out = ctx.scratch_empty(F16, shape)
+    ctx.check(ctx.lib.gd_backend_add(ctx.backend, byref(dev(ctx, x, F16).tv()), byref(dev(ctx, y, F16).tv()), byref(out.tv())), "add")
+    assert np.array_equal(host(out), rnd_np(x + y, F16))
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype,dim", [(F16, 512), (F16, 12), (F32, 8), (BF16, 64)])
+def test_embedding_forward_backward(step, dtype, dim):
+    ctx = step
+    vocab, n = 97, 301
+    table = rnd_np(rng(4).standard_normal((vocab, dim)).astype(np.float32), dtype)
+    ids = rng(5).integers(0, vocab, size=n).astype(np.int32)
+    ids[[3, 50]] = [-1, vocab]                                               # invalid ids
+    tt, it = dev(ctx, table, dtype), dev(ctx, ids, I32)
+    tt.requires_grad = True
+    out = ops.gd_embedding(ctx, tt, it)
+    got = host(out)
+    want = O.embedding_forward(t32(table), torch.from_numpy(ids)).numpy()
+    assert np.array_equal(np.isnan(got), np.isnan(want)) and np.array_equal(np.nan_to_num(got), np.nan_to_num(want))
+    g = rnd_np(rng(6).standard_normal((n, dim)).astype(np.float32), dtype)
+    out.grad = dev(ctx, g, dtype)
+    ctx.run_backward()
+    close(host(tt.grad), O.embedding_backward(t32(g), torch.from_numpy(ids), vocab, storage_name(dtype)), dtype, scale=4)
+
+
+# ------------------------------------------------------------------ dropout
+@pytest.mark.parametrize("dtype,n,p,seed", [(F16, 4096 * 16, 0.1, 0x1234567890ABCDEF), (F16, 513, 0.2, 2**64 - 5), (F32, 1000, 0.35, 42)])
+def test_dropout_family(step, dtype, n, p, seed):
+    ctx = step
+    x = rnd_np((rng(7).standard_normal(n) * 1.5).astype(np.float32), dtype)
+    res = rnd_np(rng(8).standard_normal(n).astype(np.float32), dtype)
+    xt = dev(ctx, x, dtype)
+    xt.requires_grad = True
+    y = ops.gd_dropout(ctx, xt, p, True, seed)
+    want_y, want_mask = O.dropout_forward(t32(x), p, seed, storage_name(dtype))
+    assert np.array_equal(host(y), want_y.numpy())                            # mask and values bit-exact
+    g = rnd_np(rng(9).standard_normal(n).astype(np.float32), dtype)
+    y.grad = dev(ctx, g, dtype)
+    ctx.run_backward()
+    assert np.array_equal(host(xt.grad), O.dropout_backward_mask(want_mask, t32(g), 1.0 / (1.0 - p), storage_name(dtype)).numpy())
+    # recompute-from-seed backward
+    dx = ctx.scratch_empty(dtype, (n,))
+    ctx.check(ctx.lib.gd_backend_dropout_backward(ctx.backend, byref(dev(ctx, g, dtype).tv()), byref(dx.tv()), p, seed), "dropout_backward")
+    assert np.array_equal(host(dx), host(xt.grad))
+    if dtype == F16:
+        rt, x2 = dev(ctx, res, dtype), dev(ctx, x, dtype)
+        y2 = ops.gd_dropout_add(ctx, rt, x2, p, True, seed)
+        want2, _ = O.dropout_add_forward(t32(res), t32(x), p, seed, "f16")
+        assert np.array_equal(host(y2), want2.numpy())
+
+
+# ------------------------------------------------------------------ rms_norm
+@pytest.mark.parametrize("dtype,rows,cols", [(F16, 777, 512), (F16, 33, 24), (BF16, 130, 2048), (F32, 9, 17)])
+def test_rms_norm(step, dtype, rows, cols):
+    ctx = step
+    x = rnd_np((rng(10).standard_normal((rows, cols)) * 0.5).astype(np.float32), dtype)
+    w = rnd_np((rng(11).standard_normal(cols) * 0.25 + 1).astype(np.float32), dtype)
+    g = rnd_np((rng(12).standard_normal((rows, cols)) * 0.25).astype(np.float32), dtype)
+    xt, wt = dev(ctx, x, dtype), dev(ctx, w, dtype)
+    xt.requires_grad = wt.requires_grad = True
+    y = ops.gd_rms_norm(ctx, xt, wt, 1e-5)
+    wy, winv = O.rms_norm_forward(t32(x), t32(w), 1e-5, storage_name(dtype))
+    close(host(y), wy, dtype)
+    y.grad = dev(ctx, g, dtype)
+    ctx.run_backward()
+    wdx, wdw = O.rms_norm_backward(t32(x), t32(w), winv, t32(g), storage_name(dtype))
+    close(host(xt.grad), wdx, dtype)
+    close(host(wt.grad), wdw, dtype, scale=8)
+    # non-stats entries
+    args = ops._rms_args(rows, cols, 1e-5)
+    inv = ctx.scratch_empty(F32, (rows,))
+    ctx.check(ctx.lib.gd_backend_rms_norm_inv(ctx.backend, byref(xt.tv()), byref(inv.tv()), byref(args)), "rms_inv")
+    np.testing.assert_allclose(host(inv), winv.numpy(), rtol=2e-6)
+    dx2 = ctx.scratch_empty(dtype, (rows, cols))
+    ctx.check(ctx.lib.gd_backend_rms_norm_backward(ctx.backend, byref(xt.tv()), byref(wt.tv()), byref(dev(ctx, g, dtype).tv()), byref(dx2.tv()), byref(args)), "rms_bwd")
+    close(host(dx2), wdx, dtype)
+
+
+# ------------------------------------------------------------------ GEMM family
+GEMM_SHAPES = [(5, 3, 7), (64, 128, 96), (300, 512, 1536), (257, 520, 130)]
+
+
+@pytest.mark.parametrize("dtype", [F16, BF16])
+@pytest.mark.parametrize("m,k,n", GEMM_SHAPES)
+def test_matmul_family(step, dtype, m, k, n):
+    ctx, lib = step, step.lib
+    sd = storage_name(dtype)
+    a = rnd_np((rng(13).standard_normal((m, k)) * 0.5).astype(np.float32), dtype)
+    b = rnd_np((rng(14).standard_normal((k, n)) * 0.5).astype(np.float32), dtype)
+    bias = rnd_np(rng(15).standard_normal(n).astype(np.float32), dtype)
+    want = t32(a) @ t32(b)
+    sc = np.sqrt(k) / 4
+    at, bt, btt, att = dev(ctx, a, dtype), dev(ctx, b, dtype), dev(ctx, b.T.copy(), dtype), dev(ctx, a.T.copy(), dtype)
+    y = ctx.scratch_empty(dtype, (m, n))
+    for name, fn, xv, wv in (("matmul", lib.gd_backend_matmul, at.mv(m, k), bt.mv(k, n)),
+                             ("matmul_nt", lib.gd_backend_matmul_nt, at.mv(m, k), btt.mv(n, k)),
+                             ("matmul_tn", lib.gd_backend_matmul_tn, att.mv(k, m), bt.mv(k, n))):
+        ctx.fill(y, 0)
+        yv = y.mv(m, n)
+        ctx.check(fn(ctx.backend, byref(xv), byref(wv), byref(yv)), name)
+        close(host(y), O.rnd(want, sd), dtype, scale=sc, what=name)
+    bv, yv, xv, wv = dev(ctx, bias, dtype).vv(), y.mv(m, n), at.mv(m, k), bt.mv(k, n)
+    ctx.check(lib.gd_backend_linear(ctx.backend, byref(xv), byref(wv), byref(bv), byref(yv)), "linear")
+    close(host(y), O.linear_forward(t32(a), t32(b), t32(bias), sd), dtype, scale=sc, what="linear")
+    red = ctx.scratch_empty(dtype, (k,))
+    rv, xv = red.vv(), at.mv(m, k)
+    ctx.check(lib.gd_backend_reduce_rows(ctx.backend, byref(xv), byref(rv)), "reduce_rows")
+    close(host(red), O.rnd(t32(a).sum(dim=0), sd), dtype, scale=np.sqrt(m) / 2, what="reduce_rows")
+
+
+def test_matmul_row_strided_views(step):
+    """Weight chunks are passed as row-sliced views and outputs may be strided (LM-CE chunking)."""
+    ctx, lib = step, step.lib
+    m, k, n, n_total = 40, 64, 24, 80
+    a = rnd_np(rng(16).standard_normal((m, k)).astype(np.float32), F16)
+    w = rnd_np(rng(17).standard_normal((n_total, k)).astype(np.float32), F16)
+    at, wt = dev(ctx, a, F16), dev(ctx, w, F16)
+    y = ctx.zeros(ctx.scratch, F16, (m, n_total))
+    xv, wv = at.mv(m, k), wt.mv(n, k, row_offset=32)
+    yv = y.mv(m, n, row_bytes=n_total * 2)
+    yv.offset += 32 * 2
+    ctx.check(lib.gd_backend_matmul_nt(ctx.backend, byref(xv), byref(wv), byref(yv)), "matmul_nt strided")
+    got = host(y)
+    close(got[:, 32:32 + n], O.rnd(t32(a) @ t32(w[32:32 + n]).t()), F16, scale=2)
+    assert np.all(got[:, :32] == 0) and np.all(got[:, 32 + n:] == 0)
+
+
+def test_linear_capsules_autograd(step):
+    ctx = step
+    m, k, n = 96, 64, 48
+    x = rnd_np(rng(18).standard_normal((m, k)).astype(np.float32), F16)
+    wt_ = rnd_np((rng(19).standard_normal((n, k)) * 0.1).astype(np.float32), F16)
+    w_ = rnd_np((rng(20).standard_normal((k, n)) * 0.1).astype(np.float32), F16)
+    b = rnd_np(rng(21).standard_normal(n).astype(np.float32), F16)
+    g = rnd_np(rng(22).standard_normal((m, n)).astype(np.float32), F16)
+    for transposed in (True, False):
+        xt, wt, bt = dev(ctx, x, F16), dev(ctx, wt_ if transposed else w_, F16), dev(ctx, b, F16)
+        xt.requires_grad = wt.requires_grad = bt.requires_grad = True
+        if transposed:
+            y = ops.gd_linear_transposed_weight(ctx, xt, wt, bt)
+            wy = O.linear_transposed_weight_forward(t32(x), t32(wt_), t32(b))
+            wdx, wdw, wdb = O.linear_transposed_weight_backward(t32(x), t32(wt_), t32(g))
+        else:
+            y = ops.gd_linear(ctx, xt, wt, bt)
+            wy = O.linear_forward(t32(x), t32(w_), t32(b))
+            wdx, wdw, wdb = O.linear_backward(t32(x), t32(w_), t32(g))
+        close(host(y), wy, F16, scale=2)
+        y.grad = dev(ctx, g, F16)
+        ctx.run_backward()
+        close(host(xt.grad), wdx, F16, scale=2)
+        close(host(wt.grad), wdw, F16, scale=8)
+        close(host(bt.grad), wdb, F16, scale=8)
+
+
+# ------------------------------------------------------------------ swiglu / rope
+@pytest.mark.parametrize("dtype,rows,h", [(F16, 100, 1536), (F16, 7, 5), (BF16, 64, 256)])
+def test_swiglu_split(step, dtype, rows, h):
+    ctx = step
+    x12 = rnd_np((rng(23).standard_normal((rows, 2 * h)) * 2).astype(np.float32), dtype)
+    g = rnd_np(rng(24).standard_normal((rows, h)).astype(np.float32), dtype)
+    xt = dev(ctx, x12, dtype)
+    xt.requires_grad = True
+    y = ops.gd_swiglu_split(ctx, xt)
+    close(host(y), O.swiglu_split_forward(t32(x12), storage_name(dtype)), dtype, scale=2)
+    y.grad = dev(ctx, g, dtype)
+    ctx.run_backward()
+    close(host(xt.grad), O.swiglu_split_backward(t32(x12), t32(g), storage_name(dtype)), dtype, scale=4)
+
+
+@pytest.mark.parametrize("dtype,n,heads,dh,theta,inter", [(F16, 300, 8, 64, 10000.0, False), (F16, 17, 2, 8, 500.0, True),
+                                                          (BF16, 50, 16, 128, 10000.0, False), (F16, 600, 4, 64, 10000.0, False)])
+def test_qkv_split_rope(step, dtype, n, heads, dh, theta, inter):
+    ctx = step
+    qkv = rnd_np(rng(25).standard_normal((n, 3 * heads * dh)).astype(np.float32), dtype)
+    pos = (np.arange(n) % 530).astype(np.int32)                               # crosses the 512-entry table
+    qt, pt = dev(ctx, qkv, dtype), dev(ctx, pos, I32)
+    qt.requires_grad = True
+    q, k, v = ops.gd_qkv_split_rope(ctx, qt, pt, heads, dh, theta, inter)
+    wq, wk, wv = O.qkv_split_rope_forward(t32(qkv), torch.from_numpy(pos), heads, dh, theta, inter, storage_name(dtype))
+    close(host(q), wq, dtype, scale=2)
+    close(host(k), wk, dtype, scale=2)
+    assert np.array_equal(host(v), wv.numpy())                                # V is a bit copy
+    gq, gk, gv = (rnd_np(rng(26 + i).standard_normal((n, heads, dh)).astype(np.float32), dtype) for i in range(3))
+    q.grad, k.grad, v.grad = dev(ctx, gq, dtype), dev(ctx, gk, dtype), dev(ctx, gv, dtype)
+    ctx.run_backward()
+    close(host(qt.grad), O.qkv_split_rope_backward(t32(gq), t32(gk), t32(gv), torch.from_numpy(pos), theta, inter, storage_name(dtype)), dtype, scale=2)
+
+
+# ------------------------------------------------------------------ attention
+def make_cu(lengths):
+    return np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+
+
+ATTN_CASES = [
+    # dtype, lengths, hq, hkv, dh, window, prefix
+    (F16, [5, 1, 130, 64, 200], 8, 8, 64, 0, 0),
+    (F16, [5, 1, 130, 64, 200], 8, 8, 64, 32, 0),
+    (F16, [37, 300], 4, 2, 64, 256, 0),
+    (F16, [2, 3], 2, 1, 4, 0, 0),
+    (F16, [64, 96], 2, 1, 64, 8, 4),
+    (BF16, [100, 129], 4, 4, 128, 0, 0),
+    (F32, [9, 14], 2, 2, 16, 3, 0),
+]
+
+
+@pytest.mark.parametrize("dtype,lengths,hq,hkv,dh,window,prefix", ATTN_CASES)
+def test_sdpa_varlen_forward_backward(step, dtype, lengths, hq, hkv, dh, window, prefix):
+    ctx = step
+    sd = storage_name(dtype)
+    cu = make_cu(lengths)
+    n = int(cu[-1])
+    q = rnd_np(rng(30).standard_normal((n, hq, dh)).astype(np.float32), dtype)
+    k = rnd_np(rng(31).standard_normal((n, hkv, dh)).astype(np.float32), dtype)
+    v = rnd_np(rng(32).standard_normal((n, hkv, dh)).astype(np.float32), dtype)
+    go = rnd_np(rng(33).standard_normal((n, hq, dh)).astype(np.float32), dtype)
+    qt, kt, vt, cut = dev(ctx, q, dtype), dev(ctx, k, dtype), dev(ctx, v, dtype), dev(ctx, cu, I32)
+    qt.requires_grad = kt.requires_grad = vt.requires_grad = True
+    out = ops.gd_sdpa_varlen(ctx, qt, kt, vt, cut, causal=True, sliding_window=window, prefix_len=prefix, max_seqlen=max(lengths))
+    want, _ = O.sdpa_varlen_forward(t32(q), t32(k), t32(v), cu, 0.0, True, window, prefix, sd)
+    close(host(out), want, dtype, scale=2, what="forward")
+    out.grad = dev(ctx, go, dtype)
+    ctx.run_backward()
+    wdq, wdk, wdv = O.sdpa_varlen_backward(t32(go), t32(q), t32(k), t32(v), cu, 0.0, True, window, prefix, sd)
+    close(host(qt.grad), wdq, dtype, scale=4, what="dq")
+    close(host(kt.grad), wdk, dtype, scale=6, what="dk")
+    close(host(vt.grad), wdv, dtype, scale=6, what="dv")
+
+
+@pytest.mark.parametrize("dtype,b,tq,tmax,hq,hkv,dh,window", [(F16, 5, 1, 512, 8, 8, 64, 256), (F16, 3, 2, 40, 4, 2, 64, 0),
+                                                              (BF16, 2, 1, 300, 16, 16, 128, 0), (F16, 2, 3, 11, 2, 1, 8, 4)])
+def test_kv_append_and_decode(step, dtype, b, tq, tmax, hq, hkv, dh, window):
+    ctx = step
+    sd = storage_name(dtype)
+    kc = rnd_np(rng(40).standard_normal((b, tmax, hkv, dh)).astype(np.float32), dtype)
+    vc = rnd_np(rng(41).standard_normal((b, tmax, hkv, dh)).astype(np.float32), dtype)
+    kn = rnd_np(rng(42).standard_normal((b, tq, hkv, dh)).astype(np.float32), dtype)
+    vn = rnd_np(rng(43).standard_normal((b, tq, hkv, dh)).astype(np.float32), dtype)
+    q = rnd_np(rng(44).standard_normal((b, tq, hq, dh)).astype(np.float32), dtype)
+    pos = rng(45).integers(0, tmax - tq + 1, size=b).astype(np.int32)
+    pos[-1] = tmax - tq                                                       # last slot that still fits
+    kct, vct, post = dev(ctx, kc, dtype), dev(ctx, vc, dtype), dev(ctx, pos, I32)
+    ops.gd_kv_cache_append_positions(ctx, kct, vct, post, dev(ctx, kn, dtype), dev(ctx, vn, dtype))
+    wk, wv = t32(kc).clone(), t32(vc).clone()
+    O.kv_cache_append(wk, wv, t32(kn), t32(vn), pos)
+    assert np.array_equal(host(kct), wk.numpy()) and np.array_equal(host(vct), wv.numpy())   # appended rows bit-exact
+    out = ops.gd_sdpa_decode_positions(ctx, dev(ctx, q, dtype), kct, vct, post, sliding_window=window)
+    close(host(out), O.sdpa_decode(t32(q), wk, wv, pos, 0.0, window, 0, sd), dtype, scale=2)
+
+
+def test_kv_append_packed_and_overflow_rows_dropped(step):
+    ctx = step
+    b, tmax, h, dh = 3, 16, 2, 8
+    lengths = [4, 9, 5]
+    cu = make_cu(lengths)
+    pos = np.array([0, 8, 3], dtype=np.int32)                                 # sequence 1 would cross the capacity: dropped
+    kc = np.zeros((b, tmax, h, dh), dtype=np.float32)
+    kn = rnd_np(rng(46).standard_normal((int(cu[-1]), h, dh)).astype(np.float32), F16)
+    vn = rnd_np(rng(47).standard_normal((int(cu[-1]), h, dh)).astype(np.float32), F16)
+    kct, vct = dev(ctx, kc, F16), dev(ctx, kc, F16)
+    ops.gd_kv_cache_append_packed(ctx, kct, vct, dev(ctx, pos, I32), dev(ctx, cu, I32), dev(ctx, kn, F16), dev(ctx, vn, F16))
+    wk, wv = t32(kc).clone(), t32(kc).clone()
+    O.kv_cache_append(wk, wv, t32(kn), t32(vn), pos, cu)
+    assert np.array_equal(host(kct), wk.numpy()) and np.array_equal(host(vct), wv.numpy())
+    assert np.all(host(kct)[1] == 0)
+
+
+# ------------------------------------------------------------------ LM cross entropy
+@pytest.mark.parametrize("rows,dim,vocab,cap,chunk_env", [(200, 64, 2048, 30.0, None), (37, 32, 300, 0.0, None), (64, 32, 1000, 0.75, "256")])
+def test_lm_cross_entropy(step, monkeypatch, rows, dim, vocab, cap, chunk_env):
+    ctx = step
+    if chunk_env:
+        monkeypatch.setenv("GD_LM_CE_CHUNK_SIZE", chunk_env)
+    h = rnd_np(rng(50).standard_normal((rows, dim)).astype(np.float32), F16)
+    w = rnd_np((rng(51).standard_normal((vocab, dim)) * 0.3).astype(np.float32), F16)
+    b = rnd_np((rng(52).standard_normal(vocab) * 0.1).astype(np.float32), F16)
+    tg = rng(53).integers(0, vocab, size=rows).astype(np.int32)
+    tg[::7] = -1
+    tg[5] = 3                                                                 # equals ignore_index below
+    ht, wt, bt, tt = dev(ctx, h, F16), dev(ctx, w, F16), dev(ctx, b, F16), dev(ctx, tg, I32)
+    ht.requires_grad = wt.requires_grad = bt.requires_grad = True
+    loss = ops.gd_lm_cross_entropy_softcapped_bias_ignore(ctx, ht, wt, bt, tt, cap, 3)
+    saved = O.lm_cross_entropy_forward(t32(h), t32(w), t32(b), torch.from_numpy(tg), cap, 3)
+    got = float(loss.read()[()])
+    assert abs(got - float(saved["loss"])) <= 2e-3 * max(1.0, abs(float(saved["loss"])))
+    seed = ctx.scratch_empty(F32, ())
+    seed.write(np.array(64.0, dtype=np.float32))
+    loss.grad = seed
+    ctx.run_backward()
+    dh, dw, db = O.lm_cross_entropy_backward(t32(h), t32(w), t32(b), torch.from_numpy(tg), saved, 64.0, cap)
+    close(host(ht.grad), dh, F16, scale=4)
+    close(host(wt.grad), dw, F16, scale=8)
+    close(host(bt.grad), db, F16, scale=8)
+
+
+# ------------------------------------------------------------------ optimizer
+def test_adamw_amp_clip_steps(step):
+    """Three optimizer steps incl. an overflow step: parameters, masters and the scaler state follow the oracle."""
+    ctx = step
+    optim = pkg.optim
+    shapes = [(300, 40), (40,), (1025,)]
+    p0 = [rnd_np(rng(60 + i).standard_normal(s).astype(np.float32), F16) for i, s in enumerate(shapes)]
+    params = []
+    for a in p0:
+        tns = dev(ctx, a, F16, ctx.params)
+        tns.requires_grad = True
+        params.append(tns)
+    cfg = optim.AdamwConfig(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
+    opt = optim.AdamW(ctx, params, cfg, [0.1, 0.0, 0.1])
+    scaler = optim.AmpScaler(ctx, optim.AmpConfig(init_scale=1024.0, growth_interval=2))
+    master = [t32(a).clone() for a in p0]
+    m = [torch.zeros_like(x) for x in master]
+    v = [torch.zeros_like(x) for x in master]
+    st = [{"beta1_power": np.float32(1), "beta2_power": np.float32(1)} for _ in master]
+    amp = {"scale": np.float32(1024), "inv_scale": np.float32(1 / 1024), "growth_tracker": 0, "found_inf": 0, "last_found_inf": 0}
+    acfg = dict(growth_factor=2.0, backoff_factor=0.5, min_scale=1.0, max_scale=2147483648.0, growth_interval=2)
+    for it in range(4):
+        grads = [rnd_np((rng(70 + it * 3 + i).standard_normal(s) * 1024 * 0.5).astype(np.float32), F16) for i, s in enumerate(shapes)]
+        if it == 1:
+            grads[2][7] = np.inf                                              # overflow: update skipped, scale backs off
+        for prm, g in zip(params, grads):
+            prm.grad = dev(ctx, g, F16)
+        opt.step_amp_clip_lr(scaler, 1e-2, 1.0)
+        O.amp_begin_step(amp, acfg)
+        gscale, norm, found = O.grad_clip_scale([t32(g) for g in grads], float(amp["inv_scale"]), 1.0)
+        amp["found_inf"] = int(found)
+        if not found:
+            for i in range(3):
+                master[i], m[i], v[i] = O.adamw_step(master[i], t32(grads[i]), m[i], v[i], st[i], 1e-2, 0.9, 0.95, 1e-8,
+                                                     [0.1, 0.0, 0.1][i], gscale)
+        O.amp_finish_step(amp, acfg)
+        s = scaler.sync()
+        assert s["scale"] == float(amp["scale"]) and s["last_found_inf"] == amp["last_found_inf"] and s["growth_tracker"] == amp["growth_tracker"]
+        if not found:
+            assert abs(opt.last_grad_norm() - norm) <= 1e-4 * norm
+        for i in range(3):
+            np.testing.assert_allclose(opt.slots[i].master.read(), master[i].numpy(), rtol=2e-6, atol=1e-7)
+            np.testing.assert_allclose(host(params[i]), O.rnd(master[i]).numpy(), rtol=1e-3, atol=1e-6)
+    assert opt.step_count() == 3
+
+
+def test_adamw_golden_bit_exact(step):
+    """First AdamW step and the clip step of the reference's optimizer test, compared on F16 bits."""
+    from conftest import Golden
+    ctx, optim = step, pkg.optim
+    g = Golden("ref_ctest_optim")
+    c = g["adamw_first_step"]
+    p = dev(ctx, c["p0"], F16, ctx.params)
+    p.requires_grad = True
+    opt = optim.AdamW(ctx, [p], optim.AdamwConfig(float(c["lr"]), float(c["beta1"]), float(c["beta2"]), float(c["eps"]), float(c["wd"])))
+    scaler = optim.AmpScaler(ctx, optim.AmpConfig(init_scale=1.0))
+    p.grad = dev(ctx, c["g0"], F32)
+    opt.step_amp_clip_lr(scaler, float(c["lr"]), 1.0e9)
+    assert np.array_equal(p.read().view(np.uint16), c["want_f16"])
+    c = g["adamw_clip_step"]
+    p = dev(ctx, c["p0"], F16, ctx.params)
+    p.requires_grad = True
+    opt = optim.AdamW(ctx, [p], optim.AdamwConfig(float(c["lr"]), 0.0, 0.0, 1.0, 0.0))
+    p.grad = dev(ctx, c["g0"], F16)
+    opt.step_amp_clip_lr(scaler, float(c["lr"]), float(c["max_norm"]))
+    assert np.array_equal(p.read().view(np.uint16), c["want_f16"])
+    assert abs(opt.last_grad_norm() - 5.0) < 1e-6
