@@ -73,7 +73,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose), srcs))
     if not _newer(LIB_PATH, objs):
-        cmd = [_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-lnccl",
+        cmd = [_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-ldl",
                "-gencode", "arch=compute_100a,code=sm_100a"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:

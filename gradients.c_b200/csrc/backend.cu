@@ -561,6 +561,18 @@ void gdb200_event_destroy(void *event)
     }
 }
 
+void *gdb200_pinned_alloc(size_t nbytes)
+{
+    void *p = NULL;
+    return (nbytes != 0U && cudaMallocHost(&p, nbytes) == cudaSuccess) ? p : NULL;
+}
+void gdb200_pinned_free(void *p)
+{
+    if (p != NULL) {
+        cudaFreeHost(p);
+    }
+}
+
 gd_status gdb200_flush_l2(gd_backend *be)
 {
     static unsigned tag = 0;

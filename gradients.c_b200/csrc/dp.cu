@@ -2,10 +2,63 @@
 // collective of any kind; these additive entries give its optimizer step the one exchange a
 // batch-sharded run needs: an in-place sum all-reduce of parameter gradients, issued on a
 // separate stream so it overlaps the rest of the backward pass.
+//
+// NCCL is bound at run time with dlopen("libnccl.so.2") on the first call, not at link time:
+// a process that has already loaded an NCCL (for instance through PyTorch) keeps using that
+// one copy, and single-GPU users of the backend carry no NCCL dependency at all.
 #include "common.cuh"
 
+#include <dlfcn.h>
 #include <nccl.h>
 #include <stdlib.h>
+
+namespace {
+
+struct nccl_api {
+    void *handle;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *);
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    const char *(*GetErrorString)(ncclResult_t);
+    ncclResult_t (*GroupStart)(void);
+    ncclResult_t (*GroupEnd)(void);
+};
+
+nccl_api *load_nccl(void)
+{
+    static nccl_api api;
+    static bool tried = false;
+    if (tried) {
+        return api.handle != NULL ? &api : NULL;
+    }
+    tried = true;
+    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (api.handle != NULL) {
+            break;
+        }
+    }
+    if (api.handle == NULL) {
+        return NULL;
+    }
+    api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(api.handle, "ncclGetUniqueId");
+    api.CommInitRank = (decltype(api.CommInitRank))dlsym(api.handle, "ncclCommInitRank");
+    api.AllReduce = (decltype(api.AllReduce))dlsym(api.handle, "ncclAllReduce");
+    api.CommDestroy = (decltype(api.CommDestroy))dlsym(api.handle, "ncclCommDestroy");
+    api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
+    api.GroupStart = (decltype(api.GroupStart))dlsym(api.handle, "ncclGroupStart");
+    api.GroupEnd = (decltype(api.GroupEnd))dlsym(api.handle, "ncclGroupEnd");
+    if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy || !api.GetErrorString ||
+        !api.GroupStart || !api.GroupEnd) {
+        api.handle = NULL;
+        return NULL;
+    }
+    return &api;
+}
+
+}  // namespace
 
 struct gdb_dp_state {
     ncclComm_t comm;
@@ -21,8 +74,11 @@ void gdb_dp_destroy(gd_backend *be)
         return;
     }
     gdb_dp_state *dp = be->dp;
+    nccl_api *api = load_nccl();
     cudaStreamSynchronize(dp->stream);
-    ncclCommDestroy(dp->comm);
+    if (api != NULL) {
+        api->CommDestroy(dp->comm);
+    }
     cudaEventDestroy(dp->ready);
     cudaEventDestroy(dp->done);
     cudaStreamDestroy(dp->stream);
@@ -36,7 +92,11 @@ gd_status gdb200_dp_unique_id(void *id_bytes_128)
 {
     ncclUniqueId id;
     static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
-    if (id_bytes_128 == NULL || ncclGetUniqueId(&id) != ncclSuccess) {
+    nccl_api *api = load_nccl();
+    if (api == NULL) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (id_bytes_128 == NULL || api->GetUniqueId(&id) != ncclSuccess) {
         return GD_ERR_INTERNAL;
     }
     memcpy(id_bytes_128, &id, sizeof(id));
@@ -48,6 +108,11 @@ gd_status gdb200_dp_init(gd_backend *be, const void *id_bytes_128, int rank, int
     ncclUniqueId id;
     if (be == NULL || id_bytes_128 == NULL || world < 1 || rank < 0 || rank >= world || be->dp != NULL) {
         return GD_ERR_INVALID_ARGUMENT;
+    }
+    nccl_api *api = load_nccl();
+    if (api == NULL) {
+        snprintf(be->last_error, sizeof(be->last_error), "libnccl.so.2 could not be loaded: %s", dlerror());
+        return GD_ERR_UNSUPPORTED;
     }
     cudaSetDevice(be->device);
     gdb_dp_state *dp = (gdb_dp_state *)calloc(1, sizeof(*dp));
@@ -63,9 +128,9 @@ gd_status gdb200_dp_init(gd_backend *be, const void *id_bytes_128, int rank, int
         free(dp);
         return GD_ERR_INTERNAL;
     }
-    ncclResult_t r = ncclCommInitRank(&dp->comm, world, id, rank);
+    ncclResult_t r = api->CommInitRank(&dp->comm, world, id, rank);
     if (r != ncclSuccess) {
-        snprintf(be->last_error, sizeof(be->last_error), "ncclCommInitRank: %s", ncclGetErrorString(r));
+        snprintf(be->last_error, sizeof(be->last_error), "ncclCommInitRank: %s", api->GetErrorString(r));
         cudaEventDestroy(dp->ready);
         cudaEventDestroy(dp->done);
         cudaStreamDestroy(dp->stream);
@@ -89,15 +154,16 @@ gd_status gdb200_dp_all_reduce(gd_backend *be, gd_backend_buffer *buffer, size_t
         return GD_OK;
     }
     gdb_dp_state *dp = be->dp;
+    nccl_api *api = load_nccl();
     const ncclDataType_t nt = dtype == GDB_DTYPE_F16 ? ncclFloat16 : (dtype == GDB_DTYPE_BF16 ? ncclBfloat16 : ncclFloat32);
     void *p = buffer->dptr + offset;
     if (cudaEventRecord(dp->ready, be->stream) != cudaSuccess || cudaStreamWaitEvent(dp->stream, dp->ready, 0) != cudaSuccess) {
         return GD_ERR_INTERNAL;
     }
-    ncclResult_t r = ncclAllReduce(p, p, count, nt, ncclSum, dp->comm, dp->stream);
+    ncclResult_t r = api->AllReduce(p, p, count, nt, ncclSum, dp->comm, dp->stream);
     be->launches += 1U;
     if (r != ncclSuccess) {
-        snprintf(be->last_error, sizeof(be->last_error), "ncclAllReduce: %s", ncclGetErrorString(r));
+        snprintf(be->last_error, sizeof(be->last_error), "ncclAllReduce: %s", api->GetErrorString(r));
         return GD_ERR_INTERNAL;
     }
     return GD_OK;

@@ -8,6 +8,18 @@
 // rounds once (src/ops/linear/metal_linear.metal:33-52).
 #include "common.cuh"
 
+// Optional per-launch timing of the dense contractions (benchmark instrumentation): when enabled,
+// every dispatch is bracketed by a CUDA event pair on the backend stream and its algorithmic
+// FLOPs and bytes are accumulated; gdb200_gemm_profile_read sums the elapsed times.
+struct gdb_gemm_profile {
+    static constexpr int CAP = 8192;
+    cudaEvent_t start[CAP], stop[CAP];
+    int created, used;
+    double flops, bytes;
+    bool enabled;
+};
+static gdb_gemm_profile *g_profile = nullptr;
+
 namespace {
 
 constexpr int TM = 64, TN = 64, TK = 16;
@@ -194,6 +206,33 @@ gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb, const gd_backend_mat
     const void *ap = x->buffer->dptr + x->offset;
     const void *wp = w->buffer->dptr + w->offset;
     void *cp = y->buffer->dptr + y->offset;
+    struct profile_scope {
+        gd_backend *be;
+        int slot;
+        profile_scope(gd_backend *b, double flops, double bytes) : be(b), slot(-1)
+        {
+            gdb_gemm_profile *p = g_profile;
+            if (p == nullptr || !p->enabled || p->used >= gdb_gemm_profile::CAP) {
+                return;
+            }
+            if (p->used >= p->created) {
+                if (cudaEventCreate(&p->start[p->created]) != cudaSuccess || cudaEventCreate(&p->stop[p->created]) != cudaSuccess) {
+                    return;
+                }
+                p->created += 1;
+            }
+            slot = p->used++;
+            p->flops += flops;
+            p->bytes += bytes;
+            cudaEventRecord(p->start[slot], be->stream);
+        }
+        ~profile_scope()
+        {
+            if (slot >= 0) {
+                cudaEventRecord(g_profile->stop[slot], be->stream);
+            }
+        }
+    } scope(be, 2.0 * M * N * K, (double)es * ((double)M * K + (double)K * N + (double)M * N));
     if (be->gemm_mode != 1 && dt != GDB_DTYPE_F32) {
         gd_status st = gdb_gemm_tcgen05(be, ta, tb, dt, ap, x->row_bytes, wp, w->row_bytes, cp, y->row_bytes, bp, M, N, K);
         if (st != GD_ERR_UNSUPPORTED) {
@@ -283,6 +322,42 @@ gd_status batched_dispatch(gd_backend *be, int ta, int tb, const gd_backend_batc
 }  // namespace
 
 extern "C" {
+
+void gdb200_gemm_profile_enable(gd_backend *be, int enable)
+{
+    (void)be;
+    if (g_profile == nullptr) {
+        g_profile = new gdb_gemm_profile();
+        g_profile->created = 0;
+    }
+    g_profile->enabled = enable != 0;
+    g_profile->used = 0;
+    g_profile->flops = 0.0;
+    g_profile->bytes = 0.0;
+}
+
+// Waits for the stream, then reports launches, summed device milliseconds, FLOPs and bytes since enable.
+gd_status gdb200_gemm_profile_read(gd_backend *be, uint64_t *launches, double *total_ms, double *flops, double *bytes)
+{
+    if (be == NULL || g_profile == nullptr) {
+        return GD_ERR_BAD_STATE;
+    }
+    if (cudaStreamSynchronize(be->stream) != cudaSuccess) {
+        return GD_ERR_INTERNAL;
+    }
+    double ms = 0.0;
+    for (int i = 0; i < g_profile->used; ++i) {
+        float t = 0.0f;
+        if (cudaEventElapsedTime(&t, g_profile->start[i], g_profile->stop[i]) == cudaSuccess) {
+            ms += t;
+        }
+    }
+    if (launches) *launches = (uint64_t)g_profile->used;
+    if (total_ms) *total_ms = ms;
+    if (flops) *flops = g_profile->flops;
+    if (bytes) *bytes = g_profile->bytes;
+    return GD_OK;
+}
 
 gd_status gd_backend_matmul(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_matrix_view *y)
 {

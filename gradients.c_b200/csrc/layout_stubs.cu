@@ -91,12 +91,6 @@ gd_status gd_backend_sigmoid(gd_backend *, TV, TV) UNSUPPORTED_BODY
 gd_status gd_backend_sigmoid_backward(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
 gd_status gd_backend_tanh(gd_backend *, TV, TV) UNSUPPORTED_BODY
 gd_status gd_backend_tanh_backward(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_reduce_contiguous(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
-gd_status gd_backend_reduce_axis(gd_backend *, TV, TV, uint32_t, float) UNSUPPORTED_BODY
-gd_status gd_backend_broadcast_axis(gd_backend *, TV, TV, uint32_t, float) UNSUPPORTED_BODY
-gd_status gd_backend_broadcast_to(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
-gd_status gd_backend_broadcast_scalar(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
-gd_status gd_backend_reduce_broadcast(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
 gd_status gd_backend_sigmoid_backward_from_output(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
 gd_status gd_backend_tanh_backward_from_output(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
 gd_status gd_backend_mul_backward_direct(gd_backend *, TV, TV, TV, TV, TV) UNSUPPORTED_BODY

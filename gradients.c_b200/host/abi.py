@@ -227,6 +227,10 @@ PROTOTYPES = {
     "gdb200_event_elapsed_ms": (F, [P, P]),
     "gdb200_event_destroy": (None, [P]),
     "gdb200_flush_l2": (_ST, [P]),
+    "gdb200_pinned_alloc": (P, [SZ]),
+    "gdb200_pinned_free": (None, [P]),
+    "gdb200_gemm_profile_enable": (None, [P, C.c_int]),
+    "gdb200_gemm_profile_read": (_ST, [P, C.POINTER(U64), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "gdb200_dp_unique_id": (_ST, [P]),
     "gdb200_dp_init": (_ST, [P, P, C.c_int, C.c_int]),
     "gdb200_dp_all_reduce": (_ST, [P, P, SZ, SZ, U32]),

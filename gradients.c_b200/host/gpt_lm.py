@@ -335,11 +335,13 @@ class Trainer:
         self.global_step = 0
         self.dp = dp
 
-    def train_batch(self, batch: Batch, lr: Optional[float] = None) -> Tensor:
+    def train_batch(self, batch: Optional[Batch], lr: Optional[float] = None, device_batch=None) -> Tensor:
+        """One training step. `device_batch` = (ids, targets, positions, cu_seqlens) tensors that are
+        already resident on the device; otherwise the host batch is uploaded into the data slot."""
         ctx, model = self.ctx, self.model
         ctx.begin_step()
         self.optimizer.zero_grad()
-        ids, tgt, pos, cu = model.upload_batch(batch)
+        ids, tgt, pos, cu = device_batch if device_batch is not None else model.upload_batch(batch)
         loss = model.forward(ids, tgt, pos, cu, self.global_step + 1)
         gd_backward_amp(ctx, loss, self.scaler)
         inv_override = None

@@ -207,6 +207,19 @@ class Context:
     def launch_count(self) -> int:
         return int(self.lib.gdb200_launch_count(self.backend))
 
+    def pinned_copy(self, a: np.ndarray) -> np.ndarray:
+        """Copy of `a` in page-locked host memory (kept alive by the context)."""
+        a = np.ascontiguousarray(a)
+        ptr = self.lib.gdb200_pinned_alloc(max(a.nbytes, 1))
+        if not ptr:
+            raise MemoryError("pinned host allocation failed")
+        self._pinned = getattr(self, "_pinned", [])
+        self._pinned.append(ptr)
+        buf = (C.c_byte * a.nbytes).from_address(ptr)
+        out = np.frombuffer(buf, dtype=a.dtype).reshape(a.shape)
+        out[...] = a
+        return out
+
     # ---- step scope (reference gd_begin_step / gd_end_step) ----
     def begin_step(self) -> None:
         assert not self.in_step

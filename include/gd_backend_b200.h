@@ -363,7 +363,15 @@ int gdb200_set_gemm_mode(gd_backend *backend, int mode);
 void *gdb200_event_record(gd_backend *backend);
 float gdb200_event_elapsed_ms(void *start, void *stop);
 void gdb200_event_destroy(void *event);
-/* Write `nbytes` of zeros-then-ones pattern over a private >L2 buffer to evict L2. */
+/* Page-locked host memory for upload sources / download targets (cudaMallocHost / cudaFreeHost). */
+void *gdb200_pinned_alloc(size_t nbytes);
+void gdb200_pinned_free(void *p);
+/* Benchmark instrumentation: bracket every dense-contraction dispatch with a CUDA event pair on
+ * the backend stream; read returns the number of launches, their summed device time and the
+ * algorithmic FLOPs / bytes (2MNK and one pass over each operand) accumulated since enable. */
+void gdb200_gemm_profile_enable(gd_backend *backend, int enable);
+gd_status gdb200_gemm_profile_read(gd_backend *backend, uint64_t *launches, double *total_ms, double *flops, double *bytes);
+/* Overwrite a private buffer larger than L2 so that the next kernel starts with a cold L2. */
 gd_status gdb200_flush_l2(gd_backend *backend);
 
 /* Data-parallel gradient exchange (the reference has no collective; one process per GPU).

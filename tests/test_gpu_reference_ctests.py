@@ -19,11 +19,13 @@ HOT_PATH = ["test_memory", "test_tensor", "test_transfer", "test_linear", "test_
 
 
 @pytest.mark.parametrize("name", HOT_PATH)
-def test_reference_ctest(name):
+def test_reference_ctest(name, tmp_path):
     exe = os.path.join(cref.TESTS_CUDA_DIR, name)
     if not os.path.exists(exe):
         pytest.skip("reference C tests were not built (no reference tree at build time)")
-    res = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    # the reference runs its tests from the repository root and writes checkpoints under build/
+    os.makedirs(tmp_path / "build", exist_ok=True)
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=300, cwd=tmp_path)
     out = (res.stdout + res.stderr).strip()
     assert res.returncode == 0, out[-2000:]
     assert "skipped" not in out.lower(), f"{name} skipped instead of running on the CUDA backend: {out[-500:]}"
