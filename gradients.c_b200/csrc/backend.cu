@@ -295,6 +295,16 @@ gd_status gd_backend_flush(gd_backend *be)
     if (e != cudaSuccess) {
         return gdb_fail(be, e, "flush");
     }
+    // kernels with bounded waits report a give-up through the device error word
+    e = cudaMemcpy(be->err_flag_host, be->err_flag, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        return gdb_fail(be, e, "flush error word");
+    }
+    if (*be->err_flag_host != 0) {
+        snprintf(be->last_error, sizeof(be->last_error), "device kernel gave up a bounded wait (code %d)", *be->err_flag_host);
+        cudaMemset(be->err_flag, 0, sizeof(int));
+        return GD_ERR_INTERNAL;
+    }
     return GD_OK;
 }
 

@@ -1,3 +1,460 @@
+// Blackwell (sm_100a) dense contraction: TMA-fed shared-memory ring, tcgen05.mma with the FP32
+// accumulator in tensor memory, warp-specialised roles.
+//
+//   C[M, N] = A * B (+ bias), 16-bit operands (F16 / BF16), FP32 accumulation, one rounding.
+//   A is either K-major (stored [M, K], "x" of matmul / matmul_nt) or MN-major (stored [K, M],
+//   "x" of matmul_tn); B is either K-major (stored [N, K], "w" of matmul_nt) or MN-major
+//   (stored [K, N], "w" of matmul / matmul_tn / linear). Both major-ness bits of the UMMA
+//   instruction descriptor are used, so no operand is ever transposed in memory.
+//
+// CTA = 192 threads: warp 0 issues TMA loads, warp 1 allocates tensor memory and issues the MMAs,
+// warps 2-5 drain the accumulator (tcgen05.ld), add the bias in FP32, round and store. One CTA
+// computes one 128 x BN tile (optionally one K-slice of it: split-K writes FP32 partials that a
+// second kernel sums, used for the weight-gradient shapes whose contraction runs over all tokens).
+//
+// Shared-memory operand layout is the canonical 128-byte-swizzled UMMA layout that TMA writes
+// directly: K-major tiles are rows of 64 elements (128 B), 8-row groups 1024 B apart (SBO);
+// MN-major tiles are blocks of 64 MN-elements x BK k-rows, each k-row 128 B, 8-k-row groups
+// 1024 B apart (SBO) and the 64-element MN blocks BK*128 B apart (LBO).
+//
+// Every mbarrier wait is bounded: when a wait gives up the kernel records an error code in
+// gd_backend::err_flag, falls through to the common exit (tensor memory is released there) and
+// gd_backend_flush reports GD_ERR_INTERNAL.
 #include "common.cuh"
-gd_status gdb_gemm_tcgen05(gd_backend *, int, int, uint32_t, const void *, size_t, const void *, size_t, void *, size_t, const void *, uint32_t, uint32_t, uint32_t) { return GD_ERR_UNSUPPORTED; }
-void gdb_tmap_cache_destroy(gd_backend *) {}
+
+#include <cuda.h>
+#include <type_traits>
+
+namespace {
+
+constexpr int BM = 128;      // UMMA M
+constexpr int BK = 64;       // k elements per stage: one 128-byte swizzle row of 16-bit elements
+constexpr int UMMA_K = 16;   // k elements per tcgen05.mma for 16-bit operands
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+encode_tiled_fn get_encode_fn()
+{
+    static encode_tiled_fn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess) {
+            fn = (encode_tiled_fn)p;
+        }
+    }
+    return fn;
+}
+
+// 2-D row-major global tensor [rows, cols] of 16-bit elements with a row pitch in bytes;
+// box = {box_cols (<= 64, the swizzle span), box_rows}.
+bool make_tmap(CUtensorMap *m, uint32_t dtype, const void *base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+               uint32_t box_cols, uint32_t box_rows)
+{
+    encode_tiled_fn fn = get_encode_fn();
+    if (fn == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = dtype == GDB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    return fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) {
+            return true;
+        }
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 64-bit shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFFU);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFU) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFU) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+template <int BN, int STAGES>
+struct smem_plan {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
+};
+
+template <typename T> struct half_pack;
+template <> struct half_pack<__half> {
+    static __device__ __forceinline__ uint32_t pack(float a, float b)
+    {
+        const __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+};
+template <> struct half_pack<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t pack(float a, float b)
+    {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+};
+
+// grid = (n tiles, m tiles, k splits)
+template <typename T, int BN, int STAGES, bool A_MN, bool B_MN, bool SPLITK>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, T *__restrict__ c,
+                    size_t ldc, const T *__restrict__ bias, float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K,
+                    uint32_t k_iters_per_split, int *err_flag)
+{
+    using plan = smem_plan<BN, STAGES>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * plan::STAGE_BYTES);
+    // bars[0..STAGES) full, bars[STAGES..2*STAGES) empty, bars[2*STAGES] accumulator ready
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const uint32_t total_k_iters = (K + BK - 1) / BK;
+    const uint32_t k_begin = blockIdx.z * k_iters_per_split;
+    const uint32_t k_end = min(total_k_iters, k_begin + k_iters_per_split);
+    const uint32_t n_iters = k_end > k_begin ? k_end - k_begin : 0U;
+
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (uint32_t it = 0; it < n_iters; ++it) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1U;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1U)) {
+                    atomicExch(err_flag, 101);
+                    break;
+                }
+                const uint32_t a_dst = smem_u32(smem + s * plan::STAGE_BYTES);
+                const uint32_t b_dst = a_dst + plan::A_BYTES;
+                const int k0 = (int)((k_begin + it) * BK);
+                mbar_expect_tx(full0 + 8 * s, plan::STAGE_BYTES);
+                if (A_MN) {
+                    // global [K, M]: box {64 m, BK k}; two boxes cover the 128 rows of the tile
+                    tma_load_2d(a_dst, &tma_a, (int)m0, k0, full0 + 8 * s);
+                    tma_load_2d(a_dst + BK * 128, &tma_a, (int)m0 + 64, k0, full0 + 8 * s);
+                } else {
+                    tma_load_2d(a_dst, &tma_a, k0, (int)m0, full0 + 8 * s);  // global [M, K]: box {64 k, 128 m}
+                }
+                if (B_MN) {
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j) {
+                        tma_load_2d(b_dst + j * BK * 128, &tma_b, (int)n0 + 64 * j, k0, full0 + 8 * s);
+                    }
+                } else {
+                    tma_load_2d(b_dst, &tma_b, k0, (int)n0, full0 + 8 * s);  // global [N, K]: box {64 k, BN n}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t FMT = std::is_same<T, __nv_bfloat16>::value ? 1U : 0U;
+            constexpr uint32_t IDESC = (1U << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1U : 0U) << 15) | ((B_MN ? 1U : 0U) << 16) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (uint32_t it = 0; it < n_iters && ok; ++it) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1U;
+                if (!mbar_wait(full0 + 8 * s, ph)) {
+                    atomicExch(err_flag, 102);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t a_base = smem_u32(smem + s * plan::STAGE_BYTES);
+                const uint32_t b_base = a_base + plan::A_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                    // K-major: step 16 elements = 32 bytes inside the swizzle row.
+                    // MN-major: step 16 k-rows = 2048 bytes.
+                    const uint64_t adesc = A_MN ? make_smem_desc(a_base + kk * 2048, BK * 128, 1024)
+                                                : make_smem_desc(a_base + kk * 32, 16, 1024);
+                    const uint64_t bdesc = B_MN ? make_smem_desc(b_base + kk * 2048, BK * 128, 1024)
+                                                : make_smem_desc(b_base + kk * 32, 16, 1024);
+                    tcgen05_mma_f16(tmem_base, adesc, bdesc, IDESC, (it != 0 || kk != 0) ? 1U : 0U);
+                }
+                tcgen05_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+            }
+            tcgen05_commit(accum_bar);           // accumulator complete (or nothing was issued)
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own TMEM lane quadrants 2,3,0,1 ----------------
+        const int quad = warp & 3;
+        const uint32_t row = m0 + quad * 32 + lane;
+        const bool ok = mbar_wait(accum_bar, 0);
+        if (!ok && lane == 0) {
+            atomicExch(err_flag, 103);
+        }
+        tcgen05_fence_after();
+        if (ok) {
+#pragma unroll 1
+            for (int cb = 0; cb < BN / 32; ++cb) {
+                uint32_t v[32];
+                if (n_iters != 0) {
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0U;
+                }
+                const uint32_t col0 = n0 + cb * 32;
+                if (row < M && col0 < N) {
+                    if (SPLITK) {
+                        float *dst = partial + ((size_t)blockIdx.z * M + row) * N + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (col0 + j < N) {
+                                *reinterpret_cast<float4 *>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                                   __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                            }
+                        }
+                    } else {
+                        T *dst = c + (size_t)row * ldc + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (col0 + j < N) {
+                                float f[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    f[e] = __uint_as_float(v[j + e]);
+                                    if (bias != nullptr) f[e] += gdb_io<T>::ld(bias, col0 + j + e);
+                                }
+                                uint4 o;
+                                o.x = half_pack<T>::pack(f[0], f[1]);
+                                o.y = half_pack<T>::pack(f[2], f[3]);
+                                o.z = half_pack<T>::pack(f[4], f[5]);
+                                o.w = half_pack<T>::pack(f[6], f[7]);
+                                *reinterpret_cast<uint4 *>(dst + j) = o;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// out[m, n] = round(sum_z partial[z, m, n] + bias[n])
+template <typename T>
+__global__ void splitk_reduce_kernel(const float *__restrict__ partial, T *__restrict__ c, size_t ldc, const T *__restrict__ bias,
+                                     uint32_t M, uint32_t N, uint32_t splits)
+{
+    const size_t quads = (size_t)M * (N / 4), stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += stride) {
+        const uint32_t row = (uint32_t)(q / (N / 4)), col = (uint32_t)(q % (N / 4)) * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t z = 0; z < splits; ++z) {
+            const float4 p = *reinterpret_cast<const float4 *>(partial + ((size_t)z * M + row) * N + col);
+            acc.x += p.x;
+            acc.y += p.y;
+            acc.z += p.z;
+            acc.w += p.w;
+        }
+        if (bias != nullptr) {
+            acc.x += gdb_io<T>::ld(bias, col);
+            acc.y += gdb_io<T>::ld(bias, col + 1);
+            acc.z += gdb_io<T>::ld(bias, col + 2);
+            acc.w += gdb_io<T>::ld(bias, col + 3);
+        }
+        uint2 o;
+        o.x = half_pack<T>::pack(acc.x, acc.y);
+        o.y = half_pack<T>::pack(acc.z, acc.w);
+        *reinterpret_cast<uint2 *>(c + (size_t)row * ldc + col) = o;
+    }
+}
+
+template <typename T, int BN, int STAGES, bool A_MN, bool B_MN, bool SPLITK>
+gd_status launch(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, void *c, size_t ldc, const void *bias,
+                 float *partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits, uint32_t k_per_split)
+{
+    using plan = smem_plan<BN, STAGES>;
+    auto kern = gemm_tcgen05_kernel<T, BN, STAGES, A_MN, B_MN, SPLITK>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan::TOTAL);
+        if (e != cudaSuccess) {
+            return gdb_fail(be, e, "tcgen05 gemm smem attribute");
+        }
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, splits);
+    kern<<<grid, 192, plan::TOTAL, be->stream>>>(ta, tb, (T *)c, ldc, (const T *)bias, partial, M, N, K, k_per_split, be->err_flag);
+    return gdb_launched(be, "gemm_tcgen05");
+}
+
+template <typename T, int BN, int STAGES>
+gd_status dispatch_major(gd_backend *be, int ta, int tb, const CUtensorMap &ma, const CUtensorMap &mb, void *c, size_t ldc,
+                         const void *bias, float *partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits, uint32_t kps)
+{
+    const bool sk = splits > 1;
+#define GDB_GO(AM, BMJ)                                                                                              \
+    (sk ? launch<T, BN, STAGES, AM, BMJ, true>(be, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps)            \
+        : launch<T, BN, STAGES, AM, BMJ, false>(be, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps))
+    if (ta) {
+        return tb ? GDB_GO(true, false) : GDB_GO(true, true);
+    }
+    return tb ? GDB_GO(false, false) : GDB_GO(false, true);
+#undef GDB_GO
+}
+
+}  // namespace
+
+// ta: A stored [K, M] (MN-major); tb: B stored [N, K] (K-major). Leading dimensions in bytes.
+gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b,
+                           size_t ldb_bytes, void *c, size_t ldc_bytes, const void *bias, uint32_t M, uint32_t N, uint32_t K)
+{
+    if (dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    // TMA needs 16-byte aligned bases and pitches; vector stores need N % 8 == 0; tiny problems are
+    // cheaper on the portable kernel than a 128-row tile with bounded-wait pipeline set-up.
+    if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) % 16U) != 0U || (lda_bytes % 16U) != 0U || (ldb_bytes % 16U) != 0U ||
+        (ldc_bytes % 16U) != 0U || (N % 8U) != 0U || (K % 8U) != 0U || M < 64U || N < 64U || K < 64U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (bias != NULL && ((uintptr_t)bias % 2U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const int bn = (N % 256U == 0U && (size_t)((M + BM - 1) / BM) * (N / 256U) >= (size_t)be->sm_count) ? 256 : 128;
+    CUtensorMap ma, mb;
+    const bool oka = ta ? make_tmap(&ma, dtype, a, K, M, lda_bytes, 64, BK) : make_tmap(&ma, dtype, a, M, K, lda_bytes, BK, BM);
+    const bool okb = tb ? make_tmap(&mb, dtype, b, N, K, ldb_bytes, BK, (uint32_t)bn) : make_tmap(&mb, dtype, b, K, N, ldb_bytes, 64, BK);
+    if (!oka || !okb) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    // split-K when the tile grid cannot fill the machine and the contraction is long
+    const uint32_t tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const uint32_t total_k = (K + BK - 1) / BK;
+    uint32_t splits = 1;
+    if (tiles * 2U <= (uint32_t)be->sm_count && total_k >= 16U) {
+        splits = ((uint32_t)be->sm_count * 2U + tiles - 1U) / tiles;
+        if (splits > total_k / 4U) splits = total_k / 4U;
+        if (splits > 32U) splits = 32U;
+        while (splits > 1U && (size_t)splits * M * N * sizeof(float) > be->ws_bytes / 2U) --splits;
+        if (splits < 1U) splits = 1U;
+    }
+    uint32_t kps = (total_k + splits - 1U) / splits;
+    splits = (total_k + kps - 1U) / kps;
+    float *partial = (float *)be->ws;
+    const size_t ldc = ldc_bytes / 2U;
+    gd_status st;
+    if (dtype == GDB_DTYPE_F16) {
+        st = bn == 256 ? dispatch_major<__half, 256, 4>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps)
+                       : dispatch_major<__half, 128, 3>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps);
+    } else {
+        st = bn == 256 ? dispatch_major<__nv_bfloat16, 256, 4>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps)
+                       : dispatch_major<__nv_bfloat16, 128, 3>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps);
+    }
+    if (st != GD_OK || splits == 1U) {
+        return st;
+    }
+    const size_t quads = (size_t)M * (N / 4U);
+    if (dtype == GDB_DTYPE_F16) {
+        splitk_reduce_kernel<__half><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__half *)c, ldc, (const __half *)bias, M, N, splits);
+    } else {
+        splitk_reduce_kernel<__nv_bfloat16><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits);
+    }
+    return gdb_launched(be, "gemm_splitk_reduce");
+}
+
+void gdb_tmap_cache_destroy(gd_backend *be) { (void)be; }

@@ -410,3 +410,60 @@ def test_adamw_golden_bit_exact(step):
     opt.step_amp_clip_lr(scaler, float(c["lr"]), float(c["max_norm"]))
     assert np.array_equal(p.read().view(np.uint16), c["want_f16"])
     assert abs(opt.last_grad_norm() - 5.0) < 1e-6
+
+
+# ------------------------------------------------------------------ tcgen05 GEMM (required, no fallback)
+TC_SHAPES = [
+    # m, k, n : forward / dX shapes of the model and ragged edges
+    (1024, 512, 1536), (1024, 512, 512), (1000, 512, 3072), (2048, 1536, 512), (640, 512, 2048),
+    (300, 512, 1536), (128, 64, 64), (264, 200, 136), (4096, 512, 1536),
+]
+
+
+@pytest.mark.parametrize("dtype", [F16, BF16])
+@pytest.mark.parametrize("m,k,n", TC_SHAPES)
+def test_tcgen05_gemm_all_layouts(step, dtype, m, k, n):
+    ctx, lib = step, step.lib
+    sd = storage_name(dtype)
+    a = rnd_np((rng(80).standard_normal((m, k)) * 0.5).astype(np.float32), dtype)
+    b = rnd_np((rng(81).standard_normal((k, n)) * 0.5).astype(np.float32), dtype)
+    bias = rnd_np(rng(82).standard_normal(n).astype(np.float32), dtype)
+    want = t32(a) @ t32(b)
+    sc = np.sqrt(k) / 4
+    at, bt, btt, att = dev(ctx, a, dtype), dev(ctx, b, dtype), dev(ctx, b.T.copy(), dtype), dev(ctx, a.T.copy(), dtype)
+    y = ctx.scratch_empty(dtype, (m, n))
+    old = lib.gdb200_set_gemm_mode(ctx.backend, 2)
+    try:
+        cases = [("matmul", lib.gd_backend_matmul, at.mv(m, k), bt.mv(k, n)), ("matmul_nt", lib.gd_backend_matmul_nt, at.mv(m, k), btt.mv(n, k))]
+        if (m * 2) % 16 == 0:
+            cases.append(("matmul_tn", lib.gd_backend_matmul_tn, att.mv(k, m), bt.mv(k, n)))
+        for name, fn, xv, wv in cases:
+            ctx.fill(y, 0)
+            yv = y.mv(m, n)
+            ctx.check(fn(ctx.backend, byref(xv), byref(wv), byref(yv)), name)
+            close(host(y), O.rnd(want, sd), dtype, scale=sc, what=name)
+        bv, yv, xv, wv = dev(ctx, bias, dtype).vv(), y.mv(m, n), at.mv(m, k), bt.mv(k, n)
+        ctx.check(lib.gd_backend_linear(ctx.backend, byref(xv), byref(wv), byref(bv), byref(yv)), "linear")
+        close(host(y), O.linear_forward(t32(a), t32(b), t32(bias), sd), dtype, scale=sc, what="linear")
+        ctx.flush()
+    finally:
+        lib.gdb200_set_gemm_mode(ctx.backend, old)
+
+
+@pytest.mark.parametrize("m,k,n", [(1536, 8192, 512), (512, 18432, 512), (3072, 4096, 512), (512, 9000, 1536)])
+def test_tcgen05_gemm_split_k_weight_gradient(step, m, k, n):
+    """dW = dY^T X: the contraction runs over the tokens, the output is small -> split-K path."""
+    ctx, lib = step, step.lib
+    dy = rnd_np((rng(83).standard_normal((k, m)) * 0.25).astype(np.float32), F16)   # stored [tokens, m]
+    x = rnd_np((rng(84).standard_normal((k, n)) * 0.25).astype(np.float32), F16)    # stored [tokens, n]
+    want = O.rnd(t32(dy).t() @ t32(x))
+    dyt, xt = dev(ctx, dy, F16), dev(ctx, x, F16)
+    y = ctx.scratch_empty(F16, (m, n))
+    old = lib.gdb200_set_gemm_mode(ctx.backend, 2)
+    try:
+        xv, wv, yv = dyt.mv(k, m), xt.mv(k, n), y.mv(m, n)
+        ctx.check(lib.gd_backend_matmul_tn(ctx.backend, byref(xv), byref(wv), byref(yv)), "matmul_tn split-k")
+        close(host(y), want, F16, scale=np.sqrt(k) / 16, what="matmul_tn split-k")
+        ctx.flush()
+    finally:
+        lib.gdb200_set_gemm_mode(ctx.backend, old)
