@@ -231,6 +231,9 @@ PROTOTYPES = {
     "gdb200_pinned_free": (None, [P]),
     "gdb200_gemm_profile_enable": (None, [P, C.c_int]),
     "gdb200_gemm_profile_read": (_ST, [P, C.POINTER(U64), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "gdb200_embedding_backward_static": (_ST, [P, P, P, P, U64, U64, U64, U32]),
+    "gdb200_embedding_backward_static_error": (C.c_char_p, []),
+    "gdb200_embedding_backward_static_max_elems": (U64, []),
     "gdb200_dp_unique_id": (_ST, [P]),
     "gdb200_dp_init": (_ST, [P, P, C.c_int, C.c_int]),
     "gdb200_dp_all_reduce": (_ST, [P, P, SZ, SZ, U32]),

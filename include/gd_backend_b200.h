@@ -374,6 +374,21 @@ gd_status gdb200_gemm_profile_read(gd_backend *backend, uint64_t *launches, doub
 /* Overwrite a private buffer larger than L2 so that the next kernel starts with a cold L2. */
 gd_status gdb200_flush_l2(gd_backend *backend);
 
+/* Embedding table gradient with no allocation (no counterpart in the reference). Same result as
+ * gd_backend_embedding_backward, but the FP32 accumulation table is a fixed device array inside the
+ * library instead of a caller-provided scratch tensor, for callers that cannot allocate: a runtime
+ * whose arenas already own all device memory, or an FFI caller holding only raw device pointers.
+ * Pointers are device pointers on the current device; stream is a cudaStream_t or NULL.
+ * Limits: vocab * dim <= gdb200_embedding_backward_static_max_elems() (1 Mi floats, 4 MiB resident on
+ * every GPU that loads the library), else GD_ERR_INVALID_ARGUMENT with a message from
+ * gdb200_embedding_backward_static_error(). Calls share the array: each clears what it uses, and
+ * calls that overlap on the GPU race. The first call on a device resolves the array's device
+ * address and should be made outside of stream capture. */
+gd_status gdb200_embedding_backward_static(void *stream, const void *grad_out, const int32_t *ids, void *grad_table,
+                                           uint64_t ids_count, uint64_t vocab, uint64_t dim, uint32_t dtype);
+const char *gdb200_embedding_backward_static_error(void);
+uint64_t gdb200_embedding_backward_static_max_elems(void);
+
 /* Data-parallel gradient exchange (the reference has no collective; one process per GPU).
  * id_bytes is the 128-byte ncclUniqueId produced by gdb200_dp_unique_id on rank 0. */
 gd_status gdb200_dp_unique_id(void *id_bytes_128);
