@@ -467,3 +467,62 @@ def test_tcgen05_gemm_split_k_weight_gradient(step, m, k, n):
         ctx.flush()
     finally:
         lib.gdb200_set_gemm_mode(ctx.backend, old)
+
+
+# ------------------------------------------------------------------ flash attention at benchmark-like shapes
+@pytest.mark.parametrize("dtype,hq,hkv,dh,window,total", [(F16, 8, 8, 64, 0, 3000), (F16, 8, 8, 64, 256, 3000), (F16, 8, 2, 64, 100, 1500),
+                                                          (BF16, 4, 4, 128, 0, 1200), (BF16, 4, 2, 128, 48, 700)])
+def test_flash_attention_random_segments(step, dtype, hq, hkv, dh, window, total):
+    """Lengths uniform in [16, 512] until `total` tokens, plus trailing rows outside any sequence."""
+    ctx = step
+    sd = storage_name(dtype)
+    r = rng(90)
+    lengths = []
+    while sum(lengths) < total:
+        lengths.append(int(r.integers(16, 513)))
+    cu = make_cu(lengths)
+    n = int(cu[-1]) + 37                                                      # 37 rows behind the last sequence
+    q = rnd_np(r.standard_normal((n, hq, dh)).astype(np.float32), dtype)
+    k = rnd_np(r.standard_normal((n, hkv, dh)).astype(np.float32), dtype)
+    v = rnd_np(r.standard_normal((n, hkv, dh)).astype(np.float32), dtype)
+    go = rnd_np(r.standard_normal((n, hq, dh)).astype(np.float32), dtype)
+    qt, kt, vt, cut = dev(ctx, q, dtype), dev(ctx, k, dtype), dev(ctx, v, dtype), dev(ctx, cu, I32)
+    qt.requires_grad = kt.requires_grad = vt.requires_grad = True
+    out = ops.gd_sdpa_varlen(ctx, qt, kt, vt, cut, causal=True, sliding_window=window, max_seqlen=512)
+    nv = int(cu[-1])
+    want, _ = O.sdpa_varlen_forward(t32(q[:nv]), t32(k[:nv]), t32(v[:nv]), cu, 0.0, True, window, 0, sd)
+    got = host(out)
+    close(got[:nv], want, dtype, scale=2, what="forward")
+    assert np.all(got[nv:] == 0)
+    out.grad = dev(ctx, go, dtype)
+    ctx.run_backward()
+    wdq, wdk, wdv = O.sdpa_varlen_backward(t32(go[:nv]), t32(q[:nv]), t32(k[:nv]), t32(v[:nv]), cu, 0.0, True, window, 0, sd)
+    close(host(qt.grad)[:nv], wdq, dtype, scale=4, what="dq")
+    close(host(kt.grad)[:nv], wdk, dtype, scale=8, what="dk")
+    close(host(vt.grad)[:nv], wdv, dtype, scale=8, what="dv")
+    assert np.all(host(qt.grad)[nv:] == 0) and np.all(host(kt.grad)[nv:] == 0) and np.all(host(vt.grad)[nv:] == 0)
+
+
+def test_flash_backward_without_forward_stats(step):
+    """use_forward_stats = 0: the backward entry recomputes (max, sum) itself."""
+    ctx = step
+    lengths = [70, 200, 33]
+    cu = make_cu(lengths)
+    n, hq, dh = int(cu[-1]), 4, 64
+    r = rng(91)
+    q, k, v, go = (rnd_np(r.standard_normal((n, hq, dh)).astype(np.float32), F16) for _ in range(4))
+    qt, kt, vt, gt, cut = dev(ctx, q, F16), dev(ctx, k, F16), dev(ctx, v, F16), dev(ctx, go, F16), dev(ctx, cu, I32)
+    dq, dk, dv = (ctx.scratch_empty(F16, (n, hq, dh)) for _ in range(3))
+    stats = ctx.scratch_empty(F32, (n, hq, 3))
+    ctx.fill(stats, 0x7FC00000)
+    args = abi.SdpaVarlenArgs(0.125, 1, 0, 0, 512, 0)
+    ctx.check(ctx.lib.gd_backend_sdpa_varlen_backward(ctx.backend, byref(gt.tv()), byref(qt.tv()), byref(kt.tv()), byref(vt.tv()), byref(cut.tv()),
+                                                      byref(dq.tv()), byref(dk.tv()), byref(dv.tv()), byref(stats.tv()), byref(args)), "bwd")
+    wdq, wdk, wdv = O.sdpa_varlen_backward(t32(go), t32(q), t32(k), t32(v), cu, 0.125, True, 0, 0, "f16")
+    close(host(dq), wdq, F16, scale=4)
+    close(host(dk), wdk, F16, scale=8)
+    close(host(dv), wdv, F16, scale=8)
+    # and with no stats tensor at all
+    ctx.check(ctx.lib.gd_backend_sdpa_varlen_backward(ctx.backend, byref(gt.tv()), byref(qt.tv()), byref(kt.tv()), byref(vt.tv()), byref(cut.tv()),
+                                                      byref(dq.tv()), byref(dk.tv()), byref(dv.tv()), None, byref(args)), "bwd no stats")
+    close(host(dq), wdq, F16, scale=4)
