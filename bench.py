@@ -44,9 +44,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="train", choices=["train", "decode"])
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "linear", "sdpa"])
     ap.add_argument("--cpu-sample-seqs", type=int, default=8, help="sequences in the CPU-baseline sample batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--host", default="native", choices=["native", "python"],
+                    help="who enqueues the per-step backend calls: the library's native driver or the Python op capsules")
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 portable kernel only, 2 tcgen05 required")
     return ap.parse_args()
 
@@ -216,7 +218,7 @@ def run_b200(args) -> None:
     if world > 1:
         from gradients_c_b200.host import dp as dpmod
         dp = dpmod.DataParallel(ctx, model, rank, world, dist)
-    trainer = g.Trainer(model, tc, dp=dp)
+    trainer = (g.NativeTrainer if args.host == "native" else g.Trainer)(model, tc, dp=dp)
 
     total_steps = args.warmup + args.steps
     batches = [g.synthetic_batch(cfg, N_SEQS, MIN_LEN, MAX_LEN, seed=10_000 * (rank + 1) + s, pad_to=cfg.context_length)
@@ -231,6 +233,8 @@ def run_b200(args) -> None:
         ctx.flush()
         if dist is not None:
             dist.barrier()
+
+    host_enqueue = [0.0]
 
     def timed_loop(e2e: bool):
         """Runs warm-up + K timed steps; returns (seconds, tokens, launches, last loss)."""
@@ -256,6 +260,7 @@ def run_b200(args) -> None:
                 loss_val = float(loss.read()[()])
             tokens += batches[s].real_tokens
         ev1 = lib.gdb200_event_record(ctx.backend)
+        host_enqueue[0] = time.perf_counter() - t0
         barrier()
         wall = time.perf_counter() - t0
         dev_ms = lib.gdb200_event_elapsed_ms(ev0, ev1)
@@ -273,6 +278,7 @@ def run_b200(args) -> None:
     lib.gdb200_gemm_profile_enable(ctx.backend, 0)
     sec, tokens, launches, loss_val = timed_loop(e2e=False)
     clocks = sampler.stop()
+    host_ms = 1000.0 * host_enqueue[0] / args.steps
     e_sec, e_tokens, _, _ = timed_loop(e2e=True)
 
     # roofline of the dominant kernels (dense contractions): a short separately instrumented run
@@ -308,12 +314,12 @@ def run_b200(args) -> None:
             "ms_per_step": 1000.0 * sec / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": "gpt_lm train step, vocab 2048 ctx 512 d512 L3 H8x64 F1536 untied head, dropout 0.1, softcap 30, AdamW AMP clip",
-                       "global_batch": N_SEQS * world, "seq_len": "U[64,512] packed, padded to x512", "parallelism": f"dp{world}",
+                       "global_batch": N_SEQS * world, "seq_len": "U[64,512] packed, padded to x512", "parallelism": f"dp{world}", "host": args.host,
                        "l2": "per-step working set (>2 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": e_tokens / e_sec, "unit": UNIT, "h2d_bytes_per_step": int(np.mean([b.h2d_bytes for b in batches])),
                     "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
-            "model_tflops": flops * world / sec / 1e12, "loss": loss_val,
+            "model_tflops": flops * world / sec / 1e12, "loss": loss_val, "host_enqueue_ms_per_step": host_ms,
         }
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(g, cfg, tc, args.cpu_sample_seqs)
@@ -324,10 +330,152 @@ def run_b200(args) -> None:
     ctx.destroy()
 
 
+# --------------------------------------------------------------------------------------- kernel-level workloads
+def _event_timed(ctx, fn, steps: int, warmup: int, flush_l2: bool = True) -> float:
+    """Average device milliseconds of fn() over `steps` runs, each bracketed by its own CUDA event
+    pair on the backend stream; L2 is flushed (untimed) before every run."""
+    lib = ctx.lib
+    for _ in range(warmup):
+        fn()
+    ctx.flush()
+    total = 0.0
+    for _ in range(steps):
+        if flush_l2:
+            ctx.check(lib.gdb200_flush_l2(ctx.backend), "flush_l2")
+        e0 = lib.gdb200_event_record(ctx.backend)
+        fn()
+        e1 = lib.gdb200_event_record(ctx.backend)
+        total += lib.gdb200_event_elapsed_ms(e0, e1)
+        lib.gdb200_event_destroy(e0)
+        lib.gdb200_event_destroy(e1)
+    return total / steps
+
+
+def run_linear(args) -> None:
+    """Single F16 linear forward + backward: X[4096,512], W[1536,512] (transposed-weight layout),
+    dY[4096,1536]; outputs Y, dX, dW, db."""
+    import ctypes as C
+    import numpy as np
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    abi = pkg.abi
+    m, k, n = 4096, 512, 1536
+    ctx = pkg.runtime.Context(params_bytes=64 << 20, state_bytes=64 << 20, scratch_bytes=256 << 20, data_bytes=8 << 20)
+    lib = ctx.lib
+    lib.gdb200_set_gemm_mode(ctx.backend, args.gemm_mode)
+    rng = np.random.default_rng(0)
+    x = ctx.from_numpy(ctx.params, abi.F16, rng.standard_normal((m, k)).astype(np.float32))
+    w = ctx.from_numpy(ctx.params, abi.F16, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    dy = ctx.from_numpy(ctx.params, abi.F16, rng.standard_normal((m, n)).astype(np.float32))
+    y, dx, dw, db = (ctx.empty(ctx.params, abi.F16, s) for s in ((m, n), (m, k), (n, k), (n,)))
+    xv, wv, yv, dyv, dxv, dwv = x.mv(m, k), w.mv(n, k), y.mv(m, n), dy.mv(m, n), dx.mv(m, k), dw.mv(n, k)
+    dbv = db.vv()
+
+    def step():
+        ctx.check(lib.gd_backend_matmul_nt(ctx.backend, C.byref(xv), C.byref(wv), C.byref(yv)), "y")
+        ctx.check(lib.gd_backend_matmul(ctx.backend, C.byref(dyv), C.byref(wv), C.byref(dxv)), "dx")
+        ctx.check(lib.gd_backend_matmul_tn(ctx.backend, C.byref(dyv), C.byref(xv), C.byref(dwv)), "dw")
+        ctx.check(lib.gd_backend_reduce_rows(ctx.backend, C.byref(dyv), C.byref(dbv)), "db")
+
+    l0 = ctx.launch_count()
+    ms = _event_timed(ctx, step, args.steps, args.warmup)
+    launches = (ctx.launch_count() - l0) // (args.steps + args.warmup) - 1
+    peaks = measured_peaks()
+    flops = 6.0 * m * n * k
+    tf = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({"metric": "linear_fwd_bwd_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": ms, "higher_is_better": False, "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": "linear fwd+bwd X[4096,512] W[1536,512] dY[4096,1536]", "l2": "flushed before every timed step"},
+                      "gpu_launches": launches,
+                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
+                                   "traffic": None, "peak_source": peaks["source"] + " (burst)", "note": "includes reduce_rows and launch gaps"}}))
+    ctx.destroy()
+
+
+def run_sdpa(args) -> None:
+    """Packed causal sdpa_varlen forward + backward, 8 heads x 64, 32768 tokens in sequences of
+    length U[16,512], q/k/v produced by qkv_split_rope from a fused QKV[T,1536]."""
+    import numpy as np
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    abi, ops = pkg.abi, pkg.ops
+    rng = np.random.default_rng(0)
+    lens, total = [], 32768
+    while sum(lens) < total:
+        lens.append(int(rng.integers(16, 513)))
+    lens[-1] -= sum(lens) - total
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    pos = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+    ctx = pkg.runtime.Context(params_bytes=512 << 20, state_bytes=64 << 20, scratch_bytes=1 << 30, data_bytes=8 << 20)
+    qkv = ctx.from_numpy(ctx.params, abi.F16, rng.standard_normal((total, 1536)).astype(np.float32))
+    go = ctx.from_numpy(ctx.params, abi.F16, rng.standard_normal((total, 8, 64)).astype(np.float32))
+    cut, post = ctx.from_numpy(ctx.params, abi.I32, cu), ctx.from_numpy(ctx.params, abi.I32, pos)
+    window = 0
+    pairs = float(sum(n * (n + 1) // 2 for n in lens)) * 8
+    results = {}
+    for name in ("rope", "fwd", "fwd_bwd"):
+        def step():
+            ctx.begin_step()
+            q, k, v = ops.gd_qkv_split_rope(ctx, qkv, post, 8, 64)
+            if name != "rope":
+                q.requires_grad = k.requires_grad = v.requires_grad = name == "fwd_bwd"
+                out = ops.gd_sdpa_varlen(ctx, q, k, v, cut, causal=True, sliding_window=window, max_seqlen=512)
+                if name == "fwd_bwd":
+                    out.grad = go
+                    ctx.run_backward()
+            ctx.end_step()
+        results[name] = _event_timed(ctx, step, args.steps, args.warmup)
+    fwd_ms = results["fwd"] - results["rope"]
+    bwd_ms = results["fwd_bwd"] - results["fwd"]
+    peaks = measured_peaks()
+    tf = 14.0 * 64 * pairs / ((fwd_ms + bwd_ms) * 1e-3) / 1e12
+    print(json.dumps({"metric": "sdpa_varlen_fwd_bwd_ms", "value": fwd_ms + bwd_ms, "unit": "ms", "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": fwd_ms + bwd_ms, "higher_is_better": False, "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": "sdpa_varlen fwd+bwd H8 Dh64 T32768 lengths U[16,512] causal", "segments": len(lens),
+                                 "l2": "flushed before every timed step"},
+                      "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "qkv_split_rope_ms": results["rope"],
+                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
+                                   "traffic": None, "peak_source": peaks["source"] + " (burst)", "flops": "14*Dh*pairs (FlashAttention convention)"}}))
+    ctx.destroy()
+
+
+def run_decode(args) -> None:
+    """KV-cache greedy decode: 64 prompts x 256 tokens, packed prefill, 256 decode steps, cache capacity 512."""
+    import numpy as np
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    g = pkg.gpt_lm
+    cfg = g.GptConfig.baseline()
+    cfg.dropout_p = 0.0
+    ctx = pkg.runtime.Context(params_bytes=256 << 20, state_bytes=1 << 30, scratch_bytes=2 << 30, data_bytes=16 << 20)
+    model = g.GptLm(ctx, cfg, g.init_params(cfg, seed=0))
+    model.training = False
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(64, 256)).astype(np.int32)
+    new_tokens = 256
+    g.greedy_generate(model, prompts[:, :32], 4, 512)  # warm-up (kernel loading)
+    l0 = ctx.launch_count()
+    t0 = time.perf_counter()
+    out = g.greedy_generate(model, prompts, new_tokens, 512)
+    ctx.flush()
+    dt = time.perf_counter() - t0
+    value = 64 * new_tokens / dt
+    print(json.dumps({"metric": "gpt_lm_kv_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": new_tokens, "warmup": 1,
+                      "ms_per_step": 1000.0 * dt / new_tokens, "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": "greedy KV decode, 64 prompts x 256, 256 new tokens, cache 512, host argmax per step (prefill included)"},
+                      "gpu_launches": ctx.launch_count() - l0, "checksum": int(out.astype(np.int64).sum())}))
+    ctx.destroy()
+
+
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "linear":
+        run_linear(args)
+    elif args.workload == "sdpa":
+        run_sdpa(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_b200(args)
 

@@ -233,11 +233,11 @@ __device__ __forceinline__ uint64_t gdb_splitmix64(uint64_t x)
 // ---- entry points implemented in other translation units and shared internally ----
 gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb,
                             const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
-                            const gd_backend_vector_view *bias, const gd_backend_matrix_view *y);
+                            const gd_backend_vector_view *bias, const gd_backend_matrix_view *y, int bias_mode = 1);
 // tcgen05 path: returns GD_ERR_UNSUPPORTED when the shape/alignment cannot use it.
 gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype,
                            const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
-                           void *c, size_t ldc_bytes, const void *bias,
+                           void *c, size_t ldc_bytes, const void *bias, int bias_mode,
                            uint32_t M, uint32_t N, uint32_t K);
 void gdb_tmap_cache_destroy(gd_backend *be);
 void gdb_dp_destroy(gd_backend *be);

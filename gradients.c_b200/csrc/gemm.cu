@@ -7,6 +7,7 @@
 // (src/ops/_shared/gemm/metal_gemm_common.h:124-133); reduce_rows accumulates in FP32 and
 // rounds once (src/ops/linear/metal_linear.metal:33-52).
 #include "common.cuh"
+#include "colreduce.cuh"
 
 // Optional per-launch timing of the dense contractions (benchmark instrumentation): when enabled,
 // every dispatch is bracketed by a CUDA event pair on the backend stream and its algorithmic
@@ -31,7 +32,7 @@ __global__ void gemm_portable_kernel(const T *__restrict__ a, size_t sam, size_t
                                      const T *__restrict__ b, size_t sbk, size_t sbn,
                                      T *__restrict__ c, size_t ldc, const T *__restrict__ bias,
                                      unsigned M, unsigned N, unsigned K,
-                                     size_t batch_a, size_t batch_b, size_t batch_c)
+                                     size_t batch_a, size_t batch_b, size_t batch_c, int bias_mode)
 {
     __shared__ float as[TK][TM + 4];
     __shared__ float bs[TK][TN + 4];
@@ -97,8 +98,12 @@ __global__ void gemm_portable_kernel(const T *__restrict__ a, size_t sam, size_t
         for (int j = 0; j < 4; ++j) {
             const unsigned gn = n0 + tx * 4 + j;
             if (gn < N) {
-                const float bv = bias != nullptr ? gdb_io<T>::ld(bias, gn) : 0.0f;
-                gdb_io<T>::st(c, (size_t)gm * ldc + gn, acc[i][j] + bv);
+                float val = acc[i][j];
+                if (bias != nullptr) {
+                    if (bias_mode == 2) val = gdb_io<T>::rnd(val);
+                    val += gdb_io<T>::ld(bias, gn);
+                }
+                gdb_io<T>::st(c, (size_t)gm * ldc + gn, val);
             }
         }
     }
@@ -159,14 +164,14 @@ bool mv_ok(const gd_backend_matrix_view *v, size_t es)
 template <typename T>
 void launch_portable(gd_backend *be, int ta, int tb, const void *a, size_t lda, const void *b, size_t ldb,
                      void *c, size_t ldc, const void *bias, unsigned M, unsigned N, unsigned K,
-                     unsigned batch, size_t ba, size_t bb, size_t bc)
+                     unsigned batch, size_t ba, size_t bb, size_t bc, int bias_mode)
 {
     // lda/ldb/ldc in elements. ta: A stored [K, M]; tb: B stored [N, K].
     const size_t sam = ta ? 1 : lda, sak = ta ? lda : 1;
     const size_t sbk = tb ? 1 : ldb, sbn = tb ? ldb : 1;
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, batch);
     gemm_portable_kernel<T><<<grid, 256, 0, be->stream>>>((const T *)a, sam, sak, (const T *)b, sbk, sbn, (T *)c, ldc,
-                                                           (const T *)bias, M, N, K, ba, bb, bc);
+                                                           (const T *)bias, M, N, K, ba, bb, bc, bias_mode);
 }
 
 }  // namespace
@@ -174,7 +179,7 @@ void launch_portable(gd_backend *be, int ta, int tb, const void *a, size_t lda, 
 // x: [M, K] (or [K, M] when ta), w: [K, N] (or [N, K] when tb), y: [M, N].
 gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb, const gd_backend_matrix_view *x,
                             const gd_backend_matrix_view *w, const gd_backend_vector_view *bias,
-                            const gd_backend_matrix_view *y)
+                            const gd_backend_matrix_view *y, int bias_mode)
 {
     if (be == NULL || x == NULL || w == NULL || y == NULL) {
         return GD_ERR_INVALID_ARGUMENT;
@@ -234,7 +239,7 @@ gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb, const gd_backend_mat
         }
     } scope(be, 2.0 * M * N * K, (double)es * ((double)M * K + (double)K * N + (double)M * N));
     if (be->gemm_mode != 1 && dt != GDB_DTYPE_F32) {
-        gd_status st = gdb_gemm_tcgen05(be, ta, tb, dt, ap, x->row_bytes, wp, w->row_bytes, cp, y->row_bytes, bp, M, N, K);
+        gd_status st = gdb_gemm_tcgen05(be, ta, tb, dt, ap, x->row_bytes, wp, w->row_bytes, cp, y->row_bytes, bp, bias_mode, M, N, K);
         if (st != GD_ERR_UNSUPPORTED) {
             return st;
         }
@@ -245,11 +250,11 @@ gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb, const gd_backend_mat
         return GD_ERR_UNSUPPORTED;
     }
     if (dt == GDB_DTYPE_F16) {
-        launch_portable<__half>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0);
+        launch_portable<__half>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0, bias_mode);
     } else if (dt == GDB_DTYPE_BF16) {
-        launch_portable<__nv_bfloat16>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0);
+        launch_portable<__nv_bfloat16>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0, bias_mode);
     } else {
-        launch_portable<float>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0);
+        launch_portable<float>(be, ta, tb, ap, x->row_bytes / es, wp, w->row_bytes / es, cp, y->row_bytes / es, bp, M, N, K, 1, 0, 0, 0, bias_mode);
     }
     return gdb_launched(be, "gemm_portable");
 }
@@ -375,6 +380,14 @@ gd_status gd_backend_linear(gd_backend *be, const gd_backend_matrix_view *x, con
 {
     return gdb_gemm_dispatch(be, 0, 0, x, w, bias, y);
 }
+// Additive: y = round(round(x w^T) + bias) in one pass, bit-identical to gd_backend_matmul_nt followed
+// by gd_backend_add of the bias row (the sequence of the reference's linear_transposed_weight capsule,
+// src/ops/linear_transposed_weight/core_linear_transposed_weight.c:51-79) without the extra
+// write and read of the [M, N] product.
+gd_status gdb200_matmul_nt_bias(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_vector_view *bias, const gd_backend_matrix_view *y)
+{
+    return gdb_gemm_dispatch(be, 0, 1, x, w, bias, y, 2);
+}
 gd_status gd_backend_batched_matmul(gd_backend *be, const gd_backend_batched_matrix_view *x, const gd_backend_batched_matrix_view *w, const gd_backend_batched_matrix_view *y)
 {
     return batched_dispatch(be, 0, 0, x, w, y);
@@ -402,6 +415,14 @@ gd_status gd_backend_reduce_rows(gd_backend *be, const gd_backend_matrix_view *x
         return GD_ERR_INVALID_ARGUMENT;
     }
     const size_t rows = x->rows, cols = x->cols, ld = x->row_bytes / es;
+    if (es == 2U && gdb_colreduce::usable(x->buffer->dptr + x->offset, ld, NULL, 0, cols) && cols * sizeof(float) <= be->ws_bytes) {
+        const size_t cap = be->ws_bytes / (cols * sizeof(float));
+        const void *xa = x->buffer->dptr + x->offset;
+        void *ya = y->buffer->dptr + y->offset;
+        return dt == GDB_DTYPE_F16
+                   ? gdb_colreduce::run<__half, false>(be, xa, ld, NULL, 0, NULL, (float *)be->ws, cap, ya, rows, cols)
+                   : gdb_colreduce::run<__nv_bfloat16, false>(be, xa, ld, NULL, 0, NULL, (float *)be->ws, cap, ya, rows, cols);
+    }
     const unsigned col_blocks = (unsigned)((cols + 255U) / 256U);
     size_t blocks = ((size_t)be->sm_count * 8U + col_blocks - 1U) / col_blocks;
     if (blocks > (rows + 31U) / 32U) {

@@ -178,7 +178,7 @@ template <typename T, int BN, int STAGES, bool A_MN, bool B_MN, bool SPLITK>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, T *__restrict__ c,
                     size_t ldc, const T *__restrict__ bias, float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K,
-                    uint32_t k_iters_per_split, int *err_flag)
+                    uint32_t k_iters_per_split, int bias_mode, int *err_flag)
 {
     using plan = smem_plan<BN, STAGES>;
     extern __shared__ unsigned char smem_raw[];
@@ -312,7 +312,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
                                     f[e] = __uint_as_float(v[j + e]);
-                                    if (bias != nullptr) f[e] += gdb_io<T>::ld(bias, col0 + j + e);
+                                    if (bias != nullptr) {
+                                        // mode 2 reproduces "round the product, then a rounded bias add"
+                                        if (bias_mode == 2) f[e] = gdb_io<T>::rnd(f[e]);
+                                        f[e] += gdb_io<T>::ld(bias, col0 + j + e);
+                                    }
                                 }
                                 uint4 o;
                                 o.x = half_pack<T>::pack(f[0], f[1]);
@@ -337,7 +341,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 // out[m, n] = round(sum_z partial[z, m, n] + bias[n])
 template <typename T>
 __global__ void splitk_reduce_kernel(const float *__restrict__ partial, T *__restrict__ c, size_t ldc, const T *__restrict__ bias,
-                                     uint32_t M, uint32_t N, uint32_t splits)
+                                     uint32_t M, uint32_t N, uint32_t splits, int bias_mode)
 {
     const size_t quads = (size_t)M * (N / 4), stride = (size_t)gridDim.x * blockDim.x;
     for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += stride) {
@@ -351,6 +355,12 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, T *__res
             acc.w += p.w;
         }
         if (bias != nullptr) {
+            if (bias_mode == 2) {
+                acc.x = gdb_io<T>::rnd(acc.x);
+                acc.y = gdb_io<T>::rnd(acc.y);
+                acc.z = gdb_io<T>::rnd(acc.z);
+                acc.w = gdb_io<T>::rnd(acc.w);
+            }
             acc.x += gdb_io<T>::ld(bias, col);
             acc.y += gdb_io<T>::ld(bias, col + 1);
             acc.z += gdb_io<T>::ld(bias, col + 2);
@@ -365,7 +375,7 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, T *__res
 
 template <typename T, int BN, int STAGES, bool A_MN, bool B_MN, bool SPLITK>
 gd_status launch(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, void *c, size_t ldc, const void *bias,
-                 float *partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits, uint32_t k_per_split)
+                 float *partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits, uint32_t k_per_split, int bias_mode)
 {
     using plan = smem_plan<BN, STAGES>;
     auto kern = gemm_tcgen05_kernel<T, BN, STAGES, A_MN, B_MN, SPLITK>;
@@ -378,18 +388,18 @@ gd_status launch(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, v
         configured = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, splits);
-    kern<<<grid, 192, plan::TOTAL, be->stream>>>(ta, tb, (T *)c, ldc, (const T *)bias, partial, M, N, K, k_per_split, be->err_flag);
+    kern<<<grid, 192, plan::TOTAL, be->stream>>>(ta, tb, (T *)c, ldc, (const T *)bias, partial, M, N, K, k_per_split, bias_mode, be->err_flag);
     return gdb_launched(be, "gemm_tcgen05");
 }
 
 template <typename T, int BN, int STAGES>
 gd_status dispatch_major(gd_backend *be, int ta, int tb, const CUtensorMap &ma, const CUtensorMap &mb, void *c, size_t ldc,
-                         const void *bias, float *partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits, uint32_t kps)
+                         const void *bias, float *partial, uint32_t M, uint32_t N, uint32_t K, uint32_t splits, uint32_t kps, int bias_mode)
 {
     const bool sk = splits > 1;
 #define GDB_GO(AM, BMJ)                                                                                              \
-    (sk ? launch<T, BN, STAGES, AM, BMJ, true>(be, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps)            \
-        : launch<T, BN, STAGES, AM, BMJ, false>(be, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps))
+    (sk ? launch<T, BN, STAGES, AM, BMJ, true>(be, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps, bias_mode) \
+        : launch<T, BN, STAGES, AM, BMJ, false>(be, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps, bias_mode))
     if (ta) {
         return tb ? GDB_GO(true, false) : GDB_GO(true, true);
     }
@@ -401,7 +411,7 @@ gd_status dispatch_major(gd_backend *be, int ta, int tb, const CUtensorMap &ma, 
 
 // ta: A stored [K, M] (MN-major); tb: B stored [N, K] (K-major). Leading dimensions in bytes.
 gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b,
-                           size_t ldb_bytes, void *c, size_t ldc_bytes, const void *bias, uint32_t M, uint32_t N, uint32_t K)
+                           size_t ldb_bytes, void *c, size_t ldc_bytes, const void *bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K)
 {
     if (dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) {
         return GD_ERR_UNSUPPORTED;
@@ -426,7 +436,7 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const
     const uint32_t tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     const uint32_t total_k = (K + BK - 1) / BK;
     uint32_t splits = 1;
-    if (tiles * 2U <= (uint32_t)be->sm_count && total_k >= 16U) {
+    if (tiles < (uint32_t)be->sm_count && total_k >= 16U) {
         splits = ((uint32_t)be->sm_count * 2U + tiles - 1U) / tiles;
         if (splits > total_k / 4U) splits = total_k / 4U;
         if (splits > 32U) splits = 32U;
@@ -439,20 +449,20 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const
     const size_t ldc = ldc_bytes / 2U;
     gd_status st;
     if (dtype == GDB_DTYPE_F16) {
-        st = bn == 256 ? dispatch_major<__half, 256, 4>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps)
-                       : dispatch_major<__half, 128, 3>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps);
+        st = bn == 256 ? dispatch_major<__half, 256, 4>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps, bias_mode)
+                       : dispatch_major<__half, 128, 3>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps, bias_mode);
     } else {
-        st = bn == 256 ? dispatch_major<__nv_bfloat16, 256, 4>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps)
-                       : dispatch_major<__nv_bfloat16, 128, 3>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps);
+        st = bn == 256 ? dispatch_major<__nv_bfloat16, 256, 4>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps, bias_mode)
+                       : dispatch_major<__nv_bfloat16, 128, 3>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps, bias_mode);
     }
     if (st != GD_OK || splits == 1U) {
         return st;
     }
     const size_t quads = (size_t)M * (N / 4U);
     if (dtype == GDB_DTYPE_F16) {
-        splitk_reduce_kernel<__half><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__half *)c, ldc, (const __half *)bias, M, N, splits);
+        splitk_reduce_kernel<__half><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__half *)c, ldc, (const __half *)bias, M, N, splits, bias_mode);
     } else {
-        splitk_reduce_kernel<__nv_bfloat16><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits);
+        splitk_reduce_kernel<__nv_bfloat16><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits, bias_mode);
     }
     return gdb_launched(be, "gemm_splitk_reduce");
 }

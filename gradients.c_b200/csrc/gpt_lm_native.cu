@@ -1,0 +1,628 @@
+// Native sequencing of one gpt_lm training step over the backend entries (host code only).
+//
+// The reference drives a training step from C (src/train/trainer.c:75-223 ->
+// examples/gpt_lm/gpt_lm_shared.c:602-823 -> op capsules -> tape backward -> src/optim/adamw.c:2163);
+// a Python host issuing the same ~170 backend calls per step costs more host time than the B200
+// needs to execute them. This file issues exactly the same gd_backend_* call sequence as
+// host/gpt_lm.py + host/ops.py + host/optim.py (same scratch tensors, same rounding points, same
+// gradient-accumulation order), with a bump allocator over the caller's scratch buffer, so the two
+// hosts are interchangeable and are checked against each other in the tests. Parameters, optimizer
+// state and the AMP scaler state are laid out by the caller and described by gdb200_gpt_spec.
+//
+// With a data-parallel communicator attached (gdb200_dp_init) the parameter gradients of one block
+// are allocated contiguously and summed across ranks with ONE all-reduce per block, issued as soon
+// as the block's backward has been enqueued, so the exchange overlaps the backward of the blocks
+// below it; 1/world is folded into the inverse loss scale used by the clip/AdamW kernels.
+#include "common.cuh"
+
+#include <math.h>
+#include <vector>
+
+namespace {
+
+struct Ten {
+    gd_backend_buffer *buf;
+    size_t off;
+    uint32_t dt;
+    uint32_t rank;
+    int64_t shape[4];
+    size_t count() const
+    {
+        size_t n = 1;
+        for (uint32_t i = 0; i < rank; ++i) n *= (size_t)shape[i];
+        return n;
+    }
+};
+
+gd_backend_tensor_view tv(const Ten &t)
+{
+    gd_backend_tensor_view v;
+    memset(&v, 0, sizeof(v));
+    v.buffer = t.buf;
+    v.offset = t.off;
+    v.count = t.count();
+    v.dtype = t.dt;
+    v.rank = t.rank;
+    int64_t stride = 1;
+    for (int d = (int)t.rank - 1; d >= 0; --d) {
+        v.shape[d] = t.shape[d];
+        v.strides[d] = stride;
+        stride *= t.shape[d];
+    }
+    return v;
+}
+
+gd_backend_matrix_view mv(const Ten &t, uint32_t rows, uint32_t cols, size_t row_offset = 0)
+{
+    gd_backend_matrix_view v;
+    const size_t es = gdb_dtype_size(t.dt);
+    v.buffer = t.buf;
+    v.row_bytes = (size_t)cols * es;
+    v.offset = t.off + row_offset * v.row_bytes;
+    v.rows = rows;
+    v.cols = cols;
+    v.dtype = t.dt;
+    return v;
+}
+
+gd_backend_vector_view vv(const Ten &t, size_t start, uint32_t length)
+{
+    gd_backend_vector_view v;
+    v.buffer = t.buf;
+    v.offset = t.off + start * gdb_dtype_size(t.dt);
+    v.length = length;
+    v.dtype = t.dt;
+    return v;
+}
+
+uint64_t splitmix64(uint64_t x)
+{
+    x += 0x9E3779B97F4A7C15ULL;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBULL;
+    return x ^ (x >> 31);
+}
+
+constexpr uint64_t SITE_EMBED = 0x9E3779B97F4A7C15ULL, SITE_ATTN = 0xBF58476D1CE4E5B9ULL, SITE_MLP = 0x94D049BB133111EBULL;
+
+struct Step {
+    gd_backend *be;
+    const gdb200_gpt_spec *s;
+    size_t top;
+    gd_status st;
+    const char *where;
+
+    Ten alloc(uint32_t dt, std::initializer_list<int64_t> shape, size_t align = 256)
+    {
+        Ten t;
+        memset(&t, 0, sizeof(t));
+        t.buf = s->scratch_buffer;
+        t.dt = dt;
+        t.rank = (uint32_t)shape.size();
+        int i = 0;
+        for (int64_t d : shape) t.shape[i++] = d;
+        const size_t bytes = (t.count() == 0 ? 1 : t.count()) * gdb_dtype_size(dt);
+        const size_t off = (top + align - 1) & ~(align - 1);
+        if (off + bytes > s->scratch_bytes) {
+            if (st == GD_OK) {
+                st = GD_ERR_OUT_OF_MEMORY;
+                where = "scratch arena";
+            }
+            t.off = 0;
+            return t;
+        }
+        t.off = off;
+        top = off + bytes;
+        return t;
+    }
+    bool ok(gd_status r, const char *what)
+    {
+        if (r != GD_OK && st == GD_OK) {
+            st = r;
+            where = what;
+        }
+        return st == GD_OK;
+    }
+    Ten param(int idx, std::initializer_list<int64_t> shape) const
+    {
+        Ten t;
+        memset(&t, 0, sizeof(t));
+        t.buf = s->params_buffer;
+        t.off = s->param_offset[idx];
+        t.dt = s->dtype;
+        t.rank = (uint32_t)shape.size();
+        int i = 0;
+        for (int64_t d : shape) t.shape[i++] = d;
+        return t;
+    }
+    Ten fill(Ten t, uint32_t pattern)
+    {
+        ok(gd_backend_fill(be, t.buf, t.off, t.count(), gdb_dtype_size(t.dt), pattern), "fill");
+        return t;
+    }
+    // dst += src with the storage rounding after the add (gradient accumulation)
+    void accumulate(const Ten &dst, const Ten &src) { ok(gd_backend_accumulate(be, dst.buf, dst.off, src.buf, src.off, src.count(), src.dt), "accumulate"); }
+};
+
+gd_backend_rms_norm_args rms_args(int64_t rows, int64_t cols, float eps)
+{
+    gd_backend_rms_norm_args a;
+    memset(&a, 0, sizeof(a));
+    const uint64_t rb = rows >= 4096 ? 128U : 64U;  // src/ops/rms_norm/core_rms_norm.c:9-11
+    a.rows = (uint64_t)rows;
+    a.cols = (uint64_t)cols;
+    a.row_blocks = ((uint64_t)rows + rb - 1U) / rb;
+    a.eps = eps;
+    a.simdgroups = 8;
+    a.wgrad_simdgroups = 8;
+    a.wgrad_row_block = (uint32_t)rb;
+    return a;
+}
+
+struct LayerSave {
+    Ten x, normed, inv1, qkv, q, k, v, stats, attn, mask1, resid, normed2, inv2, up_gate, act, mask2;
+};
+
+// y = x w^T + b (fused, reference rounding), w stored [n, k]
+Ten linear_t(Step &c, const Ten &x, const Ten &w, const Ten &b, int64_t m, int64_t k, int64_t n)
+{
+    Ten y = c.alloc(x.dt, {m, n});
+    gd_backend_matrix_view xm = mv(x, (uint32_t)m, (uint32_t)k), wm = mv(w, (uint32_t)n, (uint32_t)k), ym = mv(y, (uint32_t)m, (uint32_t)n);
+    gd_backend_vector_view bv = vv(b, 0, (uint32_t)n);
+    c.ok(gdb200_matmul_nt_bias(c.be, &xm, &wm, &bv, &ym), "matmul_nt_bias");
+    return y;
+}
+
+// backward of y = x w^T + b: dx = g w, dw = g^T x, db = colsum(g)
+void linear_t_backward(Step &c, const Ten &x, const Ten &w, const Ten &g, int64_t m, int64_t k, int64_t n, Ten *dx, const Ten &dw, const Ten &db)
+{
+    gd_backend_matrix_view gm = mv(g, (uint32_t)m, (uint32_t)n), wm = mv(w, (uint32_t)n, (uint32_t)k), xm = mv(x, (uint32_t)m, (uint32_t)k);
+    if (dx != NULL) {
+        *dx = c.alloc(x.dt, {m, k});
+        gd_backend_matrix_view dxm = mv(*dx, (uint32_t)m, (uint32_t)k);
+        c.ok(gd_backend_matmul(c.be, &gm, &wm, &dxm), "matmul(dX)");
+    }
+    gd_backend_matrix_view dwm = mv(dw, (uint32_t)n, (uint32_t)k);
+    c.ok(gd_backend_matmul_tn(c.be, &gm, &xm, &dwm), "matmul_tn(dW)");
+    gd_backend_vector_view dbv = vv(db, 0, (uint32_t)n);
+    c.ok(gd_backend_reduce_rows(c.be, &gm, &dbv), "reduce_rows(db)");
+}
+
+Ten rms_forward(Step &c, const Ten &x, const Ten &w, int64_t rows, int64_t cols, Ten *inv)
+{
+    gd_backend_rms_norm_args a = rms_args(rows, cols, c.s->rms_eps);
+    Ten out = c.alloc(x.dt, {rows, cols});
+    *inv = c.alloc(GDB_DTYPE_F32, {rows});
+    gd_backend_tensor_view xv = tv(x), wv = tv(w), ov = tv(out), iv = tv(*inv);
+    c.ok(gd_backend_rms_norm_forward_stats(c.be, &xv, &wv, &ov, &iv, &a), "rms_norm_forward_stats");
+    return out;
+}
+
+Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten &g, int64_t rows, int64_t cols, const Ten &dw)
+{
+    gd_backend_rms_norm_args a = rms_args(rows, cols, c.s->rms_eps);
+    Ten dx = c.alloc(x.dt, {rows, cols});
+    gd_backend_tensor_view xv = tv(x), wv = tv(w), iv = tv(inv), gv = tv(g), dxv = tv(dx), dwv = tv(dw);
+    c.ok(gd_backend_rms_norm_backward_stats(c.be, &xv, &wv, &iv, &gv, &dxv, &a), "rms_norm_backward_stats");
+    Ten partial = c.alloc(GDB_DTYPE_F32, {(int64_t)a.row_blocks, cols});
+    gd_backend_tensor_view pv = tv(partial);
+    c.ok(gd_backend_rms_norm_weight_backward_stats(c.be, &xv, &iv, &gv, &dwv, &pv, &a), "rms_norm_weight_backward_stats");
+    return dx;
+}
+
+Ten dropout_mask_backward(Step &c, const Ten &mask, const Ten &g, float scale)
+{
+    Ten dx = c.alloc(g.dt, {g.shape[0], g.shape[1]});
+    gd_backend_tensor_view mvw = tv(mask), gv = tv(g), dv = tv(dx);
+    c.ok(gd_backend_dropout_backward_mask(c.be, &mvw, &gv, &dv, scale), "dropout_backward_mask");
+    return dx;
+}
+
+}  // namespace
+
+extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec *s, const gdb200_gpt_batch *batch,
+                                           uint64_t step, float lr, size_t *loss_offset, size_t *scratch_used)
+{
+    if (be == NULL || s == NULL || batch == NULL || loss_offset == NULL || s->n_layers <= 0 || s->n_layers > GDB200_GPT_MAX_LAYERS ||
+        batch->n_tokens <= 0 || s->n_heads * s->head_dim != s->d_model) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    Step c;
+    c.be = be;
+    c.s = s;
+    c.top = 0;
+    c.st = GD_OK;
+    c.where = "";
+    const int64_t T = batch->n_tokens, D = s->d_model, F = s->mlp_hidden, V = s->vocab_size, H = s->n_heads, Dh = s->head_dim;
+    const int L = s->n_layers;
+    const uint32_t dt = s->dtype;
+    const bool drop = s->dropout_p > 0.0f;
+    const float drop_scale = 1.0f / (1.0f - s->dropout_p);
+    const int P_FINAL = 1 + 10 * L, P_LMW = s->tied_lm_head ? 0 : P_FINAL + 1, P_LMB = P_FINAL + (s->tied_lm_head ? 1 : 2);
+    const int n_params = P_LMB + 1;
+    if (n_params != s->n_params) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    auto data_tensor = [&](size_t off, int64_t n) {
+        Ten t;
+        memset(&t, 0, sizeof(t));
+        t.buf = batch->buffer;
+        t.off = off;
+        t.dt = GDB_DTYPE_I32;
+        t.rank = 1;
+        t.shape[0] = n;
+        return t;
+    };
+    const Ten ids = data_tensor(batch->input_ids_offset, T), tgt = data_tensor(batch->targets_offset, T);
+    const Ten pos = data_tensor(batch->positions_offset, T), cu = data_tensor(batch->cu_seqlens_offset, batch->n_cu);
+    auto seed_of = [&](uint64_t site, uint64_t layer) { return splitmix64(s->dropout_seed ^ site ^ (layer << 32) ^ step); };
+
+    // ---- AMP scaler: clamp the scale, clear found_inf (first use of the step) ----
+    gd_backend_amp_state_desc amp;
+    memset(&amp, 0, sizeof(amp));
+    amp.scale_buffer = s->state_buffer;
+    amp.scale_offset = s->amp_scale_offset;
+    amp.flags_buffer = s->state_buffer;
+    amp.flags_offset = s->amp_flags_offset;
+    amp.growth_factor = s->amp_growth_factor;
+    amp.backoff_factor = s->amp_backoff_factor;
+    amp.min_scale = s->amp_min_scale;
+    amp.max_scale = s->amp_max_scale;
+    amp.growth_interval = s->amp_growth_interval;
+
+    // ---------------------------------------------------------------- forward
+    const Ten emb_w = c.param(0, {V, D});
+    Ten x0 = c.alloc(dt, {T, D});
+    gd_backend_embedding_args ea = {(uint64_t)T, (uint64_t)V, (uint64_t)D};
+    {
+        gd_backend_tensor_view a = tv(emb_w), b = tv(ids), o = tv(x0);
+        c.ok(gd_backend_embedding_forward(be, &a, &b, &o, &ea), "embedding_forward");
+    }
+    Ten x = x0, emb_mask;
+    memset(&emb_mask, 0, sizeof(emb_mask));
+    if (drop) {
+        x = c.alloc(dt, {T, D});
+        emb_mask = c.alloc(GDB_DTYPE_U8, {T, D});
+        gd_backend_tensor_view a = tv(x0), y = tv(x), m = tv(emb_mask);
+        c.ok(gd_backend_dropout_forward(be, &a, &y, &m, s->dropout_p, splitmix64(s->dropout_seed ^ SITE_EMBED ^ step)), "dropout_forward");
+    }
+    std::vector<LayerSave> saves((size_t)L);
+    gd_backend_rope_args rope = {s->rope_theta, (uint32_t)Dh, 0U};
+    gd_backend_sdpa_varlen_args sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.scale = (float)(1.0 / sqrt((double)Dh));
+    sa.causal = 1;
+    sa.sliding_window = (uint32_t)s->sdpa_window;
+    sa.max_seqlen = (uint32_t)s->context_length;
+    for (int i = 0; i < L && c.st == GD_OK; ++i) {
+        LayerSave &sv = saves[(size_t)i];
+        const int pb = 1 + 10 * i;
+        sv.x = x;
+        sv.normed = rms_forward(c, x, c.param(pb + 0, {D}), T, D, &sv.inv1);
+        sv.qkv = linear_t(c, sv.normed, c.param(pb + 1, {3 * D, D}), c.param(pb + 2, {3 * D}), T, D, 3 * D);
+        sv.q = c.alloc(dt, {T, H, Dh});
+        sv.k = c.alloc(dt, {T, H, Dh});
+        sv.v = c.alloc(dt, {T, H, Dh});
+        {
+            gd_backend_tensor_view a = tv(sv.qkv), p = tv(pos), q = tv(sv.q), k = tv(sv.k), v = tv(sv.v);
+            c.ok(gd_backend_qkv_split_rope_forward(be, &a, &p, &q, &k, &v, (uint32_t)H, (uint32_t)Dh, &rope), "qkv_split_rope_forward");
+        }
+        sv.attn = c.alloc(dt, {T, D});
+        sv.stats = c.alloc(GDB_DTYPE_F32, {T, H, 3});
+        {
+            Ten attn3 = sv.attn;
+            attn3.rank = 3;
+            attn3.shape[0] = T;
+            attn3.shape[1] = H;
+            attn3.shape[2] = Dh;
+            gd_backend_tensor_view q = tv(sv.q), k = tv(sv.k), v = tv(sv.v), cv = tv(cu), o = tv(attn3), stv = tv(sv.stats);
+            sa.use_forward_stats = 0;
+            c.ok(gd_backend_sdpa_varlen(be, &q, &k, &v, &cv, &o, &stv, &sa), "sdpa_varlen");
+        }
+        Ten proj = linear_t(c, sv.attn, c.param(pb + 3, {D, D}), c.param(pb + 4, {D}), T, D, D);
+        sv.resid = c.alloc(dt, {T, D});
+        memset(&sv.mask1, 0, sizeof(sv.mask1));
+        memset(&sv.mask2, 0, sizeof(sv.mask2));
+        if (drop) {
+            sv.mask1 = c.alloc(GDB_DTYPE_U8, {T, D});
+            gd_backend_tensor_view r = tv(x), a = tv(proj), y = tv(sv.resid), m = tv(sv.mask1);
+            c.ok(gd_backend_dropout_add_forward(be, &r, &a, &y, &m, s->dropout_p, seed_of(SITE_ATTN, (uint64_t)i)), "dropout_add_forward");
+        } else {
+            gd_backend_tensor_view r = tv(x), a = tv(proj), y = tv(sv.resid);
+            c.ok(gd_backend_add(be, &r, &a, &y), "add");
+        }
+        sv.normed2 = rms_forward(c, sv.resid, c.param(pb + 5, {D}), T, D, &sv.inv2);
+        sv.up_gate = linear_t(c, sv.normed2, c.param(pb + 6, {2 * F, D}), c.param(pb + 7, {2 * F}), T, D, 2 * F);
+        sv.act = c.alloc(dt, {T, F});
+        {
+            gd_backend_tensor_view a = tv(sv.up_gate), o = tv(sv.act);
+            c.ok(gd_backend_swiglu_split_forward(be, &a, &o), "swiglu_split_forward");
+        }
+        Ten mlp = c.alloc(dt, {T, D});
+        {
+            const Ten w = c.param(pb + 8, {F, D}), b = c.param(pb + 9, {D});
+            gd_backend_matrix_view am = mv(sv.act, (uint32_t)T, (uint32_t)F), wm = mv(w, (uint32_t)F, (uint32_t)D), ym = mv(mlp, (uint32_t)T, (uint32_t)D);
+            gd_backend_vector_view bv = vv(b, 0, (uint32_t)D);
+            c.ok(gd_backend_linear(be, &am, &wm, &bv, &ym), "linear(down_proj)");
+        }
+        Ten out = c.alloc(dt, {T, D});
+        if (drop) {
+            sv.mask2 = c.alloc(GDB_DTYPE_U8, {T, D});
+            gd_backend_tensor_view r = tv(sv.resid), a = tv(mlp), y = tv(out), m = tv(sv.mask2);
+            c.ok(gd_backend_dropout_add_forward(be, &r, &a, &y, &m, s->dropout_p, seed_of(SITE_MLP, (uint64_t)i)), "dropout_add_forward");
+        } else {
+            gd_backend_tensor_view r = tv(sv.resid), a = tv(mlp), y = tv(out);
+            c.ok(gd_backend_add(be, &r, &a, &y), "add");
+        }
+        x = out;
+    }
+    Ten inv_f;
+    const Ten final_w = c.param(P_FINAL, {D});
+    Ten final_norm = rms_forward(c, x, final_w, T, D, &inv_f);
+
+    // ---- fused LM cross entropy (chunked over the vocabulary, src/ops/lm_cross_entropy/core_lm_cross_entropy.c:452-675) ----
+    const Ten lm_w = c.param(P_LMW, {V, D}), lm_b = c.param(P_LMB, {V});
+    Ten row_loss = c.fill(c.alloc(GDB_DTYPE_F32, {T}), 0U);
+    Ten row_max = c.fill(c.alloc(GDB_DTYPE_F32, {T}), 0xFF800000U);
+    Ten row_inv_sum = c.fill(c.alloc(GDB_DTYPE_F32, {T}), 0U);
+    Ten row_valid = c.fill(c.alloc(GDB_DTYPE_F32, {T}), 0U);
+    Ten inv_valid = c.alloc(GDB_DTYPE_F32, {});
+    Ten loss = c.alloc(GDB_DTYPE_F32, {});
+    const int64_t chunk = s->lm_ce_chunk > 0 && s->lm_ce_chunk < V ? s->lm_ce_chunk : V;
+    const bool single = chunk >= V;
+    Ten saved_logits;
+    memset(&saved_logits, 0, sizeof(saved_logits));
+    const size_t ce_mark = c.top;
+    gd_backend_tensor_view tgv = tv(tgt), rlv = tv(row_loss), rmv = tv(row_max), rsv = tv(row_inv_sum), rvv = tv(row_valid), ivv = tv(inv_valid), lov = tv(loss);
+    for (int64_t start = 0; start < V && c.st == GD_OK; start += chunk) {
+        const int64_t cc = chunk < V - start ? chunk : V - start;
+        if (!single) c.top = ce_mark;
+        Ten logits = c.alloc(dt, {T, cc});
+        gd_backend_matrix_view hm = mv(final_norm, (uint32_t)T, (uint32_t)D), wm = mv(lm_w, (uint32_t)cc, (uint32_t)D, (size_t)start), lm = mv(logits, (uint32_t)T, (uint32_t)cc);
+        c.ok(gd_backend_matmul_nt(be, &hm, &wm, &lm), "matmul_nt(logits)");
+        Ten bchunk = lm_b;
+        bchunk.off += (size_t)start * gdb_dtype_size(dt);
+        bchunk.shape[0] = cc;
+        gd_backend_tensor_view lv = tv(logits), bv = tv(bchunk);
+        c.ok(gd_backend_lm_cross_entropy_online_update(be, &lv, &bv, &tgv, &rlv, &rmv, &rsv, (uint64_t)start, (uint64_t)V, s->logits_softcap), "lm_ce_online_update");
+        if (single) saved_logits = logits;
+    }
+    c.ok(gd_backend_lm_cross_entropy_finalize(be, &tgv, &rlv, &rmv, &rsv, &rvv, (uint64_t)V, s->pad_token_id), "lm_ce_finalize");
+    c.ok(gd_backend_lm_cross_entropy_reduce_normalize(be, &rlv, &rvv, &lov, &ivv), "lm_ce_reduce_normalize");
+    *loss_offset = loss.off;
+    if (c.st != GD_OK) {
+        snprintf(be->last_error, sizeof(be->last_error), "gpt step forward: %s", c.where);
+        return c.st;
+    }
+
+    // ---------------------------------------------------------------- backward
+    c.ok(gd_backend_amp_begin_step(be, &amp), "amp_begin_step");
+    Ten seed = c.alloc(GDB_DTYPE_F32, {});
+    c.ok(gd_backend_amp_fill_scale(be, seed.buf, seed.off, 1, GDB_DTYPE_F32, s->state_buffer, s->amp_scale_offset), "amp_fill_scale");
+
+    std::vector<Ten> grads((size_t)n_params);
+    const size_t es = gdb_dtype_size(dt);
+    // contiguous gradient storage for a run of parameters (16-byte aligned pieces): one all-reduce range
+    auto alloc_grads = [&](int first, int count, size_t *range_off, size_t *range_elems) {
+        size_t total = 0;
+        for (int p = first; p < first + count; ++p) total += (s->param_count[p] + 7U) & ~(size_t)7U;
+        Ten block = c.alloc(dt, {(int64_t)total});
+        size_t cursor = 0;
+        for (int p = first; p < first + count; ++p) {
+            Ten g = block;
+            g.off = block.off + cursor * es;
+            g.shape[0] = (int64_t)s->param_count[p];
+            grads[(size_t)p] = g;
+            cursor += (s->param_count[p] + 7U) & ~(size_t)7U;
+        }
+        // padding elements between pieces take part in the all-reduce: keep them finite
+        c.ok(gd_backend_fill(be, block.buf, block.off, total, es, 0U), "grad block clear");
+        *range_off = block.off;
+        *range_elems = total;
+    };
+    const bool dp = be->dp != NULL && s->dp_world > 1;
+    auto reduce_range = [&](size_t off, size_t elems) {
+        if (dp) c.ok(gdb200_dp_all_reduce(be, s->scratch_buffer, off, elems, dt), "dp_all_reduce");
+    };
+
+    // head: final norm weight, LM head weight (when untied) and bias
+    size_t head_off = 0, head_elems = 0;
+    alloc_grads(P_FINAL, n_params - P_FINAL, &head_off, &head_elems);
+    Ten emb_grad;  // token embedding gradient: last to become final
+    {
+        size_t eo = 0, ee = 0;
+        alloc_grads(0, 1, &eo, &ee);
+        emb_grad = grads[0];
+    }
+    Ten dh = c.alloc(dt, {T, D});
+    if (!single) c.fill(dh, 0U);
+    Ten dh_part;
+    if (!single) dh_part = c.alloc(dt, {T, D});
+    Ten lmw_grad = s->tied_lm_head ? emb_grad : grads[(size_t)P_LMW];
+    const size_t bwd_mark = c.top;
+    gd_backend_tensor_view sdv = tv(seed);
+    for (int64_t start = 0; start < V && c.st == GD_OK; start += chunk) {
+        const int64_t cc = chunk < V - start ? chunk : V - start;
+        Ten logits = saved_logits;
+        gd_backend_matrix_view hm = mv(final_norm, (uint32_t)T, (uint32_t)D), wm = mv(lm_w, (uint32_t)cc, (uint32_t)D, (size_t)start);
+        if (!single) {
+            c.top = bwd_mark;
+            logits = c.alloc(dt, {T, cc});
+            gd_backend_matrix_view lm = mv(logits, (uint32_t)T, (uint32_t)cc);
+            c.ok(gd_backend_matmul_nt(be, &hm, &wm, &lm), "matmul_nt(logits bwd)");
+        }
+        Ten bchunk = lm_b;
+        bchunk.off += (size_t)start * es;
+        bchunk.shape[0] = cc;
+        gd_backend_tensor_view lv = tv(logits), bv = tv(bchunk);
+        c.ok(gd_backend_lm_cross_entropy_backward_chunk(be, &lv, &bv, &tgv, &rmv, &rsv, &sdv, &ivv, &lv, (uint64_t)start, (uint64_t)V, 1.0f,
+                                                        s->logits_softcap, s->pad_token_id), "lm_ce_backward_chunk");
+        gd_backend_matrix_view lm = mv(logits, (uint32_t)T, (uint32_t)cc);
+        gd_backend_matrix_view dhm = mv(single ? dh : dh_part, (uint32_t)T, (uint32_t)D);
+        c.ok(gd_backend_matmul(be, &lm, &wm, &dhm), "matmul(d_hidden)");
+        if (!single) c.accumulate(dh, dh_part);
+        gd_backend_matrix_view dwm = mv(lmw_grad, (uint32_t)cc, (uint32_t)D, (size_t)start);
+        c.ok(gd_backend_matmul_tn(be, &lm, &hm, &dwm), "matmul_tn(d_lm_w)");
+        gd_backend_vector_view dbv = vv(grads[(size_t)P_LMB], (size_t)start, (uint32_t)cc);
+        c.ok(gd_backend_reduce_rows(be, &lm, &dbv), "reduce_rows(d_lm_b)");
+    }
+    Ten gx = rms_backward(c, x, final_w, inv_f, dh, T, D, grads[(size_t)P_FINAL]);
+    reduce_range(head_off, head_elems);
+
+    for (int i = L - 1; i >= 0 && c.st == GD_OK; --i) {
+        LayerSave &sv = saves[(size_t)i];
+        const int pb = 1 + 10 * i;
+        size_t goff = 0, gelems = 0;
+        alloc_grads(pb, 10, &goff, &gelems);
+        // out = resid + dropout(mlp)
+        Ten g_mlp = drop ? dropout_mask_backward(c, sv.mask2, gx, drop_scale) : gx;
+        Ten g_resid = gx;  // adopted: later contributions accumulate into this buffer
+        // down projection y = act w + b (w stored [F, D]): dW = act^T g, db = colsum(g), dact = g w^T
+        {
+            const Ten w = c.param(pb + 8, {F, D});
+            gd_backend_matrix_view am = mv(sv.act, (uint32_t)T, (uint32_t)F), gm = mv(g_mlp, (uint32_t)T, (uint32_t)D), wm = mv(w, (uint32_t)F, (uint32_t)D);
+            gd_backend_matrix_view dwm = mv(grads[(size_t)pb + 8], (uint32_t)F, (uint32_t)D);
+            c.ok(gd_backend_matmul_tn(be, &am, &gm, &dwm), "matmul_tn(d_down_w)");
+            gd_backend_vector_view dbv = vv(grads[(size_t)pb + 9], 0, (uint32_t)D);
+            c.ok(gd_backend_reduce_rows(be, &gm, &dbv), "reduce_rows(d_down_b)");
+            Ten dact = c.alloc(dt, {T, F});
+            gd_backend_matrix_view dam = mv(dact, (uint32_t)T, (uint32_t)F);
+            c.ok(gd_backend_matmul_nt(be, &gm, &wm, &dam), "matmul_nt(d_act)");
+            Ten d_up = c.alloc(dt, {T, 2 * F});
+            gd_backend_tensor_view xv = tv(sv.up_gate), dav = tv(dact), duv = tv(d_up);
+            c.ok(gd_backend_swiglu_split_backward(be, &xv, &dav, &duv), "swiglu_split_backward");
+            Ten dn2;
+            linear_t_backward(c, sv.normed2, c.param(pb + 6, {2 * F, D}), d_up, T, D, 2 * F, &dn2, grads[(size_t)pb + 6], grads[(size_t)pb + 7]);
+            Ten d_res2 = rms_backward(c, sv.resid, c.param(pb + 5, {D}), sv.inv2, dn2, T, D, grads[(size_t)pb + 5]);
+            c.accumulate(g_resid, d_res2);
+        }
+        // resid = x + dropout(proj)
+        Ten g_proj = drop ? dropout_mask_backward(c, sv.mask1, g_resid, drop_scale) : g_resid;
+        Ten d_attn;
+        linear_t_backward(c, sv.attn, c.param(pb + 3, {D, D}), g_proj, T, D, D, &d_attn, grads[(size_t)pb + 3], grads[(size_t)pb + 4]);
+        Ten dq = c.alloc(dt, {T, H, Dh}), dk = c.alloc(dt, {T, H, Dh}), dv = c.alloc(dt, {T, H, Dh});
+        {
+            Ten g3 = d_attn;
+            g3.rank = 3;
+            g3.shape[0] = T;
+            g3.shape[1] = H;
+            g3.shape[2] = Dh;
+            gd_backend_tensor_view gv = tv(g3), q = tv(sv.q), k = tv(sv.k), v = tv(sv.v), cv = tv(cu), dqv = tv(dq), dkv = tv(dk), dvv = tv(dv), stv = tv(sv.stats);
+            sa.use_forward_stats = 1;
+            c.ok(gd_backend_sdpa_varlen_backward(be, &gv, &q, &k, &v, &cv, &dqv, &dkv, &dvv, &stv, &sa), "sdpa_varlen_backward");
+        }
+        Ten dqkv = c.alloc(dt, {T, 3 * D});
+        {
+            gd_backend_tensor_view a = tv(dq), b = tv(dk), v = tv(dv), p = tv(pos), o = tv(dqkv);
+            c.ok(gd_backend_qkv_split_rope_backward(be, &a, &b, &v, &p, &o, (uint32_t)H, (uint32_t)Dh, &rope), "qkv_split_rope_backward");
+        }
+        Ten dn1;
+        linear_t_backward(c, sv.normed, c.param(pb + 1, {3 * D, D}), dqkv, T, D, 3 * D, &dn1, grads[(size_t)pb + 1], grads[(size_t)pb + 2]);
+        Ten d_x1 = rms_backward(c, sv.x, c.param(pb + 0, {D}), sv.inv1, dn1, T, D, grads[(size_t)pb + 0]);
+        c.accumulate(g_resid, d_x1);
+        gx = g_resid;
+        reduce_range(goff, gelems);
+    }
+    if (drop) gx = dropout_mask_backward(c, emb_mask, gx, drop_scale);
+    {
+        // embedding table gradient; with a tied LM head the head contribution is already in emb_grad
+        Ten target = emb_grad;
+        if (s->tied_lm_head) target = c.alloc(dt, {V, D});
+        Ten scratch = c.alloc(GDB_DTYPE_F32, {V, D});
+        Ten t2 = target;
+        t2.rank = 2;
+        t2.shape[0] = V;
+        t2.shape[1] = D;
+        gd_backend_tensor_view gv = tv(gx), iv = tv(ids), tvw = tv(t2), sv2 = tv(scratch);
+        c.ok(gd_backend_embedding_backward(be, &gv, &iv, &tvw, &sv2, &ea), "embedding_backward");
+        if (s->tied_lm_head) c.accumulate(emb_grad, target);
+        reduce_range(emb_grad.off, (size_t)V * (size_t)D);
+    }
+    if (c.st != GD_OK) {
+        snprintf(be->last_error, sizeof(be->last_error), "gpt step backward: %s", c.where);
+        return c.st;
+    }
+
+    // ---------------------------------------------------------------- optimizer (src/optim/adamw.c:2163-2270)
+    gd_backend_buffer *scale_buf = s->state_buffer;
+    size_t inv_scale_off = s->amp_scale_offset + sizeof(float);
+    if (dp) {
+        c.ok(gdb200_dp_join(be), "dp_join");
+        // mean over ranks: fold 1/world into the inverse loss scale the clip and AdamW kernels use
+        Ten inv = c.alloc(GDB_DTYPE_F32, {});
+        c.ok(gd_backend_scale(be, inv.buf, inv.off, s->state_buffer, inv_scale_off, 1, GDB_DTYPE_F32, 1.0f / (float)s->dp_world), "scale(inv_scale/world)");
+        scale_buf = inv.buf;
+        inv_scale_off = inv.off;
+    }
+    std::vector<gd_backend_grad_norm_desc> nd((size_t)n_params);
+    std::vector<gd_backend_adamw_desc> ad((size_t)n_params);
+    size_t partial_index = 0;
+    for (int p = 0; p < n_params; ++p) {
+        const size_t groups = (s->param_count[p] + 1023U) / 1024U;
+        gd_backend_grad_norm_desc &d = nd[(size_t)p];
+        memset(&d, 0, sizeof(d));
+        d.grad_buffer = grads[(size_t)p].buf;
+        d.grad_offset = grads[(size_t)p].off;
+        d.count = s->param_count[p];
+        d.grad_dtype = dt;
+        d.partial_buffer = s->state_buffer;
+        d.partial_offset = s->partials_offset + partial_index * sizeof(float);
+        d.partial_count = groups;
+        d.grad_scale_buffer = scale_buf;
+        d.grad_scale_offset = inv_scale_off;
+        d.found_inf_buffer = s->state_buffer;
+        d.found_inf_offset = s->amp_flags_offset + sizeof(int32_t);
+        d.has_found_inf = 1;
+        partial_index += groups;
+        gd_backend_adamw_desc &a = ad[(size_t)p];
+        memset(&a, 0, sizeof(a));
+        a.param_buffer = s->params_buffer;
+        a.param_offset = s->param_offset[p];
+        a.master_buffer = s->state_buffer;
+        a.master_offset = s->master_offset[p];
+        a.has_master = 1;
+        a.grad_buffer = d.grad_buffer;
+        a.grad_offset = d.grad_offset;
+        a.grad_scale_buffer = s->state_buffer;
+        a.grad_scale_offset = s->clip_scale_offset;
+        a.has_grad_scale = 1;
+        a.found_inf_buffer = s->state_buffer;
+        a.found_inf_offset = d.found_inf_offset;
+        a.has_found_inf = 1;
+        a.m_buffer = s->state_buffer;
+        a.m_offset = s->m_offset[p];
+        a.v_buffer = s->state_buffer;
+        a.v_offset = s->v_offset[p];
+        a.state_f32_buffer = s->state_buffer;
+        a.beta1_power_offset = s->state_f32_offset + ((size_t)0 * (size_t)n_params + (size_t)p) * 4U;
+        a.beta2_power_offset = s->state_f32_offset + ((size_t)1 * (size_t)n_params + (size_t)p) * 4U;
+        a.step_scale_offset = s->state_f32_offset + ((size_t)2 * (size_t)n_params + (size_t)p) * 4U;
+        a.decay_scale_offset = s->state_f32_offset + ((size_t)3 * (size_t)n_params + (size_t)p) * 4U;
+        a.eps_scaled_offset = s->state_f32_offset + ((size_t)4 * (size_t)n_params + (size_t)p) * 4U;
+        a.state_i32_buffer = s->state_buffer;
+        a.param_step_offset = s->state_i32_offset + (size_t)p * 4U;
+        a.optimizer_step_offset = s->state_i32_offset + (size_t)n_params * 4U;
+        a.count = s->param_count[p];
+        a.param_dtype = dt;
+        a.grad_dtype = dt;
+        a.has_device_state = 1;
+        a.bias_correction = 1;
+        a.update_optimizer_step = p == 0 ? 1U : 0U;
+        a.lr = lr;
+        a.beta1 = s->adam_beta1;
+        a.beta2 = s->adam_beta2;
+        a.eps = s->adam_eps;
+        a.weight_decay = s->weight_decay[p];
+        a.bias_correction1 = a.bias_correction2 = 1.0f;
+    }
+    c.ok(gd_backend_grad_clip_scale(be, nd.data(), (uint32_t)n_params, s->state_buffer, s->clip_scale_offset, s->grad_clip_norm, 1.0e-6f), "grad_clip_scale");
+    c.ok(gd_backend_adamw_batch(be, ad.data(), (uint32_t)n_params), "adamw_batch");
+    c.ok(gd_backend_amp_finish_step(be, &amp), "amp_finish_step");
+    if (scratch_used != NULL) {
+        *scratch_used = c.top;
+    }
+    if (c.st != GD_OK) {
+        snprintf(be->last_error, sizeof(be->last_error), "gpt step optimizer: %s", c.where);
+    }
+    return c.st;
+}

@@ -57,21 +57,49 @@ __device__ __forceinline__ void for_each_logit(const T *row, const T *bias, size
     }
 }
 
+// One warp per row, one pass: every lane keeps a running (max, sum) over its classes, the lanes
+// are merged with shuffles. No block-level synchronisation.
 template <typename T>
 __global__ void lmce_online_update_kernel(const T *logits, const T *bias, const int *targets, float *target_logit,
-                                          float *row_max, float *row_sum, size_t classes, uint64_t class_start,
+                                          float *row_max, float *row_sum, size_t rows, size_t classes, uint64_t class_start,
                                           uint64_t total_classes, float cap, float inv_cap)
 {
-    __shared__ float sh[33];
-    const size_t row = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) {
+        return;
+    }
     const T *lr = logits + row * classes;
-    float lmax = NEG_BIG;
-    for_each_logit<T>(lr, bias, classes, cap, inv_cap, [&](size_t, float v) { lmax = fmaxf(lmax, v); });
-    const float cmax = gdb_block_max(lmax, sh);
-    float lsum = 0.0f;
-    for_each_logit<T>(lr, bias, classes, cap, inv_cap, [&](size_t, float v) { lsum += __expf(v - cmax); });
-    const float csum = gdb_block_sum(lsum, sh);
-    if (threadIdx.x == 0) {
+    float m = NEG_BIG, s = 0.0f;
+    if (sizeof(T) == 2 && (classes % 8U) == 0U && ((uintptr_t)lr % 16U) == 0U) {
+        const uint4 *rv = reinterpret_cast<const uint4 *>(lr);
+        for (size_t v = lane; v < classes / 8U; v += 32) {
+            gdb_vec8<T> a;
+            a.raw = rv[v];
+            float x[8], vm = NEG_BIG;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                x[e] = eff_logit<T>(a.get(e), bias, v * 8U + (size_t)e, cap, inv_cap);
+                vm = fmaxf(vm, x[e]);
+            }
+            const float nm = fmaxf(m, vm);
+            float add = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) add += __expf(x[e] - nm);
+            s = s * __expf(m - nm) + add;
+            m = nm;
+        }
+    } else {
+        for (size_t c = lane; c < classes; c += 32) {
+            const float x = eff_logit<T>(gdb_io<T>::ld(lr, c), bias, c, cap, inv_cap);
+            const float nm = fmaxf(m, x);
+            s = s * __expf(m - nm) + __expf(x - nm);
+            m = nm;
+        }
+    }
+    const float cmax = gdb_warp_max(m);
+    const float csum = gdb_warp_sum(s * __expf(m - cmax));
+    if (lane == 0) {
         const int t = targets[row];
         if (t >= 0) {
             const uint64_t tu = (uint64_t)t;
@@ -310,11 +338,11 @@ gd_status gd_backend_lm_cross_entropy_online_update(gd_backend *be, const gd_bac
         return GD_ERR_INVALID_ARGUMENT;
     }
     const float inv_cap = logits_softcap > 0.0f ? 1.0f / logits_softcap : 0.0f;
-    const unsigned threads = row_threads(cs.classes);
+    const unsigned grid = (unsigned)((cs.rows + 3U) / 4U);
     if (dt == GDB_DTYPE_F16) {
-        lmce_online_update_kernel<__half><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __half *)lp, (const __half *)bp, tp, rl, rm, rs, cs.classes, class_start, total_classes, logits_softcap, inv_cap);
+        lmce_online_update_kernel<__half><<<grid, 128, 0, be->stream>>>((const __half *)lp, (const __half *)bp, tp, rl, rm, rs, cs.rows, cs.classes, class_start, total_classes, logits_softcap, inv_cap);
     } else {
-        lmce_online_update_kernel<__nv_bfloat16><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __nv_bfloat16 *)lp, (const __nv_bfloat16 *)bp, tp, rl, rm, rs, cs.classes, class_start, total_classes, logits_softcap, inv_cap);
+        lmce_online_update_kernel<__nv_bfloat16><<<grid, 128, 0, be->stream>>>((const __nv_bfloat16 *)lp, (const __nv_bfloat16 *)bp, tp, rl, rm, rs, cs.rows, cs.classes, class_start, total_classes, logits_softcap, inv_cap);
     }
     return gdb_launched(be, "lm_cross_entropy_online_update");
 }

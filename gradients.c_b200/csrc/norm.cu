@@ -7,18 +7,12 @@
 //   dw   = sum_rows g * x * inv, via FP32 partials [row_blocks, cols] (:414-447, :554-580)
 // The simdgroup counts in gd_backend_rms_norm_args describe the Metal launch and are ignored.
 #include "common.cuh"
+#include "colreduce.cuh"
 
 namespace {
 
 constexpr int ROWS_PER_BLOCK = 4;  // 4 warps per block, one row each
 
-template <typename T> struct row_loader {
-    // Row sum of f(x) with 16-byte loads when the row allows it.
-    static __device__ __forceinline__ bool vec_ok(const T *row, size_t cols)
-    {
-        return sizeof(T) == 2 && (cols % 8U) == 0U && ((uintptr_t)row % 16U) == 0U;
-    }
-};
 
 // MODE 0: out only; MODE 1: out + inv; MODE 2: inv only.
 template <typename T, int MODE>
@@ -337,6 +331,11 @@ gd_status gd_backend_rms_norm_weight_backward_stats(gd_backend *be, const gd_bac
     void *dw = gdb_tv_ptr(grad_weight, x->dtype);
     if (xp == NULL || gp == NULL || ip == NULL || pp == NULL || dw == NULL) {
         return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (x->dtype != GDB_DTYPE_F32 && gdb_colreduce::usable(gp, a->cols, xp, a->cols, a->cols)) {
+        return x->dtype == GDB_DTYPE_F16
+                   ? gdb_colreduce::run<__half, true>(be, gp, a->cols, xp, a->cols, ip, pp, a->row_blocks, dw, a->rows, a->cols)
+                   : gdb_colreduce::run<__nv_bfloat16, true>(be, gp, a->cols, xp, a->cols, ip, pp, a->row_blocks, dw, a->rows, a->cols);
     }
     const unsigned col_blocks = (unsigned)((a->cols + 255U) / 256U);
     size_t blocks = a->row_blocks;

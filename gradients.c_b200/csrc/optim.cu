@@ -13,6 +13,7 @@ namespace {
 
 constexpr int MT_MAX = 64;          // tensors per multi-tensor launch
 constexpr unsigned NORM_BLOCK = 1024;  // elements per gradient-norm partial (reference: 1024)
+constexpr unsigned NORM_GROUP = 8;     // partial slots handled by one block of the norm kernel
 
 __device__ __forceinline__ float load_as_float(const void *p, size_t i, uint32_t dtype)
 {
@@ -123,12 +124,14 @@ __global__ void grad_norm_stage_kernel(norm_batch b)
     while (t + 1 < b.n && blockIdx.x >= b.block_start[t + 1]) {
         ++t;
     }
+    // one block covers NORM_GROUP partial slots (8192 elements) and writes the first of them; the
+    // other slots of the group stay zero (the host clears the partial range before this launch)
     const unsigned local = blockIdx.x - b.block_start[t];
-    const size_t base = (size_t)local * NORM_BLOCK;
+    const size_t base = (size_t)local * NORM_BLOCK * NORM_GROUP;
     const float gs = b.grad_scale[0];
     float sum = 0.0f;
     bool bad = false;
-    for (unsigned j = threadIdx.x; j < NORM_BLOCK; j += blockDim.x) {
+    for (unsigned j = threadIdx.x; j < NORM_BLOCK * NORM_GROUP; j += blockDim.x) {
         const size_t i = base + j;
         if (i < b.count[t]) {
             const float g = load_as_float(b.grad[t], i, b.dtype[t]) * gs;
@@ -141,7 +144,7 @@ __global__ void grad_norm_stage_kernel(norm_batch b)
     }
     sum = gdb_block_sum(sum, sh);
     if (threadIdx.x == 0) {
-        b.partial[t][local] = sum;
+        b.partial[t][(size_t)local * NORM_GROUP] = sum;
     }
 }
 __global__ void grad_clip_finalize_kernel(const float *partials, size_t n, float *out, const float *grad_scale,
@@ -493,7 +496,7 @@ gd_status gd_backend_grad_clip_scale(gd_backend *be, const gd_backend_grad_norm_
                 b.found_inf = (int *)(d->found_inf_buffer->dptr + d->found_inf_offset);
             }
             b.block_start[b.n] = blocks;
-            blocks += (unsigned)((d->count + NORM_BLOCK - 1U) / NORM_BLOCK);
+            blocks += (unsigned)((d->count + NORM_BLOCK * NORM_GROUP - 1U) / (NORM_BLOCK * NORM_GROUP));
             b.n += 1;
         }
         b.block_start[b.n] = blocks;

@@ -121,6 +121,30 @@ class KvCacheAppendArgs(C.Structure):
     _fields_ = [("cache_pos", I32_T)]
 
 
+GPT_MAX_LAYERS = 64
+GPT_MAX_PARAMS = 1 + 10 * GPT_MAX_LAYERS + 3
+
+
+class GptSpec(C.Structure):
+    _fields_ = [("params_buffer", P), ("state_buffer", P), ("scratch_buffer", P), ("scratch_bytes", SZ),
+                ("vocab_size", I32_T), ("context_length", I32_T), ("d_model", I32_T), ("n_layers", I32_T), ("n_heads", I32_T),
+                ("head_dim", I32_T), ("mlp_hidden", I32_T), ("tied_lm_head", I32_T), ("sdpa_window", I32_T), ("pad_token_id", I32_T),
+                ("lm_ce_chunk", I32_T), ("n_params", I32_T), ("dp_world", I32_T), ("dtype", U32),
+                ("dropout_p", F), ("logits_softcap", F), ("rms_eps", F), ("rope_theta", F), ("dropout_seed", U64),
+                ("adam_beta1", F), ("adam_beta2", F), ("adam_eps", F), ("grad_clip_norm", F),
+                ("amp_growth_factor", F), ("amp_backoff_factor", F), ("amp_min_scale", F), ("amp_max_scale", F),
+                ("amp_growth_interval", U32),
+                ("state_f32_offset", SZ), ("state_i32_offset", SZ), ("partials_offset", SZ), ("clip_scale_offset", SZ),
+                ("amp_scale_offset", SZ), ("amp_flags_offset", SZ),
+                ("param_offset", SZ * GPT_MAX_PARAMS), ("param_count", SZ * GPT_MAX_PARAMS), ("master_offset", SZ * GPT_MAX_PARAMS),
+                ("m_offset", SZ * GPT_MAX_PARAMS), ("v_offset", SZ * GPT_MAX_PARAMS), ("weight_decay", F * GPT_MAX_PARAMS)]
+
+
+class GptBatch(C.Structure):
+    _fields_ = [("buffer", P), ("input_ids_offset", SZ), ("targets_offset", SZ), ("positions_offset", SZ),
+                ("cu_seqlens_offset", SZ), ("n_tokens", C.c_int64), ("n_cu", C.c_int64)]
+
+
 TV = C.POINTER(TensorView)
 MV = C.POINTER(MatrixView)
 BV = C.POINTER(BatchedMatrixView)
@@ -231,9 +255,11 @@ PROTOTYPES = {
     "gdb200_pinned_free": (None, [P]),
     "gdb200_gemm_profile_enable": (None, [P, C.c_int]),
     "gdb200_gemm_profile_read": (_ST, [P, C.POINTER(U64), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "gdb200_matmul_nt_bias": (_ST, [P, MV, MV, VV, MV]),
     "gdb200_embedding_backward_static": (_ST, [P, P, P, P, U64, U64, U64, U32]),
     "gdb200_embedding_backward_static_error": (C.c_char_p, []),
     "gdb200_embedding_backward_static_max_elems": (U64, []),
+    "gdb200_gpt_train_step": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptBatch), U64, F, C.POINTER(SZ), C.POINTER(SZ)]),
     "gdb200_dp_unique_id": (_ST, [P]),
     "gdb200_dp_init": (_ST, [P, P, C.c_int, C.c_int]),
     "gdb200_dp_all_reduce": (_ST, [P, P, SZ, SZ, U32]),

@@ -353,6 +353,58 @@ class Trainer:
         return loss
 
 
+class NativeTrainer(Trainer):
+    """Same training step as Trainer, with the per-step call sequence issued by the library's
+    native driver (gdb200_gpt_train_step) instead of the Python op capsules. State layout, kernels,
+    rounding points and results are the same; only the host that enqueues the calls differs."""
+
+    def __init__(self, model: GptLm, cfg: TrainConfig, dp=None):
+        super().__init__(model, cfg, dp)
+        import ctypes as C
+        self._C = C
+        mc, ctx, opt, sc = model.cfg, model.ctx, self.optimizer, self.scaler
+        s = abi.GptSpec()
+        s.params_buffer, s.state_buffer, s.scratch_buffer = ctx.params.buffer, ctx.state.buffer, ctx.scratch.buffer
+        s.scratch_bytes = ctx.scratch.capacity
+        s.vocab_size, s.context_length, s.d_model, s.n_layers = mc.vocab_size, mc.context_length, mc.d_model, mc.n_layers
+        s.n_heads, s.head_dim, s.mlp_hidden, s.tied_lm_head = mc.n_heads, mc.head_dim, mc.mlp_hidden, 1 if mc.tied_lm_head else 0
+        s.sdpa_window, s.pad_token_id, s.dtype = mc.sdpa_window, mc.pad_token_id, mc.dtype
+        s.lm_ce_chunk = ops.lm_ce_chunk_classes(mc.vocab_size)
+        s.n_params = len(opt.slots)
+        s.dp_world = dp.world if dp is not None else 1
+        s.dropout_p = mc.dropout_p if model.training else 0.0
+        s.logits_softcap, s.rms_eps, s.rope_theta, s.dropout_seed = mc.logits_softcap, mc.rms_eps, mc.rope_theta, mc.dropout_seed
+        s.adam_beta1, s.adam_beta2, s.adam_eps, s.grad_clip_norm = cfg.beta1, cfg.beta2, cfg.eps, cfg.grad_clip_norm
+        a = cfg.amp
+        s.amp_growth_factor, s.amp_backoff_factor, s.amp_min_scale, s.amp_max_scale = a.growth_factor, a.backoff_factor, a.min_scale, a.max_scale
+        s.amp_growth_interval = a.growth_interval
+        s.state_f32_offset, s.state_i32_offset = opt.state_f32.offset, opt.state_i32.offset
+        s.partials_offset, s.clip_scale_offset = opt.partials.offset, opt.grad_clip_scale.offset
+        s.amp_scale_offset, s.amp_flags_offset = sc.scale_state.offset, sc.flag_state.offset
+        for i, slot in enumerate(opt.slots):
+            assert slot.master is not None, "the native driver expects 16-bit parameters with FP32 masters"
+            s.param_offset[i], s.param_count[i] = slot.param.offset, slot.param.count
+            s.master_offset[i], s.m_offset[i], s.v_offset[i] = slot.master.offset, slot.m.offset, slot.v.offset
+            s.weight_decay[i] = slot.weight_decay
+        self.spec = s
+
+    def train_batch(self, batch: Optional[Batch], lr: Optional[float] = None, device_batch=None) -> Tensor:
+        C, ctx = self._C, self.ctx
+        ctx.begin_step()
+        ids, tgt, pos, cu = device_batch if device_batch is not None else self.model.upload_batch(batch)
+        assert ids.arena is tgt.arena is pos.arena is cu.arena
+        b = abi.GptBatch(ids.buffer, ids.offset, tgt.offset, pos.offset, cu.offset, ids.count, cu.count)
+        loss_off, used = C.c_size_t(), C.c_size_t()
+        st = ctx.lib.gdb200_gpt_train_step(ctx.backend, C.byref(self.spec), C.byref(b), self.global_step + 1,
+                                           self.cfg.lr if lr is None else lr, C.byref(loss_off), C.byref(used))
+        ctx.check(st, "gdb200_gpt_train_step")
+        ctx.scratch.top = used.value
+        ctx.scratch.high_water = max(ctx.scratch.high_water, used.value)
+        ctx.end_step()
+        self.global_step += 1
+        return Tensor(ctx, ctx.scratch, loss_off.value, F32, ())
+
+
 def greedy_generate(model: GptLm, prompts: np.ndarray, new_tokens: int, capacity: int) -> np.ndarray:
     """Batched greedy KV-cache generation: packed prefill, then `new_tokens` decode steps with
     host argmax (first maximum wins, soft cap applied on the host as gpt_lm_shared.c:1322,1388-1398)."""

@@ -22,6 +22,9 @@ RMS_WGRAD_ROW_BLOCK_LARGE = 128
 RMS_WGRAD_LARGE_ROWS = 4096
 LM_CE_DEFAULT_CHUNK = 2048            # src/ops/lm_cross_entropy/core_lm_cross_entropy.c:14
 F32_NEG_INF_PATTERN = 0xFF800000      # :15
+# gd_linear_transposed_weight: use the additive fused entry instead of the reference's two-call
+# sequence (matmul_nt, then add). Both give bit-identical results; tests exercise both.
+FUSE_BIAS_ADD = True
 
 
 def _tvp(t: Optional[Tensor]):
@@ -185,9 +188,15 @@ def gd_linear_transposed_weight(ctx: Context, x: Tensor, w: Tensor, bias: Option
     assert w.shape[1] == k
     lib = ctx.lib
     y = ctx.scratch_empty(x.dtype, x.shape[:-1] + (n,), "linear_t")
-    _matmul(ctx, lib.gd_backend_matmul_nt, x.mv(m, k), w.mv(n, k), y.mv(m, n), "matmul_nt")
     out = y
-    if bias is not None:
+    if bias is None:
+        _matmul(ctx, lib.gd_backend_matmul_nt, x.mv(m, k), w.mv(n, k), y.mv(m, n), "matmul_nt")
+    elif FUSE_BIAS_ADD:
+        # one kernel with the same two roundings as matmul_nt + add (bit-identical results)
+        xm, wm, bv, ym = x.mv(m, k), w.mv(n, k), bias.vv(), y.mv(m, n)
+        ctx.check(lib.gdb200_matmul_nt_bias(ctx.backend, byref(xm), byref(wm), byref(bv), byref(ym)), "matmul_nt_bias")
+    else:
+        _matmul(ctx, lib.gd_backend_matmul_nt, x.mv(m, k), w.mv(n, k), y.mv(m, n), "matmul_nt")
         out = ctx.scratch_empty(x.dtype, y.shape, "linear_t_bias")
         ctx.check(lib.gd_backend_add(ctx.backend, _tvp(y), _tvp(bias), _tvp(out)), "add(bias)")
     needs = x.requires_grad or w.requires_grad or (bias is not None and bias.requires_grad)

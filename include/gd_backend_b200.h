@@ -374,6 +374,13 @@ gd_status gdb200_gemm_profile_read(gd_backend *backend, uint64_t *launches, doub
 /* Overwrite a private buffer larger than L2 so that the next kernel starts with a cold L2. */
 gd_status gdb200_flush_l2(gd_backend *backend);
 
+/* y = round(round(x w^T) + bias), w stored [y.cols, x.cols]: gd_backend_matmul_nt followed by the
+ * row-broadcast gd_backend_add of the reference's linear_transposed_weight capsule
+ * (src/ops/linear_transposed_weight/core_linear_transposed_weight.c:51-79) in one kernel, with the
+ * same two roundings, so results are bit-identical to the two-call sequence. */
+gd_status gdb200_matmul_nt_bias(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
+                                const gd_backend_vector_view *bias, const gd_backend_matrix_view *y);
+
 /* Embedding table gradient with no allocation (no counterpart in the reference). Same result as
  * gd_backend_embedding_backward, but the FP32 accumulation table is a fixed device array inside the
  * library instead of a caller-provided scratch tensor, for callers that cannot allocate: a runtime
@@ -388,6 +395,44 @@ gd_status gdb200_embedding_backward_static(void *stream, const void *grad_out, c
                                            uint64_t ids_count, uint64_t vocab, uint64_t dim, uint32_t dtype);
 const char *gdb200_embedding_backward_static_error(void);
 uint64_t gdb200_embedding_backward_static_max_elems(void);
+
+/* Native sequencing of one gpt_lm training step (no counterpart in the reference's backend ABI; it
+ * replays the call sequence of the reference's host: src/train/trainer.c:75-223,
+ * examples/gpt_lm/gpt_lm_shared.c:602-823, src/optim/adamw.c:2163-2270). The caller lays out
+ * parameters (storage dtype) in params_buffer and, in state_buffer, FP32 masters / m / v per
+ * parameter, the AdamW device scalars F32 [5][n_params] and I32 [n_params + 1], the gradient-norm
+ * partials (sum of ceil(count / 1024) floats), the clip scale F32[2] and the AMP state F32[2] + I32[3].
+ * Parameter order: token_embedding; per block attn_norm_w, qkv w/b, attn_proj w/b, mlp_norm_w,
+ * up_gate w/b, down_proj w/b; final_norm_w; lm_head weight (when untied); lm_head_bias.
+ * Activations and gradients are bump-allocated from scratch_buffer from offset 0. */
+#define GDB200_GPT_MAX_LAYERS 64
+#define GDB200_GPT_MAX_PARAMS (1 + 10 * GDB200_GPT_MAX_LAYERS + 3)
+typedef struct gdb200_gpt_spec {
+    gd_backend_buffer *params_buffer, *state_buffer, *scratch_buffer;
+    size_t scratch_bytes;
+    int32_t vocab_size, context_length, d_model, n_layers, n_heads, head_dim, mlp_hidden, tied_lm_head;
+    int32_t sdpa_window, pad_token_id, lm_ce_chunk, n_params, dp_world;
+    uint32_t dtype;
+    float dropout_p, logits_softcap, rms_eps, rope_theta;
+    uint64_t dropout_seed;
+    float adam_beta1, adam_beta2, adam_eps, grad_clip_norm;
+    float amp_growth_factor, amp_backoff_factor, amp_min_scale, amp_max_scale;
+    uint32_t amp_growth_interval;
+    size_t state_f32_offset, state_i32_offset, partials_offset, clip_scale_offset, amp_scale_offset, amp_flags_offset;
+    size_t param_offset[GDB200_GPT_MAX_PARAMS], param_count[GDB200_GPT_MAX_PARAMS];
+    size_t master_offset[GDB200_GPT_MAX_PARAMS], m_offset[GDB200_GPT_MAX_PARAMS], v_offset[GDB200_GPT_MAX_PARAMS];
+    float weight_decay[GDB200_GPT_MAX_PARAMS];
+} gdb200_gpt_spec;
+typedef struct gdb200_gpt_batch {
+    gd_backend_buffer *buffer;  /* I32 fields: input ids, targets, positions [n_tokens]; cu_seqlens [n_cu] */
+    size_t input_ids_offset, targets_offset, positions_offset, cu_seqlens_offset;
+    int64_t n_tokens, n_cu;
+} gdb200_gpt_batch;
+/* Enqueues forward, backward (loss scaled by the AMP state), gradient exchange when a data-parallel
+ * communicator is attached and spec->dp_world > 1, clipping, AdamW and the scaler update. The mean
+ * loss (F32 scalar) is left at *loss_offset of scratch_buffer. */
+gd_status gdb200_gpt_train_step(gd_backend *backend, const gdb200_gpt_spec *spec, const gdb200_gpt_batch *batch,
+                                uint64_t step, float lr, size_t *loss_offset, size_t *scratch_used);
 
 /* Data-parallel gradient exchange (the reference has no collective; one process per GPU).
  * id_bytes is the 128-byte ncclUniqueId produced by gdb200_dp_unique_id on rank 0. */

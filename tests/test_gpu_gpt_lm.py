@@ -90,3 +90,33 @@ def test_greedy_decode_matches_oracle():
                 top2 = np.sort(lg)[-2:]
                 assert top2[1] - top2[0] <= 4e-3 * max(1.0, abs(top2[1])), (b, t, got[b, t], want_tokens[b, t])
                 break
+
+
+@pytest.mark.parametrize("tied,chunk_env", [(False, None), (True, None), (False, "128")])
+def test_native_step_driver_matches_python_host(monkeypatch, tied, chunk_env):
+    """The library's native per-step driver and the Python op capsules enqueue the same calls: losses
+    and updated parameters agree to within atomics noise (embedding scatter), and both track the oracle."""
+    if chunk_env:
+        monkeypatch.setenv("GD_LM_CE_CHUNK_SIZE", chunk_env)
+    cfg = small_cfg(tied_lm_head=tied, sdpa_window=0 if not tied else 16)
+    tc = g.TrainConfig.baseline()
+    hp = g.init_params(cfg, seed=21)
+    batches = [g.synthetic_batch(cfg, n_seqs=5, min_len=4, max_len=64, seed=300 + s, pad_to=64) for s in range(3)]
+    results = {}
+    for kind in ("python", "native"):
+        with pkg.runtime.Context(params_bytes=64 << 20, state_bytes=128 << 20, scratch_bytes=1 << 30) as ctx:
+            model = g.GptLm(ctx, cfg, hp)
+            trainer = (g.NativeTrainer if kind == "native" else g.Trainer)(model, tc)
+            losses = [float(trainer.train_batch(b).read()[()]) for b in batches]
+            results[kind] = (losses, {n: host(p) for n, p in model.params.items()}, trainer.scaler.sync(), trainer.optimizer.step_count())
+    lp, ln = results["python"][0], results["native"][0]
+    assert lp[0] == ln[0]                                    # first forward: identical kernels, identical inputs
+    np.testing.assert_allclose(ln, lp, rtol=2e-4)
+    for n in results["python"][1]:
+        np.testing.assert_allclose(results["native"][1][n], results["python"][1][n], atol=2e-3, rtol=2e-2, err_msg=n)
+    assert results["python"][2] == results["native"][2] and results["python"][3] == results["native"][3] == 3
+    ref = OG.OracleGptLm(OG.config_from(cfg), hp)
+    otc = OG.train_config_from(tc)
+    for s, b in enumerate(batches):
+        want = ref.train_step(b.input_ids, b.targets, b.positions, b.cu_seqlens, s + 1, otc)
+        assert abs(ln[s] - want["loss"]) <= 2e-3 * abs(want["loss"])

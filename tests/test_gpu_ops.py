@@ -526,3 +526,20 @@ def test_flash_backward_without_forward_stats(step):
     ctx.check(ctx.lib.gd_backend_sdpa_varlen_backward(ctx.backend, byref(gt.tv()), byref(qt.tv()), byref(kt.tv()), byref(vt.tv()), byref(cut.tv()),
                                                       byref(dq.tv()), byref(dk.tv()), byref(dv.tv()), None, byref(args)), "bwd no stats")
     close(host(dq), wdq, F16, scale=4)
+
+
+@pytest.mark.parametrize("m,k,n", [(1000, 512, 1536), (77, 40, 24), (4096, 1536, 512)])
+def test_fused_matmul_nt_bias_is_bit_identical_to_two_calls(step, m, k, n):
+    ctx = step
+    x = rnd_np(rng(95).standard_normal((m, k)).astype(np.float32), F16)
+    w = rnd_np((rng(96).standard_normal((n, k)) * 0.2).astype(np.float32), F16)
+    b = rnd_np(rng(97).standard_normal(n).astype(np.float32), F16)
+    outs = []
+    for fuse in (True, False):
+        ops.FUSE_BIAS_ADD = fuse
+        try:
+            outs.append(host(ops.gd_linear_transposed_weight(ctx, dev(ctx, x, F16), dev(ctx, w, F16), dev(ctx, b, F16))))
+        finally:
+            ops.FUSE_BIAS_ADD = True
+    assert np.array_equal(outs[0], outs[1])
+    close(outs[0], O.linear_transposed_weight_forward(t32(x), t32(w), t32(b)), F16, scale=np.sqrt(k) / 4)
