@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--host", default="native", choices=["native", "python"],
                     help="who enqueues the per-step backend calls: the library's native driver or the Python op capsules")
-    ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 portable kernel only, 2 tcgen05 required")
+    ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 portable kernel only, 2 tcgen05 required, 3 auto without the CTA-pair kernel")
     return ap.parse_args()
 
 

@@ -533,7 +533,7 @@ int gdb200_set_gemm_mode(gd_backend *be, int mode)
         return -1;
     }
     const int old = be->gemm_mode;
-    if (mode >= 0 && mode <= 2) {
+    if (mode >= 0 && mode <= 3) {
         be->gemm_mode = mode;
     }
     return old;

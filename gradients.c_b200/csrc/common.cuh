@@ -239,5 +239,10 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype,
                            const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
                            void *c, size_t ldc_bytes, const void *bias, int bias_mode,
                            uint32_t M, uint32_t N, uint32_t K);
+// CTA-pair persistent variant; *splits_out > 1 means FP32 partials were left in the workspace.
+gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype,
+                                const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
+                                void *c, size_t ldc_bytes, const void *bias, int bias_mode,
+                                uint32_t M, uint32_t N, uint32_t K, uint32_t *splits_out);
 void gdb_tmap_cache_destroy(gd_backend *be);
 void gdb_dp_destroy(gd_backend *be);

@@ -22,131 +22,12 @@
 // gd_backend_flush reports GD_ERR_INTERNAL.
 #include "common.cuh"
 
-#include <cuda.h>
-#include <type_traits>
+#include "tcgen05.cuh"
 
 namespace {
+using namespace gdb_t5;
 
-constexpr int BM = 128;      // UMMA M
-constexpr int BK = 64;       // k elements per stage: one 128-byte swizzle row of 16-bit elements
-constexpr int UMMA_K = 16;   // k elements per tcgen05.mma for 16-bit operands
-constexpr unsigned WAIT_LIMIT = 1u << 22;
 
-typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-encode_tiled_fn get_encode_fn()
-{
-    static encode_tiled_fn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess) {
-            fn = (encode_tiled_fn)p;
-        }
-    }
-    return fn;
-}
-
-// 2-D row-major global tensor [rows, cols] of 16-bit elements with a row pitch in bytes;
-// box = {box_cols (<= 64, the swizzle span), box_rows}.
-bool make_tmap(CUtensorMap *m, uint32_t dtype, const void *base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
-               uint32_t box_cols, uint32_t box_rows)
-{
-    encode_tiled_fn fn = get_encode_fn();
-    if (fn == nullptr) {
-        return false;
-    }
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {pitch_bytes};
-    const cuuint32_t box[2] = {box_cols, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapDataType dt = dtype == GDB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    return fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
-{
-    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n.reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            "selp.u32 %0, 1, 0, p;\n}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) {
-            return true;
-        }
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// 64-bit shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFFU);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFU) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFU) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
 
 template <int BN, int STAGES>
 struct smem_plan {
@@ -157,21 +38,6 @@ struct smem_plan {
     static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
 };
 
-template <typename T> struct half_pack;
-template <> struct half_pack<__half> {
-    static __device__ __forceinline__ uint32_t pack(float a, float b)
-    {
-        const __half2 h = __floats2half2_rn(a, b);
-        return *reinterpret_cast<const uint32_t *>(&h);
-    }
-};
-template <> struct half_pack<__nv_bfloat16> {
-    static __device__ __forceinline__ uint32_t pack(float a, float b)
-    {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-        return *reinterpret_cast<const uint32_t *>(&h);
-    }
-};
 
 // grid = (n tiles, m tiles, k splits)
 template <typename T, int BN, int STAGES, bool A_MN, bool B_MN, bool SPLITK>
@@ -407,6 +273,18 @@ gd_status dispatch_major(gd_backend *be, int ta, int tb, const CUtensorMap &ma, 
 #undef GDB_GO
 }
 
+gd_status reduce_partials(gd_backend *be, uint32_t dtype, const float *partial, void *c, size_t ldc, const void *bias, uint32_t M,
+                          uint32_t N, uint32_t splits, int bias_mode)
+{
+    const size_t quads = (size_t)M * (N / 4U);
+    if (dtype == GDB_DTYPE_F16) {
+        splitk_reduce_kernel<__half><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__half *)c, ldc, (const __half *)bias, M, N, splits, bias_mode);
+    } else {
+        splitk_reduce_kernel<__nv_bfloat16><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits, bias_mode);
+    }
+    return gdb_launched(be, "gemm_splitk_reduce");
+}
+
 }  // namespace
 
 // ta: A stored [K, M] (MN-major); tb: B stored [N, K] (K-major). Leading dimensions in bytes.
@@ -425,6 +303,19 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const
     if (bias != NULL && ((uintptr_t)bias % 2U) != 0U) {
         return GD_ERR_UNSUPPORTED;
     }
+    const size_t ldc = ldc_bytes / 2U;
+    float *partial = (float *)be->ws;
+    uint32_t splits = 1;
+    if (be->gemm_mode != 3) {
+        gd_status pst = gdb_gemm_tcgen05_pair(be, ta, tb, dtype, a, lda_bytes, b, ldb_bytes, c, ldc_bytes, bias, bias_mode, M, N, K, &splits);
+        if (pst == GD_OK) {
+            return splits == 1U ? GD_OK : reduce_partials(be, dtype, partial, c, ldc, bias, M, N, splits, bias_mode);
+        }
+        if (pst != GD_ERR_UNSUPPORTED) {
+            return pst;
+        }
+        splits = 1;
+    }
     const int bn = (N % 256U == 0U && (size_t)((M + BM - 1) / BM) * (N / 256U) >= (size_t)be->sm_count) ? 256 : 128;
     CUtensorMap ma, mb;
     const bool oka = ta ? make_tmap(&ma, dtype, a, K, M, lda_bytes, 64, BK) : make_tmap(&ma, dtype, a, M, K, lda_bytes, BK, BM);
@@ -435,7 +326,6 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const
     // split-K when the tile grid cannot fill the machine and the contraction is long
     const uint32_t tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     const uint32_t total_k = (K + BK - 1) / BK;
-    uint32_t splits = 1;
     if (tiles < (uint32_t)be->sm_count && total_k >= 16U) {
         splits = ((uint32_t)be->sm_count * 2U + tiles - 1U) / tiles;
         if (splits > total_k / 4U) splits = total_k / 4U;
@@ -445,8 +335,6 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const
     }
     uint32_t kps = (total_k + splits - 1U) / splits;
     splits = (total_k + kps - 1U) / kps;
-    float *partial = (float *)be->ws;
-    const size_t ldc = ldc_bytes / 2U;
     gd_status st;
     if (dtype == GDB_DTYPE_F16) {
         st = bn == 256 ? dispatch_major<__half, 256, 4>(be, ta, tb, ma, mb, c, ldc, bias, partial, M, N, K, splits, kps, bias_mode)
@@ -458,13 +346,7 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const
     if (st != GD_OK || splits == 1U) {
         return st;
     }
-    const size_t quads = (size_t)M * (N / 4U);
-    if (dtype == GDB_DTYPE_F16) {
-        splitk_reduce_kernel<__half><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__half *)c, ldc, (const __half *)bias, M, N, splits, bias_mode);
-    } else {
-        splitk_reduce_kernel<__nv_bfloat16><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits, bias_mode);
-    }
-    return gdb_launched(be, "gemm_splitk_reduce");
+    return reduce_partials(be, dtype, partial, c, ldc, bias, M, N, splits, bias_mode);
 }
 
 void gdb_tmap_cache_destroy(gd_backend *be) { (void)be; }

@@ -1,0 +1,379 @@
+// Persistent CTA-pair contraction for sm_100a: two CTAs on neighbouring SMs share one
+// 256 x 256 output tile (tcgen05.mma.cta_group::2), so each CTA fetches only its own 128 rows of
+// A and its own 128 columns of B per k-step, which cuts the shared-memory fill traffic per flop
+// by a third against a single-CTA 128 x 256 tile.
+//
+//   C[M, N] = A * B (+ bias), 16-bit operands, FP32 accumulation in tensor memory, one rounding;
+//   with SPLITK the kernel writes FP32 partial tiles [splits, M, N] that splitk_reduce sums.
+//
+// One cluster of two CTAs per SM pair, resident for the whole launch; work units (output tile x
+// k-slice) are dealt round-robin to the clusters. Tensor memory holds two accumulators of 256
+// columns, so the MMA issuer starts the next unit while the epilogue warps drain the previous one.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer for this CTA's operand halves (completion
+// bytes of both CTAs are signalled on the leader CTA's "full" barrier); warp 1 = tensor-memory
+// allocation, and in the leader CTA the MMA issuer for the pair (tcgen05.commit multicasts the
+// "stage free" and "accumulator ready" arrivals to both CTAs); warps 2-5 = epilogue: tcgen05.ld,
+// bias add and rounding in registers, 128-byte-swizzled staging in shared memory, TMA tile
+// stores (clipped at the matrix edges by the tensor map).
+//
+// No load uses cluster multicast. Every mbarrier wait is bounded; a wait that gives up records a
+// code in gd_backend::err_flag and the role leaves its loop, so the kernel always reaches the
+// common exit where tensor memory is released.
+#include "tcgen05.cuh"
+
+namespace {
+using namespace gdb_t5;
+
+constexpr int PBN = 256;         // tile columns of the pair
+constexpr int PSTAGES = 6;
+constexpr int P_A_BYTES = BM * BK * 2;
+constexpr int P_B_BYTES = (PBN / 2) * BK * 2;
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_STAGING_PER_WARP = 2 * 4096;   // two 32-row x 128-byte buffers
+constexpr int P_STAGING_BYTES = 4 * P_STAGING_PER_WARP;
+constexpr int P_SMEM_TOTAL = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 256 + 1024;
+
+template <typename T, bool A_MN, bool B_MN, bool SPLITK>
+__global__ void __launch_bounds__(192, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_c, const T *__restrict__ bias, uint32_t M, uint32_t N, uint32_t K,
+                 uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t k_iters_per_split, int bias_mode, int *err_flag)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
+    unsigned char *staging = smem + PSTAGES * P_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(staging + P_STAGING_BYTES);
+    // bars: [0, S) full, [S, 2S) empty, [2S, 2S+2) accumulator full, [2S+2, 2S+4) accumulator empty
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * PSTAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    const uint32_t total_k_iters = (K + BK - 1) / BK;
+    const uint32_t units = tiles_m * tiles_n * splits;
+
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[PSTAGES]);
+    const uint32_t tfull0 = smem_u32(&bars[2 * PSTAGES]), tempty0 = smem_u32(&bars[2 * PSTAGES + 2]);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull0 + 8 * b, 1);
+            mbar_init(tempty0 + 8 * b, 8);   // four epilogue warps in each of the two CTAs
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * PBN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    cluster_sync_all();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs, own operand halves) ----------------
+        if (lane == 0) {
+            const uint32_t full_leader = mapa_shared(full0, 0);
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t u = cluster_id; u < units && ok; u += n_clusters) {
+                const uint32_t tn = u % tiles_n, tm = (u / tiles_n) % tiles_m, z = u / (tiles_n * tiles_m);
+                const int am = (int)(tm * 2 * BM + rank * BM), bn = (int)(tn * PBN + rank * (PBN / 2));
+                const uint32_t k_begin = z * k_iters_per_split;
+                const uint32_t k_end = min(total_k_iters, k_begin + k_iters_per_split);
+                for (uint32_t kb = k_begin; kb < k_end; ++kb, ++it) {
+                    const uint32_t s = it % PSTAGES, ph = (it / PSTAGES) & 1U;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1U)) {
+                        atomicExch(err_flag, 201);
+                        ok = false;
+                        break;
+                    }
+                    if (rank == 0) {
+                        mbar_expect_tx(full0 + 8 * s, 2 * P_STAGE_BYTES);
+                    }
+                    const uint32_t a_dst = smem_u32(smem + s * P_STAGE_BYTES), b_dst = a_dst + P_A_BYTES;
+                    const uint32_t bar = full_leader + 8 * s;
+                    const int k0 = (int)(kb * BK);
+                    if (A_MN) {
+                        tma_load_2d_pair(a_dst, &tma_a, am, k0, bar);
+                        tma_load_2d_pair(a_dst + BK * 128, &tma_a, am + 64, k0, bar);
+                    } else {
+                        tma_load_2d_pair(a_dst, &tma_a, k0, am, bar);
+                    }
+                    if (B_MN) {
+                        tma_load_2d_pair(b_dst, &tma_b, bn, k0, bar);
+                        tma_load_2d_pair(b_dst + BK * 128, &tma_b, bn + 64, k0, bar);
+                    } else {
+                        tma_load_2d_pair(b_dst, &tma_b, k0, bn, bar);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t FMT = std::is_same<T, __nv_bfloat16>::value ? 1U : 0U;
+            constexpr uint32_t IDESC = (1U << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1U : 0U) << 15) | ((B_MN ? 1U : 0U) << 16) |
+                                       ((uint32_t)(PBN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            uint32_t it = 0, unit_idx = 0;
+            bool ok = true;
+            for (uint32_t u = cluster_id; u < units && ok; u += n_clusters, ++unit_idx) {
+                const uint32_t z = u / (tiles_n * tiles_m);
+                const uint32_t k_begin = z * k_iters_per_split;
+                const uint32_t k_end = min(total_k_iters, k_begin + k_iters_per_split);
+                const uint32_t buf = unit_idx & 1U, acc_ph = (unit_idx >> 1) & 1U;
+                if (!mbar_wait(tempty0 + 8 * buf, acc_ph ^ 1U)) {
+                    atomicExch(err_flag, 202);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * PBN;
+                for (uint32_t kb = k_begin; kb < k_end; ++kb, ++it) {
+                    const uint32_t s = it % PSTAGES, ph = (it / PSTAGES) & 1U;
+                    if (!mbar_wait(full0 + 8 * s, ph)) {
+                        atomicExch(err_flag, 203);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_base = smem_u32(smem + s * P_STAGE_BYTES), b_base = a_base + P_A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t adesc = A_MN ? make_smem_desc(a_base + kk * 2048, BK * 128, 1024)
+                                                    : make_smem_desc(a_base + kk * 32, 16, 1024);
+                        const uint64_t bdesc = B_MN ? make_smem_desc(b_base + kk * 2048, BK * 128, 1024)
+                                                    : make_smem_desc(b_base + kk * 32, 16, 1024);
+                        tcgen05_mma_f16_pair(d_tmem, adesc, bdesc, IDESC, (kb != k_begin || kk != 0) ? 1U : 0U);
+                    }
+                    tcgen05_commit_pair(empty0 + 8 * s, 3);
+                }
+                if (ok) {
+                    tcgen05_commit_pair(tfull0 + 8 * buf, 3);
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own tensor-memory lane quadrants 2,3,0,1 ----------------
+        const int quad = warp & 3;
+        unsigned char *my_stage = staging + (warp - 2) * P_STAGING_PER_WARP;
+        const uint32_t tempty_leader = mapa_shared(tempty0, 0);
+        uint32_t unit_idx = 0, store_cnt = 0;
+        constexpr int CHUNK_COLS = SPLITK ? 32 : 64;   // 128 bytes of output per row
+        for (uint32_t u = cluster_id; u < units; u += n_clusters, ++unit_idx) {
+            const uint32_t tn = u % tiles_n, tm = (u / tiles_n) % tiles_m, z = u / (tiles_n * tiles_m);
+            const uint32_t buf = unit_idx & 1U, acc_ph = (unit_idx >> 1) & 1U;
+            const bool got = mbar_wait(tfull0 + 8 * buf, acc_ph);
+            if (!got) {
+                if (lane == 0) atomicExch(err_flag, 204);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t row0 = tm * 2 * BM + rank * BM + quad * 32;
+            const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * PBN;
+#pragma unroll 1
+            for (int c = 0; c < PBN / CHUNK_COLS; ++c) {
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32b_x32_nowait(tbase + c * CHUNK_COLS, v0);
+                if (!SPLITK) {
+                    tmem_ld_32x32b_x32_nowait(tbase + c * CHUNK_COLS + 32, v1);
+                }
+                tmem_ld_wait();
+                if (c == PBN / CHUNK_COLS - 1) {
+                    // the accumulator has been copied out: hand the buffer back to the MMA issuer
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * buf);
+                }
+                unsigned char *sb = my_stage + (store_cnt & 1U) * 4096;
+                if (lane == 0) bulk_wait_group_read<1>();   // the store that last used this buffer has read it
+                __syncwarp();
+                const uint32_t col0 = tn * PBN + c * CHUNK_COLS;
+                unsigned char *rowp = sb + lane * 128;
+                if (SPLITK) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        *reinterpret_cast<uint4 *>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(v0[4 * j], v0[4 * j + 1], v0[4 * j + 2], v0[4 * j + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float f[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int idx = j * 8 + e;
+                            f[e] = __uint_as_float(idx < 32 ? v0[idx & 31] : v1[idx & 31]);
+                            if (bias != nullptr) {
+                                // mode 2 reproduces "round the product, then a rounded bias add"
+                                if (bias_mode == 2) f[e] = gdb_io<T>::rnd(f[e]);
+                                const uint32_t col = col0 + idx;
+                                f[e] += col < N ? gdb_io<T>::ld(bias, col) : 0.0f;
+                            }
+                        }
+                        uint4 o;
+                        o.x = half_pack<T>::pack(f[0], f[1]);
+                        o.y = half_pack<T>::pack(f[2], f[3]);
+                        o.z = half_pack<T>::pack(f[4], f[5]);
+                        o.w = half_pack<T>::pack(f[6], f[7]);
+                        *reinterpret_cast<uint4 *>(rowp + ((j ^ (lane & 7)) << 4)) = o;
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (row0 < M && col0 < N) {
+                        if (SPLITK) {
+                            tma_store_3d(&tma_c, (int)col0, (int)row0, (int)z, smem_u32(sb));
+                        } else {
+                            tma_store_2d(&tma_c, (int)col0, (int)row0, smem_u32(sb));
+                        }
+                    }
+                    bulk_commit_group();
+                }
+                ++store_cnt;
+            }
+        }
+        if (lane == 0) bulk_wait_all();
+    }
+    __syncwarp();
+    tcgen05_fence_before();
+    cluster_sync_all();   // neither CTA releases tensor memory while its peer may still use it
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * PBN)) : "memory");
+    }
+}
+
+int max_clusters(gd_backend *be, const void *kern)
+{
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3((unsigned)be->sm_count & ~1U);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = P_SMEM_TOTAL;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n < be->sm_count / 2 ? n : be->sm_count / 2;
+}
+
+template <typename T, bool A_MN, bool B_MN, bool SPLITK>
+gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const void *bias, uint32_t M,
+                      uint32_t N, uint32_t K, uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t kps, int bias_mode, int *clusters_out)
+{
+    auto kern = gemm_pair_kernel<T, A_MN, B_MN, SPLITK>;
+    static int clusters = -1;
+    if (clusters < 0) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL);
+        if (e != cudaSuccess) {
+            return gdb_fail(be, e, "tcgen05 pair gemm smem attribute");
+        }
+        clusters = max_clusters(be, (const void *)kern);
+    }
+    if (clusters_out != nullptr) {
+        *clusters_out = clusters;
+        return GD_OK;
+    }
+    if (clusters <= 0) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const uint32_t units = tiles_m * tiles_n * splits;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(2U * (units < (uint32_t)clusters ? units : (uint32_t)clusters));
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = P_SMEM_TOTAL;
+    cfg.stream = be->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, (const T *)bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, be->err_flag);
+    if (e != cudaSuccess) {
+        be->launches += 1U;
+        return gdb_fail(be, e, "gemm_tcgen05_pair");
+    }
+    return gdb_launched(be, "gemm_tcgen05_pair");
+}
+
+template <typename T>
+gd_status dispatch_pair(gd_backend *be, int ta, int tb, bool sk, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc,
+                        const void *bias, uint32_t M, uint32_t N, uint32_t K, uint32_t tiles_m, uint32_t tiles_n, uint32_t splits,
+                        uint32_t kps, int bias_mode, int *clusters_out)
+{
+#define GDB_GO(AM, BMJ)                                                                                                         \
+    (sk ? launch_pair<T, AM, BMJ, true>(be, ma, mb, mc, bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, clusters_out) \
+        : launch_pair<T, AM, BMJ, false>(be, ma, mb, mc, bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, clusters_out))
+    if (ta) {
+        return tb ? GDB_GO(true, false) : GDB_GO(true, true);
+    }
+    return tb ? GDB_GO(false, false) : GDB_GO(false, true);
+#undef GDB_GO
+}
+
+}  // namespace
+
+// Same contract as gdb_gemm_tcgen05 (which calls this first). Returns GD_ERR_UNSUPPORTED when the
+// problem is too small for 256-row tiles or clusters of two cannot be scheduled; `*splits_out`
+// receives the number of FP32 partial slices written to the workspace (1 = C was written directly).
+gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b,
+                                size_t ldb_bytes, void *c, size_t ldc_bytes, const void *bias, int bias_mode, uint32_t M, uint32_t N,
+                                uint32_t K, uint32_t *splits_out)
+{
+    *splits_out = 1;
+    if (M < 256U || N < 128U || K < 64U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    CUtensorMap ma, mb, mc;
+    const bool oka = ta ? make_tmap(&ma, dtype, a, K, M, lda_bytes, 64, BK) : make_tmap(&ma, dtype, a, M, K, lda_bytes, BK, BM);
+    const bool okb = tb ? make_tmap(&mb, dtype, b, N, K, ldb_bytes, BK, PBN / 2) : make_tmap(&mb, dtype, b, K, N, ldb_bytes, 64, BK);
+    if (!oka || !okb) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    int clusters = 0;
+    gd_status st = dtype == GDB_DTYPE_F16
+                       ? dispatch_pair<__half>(be, ta, tb, false, ma, mb, ma, bias, M, N, K, 0, 0, 1, 0, bias_mode, &clusters)
+                       : dispatch_pair<__nv_bfloat16>(be, ta, tb, false, ma, mb, ma, bias, M, N, K, 0, 0, 1, 0, bias_mode, &clusters);
+    if (st != GD_OK || clusters <= 0) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const uint32_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + PBN - 1) / PBN, tiles = tiles_m * tiles_n;
+    const uint32_t total_k = (K + BK - 1) / BK;
+    uint32_t splits = 1;
+    if (tiles * 2U <= (uint32_t)clusters && total_k >= 16U) {
+        splits = (uint32_t)clusters / tiles;
+        if (splits > total_k / 4U) splits = total_k / 4U;
+        while (splits > 1U && (size_t)splits * M * N * sizeof(float) > be->ws_bytes / 2U) --splits;
+        if (splits < 1U) splits = 1U;
+    }
+    if (splits == 1U && tiles * 4U < (uint32_t)clusters) {
+        return GD_ERR_UNSUPPORTED;   // a handful of tiles: the single-CTA kernel spreads them over more SMs
+    }
+    uint32_t kps = (total_k + splits - 1U) / splits;
+    splits = (total_k + kps - 1U) / kps;
+    const bool sk = splits > 1U;
+    const bool okc = sk ? make_tmap_f32_3d(&mc, be->ws, splits, M, N, 32) : make_tmap(&mc, dtype, c, M, N, ldc_bytes, 64, 32);
+    if (!okc) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    st = dtype == GDB_DTYPE_F16
+             ? dispatch_pair<__half>(be, ta, tb, sk, ma, mb, mc, bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, nullptr)
+             : dispatch_pair<__nv_bfloat16>(be, ta, tb, sk, ma, mb, mc, bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, nullptr);
+    if (st == GD_OK) {
+        *splits_out = splits;
+    }
+    return st;
+}

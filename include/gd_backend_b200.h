@@ -356,7 +356,8 @@ uint64_t gdb200_launch_count(const gd_backend *backend);
 const char *gdb200_last_error(const gd_backend *backend);
 /* Select the GEMM implementation: 0 = automatic (tcgen05 when the shape/alignment allows,
  * else the portable tiled kernel), 1 = force the portable kernel, 2 = require tcgen05 and
- * fail with GD_ERR_UNSUPPORTED when it cannot run. Returns the previous value. */
+ * fail with GD_ERR_UNSUPPORTED when it cannot run, 3 = automatic without the CTA-pair
+ * (cta_group::2) kernel, for A/B measurements. Returns the previous value. */
 int gdb200_set_gemm_mode(gd_backend *backend, int mode);
 /* Event pair timing helper: records an event on the backend stream and returns an opaque
  * handle; gdb200_event_elapsed_ms synchronises on `stop` and returns milliseconds. */

@@ -417,6 +417,8 @@ TC_SHAPES = [
     # m, k, n : forward / dX shapes of the model and ragged edges
     (1024, 512, 1536), (1024, 512, 512), (1000, 512, 3072), (2048, 1536, 512), (640, 512, 2048),
     (300, 512, 1536), (128, 64, 64), (264, 200, 136), (4096, 512, 1536),
+    # enough 256 x 256 tiles that resident CTA pairs take three units each (both accumulator buffers reused), ragged everywhere
+    (8192, 512, 1536), (5000, 328, 776),
 ]
 
 
