@@ -452,16 +452,20 @@ def run_decode(args) -> None:
     model.training = False
     prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(64, 256)).astype(np.int32)
     new_tokens = 256
-    g.greedy_generate(model, prompts[:, :32], 4, 512)  # warm-up (kernel loading)
+    native = args.host == "native"
+    generate = (lambda p, n: g.greedy_generate_native(model, p, n, 512)) if native else (lambda p, n: g.greedy_generate(model, p, n, 512))
+    generate(prompts[:, :32], 4)  # warm-up (kernel loading)
     l0 = ctx.launch_count()
     t0 = time.perf_counter()
-    out = g.greedy_generate(model, prompts, new_tokens, 512)
+    out = generate(prompts, new_tokens)
     ctx.flush()
     dt = time.perf_counter() - t0
     value = 64 * new_tokens / dt
     print(json.dumps({"metric": "gpt_lm_kv_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": new_tokens, "warmup": 1,
                       "ms_per_step": 1000.0 * dt / new_tokens, "higher_is_better": True, "dtype": "f16", "data": "synthetic",
-                      "config": {"workload": "greedy KV decode, 64 prompts x 256, 256 new tokens, cache 512, host argmax per step (prefill included)"},
+                      "config": {"workload": "greedy KV decode, 64 prompts x 256, 256 new tokens, cache 512, prefill included",
+                                 "host": "native: device argmax, ids / positions fed back on the device, decode step replayed as a CUDA graph" if native
+                                 else "python: host argmax and three small uploads per step"},
                       "gpu_launches": ctx.launch_count() - l0, "checksum": int(out.astype(np.int64).sum())}))
     ctx.destroy()
 

@@ -626,3 +626,313 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
     }
     return c.st;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Greedy KV-cache decode with the token feedback on the device.
+//
+// The reference samples on the host: every decode step downloads logits [B, V], applies the soft
+// cap and picks the first maximum (examples/gpt_lm/gpt_lm_shared.c:1322,1388-1398), then uploads the
+// next ids, positions and cache positions (:1652-1661). Here the same rule runs in a kernel and the
+// ids / positions stay in device memory, so a run of decode steps needs no host round trip; one
+// step is recorded once as a CUDA graph and replayed.
+namespace {
+
+// One block per row: softcap, non-finite -> -inf, first maximum wins. Writes the winner to
+// tokens[row] (the next step's input) and to out_tokens[*step_counter, row]; positions[row] += 1.
+template <typename T>
+__global__ void argmax_rows_kernel(const T *__restrict__ logits, uint32_t classes, float softcap, int32_t *__restrict__ ids_out,
+                                   int32_t *__restrict__ out_tokens, const int32_t *__restrict__ step_counter, int32_t max_steps,
+                                   int32_t *__restrict__ positions, uint32_t rows)
+{
+    const uint32_t row = blockIdx.x;
+    const T *x = logits + (size_t)row * classes;
+    float best = -INFINITY;
+    uint32_t best_i = 0xFFFFFFFFU;
+    for (uint32_t i = threadIdx.x; i < classes; i += blockDim.x) {
+        float v = gdb_io<T>::ld(x, i);
+        if (softcap > 0.0f) v = softcap * tanhf(v / softcap);
+        if (!isfinite(v)) v = -INFINITY;
+        if (v > best || best_i == 0xFFFFFFFFU) {   // strided scan visits indices in increasing order
+            best = v;
+            best_i = i;
+        }
+    }
+    __shared__ float sv[32];
+    __shared__ uint32_t si[32];
+    auto merge = [](float &a, uint32_t &ai, float b, uint32_t bi) {
+        if (bi != 0xFFFFFFFFU && (ai == 0xFFFFFFFFU || b > a || (b == a && bi < ai))) {
+            a = b;
+            ai = bi;
+        }
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffU, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffU, best_i, o);
+        merge(best, best_i, ob, oi);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) {
+        sv[warp] = best;
+        si[warp] = best_i;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < nw ? sv[lane] : -INFINITY;
+        best_i = lane < nw ? si[lane] : 0xFFFFFFFFU;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffU, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffU, best_i, o);
+            merge(best, best_i, ob, oi);
+        }
+        if (lane == 0) {
+            const int32_t id = best_i == 0xFFFFFFFFU ? 0 : (int32_t)best_i;
+            ids_out[row] = id;
+            if (out_tokens != nullptr) {
+                const int32_t t = *step_counter;
+                if (t >= 0 && t < max_steps) out_tokens[(size_t)t * rows + row] = id;
+            }
+            if (positions != nullptr) positions[row] += 1;
+        }
+    }
+}
+
+__global__ void advance_counter_kernel(int32_t *counter) { *counter += 1; }
+
+gd_status argmax_launch(gd_backend *be, const gd_backend_tensor_view *logits, float softcap, int32_t *ids_out, int32_t *out_tokens,
+                        const int32_t *counter, int32_t max_steps, int32_t *positions)
+{
+    if (logits == NULL || logits->rank != 2 || logits->shape[0] <= 0 || logits->shape[1] <= 0) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t rows = (uint32_t)logits->shape[0], classes = (uint32_t)logits->shape[1];
+    const void *x = gdb_tv_ptr(logits, logits->dtype);
+    if (x == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    switch (logits->dtype) {
+    case GDB_DTYPE_F16:
+        argmax_rows_kernel<__half><<<rows, 256, 0, be->stream>>>((const __half *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        break;
+    case GDB_DTYPE_BF16:
+        argmax_rows_kernel<__nv_bfloat16><<<rows, 256, 0, be->stream>>>((const __nv_bfloat16 *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        break;
+    case GDB_DTYPE_F32:
+        argmax_rows_kernel<float><<<rows, 256, 0, be->stream>>>((const float *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        break;
+    default:
+        return GD_ERR_UNSUPPORTED;
+    }
+    return gdb_launched(be, "argmax_rows");
+}
+
+Ten i32_tensor(gd_backend_buffer *buf, size_t off, int64_t n)
+{
+    Ten t;
+    memset(&t, 0, sizeof(t));
+    t.buf = buf;
+    t.off = off;
+    t.dt = GDB_DTYPE_I32;
+    t.rank = 1;
+    t.shape[0] = n;
+    return t;
+}
+
+// Enqueues one decode step (gpt_block_decode_cached, examples/gpt_lm/gpt_lm_shared.c:961-1115, and the
+// logits head :1204-1246) followed by the device-side argmax and counter advance.
+gd_status decode_step_body(gd_backend *be, const gdb200_gpt_spec *s, const gdb200_gpt_decode_state *d, size_t *scratch_used)
+{
+    Step c;
+    c.be = be;
+    c.s = s;
+    c.top = 0;
+    c.st = GD_OK;
+    c.where = "";
+    const int64_t B = d->batch, D = s->d_model, F = s->mlp_hidden, V = s->vocab_size, H = s->n_heads, Dh = s->head_dim, CAP = d->capacity;
+    const int L = s->n_layers;
+    const uint32_t dt = s->dtype;
+    const int P_FINAL = 1 + 10 * L, P_LMW = s->tied_lm_head ? 0 : P_FINAL + 1, P_LMB = P_FINAL + (s->tied_lm_head ? 1 : 2);
+    const Ten ids = i32_tensor(d->io_buffer, d->tokens_offset, B), pos = i32_tensor(d->io_buffer, d->positions_offset, B);
+    Ten x = c.alloc(dt, {B, D});
+    gd_backend_embedding_args ea = {(uint64_t)B, (uint64_t)V, (uint64_t)D};
+    {
+        const Ten emb_w = c.param(0, {V, D});
+        gd_backend_tensor_view a = tv(emb_w), b = tv(ids), o = tv(x);
+        c.ok(gd_backend_embedding_forward(be, &a, &b, &o, &ea), "embedding_forward");
+    }
+    gd_backend_rope_args rope = {s->rope_theta, (uint32_t)Dh, 0U};
+    gd_backend_sdpa_decode_args da;
+    memset(&da, 0, sizeof(da));
+    da.scale = (float)(1.0 / sqrt((double)Dh));
+    da.sliding_window = (uint32_t)s->sdpa_window;
+    gd_backend_kv_cache_append_args ka = {0};
+    for (int i = 0; i < L && c.st == GD_OK; ++i) {
+        const int pb = 1 + 10 * i;
+        Ten inv;
+        Ten normed = rms_forward(c, x, c.param(pb + 0, {D}), B, D, &inv);
+        Ten qkv = linear_t(c, normed, c.param(pb + 1, {3 * D, D}), c.param(pb + 2, {3 * D}), B, D, 3 * D);
+        Ten q = c.alloc(dt, {B, 1, H, Dh}), k = c.alloc(dt, {B, 1, H, Dh}), v = c.alloc(dt, {B, 1, H, Dh});
+        {
+            Ten q3 = q, k3 = k, v3 = v;
+            for (Ten *t : {&q3, &k3, &v3}) {
+                t->rank = 3;
+                t->shape[0] = B;
+                t->shape[1] = H;
+                t->shape[2] = Dh;
+            }
+            gd_backend_tensor_view a = tv(qkv), p = tv(pos), qv = tv(q3), kv = tv(k3), vvw = tv(v3);
+            c.ok(gd_backend_qkv_split_rope_forward(be, &a, &p, &qv, &kv, &vvw, (uint32_t)H, (uint32_t)Dh, &rope), "qkv_split_rope_forward");
+        }
+        Ten kc, vc;
+        memset(&kc, 0, sizeof(kc));
+        kc.buf = d->cache_buffer;
+        kc.dt = dt;
+        kc.rank = 4;
+        kc.shape[0] = B;
+        kc.shape[1] = CAP;
+        kc.shape[2] = H;
+        kc.shape[3] = Dh;
+        vc = kc;
+        kc.off = d->k_cache_offset[i];
+        vc.off = d->v_cache_offset[i];
+        Ten attn = c.alloc(dt, {B, 1, H, Dh});
+        {
+            gd_backend_tensor_view kcv = tv(kc), vcv = tv(vc), pv = tv(pos), kn = tv(k), vn = tv(v), qv = tv(q), ov = tv(attn);
+            c.ok(gd_backend_kv_cache_append_positions(be, &kcv, &vcv, &pv, &kn, &vn, &ka), "kv_cache_append_positions");
+            c.ok(gd_backend_sdpa_decode_positions(be, &qv, &kcv, &vcv, &pv, &ov, &da), "sdpa_decode_positions");
+        }
+        Ten proj = linear_t(c, attn, c.param(pb + 3, {D, D}), c.param(pb + 4, {D}), B, D, D);
+        Ten resid = c.alloc(dt, {B, D});
+        {
+            gd_backend_tensor_view r = tv(x), a = tv(proj), y = tv(resid);
+            c.ok(gd_backend_add(be, &r, &a, &y), "add");
+        }
+        Ten inv2;
+        Ten normed2 = rms_forward(c, resid, c.param(pb + 5, {D}), B, D, &inv2);
+        Ten up_gate = linear_t(c, normed2, c.param(pb + 6, {2 * F, D}), c.param(pb + 7, {2 * F}), B, D, 2 * F);
+        Ten act = c.alloc(dt, {B, F});
+        {
+            gd_backend_tensor_view a = tv(up_gate), o = tv(act);
+            c.ok(gd_backend_swiglu_split_forward(be, &a, &o), "swiglu_split_forward");
+        }
+        Ten mlp = c.alloc(dt, {B, D});
+        {
+            const Ten w = c.param(pb + 8, {F, D}), b = c.param(pb + 9, {D});
+            gd_backend_matrix_view am = mv(act, (uint32_t)B, (uint32_t)F), wm = mv(w, (uint32_t)F, (uint32_t)D), ym = mv(mlp, (uint32_t)B, (uint32_t)D);
+            gd_backend_vector_view bv = vv(b, 0, (uint32_t)D);
+            c.ok(gd_backend_linear(be, &am, &wm, &bv, &ym), "linear(down_proj)");
+        }
+        Ten out = c.alloc(dt, {B, D});
+        {
+            gd_backend_tensor_view r = tv(resid), a = tv(mlp), y = tv(out);
+            c.ok(gd_backend_add(be, &r, &a, &y), "add");
+        }
+        x = out;
+    }
+    Ten inv_f;
+    Ten final_norm = rms_forward(c, x, c.param(P_FINAL, {D}), B, D, &inv_f);
+    Ten logits = linear_t(c, final_norm, c.param(P_LMW, {V, D}), c.param(P_LMB, {V}), B, D, V);
+    if (c.st == GD_OK) {
+        gd_backend_tensor_view lv = tv(logits);
+        int32_t *io = (int32_t *)gdb_raw_ptr(d->io_buffer, 0, gd_backend_buffer_nbytes(d->io_buffer));
+        if (io == NULL) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+        int32_t *tok = io + d->tokens_offset / 4U, *posp = io + d->positions_offset / 4U;
+        int32_t *outp = io + d->out_tokens_offset / 4U, *cnt = io + d->step_counter_offset / 4U;
+        c.ok(argmax_launch(be, &lv, s->logits_softcap, tok, outp, cnt, d->max_steps, posp), "argmax_rows");
+        advance_counter_kernel<<<1, 1, 0, be->stream>>>(cnt);
+        c.ok(gdb_launched(be, "advance_counter"), "advance_counter");
+    }
+    if (scratch_used != NULL) {
+        *scratch_used = c.top;
+    }
+    if (c.st != GD_OK) {
+        snprintf(be->last_error, sizeof(be->last_error), "gpt decode step: %s", c.where);
+    }
+    return c.st;
+}
+
+}  // namespace
+
+extern "C" gd_status gdb200_argmax_rows(gd_backend *be, const gd_backend_tensor_view *logits, float softcap, const gd_backend_tensor_view *out_ids)
+{
+    if (be == NULL || logits == NULL || out_ids == NULL || logits->rank != 2 || out_ids->count != (size_t)logits->shape[0]) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    int32_t *out = (int32_t *)gdb_tv_ptr(out_ids, GDB_DTYPE_I32);
+    if (out == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    return argmax_launch(be, logits, softcap, out, nullptr, nullptr, 0, nullptr);
+}
+
+extern "C" gd_status gdb200_gpt_decode_steps(gd_backend *be, const gdb200_gpt_spec *s, const gdb200_gpt_decode_state *d, int32_t n_steps,
+                                             int32_t use_graph, size_t *scratch_used)
+{
+    if (be == NULL || s == NULL || d == NULL || n_steps < 0 || d->batch <= 0 || d->capacity <= 0 || s->n_layers <= 0 ||
+        s->n_layers > GDB200_GPT_MAX_LAYERS || s->n_heads * s->head_dim != s->d_model || d->cache_buffer == NULL || d->io_buffer == NULL ||
+        ((d->tokens_offset | d->positions_offset | d->out_tokens_offset | d->step_counter_offset) % 4U) != 0U) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const size_t io_bytes = gd_backend_buffer_nbytes(d->io_buffer);
+    if (d->tokens_offset + (size_t)d->batch * 4U > io_bytes || d->positions_offset + (size_t)d->batch * 4U > io_bytes ||
+        d->step_counter_offset + 4U > io_bytes || d->out_tokens_offset + (size_t)d->max_steps * (size_t)d->batch * 4U > io_bytes) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (n_steps == 0) {
+        return GD_OK;
+    }
+    int done = 0;
+    // The first step runs eagerly: it performs the one-time kernel attribute set-up that must not
+    // happen while a stream is being captured.
+    gd_status st = decode_step_body(be, s, d, scratch_used);
+    if (st != GD_OK) {
+        return st;
+    }
+    done = 1;
+    if (use_graph && n_steps - done >= 2) {
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        const uint64_t launches0 = be->launches;
+        cudaError_t e = cudaStreamBeginCapture(be->stream, cudaStreamCaptureModeThreadLocal);
+        if (e != cudaSuccess) {
+            return gdb_fail(be, e, "decode graph: begin capture");
+        }
+        st = decode_step_body(be, s, d, nullptr);
+        e = cudaStreamEndCapture(be->stream, &graph);
+        const uint64_t per_step = be->launches - launches0;
+        be->launches = launches0;
+        if (st != GD_OK || e != cudaSuccess || graph == nullptr) {
+            if (graph != nullptr) cudaGraphDestroy(graph);
+            return st != GD_OK ? st : gdb_fail(be, e, "decode graph: end capture");
+        }
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        if (e != cudaSuccess) {
+            cudaGraphDestroy(graph);
+            return gdb_fail(be, e, "decode graph: instantiate");
+        }
+        for (; done < n_steps; ++done) {
+            e = cudaGraphLaunch(exec, be->stream);
+            if (e != cudaSuccess) {
+                break;
+            }
+            be->launches += per_step;
+        }
+        // the graph objects may be released while launches are in flight; execution keeps its own references
+        cudaGraphExecDestroy(exec);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) {
+            return gdb_fail(be, e, "decode graph: launch");
+        }
+        return GD_OK;
+    }
+    for (; done < n_steps; ++done) {
+        st = decode_step_body(be, s, d, nullptr);
+        if (st != GD_OK) {
+            return st;
+        }
+    }
+    return GD_OK;
+}

@@ -145,6 +145,12 @@ class GptBatch(C.Structure):
                 ("cu_seqlens_offset", SZ), ("n_tokens", C.c_int64), ("n_cu", C.c_int64)]
 
 
+class GptDecodeState(C.Structure):
+    _fields_ = [("cache_buffer", P), ("io_buffer", P), ("k_cache_offset", SZ * GPT_MAX_LAYERS), ("v_cache_offset", SZ * GPT_MAX_LAYERS),
+                ("tokens_offset", SZ), ("positions_offset", SZ), ("out_tokens_offset", SZ), ("step_counter_offset", SZ),
+                ("batch", I32_T), ("capacity", I32_T), ("max_steps", I32_T)]
+
+
 TV = C.POINTER(TensorView)
 MV = C.POINTER(MatrixView)
 BV = C.POINTER(BatchedMatrixView)
@@ -260,6 +266,8 @@ PROTOTYPES = {
     "gdb200_embedding_backward_static_error": (C.c_char_p, []),
     "gdb200_embedding_backward_static_max_elems": (U64, []),
     "gdb200_gpt_train_step": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptBatch), U64, F, C.POINTER(SZ), C.POINTER(SZ)]),
+    "gdb200_argmax_rows": (_ST, [P, TV, F, TV]),
+    "gdb200_gpt_decode_steps": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptDecodeState), I32_T, I32_T, C.POINTER(SZ)]),
     "gdb200_dp_unique_id": (_ST, [P]),
     "gdb200_dp_init": (_ST, [P, P, C.c_int, C.c_int]),
     "gdb200_dp_all_reduce": (_ST, [P, P, SZ, SZ, U32]),

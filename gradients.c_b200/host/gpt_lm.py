@@ -435,6 +435,70 @@ def greedy_generate(model: GptLm, prompts: np.ndarray, new_tokens: int, capacity
     return out
 
 
+def model_spec(model: GptLm) -> "abi.GptSpec":
+    """gdb200_gpt_spec with the model fields and parameter locations only (what the decode driver reads)."""
+    mc, ctx = model.cfg, model.ctx
+    s = abi.GptSpec()
+    s.params_buffer, s.state_buffer, s.scratch_buffer = ctx.params.buffer, ctx.state.buffer, ctx.scratch.buffer
+    s.scratch_bytes = ctx.scratch.capacity
+    s.vocab_size, s.context_length, s.d_model, s.n_layers = mc.vocab_size, mc.context_length, mc.d_model, mc.n_layers
+    s.n_heads, s.head_dim, s.mlp_hidden, s.tied_lm_head = mc.n_heads, mc.head_dim, mc.mlp_hidden, 1 if mc.tied_lm_head else 0
+    s.sdpa_window, s.pad_token_id, s.dtype = mc.sdpa_window, mc.pad_token_id, mc.dtype
+    s.logits_softcap, s.rms_eps, s.rope_theta, s.dropout_seed = mc.logits_softcap, mc.rms_eps, mc.rope_theta, mc.dropout_seed
+    plist = model.param_list()
+    s.n_params, s.dp_world = len(plist), 1
+    for i, t in enumerate(plist):
+        s.param_offset[i], s.param_count[i] = t.offset, t.count
+    return s
+
+
+def device_argmax(ctx, logits: Tensor, softcap: float) -> Tensor:
+    """gdb200_argmax_rows: I32 [rows] of the first maximum of softcap(logits) per row."""
+    out = ctx.scratch_empty(I32, (logits.shape[0],), "argmax")
+    lv, ov = logits.tv(), out.tv()
+    ctx.check(ctx.lib.gdb200_argmax_rows(ctx.backend, lv, softcap, ov), "argmax_rows")
+    return out
+
+
+def greedy_generate_native(model: GptLm, prompts: np.ndarray, new_tokens: int, capacity: int, use_graph: bool = True) -> np.ndarray:
+    """Same result as greedy_generate, with sampling and the id / position feedback on the device:
+    packed prefill, device argmax of the prefill logits, then new_tokens - 1 decode steps enqueued
+    by gdb200_gpt_decode_steps with no host round trip; the generated ids are read once at the end."""
+    import ctypes as C
+    ctx, cfg = model.ctx, model.cfg
+    b, plen = prompts.shape
+    model.alloc_kv_cache(b, capacity)
+    ctx.begin_step()
+    ids = ctx.from_numpy(ctx.data, I32, prompts.reshape(-1).astype(np.int32))
+    pos = ctx.from_numpy(ctx.data, I32, np.tile(np.arange(plen, dtype=np.int32), b))
+    cu = ctx.from_numpy(ctx.data, I32, (np.arange(b + 1, dtype=np.int32) * plen))
+    cpos = ctx.from_numpy(ctx.data, I32, np.zeros(b, dtype=np.int32))
+    logits = model.prefill_last_logits(ids, pos, cu, cpos, np.arange(b) * plen + plen - 1)
+    first = device_argmax(ctx, logits, cfg.logits_softcap)
+    ctx.end_step()
+    # io words: tokens [b] = argmax of the prefill logits, positions [b] = prompt length,
+    # out_tokens [new_tokens, b] with row 0 filled, step counter = 1 (one read-back per generation)
+    first_ids = first.read().astype(np.int32)
+    words = np.zeros(2 * b + new_tokens * b + 1, dtype=np.int32)
+    words[:b], words[b:2 * b], words[2 * b:3 * b], words[-1] = first_ids, plen, first_ids, 1
+    io = ctx.from_numpy(ctx.state, I32, words)
+    d = abi.GptDecodeState()
+    d.cache_buffer, d.io_buffer = ctx.state.buffer, ctx.state.buffer
+    for i in range(cfg.n_layers):
+        d.k_cache_offset[i], d.v_cache_offset[i] = model.k_cache[i].offset, model.v_cache[i].offset
+    d.tokens_offset, d.positions_offset = io.offset, io.offset + 4 * b
+    d.out_tokens_offset, d.step_counter_offset = io.offset + 8 * b, io.offset + 8 * b + 4 * new_tokens * b
+    d.batch, d.capacity, d.max_steps = b, capacity, new_tokens
+    lib, be = ctx.lib, ctx.backend
+    ctx.begin_step()
+    spec = model_spec(model)
+    ctx.check(lib.gdb200_gpt_decode_steps(be, C.byref(spec), C.byref(d), new_tokens - 1, 1 if use_graph else 0, None), "gpt_decode_steps")
+    ctx.end_step()
+    ctx.flush()
+    flat = io.read()
+    return flat[2 * b:2 * b + new_tokens * b].reshape(new_tokens, b).T.copy()
+
+
 def host_argmax(logits: np.ndarray, softcap: float) -> np.ndarray:
     x = logits.astype(np.float32)
     if softcap > 0.0:

@@ -435,6 +435,32 @@ typedef struct gdb200_gpt_batch {
 gd_status gdb200_gpt_train_step(gd_backend *backend, const gdb200_gpt_spec *spec, const gdb200_gpt_batch *batch,
                                 uint64_t step, float lr, size_t *loss_offset, size_t *scratch_used);
 
+/* Device-side greedy sampling (no counterpart in the reference's backend ABI: the reference downloads
+ * the logits and samples on the host, examples/gpt_lm/gpt_lm_shared.c:1322,1371-1442). logits [rows,
+ * classes] F16/BF16/F32; softcap > 0 applies cap * tanh(x / cap) first; non-finite values count as
+ * -inf; the FIRST maximum wins (:1393). out_ids: I32 [rows]. */
+gd_status gdb200_argmax_rows(gd_backend *backend, const gd_backend_tensor_view *logits, float softcap,
+                             const gd_backend_tensor_view *out_ids);
+
+/* Greedy KV-cache decode with the token feedback kept on the device (replays gpt_block_decode_cached,
+ * examples/gpt_lm/gpt_lm_shared.c:961-1115,1204-1246, and the argmax rule of :1388-1398).
+ * cache_buffer holds per layer K and V caches [batch, capacity, n_heads, head_dim] in the storage
+ * dtype. io_buffer holds I32 words: tokens [batch] (ids fed to the next step, replaced by each step's
+ * argmax), positions [batch] (cache slot / rotary position of that id, incremented by each step),
+ * out_tokens [max_steps, batch] and one step counter (the row of out_tokens the next step writes;
+ * steps beyond max_steps are not recorded). Only spec's model fields, params_buffer / param_offset,
+ * scratch_buffer and scratch_bytes are used. */
+typedef struct gdb200_gpt_decode_state {
+    gd_backend_buffer *cache_buffer, *io_buffer;
+    size_t k_cache_offset[GDB200_GPT_MAX_LAYERS], v_cache_offset[GDB200_GPT_MAX_LAYERS];
+    size_t tokens_offset, positions_offset, out_tokens_offset, step_counter_offset;
+    int32_t batch, capacity, max_steps;
+} gdb200_gpt_decode_state;
+/* Enqueues n_steps decode steps without any host synchronisation. With use_graph != 0 the first step
+ * runs eagerly, the second is recorded as a CUDA graph and the rest replay it. */
+gd_status gdb200_gpt_decode_steps(gd_backend *backend, const gdb200_gpt_spec *spec, const gdb200_gpt_decode_state *state,
+                                  int32_t n_steps, int32_t use_graph, size_t *scratch_used);
+
 /* Data-parallel gradient exchange (the reference has no collective; one process per GPU).
  * id_bytes is the 128-byte ncclUniqueId produced by gdb200_dp_unique_id on rank 0. */
 gd_status gdb200_dp_unique_id(void *id_bytes_128);

@@ -50,7 +50,7 @@ def _worker(rank, world, port, host, q):
             b = g.synthetic_batch(cfg, 4, 16, 128, seed=100 * (rank + 1) + s, pad_to=cfg.context_length)
             losses.append(float(trainer.train_batch(b).read()[()]))
         ctx.flush()
-        flat = np.concatenate([p.read().view(np.uint16).reshape(-1) for p in model.parameters()])
+        flat = np.concatenate([p.read().view(np.uint16).reshape(-1) for p in model.param_list()])
         mine = torch.from_numpy(flat.astype(np.int32))
         both = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(both, mine)

@@ -92,6 +92,41 @@ def test_greedy_decode_matches_oracle():
                 break
 
 
+@pytest.mark.parametrize("use_graph", [False, True])
+@pytest.mark.parametrize("batch,window", [(4, 24), (64, 0)])
+def test_native_decode_feeds_back_on_the_device_and_matches_the_host_loop(batch, window, use_graph):
+    """gdb200_gpt_decode_steps (device argmax, ids / positions kept on the device, optional graph replay)
+    generates exactly the ids of the per-step host loop: same kernels, same logits, same tie rule."""
+    cfg = small_cfg(dropout_p=0.0, tied_lm_head=(batch == 4), sdpa_window=window)
+    hp = g.init_params(cfg, seed=12, residual_scaled=False)
+    prompts = np.random.default_rng(5).integers(0, cfg.vocab_size, size=(batch, 9)).astype(np.int32)
+    with pkg.runtime.Context(params_bytes=64 << 20, state_bytes=256 << 20, scratch_bytes=1 << 30) as ctx:
+        model = g.GptLm(ctx, cfg, hp)
+        model.training = False
+        want = g.greedy_generate(model, prompts, new_tokens=14, capacity=32)
+        got = g.greedy_generate_native(model, prompts, new_tokens=14, capacity=32, use_graph=use_graph)
+    assert np.array_equal(got, want)
+
+
+def test_device_argmax_first_maximum_softcap_and_non_finite():
+    rng = np.random.default_rng(8)
+    x = (rng.standard_normal((37, 2048)) * 3).astype(np.float16)
+    x[0, 5] = x[0, 900] = np.float16(40.0)         # tie: the first index wins
+    x[1, :] = np.float16(-np.inf)                   # nothing finite: index 0
+    x[2, 7] = np.float16(np.nan)
+    x[2, 8] = np.float16(np.inf)                    # non-finite values never win
+    x[3, 2047] = np.float16(60000.0)                # the last class
+    x[4, :] = np.float16(1.0)                       # all equal
+    with pkg.runtime.Context(params_bytes=16 << 20, state_bytes=16 << 20, scratch_bytes=64 << 20) as ctx:
+        for cap in (0.0, 30.0):
+            ctx.begin_step()
+            t = ctx.from_numpy(ctx.scratch, abi.F16, x.astype(np.float32))
+            got = g.device_argmax(ctx, t, cap).read()
+            ctx.end_step()
+            assert np.array_equal(got, g.host_argmax(x.astype(np.float32), cap)), cap
+            assert got[0] == 5 and got[1] == 0 and got[4] == 0 and got[2] not in (7, 8)
+
+
 @pytest.mark.parametrize("tied,chunk_env", [(False, None), (True, None), (False, "128")])
 def test_native_step_driver_matches_python_host(monkeypatch, tied, chunk_env):
     """The library's native per-step driver and the Python op capsules enqueue the same calls: losses
