@@ -239,6 +239,9 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype,
                            const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
                            void *c, size_t ldc_bytes, const void *bias, int bias_mode,
                            uint32_t M, uint32_t N, uint32_t K);
+// At most 64 output rows (decode): mma.sync kernel with K split over the warps of a CTA.
+gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
+                          void *c, size_t ldc_bytes, const void *bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K);
 // CTA-pair persistent variant; *splits_out > 1 means FP32 partials were left in the workspace.
 gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype,
                                 const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,

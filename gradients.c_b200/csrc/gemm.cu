@@ -238,6 +238,12 @@ gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb, const gd_backend_mat
             }
         }
     } scope(be, 2.0 * M * N * K, (double)es * ((double)M * K + (double)K * N + (double)M * N));
+    if (be->gemm_mode != 1 && be->gemm_mode != 2 && !ta && M <= 64U) {
+        gd_status st = gdb_gemm_skinny(be, tb, dt, ap, x->row_bytes, wp, w->row_bytes, cp, y->row_bytes, bp, bias_mode, M, N, K);
+        if (st != GD_ERR_UNSUPPORTED) {
+            return st;
+        }
+    }
     if (be->gemm_mode != 1 && dt != GDB_DTYPE_F32) {
         gd_status st = gdb_gemm_tcgen05(be, ta, tb, dt, ap, x->row_bytes, wp, w->row_bytes, cp, y->row_bytes, bp, bias_mode, M, N, K);
         if (st != GD_ERR_UNSUPPORTED) {

@@ -1,0 +1,128 @@
+// Contraction with at most 64 output rows (one KV-decode step: M = batch): C[M, N] = A[M, K] * B (+ bias).
+//
+// At this size a 128-row tcgen05 tile pipeline is all fixed latency (tensor-map fetch, tensor-memory
+// allocation, mbarrier round trips) and fills a dozen SMs; the operands are a few hundred KB and sit
+// in L2. Here one CTA owns 16 output columns, so N / 16 CTAs spread the weight read over the chip;
+// its 8 warps split K, each issues all of its fragment loads straight from global memory (one round
+// trip), runs mma.sync m16n8k16 with FP32 accumulators, and the partial tiles are summed through
+// shared memory before the bias add and the single rounding.
+#include "common.cuh"
+
+namespace {
+
+template <typename T> struct mma16816;
+template <> struct mma16816<__half> {
+    static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
+    {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+};
+template <> struct mma16816<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
+    {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+};
+
+constexpr int SK_ROWS = 64, SK_COLS = 16, SK_WARPS = 8;
+
+// B_KMAJOR: B stored [N, K] (matmul_nt); otherwise B stored [K, N] (matmul / linear).
+template <typename T, bool B_KMAJOR>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+gemm_skinny_kernel(const T *__restrict__ A, size_t lda, const T *__restrict__ B, size_t ldb, T *__restrict__ C, size_t ldc,
+                   const T *__restrict__ bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K)
+{
+    __shared__ float red[SK_WARPS][SK_ROWS][SK_COLS + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t n0 = blockIdx.x * SK_COLS;
+    const uint32_t k_steps = K / 16U, per_warp = (k_steps + SK_WARPS - 1) / SK_WARPS;
+    const uint32_t ks0 = min(k_steps, warp * per_warp), ks1 = min(k_steps, ks0 + per_warp);
+    float acc[4][2][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
+    const unsigned short *Bu = reinterpret_cast<const unsigned short *>(B);
+#pragma unroll 4
+    for (uint32_t ks = ks0; ks < ks1; ++ks) {
+        const uint32_t k0 = ks * 16U;
+        uint32_t a[4][4], b[2][2];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            const uint32_t r0 = mt * 16 + g, r1 = r0 + 8;
+            const T *p0 = A + (size_t)r0 * lda + k0 + 2 * t, *p1 = A + (size_t)r1 * lda + k0 + 2 * t;
+            a[mt][0] = r0 < M ? __ldg(reinterpret_cast<const uint32_t *>(p0)) : 0U;
+            a[mt][1] = r1 < M ? __ldg(reinterpret_cast<const uint32_t *>(p1)) : 0U;
+            a[mt][2] = r0 < M ? __ldg(reinterpret_cast<const uint32_t *>(p0 + 8)) : 0U;
+            a[mt][3] = r1 < M ? __ldg(reinterpret_cast<const uint32_t *>(p1 + 8)) : 0U;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const uint32_t n = n0 + nt * 8 + g;
+            if (B_KMAJOR) {
+                const T *p = B + (size_t)n * ldb + k0 + 2 * t;
+                b[nt][0] = __ldg(reinterpret_cast<const uint32_t *>(p));
+                b[nt][1] = __ldg(reinterpret_cast<const uint32_t *>(p + 8));
+            } else {
+                const unsigned short *p = Bu + (size_t)(k0 + 2 * t) * ldb + n;
+                b[nt][0] = (uint32_t)__ldg(p) | ((uint32_t)__ldg(p + ldb) << 16);
+                b[nt][1] = (uint32_t)__ldg(p + 8 * ldb) | ((uint32_t)__ldg(p + 9 * ldb) << 16);
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) mma16816<T>::run(acc[mt][nt], a[mt], b[nt]);
+    }
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int r = mt * 16 + g, c = nt * 8 + 2 * t;
+            red[warp][r][c] = acc[mt][nt][0];
+            red[warp][r][c + 1] = acc[mt][nt][1];
+            red[warp][r + 8][c] = acc[mt][nt][2];
+            red[warp][r + 8][c + 1] = acc[mt][nt][3];
+        }
+    __syncthreads();
+    for (int o = threadIdx.x; o < SK_ROWS * SK_COLS; o += SK_WARPS * 32) {
+        const int r = o / SK_COLS, c = o % SK_COLS;
+        if ((uint32_t)r >= M) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) v += red[w][r][c];
+        if (bias != nullptr) {
+            if (bias_mode == 2) v = gdb_io<T>::rnd(v);   // "round the product, then a rounded bias add"
+            v += gdb_io<T>::ld(bias, n0 + c);
+        }
+        gdb_io<T>::st(C, (size_t)r * ldc + n0 + c, v);
+    }
+}
+
+}  // namespace
+
+// Returns GD_ERR_UNSUPPORTED unless M <= 64, N % 16 == 0, K % 16 == 0 and the operands are 4-byte aligned.
+gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
+                          void *c, size_t ldc_bytes, const void *bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K)
+{
+    if ((dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) || M == 0U || M > (uint32_t)SK_ROWS || (N % SK_COLS) != 0U || (K % 16U) != 0U ||
+        K == 0U || (((uintptr_t)a | (uintptr_t)b | lda_bytes | ldb_bytes) % 4U) != 0U || (ldc_bytes % 2U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const size_t lda = lda_bytes / 2U, ldb = ldb_bytes / 2U, ldc = ldc_bytes / 2U;
+    const unsigned grid = N / SK_COLS;
+#define GDB_SK(TT, KM) gemm_skinny_kernel<TT, KM><<<grid, SK_WARPS * 32, 0, be->stream>>>((const TT *)a, lda, (const TT *)b, ldb, (TT *)c, ldc, (const TT *)bias, bias_mode, M, N, K)
+    if (dtype == GDB_DTYPE_F16) {
+        if (tb) GDB_SK(__half, true); else GDB_SK(__half, false);
+    } else {
+        if (tb) GDB_SK(__nv_bfloat16, true); else GDB_SK(__nv_bfloat16, false);
+    }
+#undef GDB_SK
+    return gdb_launched(be, "gemm_skinny");
+}

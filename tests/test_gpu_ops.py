@@ -128,7 +128,9 @@ def test_rms_norm(step, dtype, rows, cols):
 
 
 # ------------------------------------------------------------------ GEMM family
-GEMM_SHAPES = [(5, 3, 7), (64, 128, 96), (300, 512, 1536), (257, 520, 130)]
+GEMM_SHAPES = [(5, 3, 7), (64, 128, 96), (300, 512, 1536), (257, 520, 130),
+               # decode-sized M: the K-split mma.sync kernel
+               (64, 512, 1536), (33, 1536, 512), (1, 64, 16)]
 
 
 @pytest.mark.parametrize("dtype", [F16, BF16])
@@ -530,7 +532,7 @@ def test_flash_backward_without_forward_stats(step):
     close(host(dq), wdq, F16, scale=4)
 
 
-@pytest.mark.parametrize("m,k,n", [(1000, 512, 1536), (77, 40, 24), (4096, 1536, 512)])
+@pytest.mark.parametrize("m,k,n", [(1000, 512, 1536), (77, 40, 24), (4096, 1536, 512), (64, 512, 2048)])
 def test_fused_matmul_nt_bias_is_bit_identical_to_two_calls(step, m, k, n):
     ctx = step
     x = rnd_np(rng(95).standard_normal((m, k)).astype(np.float32), F16)
