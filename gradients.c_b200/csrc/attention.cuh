@@ -19,3 +19,5 @@ struct gdb_flash_args {
 // then runs the general kernels.
 gd_status gdb_flash_varlen_forward(gd_backend *be, const gdb_flash_args *a);
 gd_status gdb_flash_varlen_backward(gd_backend *be, const gdb_flash_args *a, bool have_forward_stats);
+// tcgen05 / tensor-memory forward (attention_tcgen05.cu); GD_ERR_UNSUPPORTED outside its fast path.
+gd_status gdb_attn5_forward(gd_backend *be, const gdb_flash_args *a);

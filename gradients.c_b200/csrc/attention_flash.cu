@@ -632,6 +632,12 @@ gd_status gdb_flash_varlen_forward(gd_backend *be, const gdb_flash_args *a)
     if (!fast_path(a) || ((uintptr_t)a->out_or_dq % 16U) != 0U) {
         return GD_ERR_UNSUPPORTED;
     }
+    if (be->attn_mode == 0) {
+        const gd_status st = gdb_attn5_forward(be, a);
+        if (st != GD_ERR_UNSUPPORTED) {
+            return st;
+        }
+    }
     const flash_params p = make_params(a);
     return a->dtype == GDB_DTYPE_F16 ? forward_typed<__half>(be, a, p) : forward_typed<__nv_bfloat16>(be, a, p);
 }

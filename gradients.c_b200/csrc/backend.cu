@@ -539,6 +539,18 @@ int gdb200_set_gemm_mode(gd_backend *be, int mode)
     return old;
 }
 
+int gdb200_set_attention_mode(gd_backend *be, int mode)
+{
+    if (be == NULL) {
+        return -1;
+    }
+    const int old = be->attn_mode;
+    if (mode == 0 || mode == 1) {
+        be->attn_mode = mode;
+    }
+    return old;
+}
+
 void *gdb200_event_record(gd_backend *be)
 {
     cudaEvent_t ev;

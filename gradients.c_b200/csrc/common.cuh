@@ -24,7 +24,8 @@ struct gd_backend {
     int sm_count;
     cudaStream_t stream;
     uint64_t launches;
-    int gemm_mode;            // 0 auto, 1 portable, 2 tcgen05 required
+    int gemm_mode;            // 0 auto, 1 portable, 2 tcgen05 required, 3 auto without the CTA-pair kernel
+    int attn_mode;            // 0 auto (tcgen05 attention when the shape allows), 1 mma.sync flash kernels only
     char last_error[256];
     // private workspace (split-K partials, reductions, attention scratch); created once at
     // create_default so no allocation happens while a step is being enqueued.

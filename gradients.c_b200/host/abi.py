@@ -253,6 +253,7 @@ PROTOTYPES = {
     "gdb200_launch_count": (U64, [P]),
     "gdb200_last_error": (C.c_char_p, [P]),
     "gdb200_set_gemm_mode": (C.c_int, [P, C.c_int]),
+    "gdb200_set_attention_mode": (C.c_int, [P, C.c_int]),
     "gdb200_event_record": (P, [P]),
     "gdb200_event_elapsed_ms": (F, [P, P]),
     "gdb200_event_destroy": (None, [P]),

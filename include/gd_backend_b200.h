@@ -359,6 +359,10 @@ const char *gdb200_last_error(const gd_backend *backend);
  * fail with GD_ERR_UNSUPPORTED when it cannot run, 3 = automatic without the CTA-pair
  * (cta_group::2) kernel, for A/B measurements. Returns the previous value. */
 int gdb200_set_gemm_mode(gd_backend *backend, int mode);
+/* Select the sdpa_varlen forward implementation: 0 = automatic (tcgen05 / tensor-memory kernel when
+ * head_dim is 64 and the storage is 16-bit, else the mma.sync flash kernels), 1 = mma.sync flash
+ * kernels only, for A/B measurements. Returns the previous value. */
+int gdb200_set_attention_mode(gd_backend *backend, int mode);
 /* Event pair timing helper: records an event on the backend stream and returns an opaque
  * handle; gdb200_event_elapsed_ms synchronises on `stop` and returns milliseconds. */
 void *gdb200_event_record(gd_backend *backend);

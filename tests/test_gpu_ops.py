@@ -507,6 +507,42 @@ def test_flash_attention_random_segments(step, dtype, hq, hkv, dh, window, total
     assert np.all(host(qt.grad)[nv:] == 0) and np.all(host(kt.grad)[nv:] == 0) and np.all(host(vt.grad)[nv:] == 0)
 
 
+@pytest.mark.parametrize("dtype,hq,hkv,window", [(F16, 8, 8, 0), (F16, 8, 8, 256), (BF16, 4, 2, 100)])
+def test_attention_tcgen05_forward_agrees_with_mma_sync_kernels(step, dtype, hq, hkv, window):
+    """The tensor-memory forward (mode 0) and the mma.sync forward (mode 1) on the same packed batch:
+    outputs within storage rounding of each other, statistics (row max, exp-sum) nearly equal."""
+    ctx, lib = step, step.lib
+    r = rng(92)
+    lengths = []
+    while sum(lengths) < 4000:
+        lengths.append(int(r.integers(16, 513)))
+    cu = make_cu(lengths)
+    n, dh = int(cu[-1]) + 21, 64
+    q, k, v = (rnd_np(r.standard_normal((n, h, dh)).astype(np.float32), dtype) for h in (hq, hkv, hkv))
+    qt, kt, vt, cut = dev(ctx, q, dtype), dev(ctx, k, dtype), dev(ctx, v, dtype), dev(ctx, cu, I32)
+    res = []
+    for mode in (0, 1):
+        old = lib.gdb200_set_attention_mode(ctx.backend, mode)
+        try:
+            out, stats = ctx.scratch_empty(dtype, (n, hq, dh)), ctx.scratch_empty(F32, (n, hq, 3))
+            ctx.fill(out, 0x7E7E7E7E)
+            ctx.fill(stats, 0)
+            args = abi.SdpaVarlenArgs(0.125, 1, window, 0, 512, 0)
+            ctx.check(lib.gd_backend_sdpa_varlen(ctx.backend, byref(qt.tv()), byref(kt.tv()), byref(vt.tv()), byref(cut.tv()), byref(out.tv()),
+                                                 byref(stats.tv()), byref(args)), f"sdpa_varlen mode {mode}")
+            ctx.flush()
+            res.append((host(out), host(stats)))
+        finally:
+            lib.gdb200_set_attention_mode(ctx.backend, old)
+    nv = int(cu[-1])
+    want, _ = O.sdpa_varlen_forward(t32(q[:nv]), t32(k[:nv]), t32(v[:nv]), cu, 0.125, True, window, 0, storage_name(dtype))
+    close(res[0][0][:nv], want, dtype, scale=2, what="tcgen05 forward vs oracle")
+    close(res[0][0][:nv], res[1][0][:nv], dtype, scale=2, what="tcgen05 vs mma.sync")
+    assert np.all(res[0][0][nv:] == 0)
+    np.testing.assert_allclose(res[0][1][:nv, :, 0], res[1][1][:nv, :, 0], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(res[0][1][:nv, :, 1], res[1][1][:nv, :, 1], rtol=2e-3)
+
+
 def test_flash_backward_without_forward_stats(step):
     """use_forward_stats = 0: the backward entry recomputes (max, sum) itself."""
     ctx = step
