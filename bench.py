@@ -50,6 +50,7 @@ def parse_args():
     ap.add_argument("--host", default="native", choices=["native", "python"],
                     help="who enqueues the per-step backend calls: the library's native driver or the Python op capsules")
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 portable kernel only, 2 tcgen05 required, 3 auto without the CTA-pair kernel")
+    ap.add_argument("--attention-mode", type=int, default=0, help="0 auto (tcgen05 forward when the shape allows), 1 mma.sync flash kernels only")
     return ap.parse_args()
 
 
@@ -213,6 +214,7 @@ def run_b200(args) -> None:
     ctx = pkg.runtime.Context(params_bytes=256 << 20, state_bytes=1 << 30, scratch_bytes=10 << 30, data_bytes=64 << 20)
     lib = ctx.lib
     lib.gdb200_set_gemm_mode(ctx.backend, args.gemm_mode)
+    lib.gdb200_set_attention_mode(ctx.backend, args.attention_mode)
     model = g.GptLm(ctx, cfg, g.init_params(cfg, seed=0))
     dp = None
     if world > 1:
