@@ -154,9 +154,9 @@ gd_status gd_backend_create_default(gd_backend **out_backend)
     be->l2_flush_bytes = (size_t)256U << 20;
     if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc((void **)&be->ws, be->ws_bytes) != cudaSuccess ||
-        cudaMalloc((void **)&be->err_flag, 256) != cudaSuccess ||
+        cudaMalloc((void **)&be->err_flag, GDB_FLAG_BYTES) != cudaSuccess ||
         cudaMallocHost((void **)&be->err_flag_host, 256) != cudaSuccess ||
-        cudaMemset(be->err_flag, 0, 256) != cudaSuccess) {
+        cudaMemset(be->err_flag, 0, GDB_FLAG_BYTES) != cudaSuccess) {
         gd_backend_destroy(be);
         return GD_ERR_OUT_OF_MEMORY;
     }

@@ -3,7 +3,9 @@
 // Used for bias gradients (gd_backend_reduce_rows) and the RMSNorm weight gradient. HBM-bound:
 // every lane reads 16 bytes per row, a warp covers 256 adjacent columns of a row, the 8 warps of a
 // block take rows round-robin with 4 rows in flight, partial sums per row chunk go to an FP32
-// workspace [chunks, cols] and a second kernel sums the chunks and rounds once.
+// workspace [chunks, cols]; the block that arrives last at a column tile (ticket counter) sums the
+// chunks in a fixed order and rounds once, so no second launch is needed and the result does not
+// depend on which block was last.
 #pragma once
 #include "common.cuh"
 
@@ -15,7 +17,7 @@ constexpr int TILE_COLS = 256, WARPS = 8;
 template <typename T, bool MUL>
 __global__ void __launch_bounds__(256)
 stage_kernel(const T *__restrict__ a, size_t lda, const T *__restrict__ b, size_t ldb, const float *__restrict__ f,
-             float *__restrict__ partial, size_t rows, size_t cols, size_t chunk)
+             float *__restrict__ partial, size_t rows, size_t cols, size_t chunk, T *__restrict__ y, unsigned *__restrict__ tickets)
 {
     __shared__ float sh[WARPS][TILE_COLS + 8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -70,6 +72,25 @@ stage_kernel(const T *__restrict__ a, size_t lda, const T *__restrict__ b, size_
         for (int w = 0; w < WARPS; ++w) s += sh[w][threadIdx.x];
         partial[(size_t)blockIdx.y * cols + c] = s;
     }
+    if (tickets == nullptr) {
+        return;   // a separate final_kernel sums the chunks
+    }
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        last = atomicAdd(&tickets[blockIdx.x], 1U) == gridDim.y - 1U;
+    }
+    __syncthreads();
+    if (last) {
+        __threadfence();
+        if (c < cols) {
+            float t = 0.0f;
+            for (unsigned k = 0; k < gridDim.y; ++k) t += __ldcg(&partial[(size_t)k * cols + c]);
+            gdb_io<T>::st(y, c, t);
+        }
+        if (threadIdx.x == 0) tickets[blockIdx.x] = 0U;   // leave the counter ready for the next reduction
+    }
 }
 
 // y[c] = round(sum_chunk partial[chunk, c]); block = 32 columns x 8 chunk groups.
@@ -120,9 +141,11 @@ gd_status run(gd_backend *be, const void *a, size_t lda, const void *b, size_t l
     const size_t chunk = (rows + chunks - 1U) / chunks;
     chunks = (rows + chunk - 1U) / chunk;
     dim3 grid((unsigned)((cols + TILE_COLS - 1U) / TILE_COLS), (unsigned)chunks);
-    stage_kernel<T, MUL><<<grid, 256, 0, be->stream>>>((const T *)a, lda, (const T *)b, ldb, f, partial, rows, cols, chunk);
+    const bool fused = grid.x <= (unsigned)GDB_TICKET_WORDS;
+    stage_kernel<T, MUL><<<grid, 256, 0, be->stream>>>((const T *)a, lda, (const T *)b, ldb, f, partial, rows, cols, chunk, (T *)y,
+                                                       fused ? gdb_tickets(be) : nullptr);
     gd_status st = gdb_launched(be, "column reduce stage");
-    if (st != GD_OK) {
+    if (st != GD_OK || fused) {
         return st;
     }
     final_kernel<T><<<(unsigned)((cols + 31U) / 32U), 256, 0, be->stream>>>(partial, (T *)y, chunks, cols);

@@ -15,6 +15,10 @@
 #include "../../include/gd_backend_b200.h"
 
 #define GDB_SM_COUNT_DEFAULT 148
+// gd_backend::err_flag points at GDB_FLAG_BYTES of zeroed device words: word 0 is the error code of
+// bounded waits; words 64.. are arrival tickets of multi-block reductions (each user leaves them zero).
+#define GDB_FLAG_BYTES 16384
+#define GDB_TICKET_WORDS ((GDB_FLAG_BYTES / 4) - 64)
 
 struct gdb_tmap_cache;  // tcgen05 GEMM tensor-map cache (gemm_tcgen05.cu)
 struct gdb_dp_state;    // NCCL state (dp.cu)
@@ -50,6 +54,8 @@ struct gd_backend_buffer {
     size_t reserve_bytes;  // size of the host address reservation when kind == DEVICE
     int kind;
 };
+
+static inline unsigned *gdb_tickets(const struct gd_backend *be) { return (unsigned *)be->err_flag + 64; }
 
 static inline gd_status gdb_fail(gd_backend *be, cudaError_t e, const char *what)
 {
