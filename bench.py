@@ -50,6 +50,10 @@ def parse_args():
     ap.add_argument("--host", default="native", choices=["native", "python"],
                     help="who enqueues the per-step backend calls: the library's native driver or the Python op capsules")
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 portable kernel only, 2 tcgen05 required, 3 auto without the CTA-pair kernel")
+    ap.add_argument("--model", default="baseline", choices=["baseline", "reference_default", "scaled"],
+                    help="train workload: baseline = the benchmark configuration (default); reference_default = the reference's own "
+                         "defaults (F1024, tied head, dropout 0.05, window 256); scaled = BF16 d2048 L24 H16x128 F5632 V32768 ctx2048, "
+                         "32 sequences of U[256,2048] per GPU")
     ap.add_argument("--attention-mode", type=int, default=0, help="0 auto (tcgen05 forward when the shape allows), 1 mma.sync flash kernels only")
     return ap.parse_args()
 
@@ -210,8 +214,15 @@ def run_b200(args) -> None:
     import __graft_entry__ as graft
     pkg = graft.load_package()
     g, abi = pkg.gpt_lm, pkg.abi
-    cfg, tc = g.GptConfig.baseline(), g.TrainConfig.baseline()
-    ctx = pkg.runtime.Context(params_bytes=256 << 20, state_bytes=1 << 30, scratch_bytes=10 << 30, data_bytes=64 << 20)
+    n_seqs, min_len, max_len = N_SEQS, MIN_LEN, MAX_LEN
+    if args.model == "scaled":
+        cfg, tc = g.GptConfig.scaled(), g.TrainConfig.baseline()
+        n_seqs, min_len, max_len = 32, 256, 2048
+        ctx = pkg.runtime.Context(params_bytes=4 << 30, state_bytes=20 << 30, scratch_bytes=120 << 30, data_bytes=64 << 20)
+    else:
+        cfg = g.GptConfig.baseline() if args.model == "baseline" else g.GptConfig.reference_default()
+        tc = g.TrainConfig.baseline() if args.model == "baseline" else g.TrainConfig()
+        ctx = pkg.runtime.Context(params_bytes=256 << 20, state_bytes=1 << 30, scratch_bytes=10 << 30, data_bytes=64 << 20)
     lib = ctx.lib
     lib.gdb200_set_gemm_mode(ctx.backend, args.gemm_mode)
     lib.gdb200_set_attention_mode(ctx.backend, args.attention_mode)
@@ -223,7 +234,7 @@ def run_b200(args) -> None:
     trainer = (g.NativeTrainer if args.host == "native" else g.Trainer)(model, tc, dp=dp)
 
     total_steps = args.warmup + args.steps
-    batches = [g.synthetic_batch(cfg, N_SEQS, MIN_LEN, MAX_LEN, seed=10_000 * (rank + 1) + s, pad_to=cfg.context_length)
+    batches = [g.synthetic_batch(cfg, n_seqs, min_len, max_len, seed=10_000 * (rank + 1) + s, pad_to=cfg.context_length)
                for s in range(total_steps)]
 
     # end-to-end arm: the host batches live in page-locked memory
@@ -314,9 +325,11 @@ def run_b200(args) -> None:
         out = {
             "metric": METRIC, "value": tokens / sec, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1000.0 * sec / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "gpt_lm train step, vocab 2048 ctx 512 d512 L3 H8x64 F1536 untied head, dropout 0.1, softcap 30, AdamW AMP clip",
-                       "global_batch": N_SEQS * world, "seq_len": "U[64,512] packed, padded to x512", "parallelism": f"dp{world}", "host": args.host,
+            "dtype": "bf16" if args.model == "scaled" else "f16", "data": "synthetic",
+            "config": {"workload": f"gpt_lm train step ({args.model}), vocab {cfg.vocab_size} ctx {cfg.context_length} d{cfg.d_model} L{cfg.n_layers} "
+                                   f"H{cfg.n_heads}x{cfg.head_dim} F{cfg.mlp_hidden} {'tied' if cfg.tied_lm_head else 'untied'} head, dropout {cfg.dropout_p}, "
+                                   f"window {cfg.sdpa_window}, softcap {cfg.logits_softcap:g}, AdamW AMP clip",
+                       "global_batch": n_seqs * world, "seq_len": f"U[{min_len},{max_len}] packed, padded to x{cfg.context_length}", "parallelism": f"dp{world}", "host": args.host,
                        "l2": "per-step working set (>2 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": e_tokens / e_sec, "unit": UNIT, "h2d_bytes_per_step": int(np.mean([b.h2d_bytes for b in batches])),
                     "d2h_bytes_per_step": 4},

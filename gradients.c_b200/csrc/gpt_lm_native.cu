@@ -474,6 +474,9 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         const int pb = 1 + 10 * i;
         size_t goff = 0, gelems = 0;
         alloc_grads(pb, 10, &goff, &gelems);
+        // Everything else this block's backward allocates is dead once the block is done (the gradient that flows on
+        // lives in the buffer that came in), so the space is reused by the next block: backward scratch is O(1) in depth.
+        const size_t layer_mark = c.top;
         // out = resid + dropout(mlp)
         Ten g_mlp = drop ? dropout_mask_backward(c, sv.mask2, gx, drop_scale) : gx;
         Ten g_resid = gx;  // adopted: later contributions accumulate into this buffer
@@ -522,6 +525,7 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         c.accumulate(g_resid, d_x1);
         gx = g_resid;
         reduce_range(goff, gelems);
+        c.top = layer_mark;
     }
     if (drop) gx = dropout_mask_backward(c, emb_mask, gx, drop_scale);
     {
