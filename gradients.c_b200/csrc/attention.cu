@@ -65,6 +65,7 @@ template <typename T, int MODE>
 __global__ void varlen_row_kernel(const T *q, const T *k, const T *v, const T *go, const int *cu, T *out_or_dq,
                                   float *stats, varlen_params p)
 {
+    gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (w >= (long long)p.n_tokens * p.hq) {
@@ -176,6 +177,7 @@ template <typename T>
 __global__ void varlen_dkv_kernel(const T *q, const T *k, const T *v, const T *go, const int *cu, const float *stats,
                                   T *dk, T *dv, varlen_params p)
 {
+    gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (w >= (long long)p.n_tokens * p.hkv) {
@@ -279,6 +281,7 @@ template <typename T, int DH>
 __global__ void decode_split_kernel(const T *q, const T *kc, const T *vc, const int *pos_buf, float *part_ml,
                                     float *part_acc, decode_params p, int splits)
 {
+    gdb_pdl_sync();
     constexpr int LPK = DH / 16, KPW = 32 / LPK;
     const int lane = threadIdx.x & 31, sub = lane % LPK, kg = lane / LPK;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -367,6 +370,7 @@ __global__ void decode_split_kernel(const T *q, const T *kc, const T *vc, const 
 template <typename T>
 __global__ void decode_combine_kernel(const float *part_ml, const float *part_acc, T *out, long long total, int dh, int splits)
 {
+    gdb_pdl_sync();
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (w >= total) {
@@ -394,6 +398,7 @@ __global__ void decode_combine_kernel(const float *part_ml, const float *part_ac
 template <typename T>
 __global__ void decode_generic_kernel(const T *q, const T *kc, const T *vc, const int *pos_buf, T *out, decode_params p)
 {
+    gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (w >= (long long)p.batch * p.tq * p.hq) {
@@ -471,6 +476,7 @@ __device__ __forceinline__ void copy_unit(unsigned char *dst, const unsigned cha
 __global__ void kv_append_kernel(unsigned char *kc, unsigned char *vc, const unsigned char *kn, const unsigned char *vn,
                                  const int *pos_buf, append_params p)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < p.total_units; g += stride) {
         const size_t src = g * p.unit;
@@ -487,6 +493,7 @@ __global__ void kv_append_kernel(unsigned char *kc, unsigned char *vc, const uns
 __global__ void kv_append_packed_kernel(unsigned char *kc, unsigned char *vc, const unsigned char *kn,
                                         const unsigned char *vn, const int *pos_buf, const int *cu, append_params p)
 {
+    gdb_pdl_sync();
     const unsigned units_per_row = p.row_bytes / p.unit;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < p.total_units; g += stride) {
@@ -542,7 +549,7 @@ gd_status varlen_fwd_generic(gd_backend *be, const void *q, const void *k, const
                              float *stats, const varlen_params &p)
 {
     const long long warps = (long long)p.n_tokens * p.hq;
-    varlen_row_kernel<T, 0><<<(unsigned)((warps + 3) / 4), 128, 0, be->stream>>>((const T *)q, (const T *)k, (const T *)v, nullptr, cu, (T *)out, stats, p);
+    gdb_launch(varlen_row_kernel<T, 0>, (unsigned)((warps + 3) / 4), 128, 0, be->stream, (const T *)q, (const T *)k, (const T *)v, nullptr, cu, (T *)out, stats, p);
     return gdb_launched(be, "sdpa_varlen generic");
 }
 
@@ -551,14 +558,14 @@ gd_status varlen_bwd_generic(gd_backend *be, const void *go, const void *q, cons
                              void *dq, void *dk, void *dv, float *stats, const varlen_params &p)
 {
     const long long warps = (long long)p.n_tokens * p.hq;
-    varlen_row_kernel<T, 1><<<(unsigned)((warps + 3) / 4), 128, 0, be->stream>>>((const T *)q, (const T *)k, (const T *)v, (const T *)go, cu, nullptr, stats, p);
+    gdb_launch(varlen_row_kernel<T, 1>, (unsigned)((warps + 3) / 4), 128, 0, be->stream, (const T *)q, (const T *)k, (const T *)v, (const T *)go, cu, nullptr, stats, p);
     gd_status st = gdb_launched(be, "sdpa_varlen bwd stats");
     if (st != GD_OK) return st;
-    varlen_row_kernel<T, 2><<<(unsigned)((warps + 3) / 4), 128, 0, be->stream>>>((const T *)q, (const T *)k, (const T *)v, (const T *)go, cu, (T *)dq, stats, p);
+    gdb_launch(varlen_row_kernel<T, 2>, (unsigned)((warps + 3) / 4), 128, 0, be->stream, (const T *)q, (const T *)k, (const T *)v, (const T *)go, cu, (T *)dq, stats, p);
     st = gdb_launched(be, "sdpa_varlen bwd dq");
     if (st != GD_OK) return st;
     const long long kw = (long long)p.n_tokens * p.hkv;
-    varlen_dkv_kernel<T><<<(unsigned)((kw + 3) / 4), 128, 0, be->stream>>>((const T *)q, (const T *)k, (const T *)v, (const T *)go, cu, stats, (T *)dk, (T *)dv, p);
+    gdb_launch(varlen_dkv_kernel<T>, (unsigned)((kw + 3) / 4), 128, 0, be->stream, (const T *)q, (const T *)k, (const T *)v, (const T *)go, cu, stats, (T *)dk, (T *)dv, p);
     return gdb_launched(be, "sdpa_varlen bwd dkv");
 }
 
@@ -624,7 +631,7 @@ gd_status decode_common(gd_backend *be, const gd_backend_tensor_view *q, const g
             float *ml = (float *)be->ws;
             float *pa = ml + (size_t)total * splits * 2U;
             dim3 grid((unsigned)((total + 3) / 4), (unsigned)splits);
-#define GDB_DECODE(T, DH) decode_split_kernel<T, DH><<<grid, 128, 0, be->stream>>>((const T *)qp, (const T *)kp, (const T *)vp, pp, ml, pa, p, splits)
+#define GDB_DECODE(T, DH) gdb_launch(decode_split_kernel<T, DH>, grid, 128, 0, be->stream, (const T *)qp, (const T *)kp, (const T *)vp, pp, ml, pa, p, splits)
             if (dt == GDB_DTYPE_F16) {
                 if (p.dh == 64) GDB_DECODE(__half, 64); else GDB_DECODE(__half, 128);
             } else {
@@ -634,20 +641,20 @@ gd_status decode_common(gd_backend *be, const gd_backend_tensor_view *q, const g
             gd_status st = gdb_launched(be, "sdpa_decode split");
             if (st != GD_OK) return st;
             if (dt == GDB_DTYPE_F16) {
-                decode_combine_kernel<__half><<<(unsigned)((total + 3) / 4), 128, 0, be->stream>>>(ml, pa, (__half *)op, total, p.dh, splits);
+                gdb_launch(decode_combine_kernel<__half>, (unsigned)((total + 3) / 4), 128, 0, be->stream, ml, pa, (__half *)op, total, p.dh, splits);
             } else {
-                decode_combine_kernel<__nv_bfloat16><<<(unsigned)((total + 3) / 4), 128, 0, be->stream>>>(ml, pa, (__nv_bfloat16 *)op, total, p.dh, splits);
+                gdb_launch(decode_combine_kernel<__nv_bfloat16>, (unsigned)((total + 3) / 4), 128, 0, be->stream, ml, pa, (__nv_bfloat16 *)op, total, p.dh, splits);
             }
             return gdb_launched(be, "sdpa_decode combine");
         }
     }
     const unsigned grid = (unsigned)((total + 3) / 4);
     if (dt == GDB_DTYPE_F16) {
-        decode_generic_kernel<__half><<<grid, 128, 0, be->stream>>>((const __half *)qp, (const __half *)kp, (const __half *)vp, pp, (__half *)op, p);
+        gdb_launch(decode_generic_kernel<__half>, grid, 128, 0, be->stream, (const __half *)qp, (const __half *)kp, (const __half *)vp, pp, (__half *)op, p);
     } else if (dt == GDB_DTYPE_BF16) {
-        decode_generic_kernel<__nv_bfloat16><<<grid, 128, 0, be->stream>>>((const __nv_bfloat16 *)qp, (const __nv_bfloat16 *)kp, (const __nv_bfloat16 *)vp, pp, (__nv_bfloat16 *)op, p);
+        gdb_launch(decode_generic_kernel<__nv_bfloat16>, grid, 128, 0, be->stream, (const __nv_bfloat16 *)qp, (const __nv_bfloat16 *)kp, (const __nv_bfloat16 *)vp, pp, (__nv_bfloat16 *)op, p);
     } else {
-        decode_generic_kernel<float><<<grid, 128, 0, be->stream>>>((const float *)qp, (const float *)kp, (const float *)vp, pp, (float *)op, p);
+        gdb_launch(decode_generic_kernel<float>, grid, 128, 0, be->stream, (const float *)qp, (const float *)kp, (const float *)vp, pp, (float *)op, p);
     }
     return gdb_launched(be, "sdpa_decode generic");
 }
@@ -712,9 +719,9 @@ gd_status append_common(gd_backend *be, const gd_backend_tensor_view *kc, const 
     p.cache_pos = a != NULL ? a->cache_pos : 0;
     const unsigned grid = gdb_grid_for(p.total_units, 256, be, 16);
     if (mode == 3) {
-        kv_append_packed_kernel<<<grid, 256, 0, be->stream>>>(kcp, vcp, knp, vnp, pp, cup, p);
+        gdb_launch(kv_append_packed_kernel, grid, 256, 0, be->stream, kcp, vcp, knp, vnp, pp, cup, p);
     } else {
-        kv_append_kernel<<<grid, 256, 0, be->stream>>>(kcp, vcp, knp, vnp, pp, p);
+        gdb_launch(kv_append_kernel, grid, 256, 0, be->stream, kcp, vcp, knp, vnp, pp, p);
     }
     return gdb_launched(be, "kv_cache_append");
 }

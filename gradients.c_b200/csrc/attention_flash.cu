@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(128)
 flash_q_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ go,
                const int *__restrict__ cu, T *__restrict__ out, float *__restrict__ stats, flash_params p)
 {
+    gdb_pdl_sync();
     constexpr int LD = DH + 8, BQ = 64, NT = BKV / 8, KT = DH / 16;
     extern __shared__ __align__(16) unsigned char fsm[];
     T *Qs = reinterpret_cast<T *>(fsm);
@@ -410,6 +411,7 @@ flash_kv_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
                 const int *__restrict__ cu, const float *__restrict__ stats, T *__restrict__ dk, T *__restrict__ dv,
                 flash_params p)
 {
+    gdb_pdl_sync();
     constexpr int LD = DH + 8, BK = 64, NT = BQT / 8, KT = DH / 16;
     extern __shared__ __align__(16) unsigned char fsm[];
     T *Ks = reinterpret_cast<T *>(fsm);
@@ -565,7 +567,7 @@ gd_status launch_q(gd_backend *be, const gdb_flash_args *a, const flash_params &
         configured = true;
     }
     dim3 grid((unsigned)((a->n_tokens + 63) / 64), (unsigned)a->hq);
-    kern<<<grid, 128, smem, be->stream>>>((const T *)a->q, (const T *)a->k, (const T *)a->v, (const T *)a->grad_out, a->cu, (T *)out, a->stats, p);
+    gdb_launch(kern, grid, 128, smem, be->stream, (const T *)a->q, (const T *)a->k, (const T *)a->v, (const T *)a->grad_out, a->cu, (T *)out, a->stats, p);
     return gdb_launched(be, MODE == 0 ? "flash_forward" : (MODE == 1 ? "flash_stats" : "flash_backward_dq"));
 }
 
@@ -582,7 +584,7 @@ gd_status launch_kv(gd_backend *be, const gdb_flash_args *a, const flash_params 
         configured = true;
     }
     dim3 grid((unsigned)((a->n_tokens + 63) / 64), (unsigned)a->hkv);
-    kern<<<grid, 128, smem, be->stream>>>((const T *)a->q, (const T *)a->k, (const T *)a->v, (const T *)a->grad_out, a->cu, a->stats, (T *)a->dk, (T *)a->dv, p);
+    gdb_launch(kern, grid, 128, smem, be->stream, (const T *)a->q, (const T *)a->k, (const T *)a->v, (const T *)a->grad_out, a->cu, a->stats, (T *)a->dk, (T *)a->dv, p);
     return gdb_launched(be, "flash_backward_dkv");
 }
 

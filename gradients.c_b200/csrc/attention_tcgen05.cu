@@ -106,6 +106,7 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
                  const __grid_constant__ CUtensorMap tma_v, T *__restrict__ out,
                  const int *__restrict__ cu, float *__restrict__ stats, attn5_params p, int *err_flag)
 {
+    gdb_pdl_sync();
     using plan = attn5_plan;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int cu_s[A_MAX_CU + 1];
@@ -441,7 +442,7 @@ gd_status launch_fwd(gd_backend *be, const gdb_flash_args *a)
     }
     attn5_params p = {a->n_tokens, a->batch, a->hq, a->hkv, a->window, ((a->n_tokens + A_BQ - 1) / A_BQ) * a->hq, a->scale};
     const unsigned grid = (unsigned)(p.n_items < resident ? p.n_items : resident);
-    kern<<<grid, A_THREADS, plan::TOTAL, be->stream>>>(mq, mk, mv, (T *)a->out_or_dq, a->cu, a->stats, p, be->err_flag);
+    gdb_launch(kern, grid, A_THREADS, plan::TOTAL, be->stream, mq, mk, mv, (T *)a->out_or_dq, a->cu, a->stats, p, be->err_flag);
     return gdb_launched(be, "attn5_forward");
 }
 

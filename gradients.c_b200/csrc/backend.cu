@@ -43,6 +43,7 @@ int pick_device(void)
 
 __global__ void fill_kernel(unsigned char *dst, size_t count, unsigned elem_size, unsigned pattern)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         if (elem_size == 4U) {
@@ -60,6 +61,7 @@ __global__ void fill_kernel(unsigned char *dst, size_t count, unsigned elem_size
 template <typename T>
 __global__ void rand_uniform_kernel(T *dst, size_t count, uint64_t seed, float low, float high)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         const uint64_t r = gdb_splitmix64(seed + (uint64_t)i);
@@ -74,6 +76,7 @@ __global__ void rand_uniform_kernel(T *dst, size_t count, uint64_t seed, float l
 template <typename T>
 __global__ void accumulate_kernel(T *dst, const T *src, size_t count)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         gdb_io<T>::st(dst, i, gdb_io<T>::ld(dst, i) + gdb_io<T>::ld(src, i));
@@ -82,6 +85,7 @@ __global__ void accumulate_kernel(T *dst, const T *src, size_t count)
 template <typename T>
 __global__ void accumulate_vec8_kernel(uint4 *dst, const uint4 *src, size_t vecs)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride) {
         gdb_vec8<T> d, s;
@@ -98,6 +102,7 @@ __global__ void accumulate_vec8_kernel(uint4 *dst, const uint4 *src, size_t vecs
 template <typename T>
 __global__ void scale_kernel(T *dst, const T *src, size_t count, float scale)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         gdb_io<T>::st(dst, i, gdb_io<T>::ld(src, i) * scale);
@@ -106,6 +111,7 @@ __global__ void scale_kernel(T *dst, const T *src, size_t count, float scale)
 
 __global__ void l2_flush_kernel(uint4 *buf, size_t vecs, unsigned tag)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride) {
         buf[i] = make_uint4(tag, tag, tag, tag);
@@ -428,7 +434,7 @@ gd_status gd_backend_fill(gd_backend *be, gd_backend_buffer *buffer, size_t offs
         be->launches += 1U;
         return e == cudaSuccess ? GD_OK : gdb_fail(be, e, "fill");
     }
-    fill_kernel<<<gdb_grid_for(count, 256, be, 8), 256, 0, be->stream>>>(dst, count, (unsigned)elem_size, pattern);
+    gdb_launch(fill_kernel, gdb_grid_for(count, 256, be, 8), 256, 0, be->stream, dst, count, (unsigned)elem_size, pattern);
     return gdb_launched(be, "fill");
 }
 
@@ -445,11 +451,11 @@ gd_status gd_backend_rand_uniform(gd_backend *be, gd_backend_buffer *buffer, siz
     void *dst = buffer->dptr + offset;
     const unsigned grid = gdb_grid_for(count, 256, be, 8);
     if (dtype == GDB_DTYPE_F16) {
-        rand_uniform_kernel<__half><<<grid, 256, 0, be->stream>>>((__half *)dst, count, seed, low, high);
+        gdb_launch(rand_uniform_kernel<__half>, grid, 256, 0, be->stream, (__half *)dst, count, seed, low, high);
     } else if (dtype == GDB_DTYPE_BF16) {
-        rand_uniform_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((__nv_bfloat16 *)dst, count, seed, low, high);
+        gdb_launch(rand_uniform_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (__nv_bfloat16 *)dst, count, seed, low, high);
     } else {
-        rand_uniform_kernel<float><<<grid, 256, 0, be->stream>>>((float *)dst, count, seed, low, high);
+        gdb_launch(rand_uniform_kernel<float>, grid, 256, 0, be->stream, (float *)dst, count, seed, low, high);
     }
     return gdb_launched(be, "rand_uniform");
 }
@@ -471,18 +477,18 @@ gd_status gd_backend_accumulate(gd_backend *be, gd_backend_buffer *dst_buffer, s
     if (vec) {
         const unsigned grid = gdb_grid_for(count / 8U, 256, be, 8);
         if (dtype == GDB_DTYPE_F16) {
-            accumulate_vec8_kernel<__half><<<grid, 256, 0, be->stream>>>((uint4 *)d, (const uint4 *)s, count / 8U);
+            gdb_launch(accumulate_vec8_kernel<__half>, grid, 256, 0, be->stream, (uint4 *)d, (const uint4 *)s, count / 8U);
         } else {
-            accumulate_vec8_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((uint4 *)d, (const uint4 *)s, count / 8U);
+            gdb_launch(accumulate_vec8_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (uint4 *)d, (const uint4 *)s, count / 8U);
         }
     } else {
         const unsigned grid = gdb_grid_for(count, 256, be, 8);
         if (dtype == GDB_DTYPE_F16) {
-            accumulate_kernel<__half><<<grid, 256, 0, be->stream>>>((__half *)d, (const __half *)s, count);
+            gdb_launch(accumulate_kernel<__half>, grid, 256, 0, be->stream, (__half *)d, (const __half *)s, count);
         } else if (dtype == GDB_DTYPE_BF16) {
-            accumulate_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((__nv_bfloat16 *)d, (const __nv_bfloat16 *)s, count);
+            gdb_launch(accumulate_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (__nv_bfloat16 *)d, (const __nv_bfloat16 *)s, count);
         } else {
-            accumulate_kernel<float><<<grid, 256, 0, be->stream>>>((float *)d, (const float *)s, count);
+            gdb_launch(accumulate_kernel<float>, grid, 256, 0, be->stream, (float *)d, (const float *)s, count);
         }
     }
     return gdb_launched(be, "accumulate");
@@ -509,11 +515,11 @@ gd_status gd_backend_scale(gd_backend *be, gd_backend_buffer *dst_buffer, size_t
     }
     const unsigned grid = gdb_grid_for(count, 256, be, 8);
     if (dtype == GDB_DTYPE_F16) {
-        scale_kernel<__half><<<grid, 256, 0, be->stream>>>((__half *)d, (const __half *)s, count, scale);
+        gdb_launch(scale_kernel<__half>, grid, 256, 0, be->stream, (__half *)d, (const __half *)s, count, scale);
     } else if (dtype == GDB_DTYPE_BF16) {
-        scale_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((__nv_bfloat16 *)d, (const __nv_bfloat16 *)s, count, scale);
+        gdb_launch(scale_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (__nv_bfloat16 *)d, (const __nv_bfloat16 *)s, count, scale);
     } else {
-        scale_kernel<float><<<grid, 256, 0, be->stream>>>((float *)d, (const float *)s, count, scale);
+        gdb_launch(scale_kernel<float>, grid, 256, 0, be->stream, (float *)d, (const float *)s, count, scale);
     }
     return gdb_launched(be, "scale");
 }
@@ -608,7 +614,7 @@ gd_status gdb200_flush_l2(gd_backend *be)
             return gdb_fail(be, e, "l2 flush buffer");
         }
     }
-    l2_flush_kernel<<<be->sm_count * 8, 256, 0, be->stream>>>((uint4 *)be->l2_flush, be->l2_flush_bytes / 16U, ++tag);
+    gdb_launch(l2_flush_kernel, be->sm_count * 8, 256, 0, be->stream, (uint4 *)be->l2_flush, be->l2_flush_bytes / 16U, ++tag);
     return gdb_launched(be, "flush_l2");
 }
 

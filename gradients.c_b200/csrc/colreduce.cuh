@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(256)
 stage_kernel(const T *__restrict__ a, size_t lda, const T *__restrict__ b, size_t ldb, const float *__restrict__ f,
              float *__restrict__ partial, size_t rows, size_t cols, size_t chunk, T *__restrict__ y, unsigned *__restrict__ tickets)
 {
+    gdb_pdl_sync();
     __shared__ float sh[WARPS][TILE_COLS + 8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t col = (size_t)blockIdx.x * TILE_COLS + (size_t)lane * 8;
@@ -98,6 +99,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 final_kernel(const float *__restrict__ partial, T *__restrict__ y, size_t chunks, size_t cols)
 {
+    gdb_pdl_sync();
     __shared__ float sh[8][33];
     const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
     const size_t c = (size_t)blockIdx.x * 32 + cx;
@@ -142,13 +144,13 @@ gd_status run(gd_backend *be, const void *a, size_t lda, const void *b, size_t l
     chunks = (rows + chunk - 1U) / chunk;
     dim3 grid((unsigned)((cols + TILE_COLS - 1U) / TILE_COLS), (unsigned)chunks);
     const bool fused = grid.x <= (unsigned)GDB_TICKET_WORDS;
-    stage_kernel<T, MUL><<<grid, 256, 0, be->stream>>>((const T *)a, lda, (const T *)b, ldb, f, partial, rows, cols, chunk, (T *)y,
+    gdb_launch(stage_kernel<T, MUL>, grid, 256, 0, be->stream, (const T *)a, lda, (const T *)b, ldb, f, partial, rows, cols, chunk, (T *)y,
                                                        fused ? gdb_tickets(be) : nullptr);
     gd_status st = gdb_launched(be, "column reduce stage");
     if (st != GD_OK || fused) {
         return st;
     }
-    final_kernel<T><<<(unsigned)((cols + 31U) / 32U), 256, 0, be->stream>>>(partial, (T *)y, chunks, cols);
+    gdb_launch(final_kernel<T>, (unsigned)((cols + 31U) / 32U), 256, 0, be->stream, partial, (T *)y, chunks, cols);
     return gdb_launched(be, "column reduce final");
 }
 

@@ -11,6 +11,9 @@
 #include <stddef.h>
 #include <string.h>
 #include <stdio.h>
+#ifdef __cplusplus
+#include <utility>
+#endif
 
 #include "../../include/gd_backend_b200.h"
 
@@ -142,6 +145,33 @@ static inline unsigned gdb_grid_for(size_t work_items, unsigned threads, const g
 }
 
 #ifdef __CUDACC__
+// ---- programmatic dependent launch ----
+// Every kernel of the backend is launched with programmatic stream serialization and starts with
+// gdb_pdl_sync(): it waits until the preceding kernel of the stream has completed and its writes are
+// visible, then allows the following kernel to be scheduled, so launch latency and block scheduling of
+// kernel N + 1 overlap the execution of kernel N instead of following it. Stream order is unchanged.
+__device__ __forceinline__ void gdb_pdl_sync()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t gdb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 // ---- storage <-> float conversion ----
 template <typename T> struct gdb_io;
 template <> struct gdb_io<__half> {

@@ -22,6 +22,7 @@ struct bcast_desc {
 template <typename T>
 __global__ void add_direct_kernel(const T *x, const T *y, T *out, size_t n)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         gdb_io<T>::st(out, i, gdb_io<T>::ld(x, i) + gdb_io<T>::ld(y, i));
@@ -30,6 +31,7 @@ __global__ void add_direct_kernel(const T *x, const T *y, T *out, size_t n)
 template <typename T>
 __global__ void add_direct_vec8_kernel(const uint4 *x, const uint4 *y, uint4 *out, size_t vecs)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride) {
         gdb_vec8<T> a, b;
@@ -46,6 +48,7 @@ __global__ void add_direct_vec8_kernel(const uint4 *x, const uint4 *y, uint4 *ou
 template <typename T>
 __global__ void add_row_vec8_kernel(const uint4 *x, const uint4 *y, uint4 *out, size_t vecs, unsigned row_vecs)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride) {
         gdb_vec8<T> a, b;
@@ -61,6 +64,7 @@ __global__ void add_row_vec8_kernel(const uint4 *x, const uint4 *y, uint4 *out, 
 template <typename T>
 __global__ void add_bcast_kernel(const T *x, const T *y, T *out, size_t n, bcast_desc d)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         size_t rem = i, xo = 0, yo = 0;
@@ -77,6 +81,7 @@ __global__ void add_bcast_kernel(const T *x, const T *y, T *out, size_t n, bcast
 template <typename T>
 __global__ void relu_kernel(const T *x, T *y, size_t n)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const float v = gdb_io<T>::ld(x, i);
@@ -86,6 +91,7 @@ __global__ void relu_kernel(const T *x, T *y, size_t n)
 template <typename T>
 __global__ void relu_backward_kernel(const T *x, const T *g, T *dx, size_t n)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         gdb_io<T>::st(dx, i, gdb_io<T>::ld(x, i) > 0.0f ? gdb_io<T>::ld(g, i) : 0.0f);
@@ -128,18 +134,18 @@ gd_status add_typed(gd_backend *be, const gd_backend_tensor_view *x, const gd_ba
     const bool al16 = (((uintptr_t)xp | (uintptr_t)yp | (uintptr_t)op) % 16U) == 0U;
     if constexpr (sizeof(T) == 2) {
         if (direct && al16 && (n % 8U) == 0U) {
-            add_direct_vec8_kernel<T><<<gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream>>>((const uint4 *)xp, (const uint4 *)yp, (uint4 *)op, n / 8U);
+            gdb_launch(add_direct_vec8_kernel<T>, gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (uint4 *)op, n / 8U);
             return gdb_launched(be, "add");
         }
         if (!direct && row && al16 && (d.shape[d.rank - 1] % 8U) == 0U) {
-            add_row_vec8_kernel<T><<<gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream>>>((const uint4 *)xp, (const uint4 *)yp, (uint4 *)op, n / 8U, d.shape[d.rank - 1] / 8U);
+            gdb_launch(add_row_vec8_kernel<T>, gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (uint4 *)op, n / 8U, d.shape[d.rank - 1] / 8U);
             return gdb_launched(be, "add");
         }
     }
     if (direct) {
-        add_direct_kernel<T><<<gdb_grid_for(n, 256, be, 8), 256, 0, be->stream>>>(xp, yp, op, n);
+        gdb_launch(add_direct_kernel<T>, gdb_grid_for(n, 256, be, 8), 256, 0, be->stream, xp, yp, op, n);
     } else {
-        add_bcast_kernel<T><<<gdb_grid_for(n, 256, be, 8), 256, 0, be->stream>>>(xp, yp, op, n, d);
+        gdb_launch(add_bcast_kernel<T>, gdb_grid_for(n, 256, be, 8), 256, 0, be->stream, xp, yp, op, n, d);
     }
     return gdb_launched(be, "add");
 }
@@ -169,6 +175,7 @@ template <typename T, int MODE>
 __global__ void dropout_kernel(const T *x, const T *residual, const unsigned char *mask_in, T *y,
                                unsigned char *mask_out, size_t n, float scale, uint64_t seed, unsigned threshold)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         bool keep;
@@ -191,6 +198,7 @@ template <typename T, int MODE>
 __global__ void dropout_vec8_kernel(const uint4 *x, const uint4 *residual, const uint2 *mask_in, uint4 *y,
                                     uint2 *mask_out, size_t vecs, float scale, uint64_t seed, unsigned threshold)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += stride) {
         gdb_vec8<T> xv, rv;
@@ -231,15 +239,13 @@ gd_status dropout_launch(gd_backend *be, const void *x, const void *residual, co
     const uintptr_t mal = (MODE == 3 ? (uintptr_t)mask_in : 0U) | ((MODE == 0 || MODE == 1) ? (uintptr_t)mask_out : 0U);
     if constexpr (sizeof(T) == 2) {
         if ((n % 8U) == 0U && (al % 16U) == 0U && (mal % 8U) == 0U) {
-            dropout_vec8_kernel<T, MODE><<<gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream>>>(
-                (const uint4 *)x, (const uint4 *)residual, (const uint2 *)mask_in, (uint4 *)y, (uint2 *)mask_out,
+            gdb_launch(dropout_vec8_kernel<T, MODE>, gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)x, (const uint4 *)residual, (const uint2 *)mask_in, (uint4 *)y, (uint2 *)mask_out,
                 n / 8U, scale, seed, threshold);
             return gdb_launched(be, "dropout");
         }
     }
     {
-        dropout_kernel<T, MODE><<<gdb_grid_for(n, 256, be, 8), 256, 0, be->stream>>>(
-            (const T *)x, (const T *)residual, (const unsigned char *)mask_in, (T *)y, (unsigned char *)mask_out,
+        gdb_launch(dropout_kernel<T, MODE>, gdb_grid_for(n, 256, be, 8), 256, 0, be->stream, (const T *)x, (const T *)residual, (const unsigned char *)mask_in, (T *)y, (unsigned char *)mask_out,
             n, scale, seed, threshold);
     }
     return gdb_launched(be, "dropout");
@@ -275,6 +281,7 @@ __device__ __forceinline__ float swiglu_sigmoid(float x)
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T *x1, const T *x2, T *out, size_t rows, size_t h, size_t in_ld)
 {
+    gdb_pdl_sync();
     const size_t n = rows * h, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t r = i / h, c = i - r * h;
@@ -285,6 +292,7 @@ __global__ void swiglu_fwd_kernel(const T *x1, const T *x2, T *out, size_t rows,
 template <typename T>
 __global__ void swiglu_fwd_vec8_kernel(const uint4 *x1, const uint4 *x2, uint4 *out, size_t rows, size_t hv, size_t in_ldv)
 {
+    gdb_pdl_sync();
     const size_t n = rows * hv, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t r = i / hv, c = i - r * hv;
@@ -303,6 +311,7 @@ template <typename T>
 __global__ void swiglu_bwd_kernel(const T *x1, const T *x2, const T *go, T *dx1, T *dx2,
                                   size_t rows, size_t h, size_t in_ld, size_t out_ld)
 {
+    gdb_pdl_sync();
     const size_t n = rows * h, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t r = i / h, c = i - r * h;
@@ -321,6 +330,7 @@ template <typename T>
 __global__ void swiglu_bwd_vec8_kernel(const uint4 *x1, const uint4 *x2, const uint4 *go, uint4 *dx1, uint4 *dx2,
                                        size_t rows, size_t hv, size_t in_ldv, size_t out_ldv)
 {
+    gdb_pdl_sync();
     const size_t n = rows * hv, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t r = i / hv, c = i - r * hv;
@@ -344,11 +354,9 @@ gd_status swiglu_fwd_typed(gd_backend *be, const void *x1, const void *x2, void 
 {
     const uintptr_t al = (uintptr_t)x1 | (uintptr_t)x2 | (uintptr_t)out;
     if ((al % 16U) == 0U && (h % 8U) == 0U && (in_ld % 8U) == 0U) {
-        swiglu_fwd_vec8_kernel<T><<<gdb_grid_for(rows * h / 8U, 256, be, 8), 256, 0, be->stream>>>(
-            (const uint4 *)x1, (const uint4 *)x2, (uint4 *)out, rows, h / 8U, in_ld / 8U);
+        gdb_launch(swiglu_fwd_vec8_kernel<T>, gdb_grid_for(rows * h / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)x1, (const uint4 *)x2, (uint4 *)out, rows, h / 8U, in_ld / 8U);
     } else {
-        swiglu_fwd_kernel<T><<<gdb_grid_for(rows * h, 256, be, 8), 256, 0, be->stream>>>(
-            (const T *)x1, (const T *)x2, (T *)out, rows, h, in_ld);
+        gdb_launch(swiglu_fwd_kernel<T>, gdb_grid_for(rows * h, 256, be, 8), 256, 0, be->stream, (const T *)x1, (const T *)x2, (T *)out, rows, h, in_ld);
     }
     return gdb_launched(be, "swiglu_forward");
 }
@@ -358,11 +366,9 @@ gd_status swiglu_bwd_typed(gd_backend *be, const void *x1, const void *x2, const
 {
     const uintptr_t al = (uintptr_t)x1 | (uintptr_t)x2 | (uintptr_t)go | (uintptr_t)dx1 | (uintptr_t)dx2;
     if (dx1 != NULL && dx2 != NULL && (al % 16U) == 0U && (h % 8U) == 0U && (in_ld % 8U) == 0U && (out_ld % 8U) == 0U) {
-        swiglu_bwd_vec8_kernel<T><<<gdb_grid_for(rows * h / 8U, 256, be, 8), 256, 0, be->stream>>>(
-            (const uint4 *)x1, (const uint4 *)x2, (const uint4 *)go, (uint4 *)dx1, (uint4 *)dx2, rows, h / 8U, in_ld / 8U, out_ld / 8U);
+        gdb_launch(swiglu_bwd_vec8_kernel<T>, gdb_grid_for(rows * h / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)x1, (const uint4 *)x2, (const uint4 *)go, (uint4 *)dx1, (uint4 *)dx2, rows, h / 8U, in_ld / 8U, out_ld / 8U);
     } else {
-        swiglu_bwd_kernel<T><<<gdb_grid_for(rows * h, 256, be, 8), 256, 0, be->stream>>>(
-            (const T *)x1, (const T *)x2, (const T *)go, (T *)dx1, (T *)dx2, rows, h, in_ld, out_ld);
+        gdb_launch(swiglu_bwd_kernel<T>, gdb_grid_for(rows * h, 256, be, 8), 256, 0, be->stream, (const T *)x1, (const T *)x2, (const T *)go, (T *)dx1, (T *)dx2, rows, h, in_ld, out_ld);
     }
     return gdb_launched(be, "swiglu_backward");
 }
@@ -451,11 +457,11 @@ gd_status gd_backend_relu(gd_backend *be, const gd_backend_tensor_view *x, const
     }
     const unsigned grid = gdb_grid_for(x->count, 256, be, 8);
     if (x->dtype == GDB_DTYPE_F16) {
-        relu_kernel<__half><<<grid, 256, 0, be->stream>>>((const __half *)xp, (__half *)yp, x->count);
+        gdb_launch(relu_kernel<__half>, grid, 256, 0, be->stream, (const __half *)xp, (__half *)yp, x->count);
     } else if (x->dtype == GDB_DTYPE_BF16) {
-        relu_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((const __nv_bfloat16 *)xp, (__nv_bfloat16 *)yp, x->count);
+        gdb_launch(relu_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (const __nv_bfloat16 *)xp, (__nv_bfloat16 *)yp, x->count);
     } else {
-        relu_kernel<float><<<grid, 256, 0, be->stream>>>((const float *)xp, (float *)yp, x->count);
+        gdb_launch(relu_kernel<float>, grid, 256, 0, be->stream, (const float *)xp, (float *)yp, x->count);
     }
     return gdb_launched(be, "relu");
 }
@@ -479,11 +485,11 @@ gd_status gd_backend_relu_backward(gd_backend *be, const gd_backend_tensor_view 
     }
     const unsigned grid = gdb_grid_for(x->count, 256, be, 8);
     if (x->dtype == GDB_DTYPE_F16) {
-        relu_backward_kernel<__half><<<grid, 256, 0, be->stream>>>((const __half *)xp, (const __half *)gp, (__half *)dp, x->count);
+        gdb_launch(relu_backward_kernel<__half>, grid, 256, 0, be->stream, (const __half *)xp, (const __half *)gp, (__half *)dp, x->count);
     } else if (x->dtype == GDB_DTYPE_BF16) {
-        relu_backward_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, x->count);
+        gdb_launch(relu_backward_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, x->count);
     } else {
-        relu_backward_kernel<float><<<grid, 256, 0, be->stream>>>((const float *)xp, (const float *)gp, (float *)dp, x->count);
+        gdb_launch(relu_backward_kernel<float>, grid, 256, 0, be->stream, (const float *)xp, (const float *)gp, (float *)dp, x->count);
     }
     return gdb_launched(be, "relu_backward");
 }

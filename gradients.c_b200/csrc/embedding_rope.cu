@@ -21,6 +21,7 @@ constexpr float TABLE_THETA = 10000.0f;
 template <typename T>
 __global__ void embedding_fwd_kernel(const T *table, const int *ids, T *out, size_t n_ids, size_t vocab, size_t dim)
 {
+    gdb_pdl_sync();
     const size_t n = n_ids * dim, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t row = i / dim, c = i - row * dim;
@@ -36,6 +37,7 @@ __global__ void embedding_fwd_kernel(const T *table, const int *ids, T *out, siz
 __global__ void embedding_fwd_vec_kernel(const uint4 *table, const int *ids, uint4 *out, size_t n_ids, size_t vocab,
                                          size_t row_vecs, unsigned nan_word)
 {
+    gdb_pdl_sync();
     const size_t n = n_ids * row_vecs, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t row = i / row_vecs, v = i - row * row_vecs;
@@ -51,6 +53,7 @@ __global__ void embedding_fwd_vec_kernel(const uint4 *table, const int *ids, uin
 template <typename T>
 __global__ void embedding_scatter_kernel(const T *grad, const int *ids, float *acc, size_t n_ids, size_t vocab, size_t dim)
 {
+    gdb_pdl_sync();
     const size_t n = n_ids * dim, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t row = i / dim, c = i - row * dim;
@@ -63,6 +66,7 @@ __global__ void embedding_scatter_kernel(const T *grad, const int *ids, float *a
 template <typename T>
 __global__ void cast_from_f32_kernel(const float *src, T *dst, size_t n)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         gdb_io<T>::st(dst, i, src[i]);
@@ -98,6 +102,7 @@ template <typename T, bool FWD>
 __global__ void qkv_split_rope_kernel(const T *a0, const T *a1, const T *a2, const int *pos_ids, T *o0, T *o1, T *o2,
                                       rope_params p, const float *table)
 {
+    gdb_pdl_sync();
     const unsigned half_dims = p.n_dims >> 1;
     const size_t area = (size_t)p.heads * p.head_dim;
     const size_t n = p.tokens * p.heads * half_dims, stride = (size_t)gridDim.x * blockDim.x;
@@ -140,6 +145,7 @@ template <typename T, bool FWD>
 __global__ void qkv_split_rope_vec8_kernel(const T *a0, const T *a1, const T *a2, const int *pos_ids, T *o0, T *o1, T *o2,
                                            rope_params p, const float *table)
 {
+    gdb_pdl_sync();
     const unsigned half_dims = p.head_dim >> 1, groups = half_dims >> 3;
     const size_t area = (size_t)p.heads * p.head_dim;
     const size_t n = p.tokens * p.heads * groups, stride = (size_t)gridDim.x * blockDim.x;
@@ -199,6 +205,7 @@ __global__ void qkv_split_rope_vec8_kernel(const T *a0, const T *a1, const T *a2
 template <typename T>
 __global__ void rope_kernel(const T *x, const int *pos_ids, T *out, rope_params p)
 {
+    gdb_pdl_sync();
     const size_t n = p.tokens * p.heads * p.head_dim, stride = (size_t)gridDim.x * blockDim.x;
     const unsigned half_dims = p.n_dims >> 1;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -327,9 +334,9 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
 #define GDB_ROPE_LAUNCH(T)                                                                                          \
     do {                                                                                                            \
         if (vec) {                                                                                                  \
-            qkv_split_rope_vec8_kernel<T, FWD><<<grid, 256, 0, be->stream>>>((const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table); \
+            gdb_launch(qkv_split_rope_vec8_kernel<T, FWD>, grid, 256, 0, be->stream, (const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table); \
         } else {                                                                                                    \
-            qkv_split_rope_kernel<T, FWD><<<grid, 256, 0, be->stream>>>((const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table); \
+            gdb_launch(qkv_split_rope_kernel<T, FWD>, grid, 256, 0, be->stream, (const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table); \
         }                                                                                                           \
     } while (0)
     if (dt == GDB_DTYPE_F16) {
@@ -376,11 +383,11 @@ gd_status rope_dispatch(gd_backend *be, const gd_backend_tensor_view *x, const g
     p.use_table = 0;
     const unsigned grid = gdb_grid_for(x->count, 256, be, 16);
     if (x->dtype == GDB_DTYPE_F16) {
-        rope_kernel<__half><<<grid, 256, 0, be->stream>>>((const __half *)xp, ip, (__half *)op, p);
+        gdb_launch(rope_kernel<__half>, grid, 256, 0, be->stream, (const __half *)xp, ip, (__half *)op, p);
     } else if (x->dtype == GDB_DTYPE_BF16) {
-        rope_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((const __nv_bfloat16 *)xp, ip, (__nv_bfloat16 *)op, p);
+        gdb_launch(rope_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (const __nv_bfloat16 *)xp, ip, (__nv_bfloat16 *)op, p);
     } else {
-        rope_kernel<float><<<grid, 256, 0, be->stream>>>((const float *)xp, ip, (float *)op, p);
+        gdb_launch(rope_kernel<float>, grid, 256, 0, be->stream, (const float *)xp, ip, (float *)op, p);
     }
     return gdb_launched(be, "rope");
 }
@@ -411,14 +418,13 @@ gd_status gd_backend_embedding_forward(gd_backend *be, const gd_backend_tensor_v
     const size_t row_bytes = a->dim * gdb_dtype_size(table->dtype);
     if ((row_bytes % 16U) == 0U && (((uintptr_t)tp | (uintptr_t)op) % 16U) == 0U && table->dtype != GDB_DTYPE_BF16) {
         const unsigned nan_word = table->dtype == GDB_DTYPE_F16 ? 0x7e007e00U : 0x7fc00000U;
-        embedding_fwd_vec_kernel<<<gdb_grid_for(a->ids_count * (row_bytes / 16U), 256, be, 16), 256, 0, be->stream>>>(
-            (const uint4 *)tp, ip, (uint4 *)op, a->ids_count, a->vocab, row_bytes / 16U, nan_word);
+        gdb_launch(embedding_fwd_vec_kernel, gdb_grid_for(a->ids_count * (row_bytes / 16U), 256, be, 16), 256, 0, be->stream, (const uint4 *)tp, ip, (uint4 *)op, a->ids_count, a->vocab, row_bytes / 16U, nan_word);
     } else if (table->dtype == GDB_DTYPE_F16) {
-        embedding_fwd_kernel<__half><<<gdb_grid_for(out->count, 256, be, 16), 256, 0, be->stream>>>((const __half *)tp, ip, (__half *)op, a->ids_count, a->vocab, a->dim);
+        gdb_launch(embedding_fwd_kernel<__half>, gdb_grid_for(out->count, 256, be, 16), 256, 0, be->stream, (const __half *)tp, ip, (__half *)op, a->ids_count, a->vocab, a->dim);
     } else if (table->dtype == GDB_DTYPE_BF16) {
-        embedding_fwd_kernel<__nv_bfloat16><<<gdb_grid_for(out->count, 256, be, 16), 256, 0, be->stream>>>((const __nv_bfloat16 *)tp, ip, (__nv_bfloat16 *)op, a->ids_count, a->vocab, a->dim);
+        gdb_launch(embedding_fwd_kernel<__nv_bfloat16>, gdb_grid_for(out->count, 256, be, 16), 256, 0, be->stream, (const __nv_bfloat16 *)tp, ip, (__nv_bfloat16 *)op, a->ids_count, a->vocab, a->dim);
     } else {
-        embedding_fwd_kernel<float><<<gdb_grid_for(out->count, 256, be, 16), 256, 0, be->stream>>>((const float *)tp, ip, (float *)op, a->ids_count, a->vocab, a->dim);
+        gdb_launch(embedding_fwd_kernel<float>, gdb_grid_for(out->count, 256, be, 16), 256, 0, be->stream, (const float *)tp, ip, (float *)op, a->ids_count, a->vocab, a->dim);
     }
     return gdb_launched(be, "embedding_forward");
 }
@@ -463,11 +469,11 @@ gd_status gd_backend_embedding_backward(gd_backend *be, const gd_backend_tensor_
     if (a->ids_count != 0U) {
         const unsigned grid = gdb_grid_for(grad_out->count, 256, be, 16);
         if (dt == GDB_DTYPE_F16) {
-            embedding_scatter_kernel<__half><<<grid, 256, 0, be->stream>>>((const __half *)gp, ip, acc, a->ids_count, a->vocab, a->dim);
+            gdb_launch(embedding_scatter_kernel<__half>, grid, 256, 0, be->stream, (const __half *)gp, ip, acc, a->ids_count, a->vocab, a->dim);
         } else if (dt == GDB_DTYPE_BF16) {
-            embedding_scatter_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((const __nv_bfloat16 *)gp, ip, acc, a->ids_count, a->vocab, a->dim);
+            gdb_launch(embedding_scatter_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (const __nv_bfloat16 *)gp, ip, acc, a->ids_count, a->vocab, a->dim);
         } else {
-            embedding_scatter_kernel<float><<<grid, 256, 0, be->stream>>>((const float *)gp, ip, acc, a->ids_count, a->vocab, a->dim);
+            gdb_launch(embedding_scatter_kernel<float>, grid, 256, 0, be->stream, (const float *)gp, ip, acc, a->ids_count, a->vocab, a->dim);
         }
         gd_status st = gdb_launched(be, "embedding_backward scatter");
         if (st != GD_OK) {
@@ -478,9 +484,9 @@ gd_status gd_backend_embedding_backward(gd_backend *be, const gd_backend_tensor_
         return GD_OK;
     }
     if (dt == GDB_DTYPE_F16) {
-        cast_from_f32_kernel<__half><<<gdb_grid_for(total, 256, be, 8), 256, 0, be->stream>>>(acc, (__half *)tp, total);
+        gdb_launch(cast_from_f32_kernel<__half>, gdb_grid_for(total, 256, be, 8), 256, 0, be->stream, acc, (__half *)tp, total);
     } else {
-        cast_from_f32_kernel<__nv_bfloat16><<<gdb_grid_for(total, 256, be, 8), 256, 0, be->stream>>>(acc, (__nv_bfloat16 *)tp, total);
+        gdb_launch(cast_from_f32_kernel<__nv_bfloat16>, gdb_grid_for(total, 256, be, 8), 256, 0, be->stream, acc, (__nv_bfloat16 *)tp, total);
     }
     return gdb_launched(be, "embedding_backward cast");
 }

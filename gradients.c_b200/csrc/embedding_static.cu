@@ -32,6 +32,7 @@ thread_local char g_error[192];
 template <typename T>
 __global__ void static_scatter_kernel(const T *grad, const int *ids, float *acc, size_t n_ids, size_t vocab, size_t dim)
 {
+    gdb_pdl_sync();
     const size_t n = n_ids * dim, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t row = i / dim, c = i - row * dim;
@@ -45,6 +46,7 @@ __global__ void static_scatter_kernel(const T *grad, const int *ids, float *acc,
 template <typename T>
 __global__ void static_cast_kernel(const float *acc, T *out, size_t n)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         gdb_io<T>::st(out, i, acc[i]);
@@ -126,19 +128,19 @@ gd_status gdb200_embedding_backward_static(void *stream, const void *grad_out, c
     if (ids_count != 0U) {
         const size_t items = (size_t)(ids_count * dim);
         if (dtype == GDB_DTYPE_F16) {
-            static_scatter_kernel<__half><<<grid_for(items), 256, 0, s>>>((const __half *)grad_out, ids, table, ids_count, vocab, dim);
+            gdb_launch(static_scatter_kernel<__half>, grid_for(items), 256, 0, s, (const __half *)grad_out, ids, table, ids_count, vocab, dim);
         } else if (dtype == GDB_DTYPE_BF16) {
-            static_scatter_kernel<__nv_bfloat16><<<grid_for(items), 256, 0, s>>>((const __nv_bfloat16 *)grad_out, ids, table, ids_count, vocab, dim);
+            gdb_launch(static_scatter_kernel<__nv_bfloat16>, grid_for(items), 256, 0, s, (const __nv_bfloat16 *)grad_out, ids, table, ids_count, vocab, dim);
         } else {
-            static_scatter_kernel<float><<<grid_for(items), 256, 0, s>>>((const float *)grad_out, ids, table, ids_count, vocab, dim);
+            gdb_launch(static_scatter_kernel<float>, grid_for(items), 256, 0, s, (const float *)grad_out, ids, table, ids_count, vocab, dim);
         }
     }
     if (dtype == GDB_DTYPE_F16) {
-        static_cast_kernel<__half><<<grid_for(total), 256, 0, s>>>(table, (__half *)grad_table, total);
+        gdb_launch(static_cast_kernel<__half>, grid_for(total), 256, 0, s, table, (__half *)grad_table, total);
     } else if (dtype == GDB_DTYPE_BF16) {
-        static_cast_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, s>>>(table, (__nv_bfloat16 *)grad_table, total);
+        gdb_launch(static_cast_kernel<__nv_bfloat16>, grid_for(total), 256, 0, s, table, (__nv_bfloat16 *)grad_table, total);
     } else {
-        static_cast_kernel<float><<<grid_for(total), 256, 0, s>>>(table, (float *)grad_table, total);
+        gdb_launch(static_cast_kernel<float>, grid_for(total), 256, 0, s, table, (float *)grad_table, total);
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) {

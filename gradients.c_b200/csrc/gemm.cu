@@ -34,6 +34,7 @@ __global__ void gemm_portable_kernel(const T *__restrict__ a, size_t sam, size_t
                                      unsigned M, unsigned N, unsigned K,
                                      size_t batch_a, size_t batch_b, size_t batch_c, int bias_mode)
 {
+    gdb_pdl_sync();
     __shared__ float as[TK][TM + 4];
     __shared__ float bs[TK][TN + 4];
     a += (size_t)blockIdx.z * batch_a;
@@ -113,6 +114,7 @@ __global__ void gemm_portable_kernel(const T *__restrict__ a, size_t sam, size_t
 template <typename T>
 __global__ void reduce_rows_stage_kernel(const T *x, size_t ld, float *partial, size_t rows, size_t cols, size_t chunk)
 {
+    gdb_pdl_sync();
     const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t r0 = (size_t)blockIdx.y * chunk;
     size_t r1 = r0 + chunk;
@@ -138,6 +140,7 @@ __global__ void reduce_rows_stage_kernel(const T *x, size_t ld, float *partial, 
 template <typename T>
 __global__ void reduce_rows_final_kernel(const float *partial, T *y, size_t blocks, size_t cols)
 {
+    gdb_pdl_sync();
     const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= cols) {
         return;
@@ -170,7 +173,7 @@ void launch_portable(gd_backend *be, int ta, int tb, const void *a, size_t lda, 
     const size_t sam = ta ? 1 : lda, sak = ta ? lda : 1;
     const size_t sbk = tb ? 1 : ldb, sbn = tb ? ldb : 1;
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, batch);
-    gemm_portable_kernel<T><<<grid, 256, 0, be->stream>>>((const T *)a, sam, sak, (const T *)b, sbk, sbn, (T *)c, ldc,
+    gdb_launch(gemm_portable_kernel<T>, grid, 256, 0, be->stream, (const T *)a, sam, sak, (const T *)b, sbk, sbn, (T *)c, ldc,
                                                            (const T *)bias, M, N, K, ba, bb, bc, bias_mode);
 }
 
@@ -447,22 +450,22 @@ gd_status gd_backend_reduce_rows(gd_backend *be, const gd_backend_matrix_view *x
     float *ws = (float *)be->ws;
     dim3 grid(col_blocks, (unsigned)blocks);
     if (dt == GDB_DTYPE_F16) {
-        reduce_rows_stage_kernel<__half><<<grid, 256, 0, be->stream>>>((const __half *)xp, ld, ws, rows, cols, chunk);
+        gdb_launch(reduce_rows_stage_kernel<__half>, grid, 256, 0, be->stream, (const __half *)xp, ld, ws, rows, cols, chunk);
     } else if (dt == GDB_DTYPE_BF16) {
-        reduce_rows_stage_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((const __nv_bfloat16 *)xp, ld, ws, rows, cols, chunk);
+        gdb_launch(reduce_rows_stage_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (const __nv_bfloat16 *)xp, ld, ws, rows, cols, chunk);
     } else {
-        reduce_rows_stage_kernel<float><<<grid, 256, 0, be->stream>>>((const float *)xp, ld, ws, rows, cols, chunk);
+        gdb_launch(reduce_rows_stage_kernel<float>, grid, 256, 0, be->stream, (const float *)xp, ld, ws, rows, cols, chunk);
     }
     gd_status st = gdb_launched(be, "reduce_rows stage");
     if (st != GD_OK) {
         return st;
     }
     if (dt == GDB_DTYPE_F16) {
-        reduce_rows_final_kernel<__half><<<col_blocks, 256, 0, be->stream>>>(ws, (__half *)yp, blocks, cols);
+        gdb_launch(reduce_rows_final_kernel<__half>, col_blocks, 256, 0, be->stream, ws, (__half *)yp, blocks, cols);
     } else if (dt == GDB_DTYPE_BF16) {
-        reduce_rows_final_kernel<__nv_bfloat16><<<col_blocks, 256, 0, be->stream>>>(ws, (__nv_bfloat16 *)yp, blocks, cols);
+        gdb_launch(reduce_rows_final_kernel<__nv_bfloat16>, col_blocks, 256, 0, be->stream, ws, (__nv_bfloat16 *)yp, blocks, cols);
     } else {
-        reduce_rows_final_kernel<float><<<col_blocks, 256, 0, be->stream>>>(ws, (float *)yp, blocks, cols);
+        gdb_launch(reduce_rows_final_kernel<float>, col_blocks, 256, 0, be->stream, ws, (float *)yp, blocks, cols);
     }
     return gdb_launched(be, "reduce_rows final");
 }

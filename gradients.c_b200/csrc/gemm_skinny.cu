@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const T *__restrict__ A, size_t lda, const T *__restrict__ B, size_t ldb, T *__restrict__ C, size_t ldc,
                    const T *__restrict__ bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K)
 {
+    gdb_pdl_sync();
     __shared__ float red[SK_WARPS][SK_ROWS][SK_COLS + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t n0 = blockIdx.x * SK_COLS;
@@ -117,7 +118,7 @@ gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a,
     }
     const size_t lda = lda_bytes / 2U, ldb = ldb_bytes / 2U, ldc = ldc_bytes / 2U;
     const unsigned grid = N / SK_COLS;
-#define GDB_SK(TT, KM) gemm_skinny_kernel<TT, KM><<<grid, SK_WARPS * 32, 0, be->stream>>>((const TT *)a, lda, (const TT *)b, ldb, (TT *)c, ldc, (const TT *)bias, bias_mode, M, N, K)
+#define GDB_SK(TT, KM) gdb_launch(gemm_skinny_kernel<TT, KM>, grid, SK_WARPS * 32, 0, be->stream, (const TT *)a, lda, (const TT *)b, ldb, (TT *)c, ldc, (const TT *)bias, bias_mode, M, N, K)
     if (dtype == GDB_DTYPE_F16) {
         if (tb) GDB_SK(__half, true); else GDB_SK(__half, false);
     } else {

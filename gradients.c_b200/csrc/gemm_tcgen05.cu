@@ -46,6 +46,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     size_t ldc, const T *__restrict__ bias, float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K,
                     uint32_t k_iters_per_split, int bias_mode, int *err_flag)
 {
+    gdb_pdl_sync();
     using plan = smem_plan<BN, STAGES>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
@@ -209,6 +210,7 @@ template <typename T>
 __global__ void splitk_reduce_kernel(const float *__restrict__ partial, T *__restrict__ c, size_t ldc, const T *__restrict__ bias,
                                      uint32_t M, uint32_t N, uint32_t splits, int bias_mode)
 {
+    gdb_pdl_sync();
     const size_t quads = (size_t)M * (N / 4), stride = (size_t)gridDim.x * blockDim.x;
     for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += stride) {
         const uint32_t row = (uint32_t)(q / (N / 4)), col = (uint32_t)(q % (N / 4)) * 4;
@@ -254,7 +256,7 @@ gd_status launch(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, v
         configured = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, splits);
-    kern<<<grid, 192, plan::TOTAL, be->stream>>>(ta, tb, (T *)c, ldc, (const T *)bias, partial, M, N, K, k_per_split, bias_mode, be->err_flag);
+    gdb_launch(kern, grid, 192, plan::TOTAL, be->stream, ta, tb, (T *)c, ldc, (const T *)bias, partial, M, N, K, k_per_split, bias_mode, be->err_flag);
     return gdb_launched(be, "gemm_tcgen05");
 }
 
@@ -278,9 +280,9 @@ gd_status reduce_partials(gd_backend *be, uint32_t dtype, const float *partial, 
 {
     const size_t quads = (size_t)M * (N / 4U);
     if (dtype == GDB_DTYPE_F16) {
-        splitk_reduce_kernel<__half><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__half *)c, ldc, (const __half *)bias, M, N, splits, bias_mode);
+        gdb_launch(splitk_reduce_kernel<__half>, gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream, partial, (__half *)c, ldc, (const __half *)bias, M, N, splits, bias_mode);
     } else {
-        splitk_reduce_kernel<__nv_bfloat16><<<gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream>>>(partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits, bias_mode);
+        gdb_launch(splitk_reduce_kernel<__nv_bfloat16>, gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream, partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits, bias_mode);
     }
     return gdb_launched(be, "gemm_splitk_reduce");
 }

@@ -40,6 +40,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                  const __grid_constant__ CUtensorMap tma_c, const T *__restrict__ bias, uint32_t M, uint32_t N, uint32_t K,
                  uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t k_iters_per_split, int bias_mode, int *err_flag)
 {
+    gdb_pdl_sync();
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
     unsigned char *staging = smem + PSTAGES * P_STAGE_BYTES;
@@ -290,17 +291,19 @@ gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &
     }
     const uint32_t units = tiles_m * tiles_n * splits;
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see gdb_pdl_sync()
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.gridDim = dim3(2U * (units < (uint32_t)clusters ? units : (uint32_t)clusters));
     cfg.blockDim = dim3(192);
     cfg.dynamicSmemBytes = P_SMEM_TOTAL;
     cfg.stream = be->stream;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, (const T *)bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, be->err_flag);
     if (e != cudaSuccess) {
         be->launches += 1U;

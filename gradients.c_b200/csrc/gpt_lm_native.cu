@@ -648,6 +648,7 @@ __global__ void argmax_rows_kernel(const T *__restrict__ logits, uint32_t classe
                                    int32_t *__restrict__ out_tokens, const int32_t *__restrict__ step_counter, int32_t max_steps,
                                    int32_t *__restrict__ positions, uint32_t rows)
 {
+    gdb_pdl_sync();
     const uint32_t row = blockIdx.x;
     const T *x = logits + (size_t)row * classes;
     float best = -INFINITY;
@@ -702,7 +703,8 @@ __global__ void argmax_rows_kernel(const T *__restrict__ logits, uint32_t classe
     }
 }
 
-__global__ void advance_counter_kernel(int32_t *counter) { *counter += 1; }
+__global__ void advance_counter_kernel(int32_t *counter) {
+    gdb_pdl_sync(); *counter += 1; }
 
 gd_status argmax_launch(gd_backend *be, const gd_backend_tensor_view *logits, float softcap, int32_t *ids_out, int32_t *out_tokens,
                         const int32_t *counter, int32_t max_steps, int32_t *positions)
@@ -717,13 +719,13 @@ gd_status argmax_launch(gd_backend *be, const gd_backend_tensor_view *logits, fl
     }
     switch (logits->dtype) {
     case GDB_DTYPE_F16:
-        argmax_rows_kernel<__half><<<rows, 256, 0, be->stream>>>((const __half *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        gdb_launch(argmax_rows_kernel<__half>, rows, 256, 0, be->stream, (const __half *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
         break;
     case GDB_DTYPE_BF16:
-        argmax_rows_kernel<__nv_bfloat16><<<rows, 256, 0, be->stream>>>((const __nv_bfloat16 *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        gdb_launch(argmax_rows_kernel<__nv_bfloat16>, rows, 256, 0, be->stream, (const __nv_bfloat16 *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
         break;
     case GDB_DTYPE_F32:
-        argmax_rows_kernel<float><<<rows, 256, 0, be->stream>>>((const float *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        gdb_launch(argmax_rows_kernel<float>, rows, 256, 0, be->stream, (const float *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
         break;
     default:
         return GD_ERR_UNSUPPORTED;
@@ -846,7 +848,7 @@ gd_status decode_step_body(gd_backend *be, const gdb200_gpt_spec *s, const gdb20
         int32_t *tok = io + d->tokens_offset / 4U, *posp = io + d->positions_offset / 4U;
         int32_t *outp = io + d->out_tokens_offset / 4U, *cnt = io + d->step_counter_offset / 4U;
         c.ok(argmax_launch(be, &lv, s->logits_softcap, tok, outp, cnt, d->max_steps, posp), "argmax_rows");
-        advance_counter_kernel<<<1, 1, 0, be->stream>>>(cnt);
+        gdb_launch(advance_counter_kernel, 1, 1, 0, be->stream, cnt);
         c.ok(gdb_launched(be, "advance_counter"), "advance_counter");
     }
     if (scratch_used != NULL) {

@@ -10,6 +10,7 @@ namespace {
 template <typename U, bool TO_FULL>
 __global__ void slice_copy_kernel(const U *src, U *dst, size_t count, size_t slice_span, size_t full_span, size_t lead)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         const size_t o = i / slice_span, r = i - o * slice_span;
@@ -51,11 +52,11 @@ gd_status slice_copy(gd_backend *be, const gd_backend_tensor_view *slice, const 
     const void *src = TO_FULL ? sp : fp;
     void *dst = TO_FULL ? fp : sp;
     if (es == 1U) {
-        slice_copy_kernel<unsigned char, TO_FULL><<<grid, 256, 0, be->stream>>>((const unsigned char *)src, (unsigned char *)dst, count, ss, fs, lead);
+        gdb_launch(slice_copy_kernel<unsigned char, TO_FULL>, grid, 256, 0, be->stream, (const unsigned char *)src, (unsigned char *)dst, count, ss, fs, lead);
     } else if (es == 2U) {
-        slice_copy_kernel<unsigned short, TO_FULL><<<grid, 256, 0, be->stream>>>((const unsigned short *)src, (unsigned short *)dst, count, ss, fs, lead);
+        gdb_launch(slice_copy_kernel<unsigned short, TO_FULL>, grid, 256, 0, be->stream, (const unsigned short *)src, (unsigned short *)dst, count, ss, fs, lead);
     } else {
-        slice_copy_kernel<unsigned, TO_FULL><<<grid, 256, 0, be->stream>>>((const unsigned *)src, (unsigned *)dst, count, ss, fs, lead);
+        gdb_launch(slice_copy_kernel<unsigned, TO_FULL>, grid, 256, 0, be->stream, (const unsigned *)src, (unsigned *)dst, count, ss, fs, lead);
     }
     return gdb_launched(be, "slice_copy");
 }

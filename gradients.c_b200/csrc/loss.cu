@@ -64,6 +64,7 @@ __global__ void lmce_online_update_kernel(const T *logits, const T *bias, const 
                                           float *row_max, float *row_sum, size_t rows, size_t classes, uint64_t class_start,
                                           uint64_t total_classes, float cap, float inv_cap)
 {
+    gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
     const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) {
@@ -118,6 +119,7 @@ __global__ void lmce_online_update_kernel(const T *logits, const T *bias, const 
 __global__ void lmce_finalize_kernel(const int *targets, float *row_loss, float *row_max, float *row_inv_sum,
                                      float *row_valid, size_t rows, uint64_t total_classes, int ignore_index)
 {
+    gdb_pdl_sync();
     const size_t row = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (row >= rows) {
         return;
@@ -146,6 +148,7 @@ __global__ void lmce_finalize_kernel(const int *targets, float *row_loss, float 
 __global__ void lmce_reduce_normalize_kernel(const float *row_loss, const float *row_valid, float *loss,
                                              float *inv_valid_count, size_t rows)
 {
+    gdb_pdl_sync();
     __shared__ float sh[33];
     float ll = 0.0f, lv = 0.0f;
     for (size_t i = threadIdx.x; i < rows; i += blockDim.x) {
@@ -172,6 +175,7 @@ __global__ void lmce_backward_chunk_kernel(const T *logits, const T *bias, const
                                            T *dlogits, size_t classes, uint64_t class_start, uint64_t total_classes,
                                            float scale, float cap, float inv_cap, int ignore_index)
 {
+    gdb_pdl_sync();
     const size_t row = blockIdx.x;
     const T *lr = logits + row * classes;
     T *dr = dlogits + row * classes;
@@ -227,6 +231,7 @@ __global__ void lmce_backward_chunk_kernel(const T *logits, const T *bias, const
 template <typename T, bool STATS>
 __global__ void ce_loss_kernel(const T *logits, const int *targets, float *row_loss, float *row_max, float *row_inv_sum, size_t classes)
 {
+    gdb_pdl_sync();
     __shared__ float sh[33];
     const size_t row = blockIdx.x;
     const T *lr = logits + row * classes;
@@ -255,6 +260,7 @@ template <typename T, bool STATS>
 __global__ void ce_backward_kernel(const T *logits, const int *targets, const float *row_max, const float *row_inv_sum,
                                    const float *grad_loss, size_t grad_count, T *dlogits, size_t classes, float scale)
 {
+    gdb_pdl_sync();
     __shared__ float sh[33];
     const size_t row = blockIdx.x;
     const T *lr = logits + row * classes;
@@ -340,9 +346,9 @@ gd_status gd_backend_lm_cross_entropy_online_update(gd_backend *be, const gd_bac
     const float inv_cap = logits_softcap > 0.0f ? 1.0f / logits_softcap : 0.0f;
     const unsigned grid = (unsigned)((cs.rows + 3U) / 4U);
     if (dt == GDB_DTYPE_F16) {
-        lmce_online_update_kernel<__half><<<grid, 128, 0, be->stream>>>((const __half *)lp, (const __half *)bp, tp, rl, rm, rs, cs.rows, cs.classes, class_start, total_classes, logits_softcap, inv_cap);
+        gdb_launch(lmce_online_update_kernel<__half>, grid, 128, 0, be->stream, (const __half *)lp, (const __half *)bp, tp, rl, rm, rs, cs.rows, cs.classes, class_start, total_classes, logits_softcap, inv_cap);
     } else {
-        lmce_online_update_kernel<__nv_bfloat16><<<grid, 128, 0, be->stream>>>((const __nv_bfloat16 *)lp, (const __nv_bfloat16 *)bp, tp, rl, rm, rs, cs.rows, cs.classes, class_start, total_classes, logits_softcap, inv_cap);
+        gdb_launch(lmce_online_update_kernel<__nv_bfloat16>, grid, 128, 0, be->stream, (const __nv_bfloat16 *)lp, (const __nv_bfloat16 *)bp, tp, rl, rm, rs, cs.rows, cs.classes, class_start, total_classes, logits_softcap, inv_cap);
     }
     return gdb_launched(be, "lm_cross_entropy_online_update");
 }
@@ -361,7 +367,7 @@ gd_status gd_backend_lm_cross_entropy_finalize(gd_backend *be, const gd_backend_
         return GD_ERR_INVALID_ARGUMENT;
     }
     const size_t rows = targets->count;
-    lmce_finalize_kernel<<<(unsigned)((rows + 255U) / 256U), 256, 0, be->stream>>>(tp, rl, rm, rs, rv, rows, total_classes, ignore_index);
+    gdb_launch(lmce_finalize_kernel, (unsigned)((rows + 255U) / 256U), 256, 0, be->stream, tp, rl, rm, rs, rv, rows, total_classes, ignore_index);
     return gdb_launched(be, "lm_cross_entropy_finalize");
 }
 
@@ -376,7 +382,7 @@ gd_status gd_backend_lm_cross_entropy_reduce_normalize(gd_backend *be, const gd_
     if (rl == NULL || rv == NULL || lp == NULL || ip == NULL) {
         return GD_ERR_INVALID_ARGUMENT;
     }
-    lmce_reduce_normalize_kernel<<<1, 1024, 0, be->stream>>>(rl, rv, lp, ip, row_loss->count);
+    gdb_launch(lmce_reduce_normalize_kernel, 1, 1024, 0, be->stream, rl, rv, lp, ip, row_loss->count);
     return gdb_launched(be, "lm_cross_entropy_reduce_normalize");
 }
 
@@ -411,9 +417,9 @@ gd_status gd_backend_lm_cross_entropy_backward_chunk(gd_backend *be, const gd_ba
     const float inv_cap = logits_softcap > 0.0f ? 1.0f / logits_softcap : 0.0f;
     const unsigned threads = row_threads(cs.classes);
     if (dt == GDB_DTYPE_F16) {
-        lmce_backward_chunk_kernel<__half><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __half *)lp, (const __half *)bp, tp, rm, rs, gl, iv, (__half *)dp, cs.classes, class_start, total_classes, scale, logits_softcap, inv_cap, ignore_index);
+        gdb_launch(lmce_backward_chunk_kernel<__half>, (unsigned)cs.rows, threads, 0, be->stream, (const __half *)lp, (const __half *)bp, tp, rm, rs, gl, iv, (__half *)dp, cs.classes, class_start, total_classes, scale, logits_softcap, inv_cap, ignore_index);
     } else {
-        lmce_backward_chunk_kernel<__nv_bfloat16><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __nv_bfloat16 *)lp, (const __nv_bfloat16 *)bp, tp, rm, rs, gl, iv, (__nv_bfloat16 *)dp, cs.classes, class_start, total_classes, scale, logits_softcap, inv_cap, ignore_index);
+        gdb_launch(lmce_backward_chunk_kernel<__nv_bfloat16>, (unsigned)cs.rows, threads, 0, be->stream, (const __nv_bfloat16 *)lp, (const __nv_bfloat16 *)bp, tp, rm, rs, gl, iv, (__nv_bfloat16 *)dp, cs.classes, class_start, total_classes, scale, logits_softcap, inv_cap, ignore_index);
     }
     return gdb_launched(be, "lm_cross_entropy_backward_chunk");
 }
@@ -439,11 +445,11 @@ static gd_status ce_loss_common(gd_backend *be, const gd_backend_tensor_view *lo
     }
     const unsigned threads = row_threads(cs.classes);
     if (dt == GDB_DTYPE_F16) {
-        if (stats) ce_loss_kernel<__half, true><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __half *)lp, tp, rl, rm, rs, cs.classes);
-        else ce_loss_kernel<__half, false><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __half *)lp, tp, rl, rm, rs, cs.classes);
+        if (stats) gdb_launch(ce_loss_kernel<__half, true>, (unsigned)cs.rows, threads, 0, be->stream, (const __half *)lp, tp, rl, rm, rs, cs.classes);
+        else gdb_launch(ce_loss_kernel<__half, false>, (unsigned)cs.rows, threads, 0, be->stream, (const __half *)lp, tp, rl, rm, rs, cs.classes);
     } else {
-        if (stats) ce_loss_kernel<__nv_bfloat16, true><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __nv_bfloat16 *)lp, tp, rl, rm, rs, cs.classes);
-        else ce_loss_kernel<__nv_bfloat16, false><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __nv_bfloat16 *)lp, tp, rl, rm, rs, cs.classes);
+        if (stats) gdb_launch(ce_loss_kernel<__nv_bfloat16, true>, (unsigned)cs.rows, threads, 0, be->stream, (const __nv_bfloat16 *)lp, tp, rl, rm, rs, cs.classes);
+        else gdb_launch(ce_loss_kernel<__nv_bfloat16, false>, (unsigned)cs.rows, threads, 0, be->stream, (const __nv_bfloat16 *)lp, tp, rl, rm, rs, cs.classes);
     }
     return gdb_launched(be, "cross_entropy_loss");
 }
@@ -481,11 +487,11 @@ static gd_status ce_bwd_common(gd_backend *be, const gd_backend_tensor_view *log
     }
     const unsigned threads = row_threads(cs.classes);
     if (dt == GDB_DTYPE_F16) {
-        if (stats) ce_backward_kernel<__half, true><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __half *)lp, tp, rm, rs, gl, grad_loss->count, (__half *)dp, cs.classes, scale);
-        else ce_backward_kernel<__half, false><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __half *)lp, tp, rm, rs, gl, grad_loss->count, (__half *)dp, cs.classes, scale);
+        if (stats) gdb_launch(ce_backward_kernel<__half, true>, (unsigned)cs.rows, threads, 0, be->stream, (const __half *)lp, tp, rm, rs, gl, grad_loss->count, (__half *)dp, cs.classes, scale);
+        else gdb_launch(ce_backward_kernel<__half, false>, (unsigned)cs.rows, threads, 0, be->stream, (const __half *)lp, tp, rm, rs, gl, grad_loss->count, (__half *)dp, cs.classes, scale);
     } else {
-        if (stats) ce_backward_kernel<__nv_bfloat16, true><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __nv_bfloat16 *)lp, tp, rm, rs, gl, grad_loss->count, (__nv_bfloat16 *)dp, cs.classes, scale);
-        else ce_backward_kernel<__nv_bfloat16, false><<<(unsigned)cs.rows, threads, 0, be->stream>>>((const __nv_bfloat16 *)lp, tp, rm, rs, gl, grad_loss->count, (__nv_bfloat16 *)dp, cs.classes, scale);
+        if (stats) gdb_launch(ce_backward_kernel<__nv_bfloat16, true>, (unsigned)cs.rows, threads, 0, be->stream, (const __nv_bfloat16 *)lp, tp, rm, rs, gl, grad_loss->count, (__nv_bfloat16 *)dp, cs.classes, scale);
+        else gdb_launch(ce_backward_kernel<__nv_bfloat16, false>, (unsigned)cs.rows, threads, 0, be->stream, (const __nv_bfloat16 *)lp, tp, rm, rs, gl, grad_loss->count, (__nv_bfloat16 *)dp, cs.classes, scale);
     }
     return gdb_launched(be, "cross_entropy_backward");
 }

@@ -18,6 +18,7 @@ constexpr int ROWS_PER_BLOCK = 4;  // 4 warps per block, one row each
 template <typename T, int MODE>
 __global__ void rms_fwd_kernel(const T *x, const T *w, T *out, float *inv_out, size_t rows, size_t cols, float eps)
 {
+    gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
     const size_t row = (size_t)blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
     if (row >= rows) {
@@ -84,6 +85,7 @@ __global__ void rms_fwd_kernel(const T *x, const T *w, T *out, float *inv_out, s
 template <typename T, bool STATS>
 __global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, const T *g, T *dx, size_t rows, size_t cols, float eps)
 {
+    gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
     const size_t row = (size_t)blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
     if (row >= rows) {
@@ -158,6 +160,7 @@ template <typename T>
 __global__ void rms_wgrad_stage_kernel(const T *x, const float *inv, const T *g, float *partial,
                                        size_t rows, size_t cols, size_t chunk)
 {
+    gdb_pdl_sync();
     const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t r0 = (size_t)blockIdx.y * chunk;
     size_t r1 = r0 + chunk;
@@ -184,6 +187,7 @@ __global__ void rms_wgrad_stage_kernel(const T *x, const float *inv, const T *g,
 template <typename T>
 __global__ void rms_wgrad_reduce_kernel(const float *partial, T *dw, size_t blocks, size_t cols)
 {
+    gdb_pdl_sync();
     const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= cols) {
         return;
@@ -204,7 +208,7 @@ template <typename T, int MODE>
 gd_status fwd_launch(gd_backend *be, const void *x, const void *w, void *out, float *inv, const gd_backend_rms_norm_args *a)
 {
     const unsigned grid = (unsigned)((a->rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
-    rms_fwd_kernel<T, MODE><<<grid, 32 * ROWS_PER_BLOCK, 0, be->stream>>>((const T *)x, (const T *)w, (T *)out, inv, a->rows, a->cols, a->eps);
+    gdb_launch(rms_fwd_kernel<T, MODE>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const T *)x, (const T *)w, (T *)out, inv, a->rows, a->cols, a->eps);
     return gdb_launched(be, "rms_norm_forward");
 }
 
@@ -275,11 +279,11 @@ gd_status bwd_dispatch(gd_backend *be, const gd_backend_tensor_view *x, const gd
     const unsigned grid = (unsigned)((a->rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
     const unsigned threads = 32 * ROWS_PER_BLOCK;
     if (x->dtype == GDB_DTYPE_F16) {
-        rms_bwd_kernel<__half, STATS><<<grid, threads, 0, be->stream>>>((const __half *)xp, (const __half *)wp, ip, (const __half *)gp, (__half *)dp, a->rows, a->cols, a->eps);
+        gdb_launch(rms_bwd_kernel<__half, STATS>, grid, threads, 0, be->stream, (const __half *)xp, (const __half *)wp, ip, (const __half *)gp, (__half *)dp, a->rows, a->cols, a->eps);
     } else if (x->dtype == GDB_DTYPE_BF16) {
-        rms_bwd_kernel<__nv_bfloat16, STATS><<<grid, threads, 0, be->stream>>>((const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip, (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, a->rows, a->cols, a->eps);
+        gdb_launch(rms_bwd_kernel<__nv_bfloat16, STATS>, grid, threads, 0, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip, (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, a->rows, a->cols, a->eps);
     } else {
-        rms_bwd_kernel<float, STATS><<<grid, threads, 0, be->stream>>>((const float *)xp, (const float *)wp, ip, (const float *)gp, (float *)dp, a->rows, a->cols, a->eps);
+        gdb_launch(rms_bwd_kernel<float, STATS>, grid, threads, 0, be->stream, (const float *)xp, (const float *)wp, ip, (const float *)gp, (float *)dp, a->rows, a->cols, a->eps);
     }
     return gdb_launched(be, "rms_norm_backward");
 }
@@ -350,22 +354,22 @@ gd_status gd_backend_rms_norm_weight_backward_stats(gd_backend *be, const gd_bac
     blocks = (a->rows + chunk - 1U) / chunk;
     dim3 grid(col_blocks, (unsigned)blocks);
     if (x->dtype == GDB_DTYPE_F16) {
-        rms_wgrad_stage_kernel<__half><<<grid, 256, 0, be->stream>>>((const __half *)xp, ip, (const __half *)gp, pp, a->rows, a->cols, chunk);
+        gdb_launch(rms_wgrad_stage_kernel<__half>, grid, 256, 0, be->stream, (const __half *)xp, ip, (const __half *)gp, pp, a->rows, a->cols, chunk);
     } else if (x->dtype == GDB_DTYPE_BF16) {
-        rms_wgrad_stage_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream>>>((const __nv_bfloat16 *)xp, ip, (const __nv_bfloat16 *)gp, pp, a->rows, a->cols, chunk);
+        gdb_launch(rms_wgrad_stage_kernel<__nv_bfloat16>, grid, 256, 0, be->stream, (const __nv_bfloat16 *)xp, ip, (const __nv_bfloat16 *)gp, pp, a->rows, a->cols, chunk);
     } else {
-        rms_wgrad_stage_kernel<float><<<grid, 256, 0, be->stream>>>((const float *)xp, ip, (const float *)gp, pp, a->rows, a->cols, chunk);
+        gdb_launch(rms_wgrad_stage_kernel<float>, grid, 256, 0, be->stream, (const float *)xp, ip, (const float *)gp, pp, a->rows, a->cols, chunk);
     }
     gd_status st = gdb_launched(be, "rms_norm_wgrad_stage");
     if (st != GD_OK) {
         return st;
     }
     if (x->dtype == GDB_DTYPE_F16) {
-        rms_wgrad_reduce_kernel<__half><<<col_blocks, 256, 0, be->stream>>>(pp, (__half *)dw, blocks, a->cols);
+        gdb_launch(rms_wgrad_reduce_kernel<__half>, col_blocks, 256, 0, be->stream, pp, (__half *)dw, blocks, a->cols);
     } else if (x->dtype == GDB_DTYPE_BF16) {
-        rms_wgrad_reduce_kernel<__nv_bfloat16><<<col_blocks, 256, 0, be->stream>>>(pp, (__nv_bfloat16 *)dw, blocks, a->cols);
+        gdb_launch(rms_wgrad_reduce_kernel<__nv_bfloat16>, col_blocks, 256, 0, be->stream, pp, (__nv_bfloat16 *)dw, blocks, a->cols);
     } else {
-        rms_wgrad_reduce_kernel<float><<<col_blocks, 256, 0, be->stream>>>(pp, (float *)dw, blocks, a->cols);
+        gdb_launch(rms_wgrad_reduce_kernel<float>, col_blocks, 256, 0, be->stream, pp, (float *)dw, blocks, a->cols);
     }
     return gdb_launched(be, "rms_norm_wgrad_reduce");
 }

@@ -39,6 +39,7 @@ __device__ __forceinline__ void store_from_float(void *p, size_t i, uint32_t dty
 // ------------------------------------------------------------------ AMP
 __global__ void amp_begin_kernel(float *scale, int *flags, float min_scale, float max_scale)
 {
+    gdb_pdl_sync();
     const float s = fminf(fmaxf(scale[0], min_scale), max_scale);
     scale[0] = s;
     scale[1] = 1.0f / s;
@@ -47,6 +48,7 @@ __global__ void amp_begin_kernel(float *scale, int *flags, float min_scale, floa
 __global__ void amp_finish_kernel(float *scale, unsigned *flags, float growth, float backoff, float min_scale,
                                   float max_scale, unsigned interval)
 {
+    gdb_pdl_sync();
     const bool found = flags[1] != 0U;
     float s = scale[0];
     unsigned tracker = flags[0];
@@ -68,6 +70,7 @@ __global__ void amp_finish_kernel(float *scale, unsigned *flags, float growth, f
 // dst[i] = (src ? src[i] : 1) * scale[0]
 __global__ void amp_scale_kernel(void *dst, const void *src, size_t n, uint32_t dtype, const float *scale)
 {
+    gdb_pdl_sync();
     const float s = scale[0];
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -86,6 +89,7 @@ struct unscale_batch {
 };
 __global__ void amp_unscale_kernel(unscale_batch b)
 {
+    gdb_pdl_sync();
     int t = 0;
     while (t + 1 < b.n && blockIdx.x >= b.block_start[t + 1]) {
         ++t;
@@ -119,6 +123,7 @@ struct norm_batch {
 };
 __global__ void grad_norm_stage_kernel(norm_batch b)
 {
+    gdb_pdl_sync();
     __shared__ float sh[33];
     int t = 0;
     while (t + 1 < b.n && blockIdx.x >= b.block_start[t + 1]) {
@@ -150,6 +155,7 @@ __global__ void grad_norm_stage_kernel(norm_batch b)
 __global__ void grad_clip_finalize_kernel(const float *partials, size_t n, float *out, const float *grad_scale,
                                           float max_norm, float eps)
 {
+    gdb_pdl_sync();
     __shared__ float sh[33];
     float sum = 0.0f;
     for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -193,6 +199,7 @@ struct adamw_batch {
 
 __global__ void adamw_prepare_kernel(adamw_batch b)
 {
+    gdb_pdl_sync();
     const int t = threadIdx.x;
     if (t >= b.n) {
         return;
@@ -213,6 +220,7 @@ __global__ void adamw_prepare_kernel(adamw_batch b)
 
 __global__ void adamw_commit_kernel(adamw_batch b)
 {
+    gdb_pdl_sync();
     const int t = threadIdx.x;
     if (t >= b.n) {
         return;
@@ -233,6 +241,7 @@ constexpr unsigned ADAMW_BLOCK_ELEMS = 2048;  // elements per block (256 threads
 
 __global__ void adamw_update_kernel(adamw_batch b)
 {
+    gdb_pdl_sync();
     int t = 0;
     while (t + 1 < b.n && blockIdx.x >= b.block_start[t + 1]) {
         ++t;
@@ -343,7 +352,7 @@ gd_status gd_backend_amp_begin_step(gd_backend *be, const gd_backend_amp_state_d
     if (be == NULL || !amp_desc_ok(d)) {
         return GD_ERR_INVALID_ARGUMENT;
     }
-    amp_begin_kernel<<<1, 1, 0, be->stream>>>((float *)(d->scale_buffer->dptr + d->scale_offset),
+    gdb_launch(amp_begin_kernel, 1, 1, 0, be->stream, (float *)(d->scale_buffer->dptr + d->scale_offset),
                                               (int *)(d->flags_buffer->dptr + d->flags_offset), d->min_scale, d->max_scale);
     return gdb_launched(be, "amp_begin_step");
 }
@@ -353,7 +362,7 @@ gd_status gd_backend_amp_finish_step(gd_backend *be, const gd_backend_amp_state_
     if (be == NULL || !amp_desc_ok(d)) {
         return GD_ERR_INVALID_ARGUMENT;
     }
-    amp_finish_kernel<<<1, 1, 0, be->stream>>>((float *)(d->scale_buffer->dptr + d->scale_offset),
+    gdb_launch(amp_finish_kernel, 1, 1, 0, be->stream, (float *)(d->scale_buffer->dptr + d->scale_offset),
                                                (unsigned *)(d->flags_buffer->dptr + d->flags_offset), d->growth_factor,
                                                d->backoff_factor, d->min_scale, d->max_scale, d->growth_interval);
     return gdb_launched(be, "amp_finish_step");
@@ -369,7 +378,7 @@ gd_status gd_backend_amp_fill_scale(gd_backend *be, gd_backend_buffer *dst_buffe
     if (count == 0U) {
         return GD_OK;
     }
-    amp_scale_kernel<<<gdb_grid_for(count, 256, be, 8), 256, 0, be->stream>>>(dst_buffer->dptr + dst_offset, NULL, count, dtype, (const float *)(scale_buffer->dptr + scale_offset));
+    gdb_launch(amp_scale_kernel, gdb_grid_for(count, 256, be, 8), 256, 0, be->stream, dst_buffer->dptr + dst_offset, (const void *)nullptr, count, dtype, (const float *)(scale_buffer->dptr + scale_offset));
     return gdb_launched(be, "amp_fill_scale");
 }
 
@@ -384,7 +393,7 @@ gd_status gd_backend_amp_scale(gd_backend *be, gd_backend_buffer *dst_buffer, si
     if (count == 0U) {
         return GD_OK;
     }
-    amp_scale_kernel<<<gdb_grid_for(count, 256, be, 8), 256, 0, be->stream>>>(dst_buffer->dptr + dst_offset, src_buffer->dptr + src_offset, count, dtype, (const float *)(scale_buffer->dptr + scale_offset));
+    gdb_launch(amp_scale_kernel, gdb_grid_for(count, 256, be, 8), 256, 0, be->stream, dst_buffer->dptr + dst_offset, src_buffer->dptr + src_offset, count, dtype, (const float *)(scale_buffer->dptr + scale_offset));
     return gdb_launched(be, "amp_scale");
 }
 
@@ -426,7 +435,7 @@ gd_status gd_backend_amp_unscale_batch(gd_backend *be, const gd_backend_amp_unsc
         if (blocks == 0U) {
             continue;
         }
-        amp_unscale_kernel<<<blocks, 256, 0, be->stream>>>(b);
+        gdb_launch(amp_unscale_kernel, blocks, 256, 0, be->stream, b);
         gd_status st = gdb_launched(be, "amp_unscale");
         if (st != GD_OK) {
             return st;
@@ -503,13 +512,13 @@ gd_status gd_backend_grad_clip_scale(gd_backend *be, const gd_backend_grad_norm_
         if (blocks == 0U) {
             continue;
         }
-        grad_norm_stage_kernel<<<blocks, 256, 0, be->stream>>>(b);
+        gdb_launch(grad_norm_stage_kernel, blocks, 256, 0, be->stream, b);
         gd_status st = gdb_launched(be, "grad_norm_stage");
         if (st != GD_OK) {
             return st;
         }
     }
-    grad_clip_finalize_kernel<<<1, 1024, 0, be->stream>>>(partials, total_partials, (float *)(scale_buffer->dptr + scale_offset), gscale, max_norm, eps);
+    gdb_launch(grad_clip_finalize_kernel, 1, 1024, 0, be->stream, partials, total_partials, (float *)(scale_buffer->dptr + scale_offset), gscale, max_norm, eps);
     return gdb_launched(be, "grad_clip_finalize");
 }
 
@@ -546,19 +555,19 @@ gd_status gd_backend_adamw_batch(gd_backend *be, const gd_backend_adamw_desc *de
         b.block_start[b.n] = blocks;
         gd_status st;
         if (any_state) {
-            adamw_prepare_kernel<<<1, 32, 0, be->stream>>>(b);
+            gdb_launch(adamw_prepare_kernel, 1, 32, 0, be->stream, b);
             st = gdb_launched(be, "adamw_prepare");
             if (st != GD_OK) {
                 return st;
             }
         }
-        adamw_update_kernel<<<blocks, 256, 0, be->stream>>>(b);
+        gdb_launch(adamw_update_kernel, blocks, 256, 0, be->stream, b);
         st = gdb_launched(be, "adamw_update");
         if (st != GD_OK) {
             return st;
         }
         if (any_state) {
-            adamw_commit_kernel<<<1, 32, 0, be->stream>>>(b);
+            gdb_launch(adamw_commit_kernel, 1, 32, 0, be->stream, b);
             st = gdb_launched(be, "adamw_commit");
             if (st != GD_OK) {
                 return st;

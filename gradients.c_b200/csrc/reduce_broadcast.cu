@@ -22,6 +22,7 @@ __device__ __forceinline__ void st_any(void *p, size_t i, uint32_t dt, float v)
 // dst[j] = scale * sum(src[j*chunk, min((j+1)*chunk, n))), chunk = ceil(n / dst_count); one block per j.
 __global__ void reduce_contiguous_kernel(const void *src, void *dst, size_t n, size_t dst_count, uint32_t sdt, uint32_t ddt, float scale)
 {
+    gdb_pdl_sync();
     __shared__ float sh[33];
     const size_t chunk = (n + dst_count - 1) / dst_count;
     for (size_t j = blockIdx.x; j < dst_count; j += gridDim.x) {
@@ -36,6 +37,7 @@ __global__ void reduce_contiguous_kernel(const void *src, void *dst, size_t n, s
 // dst[o, i] = scale * sum_a src[o, a, i]
 __global__ void reduce_axis_kernel(const void *src, void *dst, size_t outer, size_t axis, size_t inner, uint32_t dt, float scale)
 {
+    gdb_pdl_sync();
     const size_t n = outer * inner, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
         const size_t o = e / inner, i = e - o * inner;
@@ -47,6 +49,7 @@ __global__ void reduce_axis_kernel(const void *src, void *dst, size_t outer, siz
 // dst[o, a, i] = scale * src[o, i]
 __global__ void broadcast_axis_kernel(const void *src, void *dst, size_t outer, size_t axis, size_t inner, uint32_t dt, float scale)
 {
+    gdb_pdl_sync();
     const size_t n = outer * axis * inner, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
         const size_t i = e % inner, o = e / (axis * inner);
@@ -63,6 +66,7 @@ struct nd_desc {
 // dst (big) [e] = scale * src (small)[mapped e]
 __global__ void broadcast_to_kernel(const void *src, void *dst, size_t n, nd_desc d, uint32_t sdt, uint32_t ddt, float scale)
 {
+    gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
         size_t rem = e, so = 0;
@@ -78,6 +82,7 @@ __global__ void broadcast_to_kernel(const void *src, void *dst, size_t n, nd_des
 __global__ void reduce_broadcast_kernel(const void *src, void *dst, size_t small_n, size_t big_n, nd_desc d,
                                         uint32_t small_shape_packed_rank, const uint32_t *unused, uint32_t dt, float scale)
 {
+    gdb_pdl_sync();
     (void)small_shape_packed_rank;
     (void)unused;
     const int lane = threadIdx.x & 31;
@@ -158,7 +163,7 @@ gd_status gd_backend_reduce_contiguous(gd_backend *be, const gd_backend_tensor_v
         return GD_ERR_INVALID_ARGUMENT;
     }
     const unsigned grid = (unsigned)(dst->count < 65535U * 4U ? dst->count : 65535U * 4U);
-    reduce_contiguous_kernel<<<grid, 256, 0, be->stream>>>(gdb_tv_ptr(src, src->dtype), gdb_tv_ptr(dst, dst->dtype), src->count, dst->count, src->dtype, dst->dtype, scale);
+    gdb_launch(reduce_contiguous_kernel, grid, 256, 0, be->stream, gdb_tv_ptr(src, src->dtype), gdb_tv_ptr(dst, dst->dtype), src->count, dst->count, src->dtype, dst->dtype, scale);
     return gdb_launched(be, "reduce_contiguous");
 }
 
@@ -179,9 +184,9 @@ static gd_status axis_common(gd_backend *be, const gd_backend_tensor_view *full,
     }
     void *fp = gdb_tv_ptr(full, full->dtype), *rp = gdb_tv_ptr(reduced, reduced->dtype);
     if (reduce) {
-        reduce_axis_kernel<<<gdb_grid_for(outer * inner, 256, be, 8), 256, 0, be->stream>>>(fp, rp, outer, a, inner, full->dtype, scale);
+        gdb_launch(reduce_axis_kernel, gdb_grid_for(outer * inner, 256, be, 8), 256, 0, be->stream, fp, rp, outer, a, inner, full->dtype, scale);
     } else {
-        broadcast_axis_kernel<<<gdb_grid_for(full->count, 256, be, 8), 256, 0, be->stream>>>(rp, fp, outer, a, inner, full->dtype, scale);
+        gdb_launch(broadcast_axis_kernel, gdb_grid_for(full->count, 256, be, 8), 256, 0, be->stream, rp, fp, outer, a, inner, full->dtype, scale);
     }
     return gdb_launched(be, reduce ? "reduce_axis" : "broadcast_axis");
 }
@@ -204,7 +209,7 @@ gd_status gd_backend_broadcast_to(gd_backend *be, const gd_backend_tensor_view *
     if (dst->count == 0U) {
         return GD_OK;
     }
-    broadcast_to_kernel<<<gdb_grid_for(dst->count, 256, be, 8), 256, 0, be->stream>>>(gdb_tv_ptr(src, src->dtype), gdb_tv_ptr(dst, dst->dtype), dst->count, d, src->dtype, dst->dtype, scale);
+    gdb_launch(broadcast_to_kernel, gdb_grid_for(dst->count, 256, be, 8), 256, 0, be->stream, gdb_tv_ptr(src, src->dtype), gdb_tv_ptr(dst, dst->dtype), dst->count, d, src->dtype, dst->dtype, scale);
     return gdb_launched(be, "broadcast_to");
 }
 
@@ -223,7 +228,7 @@ gd_status gd_backend_broadcast_scalar(gd_backend *be, const gd_backend_tensor_vi
     d.rank = 1;
     d.big[0] = (uint32_t)dst->count;
     d.small_stride[0] = 0;
-    broadcast_to_kernel<<<gdb_grid_for(dst->count, 256, be, 8), 256, 0, be->stream>>>(gdb_tv_ptr(src, src->dtype), gdb_tv_ptr(dst, dst->dtype), dst->count, d, src->dtype, dst->dtype, scale);
+    gdb_launch(broadcast_to_kernel, gdb_grid_for(dst->count, 256, be, 8), 256, 0, be->stream, gdb_tv_ptr(src, src->dtype), gdb_tv_ptr(dst, dst->dtype), dst->count, d, src->dtype, dst->dtype, scale);
     return gdb_launched(be, "broadcast_scalar");
 }
 
@@ -237,7 +242,7 @@ gd_status gd_backend_reduce_broadcast(gd_backend *be, const gd_backend_tensor_vi
         return GD_OK;
     }
     const size_t warps = dst->count;
-    reduce_broadcast_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, be->stream>>>(gdb_tv_ptr(src, src->dtype), gdb_tv_ptr(dst, dst->dtype), dst->count, src->count, d, 0U, NULL, src->dtype, scale);
+    gdb_launch(reduce_broadcast_kernel, (unsigned)((warps + 3) / 4), 128, 0, be->stream, gdb_tv_ptr(src, src->dtype), gdb_tv_ptr(dst, dst->dtype), dst->count, src->count, d, 0U, (const uint32_t *)nullptr, src->dtype, scale);
     return gdb_launched(be, "reduce_broadcast");
 }
 
