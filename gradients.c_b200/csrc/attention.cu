@@ -277,18 +277,41 @@ __device__ __forceinline__ bool decode_allowed(int qpos, int j, int window, int 
 // the keys [split*chunk, split*chunk+chunk) of its live range. A key is handled by DH/16 adjacent
 // lanes (16 head dims = two 16-byte loads each for K and V), so a warp has 32/(DH/16) keys in
 // flight; partial (m, l, acc) per split go to the workspace and a combine kernel merges them.
+// Merge of the per-split partials of query w: out = sum_s acc_s e^(m_s - m) / sum_s l_s e^(m_s - m).
+template <typename T>
+__device__ __forceinline__ void decode_combine_query(const float *part_ml, const float *part_acc, T *out, long long w, int dh, int splits, int lane)
+{
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, __ldcg(&part_ml[((size_t)w * splits + s) * 2U]));
+    float l = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float pm = __ldcg(&part_ml[((size_t)w * splits + s) * 2U]);
+        l += pm == -INFINITY ? 0.0f : __ldcg(&part_ml[((size_t)w * splits + s) * 2U + 1U]) * __expf(pm - m);
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    for (int c = lane; c < dh; c += 32) {
+        float a = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float pm = __ldcg(&part_ml[((size_t)w * splits + s) * 2U]);
+            if (pm != -INFINITY) a += __ldcg(&part_acc[((size_t)w * splits + s) * dh + c]) * __expf(pm - m);
+        }
+        gdb_io<T>::st(out, (size_t)w * dh + c, a * inv);
+    }
+}
+
+// `tickets` != NULL: the block that arrives last for its group of queries (over the splits) merges the
+// partials and writes `out`, so no combine launch follows.
 template <typename T, int DH>
 __global__ void decode_split_kernel(const T *q, const T *kc, const T *vc, const int *pos_buf, float *part_ml,
-                                    float *part_acc, decode_params p, int splits)
+                                    float *part_acc, decode_params p, int splits, T *out, unsigned *tickets)
 {
     gdb_pdl_sync();
     constexpr int LPK = DH / 16, KPW = 32 / LPK;
     const int lane = threadIdx.x & 31, sub = lane % LPK, kg = lane / LPK;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long total = (long long)p.batch * p.tq * p.hq;
-    if (w >= total) {
-        return;
-    }
+    const bool active = w < total;
+    if (active) {
     const int split = blockIdx.y;
     const int h = (int)(w % p.hq);
     const int t = (int)((w / p.hq) % p.tq);
@@ -365,6 +388,22 @@ __global__ void decode_split_kernel(const T *q, const T *kc, const T *vc, const 
         part_ml[((size_t)w * splits + split) * 2U] = wm;
         part_ml[((size_t)w * splits + split) * 2U + 1U] = l;
     }
+    }   // active
+    if (tickets == nullptr) {
+        return;
+    }
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        last = atomicAdd(&tickets[blockIdx.x], 1U) == gridDim.y - 1U;
+    }
+    __syncthreads();
+    if (last) {
+        __threadfence();
+        if (active) decode_combine_query<T>(part_ml, part_acc, out, w, DH, splits, lane);
+        if (threadIdx.x == 0) tickets[blockIdx.x] = 0U;
+    }
 }
 
 template <typename T>
@@ -376,22 +415,7 @@ __global__ void decode_combine_kernel(const float *part_ml, const float *part_ac
     if (w >= total) {
         return;
     }
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)w * splits + s) * 2U]);
-    float l = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float pm = part_ml[((size_t)w * splits + s) * 2U];
-        l += pm == -INFINITY ? 0.0f : part_ml[((size_t)w * splits + s) * 2U + 1U] * __expf(pm - m);
-    }
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    for (int c = lane; c < dh; c += 32) {
-        float a = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float pm = part_ml[((size_t)w * splits + s) * 2U];
-            if (pm != -INFINITY) a += part_acc[((size_t)w * splits + s) * dh + c] * __expf(pm - m);
-        }
-        gdb_io<T>::st(out, (size_t)w * dh + c, a * inv);
-    }
+    decode_combine_query<T>(part_ml, part_acc, out, w, dh, splits, lane);
 }
 
 // General head_dim decode: one warp per query, lanes split head_dim.
@@ -631,7 +655,8 @@ gd_status decode_common(gd_backend *be, const gd_backend_tensor_view *q, const g
             float *ml = (float *)be->ws;
             float *pa = ml + (size_t)total * splits * 2U;
             dim3 grid((unsigned)((total + 3) / 4), (unsigned)splits);
-#define GDB_DECODE(T, DH) gdb_launch(decode_split_kernel<T, DH>, grid, 128, 0, be->stream, (const T *)qp, (const T *)kp, (const T *)vp, pp, ml, pa, p, splits)
+            const bool fused = grid.x <= (unsigned)GDB_TICKET_WORDS;
+#define GDB_DECODE(T, DH) gdb_launch(decode_split_kernel<T, DH>, grid, 128, 0, be->stream, (const T *)qp, (const T *)kp, (const T *)vp, pp, ml, pa, p, splits, (T *)op, fused ? gdb_tickets(be) : (unsigned *)nullptr)
             if (dt == GDB_DTYPE_F16) {
                 if (p.dh == 64) GDB_DECODE(__half, 64); else GDB_DECODE(__half, 128);
             } else {
@@ -639,7 +664,7 @@ gd_status decode_common(gd_backend *be, const gd_backend_tensor_view *q, const g
             }
 #undef GDB_DECODE
             gd_status st = gdb_launched(be, "sdpa_decode split");
-            if (st != GD_OK) return st;
+            if (st != GD_OK || fused) return st;
             if (dt == GDB_DTYPE_F16) {
                 gdb_launch(decode_combine_kernel<__half>, (unsigned)((total + 3) / 4), 128, 0, be->stream, ml, pa, (__half *)op, total, p.dh, splits);
             } else {

@@ -284,5 +284,11 @@ gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype,
                                 const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
                                 void *c, size_t ldc_bytes, const void *bias, int bias_mode,
                                 uint32_t M, uint32_t N, uint32_t K, uint32_t *splits_out);
+// Fusions used by the native decode driver (GD_ERR_UNSUPPORTED when their vector paths do not apply).
+gd_status gdb_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y, const gd_backend_tensor_view *weight,
+                           const gd_backend_tensor_view *sum, const gd_backend_tensor_view *out, size_t rows, size_t cols, float eps);
+gd_status gdb_qkv_rope_append(gd_backend *be, const gd_backend_tensor_view *qkv, const gd_backend_tensor_view *pos_ids,
+                              const gd_backend_tensor_view *q, const gd_backend_tensor_view *k_cache, const gd_backend_tensor_view *v_cache,
+                              uint32_t n_heads, uint32_t head_dim, uint32_t tmax, const gd_backend_rope_args *args);
 void gdb_tmap_cache_destroy(gd_backend *be);
 void gdb_dp_destroy(gd_backend *be);

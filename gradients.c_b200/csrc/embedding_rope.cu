@@ -141,9 +141,11 @@ __global__ void qkv_split_rope_kernel(const T *a0, const T *a1, const T *a2, con
 
 // Fast path: NeoX half-split, n_dims == head_dim, head_dim % 16 == 0, 16-byte aligned tensors.
 // One thread handles 8 consecutive pairs of one (token, head): two 16-byte loads per source.
+// tmax > 0 (forward only): o1 / o2 are K / V caches [tokens, tmax, heads, head_dim] and the rotated key and the value of
+// token t go to cache slot pos_ids[t] (one new token per cache row: the decode step), skipped when the slot is out of range.
 template <typename T, bool FWD>
 __global__ void qkv_split_rope_vec8_kernel(const T *a0, const T *a1, const T *a2, const int *pos_ids, T *o0, T *o1, T *o2,
-                                           rope_params p, const float *table)
+                                           rope_params p, const float *table, unsigned tmax = 0)
 {
     gdb_pdl_sync();
     const unsigned half_dims = p.head_dim >> 1, groups = half_dims >> 3;
@@ -186,10 +188,15 @@ __global__ void qkv_split_rope_vec8_kernel(const T *a0, const T *a1, const T *a2
         if (FWD) {
             *reinterpret_cast<uint4 *>(o0 + split) = qa.raw;
             *reinterpret_cast<uint4 *>(o0 + split + half_dims) = qb.raw;
-            *reinterpret_cast<uint4 *>(o1 + split) = ka.raw;
-            *reinterpret_cast<uint4 *>(o1 + split + half_dims) = kb.raw;
-            *reinterpret_cast<uint4 *>(o2 + split) = va.raw;
-            *reinterpret_cast<uint4 *>(o2 + split + half_dims) = vb.raw;
+            size_t kv = split;
+            if (tmax != 0U) {
+                if (pos < 0 || (unsigned)pos >= tmax) continue;
+                kv = (token * tmax + (size_t)pos) * area + (size_t)h * p.head_dim + grp * 8U;
+            }
+            *reinterpret_cast<uint4 *>(o1 + kv) = ka.raw;
+            *reinterpret_cast<uint4 *>(o1 + kv + half_dims) = kb.raw;
+            *reinterpret_cast<uint4 *>(o2 + kv) = va.raw;
+            *reinterpret_cast<uint4 *>(o2 + kv + half_dims) = vb.raw;
         } else {
             *reinterpret_cast<uint4 *>(o0 + packed) = qa.raw;
             *reinterpret_cast<uint4 *>(o0 + packed + half_dims) = qb.raw;
@@ -279,7 +286,7 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
                        const gd_backend_tensor_view *s2, const gd_backend_tensor_view *pos_ids,
                        const gd_backend_tensor_view *d0, const gd_backend_tensor_view *d1,
                        const gd_backend_tensor_view *d2, uint32_t n_heads, uint32_t head_dim,
-                       const gd_backend_rope_args *args)
+                       const gd_backend_rope_args *args, uint32_t cache_tmax = 0)
 {
     // FWD: s0 = qkv, d0..d2 = q,k,v. BWD: s0..s2 = gq,gk,gv, d0 = dqkv.
     const gd_backend_tensor_view *packed = FWD ? s0 : d0;
@@ -300,8 +307,9 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
         return GD_ERR_INVALID_ARGUMENT;
     }
     const size_t tokens = (size_t)packed->shape[0];
-    if (packed->count != tokens * area * 3U || sq->count != tokens * area || sk->count != tokens * area ||
-        sv->count != tokens * area || pos_ids->count != tokens) {
+    const size_t kv_rows = cache_tmax != 0U ? tokens * cache_tmax : tokens;   // K / V destinations are caches when cache_tmax > 0
+    if (packed->count != tokens * area * 3U || sq->count != tokens * area || sk->count != kv_rows * area ||
+        sv->count != kv_rows * area || pos_ids->count != tokens || (cache_tmax != 0U && !FWD)) {
         return GD_ERR_INVALID_ARGUMENT;
     }
     void *pp = gdb_tv_ptr(packed, dt), *qp = gdb_tv_ptr(sq, dt), *kp = gdb_tv_ptr(sk, dt), *vp = gdb_tv_ptr(sv, dt);
@@ -327,6 +335,9 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
     }
     const bool vec = args->interleaved == 0U && (head_dim % 16U) == 0U &&
                      (((uintptr_t)pp | (uintptr_t)qp | (uintptr_t)kp | (uintptr_t)vp) % 16U) == 0U;
+    if (cache_tmax != 0U && !vec) {
+        return GD_ERR_UNSUPPORTED;
+    }
     const void *a0 = FWD ? pp : qp, *a1 = FWD ? NULL : kp, *a2 = FWD ? NULL : vp;
     void *o0 = FWD ? qp : pp, *o1 = FWD ? kp : NULL, *o2 = FWD ? vp : NULL;
     const size_t items = vec ? tokens * n_heads * (head_dim / 16U) : tokens * n_heads * (head_dim / 2U);
@@ -334,7 +345,7 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
 #define GDB_ROPE_LAUNCH(T)                                                                                          \
     do {                                                                                                            \
         if (vec) {                                                                                                  \
-            gdb_launch(qkv_split_rope_vec8_kernel<T, FWD>, grid, 256, 0, be->stream, (const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table); \
+            gdb_launch(qkv_split_rope_vec8_kernel<T, FWD>, grid, 256, 0, be->stream, (const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table, (unsigned)cache_tmax); \
         } else {                                                                                                    \
             gdb_launch(qkv_split_rope_kernel<T, FWD>, grid, 256, 0, be->stream, (const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table); \
         }                                                                                                           \
@@ -347,6 +358,22 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
 #undef GDB_ROPE_LAUNCH
     return gdb_launched(be, "qkv_split_rope");
 }
+
+}  // namespace
+
+// Decode step: q = rope(split(qkv)) to `q`, and the rotated key / the value of row b straight into slot pos_ids[b] of
+// the caches [rows, tmax, heads, head_dim] (qkv_split_rope_forward + kv_cache_append_positions in one launch).
+gd_status gdb_qkv_rope_append(gd_backend *be, const gd_backend_tensor_view *qkv, const gd_backend_tensor_view *pos_ids,
+                              const gd_backend_tensor_view *q, const gd_backend_tensor_view *k_cache, const gd_backend_tensor_view *v_cache,
+                              uint32_t n_heads, uint32_t head_dim, uint32_t tmax, const gd_backend_rope_args *args)
+{
+    if (tmax == 0U) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    return qkv_dispatch<true>(be, qkv, NULL, NULL, pos_ids, q, k_cache, v_cache, n_heads, head_dim, args, tmax);
+}
+
+namespace {
 
 gd_status rope_dispatch(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *pos_ids,
                         const gd_backend_tensor_view *out, const gd_backend_rope_args *args, float sin_sign)

@@ -645,8 +645,8 @@ namespace {
 // tokens[row] (the next step's input) and to out_tokens[*step_counter, row]; positions[row] += 1.
 template <typename T>
 __global__ void argmax_rows_kernel(const T *__restrict__ logits, uint32_t classes, float softcap, int32_t *__restrict__ ids_out,
-                                   int32_t *__restrict__ out_tokens, const int32_t *__restrict__ step_counter, int32_t max_steps,
-                                   int32_t *__restrict__ positions, uint32_t rows)
+                                   int32_t *__restrict__ out_tokens, const int32_t *step_counter, int32_t max_steps,
+                                   int32_t *__restrict__ positions, uint32_t rows, unsigned *tickets, int32_t *step_counter_rw)
 {
     gdb_pdl_sync();
     const uint32_t row = blockIdx.x;
@@ -699,16 +699,23 @@ __global__ void argmax_rows_kernel(const T *__restrict__ logits, uint32_t classe
                 if (t >= 0 && t < max_steps) out_tokens[(size_t)t * rows + row] = id;
             }
             if (positions != nullptr) positions[row] += 1;
+            if (tickets != nullptr) {
+                // every block reads *step_counter before it takes a ticket, so the last one may advance it
+                __threadfence();
+                if (atomicAdd(tickets, 1U) == gridDim.x - 1U) {
+                    *tickets = 0U;
+                    *step_counter_rw += 1;
+                }
+            }
         }
     }
 }
 
-__global__ void advance_counter_kernel(int32_t *counter) {
-    gdb_pdl_sync(); *counter += 1; }
-
 gd_status argmax_launch(gd_backend *be, const gd_backend_tensor_view *logits, float softcap, int32_t *ids_out, int32_t *out_tokens,
-                        const int32_t *counter, int32_t max_steps, int32_t *positions)
+                        int32_t *counter, int32_t max_steps, int32_t *positions)
 {
+    // with a step counter, the last block of the launch advances it (ticket word reserved for this kernel)
+    unsigned *tickets = counter != nullptr ? gdb_tickets(be) + (GDB_TICKET_WORDS - 1) : nullptr;
     if (logits == NULL || logits->rank != 2 || logits->shape[0] <= 0 || logits->shape[1] <= 0) {
         return GD_ERR_INVALID_ARGUMENT;
     }
@@ -719,13 +726,13 @@ gd_status argmax_launch(gd_backend *be, const gd_backend_tensor_view *logits, fl
     }
     switch (logits->dtype) {
     case GDB_DTYPE_F16:
-        gdb_launch(argmax_rows_kernel<__half>, rows, 256, 0, be->stream, (const __half *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        gdb_launch(argmax_rows_kernel<__half>, rows, 256, 0, be->stream, (const __half *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows, tickets, counter);
         break;
     case GDB_DTYPE_BF16:
-        gdb_launch(argmax_rows_kernel<__nv_bfloat16>, rows, 256, 0, be->stream, (const __nv_bfloat16 *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        gdb_launch(argmax_rows_kernel<__nv_bfloat16>, rows, 256, 0, be->stream, (const __nv_bfloat16 *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows, tickets, counter);
         break;
     case GDB_DTYPE_F32:
-        gdb_launch(argmax_rows_kernel<float>, rows, 256, 0, be->stream, (const float *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows);
+        gdb_launch(argmax_rows_kernel<float>, rows, 256, 0, be->stream, (const float *)x, classes, softcap, ids_out, out_tokens, counter, max_steps, positions, rows, tickets, counter);
         break;
     default:
         return GD_ERR_UNSUPPORTED;
@@ -773,23 +780,25 @@ gd_status decode_step_body(gd_backend *be, const gdb200_gpt_spec *s, const gdb20
     da.scale = (float)(1.0 / sqrt((double)Dh));
     da.sliding_window = (uint32_t)s->sdpa_window;
     gd_backend_kv_cache_append_args ka = {0};
+    // out = x + y and normed = rms_norm(out, w) in one launch when the vector path applies, else the two calls
+    auto add_then_rms = [&](const Ten &xa, const Ten &ya, const Ten &w, Ten *sum, Ten *normed) {
+        *sum = c.alloc(dt, {B, D});
+        *normed = c.alloc(dt, {B, D});
+        gd_backend_tensor_view xv = tv(xa), yv = tv(ya), wv = tv(w), sv = tv(*sum), nv = tv(*normed);
+        gd_status r = gdb_add_rms_norm(be, &xv, &yv, &wv, &sv, &nv, (size_t)B, (size_t)D, s->rms_eps);
+        if (r == GD_ERR_UNSUPPORTED) {
+            c.ok(gd_backend_add(be, &xv, &yv, &sv), "add");
+            gd_backend_rms_norm_args a = rms_args(B, D, s->rms_eps);
+            r = gd_backend_rms_norm_forward(be, &sv, &wv, &nv, &a);
+        }
+        c.ok(r, "add + rms_norm");
+    };
+    Ten inv0;
+    Ten normed = rms_forward(c, x, c.param(1, {D}), B, D, &inv0);
     for (int i = 0; i < L && c.st == GD_OK; ++i) {
         const int pb = 1 + 10 * i;
-        Ten inv;
-        Ten normed = rms_forward(c, x, c.param(pb + 0, {D}), B, D, &inv);
         Ten qkv = linear_t(c, normed, c.param(pb + 1, {3 * D, D}), c.param(pb + 2, {3 * D}), B, D, 3 * D);
-        Ten q = c.alloc(dt, {B, 1, H, Dh}), k = c.alloc(dt, {B, 1, H, Dh}), v = c.alloc(dt, {B, 1, H, Dh});
-        {
-            Ten q3 = q, k3 = k, v3 = v;
-            for (Ten *t : {&q3, &k3, &v3}) {
-                t->rank = 3;
-                t->shape[0] = B;
-                t->shape[1] = H;
-                t->shape[2] = Dh;
-            }
-            gd_backend_tensor_view a = tv(qkv), p = tv(pos), qv = tv(q3), kv = tv(k3), vvw = tv(v3);
-            c.ok(gd_backend_qkv_split_rope_forward(be, &a, &p, &qv, &kv, &vvw, (uint32_t)H, (uint32_t)Dh, &rope), "qkv_split_rope_forward");
-        }
+        Ten q = c.alloc(dt, {B, 1, H, Dh});
         Ten kc, vc;
         memset(&kc, 0, sizeof(kc));
         kc.buf = d->cache_buffer;
@@ -804,18 +813,33 @@ gd_status decode_step_body(gd_backend *be, const gdb200_gpt_spec *s, const gdb20
         vc.off = d->v_cache_offset[i];
         Ten attn = c.alloc(dt, {B, 1, H, Dh});
         {
-            gd_backend_tensor_view kcv = tv(kc), vcv = tv(vc), pv = tv(pos), kn = tv(k), vn = tv(v), qv = tv(q), ov = tv(attn);
-            c.ok(gd_backend_kv_cache_append_positions(be, &kcv, &vcv, &pv, &kn, &vn, &ka), "kv_cache_append_positions");
+            Ten q3 = q;
+            q3.rank = 3;
+            q3.shape[0] = B;
+            q3.shape[1] = H;
+            q3.shape[2] = Dh;
+            gd_backend_tensor_view a = tv(qkv), pv = tv(pos), q3v = tv(q3), kcv = tv(kc), vcv = tv(vc), qv = tv(q), ov = tv(attn);
+            // rotated key / value go straight into their cache slots; fall back to split + append when that path does not apply
+            gd_status r = gdb_qkv_rope_append(be, &a, &pv, &q3v, &kcv, &vcv, (uint32_t)H, (uint32_t)Dh, (uint32_t)CAP, &rope);
+            if (r == GD_ERR_UNSUPPORTED) {
+                Ten k = c.alloc(dt, {B, 1, H, Dh}), v = c.alloc(dt, {B, 1, H, Dh});
+                Ten k3 = k, v3 = v;
+                for (Ten *t : {&k3, &v3}) {
+                    t->rank = 3;
+                    t->shape[0] = B;
+                    t->shape[1] = H;
+                    t->shape[2] = Dh;
+                }
+                gd_backend_tensor_view k3v = tv(k3), v3v = tv(v3), kn = tv(k), vn = tv(v);
+                c.ok(gd_backend_qkv_split_rope_forward(be, &a, &pv, &q3v, &k3v, &v3v, (uint32_t)H, (uint32_t)Dh, &rope), "qkv_split_rope_forward");
+                r = gd_backend_kv_cache_append_positions(be, &kcv, &vcv, &pv, &kn, &vn, &ka);
+            }
+            c.ok(r, "rope + kv append");
             c.ok(gd_backend_sdpa_decode_positions(be, &qv, &kcv, &vcv, &pv, &ov, &da), "sdpa_decode_positions");
         }
         Ten proj = linear_t(c, attn, c.param(pb + 3, {D, D}), c.param(pb + 4, {D}), B, D, D);
-        Ten resid = c.alloc(dt, {B, D});
-        {
-            gd_backend_tensor_view r = tv(x), a = tv(proj), y = tv(resid);
-            c.ok(gd_backend_add(be, &r, &a, &y), "add");
-        }
-        Ten inv2;
-        Ten normed2 = rms_forward(c, resid, c.param(pb + 5, {D}), B, D, &inv2);
+        Ten resid, normed2;
+        add_then_rms(x, proj, c.param(pb + 5, {D}), &resid, &normed2);
         Ten up_gate = linear_t(c, normed2, c.param(pb + 6, {2 * F, D}), c.param(pb + 7, {2 * F}), B, D, 2 * F);
         Ten act = c.alloc(dt, {B, F});
         {
@@ -829,15 +853,12 @@ gd_status decode_step_body(gd_backend *be, const gdb200_gpt_spec *s, const gdb20
             gd_backend_vector_view bv = vv(b, 0, (uint32_t)D);
             c.ok(gd_backend_linear(be, &am, &wm, &bv, &ym), "linear(down_proj)");
         }
-        Ten out = c.alloc(dt, {B, D});
-        {
-            gd_backend_tensor_view r = tv(resid), a = tv(mlp), y = tv(out);
-            c.ok(gd_backend_add(be, &r, &a, &y), "add");
-        }
+        // residual add fused with the norm that consumes it: the next block's attention norm, or the final norm
+        Ten out;
+        add_then_rms(resid, mlp, i + 1 < L ? c.param(1 + 10 * (i + 1), {D}) : c.param(P_FINAL, {D}), &out, &normed);
         x = out;
     }
-    Ten inv_f;
-    Ten final_norm = rms_forward(c, x, c.param(P_FINAL, {D}), B, D, &inv_f);
+    Ten final_norm = normed;
     Ten logits = linear_t(c, final_norm, c.param(P_LMW, {V, D}), c.param(P_LMB, {V}), B, D, V);
     if (c.st == GD_OK) {
         gd_backend_tensor_view lv = tv(logits);
@@ -848,8 +869,6 @@ gd_status decode_step_body(gd_backend *be, const gdb200_gpt_spec *s, const gdb20
         int32_t *tok = io + d->tokens_offset / 4U, *posp = io + d->positions_offset / 4U;
         int32_t *outp = io + d->out_tokens_offset / 4U, *cnt = io + d->step_counter_offset / 4U;
         c.ok(argmax_launch(be, &lv, s->logits_softcap, tok, outp, cnt, d->max_steps, posp), "argmax_rows");
-        gdb_launch(advance_counter_kernel, 1, 1, 0, be->stream, cnt);
-        c.ok(gdb_launched(be, "advance_counter"), "advance_counter");
     }
     if (scratch_used != NULL) {
         *scratch_used = c.top;

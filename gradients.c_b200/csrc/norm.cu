@@ -81,6 +81,45 @@ __global__ void rms_fwd_kernel(const T *x, const T *w, T *out, float *inv_out, s
     }
 }
 
+// sum = round(x + y); out = round(sum * w * inv_rms(sum)): gd_backend_add followed by rms_norm_forward in one launch
+// (same rounding points). Warp per row, cols % 8 == 0, 16-byte aligned 16-bit tensors.
+template <typename T>
+__global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *w, uint4 *sum, uint4 *out, size_t rows, size_t cols, float eps)
+{
+    gdb_pdl_sync();
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+    if (row >= rows) {
+        return;
+    }
+    const size_t vecs = cols / 8U, base = row * vecs;
+    float ss = 0.0f;
+    for (size_t v = lane; v < vecs; v += 32) {
+        gdb_vec8<T> a, b;
+        a.raw = x[base + v];
+        b.raw = y[base + v];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            a.set(e, a.get(e) + b.get(e));
+            const float f = a.get(e);
+            ss += f * f;
+        }
+        sum[base + v] = a.raw;
+    }
+    ss = gdb_warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)cols + eps);
+    for (size_t v = lane; v < vecs; v += 32) {
+        gdb_vec8<T> a, b;
+        a.raw = sum[base + v];   // written by this lane above
+        b.raw = __ldg(&w[v]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            a.set(e, a.get(e) * b.get(e) * inv);
+        }
+        out[base + v] = a.raw;
+    }
+}
+
 // STATS true: inv read from inv_in; false: recomputed from x.
 template <typename T, bool STATS>
 __global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, const T *g, T *dx, size_t rows, size_t cols, float eps)
@@ -375,3 +414,34 @@ gd_status gd_backend_rms_norm_weight_backward_stats(gd_backend *be, const gd_bac
 }
 
 }  // extern "C"
+
+// Internal fusion used by the decode driver; GD_ERR_UNSUPPORTED when the vector path does not apply.
+gd_status gdb_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y, const gd_backend_tensor_view *weight,
+                           const gd_backend_tensor_view *sum, const gd_backend_tensor_view *out, size_t rows, size_t cols, float eps)
+{
+    if (be == NULL || x == NULL || y == NULL || weight == NULL || sum == NULL || out == NULL || rows == 0U || cols == 0U) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = x->dtype;
+    if ((dt != GDB_DTYPE_F16 && dt != GDB_DTYPE_BF16) || (cols % 8U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (x->count != rows * cols || y->count != x->count || sum->count != x->count || out->count != x->count || weight->count != cols) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const void *xp = gdb_tv_ptr(x, dt), *yp = gdb_tv_ptr(y, dt), *wp = gdb_tv_ptr(weight, dt);
+    void *sp = gdb_tv_ptr(sum, dt), *op = gdb_tv_ptr(out, dt);
+    if (xp == NULL || yp == NULL || wp == NULL || sp == NULL || op == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if ((((uintptr_t)xp | (uintptr_t)yp | (uintptr_t)wp | (uintptr_t)sp | (uintptr_t)op) % 16U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const unsigned grid = (unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
+    if (dt == GDB_DTYPE_F16) {
+        gdb_launch(add_rms_fwd_kernel<__half>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps);
+    } else {
+        gdb_launch(add_rms_fwd_kernel<__nv_bfloat16>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps);
+    }
+    return gdb_launched(be, "add_rms_norm");
+}
