@@ -36,6 +36,9 @@ if ROOT not in sys.path:
 METRIC = "gpt_lm_train_tokens_per_s"
 UNIT = "tokens/s"
 N_SEQS, MIN_LEN, MAX_LEN = 64, 64, 512
+# mean DRAM bytes (read + write) per dense-contraction launch of the default train step, from an ncu capture of this
+# same command (profiles/gemm_pair_train_step_dram.md): below the algorithmic 78.5 MB because outputs stay in L2
+GEMM_DRAM_BYTES_PER_LAUNCH = 64.0e6
 
 
 def parse_args():
@@ -306,7 +309,10 @@ def run_b200(args) -> None:
     achieved_tf = fl.value / (ms.value * 1e-3) / 1e12 if ms.value > 0 else 0.0
     step_ms_prof = 1000.0 * sec / args.steps
     roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                "frac": achieved_tf / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["source"] + " (sustained)",
+                "frac": achieved_tf / peaks["bf16_tflops_sustained"], "traffic": GEMM_DRAM_BYTES_PER_LAUNCH if args.model == "baseline" else None,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over the 39 gemm_pair_kernel launches of one step "
+                                  "(profiles/gemm_pair_train_step_dram.md); algorithmic bytes per launch = algorithmic_gb_per_step / launches_per_step",
+                "peak_source": peaks["source"] + " (sustained)",
                 "kernel": "dense contractions (matmul / matmul_nt / matmul_tn / linear)", "launches_per_step": n_l.value / prof_steps,
                 "avg_launch_us": 1000.0 * ms.value / max(1, n_l.value), "share_of_step": (ms.value / prof_steps) / step_ms_prof,
                 "algorithmic_gb_per_step": by.value / prof_steps / 1e9}

@@ -123,11 +123,12 @@ static inline bool usable(const void *a, size_t lda, const void *b, size_t ldb, 
            (b == NULL || ((ldb % 8U) == 0U && ((uintptr_t)b % 16U) == 0U));
 }
 
-// Number of row chunks: about four waves of blocks, at least 64 rows per chunk, capped by capacity.
+// Number of row chunks: about two waves of blocks, at least 64 rows per chunk, capped by capacity.
 static inline size_t pick_chunks(const gd_backend *be, size_t rows, size_t cols, size_t capacity_chunks)
 {
+    // two waves of blocks: enough parallelism for the row sweep, few enough chunks for the last block's final sum
     const size_t col_tiles = (cols + TILE_COLS - 1U) / TILE_COLS;
-    size_t chunks = ((size_t)be->sm_count * 4U + col_tiles - 1U) / col_tiles;
+    size_t chunks = ((size_t)be->sm_count * 2U + col_tiles - 1U) / col_tiles;
     const size_t by_rows = (rows + 63U) / 64U;
     if (chunks > by_rows) chunks = by_rows;
     if (chunks > capacity_chunks) chunks = capacity_chunks;
