@@ -8,6 +8,8 @@
 // shared memory before the bias add and the single rounding.
 #include "common.cuh"
 
+#include <stdlib.h>
+
 namespace {
 
 template <typename T> struct mma16816;
@@ -106,6 +108,144 @@ gemm_skinny_kernel(const T *__restrict__ A, size_t lda, const T *__restrict__ B,
     }
 }
 
+// ---- staged variant: operands reach shared memory with coalesced 16-byte cp.async, fragments come from ldmatrix ----
+__device__ __forceinline__ uint32_t sk_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void sk_cp16(void *dst, const void *src, bool valid)
+{
+    const int bytes = valid ? 16 : 0;   // zero-fill rows beyond M
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sk_smem(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void sk_ldm4(uint32_t (&r)[4], const void *p)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sk_smem(p)));
+}
+__device__ __forceinline__ void sk_ldm4t(uint32_t (&r)[4], const void *p)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sk_smem(p)));
+}
+
+// K is walked in chunks of CH (a multiple of 128): per chunk the CTA stages A[64, CH] and its 16 columns of B, each
+// warp multiplies its CH / 8 slice, and with more than one chunk the next one is in flight (two stages).
+template <typename T, bool B_KMAJOR>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restrict__ B, size_t ldb, T *__restrict__ C, size_t ldc,
+                          const T *__restrict__ bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K, uint32_t CH, int stages)
+{
+    gdb_pdl_sync();
+    extern __shared__ __align__(16) unsigned char sk_sm[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t n0 = blockIdx.x * SK_COLS;
+    const uint32_t LDA = CH + 8U, LDW = B_KMAJOR ? CH + 8U : 24U;
+    const uint32_t a_bytes = SK_ROWS * LDA * 2U, w_bytes = (B_KMAJOR ? (uint32_t)SK_COLS : CH) * LDW * 2U, stage_bytes = a_bytes + w_bytes;
+    const uint32_t n_chunks = K / CH, segs = CH / 8U;
+    auto load_chunk = [&](uint32_t ci, uint32_t st) {
+        T *As = reinterpret_cast<T *>(sk_sm + st * stage_bytes), *Ws = reinterpret_cast<T *>(sk_sm + st * stage_bytes + a_bytes);
+        const size_t k0 = (size_t)ci * CH;
+        for (uint32_t i = tid; i < SK_ROWS * segs; i += SK_WARPS * 32) {
+            const uint32_t r = i / segs, sgm = i % segs;
+            sk_cp16(As + r * LDA + sgm * 8U, A + (size_t)(r < M ? r : 0U) * lda + k0 + sgm * 8U, r < M);
+        }
+        if (B_KMAJOR) {
+            for (uint32_t i = tid; i < SK_COLS * segs; i += SK_WARPS * 32) {
+                const uint32_t r = i / segs, sgm = i % segs;
+                sk_cp16(Ws + r * LDW + sgm * 8U, B + (size_t)(n0 + r) * ldb + k0 + sgm * 8U, true);
+            }
+        } else {
+            for (uint32_t i = tid; i < CH * 2U; i += SK_WARPS * 32) {
+                const uint32_t k = i >> 1, sgm = i & 1U;
+                sk_cp16(Ws + k * LDW + sgm * 8U, B + (k0 + k) * ldb + n0 + sgm * 8U, true);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_chunk(0, 0);
+    if (stages == 2 && n_chunks > 1U) load_chunk(1, 1);
+    float acc[4][2][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
+    const uint32_t kw = CH / SK_WARPS;   // k elements per warp and chunk (a multiple of 16)
+    for (uint32_t ci = 0; ci < n_chunks; ++ci) {
+        const uint32_t st = stages == 2 ? (ci & 1U) : 0U;
+        if (stages == 2 && ci + 1U < n_chunks) {
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const T *As = reinterpret_cast<const T *>(sk_sm + st * stage_bytes), *Ws = reinterpret_cast<const T *>(sk_sm + st * stage_bytes + a_bytes);
+        for (uint32_t k = warp * kw; k < (warp + 1U) * kw; k += 16U) {
+            uint32_t a[4][4], b4[4];
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) sk_ldm4(a[mt], As + (mt * 16 + (lane & 15)) * LDA + k + (lane >> 4) * 8);
+            if (B_KMAJOR) {
+                sk_ldm4(b4, Ws + ((lane & 7) + ((lane >> 4) << 3)) * LDW + k + ((lane >> 3) & 1) * 8);
+            } else {
+                sk_ldm4t(b4, Ws + (k + (lane & 7) + ((lane >> 3) & 1) * 8) * LDW + (lane >> 4) * 8);
+            }
+            const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                mma16816<T>::run(acc[mt][0], a[mt], b0);
+                mma16816<T>::run(acc[mt][1], a[mt], b1);
+            }
+        }
+        __syncthreads();   // every warp is done with this stage before it is refilled (or reused for the reduction)
+        if (stages == 2) {
+            if (ci + 2U < n_chunks) load_chunk(ci + 2U, st);
+        } else if (ci + 1U < n_chunks) {
+            load_chunk(ci + 1U, 0);
+        }
+    }
+    float(*red)[SK_ROWS][SK_COLS + 1] = reinterpret_cast<float(*)[SK_ROWS][SK_COLS + 1]>(sk_sm);
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int r = mt * 16 + g, c = nt * 8 + 2 * t;
+            red[warp][r][c] = acc[mt][nt][0];
+            red[warp][r][c + 1] = acc[mt][nt][1];
+            red[warp][r + 8][c] = acc[mt][nt][2];
+            red[warp][r + 8][c + 1] = acc[mt][nt][3];
+        }
+    __syncthreads();
+    for (int o = tid; o < SK_ROWS * SK_COLS; o += SK_WARPS * 32) {
+        const int r = o / SK_COLS, c = o % SK_COLS;
+        if ((uint32_t)r >= M) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) v += red[w][r][c];
+        if (bias != nullptr) {
+            if (bias_mode == 2) v = gdb_io<T>::rnd(v);
+            v += gdb_io<T>::ld(bias, n0 + c);
+        }
+        gdb_io<T>::st(C, (size_t)r * ldc + n0 + c, v);
+    }
+}
+
+template <typename T, bool B_KMAJOR>
+gd_status launch_staged(gd_backend *be, const void *a, size_t lda, const void *b, size_t ldb, void *c, size_t ldc, const void *bias, int bias_mode,
+                        uint32_t M, uint32_t N, uint32_t K, uint32_t ch)
+{
+    auto kern = gemm_skinny_staged_kernel<T, B_KMAJOR>;
+    const int stages = K / ch > 1U ? 2 : 1;
+    const uint32_t a_bytes = SK_ROWS * (ch + 8U) * 2U, w_bytes = B_KMAJOR ? SK_COLS * (ch + 8U) * 2U : ch * 24U * 2U;
+    size_t smem = (size_t)stages * (a_bytes + w_bytes);
+    const size_t red_bytes = sizeof(float) * SK_WARPS * SK_ROWS * (SK_COLS + 1);
+    if (smem < red_bytes) smem = red_bytes;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gdb_fail(be, e, "skinny gemm smem attribute");
+        configured = smem;
+    }
+    gdb_launch(kern, N / SK_COLS, SK_WARPS * 32, smem, be->stream, (const T *)a, lda, (const T *)b, ldb, (T *)c, ldc, (const T *)bias, bias_mode, M, N, K, ch, stages);
+    return gdb_launched(be, "gemm_skinny_staged");
+}
+
 }  // namespace
 
 // Returns GD_ERR_UNSUPPORTED unless M <= 64, N % 16 == 0, K % 16 == 0 and the operands are 4-byte aligned.
@@ -117,6 +257,16 @@ gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a,
         return GD_ERR_UNSUPPORTED;
     }
     const size_t lda = lda_bytes / 2U, ldb = ldb_bytes / 2U, ldc = ldc_bytes / 2U;
+    // staged variant: K in chunks of 512 / 256 / 128 and 16-byte aligned rows
+    const uint32_t ch = (K % 512U) == 0U ? 512U : ((K % 256U) == 0U ? 256U : ((K % 128U) == 0U ? 128U : 0U));
+    if (ch != 0U && (((uintptr_t)a | (uintptr_t)b | lda_bytes | ldb_bytes) % 16U) == 0U && getenv("GDB200_SKINNY_DIRECT") == NULL) {
+        if (dtype == GDB_DTYPE_F16) {
+            return tb ? launch_staged<__half, true>(be, a, lda, b, ldb, c, ldc, bias, bias_mode, M, N, K, ch)
+                      : launch_staged<__half, false>(be, a, lda, b, ldb, c, ldc, bias, bias_mode, M, N, K, ch);
+        }
+        return tb ? launch_staged<__nv_bfloat16, true>(be, a, lda, b, ldb, c, ldc, bias, bias_mode, M, N, K, ch)
+                  : launch_staged<__nv_bfloat16, false>(be, a, lda, b, ldb, c, ldc, bias, bias_mode, M, N, K, ch);
+    }
     const unsigned grid = N / SK_COLS;
 #define GDB_SK(TT, KM) gdb_launch(gemm_skinny_kernel<TT, KM>, grid, SK_WARPS * 32, 0, be->stream, (const TT *)a, lda, (const TT *)b, ldb, (TT *)c, ldc, (const TT *)bias, bias_mode, M, N, K)
     if (dtype == GDB_DTYPE_F16) {
