@@ -237,8 +237,18 @@ def run_b200(args) -> None:
     trainer = (g.NativeTrainer if args.host == "native" else g.Trainer)(model, tc, dp=dp)
 
     total_steps = args.warmup + args.steps
-    batches = [g.synthetic_batch(cfg, n_seqs, min_len, max_len, seed=10_000 * (rank + 1) + s, pad_to=cfg.context_length)
-               for s in range(total_steps)]
+    if world == 1:
+        batches = [g.synthetic_batch(cfg, n_seqs, min_len, max_len, seed=10_000 + s, pad_to=cfg.context_length) for s in range(total_steps)]
+    else:
+        # the global batch of a step (n_seqs * world sequences, same length distribution) is drawn once on every rank
+        # from the same seed and dealt out token-balanced, because a synchronous step runs at the pace of its heaviest rank
+        from gradients_c_b200.host.dp import balanced_shards
+        batches = []
+        for s in range(total_steps):
+            lens = np.random.default_rng(77_000 + s).integers(min_len, max_len + 1, size=n_seqs * world)
+            mine = balanced_shards(lens, world)[rank]
+            batches.append(g.synthetic_batch(cfg, n_seqs, min_len, max_len, seed=10_000 * (rank + 1) + s, pad_to=cfg.context_length,
+                                             lengths=[int(lens[i]) for i in mine]))
 
     # end-to-end arm: the host batches live in page-locked memory
     for b in batches:
@@ -336,6 +346,7 @@ def run_b200(args) -> None:
                                    f"H{cfg.n_heads}x{cfg.head_dim} F{cfg.mlp_hidden} {'tied' if cfg.tied_lm_head else 'untied'} head, dropout {cfg.dropout_p}, "
                                    f"window {cfg.sdpa_window}, softcap {cfg.logits_softcap:g}, AdamW AMP clip",
                        "global_batch": n_seqs * world, "seq_len": f"U[{min_len},{max_len}] packed, padded to x{cfg.context_length}", "parallelism": f"dp{world}", "host": args.host,
+                       "sharding": "one batch" if world == 1 else "global batch dealt out token-balanced (longest first to the lightest rank)",
                        "l2": "per-step working set (>2 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": e_tokens / e_sec, "unit": UNIT, "h2d_bytes_per_step": int(np.mean([b.h2d_bytes for b in batches])),
                     "d2h_bytes_per_step": 4},

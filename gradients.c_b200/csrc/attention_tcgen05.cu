@@ -431,7 +431,7 @@ gd_status launch_fwd(gd_backend *be, const gdb_flash_args *a)
     }
     // Two CTAs fit an SM by construction (2 x 256 tensor-memory columns, 2 x 106 KB shared memory, 2 x 30720
     // registers). Nothing waits across CTAs, so if fewer were co-resident the rest would simply run later.
-    const int resident = 2 * be->sm_count;
+    const int resident = 2 * (be->sm_count - be->sm_reserve);
     CUtensorMap mq, mk, mv;
     const uint64_t n = (uint64_t)a->n_tokens;
     const bool ok = make_tmap(&mq, a->dtype, a->q, n, (uint64_t)a->hq * A_DH, (uint64_t)a->hq * A_DH * 2U, 64, A_BQ) &&

@@ -33,6 +33,7 @@ struct gd_backend {
     uint64_t launches;
     int gemm_mode;            // 0 auto, 1 portable, 2 tcgen05 required, 3 auto without the CTA-pair kernel
     int attn_mode;            // 0 auto (tcgen05 attention when the shape allows), 1 mma.sync flash kernels only
+    int sm_reserve;           // SMs the persistent kernels leave free (for a concurrent collective); 0 = none
     char last_error[256];
     // private workspace (split-K partials, reductions, attention scratch); created once at
     // create_default so no allocation happens while a step is being enqueued.

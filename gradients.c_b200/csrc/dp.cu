@@ -124,7 +124,11 @@ gd_status gdb200_dp_init(gd_backend *be, const void *id_bytes_128, int rank, int
     memcpy(&id, id_bytes_128, sizeof(id));
     dp->rank = rank;
     dp->world = world;
-    if (cudaStreamCreateWithFlags(&dp->stream, cudaStreamNonBlocking) != cudaSuccess ||
+    // the collective runs on a stream of the highest priority, so that its few CTAs are placed as soon as any
+    // compute CTA retires instead of queueing behind the persistent kernels of the backward pass
+    int prio_lo = 0, prio_hi = 0;
+    cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+    if (cudaStreamCreateWithPriority(&dp->stream, cudaStreamNonBlocking, prio_hi) != cudaSuccess ||
         cudaEventCreateWithFlags(&dp->ready, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&dp->done, cudaEventDisableTiming) != cudaSuccess) {
         free(dp);
@@ -156,6 +160,11 @@ gd_status gdb200_dp_init(gd_backend *be, const void *id_bytes_128, int rank, int
         return GD_ERR_INTERNAL;
     }
     be->dp = dp;
+    // GDB200_DP_RESERVE_SMS: SMs that the persistent GEMM / attention kernels leave free while a communicator exists,
+    // so that a collective running beside the backward pass cannot push part of a persistent grid into a second wave
+    const char *rs = getenv("GDB200_DP_RESERVE_SMS");
+    be->sm_reserve = rs != NULL ? atoi(rs) : 0;
+    if (be->sm_reserve < 0 || be->sm_reserve > be->sm_count / 2) be->sm_reserve = 0;
     return GD_OK;
 }
 

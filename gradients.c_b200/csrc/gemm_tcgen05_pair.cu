@@ -290,6 +290,7 @@ gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &
         return GD_ERR_UNSUPPORTED;
     }
     const uint32_t units = tiles_m * tiles_n * splits;
+    const int usable = clusters - (be->sm_reserve + 1) / 2 > 0 ? clusters - (be->sm_reserve + 1) / 2 : 1;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -298,7 +299,7 @@ gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see gdb_pdl_sync()
     attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.gridDim = dim3(2U * (units < (uint32_t)clusters ? units : (uint32_t)clusters));
+    cfg.gridDim = dim3(2U * (units < (uint32_t)usable ? units : (uint32_t)usable));
     cfg.blockDim = dim3(192);
     cfg.dynamicSmemBytes = P_SMEM_TOTAL;
     cfg.stream = be->stream;

@@ -16,6 +16,8 @@
 #include "common.cuh"
 
 #include <math.h>
+#include <stdlib.h>
+#include <utility>
 #include <vector>
 
 namespace {
@@ -421,8 +423,20 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         *range_elems = total;
     };
     const bool dp = be->dp != NULL && s->dp_world > 1;
+    // GDB200_DP_OVERLAP=0 defers every all-reduce to the end of the backward pass (no concurrent collective)
+    static int dp_overlap = -1;
+    if (dp_overlap < 0) {
+        const char *env = getenv("GDB200_DP_OVERLAP");
+        dp_overlap = (env != NULL && env[0] == '0') ? 0 : 1;
+    }
+    std::vector<std::pair<size_t, size_t>> deferred;
     auto reduce_range = [&](size_t off, size_t elems) {
-        if (dp) c.ok(gdb200_dp_all_reduce(be, s->scratch_buffer, off, elems, dt), "dp_all_reduce");
+        if (!dp) return;
+        if (dp_overlap) {
+            c.ok(gdb200_dp_all_reduce(be, s->scratch_buffer, off, elems, dt), "dp_all_reduce");
+        } else {
+            deferred.push_back(std::make_pair(off, elems));
+        }
     };
 
     // head: final norm weight, LM head weight (when untied) and bias
@@ -434,6 +448,10 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         alloc_grads(0, 1, &eo, &ee);
         emb_grad = grads[0];
     }
+    // the blocks' gradients follow directly, so that all parameter gradients form one address range
+    std::vector<size_t> blk_off((size_t)L), blk_elems((size_t)L);
+    for (int i = L - 1; i >= 0; --i) alloc_grads(1 + 10 * i, 10, &blk_off[(size_t)i], &blk_elems[(size_t)i]);
+    const size_t all_grads_end = c.top;
     Ten dh = c.alloc(dt, {T, D});
     if (!single) c.fill(dh, 0U);
     Ten dh_part;
@@ -472,8 +490,7 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
     for (int i = L - 1; i >= 0 && c.st == GD_OK; --i) {
         LayerSave &sv = saves[(size_t)i];
         const int pb = 1 + 10 * i;
-        size_t goff = 0, gelems = 0;
-        alloc_grads(pb, 10, &goff, &gelems);
+        const size_t goff = blk_off[(size_t)i], gelems = blk_elems[(size_t)i];
         // Everything else this block's backward allocates is dead once the block is done (the gradient that flows on
         // lives in the buffer that came in), so the space is reused by the next block: backward scratch is O(1) in depth.
         const size_t layer_mark = c.top;
@@ -551,6 +568,10 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
     gd_backend_buffer *scale_buf = s->state_buffer;
     size_t inv_scale_off = s->amp_scale_offset + sizeof(float);
     if (dp) {
+        if (!deferred.empty()) {
+            // one collective over the whole gradient range (alignment gaps between the pieces ride along)
+            c.ok(gdb200_dp_all_reduce(be, s->scratch_buffer, head_off, (all_grads_end - head_off) / es, dt), "dp_all_reduce");
+        }
         c.ok(gdb200_dp_join(be), "dp_join");
         // mean over ranks: fold 1/world into the inverse loss scale the clip and AdamW kernels use
         Ten inv = c.alloc(GDB_DTYPE_F32, {});

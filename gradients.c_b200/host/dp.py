@@ -63,3 +63,20 @@ class DataParallel:
 def split_global_batch(n_seqs: int, world: int) -> list[list[int]]:
     """Indices of the global batch owned by each rank (strided), used by tests and the launcher."""
     return [list(range(r, n_seqs, world)) for r in range(world)]
+
+
+def balanced_shards(lengths, world: int) -> list[list[int]]:
+    """Indices of the global batch per rank such that every rank gets the same number of sequences and nearly the
+    same number of tokens: sequences are taken longest first and each goes to the lightest rank that still has room.
+    A synchronous step runs at the pace of the heaviest rank, so a token-balanced shard is what keeps the ranks busy."""
+    n = len(lengths)
+    per = (n + world - 1) // world
+    order = sorted(range(n), key=lambda i: (-int(lengths[i]), i))
+    shards: list[list[int]] = [[] for _ in range(world)]
+    load = [0] * world
+    for i in order:
+        r = min((r for r in range(world) if len(shards[r]) < per), key=lambda r: (load[r], r))
+        shards[r].append(i)
+        load[r] += int(lengths[i])
+    return [sorted(sh) for sh in shards]
+

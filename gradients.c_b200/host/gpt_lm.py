@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import Optional
+from typing import Optional, Sequence
 
 import numpy as np
 
@@ -131,14 +131,15 @@ class Batch:
         return int(self.input_ids.nbytes + self.targets.nbytes + self.positions.nbytes + self.cu_seqlens.nbytes)
 
 
-def synthetic_batch(cfg: GptConfig, n_seqs: int, min_len: int, max_len: int, seed: int, pad_to: int = 0) -> Batch:
+def synthetic_batch(cfg: GptConfig, n_seqs: int, min_len: int, max_len: int, seed: int, pad_to: int = 0,
+                    lengths: Optional[Sequence[int]] = None) -> Batch:
     """Packed sequences with lengths uniform in [min_len, max_len] and ids uniform over the
     vocabulary. The target of the last token of every sequence is ignored (-1). When pad_to > 0
     the stream is padded with one fully ignored segment up to a multiple of pad_to rows
     (the reference rejects token counts that are not a multiple of the context length,
-    gpt_lm_shared.c:776)."""
+    gpt_lm_shared.c:776). `lengths` overrides the drawn lengths (a data-parallel shard of a global batch)."""
     rng = np.random.default_rng(seed)
-    lens = rng.integers(min_len, max_len + 1, size=n_seqs)
+    lens = rng.integers(min_len, max_len + 1, size=n_seqs) if lengths is None else np.asarray(lengths, dtype=np.int64)
     ids, tgt, pos, cu = [], [], [], [0]
     for n in lens:
         n = int(n)

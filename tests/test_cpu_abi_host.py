@@ -120,6 +120,18 @@ def test_dropout_site_seeds_follow_the_reference_formula():
             assert m._site_seed(g.GPT_DROPOUT_ATTN, layer, step) == want
 
 
+def test_balanced_shards_even_counts_and_tokens():
+    lens = np.random.default_rng(5).integers(64, 513, size=64 * 8)
+    shards = pkg.dp.balanced_shards(lens, 8)
+    assert sorted(i for sh in shards for i in sh) == list(range(64 * 8))
+    assert all(len(sh) == 64 for sh in shards)
+    tokens = [int(sum(lens[i] for i in sh)) for sh in shards]
+    strided = [int(sum(lens[i] for i in sh)) for sh in pkg.dp.split_global_batch(64 * 8, 8)]
+    assert max(tokens) - min(tokens) <= 64                       # within one short sequence of each other
+    assert max(tokens) - min(tokens) < max(strided) - min(strided)
+    assert pkg.dp.balanced_shards([5, 9, 1], 2) == [[1], [0, 2]]   # odd count: the first ranks take the extra one
+
+
 def _dp_worker(rank, world, port, q):
     import torch
     import torch.distributed as dist
