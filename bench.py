@@ -57,6 +57,7 @@ def parse_args():
                     help="train workload: baseline = the benchmark configuration (default); reference_default = the reference's own "
                          "defaults (F1024, tied head, dropout 0.05, window 256); scaled = BF16 d2048 L24 H16x128 F5632 V32768 ctx2048, "
                          "32 sequences of U[256,2048] per GPU")
+    ap.add_argument("--linear-shape", default="4096,512,1536", help="M,K,N of --workload linear (default: the C1 configuration)")
     ap.add_argument("--attention-mode", type=int, default=0, help="0 auto (tcgen05 forward when the shape allows), 1 mma.sync flash kernels only")
     return ap.parse_args()
 
@@ -391,8 +392,8 @@ def run_linear(args) -> None:
     import __graft_entry__ as graft
     pkg = graft.load_package()
     abi = pkg.abi
-    m, k, n = 4096, 512, 1536
-    ctx = pkg.runtime.Context(params_bytes=64 << 20, state_bytes=64 << 20, scratch_bytes=256 << 20, data_bytes=8 << 20)
+    m, k, n = (int(v) for v in args.linear_shape.split(","))
+    ctx = pkg.runtime.Context(params_bytes=max(64 << 20, 8 * (m * k + n * k + 2 * m * n)), state_bytes=64 << 20, scratch_bytes=256 << 20, data_bytes=8 << 20)
     lib = ctx.lib
     lib.gdb200_set_gemm_mode(ctx.backend, args.gemm_mode)
     rng = np.random.default_rng(0)
@@ -417,7 +418,7 @@ def run_linear(args) -> None:
     tf = flops / (ms * 1e-3) / 1e12
     print(json.dumps({"metric": "linear_fwd_bwd_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                       "ms_per_step": ms, "higher_is_better": False, "dtype": "f16", "data": "synthetic",
-                      "config": {"workload": "linear fwd+bwd X[4096,512] W[1536,512] dY[4096,1536]", "l2": "flushed before every timed step"},
+                      "config": {"workload": f"linear fwd+bwd X[{m},{k}] W[{n},{k}] dY[{m},{n}]", "l2": "flushed before every timed step"},
                       "gpu_launches": launches,
                       "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
                                    "traffic": None, "peak_source": peaks["source"] + " (burst)", "note": "includes reduce_rows and launch gaps"}}))
