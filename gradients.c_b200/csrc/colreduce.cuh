@@ -12,6 +12,7 @@
 namespace gdb_colreduce {
 
 constexpr int TILE_COLS = 256, WARPS = 8;
+constexpr int UNROLL = 8;   // rows in flight per warp (16 bytes per lane each)
 
 // MUL: multiply by b[r, c] * f[r]. lda/ldb in elements. cols % 8 == 0, bases 16-byte aligned.
 template <typename T, bool MUL>
@@ -30,22 +31,22 @@ stage_kernel(const T *__restrict__ a, size_t lda, const T *__restrict__ b, size_
     for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
     if (col < cols) {
         size_t r = r0 + warp;
-        for (; r + 3 * WARPS < r1; r += 4 * WARPS) {
-            gdb_vec8<T> va[4], vb[4];
-            float fr[4];
+        for (; r + (UNROLL - 1) * WARPS < r1; r += UNROLL * WARPS) {
+            gdb_vec8<T> va[UNROLL], vb[MUL ? UNROLL : 1];
+            float fr[MUL ? UNROLL : 1];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < UNROLL; ++u) {
                 va[u].raw = *reinterpret_cast<const uint4 *>(a + (r + u * WARPS) * lda + col);
                 if (MUL) {
-                    vb[u].raw = *reinterpret_cast<const uint4 *>(b + (r + u * WARPS) * ldb + col);
-                    fr[u] = __ldg(&f[r + u * WARPS]);
+                    vb[MUL ? u : 0].raw = *reinterpret_cast<const uint4 *>(b + (r + u * WARPS) * ldb + col);
+                    fr[MUL ? u : 0] = __ldg(&f[r + u * WARPS]);
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    acc[e] += MUL ? va[u].get(e) * vb[u].get(e) * fr[u] : va[u].get(e);
+                    acc[e] += MUL ? va[u].get(e) * vb[MUL ? u : 0].get(e) * fr[MUL ? u : 0] : va[u].get(e);
                 }
             }
         }
@@ -85,9 +86,26 @@ stage_kernel(const T *__restrict__ a, size_t lda, const T *__restrict__ b, size_
     __syncthreads();
     if (last) {
         __threadfence();
+        // warp w adds the chunks w, w + 8, ... for the lane's 8 columns; the warps' sums meet in shared memory
+        float t8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t8[e] = 0.0f;
+        if (col < cols) {
+            for (unsigned k = warp; k < gridDim.y; k += WARPS) {
+                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)k * cols + col));
+                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(partial + (size_t)k * cols + col + 4));
+                t8[0] += p0.x; t8[1] += p0.y; t8[2] += p0.z; t8[3] += p0.w;
+                t8[4] += p1.x; t8[5] += p1.y; t8[6] += p1.z; t8[7] += p1.w;
+            }
+        }
+        __syncthreads();   // sh is reused
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sh[warp][lane * 8 + e] = t8[e];
+        __syncthreads();
         if (c < cols) {
             float t = 0.0f;
-            for (unsigned k = 0; k < gridDim.y; ++k) t += __ldcg(&partial[(size_t)k * cols + c]);
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) t += sh[w][threadIdx.x];
             gdb_io<T>::st(y, c, t);
         }
         if (threadIdx.x == 0) tickets[blockIdx.x] = 0U;   // leave the counter ready for the next reduction
@@ -123,13 +141,12 @@ static inline bool usable(const void *a, size_t lda, const void *b, size_t ldb, 
            (b == NULL || ((ldb % 8U) == 0U && ((uintptr_t)b % 16U) == 0U));
 }
 
-// Number of row chunks: about two waves of blocks, at least 64 rows per chunk, capped by capacity.
+// Number of row chunks: about four waves of blocks, at least 128 rows per chunk, capped by capacity.
 static inline size_t pick_chunks(const gd_backend *be, size_t rows, size_t cols, size_t capacity_chunks)
 {
-    // two waves of blocks: enough parallelism for the row sweep, few enough chunks for the last block's final sum
     const size_t col_tiles = (cols + TILE_COLS - 1U) / TILE_COLS;
-    size_t chunks = ((size_t)be->sm_count * 2U + col_tiles - 1U) / col_tiles;
-    const size_t by_rows = (rows + 63U) / 64U;
+    size_t chunks = ((size_t)be->sm_count * 4U + col_tiles - 1U) / col_tiles;
+    const size_t by_rows = (rows + 2U * UNROLL * WARPS - 1U) / (2U * UNROLL * WARPS);   // at least two unrolled sweeps per warp
     if (chunks > by_rows) chunks = by_rows;
     if (chunks > capacity_chunks) chunks = capacity_chunks;
     if (chunks > 65535U) chunks = 65535U;
