@@ -136,12 +136,40 @@ __global__ void grad_norm_stage_kernel(norm_batch b)
     const float gs = b.grad_scale[0];
     float sum = 0.0f;
     bool bad = false;
-    for (unsigned j = threadIdx.x; j < NORM_BLOCK * NORM_GROUP; j += blockDim.x) {
-        const size_t i = base + j;
-        if (i < b.count[t]) {
-            const float g = load_as_float(b.grad[t], i, b.dtype[t]) * gs;
-            bad = bad || !isfinite(g);
-            sum = fmaf(g, g, sum);
+    const uint32_t dt = b.dtype[t];
+    const unsigned char *gp = (const unsigned char *)b.grad[t];
+    if ((dt == GDB_DTYPE_F16 || dt == GDB_DTYPE_BF16) && ((uintptr_t)(gp + base * 2U) % 16U) == 0U &&
+        base + (size_t)NORM_BLOCK * NORM_GROUP <= b.count[t]) {
+        // full group of 16-bit gradients: 16-byte loads, 8 elements each
+        const uint4 *v = reinterpret_cast<const uint4 *>(gp + base * 2U);
+        for (unsigned j = threadIdx.x; j < NORM_BLOCK * NORM_GROUP / 8U; j += blockDim.x) {
+            const uint4 raw = __ldg(&v[j]);
+            const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float g0, g1;
+                if (dt == GDB_DTYPE_F16) {
+                    g0 = gdb_io<__half>::up((unsigned short)(w[e] & 0xffffU));
+                    g1 = gdb_io<__half>::up((unsigned short)(w[e] >> 16));
+                } else {
+                    g0 = gdb_io<__nv_bfloat16>::up((unsigned short)(w[e] & 0xffffU));
+                    g1 = gdb_io<__nv_bfloat16>::up((unsigned short)(w[e] >> 16));
+                }
+                g0 *= gs;
+                g1 *= gs;
+                bad = bad || !isfinite(g0) || !isfinite(g1);
+                sum = fmaf(g0, g0, sum);
+                sum = fmaf(g1, g1, sum);
+            }
+        }
+    } else {
+        for (unsigned j = threadIdx.x; j < NORM_BLOCK * NORM_GROUP; j += blockDim.x) {
+            const size_t i = base + j;
+            if (i < b.count[t]) {
+                const float g = load_as_float(b.grad[t], i, dt) * gs;
+                bad = bad || !isfinite(g);
+                sum = fmaf(g, g, sum);
+            }
         }
     }
     if (bad && b.found_inf != nullptr) {
@@ -256,6 +284,49 @@ __global__ void adamw_update_kernel(adamw_batch b)
     const float eps_scaled = a.eps_scaled != nullptr ? a.eps_scaled[0] : a.host_eps_scaled;
     const float omb1 = __fsub_rn(1.0f, a.beta1), omb2 = __fsub_rn(1.0f, a.beta2);
     const size_t base = (size_t)(blockIdx.x - b.block_start[t]) * ADAMW_BLOCK_ELEMS;
+    // Full block of 16-bit parameters / gradients with FP32 masters: every thread owns 8 consecutive elements and moves
+    // them with 16-byte accesses; the arithmetic per element is the one of the scalar loop below, operation for operation.
+    if (a.master != nullptr && a.param_dtype == a.grad_dtype && (a.param_dtype == GDB_DTYPE_F16 || a.param_dtype == GDB_DTYPE_BF16) &&
+        base + ADAMW_BLOCK_ELEMS <= a.count &&
+        (((uintptr_t)((const unsigned char *)a.grad + base * 2U) | (uintptr_t)((unsigned char *)a.param + base * 2U) |
+          (uintptr_t)(a.master + base) | (uintptr_t)(a.m + base) | (uintptr_t)(a.v + base)) % 16U) == 0U) {
+        const size_t i0 = base + (size_t)threadIdx.x * 8U;
+        const bool f16 = a.param_dtype == GDB_DTYPE_F16;
+        const uint4 graw = __ldg(reinterpret_cast<const uint4 *>((const unsigned char *)a.grad + i0 * 2U));
+        const unsigned gw[4] = {graw.x, graw.y, graw.z, graw.w};
+        float pm[8], mm[8], vv8[8];
+        *reinterpret_cast<float4 *>(pm) = *reinterpret_cast<const float4 *>(a.master + i0);
+        *reinterpret_cast<float4 *>(pm + 4) = *reinterpret_cast<const float4 *>(a.master + i0 + 4);
+        *reinterpret_cast<float4 *>(mm) = *reinterpret_cast<const float4 *>(a.m + i0);
+        *reinterpret_cast<float4 *>(mm + 4) = *reinterpret_cast<const float4 *>(a.m + i0 + 4);
+        *reinterpret_cast<float4 *>(vv8) = *reinterpret_cast<const float4 *>(a.v + i0);
+        *reinterpret_cast<float4 *>(vv8 + 4) = *reinterpret_cast<const float4 *>(a.v + i0 + 4);
+        unsigned pw[4];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const unsigned short bits = (unsigned short)((e & 1) ? (gw[e >> 1] >> 16) : (gw[e >> 1] & 0xffffU));
+            float g = f16 ? gdb_io<__half>::up(bits) : gdb_io<__nv_bfloat16>::up(bits);
+            g = gs == 0.0f ? 0.0f : __fmul_rn(g, gs);
+            const float p = pm[e];
+            const float m_new = fmaf(a.beta1, mm[e], __fmul_rn(omb1, g));
+            const float v_new = fmaf(a.beta2, vv8[e], __fmul_rn(__fmul_rn(omb2, g), g));
+            const float denom = __fadd_rn(sqrtf(v_new), eps_scaled);
+            const float p_new = __fsub_rn(__fsub_rn(p, __fdiv_rn(__fmul_rn(step_scale, m_new), denom)), __fmul_rn(decay_scale, p));
+            mm[e] = m_new;
+            vv8[e] = v_new;
+            pm[e] = p_new;
+            const unsigned pb = f16 ? gdb_io<__half>::down(p_new) : gdb_io<__nv_bfloat16>::down(p_new);
+            if (e & 1) pw[e >> 1] |= pb << 16; else pw[e >> 1] = pb;
+        }
+        *reinterpret_cast<float4 *>(a.master + i0) = *reinterpret_cast<const float4 *>(pm);
+        *reinterpret_cast<float4 *>(a.master + i0 + 4) = *reinterpret_cast<const float4 *>(pm + 4);
+        *reinterpret_cast<float4 *>(a.m + i0) = *reinterpret_cast<const float4 *>(mm);
+        *reinterpret_cast<float4 *>(a.m + i0 + 4) = *reinterpret_cast<const float4 *>(mm + 4);
+        *reinterpret_cast<float4 *>(a.v + i0) = *reinterpret_cast<const float4 *>(vv8);
+        *reinterpret_cast<float4 *>(a.v + i0 + 4) = *reinterpret_cast<const float4 *>(vv8 + 4);
+        *reinterpret_cast<uint4 *>((unsigned char *)a.param + i0 * 2U) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        return;
+    }
 #pragma unroll 4
     for (unsigned j = threadIdx.x; j < ADAMW_BLOCK_ELEMS; j += 256) {
         const size_t i = base + j;

@@ -1,9 +1,9 @@
 """Generates the committed golden fixtures under tests/golden/ from the REFERENCE's own code.
 
-Run in a container that has the reference tree (default /root/reference) and after
+Run in a container that has the reference tree (see --ref for the default location) and after
 `python -c "import __graft_entry__ as g; g.build()"` (which builds oracle/_ref/ref_harness.so):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference tree>]
 
 Sources of truth (nothing is re-derived from this repository's oracle):
   * CPU reference functions that the reference's C tests carry (tests/test_sdpa_varlen.c:122-371,

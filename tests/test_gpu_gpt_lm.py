@@ -56,6 +56,33 @@ def test_train_steps_track_oracle(variant):
             np.testing.assert_allclose(host(prm).reshape(-1), ref.p[name].numpy().reshape(-1), atol=2e-3, rtol=2e-2, err_msg=name)
 
 
+def test_fifty_seeded_steps_track_the_oracle_loss_and_scaler_trajectory():
+    """Stated bound for the whole path: over 50 seeded steps (dropout masks identical by construction, learning rate
+    3e-3 so that the loss really moves) the mean loss of every window of 10 steps stays within 2 % of the oracle's,
+    every single step within 5 %, and the loss scale / overflow trajectory is identical."""
+    cfg, tc = small_cfg(), g.TrainConfig.baseline()
+    tc.lr = 3.0e-3
+    hp = g.init_params(cfg, seed=17)
+    ref = OG.OracleGptLm(OG.config_from(cfg), hp)
+    otc = OG.train_config_from(tc)
+    got, want, scales = [], [], []
+    with pkg.runtime.Context(params_bytes=64 << 20, state_bytes=128 << 20, scratch_bytes=1 << 30) as ctx:
+        trainer = g.NativeTrainer(g.GptLm(ctx, cfg, hp), tc)
+        for step in range(50):
+            b = g.synthetic_batch(cfg, n_seqs=6, min_len=8, max_len=64, seed=500 + step % 5, pad_to=64)   # 5 batches, revisited
+            got.append(float(trainer.train_batch(b).read()[()]))
+            w = ref.train_step(b.input_ids, b.targets, b.positions, b.cu_seqlens, step + 1, otc)
+            want.append(w["loss"])
+            s = trainer.scaler.sync()
+            scales.append((s["scale"], bool(s["last_found_inf"]), w["scale"], w["found_inf"]))
+    got, want = np.array(got), np.array(want)
+    assert all(a == c and b == d for a, b, c, d in scales)
+    assert np.all(np.abs(got - want) <= 0.05 * np.abs(want)), np.abs(got / want - 1).max()
+    for k in range(0, 50, 10):
+        assert abs(got[k:k + 10].mean() - want[k:k + 10].mean()) <= 0.02 * want[k:k + 10].mean()
+    assert want[-5:].mean() < 0.9 * want[:5].mean()          # the run does learn something
+
+
 def test_trainer_train_batch_matches_manual_sequence():
     cfg = small_cfg()
     hp = g.init_params(cfg, seed=5)
