@@ -646,11 +646,11 @@ gd_status decode_common(gd_backend *be, const gd_backend_tensor_view *q, const g
     const long long total = (long long)p.batch * p.tq * p.hq;
     const bool al16 = (((uintptr_t)kp | (uintptr_t)vp) % 16U) == 0U;
     if ((p.dh == 64 || p.dh == 128) && dt != GDB_DTYPE_F32 && al16) {
-        // choose splits so that about `wps` warps per SM are in flight (GDB200_DECODE_WARPS_PER_SM, default 16)
+        // choose splits so that about `wps` warps per SM are in flight (GDB200_DECODE_WARPS_PER_SM, default 32)
         static int wps = 0;
         if (wps == 0) {
             const char *env = getenv("GDB200_DECODE_WARPS_PER_SM");
-            wps = env != NULL && atoi(env) > 0 ? atoi(env) : 16;
+            wps = env != NULL && atoi(env) > 0 ? atoi(env) : 32;
         }
         int splits = (int)(((long long)be->sm_count * wps + total - 1) / total);
         const int max_splits = (p.tmax + 63) / 64;
