@@ -145,7 +145,7 @@ __device__ __forceinline__ float quad_sum(float v)
 // grid = (ceil(N / 64), Hq), 128 threads; warp w owns query rows 16w..16w+15 of the chunk.
 // ------------------------------------------------------------------------------------------------
 template <typename T, int DH, int BKV, int MODE>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 flash_q_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ go,
                const int *__restrict__ cu, T *__restrict__ out, float *__restrict__ stats, flash_params p)
 {
@@ -406,7 +406,7 @@ flash_q_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__rest
 // grid = (ceil(N / 64), Hkv), 128 threads; warp w owns keys 16w..16w+15 of the chunk.
 // ------------------------------------------------------------------------------------------------
 template <typename T, int DH, int BQT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 flash_kv_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ go,
                 const int *__restrict__ cu, const float *__restrict__ stats, T *__restrict__ dk, T *__restrict__ dv,
                 flash_params p)
