@@ -284,7 +284,11 @@ gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a,
 gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype,
                                 const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
                                 void *c, size_t ldc_bytes, const void *bias, int bias_mode,
-                                uint32_t M, uint32_t N, uint32_t K, uint32_t *splits_out);
+                                uint32_t M, uint32_t N, uint32_t K, uint32_t *splits_out, float **colsum_partial_out = nullptr);
+// C[M, N] = A^T B with A stored [K, M], B stored [K, N], and colsum[m] = sum_k A[k, m] from the same pass over A
+// (weight gradient + bias gradient of a linear layer). GD_ERR_UNSUPPORTED when the CTA-pair kernel does not apply.
+gd_status gdb_gemm_tcgen05_tn_colsum(gd_backend *be, uint32_t dtype, const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
+                                     void *c, size_t ldc_bytes, void *colsum, uint32_t M, uint32_t N, uint32_t K);
 // Fusions used by the native decode driver (GD_ERR_UNSUPPORTED when their vector paths do not apply).
 gd_status gdb_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y, const gd_backend_tensor_view *weight,
                            const gd_backend_tensor_view *sum, const gd_backend_tensor_view *out, size_t rows, size_t cols, float eps);

@@ -397,6 +397,30 @@ gd_status gdb200_matmul_nt_bias(gd_backend *be, const gd_backend_matrix_view *x,
 {
     return gdb_gemm_dispatch(be, 0, 1, x, w, bias, y, 2);
 }
+gd_status gdb200_matmul_tn_colsum(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_matrix_view *y,
+                                  const gd_backend_vector_view *colsum)
+{
+    if (be == NULL || x == NULL || w == NULL || y == NULL || colsum == NULL || colsum->buffer == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = y->dtype;
+    const size_t es = gdb_dtype_size(dt);
+    if (x->dtype != dt || w->dtype != dt || colsum->dtype != dt || colsum->length != x->cols) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (gdb_is_float_dtype(dt) && mv_ok(x, es) && mv_ok(w, es) && mv_ok(y, es) && x->rows == w->rows && y->rows == x->cols && y->cols == w->cols &&
+        gdb_range_ok(colsum->buffer, colsum->offset, (size_t)colsum->length * es)) {
+        const gd_status st = gdb_gemm_tcgen05_tn_colsum(be, dt, x->buffer->dptr + x->offset, x->row_bytes, w->buffer->dptr + w->offset, w->row_bytes,
+                                                        y->buffer->dptr + y->offset, y->row_bytes, colsum->buffer->dptr + colsum->offset,
+                                                        x->cols, w->cols, x->rows);
+        if (st != GD_ERR_UNSUPPORTED) {
+            return st;
+        }
+    }
+    // shapes the fused kernel does not take: the two entries it stands for
+    const gd_status st = gd_backend_matmul_tn(be, x, w, y);
+    return st != GD_OK ? st : gd_backend_reduce_rows(be, x, colsum);
+}
 gd_status gd_backend_batched_matmul(gd_backend *be, const gd_backend_batched_matrix_view *x, const gd_backend_batched_matrix_view *w, const gd_backend_batched_matrix_view *y)
 {
     return batched_dispatch(be, 0, 0, x, w, y);

@@ -208,9 +208,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 // out[m, n] = round(sum_z partial[z, m, n] + bias[n])
 template <typename T>
 __global__ void splitk_reduce_kernel(const float *__restrict__ partial, T *__restrict__ c, size_t ldc, const T *__restrict__ bias,
-                                     uint32_t M, uint32_t N, uint32_t splits, int bias_mode)
+                                     uint32_t M, uint32_t N, uint32_t splits, int bias_mode, const float *__restrict__ colsum_partial,
+                                     T *__restrict__ colsum)
 {
     gdb_pdl_sync();
+    if (colsum_partial != nullptr) {
+        // colsum[m] = round(sum_z colsum_partial[z, m])
+        for (size_t m = (size_t)blockIdx.x * blockDim.x + threadIdx.x; m < M; m += (size_t)gridDim.x * blockDim.x) {
+            float acc = 0.0f;
+            for (uint32_t z = 0; z < splits; ++z) acc += colsum_partial[(size_t)z * M + m];
+            gdb_io<T>::st(colsum, m, acc);
+        }
+    }
     const size_t quads = (size_t)M * (N / 4), stride = (size_t)gridDim.x * blockDim.x;
     for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += stride) {
         const uint32_t row = (uint32_t)(q / (N / 4)), col = (uint32_t)(q % (N / 4)) * 4;
@@ -276,13 +285,13 @@ gd_status dispatch_major(gd_backend *be, int ta, int tb, const CUtensorMap &ma, 
 }
 
 gd_status reduce_partials(gd_backend *be, uint32_t dtype, const float *partial, void *c, size_t ldc, const void *bias, uint32_t M,
-                          uint32_t N, uint32_t splits, int bias_mode)
+                          uint32_t N, uint32_t splits, int bias_mode, const float *colsum_partial = nullptr, void *colsum = nullptr)
 {
     const size_t quads = (size_t)M * (N / 4U);
     if (dtype == GDB_DTYPE_F16) {
-        gdb_launch(splitk_reduce_kernel<__half>, gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream, partial, (__half *)c, ldc, (const __half *)bias, M, N, splits, bias_mode);
+        gdb_launch(splitk_reduce_kernel<__half>, gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream, partial, (__half *)c, ldc, (const __half *)bias, M, N, splits, bias_mode, colsum_partial, (__half *)colsum);
     } else {
-        gdb_launch(splitk_reduce_kernel<__nv_bfloat16>, gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream, partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits, bias_mode);
+        gdb_launch(splitk_reduce_kernel<__nv_bfloat16>, gdb_grid_for(quads, 256, be, 8), 256, 0, be->stream, partial, (__nv_bfloat16 *)c, ldc, (const __nv_bfloat16 *)bias, M, N, splits, bias_mode, colsum_partial, (__nv_bfloat16 *)colsum);
     }
     return gdb_launched(be, "gemm_splitk_reduce");
 }
@@ -352,3 +361,21 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const
 }
 
 void gdb_tmap_cache_destroy(gd_backend *be) { (void)be; }
+
+gd_status gdb_gemm_tcgen05_tn_colsum(gd_backend *be, uint32_t dtype, const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
+                                     void *c, size_t ldc_bytes, void *colsum, uint32_t M, uint32_t N, uint32_t K)
+{
+    if ((dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) || be->gemm_mode == 1 || be->gemm_mode == 3 || colsum == NULL ||
+        (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) % 16U) != 0U || (lda_bytes % 16U) != 0U || (ldb_bytes % 16U) != 0U ||
+        (ldc_bytes % 16U) != 0U || (N % 8U) != 0U || (K % 8U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    uint32_t splits = 1;
+    float *cs = nullptr;
+    gd_status st = gdb_gemm_tcgen05_pair(be, 1, 0, dtype, a, lda_bytes, b, ldb_bytes, c, ldc_bytes, NULL, 1, M, N, K, &splits, &cs);
+    if (st != GD_OK) {
+        return st;
+    }
+    return reduce_partials(be, dtype, (const float *)be->ws, c, ldc_bytes / 2U, NULL, M, N, splits, 1, cs, colsum);
+}
+

@@ -33,13 +33,22 @@ constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_STAGING_PER_WARP = 2 * 4096;   // two 32-row x 128-byte buffers
 constexpr int P_STAGING_BYTES = 4 * P_STAGING_PER_WARP;
 constexpr int P_SMEM_TOTAL = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 256 + 1024;
+constexpr int P_SMEM_TOTAL_COLSUM = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 1024 + 1024 + 1024;   // barriers padded to 1 KB, ones tile, alignment slack
 
-template <typename T, bool A_MN, bool B_MN, bool SPLITK>
+// COLSUM (split-K output only): the units of the first tile column also accumulate the sums of A over the
+// contraction, colsum[m] = sum_k A[m, k], by one more MMA per k-step against a tile of ones (N = 16; every output
+// column holds the sum), and write them per k-slice to colsum_partial[splits, M]. This is the bias gradient of a
+// linear layer for free while its weight gradient dW = dY^T X is computed (A = dY^T). Tensor memory then holds ONE
+// accumulator (256 columns) plus the 16 column-sum columns, so units are not overlapped (split-K launches run about one
+// unit per CTA pair anyway).
+template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM>
 __global__ void __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const T *__restrict__ bias, uint32_t M, uint32_t N, uint32_t K,
-                 uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t k_iters_per_split, int bias_mode, int *err_flag)
+                 uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t k_iters_per_split, int bias_mode, int *err_flag,
+                 float *__restrict__ colsum_partial)
 {
+    static_assert(!COLSUM || SPLITK, "column sums ride on the split-K (FP32 partial) output path");
     gdb_pdl_sync();
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
@@ -56,6 +65,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[PSTAGES]);
     const uint32_t tfull0 = smem_u32(&bars[2 * PSTAGES]), tempty0 = smem_u32(&bars[2 * PSTAGES + 2]);
+    unsigned char *ones_tile = staging + P_STAGING_BYTES + 1024;   // 1 KB, 1024-byte aligned: 8 rows x 64 k of 1.0
+    if (COLSUM) {
+        const uint32_t one2 = std::is_same<T, __nv_bfloat16>::value ? 0x3F803F80U : 0x3C003C00U;
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) reinterpret_cast<uint32_t *>(ones_tile)[i] = one2;
+        fence_proxy_async_smem();   // the MMA reads this tile through the async proxy
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < PSTAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);
@@ -127,7 +142,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 const uint32_t z = u / (tiles_n * tiles_m);
                 const uint32_t k_begin = z * k_iters_per_split;
                 const uint32_t k_end = min(total_k_iters, k_begin + k_iters_per_split);
-                const uint32_t buf = unit_idx & 1U, acc_ph = (unit_idx >> 1) & 1U;
+                const uint32_t buf = COLSUM ? 0U : (unit_idx & 1U), acc_ph = COLSUM ? (unit_idx & 1U) : ((unit_idx >> 1) & 1U);
+                const bool do_colsum = COLSUM && (u % tiles_n) == 0U;
                 if (!mbar_wait(tempty0 + 8 * buf, acc_ph ^ 1U)) {
                     atomicExch(err_flag, 202);
                     break;
@@ -150,6 +166,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         const uint64_t bdesc = B_MN ? make_smem_desc(b_base + kk * 2048, BK * 128, 1024)
                                                     : make_smem_desc(b_base + kk * 32, 16, 1024);
                         tcgen05_mma_f16_pair(d_tmem, adesc, bdesc, IDESC, (kb != k_begin || kk != 0) ? 1U : 0U);
+                        if (do_colsum) {
+                            // sum over k of the same A tile: B = ones (K-major, 8 rows per CTA), N = 16, columns 256..271
+                            constexpr uint32_t IDESC_ONES = (1U << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1U : 0U) << 15) |
+                                                            ((uint32_t)(16 >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+                            tcgen05_mma_f16_pair(tmem_base + PBN, adesc, make_smem_desc(smem_u32(ones_tile) + kk * 32, 16, 1024), IDESC_ONES,
+                                                 (kb != k_begin || kk != 0) ? 1U : 0U);
+                        }
                     }
                     tcgen05_commit_pair(empty0 + 8 * s, 3);
                 }
@@ -167,7 +190,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         constexpr int CHUNK_COLS = SPLITK ? 32 : 64;   // 128 bytes of output per row
         for (uint32_t u = cluster_id; u < units; u += n_clusters, ++unit_idx) {
             const uint32_t tn = u % tiles_n, tm = (u / tiles_n) % tiles_m, z = u / (tiles_n * tiles_m);
-            const uint32_t buf = unit_idx & 1U, acc_ph = (unit_idx >> 1) & 1U;
+            const uint32_t buf = COLSUM ? 0U : (unit_idx & 1U), acc_ph = COLSUM ? (unit_idx & 1U) : ((unit_idx >> 1) & 1U);
             const bool got = mbar_wait(tfull0 + 8 * buf, acc_ph);
             if (!got) {
                 if (lane == 0) atomicExch(err_flag, 204);
@@ -176,6 +199,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             tcgen05_fence_after();
             const uint32_t row0 = tm * 2 * BM + rank * BM + quad * 32;
             const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * PBN;
+            if (COLSUM && tn == 0U) {
+                uint32_t cs[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + PBN, cs);   // every column holds the row's sum
+                const uint32_t row = row0 + lane;
+                if (row < M) colsum_partial[(size_t)z * M + row] = __uint_as_float(cs[0]);
+            }
 #pragma unroll 1
             for (int c = 0; c < PBN / CHUNK_COLS; ++c) {
                 uint32_t v0[32], v1[32];
@@ -248,7 +277,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
 }
 
-int max_clusters(gd_backend *be, const void *kern)
+int max_clusters(gd_backend *be, const void *kern, int smem_bytes)
 {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
@@ -258,7 +287,7 @@ int max_clusters(gd_backend *be, const void *kern)
     attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3((unsigned)be->sm_count & ~1U);
     cfg.blockDim = dim3(192);
-    cfg.dynamicSmemBytes = P_SMEM_TOTAL;
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
@@ -269,18 +298,20 @@ int max_clusters(gd_backend *be, const void *kern)
     return n < be->sm_count / 2 ? n : be->sm_count / 2;
 }
 
-template <typename T, bool A_MN, bool B_MN, bool SPLITK>
+template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM = false>
 gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const void *bias, uint32_t M,
-                      uint32_t N, uint32_t K, uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t kps, int bias_mode, int *clusters_out)
+                      uint32_t N, uint32_t K, uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t kps, int bias_mode, int *clusters_out,
+                      float *colsum_partial = nullptr)
 {
-    auto kern = gemm_pair_kernel<T, A_MN, B_MN, SPLITK>;
+    constexpr int SMEM = COLSUM ? P_SMEM_TOTAL_COLSUM : P_SMEM_TOTAL;
+    auto kern = gemm_pair_kernel<T, A_MN, B_MN, SPLITK, COLSUM>;
     static int clusters = -1;
     if (clusters < 0) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) {
             return gdb_fail(be, e, "tcgen05 pair gemm smem attribute");
         }
-        clusters = max_clusters(be, (const void *)kern);
+        clusters = max_clusters(be, (const void *)kern, SMEM);
     }
     if (clusters_out != nullptr) {
         *clusters_out = clusters;
@@ -301,11 +332,11 @@ gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.gridDim = dim3(2U * (units < (uint32_t)usable ? units : (uint32_t)usable));
     cfg.blockDim = dim3(192);
-    cfg.dynamicSmemBytes = P_SMEM_TOTAL;
+    cfg.dynamicSmemBytes = SMEM;
     cfg.stream = be->stream;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, (const T *)bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, be->err_flag);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, (const T *)bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, be->err_flag, colsum_partial);
     if (e != cudaSuccess) {
         be->launches += 1U;
         return gdb_fail(be, e, "gemm_tcgen05_pair");
@@ -333,12 +364,15 @@ gd_status dispatch_pair(gd_backend *be, int ta, int tb, bool sk, const CUtensorM
 // Same contract as gdb_gemm_tcgen05 (which calls this first). Returns GD_ERR_UNSUPPORTED when the
 // problem is too small for 256-row tiles or clusters of two cannot be scheduled; `*splits_out`
 // receives the number of FP32 partial slices written to the workspace (1 = C was written directly).
+// `colsum_partial_out` != NULL (only for ta = 1, tb = 0, the weight-gradient layout): the FP32 partial path is taken even
+// for a single k-slice, and *colsum_partial_out receives the workspace address of colsum partials [*splits_out, M].
 gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b,
                                 size_t ldb_bytes, void *c, size_t ldc_bytes, const void *bias, int bias_mode, uint32_t M, uint32_t N,
-                                uint32_t K, uint32_t *splits_out)
+                                uint32_t K, uint32_t *splits_out, float **colsum_partial_out)
 {
     *splits_out = 1;
-    if (M < 256U || N < 128U || K < 64U) {
+    const bool want_colsum = colsum_partial_out != nullptr;
+    if (M < 256U || N < 128U || K < 64U || (want_colsum && !(ta && !tb))) {
         return GD_ERR_UNSUPPORTED;
     }
     CUtensorMap ma, mb, mc;
@@ -368,6 +402,24 @@ gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype, 
     }
     uint32_t kps = (total_k + splits - 1U) / splits;
     splits = (total_k + kps - 1U) / kps;
+    if (want_colsum) {
+        const size_t dw_bytes = ((size_t)splits * M * N * sizeof(float) + 255U) & ~(size_t)255U;
+        if (dw_bytes + (size_t)splits * M * sizeof(float) > be->ws_bytes / 2U) {
+            return GD_ERR_UNSUPPORTED;
+        }
+        float *cs = reinterpret_cast<float *>(be->ws + dw_bytes);
+        if (!make_tmap_f32_3d(&mc, be->ws, splits, M, N, 32)) {
+            return GD_ERR_UNSUPPORTED;
+        }
+        st = dtype == GDB_DTYPE_F16
+                 ? launch_pair<__half, true, true, true, true>(be, ma, mb, mc, bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, nullptr, cs)
+                 : launch_pair<__nv_bfloat16, true, true, true, true>(be, ma, mb, mc, bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, nullptr, cs);
+        if (st == GD_OK) {
+            *splits_out = splits;
+            *colsum_partial_out = cs;
+        }
+        return st;
+    }
     const bool sk = splits > 1U;
     const bool okc = sk ? make_tmap_f32_3d(&mc, be->ws, splits, M, N, 32) : make_tmap(&mc, dtype, c, M, N, ldc_bytes, 64, 32);
     if (!okc) {

@@ -184,10 +184,10 @@ void linear_t_backward(Step &c, const Ten &x, const Ten &w, const Ten &g, int64_
         gd_backend_matrix_view dxm = mv(*dx, (uint32_t)m, (uint32_t)k);
         c.ok(gd_backend_matmul(c.be, &gm, &wm, &dxm), "matmul(dX)");
     }
+    // dW = g^T x and db = colsum(g) from one pass over g
     gd_backend_matrix_view dwm = mv(dw, (uint32_t)n, (uint32_t)k);
-    c.ok(gd_backend_matmul_tn(c.be, &gm, &xm, &dwm), "matmul_tn(dW)");
     gd_backend_vector_view dbv = vv(db, 0, (uint32_t)n);
-    c.ok(gd_backend_reduce_rows(c.be, &gm, &dbv), "reduce_rows(db)");
+    c.ok(gdb200_matmul_tn_colsum(c.be, &gm, &xm, &dwm, &dbv), "matmul_tn_colsum(dW, db)");
 }
 
 Ten rms_forward(Step &c, const Ten &x, const Ten &w, int64_t rows, int64_t cols, Ten *inv)
@@ -483,9 +483,8 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         c.ok(gd_backend_matmul(be, &lm, &wm, &dhm), "matmul(d_hidden)");
         if (!single) c.accumulate(dh, dh_part);
         gd_backend_matrix_view dwm = mv(lmw_grad, (uint32_t)cc, (uint32_t)D, (size_t)start);
-        c.ok(gd_backend_matmul_tn(be, &lm, &hm, &dwm), "matmul_tn(d_lm_w)");
         gd_backend_vector_view dbv = vv(grads[(size_t)P_LMB], (size_t)start, (uint32_t)cc);
-        c.ok(gd_backend_reduce_rows(be, &lm, &dbv), "reduce_rows(d_lm_b)");
+        c.ok(gdb200_matmul_tn_colsum(be, &lm, &hm, &dwm, &dbv), "matmul_tn_colsum(d_lm_w, d_lm_b)");
     }
     Ten gx = rms_backward(c, x, final_w, inv_f, dh, T, D, grads[(size_t)P_FINAL]);
     reduce_range(head_off, head_elems);

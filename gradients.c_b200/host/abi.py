@@ -267,6 +267,7 @@ PROTOTYPES = {
     "gdb200_embedding_backward_static_error": (C.c_char_p, []),
     "gdb200_embedding_backward_static_max_elems": (U64, []),
     "gdb200_gpt_train_step": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptBatch), U64, F, C.POINTER(SZ), C.POINTER(SZ)]),
+    "gdb200_matmul_tn_colsum": (_ST, [P, MV, MV, MV, VV]),
     "gdb200_argmax_rows": (_ST, [P, TV, F, TV]),
     "gdb200_gpt_decode_steps": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptDecodeState), I32_T, I32_T, C.POINTER(SZ)]),
     "gdb200_dp_unique_id": (_ST, [P]),

@@ -386,6 +386,13 @@ gd_status gdb200_flush_l2(gd_backend *backend);
 gd_status gdb200_matmul_nt_bias(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
                                 const gd_backend_vector_view *bias, const gd_backend_matrix_view *y);
 
+/* Weight and bias gradient of a linear layer in one pass over the upstream gradient (no counterpart in the reference,
+ * which calls matmul_tn and reduce_rows, src/ops/linear_transposed_weight/core_linear_transposed_weight_bwd.c:31-167):
+ * y[M, N] = x^T w with x stored [K, M] and w stored [K, N] (as gd_backend_matmul_tn), and colsum[m] = sum_k x[k, m]
+ * (as gd_backend_reduce_rows(x)). Shapes the fused kernel does not take run as those two entries. */
+gd_status gdb200_matmul_tn_colsum(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
+                                  const gd_backend_matrix_view *y, const gd_backend_vector_view *colsum);
+
 /* Embedding table gradient with no allocation (no counterpart in the reference). Same result as
  * gd_backend_embedding_backward, but the FP32 accumulation table is a fixed device array inside the
  * library instead of a caller-provided scratch tensor, for callers that cannot allocate: a runtime

@@ -473,6 +473,30 @@ def test_tcgen05_gemm_split_k_weight_gradient(step, m, k, n):
         lib.gdb200_set_gemm_mode(ctx.backend, old)
 
 
+@pytest.mark.parametrize("m,k,n", [(1536, 8192, 512), (512, 16384, 512), (3072, 4096, 512), (2048, 4096, 512), (300, 1000, 136), (64, 256, 64)])
+def test_matmul_tn_colsum_equals_matmul_tn_plus_reduce_rows(step, m, k, n):
+    """gdb200_matmul_tn_colsum: dW = dY^T X and db = colsum(dY) from one pass over dY (column sums by an extra MMA
+    against a tile of ones); small / ragged shapes take the two-call path inside the entry."""
+    ctx, lib = step, step.lib
+    dy = rnd_np((rng(85).standard_normal((k, m)) * 0.25).astype(np.float32), F16)   # stored [tokens, m]
+    x = rnd_np((rng(86).standard_normal((k, n)) * 0.25).astype(np.float32), F16)    # stored [tokens, n]
+    dyt, xt = dev(ctx, dy, F16), dev(ctx, x, F16)
+    y0, y1 = ctx.scratch_empty(F16, (m, n)), ctx.scratch_empty(F16, (m, n))
+    b0, b1 = ctx.scratch_empty(F16, (m,)), ctx.scratch_empty(F16, (m,))
+    xv, wv = dyt.mv(k, m), xt.mv(k, n)
+    y0v, y1v, b0v, b1v = y0.mv(m, n), y1.mv(m, n), b0.vv(), b1.vv()
+    ctx.check(lib.gd_backend_matmul_tn(ctx.backend, byref(xv), byref(wv), byref(y0v)), "matmul_tn")
+    ctx.check(lib.gd_backend_reduce_rows(ctx.backend, byref(xv), byref(b0v)), "reduce_rows")
+    ctx.check(lib.gdb200_matmul_tn_colsum(ctx.backend, byref(xv), byref(wv), byref(y1v), byref(b1v)), "matmul_tn_colsum")
+    ctx.flush()
+    want = O.rnd(t32(dy).t() @ t32(x))
+    close(host(y1), want, F16, scale=np.sqrt(k) / 16, what="dW vs oracle")
+    np.testing.assert_allclose(host(y1), host(y0), atol=1e-3 * np.sqrt(k) / 16, rtol=2e-3)
+    want_b = O.rnd(t32(dy).sum(dim=0))
+    close(host(b1), want_b, F16, scale=np.sqrt(k) / 8, what="db vs oracle")
+    close(host(b1), host(b0), F16, scale=np.sqrt(k) / 8, what="db vs reduce_rows")
+
+
 # ------------------------------------------------------------------ flash attention at benchmark-like shapes
 @pytest.mark.parametrize("dtype,hq,hkv,dh,window,total", [(F16, 8, 8, 64, 0, 3000), (F16, 8, 8, 64, 256, 3000), (F16, 8, 2, 64, 100, 1500),
                                                           (BF16, 4, 4, 128, 0, 1200), (BF16, 4, 2, 128, 48, 700)])
