@@ -106,7 +106,6 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
                  const __grid_constant__ CUtensorMap tma_v, T *__restrict__ out,
                  const int *__restrict__ cu, float *__restrict__ stats, attn5_params p, int *err_flag)
 {
-    gdb_pdl_sync();
     using plan = attn5_plan;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int cu_s[A_MAX_CU + 1];
@@ -122,7 +121,6 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = p.hq / p.hkv;
 
-    for (int i = threadIdx.x; i <= p.batch; i += blockDim.x) cu_s[i] = cu[i];
     if (threadIdx.x == 0) {
         for (int i = 0; i < N_BARS; ++i) {
             const bool eight = i == P_FULL || i == BUF_FREE || i == BUF_FREE + 1;
@@ -138,6 +136,10 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // barrier set-up and tensor-memory allocation may overlap the preceding kernel; global memory is read from here on
+    gdb_pdl_sync();
+    for (int i = threadIdx.x; i <= p.batch; i += blockDim.x) cu_s[i] = cu[i];
+    __syncthreads();
     const int n_valid = min(cu_s[p.batch], p.n_tokens);
 
     if (warp == 0) {

@@ -46,7 +46,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     size_t ldc, const T *__restrict__ bias, float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K,
                     uint32_t k_iters_per_split, int bias_mode, int *err_flag)
 {
-    gdb_pdl_sync();
     using plan = smem_plan<BN, STAGES>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
@@ -78,6 +77,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touches only shared / tensor memory: it may run while the preceding kernel finishes
+    gdb_pdl_sync();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------

@@ -49,7 +49,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                  float *__restrict__ colsum_partial)
 {
     static_assert(!COLSUM || SPLITK, "column sums ride on the split-K (FP32 partial) output path");
-    gdb_pdl_sync();
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
     unsigned char *staging = smem + PSTAGES * P_STAGE_BYTES;
@@ -90,6 +89,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     cluster_sync_all();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touches only shared / tensor memory: it may run while the preceding kernel finishes
+    gdb_pdl_sync();
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs, own operand halves) ----------------
