@@ -56,6 +56,28 @@ def test_train_steps_track_oracle(variant):
             np.testing.assert_allclose(host(prm).reshape(-1), ref.p[name].numpy().reshape(-1), atol=2e-3, rtol=2e-2, err_msg=name)
 
 
+def test_bf16_train_steps_track_oracle():
+    """BF16 storage (the scaled configuration's dtype), head_dim 128: three steps of the native driver against the oracle
+    with BF16 rounding points; loss within 1 %, same loss-scale trajectory, updated weights within BF16 tolerance."""
+    cfg = small_cfg(dtype=abi.BF16, n_heads=1, head_dim=128, dropout_p=0.1)
+    tc = g.TrainConfig.baseline()
+    hp = g.init_params(cfg, seed=23)
+    ref = OG.OracleGptLm(OG.config_from(cfg), hp)
+    otc = OG.train_config_from(tc)
+    with pkg.runtime.Context(params_bytes=64 << 20, state_bytes=128 << 20, scratch_bytes=1 << 30) as ctx:
+        model = g.GptLm(ctx, cfg, hp)
+        trainer = g.NativeTrainer(model, tc)
+        for step in range(3):
+            b = g.synthetic_batch(cfg, n_seqs=5, min_len=4, max_len=64, seed=700 + step, pad_to=64)
+            got = float(trainer.train_batch(b).read()[()])
+            want = ref.train_step(b.input_ids, b.targets, b.positions, b.cu_seqlens, step + 1, otc)
+            assert abs(got - want["loss"]) <= 1e-2 * abs(want["loss"]), (step, got, want["loss"])
+            s = trainer.scaler.sync()
+            assert s["scale"] == want["scale"] and bool(s["last_found_inf"]) == want["found_inf"]
+        for name, prm in model.params.items():
+            np.testing.assert_allclose(host(prm).reshape(-1), ref.p[name].numpy().reshape(-1), atol=1.6e-2, rtol=3e-2, err_msg=name)
+
+
 def test_fifty_seeded_steps_track_the_oracle_loss_and_scaler_trajectory():
     """Stated bound for the whole path: over 50 seeded steps (dropout masks identical by construction, learning rate
     3e-3 so that the loss really moves) the mean loss of every window of 10 steps stays within 2 % of the oracle's,
