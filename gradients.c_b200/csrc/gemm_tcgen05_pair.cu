@@ -10,10 +10,11 @@
 // k-slice) are dealt round-robin to the clusters. Tensor memory holds two accumulators of 256
 // columns, so the MMA issuer starts the next unit while the epilogue warps drain the previous one.
 //
-// Roles per CTA (192 threads): warp 0 = TMA producer for this CTA's operand halves (completion
+// Roles per CTA (320 threads): warp 0 = TMA producer for this CTA's operand halves (completion
 // bytes of both CTAs are signalled on the leader CTA's "full" barrier); warp 1 = tensor-memory
 // allocation, and in the leader CTA the MMA issuer for the pair (tcgen05.commit multicasts the
-// "stage free" and "accumulator ready" arrivals to both CTAs); warps 2-5 = epilogue: tcgen05.ld,
+// "stage free" and "accumulator ready" arrivals to both CTAs); warps 2-9 = epilogue (two warps per
+// tensor-memory lane quadrant, each draining half of the tile's columns): tcgen05.ld,
 // bias add and rounding in registers, 128-byte-swizzled staging in shared memory, TMA tile
 // stores (clipped at the matrix edges by the tensor map).
 //
@@ -26,12 +27,14 @@ namespace {
 using namespace gdb_t5;
 
 constexpr int PBN = 256;         // tile columns of the pair
-constexpr int PSTAGES = 6;
+constexpr int PSTAGES = 5;
+constexpr int P_EPI_WARPS = 8;   // two warps per tensor-memory lane quadrant, each drains half of the tile columns
+constexpr int P_THREADS = 32 * (2 + P_EPI_WARPS);
 constexpr int P_A_BYTES = BM * BK * 2;
 constexpr int P_B_BYTES = (PBN / 2) * BK * 2;
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_STAGING_PER_WARP = 2 * 4096;   // two 32-row x 128-byte buffers
-constexpr int P_STAGING_BYTES = 4 * P_STAGING_PER_WARP;
+constexpr int P_STAGING_BYTES = P_EPI_WARPS * P_STAGING_PER_WARP;
 constexpr int P_SMEM_TOTAL = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 256 + 1024;
 constexpr int P_SMEM_TOTAL_COLSUM = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 1024 + 1024 + 1024;   // barriers padded to 1 KB, ones tile, alignment slack
 
@@ -42,7 +45,7 @@ constexpr int P_SMEM_TOTAL_COLSUM = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 
 // accumulator (256 columns) plus the 16 column-sum columns, so units are not overlapped (split-K launches run about one
 // unit per CTA pair anyway).
 template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(P_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const T *__restrict__ bias, uint32_t M, uint32_t N, uint32_t K,
                  uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t k_iters_per_split, int bias_mode, int *err_flag,
@@ -77,7 +80,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull0 + 8 * b, 1);
-            mbar_init(tempty0 + 8 * b, 8);   // four epilogue warps in each of the two CTAs
+            mbar_init(tempty0 + 8 * b, 2 * P_EPI_WARPS);   // the epilogue warps of the two CTAs
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -183,8 +186,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5 own tensor-memory lane quadrants 2,3,0,1 ----------------
-        const int quad = warp & 3;
+        // ---------------- epilogue: warps 2..9; warps w and w + 4 share lane quadrant w & 3 and split the columns ----------------
+        const int quad = warp & 3, chalf = (warp - 2) >> 2;
         unsigned char *my_stage = staging + (warp - 2) * P_STAGING_PER_WARP;
         const uint32_t tempty_leader = mapa_shared(tempty0, 0);
         uint32_t unit_idx = 0, store_cnt = 0;
@@ -200,21 +203,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             tcgen05_fence_after();
             const uint32_t row0 = tm * 2 * BM + rank * BM + quad * 32;
             const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * PBN;
-            if (COLSUM && tn == 0U) {
+            if (COLSUM && tn == 0U && chalf == 0) {
                 uint32_t cs[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + PBN, cs);   // every column holds the row's sum
                 const uint32_t row = row0 + lane;
                 if (row < M) colsum_partial[(size_t)z * M + row] = __uint_as_float(cs[0]);
             }
+            constexpr int NCH = PBN / CHUNK_COLS / 2;   // chunks per warp
 #pragma unroll 1
-            for (int c = 0; c < PBN / CHUNK_COLS; ++c) {
+            for (int c = chalf * NCH; c < (chalf + 1) * NCH; ++c) {
                 uint32_t v0[32], v1[32];
                 tmem_ld_32x32b_x32_nowait(tbase + c * CHUNK_COLS, v0);
                 if (!SPLITK) {
                     tmem_ld_32x32b_x32_nowait(tbase + c * CHUNK_COLS + 32, v1);
                 }
                 tmem_ld_wait();
-                if (c == PBN / CHUNK_COLS - 1) {
+                if (c == (chalf + 1) * NCH - 1) {
                     // the accumulator has been copied out: hand the buffer back to the MMA issuer
                     tcgen05_fence_before();
                     __syncwarp();
@@ -287,7 +291,7 @@ int max_clusters(gd_backend *be, const void *kern, int smem_bytes)
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3((unsigned)be->sm_count & ~1U);
-    cfg.blockDim = dim3(192);
+    cfg.blockDim = dim3(P_THREADS);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
@@ -332,7 +336,7 @@ gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see gdb_pdl_sync()
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.gridDim = dim3(2U * (units < (uint32_t)usable ? units : (uint32_t)usable));
-    cfg.blockDim = dim3(192);
+    cfg.blockDim = dim3(P_THREADS);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = be->stream;
     cfg.attrs = attr;
