@@ -179,6 +179,38 @@ void launch_portable(gd_backend *be, int ta, int tb, const void *a, size_t lda, 
 
 }  // namespace
 
+namespace {
+// Brackets one contraction with a pair of events when GEMM profiling is enabled (gdb200_gemm_profile_enable).
+struct profile_scope {
+    gd_backend *be;
+    int slot;
+    profile_scope(gd_backend *b, double flops, double bytes) : be(b), slot(-1)
+    {
+        gdb_gemm_profile *p = g_profile;
+        if (p == nullptr || !p->enabled || p->used >= gdb_gemm_profile::CAP) {
+            return;
+        }
+        if (p->used >= p->created) {
+            if (cudaEventCreate(&p->start[p->created]) != cudaSuccess || cudaEventCreate(&p->stop[p->created]) != cudaSuccess) {
+                return;
+            }
+            p->created += 1;
+        }
+        slot = p->used++;
+        p->flops += flops;
+        p->bytes += bytes;
+        cudaEventRecord(p->start[slot], be->stream);
+    }
+    ~profile_scope()
+    {
+        if (slot >= 0) {
+            cudaEventRecord(g_profile->stop[slot], be->stream);
+        }
+    }
+};
+
+}  // namespace
+
 // x: [M, K] (or [K, M] when ta), w: [K, N] (or [N, K] when tb), y: [M, N].
 gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb, const gd_backend_matrix_view *x,
                             const gd_backend_matrix_view *w, const gd_backend_vector_view *bias,
@@ -214,33 +246,7 @@ gd_status gdb_gemm_dispatch(gd_backend *be, int ta, int tb, const gd_backend_mat
     const void *ap = x->buffer->dptr + x->offset;
     const void *wp = w->buffer->dptr + w->offset;
     void *cp = y->buffer->dptr + y->offset;
-    struct profile_scope {
-        gd_backend *be;
-        int slot;
-        profile_scope(gd_backend *b, double flops, double bytes) : be(b), slot(-1)
-        {
-            gdb_gemm_profile *p = g_profile;
-            if (p == nullptr || !p->enabled || p->used >= gdb_gemm_profile::CAP) {
-                return;
-            }
-            if (p->used >= p->created) {
-                if (cudaEventCreate(&p->start[p->created]) != cudaSuccess || cudaEventCreate(&p->stop[p->created]) != cudaSuccess) {
-                    return;
-                }
-                p->created += 1;
-            }
-            slot = p->used++;
-            p->flops += flops;
-            p->bytes += bytes;
-            cudaEventRecord(p->start[slot], be->stream);
-        }
-        ~profile_scope()
-        {
-            if (slot >= 0) {
-                cudaEventRecord(g_profile->stop[slot], be->stream);
-            }
-        }
-    } scope(be, 2.0 * M * N * K, (double)es * ((double)M * K + (double)K * N + (double)M * N));
+    profile_scope scope(be, 2.0 * M * N * K, (double)es * ((double)M * K + (double)K * N + (double)M * N));
     if (be->gemm_mode != 1 && be->gemm_mode != 2 && !ta && M <= 64U) {
         gd_status st = gdb_gemm_skinny(be, tb, dt, ap, x->row_bytes, wp, w->row_bytes, cp, y->row_bytes, bp, bias_mode, M, N, K);
         if (st != GD_ERR_UNSUPPORTED) {
@@ -410,6 +416,8 @@ gd_status gdb200_matmul_tn_colsum(gd_backend *be, const gd_backend_matrix_view *
     }
     if (gdb_is_float_dtype(dt) && mv_ok(x, es) && mv_ok(w, es) && mv_ok(y, es) && x->rows == w->rows && y->rows == x->cols && y->cols == w->cols &&
         gdb_range_ok(colsum->buffer, colsum->offset, (size_t)colsum->length * es)) {
+        profile_scope scope(be, 2.0 * x->cols * w->cols * x->rows,
+                            (double)es * ((double)x->rows * x->cols + (double)x->rows * w->cols + (double)x->cols * w->cols));
         const gd_status st = gdb_gemm_tcgen05_tn_colsum(be, dt, x->buffer->dptr + x->offset, x->row_bytes, w->buffer->dptr + w->offset, w->row_bytes,
                                                         y->buffer->dptr + y->offset, y->row_bytes, colsum->buffer->dptr + colsum->offset,
                                                         x->cols, w->cols, x->rows);
