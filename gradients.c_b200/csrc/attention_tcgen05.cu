@@ -7,7 +7,8 @@
 //   allowed(i, j)  <=>  seg_start(i) <= j <= i  and  (window == 0 or i - j < window)
 // (src/ops/sdpa_varlen/metal_sdpa_varlen.metal:30-55, prefix 0), so a tile may span sequences.
 //
-// The kernel is persistent: two CTAs per SM stay resident and walk the item list, so tensor-memory
+// The kernel is persistent: two CTAs per SM stay resident and draw items from a launch-wide ticket counter
+// (an item costs 1-5 key tiles, so a fixed deal leaves CTAs up to 1.6x out of balance), so tensor-memory
 // allocation, barrier set-up and the cu_seqlens copy are paid once per CTA, and the TMA producer and
 // the MMA issuer run ahead into the next item while the softmax warps finish the current one (at the
 // model's sequence lengths an item has only 1-5 key tiles).
@@ -84,17 +85,6 @@ __device__ __forceinline__ void item_range(const int *cu_s, const attn5_params &
     }
 }
 
-// Named barrier for the two warps that share a tensor-memory lane quadrant. The id is an immediate so
-// that the CTA reserves 5 of the SM's 16 hardware barriers, not all of them.
-__device__ __forceinline__ void pair_barrier_sync(int quad)
-{
-    switch (quad) {
-    case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
-    case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
-    case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
-    default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
-    }
-}
 __device__ __forceinline__ void mbar_arrive_local(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -104,17 +94,20 @@ template <typename T>
 __global__ void __launch_bounds__(A_THREADS, 2)
 attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                  const __grid_constant__ CUtensorMap tma_v, T *__restrict__ out,
-                 const int *__restrict__ cu, float *__restrict__ stats, attn5_params p, int *err_flag)
+                 const int *__restrict__ cu, float *__restrict__ stats, attn5_params p, int *err_flag, unsigned *work_counter,
+                 unsigned *done_counter)
 {
     using plan = attn5_plan;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int cu_s[A_MAX_CU + 1];
     __shared__ float xch[2][2][A_BQ];   // [tile parity][column half][row]: row maxima of the two column halves
     __shared__ float xsum[2][2][A_BQ];  // [item parity][column half][row]: partial sums of exp, exchanged once per item
+    __shared__ int sched_item[4];       // work items handed out by the producer thread (-1: no more work)
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + plan::OFF_BAR);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
-    enum { Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 7, S_FULL = 8, P_FULL = 10, P_EMPTY = 11, O_FULL = 12, BUF_FREE = 14, N_BARS = 16 };
+    enum { Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 7, S_FULL = 8, P_FULL = 10, P_EMPTY = 11, O_FULL = 12, BUF_FREE = 14,
+           SCHED_FULL = 16, SCHED_EMPTY = 20, PAIR = 24, N_BARS = 28 };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + N_BARS);
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8U * (uint32_t)i; };
 
@@ -124,7 +117,9 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     if (threadIdx.x == 0) {
         for (int i = 0; i < N_BARS; ++i) {
             const bool eight = i == P_FULL || i == BUF_FREE || i == BUF_FREE + 1;
-            mbar_init(bar(i), eight ? 8U : 1U);
+            // schedule slots are released by the MMA thread and the 8 softmax warps; pair barriers by 2 warps
+            const uint32_t count = eight ? 8U : (i >= SCHED_EMPTY && i < SCHED_EMPTY + 4 ? 9U : (i >= PAIR ? 2U : 1U));
+            mbar_init(bar(i), count);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -145,9 +140,30 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t g = 0, iq = 0;   // running key-tile and item counters (items with at least one tile)
+            uint32_t g = 0, iq = 0, si = 0;   // running key-tile, item-with-tiles and schedule counters
             bool ok = true;
-            for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+            // Draws a ticket from the launch-wide counter and publishes the item to the other roles of this CTA.
+            // Tickets count down the item list: the query tiles past the last token (no key tiles) come first, and
+            // within a sequence the later query tiles (more key tiles) go before the earlier ones.
+            auto draw = [&]() -> int {
+                const uint32_t slot = si & 3U;
+                if (!mbar_wait(bar(SCHED_EMPTY + slot), ((si >> 2) & 1U) ^ 1U)) {
+                    atomicExch(err_flag, 310);
+                    ok = false;
+                    return -1;
+                }
+                const int ticket = (int)atomicAdd(work_counter, 1U);
+                const int it = ticket < p.n_items ? p.n_items - 1 - ticket : -1;
+                sched_item[slot] = it;
+                mbar_arrive_local(bar(SCHED_FULL + slot));
+                ++si;
+                return it;
+            };
+            // The schedule runs one item ahead of the loads: the MMA thread looks up the next item right after the
+            // last S of the current one, while this thread may still wait for a V slot that only a later P V frees.
+            int item = draw(), next = -1;
+            for (; ok && item >= 0; item = next) {
+                next = draw();
                 const int q0 = (item / p.hq) * A_BQ, h = item % p.hq, hk = h / group;
                 int kv_begin, n_tiles;
                 item_range(cu_s, p, n_valid, q0, &kv_begin, &n_tiles);
@@ -187,17 +203,26 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
             const uint32_t q_base = smem_u32(smem), p_base = smem_u32(smem + plan::OFF_P), v_base = smem_u32(smem + plan::OFF_V);
             // Walks the same (item, tile) sequence twice: `s_*` is the cursor of the S issue (one tile ahead),
             // `pv_g` the cursor of the P V issue.
-            int s_item = blockIdx.x, s_t = 0, s_tiles = 0;
-            uint32_t s_g = 0, s_iq = 0;
+            int s_item = -1, s_t = 0, s_tiles = 0;
+            uint32_t s_g = 0, s_iq = 0, s_si = 0;
             bool ok = true;
-            auto s_seek = [&]() {   // position the S cursor on the next item that has tiles
-                while (s_item < p.n_items) {
+            auto s_seek = [&]() {   // position the S cursor on the next scheduled item that has tiles
+                for (;;) {
+                    const uint32_t slot = s_si & 3U;
+                    if (!mbar_wait(bar(SCHED_FULL + slot), (s_si >> 2) & 1U)) {
+                        atomicExch(err_flag, 311);
+                        s_item = -1;
+                    } else {
+                        s_item = *reinterpret_cast<volatile int *>(&sched_item[slot]);
+                        mbar_arrive_local(bar(SCHED_EMPTY + slot));
+                        ++s_si;
+                    }
+                    s_tiles = 0;
+                    if (s_item < 0) return;
                     int kb;
                     item_range(cu_s, p, n_valid, (s_item / p.hq) * A_BQ, &kb, &s_tiles);
                     if (s_tiles > 0) return;
-                    s_item += gridDim.x;
                 }
-                s_tiles = 0;
             };
             auto issue_s = [&]() -> bool {   // S[s_g] = Q K^T for tile s_t of item s_item
                 const uint32_t ks = s_g & 1U, b = s_g & 1U;
@@ -227,7 +252,6 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
                     tcgen05_commit(bar(Q_EMPTY));
                     ++s_iq;
                     s_t = 0;
-                    s_item += gridDim.x;
                     s_seek();
                 }
                 return true;
@@ -281,7 +305,23 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
                 if (lane == 0) atomicExch(err_flag, code);
             }
         };
-        for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
+        // bounded rendezvous of the two warps of a lane quadrant (mbarrier with two arrivals per phase)
+        uint32_t pair_phase = 0;
+        auto pair_sync = [&]() {
+            __syncwarp();
+            if (lane == 0) mbar_arrive_local(bar(PAIR + quad));
+            wait_or_die(PAIR + quad, pair_phase & 1U, 312);
+            ++pair_phase;
+        };
+        for (uint32_t si = 0;; ++si) {
+            // next scheduled item; a dead warp stops consuming (its partner then gives up at the next rendezvous)
+            const uint32_t slot = si & 3U;
+            wait_or_die(SCHED_FULL + slot, (si >> 2) & 1U, 313);
+            if (dead) break;
+            const int item = *reinterpret_cast<volatile int *>(&sched_item[slot]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive_local(bar(SCHED_EMPTY + slot));
+            if (item < 0) break;
             const int q0 = (item / p.hq) * A_BQ, h = item % p.hq, qi = q0 + r;
             int kv_begin, n_tiles;
             item_range(cu_s, p, n_valid, q0, &kv_begin, &n_tiles);
@@ -334,7 +374,7 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
                 }
                 // exchange the row maximum with the thread that owns the other 64 columns
                 xch[g & 1U][half][r] = tmax;
-                pair_barrier_sync(quad);
+                pair_sync();
                 tmax = fmaxf(tmax, xch[g & 1U][half ^ 1][r]);
                 if (t >= 1) accumulate_o(g - 1U);
                 const float m_new = fmaxf(m, tmax * sl2);
@@ -388,7 +428,7 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
             if (n_tiles > 0) accumulate_o(g - 1U);   // also implies that every MMA of this item has completed
             // ---- total row sum, normalise, store this thread's 32 output columns (two full 32-byte sectors) ----
             xsum[n_item & 1U][half][r] = l;
-            pair_barrier_sync(quad);
+            pair_sync();
             const float l_tot = l + xsum[n_item & 1U][half ^ 1][r];
             ++n_item;
             const float inv = (!dead && l_tot > 0.0f) ? 1.0f / l_tot : 0.0f;
@@ -415,6 +455,14 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     __syncwarp();
     tcgen05_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) {
+        // the CTA that leaves last puts the launch-wide counters back to zero for the next launch
+        __threadfence();
+        if (atomicAdd(done_counter, 1U) == gridDim.x - 1U) {
+            *work_counter = 0U;
+            *done_counter = 0U;
+        }
+    }
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)plan::TMEM_COLS) : "memory");
     }
@@ -444,7 +492,8 @@ gd_status launch_fwd(gd_backend *be, const gdb_flash_args *a)
     }
     attn5_params p = {a->n_tokens, a->batch, a->hq, a->hkv, a->window, ((a->n_tokens + A_BQ - 1) / A_BQ) * a->hq, a->scale};
     const unsigned grid = (unsigned)(p.n_items < resident ? p.n_items : resident);
-    gdb_launch(kern, grid, A_THREADS, plan::TOTAL, be->stream, mq, mk, mv, (T *)a->out_or_dq, a->cu, a->stats, p, be->err_flag);
+    gdb_launch(kern, grid, A_THREADS, plan::TOTAL, be->stream, mq, mk, mv, (T *)a->out_or_dq, a->cu, a->stats, p, be->err_flag,
+               gdb_tickets(be) + (GDB_TICKET_WORDS - 2), gdb_tickets(be) + (GDB_TICKET_WORDS - 3));
     return gdb_launched(be, "attn5_forward");
 }
 
