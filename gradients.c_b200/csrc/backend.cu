@@ -411,6 +411,37 @@ gd_status gd_backend_download(gd_backend *be, gd_backend_buffer *buffer, size_t 
     return e == cudaSuccess ? GD_OK : gdb_fail(be, e, "download");
 }
 
+// Stream-ordered copies between page-locked host memory and a buffer: enqueued behind the work already
+// submitted and not waited for, so the host can prepare step k + 1 while step k runs. This is the device half of
+// the reference's data-slot ring, where loader threads fill the next slot's host span while the device still
+// reads the previous one and a fence guards reuse (src/core/memory.c:1149-1208, src/dataset/dataloader.c:487-492).
+// The host range must stay untouched (upload) or unread (download) until a fence recorded after the call completes.
+gd_status gdb200_upload_async(gd_backend *be, gd_backend_buffer *buffer, size_t offset, const void *pinned_src, size_t nbytes)
+{
+    if (be == NULL || (pinned_src == NULL && nbytes != 0U) || !gdb_range_ok(buffer, offset, nbytes)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (nbytes == 0U) {
+        return GD_OK;
+    }
+    cudaSetDevice(be->device);
+    cudaError_t e = cudaMemcpyAsync(buffer->dptr + offset, pinned_src, nbytes, cudaMemcpyHostToDevice, be->stream);
+    return e == cudaSuccess ? GD_OK : gdb_fail(be, e, "upload_async");
+}
+
+gd_status gdb200_download_async(gd_backend *be, gd_backend_buffer *buffer, size_t offset, void *pinned_dst, size_t nbytes)
+{
+    if (be == NULL || (pinned_dst == NULL && nbytes != 0U) || !gdb_range_ok(buffer, offset, nbytes)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (nbytes == 0U) {
+        return GD_OK;
+    }
+    cudaSetDevice(be->device);
+    cudaError_t e = cudaMemcpyAsync(pinned_dst, buffer->dptr + offset, nbytes, cudaMemcpyDeviceToHost, be->stream);
+    return e == cudaSuccess ? GD_OK : gdb_fail(be, e, "download_async");
+}
+
 gd_status gd_backend_fill(gd_backend *be, gd_backend_buffer *buffer, size_t offset, size_t count, size_t elem_size, uint32_t pattern)
 {
     if (be == NULL || elem_size == 0U || elem_size > 4U || count > SIZE_MAX / elem_size ||

@@ -145,6 +145,16 @@ class GptBatch(C.Structure):
                 ("cu_seqlens_offset", SZ), ("n_tokens", C.c_int64), ("n_cu", C.c_int64)]
 
 
+class GptCompactBatch(C.Structure):
+    _fields_ = [("buffer", P), ("tokens_offset", SZ), ("segment_lengths_offset", SZ), ("record_offsets_offset", SZ),
+                ("input_ids_offset", SZ), ("targets_offset", SZ), ("positions_offset", SZ), ("cu_seqlens_offset", SZ),
+                ("status_offset", SZ), ("n_records", C.c_int64), ("n_segments", C.c_int64), ("context_length", I32_T),
+                ("vocab_size", I32_T), ("pad_id", I32_T), ("im_start_id", I32_T), ("im_end_id", I32_T)]
+
+
+COMPACT_BAD_TOKEN, COMPACT_BAD_LENGTH, COMPACT_BAD_COVER = 1, 2, 4
+
+
 class GptDecodeState(C.Structure):
     _fields_ = [("cache_buffer", P), ("io_buffer", P), ("k_cache_offset", SZ * GPT_MAX_LAYERS), ("v_cache_offset", SZ * GPT_MAX_LAYERS),
                 ("tokens_offset", SZ), ("positions_offset", SZ), ("out_tokens_offset", SZ), ("step_counter_offset", SZ),
@@ -260,12 +270,15 @@ PROTOTYPES = {
     "gdb200_flush_l2": (_ST, [P]),
     "gdb200_pinned_alloc": (P, [SZ]),
     "gdb200_pinned_free": (None, [P]),
+    "gdb200_upload_async": (_ST, [P, P, SZ, P, SZ]),
+    "gdb200_download_async": (_ST, [P, P, SZ, P, SZ]),
     "gdb200_gemm_profile_enable": (None, [P, C.c_int]),
     "gdb200_gemm_profile_read": (_ST, [P, C.POINTER(U64), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "gdb200_matmul_nt_bias": (_ST, [P, MV, MV, VV, MV]),
     "gdb200_embedding_backward_static": (_ST, [P, P, P, P, U64, U64, U64, U32]),
     "gdb200_embedding_backward_static_error": (C.c_char_p, []),
     "gdb200_embedding_backward_static_max_elems": (U64, []),
+    "gdb200_gpt_compact_expand": (_ST, [P, C.POINTER(GptCompactBatch)]),
     "gdb200_gpt_train_step": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptBatch), U64, F, C.POINTER(SZ), C.POINTER(SZ)]),
     "gdb200_matmul_tn_colsum": (_ST, [P, MV, MV, MV, VV]),
     "gdb200_argmax_rows": (_ST, [P, TV, F, TV]),

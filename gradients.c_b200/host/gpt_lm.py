@@ -17,7 +17,7 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import abi, ops
-from .abi import F16, BF16, F32, I32
+from .abi import F16, BF16, F32, I32, U16, BackendError
 from .optim import AdamW, AdamwConfig, AmpConfig, AmpScaler, gd_backward_amp
 from .runtime import Context, Tensor
 
@@ -131,6 +131,37 @@ class Batch:
         return int(self.input_ids.nbytes + self.targets.nbytes + self.positions.nbytes + self.cu_seqlens.nbytes)
 
 
+@dataclass
+class CompactBatch:
+    """A batch of compact records as the reference stores them on disk (examples/gpt_lm/main.c:835-857): u16
+    tokens [n_records, context_length + 1], the I32 lengths of the documents packed into each record, one list
+    after another, and the index of each record's first length (record_offsets[n_records] = number of segments)."""
+    tokens: np.ndarray
+    segment_lengths: np.ndarray
+    record_offsets: np.ndarray
+    im_start_id: int = 1
+    im_end_id: int = 2
+    real_tokens: int = 0
+
+    @property
+    def h2d_bytes(self) -> int:
+        return int(self.tokens.nbytes + self.segment_lengths.nbytes + self.record_offsets.nbytes)
+
+
+def synthetic_compact_batch(cfg: GptConfig, n_records: int, seed: int, max_segments: int = 6) -> CompactBatch:
+    """Records of context_length + 1 uniform token ids, each cut into 1..max_segments documents at random places."""
+    rng = np.random.default_rng(seed)
+    ctx = cfg.context_length
+    tokens = rng.integers(0, cfg.vocab_size, size=(n_records, ctx + 1)).astype(np.uint16)
+    lens, offs = [], [0]
+    for _ in range(n_records):
+        n = int(rng.integers(1, min(max_segments, ctx) + 1))
+        cuts = np.sort(rng.choice(np.arange(1, ctx), size=n - 1, replace=False)) if n > 1 else np.zeros(0, dtype=np.int64)
+        lens.extend(np.diff(np.concatenate([[0], cuts, [ctx]])).tolist())
+        offs.append(len(lens))
+    return CompactBatch(tokens, np.asarray(lens, dtype=np.int32), np.asarray(offs, dtype=np.int32), real_tokens=n_records * ctx)
+
+
 def synthetic_batch(cfg: GptConfig, n_seqs: int, min_len: int, max_len: int, seed: int, pad_to: int = 0,
                     lengths: Optional[Sequence[int]] = None) -> Batch:
     """Packed sequences with lengths uniform in [min_len, max_len] and ids uniform over the
@@ -233,12 +264,53 @@ class GptLm:
         return ops.gd_lm_cross_entropy_softcapped_bias_ignore(ctx, final, self.lm_head_weight(), p["lm_head_bias"], target_ids,
                                                               cfg.logits_softcap, cfg.pad_token_id)
 
-    def upload_batch(self, batch: Batch):
+    def upload_batch(self, batch: Batch, stream_ordered: bool = False):
+        """Places the batch in the data slot. `stream_ordered`: the arrays are page-locked and are copied behind
+        the work already submitted, without a wait (they must stay unchanged until the step's fence completes)."""
         ctx = self.ctx
+        if isinstance(batch, CompactBatch):
+            return self.expand_compact_batch(batch, stream_ordered)[:4]
+        if stream_ordered:
+            out = []
+            for a, name in ((batch.input_ids, "input_ids"), (batch.targets, "targets"), (batch.positions, "positions"), (batch.cu_seqlens, "cu_seqlens")):
+                t = ctx.empty(ctx.data, I32, a.shape, name)
+                t.write_async(a)
+                out.append(t)
+            return tuple(out)
         return (ctx.from_numpy(ctx.data, I32, batch.input_ids, "input_ids"),
                 ctx.from_numpy(ctx.data, I32, batch.targets, "targets"),
                 ctx.from_numpy(ctx.data, I32, batch.positions, "positions"),
                 ctx.from_numpy(ctx.data, I32, batch.cu_seqlens, "cu_seqlens"))
+
+    def expand_compact_batch(self, cb: CompactBatch, stream_ordered: bool = False, check: bool = True):
+        """Copies the compact records into the data slot and expands them on the device into (input_ids, targets,
+        positions, cu_seqlens, status). `check` reads the status word back (a host wait) and raises on input the
+        reference's transform rejects (examples/gpt_lm/main.c:934-959)."""
+        import ctypes as C
+        ctx, cfg = self.ctx, self.cfg
+        n_rec, n_seg = int(cb.tokens.shape[0]), int(cb.segment_lengths.size)
+        assert cb.tokens.dtype == np.uint16 and cb.tokens.shape == (n_rec, cfg.context_length + 1)
+        src = []
+        for a, dt, name in ((cb.tokens.reshape(-1), U16, "compact.tokens"), (cb.segment_lengths, I32, "compact.segment_lengths"),
+                            (cb.record_offsets, I32, "compact.record_offsets")):
+            t = ctx.empty(ctx.data, dt, a.shape, name)
+            if stream_ordered:
+                t.write_async(a)
+            else:
+                t.write(a)
+            src.append(t)
+        n_tok = n_rec * cfg.context_length
+        ids, tgt, pos = (ctx.empty(ctx.data, I32, (n_tok,), n) for n in ("input_ids", "targets", "positions"))
+        cu = ctx.empty(ctx.data, I32, (n_seg + 1,), "cu_seqlens")
+        status = ctx.empty(ctx.data, I32, (1,), "compact.status")
+        b = abi.GptCompactBatch(ids.buffer, src[0].offset, src[1].offset, src[2].offset, ids.offset, tgt.offset, pos.offset, cu.offset,
+                                status.offset, n_rec, n_seg, cfg.context_length, cfg.vocab_size, cfg.pad_token_id, cb.im_start_id, cb.im_end_id)
+        ctx.check(ctx.lib.gdb200_gpt_compact_expand(ctx.backend, C.byref(b)), "gdb200_gpt_compact_expand")
+        if check and not stream_ordered:
+            flags = int(status.read()[0])
+            if flags != 0:
+                raise BackendError(abi.GD_ERR_INVALID_ARGUMENT, "gdb200_gpt_compact_expand", f"compact records rejected (flags {flags})")
+        return ids, tgt, pos, cu, status
 
     # ---- KV-cache generation ----
     def alloc_kv_cache(self, batch: int, capacity: int) -> None:
@@ -336,19 +408,24 @@ class Trainer:
         self.global_step = 0
         self.dp = dp
 
-    def train_batch(self, batch: Optional[Batch], lr: Optional[float] = None, device_batch=None) -> Tensor:
+    def train_batch(self, batch: Optional[Batch], lr: Optional[float] = None, device_batch=None, loss_out=None) -> Tensor:
         """One training step. `device_batch` = (ids, targets, positions, cu_seqlens) tensors that are
-        already resident on the device; otherwise the host batch is uploaded into the data slot."""
+        already resident on the device; otherwise the host batch is uploaded into the data slot.
+        `loss_out` (a page-locked FP32 array of one element) selects the pipelined form: the batch, which must be
+        page-locked too, is copied in stream order, the loss is copied to `loss_out` in stream order, and nothing
+        is waited for; the value is valid once the step's fence has completed (Context.wait_steps)."""
         ctx, model = self.ctx, self.model
         ctx.begin_step()
         self.optimizer.zero_grad()
-        ids, tgt, pos, cu = device_batch if device_batch is not None else model.upload_batch(batch)
+        ids, tgt, pos, cu = device_batch if device_batch is not None else model.upload_batch(batch, loss_out is not None)
         loss = model.forward(ids, tgt, pos, cu, self.global_step + 1)
         gd_backward_amp(ctx, loss, self.scaler)
         inv_override = None
         if self.dp is not None:
             inv_override = self.dp.reduce_gradients(self.optimizer, self.scaler)
         self.optimizer.step_amp_clip_lr(self.scaler, self.cfg.lr if lr is None else lr, self.cfg.grad_clip_norm, inv_override)
+        if loss_out is not None:
+            loss.read_async(loss_out)
         ctx.end_step()
         self.global_step += 1
         return loss
@@ -389,10 +466,10 @@ class NativeTrainer(Trainer):
             s.weight_decay[i] = slot.weight_decay
         self.spec = s
 
-    def train_batch(self, batch: Optional[Batch], lr: Optional[float] = None, device_batch=None) -> Tensor:
+    def train_batch(self, batch: Optional[Batch], lr: Optional[float] = None, device_batch=None, loss_out=None) -> Tensor:
         C, ctx = self._C, self.ctx
         ctx.begin_step()
-        ids, tgt, pos, cu = device_batch if device_batch is not None else self.model.upload_batch(batch)
+        ids, tgt, pos, cu = device_batch if device_batch is not None else self.model.upload_batch(batch, loss_out is not None)
         assert ids.arena is tgt.arena is pos.arena is cu.arena
         b = abi.GptBatch(ids.buffer, ids.offset, tgt.offset, pos.offset, cu.offset, ids.count, cu.count)
         loss_off, used = C.c_size_t(), C.c_size_t()
@@ -401,9 +478,12 @@ class NativeTrainer(Trainer):
         ctx.check(st, "gdb200_gpt_train_step")
         ctx.scratch.top = used.value
         ctx.scratch.high_water = max(ctx.scratch.high_water, used.value)
+        loss = Tensor(ctx, ctx.scratch, loss_off.value, F32, ())
+        if loss_out is not None:
+            loss.read_async(loss_out)
         ctx.end_step()
         self.global_step += 1
-        return Tensor(ctx, ctx.scratch, loss_off.value, F32, ())
+        return loss
 
 
 def greedy_generate(model: GptLm, prompts: np.ndarray, new_tokens: int, capacity: int) -> np.ndarray:

@@ -138,6 +138,19 @@ class Tensor:
         self.ctx.check(self.ctx.lib.gd_backend_upload(self.ctx.backend, self.buffer, self.offset,
                                                       a.ctypes.data_as(C.c_void_p), a.nbytes), "upload")
 
+    def write_async(self, pinned: np.ndarray) -> None:
+        """Stream-ordered upload from page-locked memory (Context.pinned_copy); not waited for. `pinned` must
+        keep its contents until a fence recorded after this call has completed."""
+        assert pinned.dtype == NP_DTYPES[self.dtype] and pinned.size == self.count and pinned.flags.c_contiguous
+        self.ctx.check(self.ctx.lib.gdb200_upload_async(self.ctx.backend, self.buffer, self.offset,
+                                                        pinned.ctypes.data_as(C.c_void_p), pinned.nbytes), "upload_async")
+
+    def read_async(self, pinned_out: np.ndarray) -> None:
+        """Stream-ordered download into page-locked memory; valid once a later fence has completed."""
+        assert pinned_out.dtype == NP_DTYPES[self.dtype] and pinned_out.size == self.count and pinned_out.flags.c_contiguous
+        self.ctx.check(self.ctx.lib.gdb200_download_async(self.ctx.backend, self.buffer, self.offset,
+                                                          pinned_out.ctypes.data_as(C.c_void_p), pinned_out.nbytes), "download_async")
+
     def read(self) -> np.ndarray:
         out = np.empty(self.shape, dtype=NP_DTYPES[self.dtype])
         self.ctx.check(self.ctx.lib.gd_backend_download(self.ctx.backend, self.buffer, self.offset,
@@ -154,7 +167,11 @@ class Context:
 
     The reference keeps `scratch_slots` ring buffers and waits on the slot's fence before
     reuse (memory.c:701); with one slot that is a wait for the previous step's fence at
-    begin_step, which is what this class does.
+    begin_step, which is what this class does by default (`run_ahead` 0). With `run_ahead` = n the
+    host may enqueue up to n steps beyond the one the device is executing: begin_step then waits
+    only for the fence of step k - n. The device arenas need no ring for that, because every
+    kernel and every stream-ordered copy of step k + 1 is queued behind step k on the one in-order
+    stream; only host memory handed to write_async / read_async must be rotated by the caller.
     """
 
     def __init__(self, params_bytes: int = 256 << 20, state_bytes: int = 512 << 20,
@@ -171,7 +188,8 @@ class Context:
         self.data = Arena(self, "data", data_bytes)
         self.tape: list[Callable[[], None]] = []
         self.grad_enabled = True
-        self._fence: Optional[abi.Fence] = None
+        self._fences: list[abi.Fence] = []
+        self.run_ahead = 0
         self.in_step = False
         self.grad_ready_hook: Optional[Callable[[Tensor], None]] = None
 
@@ -187,9 +205,9 @@ class Context:
     def destroy(self) -> None:
         if getattr(self, "backend", None):
             self.flush()
-            if self._fence is not None:
-                self.lib.gd_backend_fence_destroy(C.byref(self._fence))
-                self._fence = None
+            for f in self._fences:
+                self.lib.gd_backend_fence_destroy(C.byref(f))
+            self._fences = []
             for a in (self.params, self.state, self.scratch, self.data):
                 a.destroy()
             self.lib.gd_backend_destroy(self.backend)
@@ -223,10 +241,7 @@ class Context:
     # ---- step scope (reference gd_begin_step / gd_end_step) ----
     def begin_step(self) -> None:
         assert not self.in_step
-        if self._fence is not None:
-            self.check(self.lib.gd_backend_fence_wait(C.byref(self._fence)), "fence_wait")
-            self.lib.gd_backend_fence_destroy(C.byref(self._fence))
-            self._fence = None
+        self.wait_steps(self.run_ahead)
         self.scratch.reset()
         self.data.reset()
         self.tape.clear()
@@ -237,9 +252,17 @@ class Context:
         assert self.in_step
         f = abi.Fence()
         self.check(self.lib.gd_backend_record_fence(self.backend, C.byref(f)), "record_fence")
-        self._fence = f
+        self._fences.append(f)
         self.tape.clear()
         self.in_step = False
+
+    def wait_steps(self, keep: int = 0) -> None:
+        """Waits until at most `keep` recorded steps are still in flight (oldest first)."""
+        while len(self._fences) > keep:
+            f = self._fences.pop(0)
+            st = self.lib.gd_backend_fence_wait(C.byref(f))
+            self.lib.gd_backend_fence_destroy(C.byref(f))
+            self.check(st, "fence_wait")
 
     # ---- tensors ----
     def empty(self, arena: Arena, dtype: int, shape: Sequence[int], name: str = "") -> Tensor:

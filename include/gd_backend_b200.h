@@ -371,6 +371,13 @@ void gdb200_event_destroy(void *event);
 /* Page-locked host memory for upload sources / download targets (cudaMallocHost / cudaFreeHost). */
 void *gdb200_pinned_alloc(size_t nbytes);
 void gdb200_pinned_free(void *p);
+/* Stream-ordered copies between page-locked host memory and a buffer, enqueued behind the submitted work and not
+ * waited for (gd_backend_upload / gd_backend_download are synchronous, src/core/backend.h upload/download). They
+ * are the device half of the reference's data-slot ring: the next batch is staged while the device still works on
+ * the previous one and a fence guards reuse (src/core/memory.c:1149-1208, src/dataset/dataloader.c:487-492). The
+ * host range must not be written (upload) or read (download) until a fence recorded after the call has completed. */
+gd_status gdb200_upload_async(gd_backend *backend, gd_backend_buffer *buffer, size_t offset, const void *pinned_src, size_t nbytes);
+gd_status gdb200_download_async(gd_backend *backend, gd_backend_buffer *buffer, size_t offset, void *pinned_dst, size_t nbytes);
 /* Benchmark instrumentation: bracket every dense-contraction dispatch with a CUDA event pair on
  * the backend stream; read returns the number of launches, their summed device time and the
  * algorithmic FLOPs / bytes (2MNK and one pass over each operand) accumulated since enable. */
@@ -445,6 +452,35 @@ typedef struct gdb200_gpt_batch {
  * loss (F32 scalar) is left at *loss_offset of scratch_buffer. */
 gd_status gdb200_gpt_train_step(gd_backend *backend, const gdb200_gpt_spec *spec, const gdb200_gpt_batch *batch,
                                 uint64_t step, float lr, size_t *loss_offset, size_t *scratch_used);
+
+/* Expansion of a batch of compact GPT-LM records on the device. The reference expands each record on a loader
+ * thread (examples/gpt_lm/main.c:873-970: u16 tokens[context_length + 1] and the record's I32 segment lengths ->
+ * I32 input ids, next-token targets with cross-document targets replaced by pad_id, positions restarting per
+ * segment) and its packed-sequence collate generates cu_seqlens from all lengths of the batch
+ * (src/dataset/gdds_dataset.c:2191-2224); with this entry a step uploads 2 bytes per token instead of 12.
+ * segment_lengths holds the records' length lists one after another and record_offsets[r] the index of record r's
+ * first length in it (record_offsets[n_records] = n_segments: the per-sample offsets the reference's collate
+ * keeps for a packed-sequence field, gdds_dataset.c:2181-2186). The outputs are the fields of
+ * gdb200_gpt_batch (n_tokens = n_records * context_length, n_cu = n_segments + 1). Input the reference's transform
+ * rejects with GD_ERR_INVALID_ARGUMENT is reported asynchronously: *status (I32 in the buffer) receives 0 or
+ * GDB200_COMPACT_* flags, the outputs are then unspecified but stay inside their ranges. */
+enum {
+    GDB200_COMPACT_BAD_TOKEN = 1,   /* a token id >= vocab_size (main.c:934-939) */
+    GDB200_COMPACT_BAD_LENGTH = 2,  /* a segment length <= 0 (main.c:946) */
+    GDB200_COMPACT_BAD_COVER = 4    /* the lengths of a record do not add up to context_length (main.c:946,957) */
+};
+typedef struct gdb200_gpt_compact_batch {
+    gd_backend_buffer *buffer;
+    size_t tokens_offset;           /* in:  U16 [n_records, context_length + 1] */
+    size_t segment_lengths_offset;  /* in:  I32 [n_segments] */
+    size_t record_offsets_offset;   /* in:  I32 [n_records + 1] */
+    size_t input_ids_offset, targets_offset, positions_offset;  /* out: I32 [n_records * context_length] */
+    size_t cu_seqlens_offset;       /* out: I32 [n_segments + 1] */
+    size_t status_offset;           /* out: I32 */
+    int64_t n_records, n_segments;
+    int32_t context_length, vocab_size, pad_id, im_start_id, im_end_id;
+} gdb200_gpt_compact_batch;
+gd_status gdb200_gpt_compact_expand(gd_backend *backend, const gdb200_gpt_compact_batch *batch);
 
 /* Device-side greedy sampling (no counterpart in the reference's backend ABI: the reference downloads
  * the logits and samples on the host, examples/gpt_lm/gpt_lm_shared.c:1322,1371-1442). logits [rows,

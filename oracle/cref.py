@@ -14,6 +14,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 INT_LIB = os.path.join(HERE, "c", "liboracle_int.so")
 HARNESS_LIB = os.path.join(HERE, "_ref", "ref_harness.so")
+COMPACT_LIB = os.path.join(HERE, "_ref", "ref_compact.so")
 TESTS_CUDA_DIR = os.path.join(HERE, "_ref", "tests_cuda")
 
 
@@ -66,6 +67,32 @@ class OracleInt:
 
 def harness_available() -> bool:
     return os.path.exists(HARNESS_LIB)
+
+
+def compact_available() -> bool:
+    return os.path.exists(COMPACT_LIB)
+
+
+class RefCompact:
+    """The reference's own compact-record transform (examples/gpt_lm/main.c:873-970), see
+    oracle/ref_harness/harness_compact.c."""
+
+    def __init__(self):
+        self.lib = C.CDLL(COMPACT_LIB)
+        i32, vp = C.c_int32, C.c_void_p
+        self.lib.gdref_compact_transform.restype = C.c_int
+        self.lib.gdref_compact_transform.argtypes = [vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp]
+
+    def transform(self, tokens: np.ndarray, segment_lengths, context_length: int, vocab_size: int, pad_id: int, im_start_id: int,
+                  im_end_id: int):
+        """Returns (status, input_ids, positions, target_ids); the arrays are None unless status is 0 (GD_OK)."""
+        tok = np.ascontiguousarray(tokens, dtype=np.uint16)
+        seg = np.ascontiguousarray(segment_lengths, dtype=np.int32)
+        assert tok.size == context_length + 1
+        ids, pos, tgt = (np.zeros(context_length, dtype=np.int32) for _ in range(3))
+        st = int(self.lib.gdref_compact_transform(_p(tok), context_length, _p(seg), seg.size, vocab_size, pad_id, im_start_id, im_end_id,
+                                                  _p(ids), _p(pos), _p(tgt)))
+        return (st, ids, pos, tgt) if st == 0 else (st, None, None, None)
 
 
 class RefHarness:

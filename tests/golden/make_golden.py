@@ -14,6 +14,8 @@ Sources of truth (nothing is re-derived from this repository's oracle):
     reference tree: src/ops/rms_norm/{fwd,bwd}.py (make_inputs, reference), src/ops/dropout/fwd.py
     (case_input, dropout_mask, ref_dropout). src/ops/linear/{fwd,bwd}.py compute their reference
     inline in run_case (fwd.py:147-156, bwd.py:171-190); those lines are transcribed here.
+  * The reference's compact-record transform (examples/gpt_lm/main.c:873-970), compiled from the reference
+    tree into oracle/_ref/ref_compact.so, on seeded records (valid ones and ones it must reject).
   * Closed-form expectations of tests/test_optim.c:197-211,228-229,293,313,363-372 and the
     schedule points of tests/test_optim.c:50-61.
 The fixtures are small .npz files; tests/test_oracle_golden.py checks oracle/ against them on CPU
@@ -182,6 +184,49 @@ def optim_cases() -> dict:
     return out
 
 
+def compact_cases() -> dict:
+    """Seeded compact records through the reference transform: status and, when accepted, the three outputs."""
+    rc = cref.RefCompact()
+    rng = np.random.default_rng(20240)
+    cases = {}
+
+    def split(total: int, n: int) -> list:
+        cuts = np.sort(rng.choice(np.arange(1, total), size=n - 1, replace=False)) if n > 1 else np.array([], dtype=np.int64)
+        return np.diff(np.concatenate([[0], cuts, [total]])).astype(np.int32).tolist()
+
+    def add(name, tokens, seg, ctx, vocab, pad, ims, ime):
+        st, ids, pos, tgt = rc.transform(tokens, seg, ctx, vocab, pad, ims, ime)
+        c = dict(tokens=np.asarray(tokens, dtype=np.uint16), segment_lengths=np.asarray(seg, dtype=np.int32),
+                 params=np.asarray([ctx, vocab, pad, ims, ime], dtype=np.int32), status=np.int32(st))
+        if st == 0:
+            c.update(input_ids=ids, positions=pos, target_ids=tgt)
+        cases[name] = c
+
+    for k, (ctx, vocab, n_seg) in enumerate([(8, 16, 1), (8, 16, 3), (64, 320, 5), (64, 320, 64), (512, 2048, 1), (512, 2048, 7), (512, 2048, 40)]):
+        add(f"valid{k}", rng.integers(0, vocab, size=ctx + 1), split(ctx, n_seg), ctx, vocab, 0, 1, 2)
+    # the record ends on <|im_end|> and the extra token is <|im_start|>: the last target is masked (main.c:960-963)
+    t = rng.integers(3, 320, size=65)
+    t[63], t[64] = 2, 1
+    add("tail_masked", t, split(64, 4), 64, 320, 0, 1, 2)
+    t = t.copy()
+    t[64] = 5
+    add("tail_kept", t, split(64, 4), 64, 320, 0, 1, 2)
+    # a document boundary right after an <|im_end|> inside the record
+    add("pad_is_last_id", rng.integers(0, 320, size=65), split(64, 6), 64, 320, 319, 1, 2)
+    # rejected inputs (main.c:934-959)
+    bad = rng.integers(0, 320, size=65)
+    bad[17] = 320
+    add("bad_token", bad, split(64, 3), 64, 320, 0, 1, 2)
+    bad = rng.integers(0, 320, size=65)
+    bad[64] = 400
+    add("bad_extra_token", bad, split(64, 3), 64, 320, 0, 1, 2)
+    add("bad_zero_length", rng.integers(0, 320, size=65), [10, 0, 54], 64, 320, 0, 1, 2)
+    add("bad_negative_length", rng.integers(0, 320, size=65), [70, -6], 64, 320, 0, 1, 2)
+    add("bad_short", rng.integers(0, 320, size=65), [10, 20], 64, 320, 0, 1, 2)
+    add("bad_long", rng.integers(0, 320, size=65), [40, 30], 64, 320, 0, 1, 2)
+    return cases
+
+
 def save(group: str, cases: dict) -> None:
     flat = {}
     for cname, fields in cases.items():
@@ -204,6 +249,9 @@ def main() -> None:
     save("ref_ctest_rope_rms", rope_rms_cases(h))
     save("ref_py_scripts", script_cases(args.ref))
     save("ref_ctest_optim", optim_cases())
+    if not cref.compact_available():
+        raise SystemExit("oracle/_ref/ref_compact.so is missing: run __graft_entry__.build() where the reference tree exists")
+    save("ref_compact_transform", compact_cases())
 
 
 if __name__ == "__main__":

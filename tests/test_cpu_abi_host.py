@@ -38,7 +38,7 @@ def test_struct_layouts_match_the_c_header(tmp_path):
                "gd_backend_adamw_desc", "gd_backend_amp_state_desc", "gd_backend_amp_unscale_desc", "gd_backend_grad_norm_desc",
                "gd_backend_embedding_args", "gd_backend_rope_args", "gd_backend_rms_norm_args", "gd_backend_concat_args",
                "gd_backend_sdpa_varlen_args", "gd_backend_sdpa_decode_args", "gd_backend_kv_cache_append_args",
-               "gdb200_gpt_spec", "gdb200_gpt_batch"]
+               "gdb200_gpt_spec", "gdb200_gpt_batch", "gdb200_gpt_compact_batch"]
     body = "\n".join(f'printf("%zu\\n", sizeof({s}));' for s in structs)
     src.write_text(f'#include <stdio.h>\n#include "{HEADER}"\nint main(void){{{body} return 0;}}\n')
     exe = tmp_path / "sizes"
@@ -46,7 +46,7 @@ def test_struct_layouts_match_the_c_header(tmp_path):
     sizes = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
     py = [abi.MatrixView, abi.BatchedMatrixView, abi.VectorView, abi.TensorView, abi.AdamwDesc, abi.AmpStateDesc, abi.AmpUnscaleDesc,
           abi.GradNormDesc, abi.EmbeddingArgs, abi.RopeArgs, abi.RmsNormArgs, abi.ConcatArgs, abi.SdpaVarlenArgs, abi.SdpaDecodeArgs,
-          abi.KvCacheAppendArgs, abi.GptSpec, abi.GptBatch]
+          abi.KvCacheAppendArgs, abi.GptSpec, abi.GptBatch, abi.GptCompactBatch]
     assert sizes == [C.sizeof(t) for t in py]
 
 

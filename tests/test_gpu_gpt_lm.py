@@ -204,3 +204,44 @@ def test_native_step_driver_matches_python_host(monkeypatch, tied, chunk_env):
     for s, b in enumerate(batches):
         want = ref.train_step(b.input_ids, b.targets, b.positions, b.cu_seqlens, s + 1, otc)
         assert abs(ln[s] - want["loss"]) <= 2e-3 * abs(want["loss"])
+
+
+@pytest.mark.parametrize("kind", ["python", "native"])
+def test_pipelined_steps_match_synchronous_steps(kind):
+    """Stream-ordered batch upload and loss download with one step of host run-ahead (the reference's slot rings,
+    src/core/memory.c:701,1149-1208) give the same losses, parameters and scaler state as the synchronous form."""
+    cfg = small_cfg()
+    tc = g.TrainConfig.baseline()
+    hp = g.init_params(cfg, seed=33)
+    batches = [g.synthetic_batch(cfg, n_seqs=5, min_len=4, max_len=64, seed=500 + s, pad_to=64) for s in range(6)]
+    results = {}
+    for mode in ("sync", "pipelined"):
+        with pkg.runtime.Context(params_bytes=64 << 20, state_bytes=128 << 20, scratch_bytes=1 << 30) as ctx:
+            model = g.GptLm(ctx, cfg, hp)
+            trainer = (g.NativeTrainer if kind == "native" else g.Trainer)(model, tc)
+            if mode == "sync":
+                losses = [float(trainer.train_batch(b).read()[()]) for b in batches]
+            else:
+                ctx.run_ahead = 1
+                slots = [ctx.pinned_copy(np.full(1, np.nan, dtype=np.float32)) for _ in range(2)]
+                pinned = []
+                for b in batches:
+                    b.input_ids, b.targets = ctx.pinned_copy(b.input_ids), ctx.pinned_copy(b.targets)
+                    b.positions, b.cu_seqlens = ctx.pinned_copy(b.positions), ctx.pinned_copy(b.cu_seqlens)
+                    pinned.append(b)
+                losses = []
+                for s, b in enumerate(pinned):
+                    trainer.train_batch(b, loss_out=slots[s & 1])
+                    ctx.wait_steps(1)
+                    if s > 0:
+                        losses.append(float(slots[(s - 1) & 1][0]))
+                ctx.wait_steps(0)
+                losses.append(float(slots[(len(pinned) - 1) & 1][0]))
+                ctx.run_ahead = 0
+            results[mode] = (losses, {n: host(p) for n, p in model.params.items()}, trainer.scaler.sync(), trainer.optimizer.step_count())
+    ls, lpipe = results["sync"][0], results["pipelined"][0]
+    assert len(lpipe) == len(ls) == 6 and ls[0] == lpipe[0]
+    np.testing.assert_allclose(lpipe, ls, rtol=2e-4)
+    for n in results["sync"][1]:
+        np.testing.assert_allclose(results["pipelined"][1][n], results["sync"][1][n], atol=2e-3, rtol=2e-2, err_msg=n)
+    assert results["sync"][2] == results["pipelined"][2] and results["sync"][3] == results["pipelined"][3] == 6
