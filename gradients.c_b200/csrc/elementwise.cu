@@ -19,16 +19,25 @@ struct bcast_desc {
     uint64_t ys[8];
 };
 
-template <typename T>
+// OP: 0 add, 1 mul, 2 sub; computed in FP32 and rounded once to the storage type (for 16-bit storage that equals
+// the reference's half-precision arithmetic, src/ops/{add,mul,sub}/metal_*.metal).
+enum { BIN_ADD = 0, BIN_MUL = 1, BIN_SUB = 2 };
+template <int OP>
+__device__ __forceinline__ float binop(float a, float b)
+{
+    return OP == BIN_ADD ? a + b : (OP == BIN_MUL ? a * b : a - b);
+}
+
+template <typename T, int OP>
 __global__ void add_direct_kernel(const T *x, const T *y, T *out, size_t n)
 {
     gdb_pdl_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        gdb_io<T>::st(out, i, gdb_io<T>::ld(x, i) + gdb_io<T>::ld(y, i));
+        gdb_io<T>::st(out, i, binop<OP>(gdb_io<T>::ld(x, i), gdb_io<T>::ld(y, i)));
     }
 }
-template <typename T>
+template <typename T, int OP>
 __global__ void add_direct_vec8_kernel(const uint4 *x, const uint4 *y, uint4 *out, size_t vecs)
 {
     gdb_pdl_sync();
@@ -39,13 +48,13 @@ __global__ void add_direct_vec8_kernel(const uint4 *x, const uint4 *y, uint4 *ou
         b.raw = y[i];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            a.set(e, a.get(e) + b.get(e));
+            a.set(e, binop<OP>(a.get(e), b.get(e)));
         }
         out[i] = a.raw;
     }
 }
 // out[r, c] = x[r, c] + y[c]; cols % 8 == 0, all pointers 16-byte aligned.
-template <typename T>
+template <typename T, int OP>
 __global__ void add_row_vec8_kernel(const uint4 *x, const uint4 *y, uint4 *out, size_t vecs, unsigned row_vecs)
 {
     gdb_pdl_sync();
@@ -56,12 +65,12 @@ __global__ void add_row_vec8_kernel(const uint4 *x, const uint4 *y, uint4 *out, 
         b.raw = __ldg(&y[i % row_vecs]);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            a.set(e, a.get(e) + b.get(e));
+            a.set(e, binop<OP>(a.get(e), b.get(e)));
         }
         out[i] = a.raw;
     }
 }
-template <typename T>
+template <typename T, int OP>
 __global__ void add_bcast_kernel(const T *x, const T *y, T *out, size_t n, bcast_desc d)
 {
     gdb_pdl_sync();
@@ -74,7 +83,7 @@ __global__ void add_bcast_kernel(const T *x, const T *y, T *out, size_t n, bcast
             xo += idx * d.xs[dim];
             yo += idx * d.ys[dim];
         }
-        gdb_io<T>::st(out, i, gdb_io<T>::ld(x, xo) + gdb_io<T>::ld(y, yo));
+        gdb_io<T>::st(out, i, binop<OP>(gdb_io<T>::ld(x, xo), gdb_io<T>::ld(y, yo)));
     }
 }
 
@@ -123,7 +132,7 @@ bool bcast_stride(const gd_backend_tensor_view *arg, const gd_backend_tensor_vie
     return false;
 }
 
-template <typename T>
+template <typename T, int OP>
 gd_status add_typed(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y,
                     const gd_backend_tensor_view *out, const bcast_desc &d, bool direct, bool row)
 {
@@ -134,20 +143,20 @@ gd_status add_typed(gd_backend *be, const gd_backend_tensor_view *x, const gd_ba
     const bool al16 = (((uintptr_t)xp | (uintptr_t)yp | (uintptr_t)op) % 16U) == 0U;
     if constexpr (sizeof(T) == 2) {
         if (direct && al16 && (n % 8U) == 0U) {
-            gdb_launch(add_direct_vec8_kernel<T>, gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (uint4 *)op, n / 8U);
-            return gdb_launched(be, "add");
+            gdb_launch(add_direct_vec8_kernel<T, OP>, gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (uint4 *)op, n / 8U);
+            return gdb_launched(be, OP == BIN_ADD ? "add" : (OP == BIN_MUL ? "mul" : "sub"));
         }
         if (!direct && row && al16 && (d.shape[d.rank - 1] % 8U) == 0U) {
-            gdb_launch(add_row_vec8_kernel<T>, gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (uint4 *)op, n / 8U, d.shape[d.rank - 1] / 8U);
-            return gdb_launched(be, "add");
+            gdb_launch(add_row_vec8_kernel<T, OP>, gdb_grid_for(n / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (uint4 *)op, n / 8U, d.shape[d.rank - 1] / 8U);
+            return gdb_launched(be, OP == BIN_ADD ? "add" : (OP == BIN_MUL ? "mul" : "sub"));
         }
     }
     if (direct) {
-        gdb_launch(add_direct_kernel<T>, gdb_grid_for(n, 256, be, 8), 256, 0, be->stream, xp, yp, op, n);
+        gdb_launch(add_direct_kernel<T, OP>, gdb_grid_for(n, 256, be, 8), 256, 0, be->stream, xp, yp, op, n);
     } else {
-        gdb_launch(add_bcast_kernel<T>, gdb_grid_for(n, 256, be, 8), 256, 0, be->stream, xp, yp, op, n, d);
+        gdb_launch(add_bcast_kernel<T, OP>, gdb_grid_for(n, 256, be, 8), 256, 0, be->stream, xp, yp, op, n, d);
     }
-    return gdb_launched(be, "add");
+    return gdb_launched(be, OP == BIN_ADD ? "add" : (OP == BIN_MUL ? "mul" : "sub"));
 }
 
 // ------------------------------------------------------------------ dropout
@@ -377,9 +386,9 @@ bool half_dtype(uint32_t dt) { return dt == GDB_DTYPE_F16 || dt == GDB_DTYPE_BF1
 
 }  // namespace
 
-extern "C" {
-
-gd_status gd_backend_add(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y, const gd_backend_tensor_view *out)
+// Broadcasting binary op (src/core/backend_generated.h:14-28): out = x OP y with numpy-style broadcasting of x and y.
+template <int OP>
+static gd_status binary_entry(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y, const gd_backend_tensor_view *out)
 {
     bcast_desc d;
     bool direct = true;
@@ -431,12 +440,27 @@ gd_status gd_backend_add(gd_backend *be, const gd_backend_tensor_view *x, const 
         }
     }
     if (out->dtype == GDB_DTYPE_F16) {
-        return add_typed<__half>(be, x, y, out, d, direct, row);
+        return add_typed<__half, OP>(be, x, y, out, d, direct, row);
     }
     if (out->dtype == GDB_DTYPE_BF16) {
-        return add_typed<__nv_bfloat16>(be, x, y, out, d, direct, row);
+        return add_typed<__nv_bfloat16, OP>(be, x, y, out, d, direct, row);
     }
-    return add_typed<float>(be, x, y, out, d, direct, row);
+    return add_typed<float, OP>(be, x, y, out, d, direct, row);
+}
+
+extern "C" {
+
+gd_status gd_backend_add(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y, const gd_backend_tensor_view *out)
+{
+    return binary_entry<BIN_ADD>(be, x, y, out);
+}
+gd_status gd_backend_mul(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y, const gd_backend_tensor_view *out)
+{
+    return binary_entry<BIN_MUL>(be, x, y, out);
+}
+gd_status gd_backend_sub(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y, const gd_backend_tensor_view *out)
+{
+    return binary_entry<BIN_SUB>(be, x, y, out);
 }
 
 gd_status gd_backend_relu(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *y)

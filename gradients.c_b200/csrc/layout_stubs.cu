@@ -1,5 +1,5 @@
 // Slice copies used by concat / split (multi-prompt prefill gathers last rows through
-// gd_backend_concat_to_full) and the entries that are off the gpt_lm path, which answer
+// gd_backend_concat_to_full) and the MiniMax-M3 sparse-attention entries, which are not built and answer
 // GD_ERR_UNSUPPORTED exactly like the reference's null backend
 // (src/backends/null/backend_null.c). Slice semantics: src/core/backend.h:579-615.
 #include "common.cuh"
@@ -85,25 +85,6 @@ gd_status gd_backend_split_to_full(gd_backend *be, TV slice, TV full, const gd_b
     return a == NULL ? GD_ERR_INVALID_ARGUMENT : slice_copy<true>(be, slice, full, a->count, a->inner, a->slice_axis, a->full_axis, a->axis_offset);
 }
 
-gd_status gd_backend_permute(gd_backend *, TV, TV, const gd_backend_permute_args *) UNSUPPORTED_BODY
-gd_status gd_backend_mul(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_sub(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_sigmoid(gd_backend *, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_sigmoid_backward(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_tanh(gd_backend *, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_tanh_backward(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_sigmoid_backward_from_output(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_tanh_backward_from_output(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_mul_backward_direct(gd_backend *, TV, TV, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_mul_reduce_suffix(gd_backend *, TV, TV, TV) UNSUPPORTED_BODY
-gd_status gd_backend_mse_forward(gd_backend *, TV, TV, TV, uint64_t, float) UNSUPPORTED_BODY
-gd_status gd_backend_mse_backward(gd_backend *, TV, TV, TV, TV, TV, float) UNSUPPORTED_BODY
-gd_status gd_backend_huber_forward(gd_backend *, TV, TV, TV, uint64_t, float, float) UNSUPPORTED_BODY
-gd_status gd_backend_huber_backward(gd_backend *, TV, TV, TV, TV, TV, float, float) UNSUPPORTED_BODY
-gd_status gd_backend_powlu_forward(gd_backend *, TV, TV, TV, float) UNSUPPORTED_BODY
-gd_status gd_backend_powlu_backward(gd_backend *, TV, TV, TV, TV, TV, float) UNSUPPORTED_BODY
-gd_status gd_backend_powlu_split_forward(gd_backend *, TV, TV, float) UNSUPPORTED_BODY
-gd_status gd_backend_powlu_split_backward(gd_backend *, TV, TV, TV, float) UNSUPPORTED_BODY
 gd_status gd_backend_minimax_m3_index_topk(gd_backend *, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY
 gd_status gd_backend_minimax_m3_sparse_attention(gd_backend *, TV, TV, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY
 gd_status gd_backend_minimax_m3_sparse_attention_backward(gd_backend *, TV, TV, TV, TV, TV, TV, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY

@@ -16,9 +16,14 @@ HOT_PATH = ["test_memory", "test_tensor", "test_transfer", "test_linear", "test_
             "test_kv_cache_decode", "test_rms_norm", "test_embedding", "test_rope", "test_swiglu", "test_dropout_ops",
             "test_lm_cross_entropy", "test_optim", "test_autograd", "test_backward_null_outputs", "test_module",
             "test_module_io", "test_dataloader"]
+# The rest of the reference's suite: data formats either side of the path and the ops of its other examples
+# (everything but the MiniMax-M3 sparse-attention test, whose entries are not built).
+WIDER = ["test_ops", "test_binary_ops", "test_reduce_ops", "test_reshape", "test_concat", "test_split", "test_permute",
+         "test_sigmoid_ops", "test_tanh_ops", "test_mse", "test_huber", "test_cross_entropy", "test_powlu", "test_powlu_split_linear",
+         "test_dataset", "test_gdds", "test_gdds_varlen", "test_tokenizer", "test_metrics"]
 
 
-@pytest.mark.parametrize("name", HOT_PATH)
+@pytest.mark.parametrize("name", HOT_PATH + WIDER)
 def test_reference_ctest(name, tmp_path):
     exe = os.path.join(cref.TESTS_CUDA_DIR, name)
     if not os.path.exists(exe):
