@@ -140,6 +140,10 @@ class GptSpec(C.Structure):
                 ("m_offset", SZ * GPT_MAX_PARAMS), ("v_offset", SZ * GPT_MAX_PARAMS), ("weight_decay", F * GPT_MAX_PARAMS)]
 
 
+class PermuteArgs(C.Structure):
+    _fields_ = [("count", U64), ("inner", U64), ("rank", U32), ("active_rank", U32), ("axes", U32 * 8), ("reserved0", U32)]
+
+
 class GptBatch(C.Structure):
     _fields_ = [("buffer", P), ("input_ids_offset", SZ), ("targets_offset", SZ), ("positions_offset", SZ),
                 ("cu_seqlens_offset", SZ), ("n_tokens", C.c_int64), ("n_cu", C.c_int64)]
@@ -207,6 +211,19 @@ PROTOTYPES = {
     "gd_backend_sigmoid_backward": (_ST, [P, TV, TV, TV]),
     "gd_backend_tanh": (_ST, [P, TV, TV]),
     "gd_backend_tanh_backward": (_ST, [P, TV, TV, TV]),
+    "gd_backend_sigmoid_backward_from_output": (_ST, [P, TV, TV, TV]),
+    "gd_backend_tanh_backward_from_output": (_ST, [P, TV, TV, TV]),
+    "gd_backend_mul_backward_direct": (_ST, [P, TV, TV, TV, TV, TV]),
+    "gd_backend_mul_reduce_suffix": (_ST, [P, TV, TV, TV]),
+    "gd_backend_mse_forward": (_ST, [P, TV, TV, TV, U64, F]),
+    "gd_backend_mse_backward": (_ST, [P, TV, TV, TV, TV, TV, F]),
+    "gd_backend_huber_forward": (_ST, [P, TV, TV, TV, U64, F, F]),
+    "gd_backend_huber_backward": (_ST, [P, TV, TV, TV, TV, TV, F, F]),
+    "gd_backend_powlu_forward": (_ST, [P, TV, TV, TV, F]),
+    "gd_backend_powlu_backward": (_ST, [P, TV, TV, TV, TV, TV, F]),
+    "gd_backend_powlu_split_forward": (_ST, [P, TV, TV, F]),
+    "gd_backend_powlu_split_backward": (_ST, [P, TV, TV, TV, F]),
+    "gd_backend_permute": (_ST, [P, TV, TV, C.POINTER(PermuteArgs)]),
     "gd_backend_dropout_forward": (_ST, [P, TV, TV, TV, F, U64]),
     "gd_backend_dropout_add_forward": (_ST, [P, TV, TV, TV, TV, F, U64]),
     "gd_backend_dropout_backward": (_ST, [P, TV, TV, F, U64]),
@@ -290,15 +307,12 @@ PROTOTYPES = {
     "gdb200_dp_shutdown": (None, [P]),
 }
 
-# Entries that exist only to answer GD_ERR_UNSUPPORTED (not bound with prototypes above).
-UNSUPPORTED_ENTRIES = [
-    "gd_backend_permute", "gd_backend_reduce_contiguous", "gd_backend_reduce_axis", "gd_backend_broadcast_axis",
+# Exported entries that the Python host never calls (checked for presence only): helpers the reference's C host
+# uses and the MiniMax-M3 entries, which answer GD_ERR_UNSUPPORTED.
+UNBOUND_ENTRIES = [
+    "gd_backend_reduce_contiguous", "gd_backend_reduce_axis", "gd_backend_broadcast_axis",
     "gd_backend_broadcast_to", "gd_backend_broadcast_scalar", "gd_backend_reduce_broadcast",
-    "gd_backend_sigmoid_backward_from_output", "gd_backend_tanh_backward_from_output",
-    "gd_backend_mul_backward_direct", "gd_backend_mul_reduce_suffix", "gd_backend_mse_forward",
-    "gd_backend_mse_backward", "gd_backend_huber_forward", "gd_backend_huber_backward",
-    "gd_backend_powlu_forward", "gd_backend_powlu_backward", "gd_backend_powlu_split_forward",
-    "gd_backend_powlu_split_backward", "gd_backend_minimax_m3_index_topk",
+    "gd_backend_minimax_m3_index_topk",
     "gd_backend_minimax_m3_sparse_attention", "gd_backend_minimax_m3_sparse_attention_backward",
 ]
 
@@ -325,7 +339,7 @@ def load_library() -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError here means a declared symbol is not exported
         fn.restype = restype
         fn.argtypes = argtypes
-    for name in UNSUPPORTED_ENTRIES:
+    for name in UNBOUND_ENTRIES:
         getattr(lib, name)
     _lib = lib
     return lib

@@ -308,7 +308,11 @@ gd_status gd_backend_split_from_full(gd_backend *backend, GDB_TV full, GDB_TV sl
 gd_status gd_backend_split_to_full(gd_backend *backend, GDB_TV slice, GDB_TV full, const gd_backend_split_args *args);
 gd_status gd_backend_permute(gd_backend *backend, GDB_TV src, GDB_TV dst, const gd_backend_permute_args *args);
 
-/* ---- entries off the gpt_lm path: always GD_ERR_UNSUPPORTED (as src/backends/null/backend_null.c) ---- */
+/* ---- entries off the gpt_lm path, used by the reference's other examples and tests (src/core/backend.h:243-268,
+ * 355-382, 452-506). F16 / BF16 / F32 unless noted. reduce_* / broadcast_*: sums and broadcasts of contiguous tensors
+ * times `scale`. *_backward_from_output: gradients from the saved forward output. mul_backward_direct and
+ * mul_reduce_suffix: 16-bit fast paths of the mul backward. mse / huber: per-chunk partial sums (F32) forward,
+ * +/- grad_out[0] * scale * d backward into either optional gradient. powlu: out = x1 * gate(x2, m), 16-bit. ---- */
 gd_status gd_backend_reduce_contiguous(gd_backend *backend, GDB_TV src, GDB_TV dst, float scale);
 gd_status gd_backend_reduce_axis(gd_backend *backend, GDB_TV src, GDB_TV dst, uint32_t axis, float scale);
 gd_status gd_backend_broadcast_axis(gd_backend *backend, GDB_TV src, GDB_TV dst, uint32_t axis, float scale);
@@ -327,6 +331,7 @@ gd_status gd_backend_powlu_forward(gd_backend *backend, GDB_TV x1, GDB_TV x2, GD
 gd_status gd_backend_powlu_backward(gd_backend *backend, GDB_TV x1, GDB_TV x2, GDB_TV grad_out, GDB_TV grad_x1, GDB_TV grad_x2, float m);
 gd_status gd_backend_powlu_split_forward(gd_backend *backend, GDB_TV x12, GDB_TV out, float m);
 gd_status gd_backend_powlu_split_backward(gd_backend *backend, GDB_TV x12, GDB_TV grad_out, GDB_TV grad_x12, float m);
+/* MiniMax-M3 sparse attention is not built: always GD_ERR_UNSUPPORTED (as src/backends/null/backend_null.c). */
 gd_status gd_backend_minimax_m3_index_topk(gd_backend *backend, GDB_TV index_q, GDB_TV index_k, GDB_TV cu_seqlens, GDB_TV topk_idx, const gd_backend_minimax_m3_sparse_args *args);
 gd_status gd_backend_minimax_m3_sparse_attention(gd_backend *backend, GDB_TV q, GDB_TV k, GDB_TV v, GDB_TV cu_seqlens, GDB_TV topk_idx, GDB_TV out, const gd_backend_minimax_m3_sparse_args *args);
 gd_status gd_backend_minimax_m3_sparse_attention_backward(gd_backend *backend, GDB_TV grad_out, GDB_TV q, GDB_TV k, GDB_TV v, GDB_TV cu_seqlens, GDB_TV topk_idx, GDB_TV grad_q, GDB_TV grad_k, GDB_TV grad_v, GDB_TV stats, const gd_backend_minimax_m3_sparse_args *args);
