@@ -174,6 +174,15 @@ static inline cudaError_t gdb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 b
 }
 
 // ---- storage <-> float conversion ----
+// Sigmoid of the SwiGLU gate, one definition for the stand-alone kernels and the fused GEMM epilogue
+// (stable form of src/ops/swiglu/metal_swiglu.metal: exp of a non-positive argument only).
+__device__ __forceinline__ float gdb_swiglu_sigmoid(float x)
+{
+    const float e = __expf(-fabsf(x));
+    const float inv = 1.0f / (1.0f + e);
+    return x >= 0.0f ? inv : e * inv;
+}
+
 template <typename T> struct gdb_io;
 template <> struct gdb_io<__half> {
     static __device__ __forceinline__ float ld(const __half *p, size_t i) { return __half2float(p[i]); }
@@ -278,6 +287,8 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype,
                            void *c, size_t ldc_bytes, const void *bias, int bias_mode,
                            uint32_t M, uint32_t N, uint32_t K);
 // At most 64 output rows (decode): mma.sync kernel with K split over the warps of a CTA.
+gd_status gdb_gemm_skinny_swiglu(gd_backend *be, uint32_t dtype, const void *a, size_t lda_bytes, const void *w, size_t ldw_bytes,
+                                 const void *bias, void *c, size_t ldc_bytes, uint32_t M, uint32_t N, uint32_t K);
 gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
                           void *c, size_t ldc_bytes, const void *bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K);
 // CTA-pair persistent variant; *splits_out > 1 means FP32 partials were left in the workspace.

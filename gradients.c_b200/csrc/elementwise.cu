@@ -279,12 +279,7 @@ gd_status dropout_dispatch(gd_backend *be, uint32_t dtype, const void *x, const 
 bool dropout_p_ok(float p) { return p >= 0.0f && p < 1.0f; }
 
 // ------------------------------------------------------------------ SwiGLU
-__device__ __forceinline__ float swiglu_sigmoid(float x)
-{
-    const float e = __expf(-fabsf(x));
-    const float inv = 1.0f / (1.0f + e);
-    return x >= 0.0f ? inv : e * inv;
-}
+__device__ __forceinline__ float swiglu_sigmoid(float x) { return gdb_swiglu_sigmoid(x); }
 
 // out[r, c] = x1[r, c] * silu(x2[r, c]); x1/x2 rows may live in one [rows, 2H] tensor.
 template <typename T>

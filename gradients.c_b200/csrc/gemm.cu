@@ -403,6 +403,30 @@ gd_status gdb200_matmul_nt_bias(gd_backend *be, const gd_backend_matrix_view *x,
 {
     return gdb_gemm_dispatch(be, 0, 1, x, w, bias, y, 2);
 }
+// out[M, F] = swiglu_split(round(round(x w^T) + bias)) for w [2F, K], bias [2F]: the up / gate projection of the decode step
+// (examples/gpt_lm/gpt_lm_shared.c:1032-1046) in one launch. Only the 64-row kernel has this epilogue: other shapes
+// answer GD_ERR_UNSUPPORTED and the caller issues gdb200_matmul_nt_bias + gd_backend_swiglu_split_forward.
+gd_status gdb200_matmul_nt_bias_swiglu(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
+                                       const gd_backend_vector_view *bias, const gd_backend_matrix_view *out)
+{
+    if (be == NULL || x == NULL || w == NULL || bias == NULL || out == NULL || bias->buffer == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = out->dtype;
+    const size_t es = gdb_dtype_size(dt);
+    if (x->dtype != dt || w->dtype != dt || bias->dtype != dt || !mv_ok(x, es) || !mv_ok(w, es) || !mv_ok(out, es) || x->cols != w->cols ||
+        w->rows != 2U * out->cols || out->rows != x->rows || bias->length != w->rows ||
+        !gdb_range_ok(bias->buffer, bias->offset, (size_t)bias->length * es)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (be->gemm_mode == 1 || be->gemm_mode == 2) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    cudaSetDevice(be->device);
+    return gdb_gemm_skinny_swiglu(be, dt, x->buffer->dptr + x->offset, x->row_bytes, w->buffer->dptr + w->offset, w->row_bytes,
+                                  bias->buffer->dptr + bias->offset, out->buffer->dptr + out->offset, out->row_bytes, (uint32_t)x->rows,
+                                  (uint32_t)out->cols, (uint32_t)x->cols);
+}
 gd_status gdb200_matmul_tn_colsum(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_matrix_view *y,
                                   const gd_backend_vector_view *colsum)
 {

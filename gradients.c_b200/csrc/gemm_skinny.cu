@@ -126,7 +126,11 @@ __device__ __forceinline__ void sk_ldm4t(uint32_t (&r)[4], const void *p)
 
 // K is walked in chunks of CH (a multiple of 128): per chunk the CTA stages A[64, CH] and its 16 columns of B, each
 // warp multiplies its CH / 8 slice, and with more than one chunk the next one is in flight (two stages).
-template <typename T, bool B_KMAJOR>
+// SWIGLU (B K-major, i.e. a transposed weight [2N, K] = [up | gate] rows): the CTA takes 8 "up" rows and the 8 "gate"
+// rows N further down, and its epilogue applies out = up * silu(gate) to the two rounded linear outputs, so C is the
+// [M, N] activation and the [M, 2N] intermediate is never written. Rounding points are those of the two separate
+// calls: round(product), round(+ bias), round(up * silu(gate)).
+template <typename T, bool B_KMAJOR, bool SWIGLU = false>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restrict__ B, size_t ldb, T *__restrict__ C, size_t ldc,
                           const T *__restrict__ bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K, uint32_t CH, int stages)
@@ -134,7 +138,8 @@ gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restri
     gdb_pdl_sync();
     extern __shared__ __align__(16) unsigned char sk_sm[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t n0 = blockIdx.x * SK_COLS;
+    static_assert(!SWIGLU || B_KMAJOR, "the fused SwiGLU epilogue reads a transposed weight");
+    const uint32_t n0 = blockIdx.x * (SWIGLU ? SK_COLS / 2 : SK_COLS);
     const uint32_t LDA = CH + 8U, LDW = B_KMAJOR ? CH + 8U : 24U;
     const uint32_t a_bytes = SK_ROWS * LDA * 2U, w_bytes = (B_KMAJOR ? (uint32_t)SK_COLS : CH) * LDW * 2U, stage_bytes = a_bytes + w_bytes;
     const uint32_t n_chunks = K / CH, segs = CH / 8U;
@@ -148,7 +153,8 @@ gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restri
         if (B_KMAJOR) {
             for (uint32_t i = tid; i < SK_COLS * segs; i += SK_WARPS * 32) {
                 const uint32_t r = i / segs, sgm = i % segs;
-                sk_cp16(Ws + r * LDW + sgm * 8U, B + (size_t)(n0 + r) * ldb + k0 + sgm * 8U, true);
+                const uint32_t wrow = SWIGLU ? (r < 8U ? n0 + r : N + n0 + (r - 8U)) : n0 + r;
+                sk_cp16(Ws + r * LDW + sgm * 8U, B + (size_t)wrow * ldb + k0 + sgm * 8U, true);
             }
         } else {
             for (uint32_t i = tid; i < CH * 2U; i += SK_WARPS * 32) {
@@ -212,6 +218,30 @@ gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restri
             red[warp][r + 8][c + 1] = acc[mt][nt][3];
         }
     __syncthreads();
+    if (SWIGLU) {
+        for (int o = tid; o < SK_ROWS * (SK_COLS / 2); o += SK_WARPS * 32) {
+            const int r = o / (SK_COLS / 2), c = o % (SK_COLS / 2);
+            if ((uint32_t)r >= M) continue;
+            float up = 0.0f, gate = 0.0f;
+#pragma unroll
+            for (int w = 0; w < SK_WARPS; ++w) {
+                up += red[w][r][c];
+                gate += red[w][r][c + 8];
+            }
+            if (bias != nullptr) {
+                if (bias_mode == 2) {
+                    up = gdb_io<T>::rnd(up);
+                    gate = gdb_io<T>::rnd(gate);
+                }
+                up += gdb_io<T>::ld(bias, n0 + c);
+                gate += gdb_io<T>::ld(bias, N + n0 + c);
+            }
+            up = gdb_io<T>::rnd(up);       // the values the separate linear call would have stored
+            gate = gdb_io<T>::rnd(gate);
+            gdb_io<T>::st(C, (size_t)r * ldc + n0 + c, up * (gate * gdb_swiglu_sigmoid(gate)));
+        }
+        return;
+    }
     for (int o = tid; o < SK_ROWS * SK_COLS; o += SK_WARPS * 32) {
         const int r = o / SK_COLS, c = o % SK_COLS;
         if ((uint32_t)r >= M) continue;
@@ -226,11 +256,11 @@ gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restri
     }
 }
 
-template <typename T, bool B_KMAJOR>
+template <typename T, bool B_KMAJOR, bool SWIGLU = false>
 gd_status launch_staged(gd_backend *be, const void *a, size_t lda, const void *b, size_t ldb, void *c, size_t ldc, const void *bias, int bias_mode,
                         uint32_t M, uint32_t N, uint32_t K, uint32_t ch)
 {
-    auto kern = gemm_skinny_staged_kernel<T, B_KMAJOR>;
+    auto kern = gemm_skinny_staged_kernel<T, B_KMAJOR, SWIGLU>;
     const int stages = K / ch > 1U ? 2 : 1;
     const uint32_t a_bytes = SK_ROWS * (ch + 8U) * 2U, w_bytes = B_KMAJOR ? SK_COLS * (ch + 8U) * 2U : ch * 24U * 2U;
     size_t smem = (size_t)stages * (a_bytes + w_bytes);
@@ -242,7 +272,7 @@ gd_status launch_staged(gd_backend *be, const void *a, size_t lda, const void *b
         if (e != cudaSuccess) return gdb_fail(be, e, "skinny gemm smem attribute");
         configured = smem;
     }
-    gdb_launch(kern, N / SK_COLS, SK_WARPS * 32, smem, be->stream, (const T *)a, lda, (const T *)b, ldb, (T *)c, ldc, (const T *)bias, bias_mode, M, N, K, ch, stages);
+    gdb_launch(kern, N / (SWIGLU ? SK_COLS / 2 : SK_COLS), SK_WARPS * 32, smem, be->stream, (const T *)a, lda, (const T *)b, ldb, (T *)c, ldc, (const T *)bias, bias_mode, M, N, K, ch, stages);
     return gdb_launched(be, "gemm_skinny_staged");
 }
 
@@ -276,4 +306,21 @@ gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a,
     }
 #undef GDB_SK
     return gdb_launched(be, "gemm_skinny");
+}
+
+// out[M, N] = swiglu(x W^T + bias) for a transposed weight W [2N, K] = [up rows | gate rows] and bias [2N]: the linear layer
+// and the gate of examples/gpt_lm/gpt_lm_shared.c:1032-1046 (gd_linear_transposed_weight + gd_swiglu_split) in one launch,
+// with the rounding points of the two calls. Returns GD_ERR_UNSUPPORTED unless M <= 64, N % 8 == 0, K a multiple of 128
+// and everything 16-byte aligned (the caller then issues the two calls).
+gd_status gdb_gemm_skinny_swiglu(gd_backend *be, uint32_t dtype, const void *a, size_t lda_bytes, const void *w, size_t ldw_bytes,
+                                 const void *bias, void *c, size_t ldc_bytes, uint32_t M, uint32_t N, uint32_t K)
+{
+    const uint32_t ch = (K % 512U) == 0U ? 512U : ((K % 256U) == 0U ? 256U : ((K % 128U) == 0U ? 128U : 0U));
+    if ((dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) || M == 0U || M > (uint32_t)SK_ROWS || N == 0U || (N % 8U) != 0U || ch == 0U ||
+        (((uintptr_t)a | (uintptr_t)w | lda_bytes | ldw_bytes) % 16U) != 0U || (ldc_bytes % 2U) != 0U || getenv("GDB200_SKINNY_DIRECT") != NULL) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const size_t lda = lda_bytes / 2U, ldw = ldw_bytes / 2U, ldc = ldc_bytes / 2U;
+    return dtype == GDB_DTYPE_F16 ? launch_staged<__half, true, true>(be, a, lda, w, ldw, c, ldc, bias, 2, M, N, K, ch)
+                                  : launch_staged<__nv_bfloat16, true, true>(be, a, lda, w, ldw, c, ldc, bias, 2, M, N, K, ch);
 }

@@ -863,11 +863,22 @@ gd_status decode_step_body(gd_backend *be, const gdb200_gpt_spec *s, const gdb20
         Ten proj = linear_t(c, attn, c.param(pb + 3, {D, D}), c.param(pb + 4, {D}), B, D, D);
         Ten resid, normed2;
         add_then_rms(x, proj, c.param(pb + 5, {D}), &resid, &normed2);
-        Ten up_gate = linear_t(c, normed2, c.param(pb + 6, {2 * F, D}), c.param(pb + 7, {2 * F}), B, D, 2 * F);
         Ten act = c.alloc(dt, {B, F});
         {
-            gd_backend_tensor_view a = tv(up_gate), o = tv(act);
-            c.ok(gd_backend_swiglu_split_forward(be, &a, &o), "swiglu_split_forward");
+            // up / gate projection and the gate in one launch when the 64-row kernel takes the shape, else the two calls
+            const Ten w = c.param(pb + 6, {2 * F, D}), bv = c.param(pb + 7, {2 * F});
+            const size_t es = gdb_dtype_size(dt);
+            gd_status r = GD_ERR_UNSUPPORTED;
+            if (c.st == GD_OK && be->gemm_mode != 1 && be->gemm_mode != 2) {
+                r = gdb_gemm_skinny_swiglu(be, dt, normed2.buf->dptr + normed2.off, (size_t)D * es, w.buf->dptr + w.off, (size_t)D * es,
+                                           bv.buf->dptr + bv.off, act.buf->dptr + act.off, (size_t)F * es, (uint32_t)B, (uint32_t)F, (uint32_t)D);
+            }
+            if (r == GD_ERR_UNSUPPORTED) {
+                Ten up_gate = linear_t(c, normed2, w, bv, B, D, 2 * F);
+                gd_backend_tensor_view a = tv(up_gate), o = tv(act);
+                r = gd_backend_swiglu_split_forward(be, &a, &o);
+            }
+            c.ok(r, "up_gate linear + swiglu");
         }
         Ten mlp = c.alloc(dt, {B, D});
         {

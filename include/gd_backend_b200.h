@@ -398,6 +398,13 @@ gd_status gdb200_flush_l2(gd_backend *backend);
 gd_status gdb200_matmul_nt_bias(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
                                 const gd_backend_vector_view *bias, const gd_backend_matrix_view *y);
 
+/* out [M, F] = x1 * silu(x2) with [x1 | x2] = round(round(x w^T) + bias), w stored [2F, K]: gdb200_matmul_nt_bias followed by
+ * gd_backend_swiglu_split_forward (the up / gate projection of examples/gpt_lm/gpt_lm_shared.c:1032-1046) in one
+ * launch, bit-identical to the two calls; the [M, 2F] intermediate is not written. Built for decode (M <= 64, K a
+ * multiple of 128, 16-byte aligned rows); GD_ERR_UNSUPPORTED otherwise, and the caller issues the two calls. */
+gd_status gdb200_matmul_nt_bias_swiglu(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
+                                       const gd_backend_vector_view *bias, const gd_backend_matrix_view *out);
+
 /* Weight and bias gradient of a linear layer in one pass over the upstream gradient (no counterpart in the reference,
  * which calls matmul_tn and reduce_rows, src/ops/linear_transposed_weight/core_linear_transposed_weight_bwd.c:31-167):
  * y[M, N] = x^T w with x stored [K, M] and w stored [K, N] (as gd_backend_matmul_tn), and colsum[m] = sum_k x[k, m]

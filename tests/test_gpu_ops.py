@@ -607,3 +607,28 @@ def test_fused_matmul_nt_bias_is_bit_identical_to_two_calls(step, m, k, n):
             ops.FUSE_BIAS_ADD = True
     assert np.array_equal(outs[0], outs[1])
     close(outs[0], O.linear_transposed_weight_forward(t32(x), t32(w), t32(b)), F16, scale=np.sqrt(k) / 4)
+
+
+@pytest.mark.parametrize("dtype", [F16, BF16])
+@pytest.mark.parametrize("m,k,f", [(64, 512, 1536), (1, 512, 1024), (37, 1536, 512), (8, 128, 8)])
+def test_fused_linear_swiglu_is_bit_identical_to_two_calls(step, dtype, m, k, f):
+    """Up / gate projection + gate of the decode step in one launch (64-row kernel) against
+    gdb200_matmul_nt_bias + gd_backend_swiglu_split_forward; shapes it does not take answer UNSUPPORTED."""
+    ctx = step
+    x = rnd_np(rng(120).standard_normal((m, k)).astype(np.float32), dtype)
+    w = rnd_np((rng(121).standard_normal((2 * f, k)) * 0.1).astype(np.float32), dtype)
+    b = rnd_np(rng(122).standard_normal(2 * f).astype(np.float32), dtype)
+    dx, dw, db = dev(ctx, x, dtype), dev(ctx, w, dtype), dev(ctx, b, dtype)
+    up_gate, act, fused = ctx.scratch_empty(dtype, (m, 2 * f)), ctx.scratch_empty(dtype, (m, f)), ctx.scratch_empty(dtype, (m, f))
+    lib = ctx.lib
+    bv = db.vv()
+    xm, wm = dx.mv(m, k), dw.mv(2 * f, k)
+    ugm, fm = up_gate.mv(m, 2 * f), fused.mv(m, f)
+    ctx.check(lib.gdb200_matmul_nt_bias(ctx.backend, byref(xm), byref(wm), byref(bv), byref(ugm)), "nt_bias")
+    ctx.check(lib.gd_backend_swiglu_split_forward(ctx.backend, byref(up_gate.tv()), byref(act.tv())), "swiglu")
+    ctx.check(lib.gdb200_matmul_nt_bias_swiglu(ctx.backend, byref(xm), byref(wm), byref(bv), byref(fm)), "fused")
+    assert np.array_equal(host(fused), host(act))
+    big = ctx.scratch_empty(dtype, (65, k))
+    out65 = ctx.scratch_empty(dtype, (65, f))
+    assert lib.gdb200_matmul_nt_bias_swiglu(ctx.backend, byref(big.mv(65, k)), byref(wm), byref(bv), byref(out65.mv(65, f))) == abi.GD_ERR_UNSUPPORTED
+    assert lib.gdb200_matmul_nt_bias_swiglu(ctx.backend, byref(xm), byref(wm), byref(bv), byref(ugm)) == abi.GD_ERR_INVALID_ARGUMENT
