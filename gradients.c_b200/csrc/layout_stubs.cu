@@ -1,7 +1,5 @@
 // Slice copies used by concat / split (multi-prompt prefill gathers last rows through
-// gd_backend_concat_to_full) and the MiniMax-M3 sparse-attention entries, which are not built and answer
-// GD_ERR_UNSUPPORTED exactly like the reference's null backend
-// (src/backends/null/backend_null.c). Slice semantics: src/core/backend.h:579-615.
+// gd_backend_concat_to_full). Slice semantics: src/core/backend.h:579-615.
 #include "common.cuh"
 
 namespace {
@@ -64,7 +62,6 @@ gd_status slice_copy(gd_backend *be, const gd_backend_tensor_view *slice, const 
 }  // namespace
 
 #define TV const gd_backend_tensor_view *
-#define UNSUPPORTED_BODY { return GD_ERR_UNSUPPORTED; }
 
 extern "C" {
 
@@ -85,8 +82,5 @@ gd_status gd_backend_split_to_full(gd_backend *be, TV slice, TV full, const gd_b
     return a == NULL ? GD_ERR_INVALID_ARGUMENT : slice_copy<true>(be, slice, full, a->count, a->inner, a->slice_axis, a->full_axis, a->axis_offset);
 }
 
-gd_status gd_backend_minimax_m3_index_topk(gd_backend *, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY
-gd_status gd_backend_minimax_m3_sparse_attention(gd_backend *, TV, TV, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY
-gd_status gd_backend_minimax_m3_sparse_attention_backward(gd_backend *, TV, TV, TV, TV, TV, TV, TV, TV, TV, TV, const gd_backend_minimax_m3_sparse_args *) UNSUPPORTED_BODY
 
 }  // extern "C"

@@ -308,8 +308,8 @@ PROTOTYPES = {
     "gdb200_dp_shutdown": (None, [P]),
 }
 
-# Exported entries that the Python host never calls (checked for presence only): helpers the reference's C host
-# uses and the MiniMax-M3 entries, which answer GD_ERR_UNSUPPORTED.
+# Exported entries that the Python host never calls (checked for presence only; the tests bind the MiniMax-M3
+# entries themselves): helpers the reference's C host uses.
 UNBOUND_ENTRIES = [
     "gd_backend_reduce_contiguous", "gd_backend_reduce_axis", "gd_backend_broadcast_axis",
     "gd_backend_broadcast_to", "gd_backend_broadcast_scalar", "gd_backend_reduce_broadcast",

@@ -331,7 +331,9 @@ gd_status gd_backend_powlu_forward(gd_backend *backend, GDB_TV x1, GDB_TV x2, GD
 gd_status gd_backend_powlu_backward(gd_backend *backend, GDB_TV x1, GDB_TV x2, GDB_TV grad_out, GDB_TV grad_x1, GDB_TV grad_x2, float m);
 gd_status gd_backend_powlu_split_forward(gd_backend *backend, GDB_TV x12, GDB_TV out, float m);
 gd_status gd_backend_powlu_split_backward(gd_backend *backend, GDB_TV x12, GDB_TV grad_out, GDB_TV grad_x12, float m);
-/* MiniMax-M3 sparse attention is not built: always GD_ERR_UNSUPPORTED (as src/backends/null/backend_null.c). */
+/* MiniMax-M3 block-sparse attention (src/core/backend.h:632-668): index_q / index_k [N, Hkv, Dh] -> topk_idx I32 [Hkv, N, topk]
+ * (sequence-local block ids, -1 padded); q [N, Hq, Dh], k / v [N, Hkv, Dh], Dh <= 64, topk <= 16, block_size <= 128; stats F32 [N, Hq, 3]
+ * is scratch of the backward. Rows of a sequence beyond max_seqlen are not visited. */
 gd_status gd_backend_minimax_m3_index_topk(gd_backend *backend, GDB_TV index_q, GDB_TV index_k, GDB_TV cu_seqlens, GDB_TV topk_idx, const gd_backend_minimax_m3_sparse_args *args);
 gd_status gd_backend_minimax_m3_sparse_attention(gd_backend *backend, GDB_TV q, GDB_TV k, GDB_TV v, GDB_TV cu_seqlens, GDB_TV topk_idx, GDB_TV out, const gd_backend_minimax_m3_sparse_args *args);
 gd_status gd_backend_minimax_m3_sparse_attention_backward(gd_backend *backend, GDB_TV grad_out, GDB_TV q, GDB_TV k, GDB_TV v, GDB_TV cu_seqlens, GDB_TV topk_idx, GDB_TV grad_q, GDB_TV grad_k, GDB_TV grad_v, GDB_TV stats, const gd_backend_minimax_m3_sparse_args *args);

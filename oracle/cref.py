@@ -112,6 +112,10 @@ class RefHarness:
         self.lib.gdref_lmce_oracle.argtypes = [vp] * 4 + [f] + [vp] * 4
         self.lib.gdref_rope.argtypes = [vp] * 4 + [u32, f, C.c_int32, i32, f]
         self.lib.gdref_rms.argtypes = [vp] * 3 + [u32, u32, f, vp, vp, vp]
+        if hasattr(self.lib, "gdref_m3_topk"):
+            self.lib.gdref_m3_topk.argtypes = [vp] * 3 + [u32] * 7 + [vp]
+            self.lib.gdref_m3_fwd.argtypes = [vp] * 5 + [u32] * 6 + [f, vp]
+            self.lib.gdref_m3_bwd.argtypes = [vp] * 6 + [u32] * 6 + [f, vp, vp, vp]
 
     def fill_tokens(self, count: int, base: float) -> np.ndarray:
         out = np.empty(count, dtype=np.uint16)
@@ -171,3 +175,31 @@ class RefHarness:
         self.lib.gdref_rms(_p(x), _p(np.ascontiguousarray(w, dtype=np.float32)), _p(np.ascontiguousarray(g, dtype=np.float32)),
                            rows, cols, eps, _p(out), _p(dx), _p(dw))
         return out, dx, dw
+
+    # MiniMax-M3 sparse attention references of tests/test_minimax_m3_sparse_attention.c (F16 bit patterns in, FP32 out)
+    def m3_topk(self, q_bits, k_bits, cu, block_size: int, topk: int, init_blocks: int, local_blocks: int) -> np.ndarray:
+        n, h, dh = q_bits.shape
+        out = np.zeros((h, n, topk), dtype=np.int32)
+        cu = np.ascontiguousarray(cu, dtype=np.int32)
+        self.lib.gdref_m3_topk(_p(np.ascontiguousarray(q_bits)), _p(np.ascontiguousarray(k_bits)), _p(cu), len(cu) - 1, h, dh, block_size, topk,
+                               init_blocks, local_blocks, _p(out))
+        return out
+
+    def m3_forward(self, q_bits, k_bits, v_bits, cu, topk_idx, block_size: int, scale: float) -> np.ndarray:
+        n, hq, dh = q_bits.shape
+        out = np.zeros((n, hq, dh), dtype=np.float32)
+        cu, tk = np.ascontiguousarray(cu, dtype=np.int32), np.ascontiguousarray(topk_idx, dtype=np.int32)
+        self.lib.gdref_m3_fwd(_p(np.ascontiguousarray(q_bits)), _p(np.ascontiguousarray(k_bits)), _p(np.ascontiguousarray(v_bits)), _p(cu), _p(tk),
+                              len(cu) - 1, hq, k_bits.shape[1], dh, block_size, tk.shape[2], scale, _p(out))
+        return out
+
+    def m3_backward(self, go_bits, q_bits, k_bits, v_bits, cu, topk_idx, block_size: int, scale: float):
+        n, hq, dh = q_bits.shape
+        hkv = k_bits.shape[1]
+        dq = np.zeros((n, hq, dh), dtype=np.float32)
+        dk, dv = np.zeros((n, hkv, dh), dtype=np.float32), np.zeros((n, hkv, dh), dtype=np.float32)
+        cu, tk = np.ascontiguousarray(cu, dtype=np.int32), np.ascontiguousarray(topk_idx, dtype=np.int32)
+        self.lib.gdref_m3_bwd(_p(np.ascontiguousarray(go_bits)), _p(np.ascontiguousarray(q_bits)), _p(np.ascontiguousarray(k_bits)),
+                              _p(np.ascontiguousarray(v_bits)), _p(cu), _p(tk), len(cu) - 1, hq, hkv, dh, block_size, tk.shape[2], scale,
+                              _p(dq), _p(dk), _p(dv))
+        return dq, dk, dv

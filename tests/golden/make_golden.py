@@ -16,6 +16,9 @@ Sources of truth (nothing is re-derived from this repository's oracle):
     inline in run_case (fwd.py:147-156, bwd.py:171-190); those lines are transcribed here.
   * The reference's compact-record transform (examples/gpt_lm/main.c:873-970), compiled from the reference
     tree into oracle/_ref/ref_compact.so, on seeded records (valid ones and ones it must reject).
+  * The CPU references of tests/test_minimax_m3_sparse_attention.c:145-213,423-600 (block selection, forward and
+    backward of the MiniMax-M3 sparse attention), from the same ref_harness.so, on the test's own pattern case and on
+    seeded cases.
   * Closed-form expectations of tests/test_optim.c:197-211,228-229,293,313,363-372 and the
     schedule points of tests/test_optim.c:50-61.
 The fixtures are small .npz files; tests/test_oracle_golden.py checks oracle/ against them on CPU
@@ -227,6 +230,39 @@ def compact_cases() -> dict:
     return cases
 
 
+def m3_cases(h: cref.RefHarness) -> dict:
+    """MiniMax-M3 sparse attention: the reference test's pattern case and seeded ones (values on a 1/8 grid, so that
+    index scores are exact in FP32 and FP64 alike and the selected blocks do not depend on the summation order)."""
+    cases = {}
+
+    def add(name, q, k, v, go, iq, ik, cu, block, topk, init_b, local_b, scale):
+        bits = lambda a: np.ascontiguousarray(a.astype(np.float16)).view(np.uint16)
+        tk = h.m3_topk(bits(iq), bits(ik), cu, block, topk, init_b, local_b)
+        out = h.m3_forward(bits(q), bits(k), bits(v), cu, tk, block, scale)
+        dq, dk, dv = h.m3_backward(bits(go), bits(q), bits(k), bits(v), cu, tk, block, scale)
+        cases[name] = dict(q=bits(q), k=bits(k), v=bits(v), go=bits(go), iq=bits(iq), ik=bits(ik), cu=np.asarray(cu, dtype=np.int32),
+                           params=np.asarray([block, topk, init_b, local_b], dtype=np.int32), scale=np.float32(scale), topk=tk, out=out,
+                           dq=dq, dk=dk, dv=dv)
+
+    # the reference test's own case (test_sparse_fwd_bwd: N 6, H 2, Dh 4, cu {0, 3, 6}, block 2, topk 2, fill_tokens patterns)
+    def pattern(count, base):
+        return h.fill_tokens(count, base).view(np.float16).astype(np.float32)
+    n, hh, dh = 6, 2, 4
+    q, k, v, go = (pattern(n * hh * dh, b).reshape(n, hh, dh) for b in (-0.25, 0.125, -0.375, 0.0625))
+    add("ctest_pattern", q, k, v, go, q, k, [0, 3, 6], 2, 2, 1, 1, 0.5)
+    rng = np.random.default_rng(77)
+    grid = lambda shape: rng.integers(-8, 9, size=shape).astype(np.float32) / 8.0
+    for name, (lens, hq, hkv, dh, block, topk, init_b, local_b) in {
+            "seeded_mha": ([13, 40, 7], 2, 2, 8, 4, 3, 1, 1),
+            "seeded_gqa": ([9, 17, 6], 4, 2, 16, 4, 4, 1, 2),      # the test reference holds statistics of at most 128 (row, head) pairs
+            "seeded_no_forced": ([50], 2, 1, 8, 4, 2, 0, 0)}.items():
+        cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        n = int(cu[-1])
+        add(name, grid((n, hq, dh)), grid((n, hkv, dh)), grid((n, hkv, dh)), grid((n, hq, dh)), grid((n, hkv, dh)), grid((n, hkv, dh)), cu,
+            block, topk, init_b, local_b, 1.0 / np.sqrt(dh))
+    return cases
+
+
 def save(group: str, cases: dict) -> None:
     flat = {}
     for cname, fields in cases.items():
@@ -249,6 +285,7 @@ def main() -> None:
     save("ref_ctest_rope_rms", rope_rms_cases(h))
     save("ref_py_scripts", script_cases(args.ref))
     save("ref_ctest_optim", optim_cases())
+    save("ref_m3_sparse", m3_cases(h))
     if not cref.compact_available():
         raise SystemExit("oracle/_ref/ref_compact.so is missing: run __graft_entry__.build() where the reference tree exists")
     save("ref_compact_transform", compact_cases())
