@@ -799,7 +799,9 @@ gd_status gd_backend_sdpa_varlen(gd_backend *be, const gd_backend_tensor_view *q
     return varlen_fwd_generic<float>(be, qp, kp, vp, cu, op, sp, p);
 }
 
-gd_status gd_backend_sdpa_varlen_backward(gd_backend *be, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k, const gd_backend_tensor_view *v, const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats, const gd_backend_sdpa_varlen_args *args)
+// `out` (the forward output) and `dq_accum` (FP32 scratch of q's element count) are optional: with both, forward
+// statistics and head_dim 64 the backward runs as one attention pass.
+static gd_status sdpa_varlen_backward_impl(gd_backend *be, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k, const gd_backend_tensor_view *v, const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats, const gd_backend_sdpa_varlen_args *args, const gd_backend_tensor_view *out, const gd_backend_tensor_view *dq_accum)
 {
     varlen_params p;
     if (be == NULL || grad_out == NULL || grad_q == NULL || grad_k == NULL || grad_v == NULL) {
@@ -837,6 +839,20 @@ gd_status gd_backend_sdpa_varlen_backward(gd_backend *be, const gd_backend_tenso
     }
     gdb_flash_args fa = {qp, kp, vp, gp, cu, dq, dk, dv, sp, p.n_tokens, p.batch, p.hq, p.hkv, p.dh,
                          p.causal, p.window, p.prefix, (int)args->max_seqlen, p.scale, dt};
+    if (out != NULL && dq_accum != NULL && have_fwd_stats) {
+        if (out->dtype != dt || out->count != q->count || dq_accum->count != q->count) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+        const void *op = gdb_tv_ptr(out, dt);
+        float *acc = (float *)gdb_tv_ptr(dq_accum, GDB_DTYPE_F32);
+        if (op == NULL || acc == NULL) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+        st = gdb_flash_varlen_backward_with_out(be, &fa, op, acc);
+        if (st != GD_ERR_UNSUPPORTED) {
+            return st;
+        }
+    }
     st = gdb_flash_varlen_backward(be, &fa, have_fwd_stats);
     if (st != GD_ERR_UNSUPPORTED) {
         return st;
@@ -844,6 +860,19 @@ gd_status gd_backend_sdpa_varlen_backward(gd_backend *be, const gd_backend_tenso
     if (dt == GDB_DTYPE_F16) return varlen_bwd_generic<__half>(be, gp, qp, kp, vp, cu, dq, dk, dv, sp, p);
     if (dt == GDB_DTYPE_BF16) return varlen_bwd_generic<__nv_bfloat16>(be, gp, qp, kp, vp, cu, dq, dk, dv, sp, p);
     return varlen_bwd_generic<float>(be, gp, qp, kp, vp, cu, dq, dk, dv, sp, p);
+}
+
+gd_status gd_backend_sdpa_varlen_backward(gd_backend *be, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k, const gd_backend_tensor_view *v, const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats, const gd_backend_sdpa_varlen_args *args)
+{
+    return sdpa_varlen_backward_impl(be, grad_out, q, k, v, cu_seqlens, grad_q, grad_k, grad_v, stats, args, NULL, NULL);
+}
+
+gd_status gdb200_sdpa_varlen_backward_with_output(gd_backend *be, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k, const gd_backend_tensor_view *v, const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *out, const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats, const gd_backend_tensor_view *dq_accum, const gd_backend_sdpa_varlen_args *args)
+{
+    if (out == NULL || dq_accum == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    return sdpa_varlen_backward_impl(be, grad_out, q, k, v, cu_seqlens, grad_q, grad_k, grad_v, stats, args, out, dq_accum);
 }
 
 gd_status gd_backend_sdpa_decode(gd_backend *be, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k_cache, const gd_backend_tensor_view *v_cache, const gd_backend_tensor_view *cache_pos, const gd_backend_tensor_view *out, const gd_backend_sdpa_decode_args *args)

@@ -19,5 +19,7 @@ struct gdb_flash_args {
 // then runs the general kernels.
 gd_status gdb_flash_varlen_forward(gd_backend *be, const gdb_flash_args *a);
 gd_status gdb_flash_varlen_backward(gd_backend *be, const gdb_flash_args *a, bool have_forward_stats);
+// Single-pass backward when the forward output is available (attention_flash.cu); dq32: FP32 scratch [N, Hq, 64].
+gd_status gdb_flash_varlen_backward_with_out(gd_backend *be, const gdb_flash_args *a, const void *out, float *dq32);
 // tcgen05 / tensor-memory forward (attention_tcgen05.cu); GD_ERR_UNSUPPORTED outside its fast path.
 gd_status gdb_attn5_forward(gd_backend *be, const gdb_flash_args *a);

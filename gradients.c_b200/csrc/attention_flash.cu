@@ -405,11 +405,25 @@ flash_q_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__rest
 // Key-stationary backward: dK, dV for a 64-key chunk of one KV head.
 // grid = (ceil(N / 64), Hkv), 128 threads; warp w owns keys 16w..16w+15 of the chunk.
 // ------------------------------------------------------------------------------------------------
-template <typename T, int DH, int BQT>
+// FUSE_DQ: the kernel also forms dQ. Each warp multiplies its dS slice (16 keys, transposed in registers with movmatrix)
+// by its 16 rows of K and adds the 64 x DH partial product to an FP32 accumulator in global memory (red.add), so the
+// query-stationary pass is not needed when D is known beforehand; dq32 [N, Hq, DH] must be zero on entry.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a)
+{
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ void red_add_v2(float *addr, float a, float b)
+{
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+
+template <typename T, int DH, int BQT, bool FUSE_DQ = false>
 __global__ void __launch_bounds__(128, 3)
 flash_kv_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, const T *__restrict__ go,
                 const int *__restrict__ cu, const float *__restrict__ stats, T *__restrict__ dk, T *__restrict__ dv,
-                flash_params p)
+                flash_params p, float *__restrict__ dq32)
 {
     gdb_pdl_sync();
     constexpr int LD = DH + 8, BK = 64, NT = BQT / 8, KT = DH / 16;
@@ -419,6 +433,8 @@ flash_kv_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
     T *Qs = Vs + BK * LD;                  // [2][BQT][LD]
     T *Gs = Qs + 2 * BQT * LD;             // [2][BQT][LD]
     float *St = reinterpret_cast<float *>(Gs + 2 * BQT * LD);  // [2][BQT][3]: m (log2), 1/l, D
+    constexpr int LDS = BK + 8;
+    T *Ds = reinterpret_cast<T *>(St + 2 * BQT * 3);          // FUSE_DQ: dS tile [BQT][LDS]
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int k0 = blockIdx.x * BK, hk = blockIdx.y, group = p.hq / p.hkv;
@@ -537,6 +553,45 @@ flash_kv_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
                     mma16816<T>::run(acck[2 * np], ad, b[0], b[1]);
                     mma16816<T>::run(acck[2 * np + 1], ad, b[2], b[3]);
                 }
+                if (FUSE_DQ) {
+                    // dS[q rows 16 kk .. +15, this warp's 16 keys] goes to shared memory as [q][key] (transposed in registers)
+                    const uint32_t t0 = movmatrix_trans(ad[0]), t1 = movmatrix_trans(ad[2]), t2 = movmatrix_trans(ad[1]), t3 = movmatrix_trans(ad[3]);
+                    T *rowp = Ds + (kk * 16 + g) * LDS + warp * 16 + 2 * t;
+                    *reinterpret_cast<uint32_t *>(rowp) = t0;
+                    *reinterpret_cast<uint32_t *>(rowp + 8 * LDS) = t1;
+                    *reinterpret_cast<uint32_t *>(rowp + 8) = t2;
+                    *reinterpret_cast<uint32_t *>(rowp + 8 * LDS + 8) = t3;
+                }
+            }
+            if (FUSE_DQ) {
+                // dQ[q rows 16 warp .. +15, :] += dS[q, all 64 keys of the chunk] K: one red per element and chunk
+                __syncthreads();
+                float dqa[DH / 8][4];
+#pragma unroll
+                for (int n = 0; n < DH / 8; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) dqa[n][e] = 0.0f;
+                }
+#pragma unroll
+                for (int k2 = 0; k2 < BK / 16; ++k2) {
+                    uint32_t a4[4];
+                    load_a<LDS>(a4, Ds, warp * 16, k2 * 16, lane);
+#pragma unroll
+                    for (int np = 0; np < DH / 16; ++np) {
+                        uint32_t b[4];
+                        load_b_kn<LD>(b, Ks, k2 * 16, np * 16, lane);
+                        mma16816<T>::run(dqa[2 * np], a4, b[0], b[1]);
+                        mma16816<T>::run(dqa[2 * np + 1], a4, b[2], b[3]);
+                    }
+                }
+                const int rowA = qt0 + warp * 16 + g, rowB = rowA + 8;
+                const int hcur = hk * group + w / n_tiles;
+                float *dA = dq32 + ((size_t)rowA * p.hq + hcur) * DH + 2 * t, *dB = dq32 + ((size_t)rowB * p.hq + hcur) * DH + 2 * t;
+#pragma unroll
+                for (int n = 0; n < DH / 8; ++n) {
+                    if (rowA < n_valid) red_add_v2(dA + n * 8, dqa[n][0], dqa[n][1]);
+                    if (rowB < n_valid) red_add_v2(dB + n * 8, dqa[n][2], dqa[n][3]);
+                }
             }
             __syncthreads();
         }
@@ -571,12 +626,12 @@ gd_status launch_q(gd_backend *be, const gdb_flash_args *a, const flash_params &
     return gdb_launched(be, MODE == 0 ? "flash_forward" : (MODE == 1 ? "flash_stats" : "flash_backward_dq"));
 }
 
-template <typename T, int DH, int BQT>
-gd_status launch_kv(gd_backend *be, const gdb_flash_args *a, const flash_params &p)
+template <typename T, int DH, int BQT, bool FUSE_DQ = false>
+gd_status launch_kv(gd_backend *be, const gdb_flash_args *a, const flash_params &p, float *dq32 = nullptr)
 {
     constexpr int LD = DH + 8;
-    constexpr size_t smem = (size_t)(2 * 64 * LD + 4 * BQT * LD) * 2U + (size_t)2 * BQT * 3 * sizeof(float);
-    auto kern = flash_kv_kernel<T, DH, BQT>;
+    constexpr size_t smem = (size_t)(2 * 64 * LD + 4 * BQT * LD) * 2U + (size_t)2 * BQT * 3 * sizeof(float) + (FUSE_DQ ? (size_t)BQT * (64 + 8) * 2U : 0U);
+    auto kern = flash_kv_kernel<T, DH, BQT, FUSE_DQ>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -584,7 +639,7 @@ gd_status launch_kv(gd_backend *be, const gdb_flash_args *a, const flash_params 
         configured = true;
     }
     dim3 grid((unsigned)((a->n_tokens + 63) / 64), (unsigned)a->hkv);
-    gdb_launch(kern, grid, 128, smem, be->stream, (const T *)a->q, (const T *)a->k, (const T *)a->v, (const T *)a->grad_out, a->cu, a->stats, (T *)a->dk, (T *)a->dv, p);
+    gdb_launch(kern, grid, 128, smem, be->stream, (const T *)a->q, (const T *)a->k, (const T *)a->v, (const T *)a->grad_out, a->cu, a->stats, (T *)a->dk, (T *)a->dv, p, dq32);
     return gdb_launched(be, "flash_backward_dkv");
 }
 
@@ -612,6 +667,62 @@ template <typename T>
 gd_status forward_typed(gd_backend *be, const gdb_flash_args *a, const flash_params &p)
 {
     return a->dh == 64 ? launch_q<T, 64, 64, 0>(be, a, p, a->out_or_dq) : launch_q<T, 128, 64, 0>(be, a, p, a->out_or_dq);
+}
+
+// dq[i] = round(dq32[i]), eight values per thread.
+template <typename T>
+__global__ void dq_convert_kernel(const float4 *__restrict__ src, uint4 *__restrict__ dst, size_t n8)
+{
+    gdb_pdl_sync();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        const float4 a = src[2 * i], b = src[2 * i + 1];
+        uint4 o;
+        o.x = mma16816<T>::pack(a.x, a.y);
+        o.y = mma16816<T>::pack(a.z, a.w);
+        o.z = mma16816<T>::pack(b.x, b.y);
+        o.w = mma16816<T>::pack(b.z, b.w);
+        dst[i] = o;
+    }
+}
+
+// Preparation of the single-pass backward: D[row, head] = sum_c dO * O (stats[.., 2]) and dq32 = 0.
+// Eight threads per (row, head) of 64 elements, 16 bytes of dO and of O each.
+template <typename T>
+__global__ void bwd_prep_kernel(const uint4 *__restrict__ go, const uint4 *__restrict__ out, float *__restrict__ stats, float4 *__restrict__ dq32,
+                                size_t n_vec)
+{
+    gdb_pdl_sync();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // one 8-element piece; n_vec is a multiple of 8
+    float s = 0.0f;
+    if (i < n_vec) {
+        gdb_vec8<T> a, b;
+        a.raw = go[i];
+        b.raw = out[i];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += a.get(e) * b.get(e);
+        dq32[2 * i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        dq32[2 * i + 1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) s += __shfl_xor_sync(0xffffffffU, s, o);
+    if (i < n_vec && (threadIdx.x & 7) == 0) stats[(i >> 3) * 3U + 2U] = s;
+}
+
+// Backward in one attention pass (head_dim 64, statistics (max, sum) saved by the forward): D from dO and the forward
+// output, then the key-stationary kernel forms dK, dV and accumulates dQ in FP32, then dQ is rounded.
+template <typename T>
+gd_status backward_single_pass(gd_backend *be, const gdb_flash_args *a, const flash_params &p, const void *out, float *dq32)
+{
+    const size_t n = (size_t)a->n_tokens * a->hq * 64U, n_vec = n / 8U;
+    gdb_launch(bwd_prep_kernel<T>, (unsigned)((n_vec + 255U) / 256U), 256, 0, be->stream, (const uint4 *)a->grad_out, (const uint4 *)out, a->stats,
+               (float4 *)dq32, n_vec);
+    gd_status st = gdb_launched(be, "flash_backward_prep");
+    if (st != GD_OK) return st;
+    st = launch_kv<T, 64, 64, true>(be, a, p, dq32);
+    if (st != GD_OK) return st;
+    gdb_launch(dq_convert_kernel<T>, gdb_grid_for(n_vec, 256, be, 8), 256, 0, be->stream, (const float4 *)dq32, (uint4 *)a->out_or_dq, n_vec);
+    return gdb_launched(be, "flash_backward_dq_convert");
 }
 
 template <typename T>
@@ -653,4 +764,16 @@ gd_status gdb_flash_varlen_backward(gd_backend *be, const gdb_flash_args *a, boo
     const flash_params p = make_params(a);
     return a->dtype == GDB_DTYPE_F16 ? backward_typed<__half>(be, a, p, have_forward_stats)
                                      : backward_typed<__nv_bfloat16>(be, a, p, have_forward_stats);
+}
+
+// Backward with the forward output at hand (not part of the reference's entry, src/core/backend.h:699-709): D = rowsum(dO o O)
+// replaces the query-stationary pass. `dq32`: FP32 scratch [N, Hq, 64]. GD_ERR_UNSUPPORTED outside head_dim 64 / the fast path.
+gd_status gdb_flash_varlen_backward_with_out(gd_backend *be, const gdb_flash_args *a, const void *out, float *dq32)
+{
+    const uintptr_t al = (uintptr_t)a->grad_out | (uintptr_t)a->out_or_dq | (uintptr_t)a->dk | (uintptr_t)a->dv | (uintptr_t)out | (uintptr_t)dq32;
+    if (!fast_path(a) || a->dh != 64 || (al % 16U) != 0U || a->stats == NULL || out == NULL || dq32 == NULL) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const flash_params p = make_params(a);
+    return a->dtype == GDB_DTYPE_F16 ? backward_single_pass<__half>(be, a, p, out, dq32) : backward_single_pass<__nv_bfloat16>(be, a, p, out, dq32);
 }

@@ -531,7 +531,15 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             g3.shape[2] = Dh;
             gd_backend_tensor_view gv = tv(g3), q = tv(sv.q), k = tv(sv.k), v = tv(sv.v), cv = tv(cu), dqv = tv(dq), dkv = tv(dk), dvv = tv(dv), stv = tv(sv.stats);
             sa.use_forward_stats = 1;
-            c.ok(gd_backend_sdpa_varlen_backward(be, &gv, &q, &k, &v, &cv, &dqv, &dkv, &dvv, &stv, &sa), "sdpa_varlen_backward");
+            // the forward output is still held for the projection's weight gradient: one attention pass instead of two
+            Ten attn3 = sv.attn;
+            attn3.rank = 3;
+            attn3.shape[0] = T;
+            attn3.shape[1] = H;
+            attn3.shape[2] = Dh;
+            Ten acc = c.alloc(GDB_DTYPE_F32, {T, H, Dh});
+            gd_backend_tensor_view ov = tv(attn3), av = tv(acc);
+            c.ok(gdb200_sdpa_varlen_backward_with_output(be, &gv, &q, &k, &v, &cv, &ov, &dqv, &dkv, &dvv, &stv, &av, &sa), "sdpa_varlen_backward");
         }
         Ten dqkv = c.alloc(dt, {T, 3 * D});
         {

@@ -293,6 +293,7 @@ PROTOTYPES = {
     "gdb200_gemm_profile_read": (_ST, [P, C.POINTER(U64), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "gdb200_matmul_nt_bias": (_ST, [P, MV, MV, VV, MV]),
     "gdb200_matmul_nt_bias_swiglu": (_ST, [P, MV, MV, VV, MV]),
+    "gdb200_sdpa_varlen_backward_with_output": (_ST, [P] + [TV] * 11 + [C.POINTER(SdpaVarlenArgs)]),
     "gdb200_embedding_backward_static": (_ST, [P, P, P, P, U64, U64, U64, U32]),
     "gdb200_embedding_backward_static_error": (C.c_char_p, []),
     "gdb200_embedding_backward_static_max_elems": (U64, []),

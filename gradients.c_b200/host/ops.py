@@ -25,6 +25,8 @@ F32_NEG_INF_PATTERN = 0xFF800000      # :15
 # gd_linear_transposed_weight: use the additive fused entry instead of the reference's two-call
 # sequence (matmul_nt, then add). Both give bit-identical results; tests exercise both.
 FUSE_BIAS_ADD = True
+# gd_sdpa_varlen's backward through gdb200_sdpa_varlen_backward_with_output (False: the reference entry, two passes)
+SDPA_BACKWARD_WITH_OUTPUT = True
 
 
 def _tvp(t: Optional[Tensor]):
@@ -378,8 +380,15 @@ def gd_sdpa_varlen(ctx: Context, q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Te
             dk = ctx.scratch_empty(k.dtype, k.shape, "dk")
             dv = ctx.scratch_empty(v.dtype, v.shape, "dv")
             bargs = abi.SdpaVarlenArgs(scale, args.causal, sliding_window, prefix_len, args.max_seqlen, 1)
-            ctx.check(ctx.lib.gd_backend_sdpa_varlen_backward(ctx.backend, _tvp(out.grad), _tvp(q), _tvp(k), _tvp(v), _tvp(cu_seqlens),
-                                                              _tvp(dq), _tvp(dk), _tvp(dv), _tvp(stats), byref(bargs)), "sdpa_varlen_backward")
+            if SDPA_BACKWARD_WITH_OUTPUT:
+                # the capsule still holds the forward output: the additive entry runs one attention pass where it can
+                acc = ctx.scratch_empty(F32, q.shape, "dq_accum")
+                ctx.check(ctx.lib.gdb200_sdpa_varlen_backward_with_output(ctx.backend, _tvp(out.grad), _tvp(q), _tvp(k), _tvp(v), _tvp(cu_seqlens),
+                                                                          _tvp(out), _tvp(dq), _tvp(dk), _tvp(dv), _tvp(stats), _tvp(acc),
+                                                                          byref(bargs)), "sdpa_varlen_backward")
+            else:
+                ctx.check(ctx.lib.gd_backend_sdpa_varlen_backward(ctx.backend, _tvp(out.grad), _tvp(q), _tvp(k), _tvp(v), _tvp(cu_seqlens),
+                                                                  _tvp(dq), _tvp(dk), _tvp(dv), _tvp(stats), byref(bargs)), "sdpa_varlen_backward")
             ctx.accumulate_grad(q, dq)
             ctx.accumulate_grad(k, dk)
             ctx.accumulate_grad(v, dv)

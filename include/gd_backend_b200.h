@@ -407,6 +407,18 @@ gd_status gdb200_matmul_nt_bias(gd_backend *backend, const gd_backend_matrix_vie
 gd_status gdb200_matmul_nt_bias_swiglu(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
                                        const gd_backend_vector_view *bias, const gd_backend_matrix_view *out);
 
+/* gd_backend_sdpa_varlen_backward (src/core/backend.h:699-709) for a caller that still holds the forward output `out`
+ * [N, Hq, Dh] and can lend FP32 scratch `dq_accum` of q's element count: D = rowsum(grad_out o out) replaces the
+ * query-stationary recomputation, and dK, dV and dQ come from one key-stationary pass (dQ accumulated in dq_accum, then
+ * rounded). Needs the forward's statistics (args->use_forward_stats) and head_dim 64; every other case runs exactly
+ * as gd_backend_sdpa_varlen_backward. Results agree with it to FP32 rounding of D (out is a rounded tensor). */
+gd_status gdb200_sdpa_varlen_backward_with_output(gd_backend *backend, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q,
+                                                  const gd_backend_tensor_view *k, const gd_backend_tensor_view *v,
+                                                  const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *out,
+                                                  const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k,
+                                                  const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats,
+                                                  const gd_backend_tensor_view *dq_accum, const gd_backend_sdpa_varlen_args *args);
+
 /* Weight and bias gradient of a linear layer in one pass over the upstream gradient (no counterpart in the reference,
  * which calls matmul_tn and reduce_rows, src/ops/linear_transposed_weight/core_linear_transposed_weight_bwd.c:31-167):
  * y[M, N] = x^T w with x stored [K, M] and w stored [K, N] (as gd_backend_matmul_tn), and colsum[m] = sum_k x[k, m]

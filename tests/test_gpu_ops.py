@@ -632,3 +632,32 @@ def test_fused_linear_swiglu_is_bit_identical_to_two_calls(step, dtype, m, k, f)
     out65 = ctx.scratch_empty(dtype, (65, f))
     assert lib.gdb200_matmul_nt_bias_swiglu(ctx.backend, byref(big.mv(65, k)), byref(wm), byref(bv), byref(out65.mv(65, f))) == abi.GD_ERR_UNSUPPORTED
     assert lib.gdb200_matmul_nt_bias_swiglu(ctx.backend, byref(xm), byref(wm), byref(bv), byref(ugm)) == abi.GD_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("dtype,lengths,hq,hkv,window", [(F16, [300, 17, 512, 64, 131], 8, 8, 0), (BF16, [257, 90], 4, 2, 0), (F16, [400, 200], 2, 2, 96)])
+def test_sdpa_backward_with_forward_output_matches_the_two_pass_backward(step, dtype, lengths, hq, hkv, window):
+    """gdb200_sdpa_varlen_backward_with_output (D from dO and the forward output, dQ accumulated in FP32 by the
+    key-stationary kernel) against gd_backend_sdpa_varlen_backward on the same tensors, and both against the oracle."""
+    ctx = step
+    n, dh = sum(lengths), 64
+    cu = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    q, k, v, go = (rnd_np(rng(130 + i).standard_normal((n, h, dh)).astype(np.float32) * s, dtype)
+                   for i, (h, s) in enumerate(((hq, 0.5), (hkv, 0.5), (hkv, 1.0), (hq, 1.0))))
+    grads = {}
+    for with_out in (True, False):
+        ops.SDPA_BACKWARD_WITH_OUTPUT = with_out
+        try:
+            qt, kt, vt = dev(ctx, q, dtype), dev(ctx, k, dtype), dev(ctx, v, dtype)
+            qt.requires_grad = kt.requires_grad = vt.requires_grad = True
+            out = ops.gd_sdpa_varlen(ctx, qt, kt, vt, dev(ctx, cu, I32), causal=True, sliding_window=window, max_seqlen=max(lengths))
+            out.grad = dev(ctx, go, dtype)
+            ctx.run_backward()
+            grads[with_out] = (host(qt.grad), host(kt.grad), host(vt.grad))
+        finally:
+            ops.SDPA_BACKWARD_WITH_OUTPUT = True
+    sd = storage_name(dtype)
+    wdq, wdk, wdv = O.sdpa_varlen_backward(t32(go), t32(q), t32(k), t32(v), cu, 0.0, True, window, 0, sd)
+    for i, (want, what, sc) in enumerate(((wdq, "dq", 4), (wdk, "dk", 6), (wdv, "dv", 6))):
+        close(grads[True][i], want, dtype, scale=sc, what=what + " single pass")
+        close(grads[False][i], want, dtype, scale=sc, what=what + " two passes")
+    assert np.array_equal(grads[True][2], grads[False][2])          # dV does not depend on D
