@@ -275,6 +275,25 @@ __device__ __forceinline__ uint64_t gdb_splitmix64(uint64_t x)
     x = (x ^ (x >> 27)) * 0x94D049BB133111EBULL;
     return x ^ (x >> 31);
 }
+
+// Dropout decision of element `index` (src/ops/dropout/metal_dropout.metal: 24 bits of splitmix64(seed + index) against a
+// threshold of ceil(p * 2^24)); one definition for the stand-alone kernels and the fused residual + norm kernel.
+__device__ __forceinline__ bool gdb_dropout_keep(uint64_t seed, uint64_t index, unsigned threshold)
+{
+    const uint64_t r = gdb_splitmix64(seed + index);
+    return (unsigned)((r >> 40) & 0xffffffULL) >= threshold;
+}
+static inline unsigned gdb_dropout_threshold(float p)
+{
+    const double t = ceil((double)p * 16777216.0);
+    if (t <= 0.0) {
+        return 0U;
+    }
+    if (t >= 16777216.0) {
+        return 16777216U;
+    }
+    return (unsigned)t;
+}
 #endif  // __CUDACC__
 
 // ---- entry points implemented in other translation units and shared internally ----
@@ -287,6 +306,12 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype,
                            void *c, size_t ldc_bytes, const void *bias, int bias_mode,
                            uint32_t M, uint32_t N, uint32_t K);
 // At most 64 output rows (decode): mma.sync kernel with K split over the warps of a CTA.
+// sum = residual + dropout(x) (mask written), out = rms_norm(sum, weight), inv_rms saved: gd_backend_dropout_add_forward followed by
+// gd_backend_rms_norm_forward_stats in one launch, same rounding points. GD_ERR_UNSUPPORTED when the vector path does not apply.
+gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *residual, const gd_backend_tensor_view *x,
+                                   const gd_backend_tensor_view *weight, const gd_backend_tensor_view *sum, const gd_backend_tensor_view *mask,
+                                   const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv, size_t rows, size_t cols, float eps,
+                                   float p, uint64_t seed);
 gd_status gdb_gemm_skinny_swiglu(gd_backend *be, uint32_t dtype, const void *a, size_t lda_bytes, const void *w, size_t ldw_bytes,
                                  const void *bias, void *c, size_t ldc_bytes, uint32_t M, uint32_t N, uint32_t K);
 gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,

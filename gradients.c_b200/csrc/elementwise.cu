@@ -160,23 +160,8 @@ gd_status add_typed(gd_backend *be, const gd_backend_tensor_view *x, const gd_ba
 }
 
 // ------------------------------------------------------------------ dropout
-__device__ __forceinline__ bool dropout_keep(uint64_t seed, uint64_t index, unsigned threshold)
-{
-    const uint64_t r = gdb_splitmix64(seed + index);
-    return (unsigned)((r >> 40) & 0xffffffULL) >= threshold;
-}
-
-unsigned dropout_threshold(float p)
-{
-    const double t = ceil((double)p * 16777216.0);
-    if (t <= 0.0) {
-        return 0U;
-    }
-    if (t >= 16777216.0) {
-        return 16777216U;
-    }
-    return (unsigned)t;
-}
+__device__ __forceinline__ bool dropout_keep(uint64_t seed, uint64_t index, unsigned threshold) { return gdb_dropout_keep(seed, index, threshold); }
+unsigned dropout_threshold(float p) { return gdb_dropout_threshold(p); }
 
 // MODE 0: y = dropout(x), write mask. MODE 1: y = residual + dropout(x), write mask.
 // MODE 2: dx = g * keep(seed) * scale (recompute). MODE 3: dx = g * mask * scale.

@@ -296,11 +296,44 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
     sa.causal = 1;
     sa.sliding_window = (uint32_t)s->sdpa_window;
     sa.max_seqlen = (uint32_t)s->context_length;
+    // sum = residual + dropout(y) and normed = rms_norm(sum, w) (inv_rms saved): one launch when the fused kernel takes the
+    // shape, else dropout_add_forward (or add) followed by rms_norm_forward_stats
+    auto residual_then_norm = [&](const Ten &residual, const Ten &y, const Ten &w, uint64_t seed, Ten *sum, Ten *mask, Ten *normed, Ten *inv) {
+        *sum = c.alloc(dt, {T, D});
+        memset(mask, 0, sizeof(*mask));
+        if (drop) {
+            *mask = c.alloc(GDB_DTYPE_U8, {T, D});
+            Ten nrm = c.alloc(dt, {T, D}), iv = c.alloc(GDB_DTYPE_F32, {T});
+            gd_backend_tensor_view r = tv(residual), a = tv(y), wv = tv(w), sv_ = tv(*sum), m = tv(*mask), nv = tv(nrm), ivv = tv(iv);
+            gd_status st = c.st == GD_OK ? gdb_dropout_add_rms_norm(be, &r, &a, &wv, &sv_, &m, &nv, &ivv, (size_t)T, (size_t)D, s->rms_eps, s->dropout_p, seed)
+                                         : GD_ERR_UNSUPPORTED;
+            if (st == GD_OK) {
+                *normed = nrm;
+                *inv = iv;
+                return;
+            }
+            if (st != GD_ERR_UNSUPPORTED) {
+                c.ok(st, "dropout_add + rms_norm");
+            }
+            c.ok(gd_backend_dropout_add_forward(be, &r, &a, &sv_, &m, s->dropout_p, seed), "dropout_add_forward");
+        } else {
+            gd_backend_tensor_view r = tv(residual), a = tv(y), sv_ = tv(*sum);
+            c.ok(gd_backend_add(be, &r, &a, &sv_), "add");
+        }
+        *normed = rms_forward(c, *sum, w, T, D, inv);
+    };
+    Ten next_normed, next_inv;
+    bool have_next_norm = false;
     for (int i = 0; i < L && c.st == GD_OK; ++i) {
         LayerSave &sv = saves[(size_t)i];
         const int pb = 1 + 10 * i;
         sv.x = x;
-        sv.normed = rms_forward(c, x, c.param(pb + 0, {D}), T, D, &sv.inv1);
+        if (have_next_norm) {
+            sv.normed = next_normed;   // produced together with the previous block's residual add
+            sv.inv1 = next_inv;
+        } else {
+            sv.normed = rms_forward(c, x, c.param(pb + 0, {D}), T, D, &sv.inv1);
+        }
         sv.qkv = linear_t(c, sv.normed, c.param(pb + 1, {3 * D, D}), c.param(pb + 2, {3 * D}), T, D, 3 * D);
         sv.q = c.alloc(dt, {T, H, Dh});
         sv.k = c.alloc(dt, {T, H, Dh});
@@ -322,18 +355,8 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             c.ok(gd_backend_sdpa_varlen(be, &q, &k, &v, &cv, &o, &stv, &sa), "sdpa_varlen");
         }
         Ten proj = linear_t(c, sv.attn, c.param(pb + 3, {D, D}), c.param(pb + 4, {D}), T, D, D);
-        sv.resid = c.alloc(dt, {T, D});
-        memset(&sv.mask1, 0, sizeof(sv.mask1));
         memset(&sv.mask2, 0, sizeof(sv.mask2));
-        if (drop) {
-            sv.mask1 = c.alloc(GDB_DTYPE_U8, {T, D});
-            gd_backend_tensor_view r = tv(x), a = tv(proj), y = tv(sv.resid), m = tv(sv.mask1);
-            c.ok(gd_backend_dropout_add_forward(be, &r, &a, &y, &m, s->dropout_p, seed_of(SITE_ATTN, (uint64_t)i)), "dropout_add_forward");
-        } else {
-            gd_backend_tensor_view r = tv(x), a = tv(proj), y = tv(sv.resid);
-            c.ok(gd_backend_add(be, &r, &a, &y), "add");
-        }
-        sv.normed2 = rms_forward(c, sv.resid, c.param(pb + 5, {D}), T, D, &sv.inv2);
+        residual_then_norm(x, proj, c.param(pb + 5, {D}), seed_of(SITE_ATTN, (uint64_t)i), &sv.resid, &sv.mask1, &sv.normed2, &sv.inv2);
         sv.up_gate = linear_t(c, sv.normed2, c.param(pb + 6, {2 * F, D}), c.param(pb + 7, {2 * F}), T, D, 2 * F);
         sv.act = c.alloc(dt, {T, F});
         {
@@ -347,20 +370,21 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             gd_backend_vector_view bv = vv(b, 0, (uint32_t)D);
             c.ok(gd_backend_linear(be, &am, &wm, &bv, &ym), "linear(down_proj)");
         }
-        Ten out = c.alloc(dt, {T, D});
-        if (drop) {
-            sv.mask2 = c.alloc(GDB_DTYPE_U8, {T, D});
-            gd_backend_tensor_view r = tv(sv.resid), a = tv(mlp), y = tv(out), m = tv(sv.mask2);
-            c.ok(gd_backend_dropout_add_forward(be, &r, &a, &y, &m, s->dropout_p, seed_of(SITE_MLP, (uint64_t)i)), "dropout_add_forward");
-        } else {
-            gd_backend_tensor_view r = tv(sv.resid), a = tv(mlp), y = tv(out);
-            c.ok(gd_backend_add(be, &r, &a, &y), "add");
-        }
+        // the norm that consumes this block's output: the next block's attention norm, or the final norm
+        Ten out;
+        residual_then_norm(sv.resid, mlp, i + 1 < L ? c.param(1 + 10 * (i + 1), {D}) : c.param(P_FINAL, {D}), seed_of(SITE_MLP, (uint64_t)i), &out,
+                           &sv.mask2, &next_normed, &next_inv);
+        have_next_norm = true;
         x = out;
     }
-    Ten inv_f;
     const Ten final_w = c.param(P_FINAL, {D});
-    Ten final_norm = rms_forward(c, x, final_w, T, D, &inv_f);
+    Ten inv_f, final_norm;
+    if (have_next_norm) {
+        final_norm = next_normed;
+        inv_f = next_inv;
+    } else {
+        final_norm = rms_forward(c, x, final_w, T, D, &inv_f);
+    }
 
     // ---- fused LM cross entropy (chunked over the vocabulary, src/ops/lm_cross_entropy/core_lm_cross_entropy.c:452-675) ----
     const Ten lm_w = c.param(P_LMW, {V, D}), lm_b = c.param(P_LMB, {V});

@@ -83,8 +83,11 @@ __global__ void rms_fwd_kernel(const T *x, const T *w, T *out, float *inv_out, s
 
 // sum = round(x + y); out = round(sum * w * inv_rms(sum)): gd_backend_add followed by rms_norm_forward in one launch
 // (same rounding points). Warp per row, cols % 8 == 0, 16-byte aligned 16-bit tensors.
-template <typename T>
-__global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *w, uint4 *sum, uint4 *out, size_t rows, size_t cols, float eps)
+// DROP: y goes through inverted dropout first (round(y * scale) or 0, decision per element index, mask bytes written),
+// i.e. gd_backend_dropout_add_forward; inv_out != NULL saves 1 / rms per row (rms_norm_forward_stats).
+template <typename T, bool DROP>
+__global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *w, uint4 *sum, uint4 *out, size_t rows, size_t cols, float eps,
+                                   uint2 *mask_out, float *inv_out, float scale, uint64_t seed, unsigned threshold)
 {
     gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
@@ -98,16 +101,26 @@ __global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *
         gdb_vec8<T> a, b;
         a.raw = x[base + v];
         b.raw = y[base + v];
+        uint2 m = make_uint2(0U, 0U);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            a.set(e, a.get(e) + b.get(e));
+            float add = b.get(e);
+            if (DROP) {
+                const bool keep = gdb_dropout_keep(seed, (uint64_t)(base + v) * 8U + (uint64_t)e, threshold);
+                unsigned *mw = e < 4 ? &m.x : &m.y;
+                *mw |= (keep ? 1U : 0U) << (8U * (unsigned)(e & 3));
+                add = keep ? gdb_io<T>::rnd(add * scale) : 0.0f;
+            }
+            a.set(e, a.get(e) + add);
             const float f = a.get(e);
             ss += f * f;
         }
         sum[base + v] = a.raw;
+        if (DROP) mask_out[base + v] = m;
     }
     ss = gdb_warp_sum(ss);
     const float inv = rsqrtf(ss / (float)cols + eps);
+    if (inv_out != nullptr && lane == 0) inv_out[row] = inv;
     for (size_t v = lane; v < vecs; v += 32) {
         gdb_vec8<T> a, b;
         a.raw = sum[base + v];   // written by this lane above
@@ -439,9 +452,51 @@ gd_status gdb_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *x, cons
     }
     const unsigned grid = (unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
     if (dt == GDB_DTYPE_F16) {
-        gdb_launch(add_rms_fwd_kernel<__half>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps);
+        gdb_launch(add_rms_fwd_kernel<__half, false>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps,
+                   (uint2 *)nullptr, (float *)nullptr, 1.0f, (uint64_t)0, 0U);
     } else {
-        gdb_launch(add_rms_fwd_kernel<__nv_bfloat16>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps);
+        gdb_launch(add_rms_fwd_kernel<__nv_bfloat16, false>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps,
+                   (uint2 *)nullptr, (float *)nullptr, 1.0f, (uint64_t)0, 0U);
     }
     return gdb_launched(be, "add_rms_norm");
+}
+
+gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *residual, const gd_backend_tensor_view *x,
+                                   const gd_backend_tensor_view *weight, const gd_backend_tensor_view *sum, const gd_backend_tensor_view *mask,
+                                   const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv, size_t rows, size_t cols, float eps,
+                                   float p, uint64_t seed)
+{
+    if (be == NULL || residual == NULL || x == NULL || weight == NULL || sum == NULL || mask == NULL || out == NULL || inv == NULL || rows == 0U ||
+        cols == 0U || !(p >= 0.0f && p < 1.0f)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = x->dtype;
+    if ((dt != GDB_DTYPE_F16 && dt != GDB_DTYPE_BF16) || (cols % 8U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (x->count != rows * cols || residual->count != x->count || sum->count != x->count || out->count != x->count || mask->count != x->count ||
+        weight->count != cols || inv->count != rows || residual->dtype != dt || sum->dtype != dt || out->dtype != dt || weight->dtype != dt) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const void *rp = gdb_tv_ptr(residual, dt), *xp = gdb_tv_ptr(x, dt), *wp = gdb_tv_ptr(weight, dt);
+    void *sp = gdb_tv_ptr(sum, dt), *op = gdb_tv_ptr(out, dt), *mp = gdb_tv_ptr(mask, GDB_DTYPE_U8);
+    float *ip = (float *)gdb_tv_ptr(inv, GDB_DTYPE_F32);
+    if (rp == NULL || xp == NULL || wp == NULL || sp == NULL || op == NULL || mp == NULL || ip == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if ((((uintptr_t)rp | (uintptr_t)xp | (uintptr_t)wp | (uintptr_t)sp | (uintptr_t)op) % 16U) != 0U || ((uintptr_t)mp % 8U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    cudaSetDevice(be->device);
+    const unsigned grid = (unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
+    const float scale = 1.0f / (1.0f - p);
+    const unsigned threshold = gdb_dropout_threshold(p);
+    if (dt == GDB_DTYPE_F16) {
+        gdb_launch(add_rms_fwd_kernel<__half, true>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)rp, (const uint4 *)xp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps,
+                   (uint2 *)mp, ip, scale, seed, threshold);
+    } else {
+        gdb_launch(add_rms_fwd_kernel<__nv_bfloat16, true>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)rp, (const uint4 *)xp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps,
+                   (uint2 *)mp, ip, scale, seed, threshold);
+    }
+    return gdb_launched(be, "dropout_add_rms_norm");
 }
