@@ -593,7 +593,9 @@ flash_kv_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
                     if (rowB < n_valid) red_add_v2(dB + n * 8, dqa[n][2], dqa[n][3]);
                 }
             }
-            __syncthreads();
+            // The Q / dO stage of this iteration is last read before the barrier that precedes the dQ product, and the dS
+            // tile is next written after the barrier at the top of the next iteration: the fused form needs no third barrier.
+            if (!FUSE_DQ) __syncthreads();
         }
     }
 #pragma unroll
