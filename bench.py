@@ -47,7 +47,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "linear", "sdpa"])
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "linear", "sdpa", "timeline"],
+                    help="timeline: per-kernel time of the running train step from CUPTI activity records (not a bench line)")
     ap.add_argument("--cpu-sample-seqs", type=int, default=8, help="sequences in the CPU-baseline sample batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--host", default="native", choices=["native", "python"],
@@ -522,6 +523,50 @@ def run_decode(args) -> None:
     ctx.destroy()
 
 
+def run_timeline(args) -> None:
+    """Per-kernel time of the default train step as it runs (real cache state, programmatic dependent launch in effect):
+    CUPTI activity records collected by torch.profiler around `--steps` steps (default 100 is capped at 8). Kernels are
+    launched before their predecessor ends and then wait, so raw durations overlap; the time attributed to a kernel is the
+    increment of the completion front, end(k) - max(end(k-1), start(k)), which sums to the step. Prints a markdown table."""
+    import collections
+    import re
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    g = pkg.gpt_lm
+    cfg, tc = g.GptConfig.baseline(), g.TrainConfig.baseline()
+    ctx = pkg.runtime.Context(params_bytes=256 << 20, state_bytes=1 << 30, scratch_bytes=10 << 30, data_bytes=64 << 20)
+    trainer = g.NativeTrainer(g.GptLm(ctx, cfg, g.init_params(cfg, seed=0)), tc)
+    steps, warm = min(args.steps, 8), max(args.warmup, 3)
+    batches = [g.synthetic_batch(cfg, 64, 64, 512, seed=10_000 + s, pad_to=cfg.context_length) for s in range(warm + steps)]
+    staged = [tuple(ctx.from_numpy(ctx.state, pkg.abi.I32, a) for a in (b.input_ids, b.targets, b.positions, b.cu_seqlens)) for b in batches]
+    for s in range(warm):
+        trainer.train_batch(batches[s], device_batch=staged[s])
+    ctx.flush()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for s in range(warm, warm + steps):
+            trainer.train_batch(batches[s], device_batch=staged[s])
+        ctx.flush()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.end)
+    agg = collections.defaultdict(lambda: [0, 0.0, 0.0])
+    prev_end, t0, t1 = ev[0].time_range.start, ev[0].time_range.start, ev[-1].time_range.end
+    for e in ev:
+        name = re.sub(r"\(.*", "", e.name.replace("void ", "").replace("(anonymous namespace)::", "").replace("gdb_t5::", ""))
+        a = agg[name]
+        a[0] += 1
+        a[1] += e.time_range.end - max(prev_end, e.time_range.start)
+        a[2] += e.time_range.end - e.time_range.start
+        prev_end = e.time_range.end
+    tot = sum(v[1] for v in agg.values())
+    print(f"span {(t1 - t0) / steps:.1f} us/step, attributed {tot / steps:.1f} us/step, {len(ev)} records over {steps} steps")
+    print("| kernel | launches/step | us/step (completion increments) | share | avg us | avg raw duration us |")
+    print("|---|---|---|---|---|---|")
+    for name, (c, t, d) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        print(f"| {name[:64]} | {c / steps:.1f} | {t / steps:.1f} | {100 * t / tot:.1f}% | {t / c:.1f} | {d / c:.1f} |")
+    ctx.destroy()
+
+
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
@@ -532,6 +577,8 @@ def main() -> None:
         run_sdpa(args)
     elif args.workload == "decode":
         run_decode(args)
+    elif args.workload == "timeline":
+        run_timeline(args)
     else:
         run_b200(args)
 
