@@ -179,7 +179,7 @@ static inline cudaError_t gdb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 b
 __device__ __forceinline__ float gdb_swiglu_sigmoid(float x)
 {
     const float e = __expf(-fabsf(x));
-    const float inv = 1.0f / (1.0f + e);
+    const float inv = __fdividef(1.0f, 1.0f + e);   // 1 + e lies in [1, 2]: the approximate reciprocal is good to 1-2 ulp there
     return x >= 0.0f ? inv : e * inv;
 }
 

@@ -279,15 +279,16 @@ __global__ void swiglu_fwd_kernel(const T *x1, const T *x2, T *out, size_t rows,
     }
 }
 template <typename T>
-__global__ void swiglu_fwd_vec8_kernel(const uint4 *x1, const uint4 *x2, uint4 *out, size_t rows, size_t hv, size_t in_ldv)
+__global__ void swiglu_fwd_vec8_kernel(const uint4 *x1, const uint4 *x2, uint4 *out, unsigned rows, unsigned hv, unsigned in_ldv)
 {
     gdb_pdl_sync();
-    const size_t n = rows * hv, stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const size_t r = i / hv, c = i - r * hv;
+    // 32-bit index arithmetic (the host checks rows * hv < 2^32): a 64-bit division per 16-byte vector costs more than the gate
+    const unsigned n = rows * hv, stride = gridDim.x * blockDim.x;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const unsigned r = i / hv, c = i - r * hv;
         gdb_vec8<T> a, b;
-        a.raw = x1[r * in_ldv + c];
-        b.raw = x2[r * in_ldv + c];
+        a.raw = x1[(size_t)r * in_ldv + c];
+        b.raw = x2[(size_t)r * in_ldv + c];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const float z = b.get(e);
@@ -317,15 +318,15 @@ __global__ void swiglu_bwd_kernel(const T *x1, const T *x2, const T *go, T *dx1,
 }
 template <typename T>
 __global__ void swiglu_bwd_vec8_kernel(const uint4 *x1, const uint4 *x2, const uint4 *go, uint4 *dx1, uint4 *dx2,
-                                       size_t rows, size_t hv, size_t in_ldv, size_t out_ldv)
+                                       unsigned rows, unsigned hv, unsigned in_ldv, unsigned out_ldv)
 {
     gdb_pdl_sync();
-    const size_t n = rows * hv, stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const size_t r = i / hv, c = i - r * hv;
+    const unsigned n = rows * hv, stride = gridDim.x * blockDim.x;   // 32-bit index arithmetic, see the forward kernel
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const unsigned r = i / hv, c = i - r * hv;
         gdb_vec8<T> a, b, g, d1, d2;
-        a.raw = x1[r * in_ldv + c];
-        b.raw = x2[r * in_ldv + c];
+        a.raw = x1[(size_t)r * in_ldv + c];
+        b.raw = x2[(size_t)r * in_ldv + c];
         g.raw = go[i];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -333,8 +334,8 @@ __global__ void swiglu_bwd_vec8_kernel(const uint4 *x1, const uint4 *x2, const u
             d1.set(e, gv * (z * s));
             d2.set(e, gv * a.get(e) * (s * (1.0f + z * (1.0f - s))));
         }
-        dx1[r * out_ldv + c] = d1.raw;
-        dx2[r * out_ldv + c] = d2.raw;
+        dx1[(size_t)r * out_ldv + c] = d1.raw;
+        dx2[(size_t)r * out_ldv + c] = d2.raw;
     }
 }
 
@@ -342,8 +343,8 @@ template <typename T>
 gd_status swiglu_fwd_typed(gd_backend *be, const void *x1, const void *x2, void *out, size_t rows, size_t h, size_t in_ld)
 {
     const uintptr_t al = (uintptr_t)x1 | (uintptr_t)x2 | (uintptr_t)out;
-    if ((al % 16U) == 0U && (h % 8U) == 0U && (in_ld % 8U) == 0U) {
-        gdb_launch(swiglu_fwd_vec8_kernel<T>, gdb_grid_for(rows * h / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)x1, (const uint4 *)x2, (uint4 *)out, rows, h / 8U, in_ld / 8U);
+    if ((al % 16U) == 0U && (h % 8U) == 0U && (in_ld % 8U) == 0U && rows * (h / 8U) < 0xffffffffULL && in_ld / 8U < 0xffffffffULL) {
+        gdb_launch(swiglu_fwd_vec8_kernel<T>, gdb_grid_for(rows * h / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)x1, (const uint4 *)x2, (uint4 *)out, (unsigned)rows, (unsigned)(h / 8U), (unsigned)(in_ld / 8U));
     } else {
         gdb_launch(swiglu_fwd_kernel<T>, gdb_grid_for(rows * h, 256, be, 8), 256, 0, be->stream, (const T *)x1, (const T *)x2, (T *)out, rows, h, in_ld);
     }
@@ -354,8 +355,8 @@ gd_status swiglu_bwd_typed(gd_backend *be, const void *x1, const void *x2, const
                            size_t rows, size_t h, size_t in_ld, size_t out_ld)
 {
     const uintptr_t al = (uintptr_t)x1 | (uintptr_t)x2 | (uintptr_t)go | (uintptr_t)dx1 | (uintptr_t)dx2;
-    if (dx1 != NULL && dx2 != NULL && (al % 16U) == 0U && (h % 8U) == 0U && (in_ld % 8U) == 0U && (out_ld % 8U) == 0U) {
-        gdb_launch(swiglu_bwd_vec8_kernel<T>, gdb_grid_for(rows * h / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)x1, (const uint4 *)x2, (const uint4 *)go, (uint4 *)dx1, (uint4 *)dx2, rows, h / 8U, in_ld / 8U, out_ld / 8U);
+    if (dx1 != NULL && dx2 != NULL && (al % 16U) == 0U && (h % 8U) == 0U && (in_ld % 8U) == 0U && (out_ld % 8U) == 0U && rows * (h / 8U) < 0xffffffffULL && in_ld / 8U < 0xffffffffULL && out_ld / 8U < 0xffffffffULL) {
+        gdb_launch(swiglu_bwd_vec8_kernel<T>, gdb_grid_for(rows * h / 8U, 256, be, 8), 256, 0, be->stream, (const uint4 *)x1, (const uint4 *)x2, (const uint4 *)go, (uint4 *)dx1, (uint4 *)dx2, (unsigned)rows, (unsigned)(h / 8U), (unsigned)(in_ld / 8U), (unsigned)(out_ld / 8U));
     } else {
         gdb_launch(swiglu_bwd_kernel<T>, gdb_grid_for(rows * h, 256, be, 8), 256, 0, be->stream, (const T *)x1, (const T *)x2, (const T *)go, (T *)dx1, (T *)dx2, rows, h, in_ld, out_ld);
     }
