@@ -460,7 +460,8 @@ gd_status gd_backend_fill(gd_backend *be, gd_backend_buffer *buffer, size_t offs
     for (size_t b = 1; b < elem_size; ++b) {
         uniform = uniform && (((pattern >> (8U * b)) & 255U) == bytepat);
     }
-    if (uniform) {
+    // small fills go through the kernel: a memset node between two kernels gives up their programmatic launch overlap
+    if (uniform && count * elem_size > (1U << 20)) {
         cudaError_t e = cudaMemsetAsync(dst, (int)bytepat, count * elem_size, be->stream);
         be->launches += 1U;
         return e == cudaSuccess ? GD_OK : gdb_fail(be, e, "fill");

@@ -152,10 +152,20 @@ __global__ void qkv_split_rope_vec8_kernel(const T *a0, const T *a1, const T *a2
     const size_t area = (size_t)p.heads * p.head_dim;
     const size_t n = p.tokens * p.heads * groups, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const unsigned grp = (unsigned)(i % groups);
-        const size_t th = i / groups;
-        const unsigned h = (unsigned)(th % p.heads);
-        const size_t token = th / p.heads;
+        unsigned grp, h;
+        size_t token;
+        if (n <= 0xffffffffULL) {   // 32-bit divisions (a 64-bit one costs tens of instructions per vector)
+            const unsigned iu = (unsigned)i, th = iu / groups;
+            grp = iu - th * groups;
+            const unsigned tk = th / (unsigned)p.heads;
+            h = th - tk * (unsigned)p.heads;
+            token = tk;
+        } else {
+            grp = (unsigned)(i % groups);
+            const size_t th = i / groups;
+            h = (unsigned)(th % p.heads);
+            token = th / p.heads;
+        }
         const int pos = __ldg(&pos_ids[token]);
         const size_t packed = token * area * 3U + (size_t)h * p.head_dim + grp * 8U;
         const size_t split = token * area + (size_t)h * p.head_dim + grp * 8U;
