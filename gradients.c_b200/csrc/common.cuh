@@ -312,6 +312,9 @@ gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view 
                                    const gd_backend_tensor_view *weight, const gd_backend_tensor_view *sum, const gd_backend_tensor_view *mask,
                                    const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv, size_t rows, size_t cols, float eps,
                                    float p, uint64_t seed);
+gd_status gdb_rms_norm_backward_accumulate(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                                           const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
+                                           const gd_backend_tensor_view *grad_accum, const gd_backend_rms_norm_args *args);
 gd_status gdb_gemm_skinny_swiglu(gd_backend *be, uint32_t dtype, const void *a, size_t lda_bytes, const void *w, size_t ldw_bytes,
                                  const void *bias, void *c, size_t ldc_bytes, uint32_t M, uint32_t N, uint32_t K);
 gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,

@@ -200,12 +200,19 @@ Ten rms_forward(Step &c, const Ten &x, const Ten &w, int64_t rows, int64_t cols,
     return out;
 }
 
-Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten &g, int64_t rows, int64_t cols, const Ten &dw)
+// `accum` != NULL: the input gradient is added into *accum (rounded, then added, then rounded: the two calls
+// rms_norm_backward_stats + accumulate in one launch) and *accum is returned.
+Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten &g, int64_t rows, int64_t cols, const Ten &dw,
+                 const Ten *accum = nullptr)
 {
     gd_backend_rms_norm_args a = rms_args(rows, cols, c.s->rms_eps);
-    Ten dx = c.alloc(x.dt, {rows, cols});
+    Ten dx = accum != nullptr ? *accum : c.alloc(x.dt, {rows, cols});
     gd_backend_tensor_view xv = tv(x), wv = tv(w), iv = tv(inv), gv = tv(g), dxv = tv(dx), dwv = tv(dw);
-    c.ok(gd_backend_rms_norm_backward_stats(c.be, &xv, &wv, &iv, &gv, &dxv, &a), "rms_norm_backward_stats");
+    if (accum != nullptr) {
+        c.ok(gdb_rms_norm_backward_accumulate(c.be, &xv, &wv, &iv, &gv, &dxv, &a), "rms_norm_backward_stats + accumulate");
+    } else {
+        c.ok(gd_backend_rms_norm_backward_stats(c.be, &xv, &wv, &iv, &gv, &dxv, &a), "rms_norm_backward_stats");
+    }
     Ten partial = c.alloc(GDB_DTYPE_F32, {(int64_t)a.row_blocks, cols});
     gd_backend_tensor_view pv = tv(partial);
     c.ok(gd_backend_rms_norm_weight_backward_stats(c.be, &xv, &iv, &gv, &dwv, &pv, &a), "rms_norm_weight_backward_stats");
@@ -539,8 +546,7 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             c.ok(gd_backend_swiglu_split_backward(be, &xv, &dav, &duv), "swiglu_split_backward");
             Ten dn2;
             linear_t_backward(c, sv.normed2, c.param(pb + 6, {2 * F, D}), d_up, T, D, 2 * F, &dn2, grads[(size_t)pb + 6], grads[(size_t)pb + 7]);
-            Ten d_res2 = rms_backward(c, sv.resid, c.param(pb + 5, {D}), sv.inv2, dn2, T, D, grads[(size_t)pb + 5]);
-            c.accumulate(g_resid, d_res2);
+            rms_backward(c, sv.resid, c.param(pb + 5, {D}), sv.inv2, dn2, T, D, grads[(size_t)pb + 5], &g_resid);
         }
         // resid = x + dropout(proj)
         Ten g_proj = drop ? dropout_mask_backward(c, sv.mask1, g_resid, drop_scale) : g_resid;
@@ -572,8 +578,7 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         }
         Ten dn1;
         linear_t_backward(c, sv.normed, c.param(pb + 1, {3 * D, D}), dqkv, T, D, 3 * D, &dn1, grads[(size_t)pb + 1], grads[(size_t)pb + 2]);
-        Ten d_x1 = rms_backward(c, sv.x, c.param(pb + 0, {D}), sv.inv1, dn1, T, D, grads[(size_t)pb + 0]);
-        c.accumulate(g_resid, d_x1);
+        rms_backward(c, sv.x, c.param(pb + 0, {D}), sv.inv1, dn1, T, D, grads[(size_t)pb + 0], &g_resid);
         gx = g_resid;
         reduce_range(goff, gelems);
         c.top = layer_mark;

@@ -135,7 +135,7 @@ __global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *
 
 // STATS true: inv read from inv_in; false: recomputed from x.
 template <typename T, bool STATS>
-__global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, const T *g, T *dx, size_t rows, size_t cols, float eps)
+__global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, const T *g, T *dx, size_t rows, size_t cols, float eps, bool add_to_dx)
 {
     gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
@@ -196,13 +196,21 @@ __global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, cons
                 for (int e = 0; e < 8; ++e) {
                     ga.set(e, inv * ga.get(e) * wa.get(e) - xa.get(e) * k * a);
                 }
+                if (add_to_dx) {
+                    // dx += rounded gradient, rounded again: rms_norm_backward followed by gd_backend_accumulate, in place
+                    gdb_vec8<T> da;
+                    da.raw = dv[v];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ga.set(e, da.get(e) + ga.get(e));
+                }
                 dv[v] = ga.raw;
             }
             return;
         }
     }
     for (size_t c = lane; c < cols; c += 32) {
-        gdb_io<T>::st(dr, c, inv * gdb_io<T>::ld(gr, c) * gdb_io<T>::ld(w, c) - gdb_io<T>::ld(xr, c) * k * a);
+        const float val = inv * gdb_io<T>::ld(gr, c) * gdb_io<T>::ld(w, c) - gdb_io<T>::ld(xr, c) * k * a;
+        gdb_io<T>::st(dr, c, add_to_dx ? gdb_io<T>::ld(dr, c) + gdb_io<T>::rnd(val) : val);
     }
 }
 
@@ -312,7 +320,7 @@ gd_status fwd_dispatch(gd_backend *be, const gd_backend_tensor_view *x, const gd
 template <bool STATS>
 gd_status bwd_dispatch(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
                        const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
-                       const gd_backend_tensor_view *grad_x, const gd_backend_rms_norm_args *a)
+                       const gd_backend_tensor_view *grad_x, const gd_backend_rms_norm_args *a, bool add_to_dx = false)
 {
     if (be == NULL || x == NULL || weight == NULL || grad_out == NULL || grad_x == NULL || !args_ok(a) ||
         x->count != a->rows * a->cols || weight->count != a->cols || grad_out->count != x->count ||
@@ -331,11 +339,11 @@ gd_status bwd_dispatch(gd_backend *be, const gd_backend_tensor_view *x, const gd
     const unsigned grid = (unsigned)((a->rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
     const unsigned threads = 32 * ROWS_PER_BLOCK;
     if (x->dtype == GDB_DTYPE_F16) {
-        gdb_launch(rms_bwd_kernel<__half, STATS>, grid, threads, 0, be->stream, (const __half *)xp, (const __half *)wp, ip, (const __half *)gp, (__half *)dp, a->rows, a->cols, a->eps);
+        gdb_launch(rms_bwd_kernel<__half, STATS>, grid, threads, 0, be->stream, (const __half *)xp, (const __half *)wp, ip, (const __half *)gp, (__half *)dp, a->rows, a->cols, a->eps, add_to_dx);
     } else if (x->dtype == GDB_DTYPE_BF16) {
-        gdb_launch(rms_bwd_kernel<__nv_bfloat16, STATS>, grid, threads, 0, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip, (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, a->rows, a->cols, a->eps);
+        gdb_launch(rms_bwd_kernel<__nv_bfloat16, STATS>, grid, threads, 0, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip, (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, a->rows, a->cols, a->eps, add_to_dx);
     } else {
-        gdb_launch(rms_bwd_kernel<float, STATS>, grid, threads, 0, be->stream, (const float *)xp, (const float *)wp, ip, (const float *)gp, (float *)dp, a->rows, a->cols, a->eps);
+        gdb_launch(rms_bwd_kernel<float, STATS>, grid, threads, 0, be->stream, (const float *)xp, (const float *)wp, ip, (const float *)gp, (float *)dp, a->rows, a->cols, a->eps, add_to_dx);
     }
     return gdb_launched(be, "rms_norm_backward");
 }
@@ -459,6 +467,15 @@ gd_status gdb_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *x, cons
                    (uint2 *)nullptr, (float *)nullptr, 1.0f, (uint64_t)0, 0U);
     }
     return gdb_launched(be, "add_rms_norm");
+}
+
+// grad_accum += rms_norm_backward(x, weight, inv_rms, grad_out): gd_backend_rms_norm_backward_stats followed by
+// gd_backend_accumulate of its result (src/autograd/autograd.c:517-685: 16-bit storage rounds after every add) in one launch.
+gd_status gdb_rms_norm_backward_accumulate(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                                           const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
+                                           const gd_backend_tensor_view *grad_accum, const gd_backend_rms_norm_args *args)
+{
+    return bwd_dispatch<true>(be, x, weight, inv_rms, grad_out, grad_accum, args, true);
 }
 
 gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *residual, const gd_backend_tensor_view *x,
