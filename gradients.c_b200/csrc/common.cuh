@@ -46,6 +46,9 @@ struct gd_backend {
     size_t l2_flush_bytes;
     gdb_tmap_cache *tmaps;
     gdb_dp_state *dp;
+    // scratch offsets of the parameter gradients of the last gdb200_gpt_train_step (valid until the arena is reused)
+    int32_t last_grad_count;
+    size_t last_grad_offset[GDB200_GPT_MAX_PARAMS];
 };
 
 enum { GDB_BUF_DEVICE = 0, GDB_BUF_MANAGED = 1 };
@@ -312,6 +315,13 @@ gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view 
                                    const gd_backend_tensor_view *weight, const gd_backend_tensor_view *sum, const gd_backend_tensor_view *mask,
                                    const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv, size_t rows, size_t cols, float eps,
                                    float p, uint64_t seed);
+// Loss normaliser of a data-parallel step: counts F32 [2] = {valid target rows of the global batch, of this rank's shard}.
+// gdb_lm_ce_count_valid writes the local count into both; the caller sums element 0 over the ranks before
+// gdb_lm_ce_reduce_normalize_global divides by it (the reference's kernel, src/ops/lm_cross_entropy/metal_lm_cross_entropy.metal:244-252,
+// divides by the local count because it knows one device only).
+gd_status gdb_lm_ce_count_valid(gd_backend *be, const gd_backend_tensor_view *targets, int32_t ignore_index, const gd_backend_tensor_view *counts);
+gd_status gdb_lm_ce_reduce_normalize_global(gd_backend *be, const gd_backend_tensor_view *row_loss, const gd_backend_tensor_view *counts,
+                                            const gd_backend_tensor_view *loss, const gd_backend_tensor_view *inv_valid_count);
 gd_status gdb_rms_norm_backward_accumulate(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
                                            const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
                                            const gd_backend_tensor_view *grad_accum, const gd_backend_rms_norm_args *args);

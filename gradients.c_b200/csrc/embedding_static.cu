@@ -26,7 +26,9 @@ namespace {
 static __device__ __align__(256) float g_static_table[GDB200_STATIC_EMBEDDING_MAX_ELEMS];
 
 constexpr int MAX_DEVICES = 64;
-float *g_table_addr[MAX_DEVICES];  // device address of g_static_table, per device, filled on first use
+// Device address of g_static_table, per device, filled on first use. Host threads may race on the first call for a
+// device; every one of them obtains the same address from cudaGetSymbolAddress, so the duplicate stores are harmless.
+float *g_table_addr[MAX_DEVICES];
 thread_local char g_error[192];
 
 template <typename T>
@@ -112,6 +114,9 @@ gd_status gdb200_embedding_backward_static(void *stream, const void *grad_out, c
         snprintf(g_error, sizeof(g_error), "vocab * dim = %llu exceeds the static scratch of %u floats",
                  (unsigned long long)(vocab * dim), GDB200_STATIC_EMBEDDING_MAX_ELEMS);
         return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (ids_count > SIZE_MAX / dim) {
+        return fail(GD_ERR_INVALID_ARGUMENT, "ids_count * dim overflows size_t");
     }
     float *table = NULL;
     gd_status st = table_for_current_device(&table);

@@ -279,6 +279,26 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
     amp.max_scale = s->amp_max_scale;
     amp.growth_interval = s->amp_growth_interval;
 
+    // ---- loss normaliser of a sharded batch: the number of valid target rows of the GLOBAL batch ----
+    // Known from the targets alone, so it is counted and summed over the ranks first and the collective
+    // hides behind the forward pass. A caller that knows the figure passes it in spec->global_valid_rows.
+    const bool dp = be->dp != NULL && s->dp_world > 1;
+    const bool global_norm = dp || s->global_valid_rows > 0.0f;
+    Ten counts;
+    memset(&counts, 0, sizeof(counts));
+    if (global_norm) {
+        counts = c.alloc(GDB_DTYPE_F32, {2});
+        gd_backend_tensor_view tgv0 = tv(tgt), cv0 = tv(counts);
+        c.ok(gdb_lm_ce_count_valid(be, &tgv0, s->pad_token_id, &cv0), "lm_ce_count_valid");
+        if (s->global_valid_rows > 0.0f) {
+            uint32_t bits;
+            memcpy(&bits, &s->global_valid_rows, sizeof(bits));
+            c.ok(gd_backend_fill(be, counts.buf, counts.off, 1, sizeof(float), bits), "fill(global rows)");
+        } else {
+            c.ok(gdb200_dp_all_reduce(be, counts.buf, counts.off, 1, GDB_DTYPE_F32), "dp_all_reduce(valid rows)");
+        }
+    }
+
     // ---------------------------------------------------------------- forward
     const Ten emb_w = c.param(0, {V, D});
     Ten x0 = c.alloc(dt, {T, D});
@@ -421,7 +441,15 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         if (single) saved_logits = logits;
     }
     c.ok(gd_backend_lm_cross_entropy_finalize(be, &tgv, &rlv, &rmv, &rsv, &rvv, (uint64_t)V, s->pad_token_id), "lm_ce_finalize");
-    c.ok(gd_backend_lm_cross_entropy_reduce_normalize(be, &rlv, &rvv, &lov, &ivv), "lm_ce_reduce_normalize");
+    if (global_norm) {
+        // loss = this rank's share of the global mean; the shares are summed below so that every rank reports the mean
+        gd_backend_tensor_view cv1 = tv(counts);
+        if (dp && !(s->global_valid_rows > 0.0f)) c.ok(gdb200_dp_join(be), "dp_join(valid rows)");
+        c.ok(gdb_lm_ce_reduce_normalize_global(be, &rlv, &cv1, &lov, &ivv), "lm_ce_reduce_normalize(global)");
+        if (dp) c.ok(gdb200_dp_all_reduce(be, loss.buf, loss.off, 1, GDB_DTYPE_F32), "dp_all_reduce(loss)");
+    } else {
+        c.ok(gd_backend_lm_cross_entropy_reduce_normalize(be, &rlv, &rvv, &lov, &ivv), "lm_ce_reduce_normalize");
+    }
     *loss_offset = loss.off;
     if (c.st != GD_OK) {
         snprintf(be->last_error, sizeof(be->last_error), "gpt step forward: %s", c.where);
@@ -453,7 +481,6 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         *range_off = block.off;
         *range_elems = total;
     };
-    const bool dp = be->dp != NULL && s->dp_world > 1;
     // Default: ONE all-reduce over the whole (contiguous) gradient range after the backward pass. GDB200_DP_OVERLAP=1
     // issues one collective per transformer block as soon as that block's backward is enqueued instead; on 2 and 8
     // B200s that was slower (4.07 vs 4.01 ms per step at 8 GPUs): the collective's CTAs compete with the persistent
@@ -611,12 +638,8 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             // one collective over the whole gradient range (alignment gaps between the pieces ride along)
             c.ok(gdb200_dp_all_reduce(be, s->scratch_buffer, head_off, (all_grads_end - head_off) / es, dt), "dp_all_reduce");
         }
+        // every rank divided by the global row count already: the sum over ranks IS the gradient of the global mean loss
         c.ok(gdb200_dp_join(be), "dp_join");
-        // mean over ranks: fold 1/world into the inverse loss scale the clip and AdamW kernels use
-        Ten inv = c.alloc(GDB_DTYPE_F32, {});
-        c.ok(gd_backend_scale(be, inv.buf, inv.off, s->state_buffer, inv_scale_off, 1, GDB_DTYPE_F32, 1.0f / (float)s->dp_world), "scale(inv_scale/world)");
-        scale_buf = inv.buf;
-        inv_scale_off = inv.off;
     }
     std::vector<gd_backend_grad_norm_desc> nd((size_t)n_params);
     std::vector<gd_backend_adamw_desc> ad((size_t)n_params);
@@ -679,6 +702,8 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         a.weight_decay = s->weight_decay[p];
         a.bias_correction1 = a.bias_correction2 = 1.0f;
     }
+    be->last_grad_count = n_params;
+    for (int p = 0; p < n_params; ++p) be->last_grad_offset[p] = grads[(size_t)p].off;
     c.ok(gd_backend_grad_clip_scale(be, nd.data(), (uint32_t)n_params, s->state_buffer, s->clip_scale_offset, s->grad_clip_norm, 1.0e-6f), "grad_clip_scale");
     c.ok(gd_backend_adamw_batch(be, ad.data(), (uint32_t)n_params), "adamw_batch");
     c.ok(gd_backend_amp_finish_step(be, &amp), "amp_finish_step");
@@ -689,6 +714,13 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         snprintf(be->last_error, sizeof(be->last_error), "gpt step optimizer: %s", c.where);
     }
     return c.st;
+}
+
+extern "C" int32_t gdb200_gpt_train_step_grad_offsets(const gd_backend *be, size_t *offsets, int32_t capacity)
+{
+    if (be == NULL) return 0;
+    for (int32_t p = 0; p < be->last_grad_count && p < capacity && offsets != NULL; ++p) offsets[p] = be->last_grad_offset[p];
+    return be->last_grad_count;
 }
 
 // ---------------------------------------------------------------------------------------------

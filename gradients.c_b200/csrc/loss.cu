@@ -169,6 +169,49 @@ __global__ void lmce_reduce_normalize_kernel(const float *row_loss, const float 
     }
 }
 
+// Data-parallel form of the normaliser: counts[0] holds the number of valid target rows of the GLOBAL batch
+// (all ranks), so loss[0] becomes this rank's share of the global mean (the shares add up to it) and the
+// backward pass divides by the global count instead of the local one.
+__global__ void lmce_reduce_normalize_global_kernel(const float *row_loss, const float *counts, float *loss,
+                                                    float *inv_valid_count, size_t rows)
+{
+    gdb_pdl_sync();
+    __shared__ float sh[33];
+    float ll = 0.0f;
+    for (size_t i = threadIdx.x; i < rows; i += blockDim.x) {
+        ll += row_loss[i];
+    }
+    const float loss_sum = gdb_block_sum(ll, sh);
+    if (threadIdx.x == 0) {
+        const float global = counts[0];
+        if (global > 0.0f) {
+            const float inv = 1.0f / global;
+            inv_valid_count[0] = inv;
+            loss[0] = loss_sum * inv;
+        } else {
+            inv_valid_count[0] = 0.0f;
+            loss[0] = __int_as_float(0x7fc00000);
+        }
+    }
+}
+
+// counts[0] = counts[1] = number of rows whose target takes part in the loss (same rule as lmce_finalize_kernel).
+__global__ void lmce_count_valid_kernel(const int *targets, size_t rows, int ignore_index, float *counts)
+{
+    gdb_pdl_sync();
+    __shared__ float sh[33];
+    float n = 0.0f;
+    for (size_t i = threadIdx.x; i < rows; i += blockDim.x) {
+        const int t = targets[i];
+        n += (t >= 0 && t != ignore_index) ? 1.0f : 0.0f;   // out-of-range ids count (their loss is NaN), as in finalize
+    }
+    const float total = gdb_block_sum(n, sh);
+    if (threadIdx.x == 0) {
+        counts[0] = total;
+        counts[1] = total;
+    }
+}
+
 template <typename T>
 __global__ void lmce_backward_chunk_kernel(const T *logits, const T *bias, const int *targets, const float *row_max,
                                            const float *row_inv_sum, const float *grad_loss, const float *inv_valid,
@@ -506,3 +549,33 @@ gd_status gd_backend_cross_entropy_backward_stats(gd_backend *be, const gd_backe
 }
 
 }  // extern "C"
+
+gd_status gdb_lm_ce_count_valid(gd_backend *be, const gd_backend_tensor_view *targets, int32_t ignore_index, const gd_backend_tensor_view *counts)
+{
+    if (be == NULL || targets == NULL || counts == NULL || targets->count == 0U || counts->count != 2U) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const int *tp = (const int *)gdb_tv_ptr(targets, GDB_DTYPE_I32);
+    float *cp = (float *)gdb_tv_ptr(counts, GDB_DTYPE_F32);
+    if (tp == NULL || cp == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    gdb_launch(lmce_count_valid_kernel, 1, 1024, 0, be->stream, tp, (size_t)targets->count, (int)ignore_index, cp);
+    return gdb_launched(be, "lm_cross_entropy_count_valid");
+}
+
+gd_status gdb_lm_ce_reduce_normalize_global(gd_backend *be, const gd_backend_tensor_view *row_loss, const gd_backend_tensor_view *counts,
+                                            const gd_backend_tensor_view *loss, const gd_backend_tensor_view *inv_valid_count)
+{
+    if (be == NULL || row_loss == NULL || counts == NULL || loss == NULL || inv_valid_count == NULL || row_loss->count == 0U ||
+        counts->count != 2U || loss->count != 1U || inv_valid_count->count != 1U) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const float *rl = (const float *)gdb_tv_ptr(row_loss, GDB_DTYPE_F32), *cp = (const float *)gdb_tv_ptr(counts, GDB_DTYPE_F32);
+    float *lp = (float *)gdb_tv_ptr(loss, GDB_DTYPE_F32), *ip = (float *)gdb_tv_ptr(inv_valid_count, GDB_DTYPE_F32);
+    if (rl == NULL || cp == NULL || lp == NULL || ip == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    gdb_launch(lmce_reduce_normalize_global_kernel, 1, 1024, 0, be->stream, rl, cp, lp, ip, (size_t)row_loss->count);
+    return gdb_launched(be, "lm_cross_entropy_reduce_normalize(global)");
+}

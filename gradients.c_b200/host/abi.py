@@ -137,7 +137,8 @@ class GptSpec(C.Structure):
                 ("state_f32_offset", SZ), ("state_i32_offset", SZ), ("partials_offset", SZ), ("clip_scale_offset", SZ),
                 ("amp_scale_offset", SZ), ("amp_flags_offset", SZ),
                 ("param_offset", SZ * GPT_MAX_PARAMS), ("param_count", SZ * GPT_MAX_PARAMS), ("master_offset", SZ * GPT_MAX_PARAMS),
-                ("m_offset", SZ * GPT_MAX_PARAMS), ("v_offset", SZ * GPT_MAX_PARAMS), ("weight_decay", F * GPT_MAX_PARAMS)]
+                ("m_offset", SZ * GPT_MAX_PARAMS), ("v_offset", SZ * GPT_MAX_PARAMS), ("weight_decay", F * GPT_MAX_PARAMS),
+                ("global_valid_rows", F)]
 
 
 class PermuteArgs(C.Structure):
@@ -299,6 +300,7 @@ PROTOTYPES = {
     "gdb200_embedding_backward_static_max_elems": (U64, []),
     "gdb200_gpt_compact_expand": (_ST, [P, C.POINTER(GptCompactBatch)]),
     "gdb200_gpt_train_step": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptBatch), U64, F, C.POINTER(SZ), C.POINTER(SZ)]),
+    "gdb200_gpt_train_step_grad_offsets": (I32_T, [P, C.POINTER(SZ), I32_T]),
     "gdb200_matmul_tn_colsum": (_ST, [P, MV, MV, MV, VV]),
     "gdb200_argmax_rows": (_ST, [P, TV, F, TV]),
     "gdb200_gpt_decode_steps": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptDecodeState), I32_T, I32_T, C.POINTER(SZ)]),

@@ -44,20 +44,30 @@ class DataParallel:
         """Sequences rank, rank + world, ... of the global batch."""
         return items[self.rank::self.world]
 
-    def reduce_gradients(self, optimizer, scaler):
-        """Python-host path: in-place sum all-reduce of every parameter gradient, then a device
-        scalar inv_scale / world that the clip and AdamW kernels use as their gradient multiplier
-        (mean over ranks with no extra pass over the gradients)."""
+    def shard_share(self, batch, pad_token_id: int) -> float:
+        """Valid target rows of this rank's batch divided by those of the global batch (counts summed over the
+        ranks on the host through the rendezvous group). Every rank must call it once per step."""
+        import torch
+        t = np.asarray(batch.targets)
+        local = float(np.count_nonzero((t >= 0) & (t != pad_token_id)))
+        total = torch.tensor([local], dtype=torch.float64)
+        self.dist.all_reduce(total)
+        return local / float(total[0]) if float(total[0]) > 0 else 1.0
+
+    def reduce_gradients(self, optimizer, loss=None) -> None:
+        """Python-host path: in-place sum all-reduce of every parameter gradient, in the optimizer's fixed
+        parameter order on every rank (a parameter that received no gradient on this rank contributes zeros, so
+        the ranks always issue the same collectives), and of the loss share. With the loss normalised by the
+        global row count (shard_share) the sum IS the gradient of the global mean loss: no division by world."""
         ctx, lib = self.ctx, self.ctx.lib
         for slot in optimizer.slots:
+            if slot.param.grad is None:
+                slot.param.grad = ctx.zeros(ctx.scratch, slot.param.dtype, slot.param.shape, "zero_grad")
             g = slot.param.grad
-            if g is not None:
-                ctx.check(lib.gdb200_dp_all_reduce(ctx.backend, g.buffer, g.offset, g.count, g.dtype), "dp_all_reduce")
+            ctx.check(lib.gdb200_dp_all_reduce(ctx.backend, g.buffer, g.offset, g.count, g.dtype), "dp_all_reduce")
+        if loss is not None:
+            ctx.check(lib.gdb200_dp_all_reduce(ctx.backend, loss.buffer, loss.offset, 1, F32), "dp_all_reduce(loss)")
         ctx.check(lib.gdb200_dp_join(ctx.backend), "dp_join")
-        inv = ctx.scratch_empty(F32, (), "inv_scale_over_world")
-        ctx.check(lib.gd_backend_scale(ctx.backend, inv.buffer, inv.offset, scaler.scale_state.buffer, scaler.scale_state.offset + 4,
-                                       1, F32, 1.0 / self.world), "scale(inv_scale)")
-        return inv
 
 
 def split_global_batch(n_seqs: int, world: int) -> list[list[int]]:

@@ -131,6 +131,31 @@ class Batch:
         return int(self.input_ids.nbytes + self.targets.nbytes + self.positions.nbytes + self.cu_seqlens.nbytes)
 
 
+def take_sequences(batch: Batch, indices: Sequence[int], pad_to: int = 0, context_length: int = 0) -> Batch:
+    """The shard of a packed batch made of the given sequences (in the given order): same ids and targets, positions
+    and cu_seqlens rebuilt, padding segments of the source dropped and, when pad_to > 0, appended anew as ignored rows."""
+    cu = np.asarray(batch.cu_seqlens, dtype=np.int64)
+    ids, tgt, pos, out_cu = [], [], [], [0]
+    for i in indices:
+        a, b = int(cu[i]), int(cu[i + 1])
+        ids.append(np.asarray(batch.input_ids[a:b]))
+        tgt.append(np.asarray(batch.targets[a:b]))
+        pos.append(np.asarray(batch.positions[a:b]))
+        out_cu.append(out_cu[-1] + (b - a))
+    real = out_cu[-1]
+    if pad_to > 0 and real % pad_to != 0:
+        pad = pad_to - real % pad_to
+        while pad > 0:
+            n = min(pad, context_length or pad)
+            ids.append(np.zeros(n, dtype=np.int32))
+            tgt.append(np.full(n, -1, dtype=np.int32))
+            pos.append(np.arange(n, dtype=np.int32))
+            out_cu.append(out_cu[-1] + n)
+            pad -= n
+    return Batch(np.concatenate(ids).astype(np.int32), np.concatenate(tgt).astype(np.int32), np.concatenate(pos).astype(np.int32),
+                 np.asarray(out_cu, dtype=np.int32), real)
+
+
 @dataclass
 class CompactBatch:
     """A batch of compact records as the reference stores them on disk (examples/gpt_lm/main.c:835-857): u16
@@ -253,8 +278,10 @@ class GptLm:
         mlp = ops.gd_swiglu_split_linear(ctx, up_gate, p[pre + "down_proj.weight"], p[pre + "down_proj.bias"])
         return ops.gd_dropout_add(ctx, resid, mlp, cfg.dropout_p, self.training, self._site_seed(GPT_DROPOUT_MLP, i, step))
 
-    def forward(self, input_ids: Tensor, target_ids: Tensor, positions: Tensor, cu_seqlens: Tensor, step: int) -> Tensor:
-        """gpt_lm_forward: returns the scalar F32 mean loss tensor."""
+    def forward(self, input_ids: Tensor, target_ids: Tensor, positions: Tensor, cu_seqlens: Tensor, step: int,
+                shard_share: float = 1.0) -> Tensor:
+        """gpt_lm_forward: returns the scalar F32 mean loss tensor (this shard's share of the global mean when
+        shard_share < 1, see gd_lm_cross_entropy_softcapped_bias_ignore)."""
         ctx, cfg, p = self.ctx, self.cfg, self.params
         x = ops.gd_embedding(ctx, p["token_embedding"], input_ids)
         x = ops.gd_dropout(ctx, x, cfg.dropout_p, self.training, splitmix64((cfg.dropout_seed ^ GPT_DROPOUT_EMBED ^ step) & MASK64))
@@ -262,7 +289,7 @@ class GptLm:
             x = self.block_forward(i, x, positions, cu_seqlens, step)
         final = ops.gd_rms_norm(ctx, x, p["final_norm_w"], cfg.rms_eps)
         return ops.gd_lm_cross_entropy_softcapped_bias_ignore(ctx, final, self.lm_head_weight(), p["lm_head_bias"], target_ids,
-                                                              cfg.logits_softcap, cfg.pad_token_id)
+                                                              cfg.logits_softcap, cfg.pad_token_id, shard_share)
 
     def upload_batch(self, batch: Batch, stream_ordered: bool = False):
         """Places the batch in the data slot. `stream_ordered`: the arrays are page-locked and are copied behind
@@ -418,12 +445,13 @@ class Trainer:
         ctx.begin_step()
         self.optimizer.zero_grad()
         ids, tgt, pos, cu = device_batch if device_batch is not None else model.upload_batch(batch, loss_out is not None)
-        loss = model.forward(ids, tgt, pos, cu, self.global_step + 1)
+        # data parallel: the loss and its gradient are normalised by the valid rows of the GLOBAL batch
+        share = self.dp.shard_share(batch, model.cfg.pad_token_id) if self.dp is not None else 1.0
+        loss = model.forward(ids, tgt, pos, cu, self.global_step + 1, share)
         gd_backward_amp(ctx, loss, self.scaler)
-        inv_override = None
         if self.dp is not None:
-            inv_override = self.dp.reduce_gradients(self.optimizer, self.scaler)
-        self.optimizer.step_amp_clip_lr(self.scaler, self.cfg.lr if lr is None else lr, self.cfg.grad_clip_norm, inv_override)
+            self.dp.reduce_gradients(self.optimizer, loss)
+        self.optimizer.step_amp_clip_lr(self.scaler, self.cfg.lr if lr is None else lr, self.cfg.grad_clip_norm)
         if loss_out is not None:
             loss.read_async(loss_out)
         ctx.end_step()
@@ -466,8 +494,12 @@ class NativeTrainer(Trainer):
             s.weight_decay[i] = slot.weight_decay
         self.spec = s
 
-    def train_batch(self, batch: Optional[Batch], lr: Optional[float] = None, device_batch=None, loss_out=None) -> Tensor:
+    def train_batch(self, batch: Optional[Batch], lr: Optional[float] = None, device_batch=None, loss_out=None,
+                    global_valid_rows: float = 0.0) -> Tensor:
+        """`global_valid_rows` > 0: the batch is a shard of a global batch with that many valid target rows; loss and
+        gradients are normalised by it (the loss returned is the shard's share of the global mean)."""
         C, ctx = self._C, self.ctx
+        self.spec.global_valid_rows = float(global_valid_rows)
         ctx.begin_step()
         ids, tgt, pos, cu = device_batch if device_batch is not None else self.model.upload_batch(batch, loss_out is not None)
         assert ids.arena is tgt.arena is pos.arena is cu.arena
@@ -484,6 +516,20 @@ class NativeTrainer(Trainer):
         ctx.end_step()
         self.global_step += 1
         return loss
+
+
+def native_step_gradients(trainer: "NativeTrainer") -> dict[str, np.ndarray]:
+    """Parameter gradients of the step the native driver enqueued last, read from the scratch arena before it is
+    reused (float32, still multiplied by the loss scale of that step)."""
+    import ctypes as C
+    ctx, model = trainer.ctx, trainer.model
+    names = list(model.params.keys())
+    offs = (C.c_size_t * len(names))()
+    n = ctx.lib.gdb200_gpt_train_step_grad_offsets(ctx.backend, offs, len(names))
+    assert n == len(names), (n, len(names))
+    ctx.flush()
+    return {name: Tensor(ctx, ctx.scratch, int(offs[i]), model.cfg.dtype, model.params[name].shape).read_f32()
+            for i, name in enumerate(names)}
 
 
 def greedy_generate(model: GptLm, prompts: np.ndarray, new_tokens: int, capacity: int) -> np.ndarray:

@@ -431,10 +431,14 @@ def lm_ce_chunk_classes(classes: int) -> int:
 
 
 def gd_lm_cross_entropy_softcapped_bias_ignore(ctx: Context, hidden: Tensor, weight: Tensor, bias: Optional[Tensor],
-                                               targets: Tensor, logits_softcap: float, ignore_index: int) -> Tensor:
+                                               targets: Tensor, logits_softcap: float, ignore_index: int,
+                                               shard_share: float = 1.0) -> Tensor:
     """Mean cross entropy of softcap(hidden w^T + b) against targets, computed chunk by chunk
     over the vocabulary with an online (max, sum) merge; returns a scalar F32 tensor
-    (src/ops/lm_cross_entropy/core_lm_cross_entropy.c:452-675, backward :676-974)."""
+    (src/ops/lm_cross_entropy/core_lm_cross_entropy.c:452-675, backward :676-974).
+    `shard_share` = valid target rows of this batch / valid target rows of the global batch it is a shard of:
+    loss and 1/valid_count are multiplied by it, so the loss is the shard's share of the global mean and the
+    backward pass divides by the global count (data parallelism; 1.0 = the reference's local normaliser)."""
     lib = ctx.lib
     rows, k = _flat2(hidden)
     n = weight.shape[0]
@@ -467,6 +471,9 @@ def gd_lm_cross_entropy_softcapped_bias_ignore(ctx: Context, hidden: Tensor, wei
     ctx.check(lib.gd_backend_lm_cross_entropy_finalize(ctx.backend, _tvp(targets), _tvp(row_loss), _tvp(row_max), _tvp(row_inv_sum),
                                                        _tvp(row_valid), n, ignore_index), "lm_ce_finalize")
     ctx.check(lib.gd_backend_lm_cross_entropy_reduce_normalize(ctx.backend, _tvp(row_loss), _tvp(row_valid), _tvp(loss), _tvp(inv_valid)), "lm_ce_reduce_normalize")
+    if shard_share != 1.0:
+        for t in (loss, inv_valid):
+            ctx.check(lib.gd_backend_scale(ctx.backend, t.buffer, t.offset, t.buffer, t.offset, 1, F32, float(shard_share)), "scale(shard share)")
     loss.requires_grad = needs
     if needs:
         def backward():

@@ -467,6 +467,9 @@ typedef struct gdb200_gpt_spec {
     size_t param_offset[GDB200_GPT_MAX_PARAMS], param_count[GDB200_GPT_MAX_PARAMS];
     size_t master_offset[GDB200_GPT_MAX_PARAMS], m_offset[GDB200_GPT_MAX_PARAMS], v_offset[GDB200_GPT_MAX_PARAMS];
     float weight_decay[GDB200_GPT_MAX_PARAMS];
+    /* Valid target rows of the GLOBAL batch when this batch is one shard of it and the caller knows the figure;
+     * 0 = count the shard and, with a data-parallel communicator attached, sum the counts over the ranks. */
+    float global_valid_rows;
 } gdb200_gpt_spec;
 typedef struct gdb200_gpt_batch {
     gd_backend_buffer *buffer;  /* I32 fields: input ids, targets, positions [n_tokens]; cu_seqlens [n_cu] */
@@ -475,9 +478,16 @@ typedef struct gdb200_gpt_batch {
 } gdb200_gpt_batch;
 /* Enqueues forward, backward (loss scaled by the AMP state), gradient exchange when a data-parallel
  * communicator is attached and spec->dp_world > 1, clipping, AdamW and the scaler update. The mean
- * loss (F32 scalar) is left at *loss_offset of scratch_buffer. */
+ * loss (F32 scalar) is left at *loss_offset of scratch_buffer. Under data parallelism the loss and the
+ * gradients are those of the GLOBAL batch: every rank divides by the number of valid target rows of all
+ * ranks (one scalar all-reduce that overlaps the forward pass), the gradient sum over the ranks needs no
+ * further division, and the reported loss is the global mean on every rank. */
 gd_status gdb200_gpt_train_step(gd_backend *backend, const gdb200_gpt_spec *spec, const gdb200_gpt_batch *batch,
                                 uint64_t step, float lr, size_t *loss_offset, size_t *scratch_used);
+/* Scratch-buffer offsets of the parameter gradients the last gdb200_gpt_train_step produced, in parameter order
+ * (storage dtype, still multiplied by the loss scale; summed over the ranks under data parallelism). They stay valid
+ * until the scratch arena is written again. Returns the number of parameters; at most `capacity` offsets are stored. */
+int32_t gdb200_gpt_train_step_grad_offsets(const gd_backend *backend, size_t *offsets, int32_t capacity);
 
 /* Expansion of a batch of compact GPT-LM records on the device. The reference expands each record on a loader
  * thread (examples/gpt_lm/main.c:873-970: u16 tokens[context_length + 1] and the record's I32 segment lengths ->

@@ -95,14 +95,17 @@ void oracle_kv_append(uint8_t *k_cache, uint8_t *v_cache, const uint8_t *k_new, 
 
 int32_t oracle_argmax_first(const float *logits, uint32_t n)
 {
-    int32_t best = -1;
-    float best_v = 0.0f;
+    /* index 0 when no value is finite, as the reference's `int best = 0` leaves it (gpt_lm_shared.c:1380,1397) */
+    int32_t best = 0;
+    int have_best = 0;
+    double best_v = 0.0;
     for (uint32_t i = 0; i < n; ++i) {
-        const float v = logits[i];
+        const double v = (double)logits[i];
         if (!isfinite(v)) continue;
-        if (best < 0 || v > best_v) {
+        if (!have_best || v > best_v) {
             best = (int32_t)i;
             best_v = v;
+            have_best = 1;
         }
     }
     return best;

@@ -133,6 +133,9 @@ def test_balanced_shards_even_counts_and_tokens():
 
 
 def _dp_worker(rank, world, port, q):
+    """One data-parallel rank on CPU: the oracle computes this rank's gradients on its shard with the loss normalised
+    by the valid rows of the GLOBAL batch (DataParallel.shard_share, counts summed over gloo), the gradients and the loss
+    shares are summed over the ranks, and the result must equal ONE oracle step on the union batch."""
     import torch
     import torch.distributed as dist
     from oracle import gpt_lm as OG
@@ -141,30 +144,25 @@ def _dp_worker(rank, world, port, q):
     cfg = g.GptConfig(vocab_size=64, context_length=16, d_model=32, n_layers=1, n_heads=2, head_dim=16, mlp_hidden=32,
                       tied_lm_head=False, dropout_p=0.0, sdpa_window=0)
     hp = g.init_params(cfg, seed=1)
-    shards = pkg.dp.split_global_batch(4, world)
-    batches = [g.synthetic_batch(cfg, 1, 6, 16, seed=50 + i) for i in range(4)]
-
-    def grads_of(idx):
-        ref = OG.OracleGptLm(OG.config_from(cfg), hp)
-        acc = None
-        for i in idx:
-            b = batches[i]
-            r = ref.loss_and_grads(b.input_ids, b.targets, b.positions, b.cu_seqlens, 1, 1.0)["grads"]
-            acc = r if acc is None else {k: acc[k] + r[k] for k in r}
-        return {k: v / len(idx) for k, v in acc.items()}
-
-    mine = grads_of(shards[rank])
-    flat = torch.cat([mine[k].reshape(-1) for k in sorted(mine)])
-    dist.all_reduce(flat, op=dist.ReduceOp.SUM)
-    flat = flat / world                                     # what folding 1/world into the inverse loss scale does
-    both = [grads_of(s) for s in shards]
-    want = torch.cat([sum(b[k] for b in both).reshape(-1) / world for k in sorted(mine)])
-    q.put((rank, float((flat - want).abs().max()), shards))
+    union = g.synthetic_batch(cfg, 5, 3, 16, seed=50)              # five sequences of unequal length: uneven shards
+    shards = pkg.dp.split_global_batch(5, world)
+    mine = g.take_sequences(union, shards[rank])
+    dp = pkg.dp.DataParallel(None, None, rank, world, dist, connect=False)
+    share = dp.shard_share(mine, cfg.pad_token_id)
+    ref = OG.OracleGptLm(OG.config_from(cfg), hp)
+    r = ref.loss_and_grads(mine.input_ids, mine.targets, mine.positions, mine.cu_seqlens, 1, share)   # d(share * local mean)
+    names = sorted(r["grads"])
+    flat = torch.cat([r["grads"][k].reshape(-1) for k in names] + [torch.tensor([r["loss"] * share], dtype=torch.float32)])
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM)                   # no division by world: the shares already add up
+    w = OG.OracleGptLm(OG.config_from(cfg), hp).loss_and_grads(union.input_ids, union.targets, union.positions, union.cu_seqlens, 1, 1.0)
+    want = torch.cat([w["grads"][k].reshape(-1) for k in names] + [torch.tensor([w["loss"]], dtype=torch.float32)])
+    valid = int(np.count_nonzero(mine.targets >= 0))
+    q.put((rank, float((flat - want).abs().max() / want.abs().max()), shards, share, valid))
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_data_parallel_gradient_mean_over_two_gloo_ranks():
+def test_data_parallel_global_mean_over_two_gloo_ranks_equals_the_union_batch():
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -172,10 +170,18 @@ def test_data_parallel_gradient_mean_over_two_gloo_ranks():
     procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=240) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
-    for rank, err, shards in res:
-        assert err < 1e-6
-        assert shards == [[0, 2], [1, 3]]
+    try:
+        res = [q.get(timeout=240) for _ in procs]
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+    total = sum(r[4] for r in res)
+    for rank, err, shards, share, valid in res:
+        assert err < 2e-3            # F16 rounding points sit at differently scaled values on the two sides
+        assert shards == [[0, 2, 4], [1, 3]]
+        assert abs(share - valid / total) < 1e-12 and 0.0 < share < 1.0
+    assert abs(sum(r[3] for r in res) - 1.0) < 1e-12

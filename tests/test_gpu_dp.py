@@ -1,6 +1,7 @@
-"""GPU, two devices: NCCL gradient all-reduce through the gdb200_dp_* entries, and lock-step
-parameters after data-parallel train steps (native and Python hosts). Skipped on a one-GPU box;
-the rank logic itself is covered on CPU by the gloo test in test_cpu_abi_host.py."""
+"""GPU, two devices: NCCL gradient all-reduce through the gdb200_dp_* entries, lock-step parameters after
+data-parallel train steps (native and Python hosts), and parity of a two-rank step with a one-GPU step on the
+union batch (global loss normaliser). Skipped on a one-GPU box; there the normaliser is covered by
+test_gpu_gpt_lm.py (shards stepped one after the other) and the rank logic by the gloo test in test_cpu_abi_host.py."""
 import os
 
 import numpy as np
@@ -54,13 +55,48 @@ def _worker(rank, world, port, host, q):
         mine = torch.from_numpy(flat.astype(np.int32))
         both = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(both, mine)
-        q.put((rank, ok_sum, bool(torch.equal(both[0], both[1])), losses, None))
+        # 3. one step on the two halves of a batch == one step of ONE rank on the whole batch (global loss normaliser):
+        #    the reduced gradients and the reported loss are compared with a single-GPU step computed afterwards
+        cfg2 = g.GptConfig(vocab_size=512, context_length=128, d_model=128, n_layers=2, n_heads=2, head_dim=64, mlp_hidden=256,
+                           tied_lm_head=False, dropout_p=0.0, sdpa_window=0)
+        hp2 = g.init_params(cfg2, seed=9)
+        union = g.synthetic_batch(cfg2, 6, 16, 128, seed=321)
+        half = g.take_sequences(union, [0, 2, 4] if rank == 0 else [1, 3, 5], pad_to=128, context_length=128)
+        m2 = g.GptLm(ctx, cfg2, hp2)
+        dp2 = pkg.dp.DataParallel(ctx, m2, rank, world, dist, connect=False)     # the communicator of step 2 is still attached
+        t2 = (g.NativeTrainer if host == "native" else g.Trainer)(m2, g.TrainConfig.baseline(), dp=dp2)
+        if host == "native":
+            dp_loss = float(t2.train_batch(half).read()[()])
+            dp_grads = g.native_step_gradients(t2)
+        else:
+            ctx.begin_step()
+            t2.optimizer.zero_grad()
+            ids, tgt, pos, cu = m2.upload_batch(half)
+            share = dp2.shard_share(half, cfg2.pad_token_id)
+            lt = m2.forward(ids, tgt, pos, cu, 1, share)
+            pkg.optim.gd_backward_amp(ctx, lt, t2.scaler)
+            dp2.reduce_gradients(t2.optimizer, lt)
+            ctx.flush()
+            dp_loss = float(lt.read()[()])
+            dp_grads = {n: p.grad.read_f32() for n, p in m2.params.items()}
+            ctx.end_step()
+        dist.barrier()
+        parity = None
+        ctx1 = pkg.runtime.Context(params_bytes=64 << 20, state_bytes=256 << 20, scratch_bytes=2 << 30, data_bytes=16 << 20)
+        t1 = g.NativeTrainer(g.GptLm(ctx1, cfg2, hp2), g.TrainConfig.baseline())
+        whole = g.take_sequences(union, list(range(6)), pad_to=128, context_length=128)
+        one_loss = float(t1.train_batch(whole).read()[()])
+        one_grads = g.native_step_gradients(t1)
+        worst = max(float(np.abs(dp_grads[n].reshape(one_grads[n].shape) - one_grads[n]).max() / (np.abs(one_grads[n]).max() + 1e-6)) for n in one_grads)
+        parity = (dp_loss, one_loss, worst)
+        ctx1.destroy()
+        q.put((rank, ok_sum, bool(torch.equal(both[0], both[1])), losses, None, parity))
         dist.barrier()
         ctx.destroy()
         dist.destroy_process_group()
     except Exception as e:  # reported to the parent instead of a silent non-zero exit
         import traceback
-        q.put((rank, False, False, [], traceback.format_exc()))
+        q.put((rank, False, False, [], traceback.format_exc(), None))
         raise
 
 
@@ -74,13 +110,21 @@ def test_two_rank_all_reduce_and_lockstep_parameters(host):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, host, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=600) for _ in procs]
-    for p in procs:
-        p.join(timeout=120)
-    for rank, ok_sum, same, losses, err in res:
+    try:
+        res = [q.get(timeout=300) for _ in procs]
+        for p in procs:
+            p.join(timeout=120)
+    finally:
+        for p in procs:            # a rank that failed before a collective leaves its peer waiting inside it
+            if p.is_alive():
+                p.kill()
+    for rank, ok_sum, same, losses, err, parity in res:
         assert err is None, err
         assert ok_sum, f"rank {rank}: all-reduced buffer is not 3x"
         assert same, f"rank {rank}: parameters diverged across ranks"
         assert all(np.isfinite(l) for l in losses)
+        dp_loss, one_loss, worst = parity
+        assert abs(dp_loss - one_loss) <= 1e-5 * abs(one_loss), (dp_loss, one_loss)     # every rank reports the global mean
+        assert worst <= 1e-2, worst                                                     # reduced gradients == one-GPU gradients
     for p in procs:
         assert p.exitcode == 0

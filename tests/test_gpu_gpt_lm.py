@@ -5,6 +5,9 @@ import pytest
 
 from gpu_util import F16, abi, host, pkg
 from oracle import gpt_lm as OG
+from oracle.cref import OracleInt
+
+oracle_int = OracleInt()
 
 pytestmark = pytest.mark.gpu
 g = pkg.gpt_lm
@@ -105,6 +108,37 @@ def test_fifty_seeded_steps_track_the_oracle_loss_and_scaler_trajectory():
     assert want[-5:].mean() < 0.9 * want[:5].mean()          # the run does learn something
 
 
+def test_shards_normalised_by_the_global_row_count_add_up_to_the_union_batch():
+    """The data-parallel loss normaliser without a second GPU: the two shards of a batch are stepped one after the other
+    through the native driver with global_valid_rows = valid target rows of the whole batch; the sum of the two gradient
+    sets and of the two loss shares must equal one step on the union batch (and the oracle's)."""
+    cfg = small_cfg(dropout_p=0.0, d_model=128, mlp_hidden=256)
+    tc = g.TrainConfig.baseline()
+    hp = g.init_params(cfg, seed=41)
+    union = g.synthetic_batch(cfg, 7, 5, 64, seed=77)
+    shards = [g.take_sequences(union, idx, pad_to=64, context_length=64) for idx in ([0, 2, 4, 6], [1, 3, 5])]
+    union_p = g.take_sequences(union, list(range(7)), pad_to=64, context_length=64)
+    total_rows = float(np.count_nonzero(union.targets >= 0))
+
+    def one_step(batch, rows):
+        with pkg.runtime.Context(params_bytes=64 << 20, state_bytes=128 << 20, scratch_bytes=1 << 30) as ctx:
+            trainer = g.NativeTrainer(g.GptLm(ctx, cfg, hp), tc)
+            loss = float(trainer.train_batch(batch, global_valid_rows=rows).read()[()])
+            return loss, g.native_step_gradients(trainer)
+
+    (l0, g0), (l1, g1) = one_step(shards[0], total_rows), one_step(shards[1], total_rows)
+    lu, gu = one_step(union_p, 0.0)
+    assert abs((l0 + l1) - lu) <= 1e-5 * abs(lu)
+    ref = OG.OracleGptLm(OG.config_from(cfg), hp)
+    want = ref.loss_and_grads(union.input_ids, union.targets, union.positions, union.cu_seqlens, 1, 65536.0)
+    assert abs((l0 + l1) - want["loss"]) <= 2e-3 * abs(want["loss"])
+    for name in gu:
+        both, one, w = g0[name] + g1[name], gu[name], want["grads"][name].numpy().reshape(gu[name].shape)
+        denom = np.abs(one).max() + 1e-6
+        assert np.abs(both - one).max() <= 1e-2 * denom, name       # F16 roundings at differently scaled values
+        assert np.abs(both - w).max() <= 2e-2 * (np.abs(w).max() + 1e-6), name
+
+
 def test_trainer_train_batch_matches_manual_sequence():
     cfg = small_cfg()
     hp = g.init_params(cfg, seed=5)
@@ -173,6 +207,11 @@ def test_device_argmax_first_maximum_softcap_and_non_finite():
             got = g.device_argmax(ctx, t, cap).read()
             ctx.end_step()
             assert np.array_equal(got, g.host_argmax(x.astype(np.float32), cap)), cap
+            # the C restatement of the reference's rule (soft cap applied first, as gpt_apply_logits_softcap does)
+            capped = x.astype(np.float32)
+            if cap > 0.0:
+                capped = (np.float32(cap) * np.tanh(capped / np.float32(cap))).astype(np.float32)
+            assert np.array_equal(got, np.array([oracle_int.argmax_first(row) for row in capped], dtype=np.int32)), cap
             assert got[0] == 5 and got[1] == 0 and got[4] == 0 and got[2] != 7 and (got[2] == 8) == (cap > 0.0)
 
 

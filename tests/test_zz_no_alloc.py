@@ -11,8 +11,10 @@ import ctypes as C
 
 import numpy as np
 import pytest
+import torch
 
-from gpu_util import F16, F32, I32, TOL, abi, dev, host, pkg
+from gpu_util import BF16, F16, F32, I32, TOL, abi, dev, host, pkg, rnd_np, storage_name
+from oracle import ops as O
 
 pytestmark = pytest.mark.gpu
 
@@ -21,7 +23,8 @@ def raw(ctx, t):
     return ctx.lib.gdb200_buffer_device_ptr(t.buffer, t.offset)
 
 
-def test_static_scratch_embedding_backward_matches_regular_entry():
+@pytest.mark.parametrize("dtype", [F16, BF16, F32])
+def test_static_scratch_embedding_backward_matches_regular_entry(dtype):
     with pkg.runtime.Context(params_bytes=16 << 20, state_bytes=16 << 20, scratch_bytes=256 << 20, data_bytes=8 << 20) as ctx:
         lib = ctx.lib
         stream = lib.gdb200_stream(ctx.backend)
@@ -32,24 +35,35 @@ def test_static_scratch_embedding_backward_matches_regular_entry():
             rng = np.random.default_rng(call)
             ids = rng.integers(0, vocab, size=n_ids).astype(np.int32)
             ids[::97] = -1
-            g = (rng.standard_normal((n_ids, dim)) * (1.0 + call)).astype(np.float16).astype(np.float32)
-            gt, it = dev(ctx, g, F16), dev(ctx, ids, I32)
-            want_t = ctx.scratch_empty(F16, (vocab, dim))
+            g = rnd_np((rng.standard_normal((n_ids, dim)) * (1.0 + call)).astype(np.float32), dtype)
+            gt, it = dev(ctx, g, dtype), dev(ctx, ids, I32)
+            want_t = ctx.scratch_empty(dtype, (vocab, dim))
             scratch = ctx.scratch_empty(F32, (vocab, dim))
             args = abi.EmbeddingArgs(n_ids, vocab, dim)
             ctx.check(lib.gd_backend_embedding_backward(ctx.backend, C.byref(gt.tv()), C.byref(it.tv()), C.byref(want_t.tv()),
                                                         C.byref(scratch.tv()), C.byref(args)), "embedding_backward")
-            got_t = ctx.scratch_empty(F16, (vocab, dim))
-            ctx.fill(got_t, 0x7E00)                 # NaN pattern: every element must be overwritten
-            st = lib.gdb200_embedding_backward_static(stream, raw(ctx, gt), raw(ctx, it), raw(ctx, got_t), n_ids, vocab, dim, F16)
+            got_t = ctx.scratch_empty(dtype, (vocab, dim))
+            ctx.fill(got_t, {F16: 0x7E00, BF16: 0x7FC0, F32: 0x7FC00000}[dtype])   # NaN pattern: every element must be overwritten
+            st = lib.gdb200_embedding_backward_static(stream, raw(ctx, gt), raw(ctx, it), raw(ctx, got_t), n_ids, vocab, dim, dtype)
             assert st == abi.GD_OK, lib.gdb200_embedding_backward_static_error()
             ctx.flush()
             got, want = host(got_t), host(want_t)
             assert np.isfinite(got).all()
             # both paths accumulate with FP32 atomics (order differs run to run), then round once
-            np.testing.assert_allclose(got, want, atol=TOL[F16]["atol"] * 4, rtol=TOL[F16]["rtol"])
+            np.testing.assert_allclose(got, want, atol=TOL[dtype]["atol"] * 4, rtol=TOL[dtype]["rtol"])
+            # and against the CPU oracle's scatter-add
+            oracle = O.embedding_backward(torch.from_numpy(g), torch.from_numpy(ids), vocab, storage_name(dtype)).numpy()
+            np.testing.assert_allclose(got, oracle, atol=TOL[dtype]["atol"] * 4, rtol=TOL[dtype]["rtol"])
+        # no ids at all: the table is still cleared and written, so the result is all zeros (the static array holds the last call's sums)
+        ctx.fill(got_t, {F16: 0x7E00, BF16: 0x7FC0, F32: 0x7FC00000}[dtype])
+        st = lib.gdb200_embedding_backward_static(stream, raw(ctx, gt), raw(ctx, it), raw(ctx, got_t), 0, vocab, dim, dtype)
+        assert st == abi.GD_OK, lib.gdb200_embedding_backward_static_error()
+        ctx.flush()
+        assert not host(got_t).any()
         # beyond the maximum: refused with a message, nothing launched
-        st = lib.gdb200_embedding_backward_static(stream, raw(ctx, gt), raw(ctx, it), raw(ctx, got_t), 1, vocab + 1, dim, F16)
+        st = lib.gdb200_embedding_backward_static(stream, raw(ctx, gt), raw(ctx, it), raw(ctx, got_t), 1, vocab + 1, dim, dtype)
         assert st == abi.GD_ERR_INVALID_ARGUMENT
         assert b"exceeds" in lib.gdb200_embedding_backward_static_error()
+        st = lib.gdb200_embedding_backward_static(stream, raw(ctx, gt), raw(ctx, it), raw(ctx, got_t), (1 << 64) - 1, 4, 4, dtype)
+        assert st == abi.GD_ERR_INVALID_ARGUMENT
         ctx.end_step()
