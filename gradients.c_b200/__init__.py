@@ -6,6 +6,6 @@ The directory name contains a dot, so it is loaded by path (see __graft_entry__.
 under the module name `gradients_c_b200`.
 """
 from . import _build
-from .host import abi, runtime, ops, optim, gpt_lm, dp  # noqa: F401
+from .host import abi, runtime, ops, optim, gpt_lm, dp, c_host  # noqa: F401
 
-__all__ = ["_build", "abi", "runtime", "ops", "optim", "gpt_lm", "dp"]
+__all__ = ["_build", "abi", "runtime", "ops", "optim", "gpt_lm", "dp", "c_host"]

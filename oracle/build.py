@@ -8,10 +8,15 @@ import os
 import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REF = "/root/reference"
 
 
-def build(ref: str = DEFAULT_REF, jobs: int = 8) -> None:
+def reference_dir() -> str:
+    """The reference source tree: $GD_REFERENCE_DIR, else a directory `reference` beside the repository."""
+    return os.environ.get("GD_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref: str = "", jobs: int = 8) -> None:
+    ref = ref or reference_dir()
     targets = ["cref"]
     if os.path.exists(os.path.join(ref, "src", "core", "backend.h")):
         targets += ["ref", "tests_cuda"]

@@ -275,7 +275,8 @@ def save(group: str, cases: dict) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("GD_REFERENCE_DIR", ""), required=not os.environ.get("GD_REFERENCE_DIR"),
+                    help="the reference source tree (or set GD_REFERENCE_DIR)")
     args = ap.parse_args()
     if not cref.harness_available():
         raise SystemExit("oracle/_ref/ref_harness.so is missing: run __graft_entry__.build() where the reference tree exists")

@@ -50,7 +50,7 @@ def test_struct_layouts_match_the_c_header(tmp_path):
     assert sizes == [C.sizeof(t) for t in py]
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/src/core/backend.h"), reason="reference tree not present")
+@pytest.mark.skipif(pkg.c_host.reference_dir() is None, reason="reference tree not present")
 def test_struct_layouts_match_the_reference_header(tmp_path):
     fields = {"gd_backend_matrix_view": ["buffer", "offset", "rows", "cols", "row_bytes", "dtype"],
               "gd_backend_tensor_view": ["buffer", "offset", "count", "dtype", "rank", "shape", "strides"],
@@ -59,7 +59,8 @@ def test_struct_layouts_match_the_reference_header(tmp_path):
               "gd_backend_rms_norm_args": ["rows", "eps", "wgrad_row_block"], "gd_backend_sdpa_varlen_args": ["scale", "max_seqlen", "use_forward_stats"]}
     lines = [f'printf("%zu %zu\\n", sizeof({s}), offsetof({s}, {f}));' for s, fs in fields.items() for f in fs]
     outs = []
-    for hdr, extra in ((HEADER, []), ("/root/reference/src/core/backend.h", ["-I/root/reference/include", "-I/root/reference/src"])):
+    ref = pkg.c_host.reference_dir()
+    for hdr, extra in ((HEADER, []), (f"{ref}/src/core/backend.h", [f"-I{ref}/include", f"-I{ref}/src"])):
         src = tmp_path / "off.c"
         src.write_text(f'#include <stdio.h>\n#include <stddef.h>\n#include "{hdr}"\nint main(void){{{chr(10).join(lines)} return 0;}}\n')
         exe = tmp_path / "off"
