@@ -587,21 +587,28 @@ def device_argmax(ctx, logits: Tensor, softcap: float) -> Tensor:
     return out
 
 
-def greedy_generate_native(model: GptLm, prompts: np.ndarray, new_tokens: int, capacity: int, use_graph: bool = True) -> np.ndarray:
+def greedy_generate_native(model: GptLm, prompts: np.ndarray, new_tokens: int, capacity: int, use_graph: bool = True,
+                           timing: Optional[dict] = None) -> np.ndarray:
     """Same result as greedy_generate, with sampling and the id / position feedback on the device:
     packed prefill, device argmax of the prefill logits, then new_tokens - 1 decode steps enqueued
-    by gdb200_gpt_decode_steps with no host round trip; the generated ids are read once at the end."""
+    by gdb200_gpt_decode_steps with no host round trip; the generated ids are read once at the end.
+    `timing` (a dict) receives device milliseconds measured with events on the backend stream: "prefill_ms"
+    (packed prefill + first argmax) and "decode_ms" (the new_tokens - 1 decode steps), and "decode_launches"."""
     import ctypes as C
     ctx, cfg = model.ctx, model.cfg
     b, plen = prompts.shape
     model.alloc_kv_cache(b, capacity)
+    lib, be = ctx.lib, ctx.backend
     ctx.begin_step()
     ids = ctx.from_numpy(ctx.data, I32, prompts.reshape(-1).astype(np.int32))
     pos = ctx.from_numpy(ctx.data, I32, np.tile(np.arange(plen, dtype=np.int32), b))
     cu = ctx.from_numpy(ctx.data, I32, (np.arange(b + 1, dtype=np.int32) * plen))
     cpos = ctx.from_numpy(ctx.data, I32, np.zeros(b, dtype=np.int32))
+    ev = [lib.gdb200_event_record(be)] if timing is not None else None
     logits = model.prefill_last_logits(ids, pos, cu, cpos, np.arange(b) * plen + plen - 1)
     first = device_argmax(ctx, logits, cfg.logits_softcap)
+    if ev is not None:
+        ev.append(lib.gdb200_event_record(be))
     ctx.end_step()
     # io words: tokens [b] = argmax of the prefill logits, positions [b] = prompt length,
     # out_tokens [new_tokens, b] with row 0 filled, step counter = 1 (one read-back per generation)
@@ -616,12 +623,22 @@ def greedy_generate_native(model: GptLm, prompts: np.ndarray, new_tokens: int, c
     d.tokens_offset, d.positions_offset = io.offset, io.offset + 4 * b
     d.out_tokens_offset, d.step_counter_offset = io.offset + 8 * b, io.offset + 8 * b + 4 * new_tokens * b
     d.batch, d.capacity, d.max_steps = b, capacity, new_tokens
-    lib, be = ctx.lib, ctx.backend
     ctx.begin_step()
     spec = model_spec(model)
+    launches0 = ctx.launch_count()
+    if ev is not None:
+        ev.append(lib.gdb200_event_record(be))
     ctx.check(lib.gdb200_gpt_decode_steps(be, C.byref(spec), C.byref(d), new_tokens - 1, 1 if use_graph else 0, None), "gpt_decode_steps")
+    if ev is not None:
+        ev.append(lib.gdb200_event_record(be))
     ctx.end_step()
     ctx.flush()
+    if ev is not None:
+        timing["prefill_ms"] = float(lib.gdb200_event_elapsed_ms(ev[0], ev[1]))
+        timing["decode_ms"] = float(lib.gdb200_event_elapsed_ms(ev[2], ev[3]))
+        timing["decode_launches"] = int(ctx.launch_count() - launches0)
+        for e in ev:
+            lib.gdb200_event_destroy(e)
     flat = io.read()
     return flat[2 * b:2 * b + new_tokens * b].reshape(new_tokens, b).T.copy()
 
