@@ -23,3 +23,6 @@ gd_status gdb_flash_varlen_backward(gd_backend *be, const gdb_flash_args *a, boo
 gd_status gdb_flash_varlen_backward_with_out(gd_backend *be, const gdb_flash_args *a, const void *out, float *dq32);
 // tcgen05 / tensor-memory forward (attention_tcgen05.cu); GD_ERR_UNSUPPORTED outside its fast path.
 gd_status gdb_attn5_forward(gd_backend *be, const gdb_flash_args *a);
+// tcgen05 / tensor-memory key-stationary backward (attention_tcgen05_bwd.cu): dK, dV and the FP32 dQ accumulator dq32
+// [N, Hq, 64] (zero on entry) from complete statistics (max, sum, D). GD_ERR_UNSUPPORTED outside its fast path.
+gd_status gdb_attn5_backward(gd_backend *be, const gdb_flash_args *a, float *dq32);
