@@ -24,5 +24,7 @@ gd_status gdb_flash_varlen_backward_with_out(gd_backend *be, const gdb_flash_arg
 // tcgen05 / tensor-memory forward (attention_tcgen05.cu); GD_ERR_UNSUPPORTED outside its fast path.
 gd_status gdb_attn5_forward(gd_backend *be, const gdb_flash_args *a);
 // tcgen05 / tensor-memory key-stationary backward (attention_tcgen05_bwd.cu): dK, dV and the FP32 dQ accumulator dq32
-// [N, Hq, 64] (zero on entry) from complete statistics (max, sum, D). GD_ERR_UNSUPPORTED outside its fast path.
-gd_status gdb_attn5_backward(gd_backend *be, const gdb_flash_args *a, float *dq32);
+// [N, Hq, 64] (zero on entry) from complete statistics (max, sum, D) and the mask bounds `meta` (int [N + ceil(N / 128)]:
+// first allowed key per query row, query tiles per key tile; written by the preparation kernel in attention_flash.cu).
+// GD_ERR_UNSUPPORTED outside its fast path.
+gd_status gdb_attn5_backward(gd_backend *be, const gdb_flash_args *a, float *dq32, const int *meta);

@@ -689,10 +689,14 @@ __global__ void dq_convert_kernel(const float4 *__restrict__ src, uint4 *__restr
 }
 
 // Preparation of the single-pass backward: D[row, head] = sum_c dO * O (stats[.., 2]) and dq32 = 0.
-// Eight threads per (row, head) of 64 elements, 16 bytes of dO and of O each.
+// Eight threads per (row, head) of 64 elements, 16 bytes of dO and of O each. With `meta` != NULL it also leaves the mask
+// bounds the tensor-memory kernel reads instead of searching cu_seqlens per step: meta[row] = first key row `row` may
+// attend to (start of its sequence, moved up by the window; INT_MAX behind the last sequence), and, for every tile of 128
+// keys, meta[n_tokens + tile] = number of 128-row query tiles, starting with the tile's own, that hold a query allowed to
+// see one of its keys (0 behind the last sequence).
 template <typename T>
 __global__ void bwd_prep_kernel(const uint4 *__restrict__ go, const uint4 *__restrict__ out, float *__restrict__ stats, float4 *__restrict__ dq32,
-                                size_t n_vec)
+                                size_t n_vec, const int *__restrict__ cu, int batch, int n_tokens, int hq, int window, int *__restrict__ meta)
 {
     gdb_pdl_sync();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // one 8-element piece; n_vec is a multiple of 8
@@ -709,6 +713,27 @@ __global__ void bwd_prep_kernel(const uint4 *__restrict__ go, const uint4 *__res
 #pragma unroll
     for (int o = 1; o < 8; o <<= 1) s += __shfl_xor_sync(0xffffffffU, s, o);
     if (i < n_vec && (threadIdx.x & 7) == 0) stats[(i >> 3) * 3U + 2U] = s;
+    if (meta != nullptr && i < n_vec && (i % ((size_t)hq * 8U)) == 0U) {
+        const int row = (int)(i / ((size_t)hq * 8U));
+        const int n_valid = min(cu[batch], n_tokens);
+        int lo = 0x7fffffff;
+        if (row < n_valid) {
+            lo = cu[seg_of(cu, batch, row)];
+            if (window > 0) lo = max(lo, row - window + 1);
+        }
+        meta[row] = lo;
+        if ((row & 127) == 0) {
+            int n_qt = 0;
+            if (row < n_valid) {
+                const int last_key = min(row + 128, n_valid) - 1;
+                int q_hi = cu[seg_of(cu, batch, last_key) + 1];       // exclusive
+                if (window > 0) q_hi = min(q_hi, last_key + window);
+                q_hi = min(q_hi, n_valid);
+                n_qt = (q_hi - 1) / 128 - row / 128 + 1;
+            }
+            meta[n_tokens + (row >> 7)] = n_qt;
+        }
+    }
 }
 
 // Backward in one attention pass (head_dim 64, statistics (max, sum) saved by the forward): D from dO and the forward
@@ -717,11 +742,14 @@ template <typename T>
 gd_status backward_single_pass(gd_backend *be, const gdb_flash_args *a, const flash_params &p, const void *out, float *dq32)
 {
     const size_t n = (size_t)a->n_tokens * a->hq * 64U, n_vec = n / 8U;
+    // mask bounds for the tensor-memory kernel live at the start of the backend workspace between the two launches
+    const size_t meta_bytes = ((size_t)a->n_tokens + (size_t)(a->n_tokens + 127) / 128U) * sizeof(int);
+    int *meta = (be->attn_mode == 0 && meta_bytes <= be->ws_bytes) ? (int *)be->ws : nullptr;
     gdb_launch(bwd_prep_kernel<T>, (unsigned)((n_vec + 255U) / 256U), 256, 0, be->stream, (const uint4 *)a->grad_out, (const uint4 *)out, a->stats,
-               (float4 *)dq32, n_vec);
+               (float4 *)dq32, n_vec, a->cu, a->batch, a->n_tokens, a->hq, a->window, meta);
     gd_status st = gdb_launched(be, "flash_backward_prep");
     if (st != GD_OK) return st;
-    st = be->attn_mode == 0 ? gdb_attn5_backward(be, a, dq32) : GD_ERR_UNSUPPORTED;   // tensor-memory kernel where the shape allows
+    st = meta != nullptr ? gdb_attn5_backward(be, a, dq32, meta) : GD_ERR_UNSUPPORTED;   // tensor-memory kernel where the shape allows
     if (st == GD_ERR_UNSUPPORTED) st = launch_kv<T, 64, 64, true>(be, a, p, dq32);
     if (st != GD_OK) return st;
     gdb_launch(dq_convert_kernel<T>, gdb_grid_for(n_vec, 256, be, 8), 256, 0, be->stream, (const float4 *)dq32, (uint4 *)a->out_or_dq, n_vec);

@@ -660,4 +660,6 @@ def test_sdpa_backward_with_forward_output_matches_the_two_pass_backward(step, d
     for i, (want, what, sc) in enumerate(((wdq, "dq", 4), (wdk, "dk", 6), (wdv, "dv", 6))):
         close(grads[True][i], want, dtype, scale=sc, what=what + " single pass")
         close(grads[False][i], want, dtype, scale=sc, what=what + " two passes")
-    assert np.array_equal(grads[True][2], grads[False][2])          # dV does not depend on D
+    # dV does not depend on D; the two paths form P in different kernels (tensor-memory kernel: exp2 with 1/l folded
+    # into the exponent; mma.sync kernel: exp2 times 1/l), so it agrees to the rounding of P, not bit for bit
+    close(grads[True][2], grads[False][2], dtype, scale=2, what="dv single pass vs two passes")
