@@ -308,6 +308,10 @@ gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype,
                            const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
                            void *c, size_t ldc_bytes, const void *bias, int bias_mode,
                            uint32_t M, uint32_t N, uint32_t K);
+// `batch` equal-shaped contractions in one launch (byte pitches between batch elements; 0 broadcasts the operand).
+gd_status gdb_gemm_tcgen05_batched(gd_backend *be, int ta, int tb, uint32_t dtype, const void *a, size_t lda_bytes, size_t a_batch_bytes,
+                                   const void *b, size_t ldb_bytes, size_t b_batch_bytes, void *c, size_t ldc_bytes, size_t c_batch_bytes,
+                                   uint32_t M, uint32_t N, uint32_t K, uint32_t batch);
 // At most 64 output rows (decode): mma.sync kernel with K split over the warps of a CTA.
 // sum = residual + dropout(x) (mask written), out = rms_norm(sum, weight), inv_rms saved: gd_backend_dropout_add_forward followed by
 // gd_backend_rms_norm_forward_stats in one launch, same rounding points. GD_ERR_UNSUPPORTED when the vector path does not apply.

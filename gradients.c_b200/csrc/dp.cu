@@ -10,7 +10,9 @@
 
 #include <dlfcn.h>
 #include <nccl.h>
+#include <sched.h>
 #include <stdlib.h>
+#include <time.h>
 
 namespace {
 
@@ -24,6 +26,7 @@ struct nccl_api {
     const char *(*GetErrorString)(ncclResult_t);
     ncclResult_t (*GroupStart)(void);
     ncclResult_t (*GroupEnd)(void);
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *);   // optional
 };
 
 nccl_api *load_nccl(void)
@@ -52,6 +55,7 @@ nccl_api *load_nccl(void)
     api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
     api.GroupStart = (decltype(api.GroupStart))dlsym(api.handle, "ncclGroupStart");
     api.GroupEnd = (decltype(api.GroupEnd))dlsym(api.handle, "ncclGroupEnd");
+    api.CommGetAsyncError = (decltype(api.CommGetAsyncError))dlsym(api.handle, "ncclCommGetAsyncError");   // optional
     if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy || !api.GetErrorString ||
         !api.GroupStart || !api.GroupEnd) {
         api.handle = NULL;
@@ -196,6 +200,57 @@ gd_status gdb200_dp_all_reduce(gd_backend *be, gd_backend_buffer *buffer, size_t
     return GD_OK;
 }
 
+// Host-side wait shared by gdb200_dp_join and its CPU test: polls `completed` (1 = the awaited work is done) and
+// `failed` (non-zero = the communicator reports an asynchronous error) until one of them answers or timeout_ms runs out.
+// Returns GD_OK, or GD_ERR_INTERNAL with *reason = 1 (error reported) / 2 (timeout). The callbacks carry no CUDA types,
+// so the loop can be driven by stubs on a machine without a GPU.
+gd_status gdb200_dp_wait_with(int (*completed)(void *), int (*failed)(void *), void *user, uint32_t timeout_ms, int32_t *reason)
+{
+    if (reason != NULL) *reason = 0;
+    if (completed == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    struct timespec t0, t;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (;;) {
+        if (failed != NULL && failed(user) != 0) {
+            if (reason != NULL) *reason = 1;
+            return GD_ERR_INTERNAL;
+        }
+        if (completed(user) != 0) {
+            return GD_OK;
+        }
+        clock_gettime(CLOCK_MONOTONIC, &t);
+        const double ms = (double)(t.tv_sec - t0.tv_sec) * 1.0e3 + (double)(t.tv_nsec - t0.tv_nsec) * 1.0e-6;
+        if (ms >= (double)timeout_ms) {
+            if (reason != NULL) *reason = 2;
+            return GD_ERR_INTERNAL;
+        }
+        sched_yield();
+    }
+}
+
+namespace {
+int dp_done_query(void *user)
+{
+    gd_backend *be = (gd_backend *)user;
+    return cudaEventQuery(be->dp->done) == cudaSuccess ? 1 : 0;
+}
+int dp_async_error(void *user)
+{
+    gd_backend *be = (gd_backend *)user;
+    nccl_api *api = load_nccl();
+    ncclResult_t async = ncclSuccess;
+    if (api == NULL || api->CommGetAsyncError == NULL) return 0;
+    if (api->CommGetAsyncError(be->dp->comm, &async) != ncclSuccess) return 1;
+    return (async != ncclSuccess && async != ncclInProgress) ? 1 : 0;
+}
+}  // namespace
+
+// Makes the compute stream wait for all outstanding all-reduces. The communicator's asynchronous error state is
+// polled on every call (a failed or aborted collective then surfaces here as GD_ERR_INTERNAL instead of as a hang at the
+// next synchronisation); with GDB200_DP_TIMEOUT_MS > 0 the host also waits, at most that long, for the collectives
+// themselves, so that a peer that never joins ends this rank's step with an error.
 gd_status gdb200_dp_join(gd_backend *be)
 {
     if (be == NULL || be->dp == NULL) {
@@ -204,6 +259,25 @@ gd_status gdb200_dp_join(gd_backend *be)
     if (cudaEventRecord(be->dp->done, be->dp->stream) != cudaSuccess ||
         cudaStreamWaitEvent(be->stream, be->dp->done, 0) != cudaSuccess) {
         return GD_ERR_INTERNAL;
+    }
+    if (dp_async_error(be) != 0) {
+        snprintf(be->last_error, sizeof(be->last_error), "NCCL communicator reports an asynchronous error");
+        return GD_ERR_INTERNAL;
+    }
+    static int timeout_ms = -1;
+    if (timeout_ms < 0) {
+        const char *env = getenv("GDB200_DP_TIMEOUT_MS");
+        timeout_ms = env != NULL ? atoi(env) : 0;
+        if (timeout_ms < 0) timeout_ms = 0;
+    }
+    if (timeout_ms > 0) {
+        int32_t reason = 0;
+        const gd_status st = gdb200_dp_wait_with(dp_done_query, dp_async_error, be, (uint32_t)timeout_ms, &reason);
+        if (st != GD_OK) {
+            snprintf(be->last_error, sizeof(be->last_error), reason == 2 ? "data-parallel exchange did not complete within %d ms"
+                                                                          : "NCCL communicator reports an asynchronous error (after %d ms limit armed)", timeout_ms);
+            return st;
+        }
     }
     return GD_OK;
 }

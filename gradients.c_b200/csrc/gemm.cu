@@ -319,6 +319,56 @@ gd_status batched_dispatch(gd_backend *be, int ta, int tb, const gd_backend_batc
     if (total == 0U || total != y->batch_count) {
         return GD_ERR_INVALID_ARGUMENT;
     }
+    // The innermost batch dimension goes into ONE launch (third grid dimension / third tensor-map coordinate) wherever the
+    // tensor-memory kernel takes the shape; when all batch dimensions are nested (each operand's pitch of a dimension is the
+    // extent times the pitch of the next, or the operand is broadcast over all of them) they collapse into that one
+    // dimension, otherwise the outer dimensions are walked on the host.
+    if (y->batch_rank >= 1U && total > 1U) {
+        const uint32_t r = y->batch_rank;
+        auto eff = [&](const gd_backend_batched_matrix_view *v, uint32_t d) { return v->batch_shape[d] == 1U ? (size_t)0 : v->batch_strides[d]; };
+        bool nested = true;
+        for (const gd_backend_batched_matrix_view *v : {x, w, y}) {
+            bool all_bcast = true, all_full = true;
+            for (uint32_t d = 0; d < r; ++d) {
+                all_bcast = all_bcast && (v->batch_shape[d] == 1U || y->batch_shape[d] == 1U);
+                all_full = all_full && (v->batch_shape[d] == y->batch_shape[d]);
+            }
+            bool chain = all_full;
+            for (uint32_t d = 0; chain && d + 1U < r; ++d) chain = v->batch_strides[d] == (size_t)y->batch_shape[d + 1U] * v->batch_strides[d + 1U];
+            nested = nested && (all_bcast || chain);
+        }
+        const uint32_t inner = nested ? (uint32_t)total : y->batch_shape[r - 1U];
+        const size_t outer = total / inner;
+        if (inner > 1U && inner <= 65535U) {
+            bool fast = true;
+            for (size_t bo = 0; bo < outer && fast; ++bo) {
+                size_t rem = bo, xo = 0, wo = 0, yo = 0;
+                for (int d = (int)r - 2; d >= 0 && !nested; --d) {
+                    const size_t idx = rem % y->batch_shape[d];
+                    rem /= y->batch_shape[d];
+                    xo += idx * eff(x, (uint32_t)d);
+                    wo += idx * eff(w, (uint32_t)d);
+                    yo += idx * y->batch_strides[d];
+                }
+                bool x_b = true, w_b = true;   // broadcast over everything that is batched inside the launch
+                for (uint32_t d = nested ? 0U : r - 1U; d < r; ++d) {
+                    x_b = x_b && eff(x, d) == 0U;
+                    w_b = w_b && eff(w, d) == 0U;
+                }
+                const gd_status st = gdb_gemm_tcgen05_batched(be, ta, tb, dt, x->buffer->dptr + x->offset + xo, x->row_bytes, x_b ? 0U : x->batch_strides[r - 1U],
+                                                              w->buffer->dptr + w->offset + wo, w->row_bytes, w_b ? 0U : w->batch_strides[r - 1U],
+                                                              y->buffer->dptr + y->offset + yo, y->row_bytes, y->batch_strides[r - 1U], M, N, K, inner);
+                if (st == GD_ERR_UNSUPPORTED && bo == 0U) {
+                    fast = false;            // nothing launched yet: the loop below handles every element
+                } else if (st != GD_OK) {
+                    return st;
+                }
+            }
+            if (fast) {
+                return GD_OK;
+            }
+        }
+    }
     for (size_t bi = 0; bi < total; ++bi) {
         size_t rem = bi, xo = 0, wo = 0, yo = 0;
         for (int d = (int)y->batch_rank - 1; d >= 0; --d) {

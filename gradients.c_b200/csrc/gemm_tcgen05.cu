@@ -39,13 +39,16 @@ struct smem_plan {
 };
 
 
-// grid = (n tiles, m tiles, k splits)
-template <typename T, int BN, int STAGES, bool A_MN, bool B_MN, bool SPLITK>
+// grid = (n tiles, m tiles, k splits), or, BATCHED, (n tiles, m tiles, batch): the tensor maps then have the batch as third
+// dimension (a broadcast operand has extent 1 there and is always read at index 0: za / zb say which), the output of
+// batch element z starts c_batch elements after that of z - 1, and there is no split over k.
+template <typename T, int BN, int STAGES, bool A_MN, bool B_MN, bool SPLITK, bool BATCHED = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, T *__restrict__ c,
                     size_t ldc, const T *__restrict__ bias, float *__restrict__ partial, uint32_t M, uint32_t N, uint32_t K,
-                    uint32_t k_iters_per_split, int bias_mode, int *err_flag)
+                    uint32_t k_iters_per_split, int bias_mode, int *err_flag, size_t c_batch, int a_bcast, int b_bcast)
 {
+    static_assert(!(SPLITK && BATCHED), "a batched launch uses the third grid dimension for the batch");
     using plan = smem_plan<BN, STAGES>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
@@ -56,7 +59,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const uint32_t total_k_iters = (K + BK - 1) / BK;
-    const uint32_t k_begin = blockIdx.z * k_iters_per_split;
+    const uint32_t k_begin = BATCHED ? 0U : blockIdx.z * k_iters_per_split;
+    const int za = (BATCHED && !a_bcast) ? (int)blockIdx.z : 0, zb = (BATCHED && !b_bcast) ? (int)blockIdx.z : 0;
+    if (BATCHED) c += (size_t)blockIdx.z * c_batch;
     const uint32_t k_end = min(total_k_iters, k_begin + k_iters_per_split);
     const uint32_t n_iters = k_end > k_begin ? k_end - k_begin : 0U;
 
@@ -93,20 +98,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 const uint32_t b_dst = a_dst + plan::A_BYTES;
                 const int k0 = (int)((k_begin + it) * BK);
                 mbar_expect_tx(full0 + 8 * s, plan::STAGE_BYTES);
+                auto load_a = [&](uint32_t dst, int x, int y) {
+                    if (BATCHED) tma_load_3d(dst, &tma_a, x, y, za, full0 + 8 * s); else tma_load_2d(dst, &tma_a, x, y, full0 + 8 * s);
+                };
+                auto load_b = [&](uint32_t dst, int x, int y) {
+                    if (BATCHED) tma_load_3d(dst, &tma_b, x, y, zb, full0 + 8 * s); else tma_load_2d(dst, &tma_b, x, y, full0 + 8 * s);
+                };
                 if (A_MN) {
                     // global [K, M]: box {64 m, BK k}; two boxes cover the 128 rows of the tile
-                    tma_load_2d(a_dst, &tma_a, (int)m0, k0, full0 + 8 * s);
-                    tma_load_2d(a_dst + BK * 128, &tma_a, (int)m0 + 64, k0, full0 + 8 * s);
+                    load_a(a_dst, (int)m0, k0);
+                    load_a(a_dst + BK * 128, (int)m0 + 64, k0);
                 } else {
-                    tma_load_2d(a_dst, &tma_a, k0, (int)m0, full0 + 8 * s);  // global [M, K]: box {64 k, 128 m}
+                    load_a(a_dst, k0, (int)m0);  // global [M, K]: box {64 k, 128 m}
                 }
                 if (B_MN) {
 #pragma unroll
                     for (int j = 0; j < BN / 64; ++j) {
-                        tma_load_2d(b_dst + j * BK * 128, &tma_b, (int)n0 + 64 * j, k0, full0 + 8 * s);
+                        load_b(b_dst + j * BK * 128, (int)n0 + 64 * j, k0);
                     }
                 } else {
-                    tma_load_2d(b_dst, &tma_b, k0, (int)n0, full0 + 8 * s);  // global [N, K]: box {64 k, BN n}
+                    load_b(b_dst, k0, (int)n0);  // global [N, K]: box {64 k, BN n}
                 }
             }
         }
@@ -266,7 +277,7 @@ gd_status launch(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, v
         configured = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, splits);
-    gdb_launch(kern, grid, 192, plan::TOTAL, be->stream, ta, tb, (T *)c, ldc, (const T *)bias, partial, M, N, K, k_per_split, bias_mode, be->err_flag);
+    gdb_launch(kern, grid, 192, plan::TOTAL, be->stream, ta, tb, (T *)c, ldc, (const T *)bias, partial, M, N, K, k_per_split, bias_mode, be->err_flag, (size_t)0, 0, 0);
     return gdb_launched(be, "gemm_tcgen05");
 }
 
@@ -297,7 +308,57 @@ gd_status reduce_partials(gd_backend *be, uint32_t dtype, const float *partial, 
     return gdb_launched(be, "gemm_splitk_reduce");
 }
 
+template <typename T, bool A_MN, bool B_MN>
+gd_status launch_batched(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, void *c, size_t ldc, size_t c_batch, uint32_t M, uint32_t N,
+                         uint32_t K, uint32_t batch, int a_bcast, int b_bcast)
+{
+    using plan = smem_plan<128, 4>;
+    auto kern = gemm_tcgen05_kernel<T, 128, 4, A_MN, B_MN, false, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan::TOTAL);
+    if (e != cudaSuccess) {
+        return gdb_fail(be, e, "tcgen05 batched gemm smem attribute");
+    }
+    dim3 grid((N + 127) / 128, (M + BM - 1) / BM, batch);
+    gdb_launch(kern, grid, 192, plan::TOTAL, be->stream, ta, tb, (T *)c, ldc, (const T *)nullptr, (float *)nullptr, M, N, K, (K + BK - 1) / BK, 0,
+               be->err_flag, c_batch, a_bcast, b_bcast);
+    return gdb_launched(be, "gemm_tcgen05_batched");
+}
+
 }  // namespace
+
+// `batch` contractions of one shape in ONE launch (the batch index is the third grid dimension and the third tensor-map
+// coordinate): C_z[M, N] = A_z B_z, z < batch, with byte pitches between consecutive batch elements; a pitch of 0
+// broadcasts that operand. GD_ERR_UNSUPPORTED when the shape or the alignment cannot use the TMA path.
+gd_status gdb_gemm_tcgen05_batched(gd_backend *be, int ta, int tb, uint32_t dtype, const void *a, size_t lda_bytes, size_t a_batch_bytes,
+                                   const void *b, size_t ldb_bytes, size_t b_batch_bytes, void *c, size_t ldc_bytes, size_t c_batch_bytes,
+                                   uint32_t M, uint32_t N, uint32_t K, uint32_t batch)
+{
+    if ((dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) || be->gemm_mode == 1 || batch == 0U || batch > 65535U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) % 16U) != 0U || (lda_bytes % 16U) != 0U || (ldb_bytes % 16U) != 0U || (ldc_bytes % 16U) != 0U ||
+        (a_batch_bytes % 16U) != 0U || (b_batch_bytes % 16U) != 0U || (c_batch_bytes % 2U) != 0U || (N % 8U) != 0U || (K % 8U) != 0U ||
+        M < 64U || N < 64U || K < 64U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const int a_bcast = a_batch_bytes == 0U, b_bcast = b_batch_bytes == 0U;
+    const uint64_t a_n = a_bcast ? 1U : batch, b_n = b_bcast ? 1U : batch;
+    // a broadcast operand still needs a valid (non-zero) batch pitch in its map: one whole matrix
+    const uint64_t a_bp = a_bcast ? (uint64_t)lda_bytes * (ta ? K : M) : a_batch_bytes, b_bp = b_bcast ? (uint64_t)ldb_bytes * (tb ? N : K) : b_batch_bytes;
+    CUtensorMap ma, mb;
+    const bool oka = ta ? make_tmap_batched(&ma, dtype, a, a_n, K, M, lda_bytes, a_bp, 64, BK) : make_tmap_batched(&ma, dtype, a, a_n, M, K, lda_bytes, a_bp, BK, BM);
+    const bool okb = tb ? make_tmap_batched(&mb, dtype, b, b_n, N, K, ldb_bytes, b_bp, BK, 128) : make_tmap_batched(&mb, dtype, b, b_n, K, N, ldb_bytes, b_bp, 64, BK);
+    if (!oka || !okb) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const size_t ldc = ldc_bytes / 2U, cb = c_batch_bytes / 2U;
+#define GDB_GO_B(TT) (ta ? (tb ? launch_batched<TT, true, false>(be, ma, mb, c, ldc, cb, M, N, K, batch, a_bcast, b_bcast)  \
+                               : launch_batched<TT, true, true>(be, ma, mb, c, ldc, cb, M, N, K, batch, a_bcast, b_bcast))  \
+                         : (tb ? launch_batched<TT, false, false>(be, ma, mb, c, ldc, cb, M, N, K, batch, a_bcast, b_bcast) \
+                               : launch_batched<TT, false, true>(be, ma, mb, c, ldc, cb, M, N, K, batch, a_bcast, b_bcast)))
+    return dtype == GDB_DTYPE_F16 ? GDB_GO_B(__half) : GDB_GO_B(__nv_bfloat16);
+#undef GDB_GO_B
+}
 
 // ta: A stored [K, M] (MN-major); tb: B stored [N, K] (K-major). Leading dimensions in bytes.
 gd_status gdb_gemm_tcgen05(gd_backend *be, int ta, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b,

@@ -53,6 +53,25 @@ inline bool make_tmap(CUtensorMap *m, uint32_t dtype, const void *base, uint64_t
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 3-D tensor [batch, rows, cols] of 16-bit elements (row pitch and batch pitch in bytes, both multiples of 16);
+// box = {box_cols (<= 64), box_rows, 1}. Loads are clipped per dimension, so a ragged last row tile of one batch
+// element never reads the next one.
+inline bool make_tmap_batched(CUtensorMap *m, uint32_t dtype, const void *base, uint64_t batch, uint64_t rows, uint64_t cols,
+                              uint64_t pitch_bytes, uint64_t batch_pitch_bytes, uint32_t box_cols, uint32_t box_rows)
+{
+    encode_tiled_fn fn = get_encode_fn();
+    if (fn == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[3] = {cols, rows, batch};
+    const cuuint64_t strides[2] = {pitch_bytes, batch_pitch_bytes};
+    const cuuint32_t box[3] = {box_cols, box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt = dtype == GDB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    return fn(m, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // 3-D FP32 tensor [slices, rows, cols] (dense), box = {32 cols (128 bytes), box_rows, 1}: the
 // destination of split-K partial tiles. Stores are clipped per dimension, so a ragged last row
 // tile never spills into the next slice.
@@ -103,6 +122,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
                  : "memory");
 }
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar)

@@ -304,6 +304,9 @@ PROTOTYPES = {
     "gdb200_matmul_tn_colsum": (_ST, [P, MV, MV, MV, VV]),
     "gdb200_argmax_rows": (_ST, [P, TV, F, TV]),
     "gdb200_gpt_decode_steps": (_ST, [P, C.POINTER(GptSpec), C.POINTER(GptDecodeState), I32_T, I32_T, C.POINTER(SZ)]),
+    "gdb200_inject_device_error": (_ST, [P, I32_T]),
+    "gdb200_selftest_bounded_wait": (_ST, [P, U32]),
+    "gdb200_dp_wait_with": (_ST, [P, P, P, U32, C.POINTER(I32_T)]),
     "gdb200_dp_unique_id": (_ST, [P]),
     "gdb200_dp_init": (_ST, [P, P, C.c_int, C.c_int]),
     "gdb200_dp_all_reduce": (_ST, [P, P, SZ, SZ, U32]),

@@ -16,12 +16,45 @@ from . import abi
 from .abi import F32
 
 
+class PeerLeft(RuntimeError):
+    """A rank of the job has announced that it is leaving; the ranks that remain must not enter another collective."""
+
+    def __init__(self, ranks):
+        super().__init__(f"data-parallel rank(s) {sorted(ranks)} left the job: stopping before the next collective")
+        self.ranks = sorted(ranks)
+
+
 class DataParallel:
     def __init__(self, ctx, model, rank: int, world: int, dist=None, connect: bool = True):
+        if world < 1 or not 0 <= rank < world:
+            raise ValueError(f"rank {rank} is outside a world of {world}")
+        if dist is not None and dist.is_initialized() and (dist.get_world_size() != world or dist.get_rank() != rank):
+            # a launcher and a process group that disagree would leave some rank waiting in a collective for ever
+            raise ValueError(f"rank {rank} of {world} does not match the process group (rank {dist.get_rank()} of {dist.get_world_size()})")
         self.ctx, self.model, self.rank, self.world, self.dist = ctx, model, rank, world, dist
         self.connected = False
         if connect and world > 1:
             self.connect()
+
+    # ---- departures: a rank leaves only between steps and says so first; the others look before their next launch ----
+    def _store(self):
+        from torch.distributed import distributed_c10d
+        return distributed_c10d._get_default_store()
+
+    def announce_leave(self) -> None:
+        """Called by a rank that is about to leave (between steps, nothing of its own in flight)."""
+        self._store().set(f"gdb200/left/{self.rank}", "1")
+
+    def departed(self) -> list[int]:
+        store = self._store()
+        return [r for r in range(self.world) if r != self.rank and store.check([f"gdb200/left/{r}"])]
+
+    def check_peers(self) -> None:
+        """Raises PeerLeft when a peer has announced its departure (one round trip to the rendezvous store: call it
+        before a step whenever that cost is acceptable, not from inside the step)."""
+        gone = self.departed()
+        if gone:
+            raise PeerLeft(gone)
 
     def exchange_unique_id(self) -> bytes:
         """Rank 0 creates the NCCL id; every rank returns the same 128 bytes."""

@@ -544,6 +544,15 @@ typedef struct gdb200_gpt_decode_state {
 gd_status gdb200_gpt_decode_steps(gd_backend *backend, const gdb200_gpt_spec *spec, const gdb200_gpt_decode_state *state,
                                   int32_t n_steps, int32_t use_graph, size_t *scratch_used);
 
+/* Failure detection without a fault (the reference reports a failed command buffer as GD_ERR_INTERNAL at flush,
+ * src/backends/metal/backend_metal.m:569-573; here every device-side wait is bounded and reports through an error word
+ * that flush / fence_wait read). gdb200_inject_device_error stores `code` in that word in stream order;
+ * gdb200_selftest_bounded_wait runs a one-warp kernel that polls an mbarrier nobody arrives at for at most max_iters
+ * (<= 2^20) iterations, stores code 399 and returns. After either, gd_backend_flush returns GD_ERR_INTERNAL once,
+ * gdb200_last_error names the code, and the backend stays usable. */
+gd_status gdb200_inject_device_error(gd_backend *backend, int32_t code);
+gd_status gdb200_selftest_bounded_wait(gd_backend *backend, uint32_t max_iters);
+
 /* Data-parallel gradient exchange (the reference has no collective; one process per GPU).
  * id_bytes is the 128-byte ncclUniqueId produced by gdb200_dp_unique_id on rank 0. */
 gd_status gdb200_dp_unique_id(void *id_bytes_128);
@@ -551,8 +560,13 @@ gd_status gdb200_dp_init(gd_backend *backend, const void *id_bytes_128, int rank
 /* In-place sum all-reduce of `count` elements of dtype (F16/BF16/F32) on the comm stream,
  * ordered after everything already enqueued on the compute stream. */
 gd_status gdb200_dp_all_reduce(gd_backend *backend, gd_backend_buffer *buffer, size_t offset, size_t count, uint32_t dtype);
-/* Make the compute stream wait for all outstanding all-reduces. */
+/* Make the compute stream wait for all outstanding all-reduces. Polls the communicator's asynchronous error state
+ * (GD_ERR_INTERNAL when it reports one); with GDB200_DP_TIMEOUT_MS > 0 in the environment the host also waits, at most
+ * that long, for the collectives to complete and returns GD_ERR_INTERNAL when they do not (a peer that never joined). */
 gd_status gdb200_dp_join(gd_backend *backend);
+/* The polling loop behind that wait, with the two queries as callbacks (completed: 1 = done; failed: non-zero = the
+ * communicator reports an error) so that it can be exercised without a GPU. *reason: 0 ok, 1 error reported, 2 timeout. */
+gd_status gdb200_dp_wait_with(int (*completed)(void *), int (*failed)(void *), void *user, uint32_t timeout_ms, int32_t *reason);
 void gdb200_dp_shutdown(gd_backend *backend);
 
 #ifdef __cplusplus

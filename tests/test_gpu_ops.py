@@ -2,6 +2,7 @@
 oracle on the same seeded inputs. Integer / mask / copy work is bit-exact; floating-point work
 is within gpu_util.TOL of the FP32 oracle."""
 import ctypes as C
+import math
 
 import numpy as np
 import pytest
@@ -663,3 +664,61 @@ def test_sdpa_backward_with_forward_output_matches_the_two_pass_backward(step, d
     # dV does not depend on D; the two paths form P in different kernels (tensor-memory kernel: exp2 with 1/l folded
     # into the exponent; mma.sync kernel: exp2 times 1/l), so it agrees to the rounding of P, not bit for bit
     close(grads[True][2], grads[False][2], dtype, scale=2, what="dv single pass vs two passes")
+
+
+# ------------------------------------------------------------------ batched contractions (src/ops/matmul/core_matmul.c:47,54)
+def _bview(t, batch_shape, rows, cols, strides_elems, es):
+    v = abi.BatchedMatrixView()
+    v.buffer, v.offset, v.rows, v.cols, v.row_bytes, v.dtype = t.buffer, t.offset, rows, cols, cols * es, t.dtype
+    v.batch_rank = len(batch_shape)
+    v.batch_count = int(np.prod(batch_shape))
+    for d, (n, s) in enumerate(zip(batch_shape, strides_elems)):
+        v.batch_shape[d], v.batch_strides[d] = n, s * es
+    return v
+
+
+@pytest.mark.parametrize("entry,ta,tb", [("batched_matmul", 0, 0), ("batched_matmul_nt", 0, 1), ("batched_matmul_tn", 1, 0)])
+@pytest.mark.parametrize("case", ["plain", "broadcast_w", "rank2_nested", "rank2_strided", "small_fallback"])
+def test_batched_matmul_against_oracle(step, entry, ta, tb, case):
+    """x[..., M, K] w[..., K, N] with numpy-style broadcasting over the batch dimensions, against torch.matmul in FP32 rounded
+    once. `plain` / `broadcast_w` / `rank2_nested` run as ONE launch with the batch as third grid dimension, `rank2_strided`
+    (a permuted outer dimension) as one launch per outer index, `small_fallback` on the portable kernel per element."""
+    ctx, lib, dtype, es = step, step.lib, F16, 2
+    m, k, n = (200, 192, 136) if case != "small_fallback" else (24, 40, 16)
+    ybs = {"plain": (5,), "broadcast_w": (4,), "rank2_nested": (2, 3), "rank2_strided": (2, 3), "small_fallback": (3,)}[case]
+    xbs = ybs
+    wbs = tuple(1 for _ in ybs) if case == "broadcast_w" else ybs
+    r = rng(300 + len(case))
+    xs, ws = ((k, m) if ta else (m, k)), ((n, k) if tb else (k, n))
+    x = rnd_np(r.standard_normal(xbs + xs).astype(np.float32), dtype)
+    w = rnd_np((r.standard_normal(wbs + ws) * 0.1).astype(np.float32), dtype)
+    xt, wt = dev(ctx, x, dtype), dev(ctx, w, dtype)
+    yt = ctx.scratch_empty(dtype, ybs + (m, n))
+
+    def strides(bs, mat, permuted=False):
+        st, acc = [], mat[0] * mat[1]
+        for d in reversed(range(len(bs))):
+            st.insert(0, 0 if bs[d] == 1 else acc)
+            acc *= bs[d]
+        return st
+
+    xst, wst, yst = strides(xbs, xs), strides(wbs, ws), strides(ybs, (m, n))
+    if case == "rank2_strided":
+        # x is stored [3, 2, ...] and viewed as [2, 3, ...]: the outer pitch is not the inner extent times the inner pitch
+        x = np.ascontiguousarray(np.transpose(x, (1, 0, 2, 3)))      # storage order [3, 2, ...]
+        xt = dev(ctx, x, dtype)
+        xst = [xs[0] * xs[1], 2 * xs[0] * xs[1]]                     # view dim 0 (size 2) steps one matrix, dim 1 (size 3) steps two
+        x = np.transpose(x, (1, 0, 2, 3))                            # logical [2, 3, ...] for the oracle
+    xv, wv, yv = _bview(xt, xbs, xs[0], xs[1], xst, es), _bview(wt, wbs, ws[0], ws[1], wst, es), _bview(yt, ybs, m, n, yst, es)
+    launches0 = ctx.launch_count()
+    ctx.check(getattr(lib, "gd_backend_" + entry)(ctx.backend, byref(xv), byref(wv), byref(yv)), entry)
+    n_launch = ctx.launch_count() - launches0
+    tx, tw = torch.from_numpy(x), torch.from_numpy(w)
+    if ta:
+        tx = tx.transpose(-1, -2)
+    if tb:
+        tw = tw.transpose(-1, -2)
+    want = rnd_np(torch.matmul(tx, tw).numpy(), dtype)
+    close(host(yt), want, dtype, scale=math.sqrt(k) / 4, what=f"{entry} {case}")
+    expect = {"plain": 1, "broadcast_w": 1, "rank2_nested": 1, "rank2_strided": 2, "small_fallback": 3}[case]
+    assert n_launch == expect, (case, n_launch)
