@@ -333,6 +333,10 @@ gd_status gdb_gemm_skinny_swiglu(gd_backend *be, uint32_t dtype, const void *a, 
                                  const void *bias, void *c, size_t ldc_bytes, uint32_t M, uint32_t N, uint32_t K);
 gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,
                           void *c, size_t ldc_bytes, const void *bias, int bias_mode, uint32_t M, uint32_t N, uint32_t K);
+// up / gate projection with the SwiGLU gate in the epilogue of the CTA-pair kernel: x12 [M, 2F] and act [M, F] from one contraction.
+gd_status gdb_gemm_tcgen05_pair_swiglu(gd_backend *be, uint32_t dtype, const void *x, size_t ldx_bytes, const void *w, size_t ldw_bytes,
+                                       const void *bias, void *x12, size_t ld12_bytes, void *act, size_t ldact_bytes, uint32_t M, uint32_t F,
+                                       uint32_t K);
 // CTA-pair persistent variant; *splits_out > 1 means FP32 partials were left in the workspace.
 gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype,
                                 const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,

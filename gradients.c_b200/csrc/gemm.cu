@@ -477,6 +477,47 @@ gd_status gdb200_matmul_nt_bias_swiglu(gd_backend *be, const gd_backend_matrix_v
                                   bias->buffer->dptr + bias->offset, out->buffer->dptr + out->offset, out->row_bytes, (uint32_t)x->rows,
                                   (uint32_t)out->cols, (uint32_t)x->cols);
 }
+// up_gate[M, 2F] = round(round(x w^T) + bias) AND act[M, F] = swiglu_split(up_gate) from one contraction (training path:
+// the backward pass needs up_gate). Same bits as gdb200_matmul_nt_bias followed by gd_backend_swiglu_split_forward, which is
+// also what runs when the fused kernel does not take the shape.
+gd_status gdb200_matmul_nt_bias_swiglu_both(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
+                                            const gd_backend_vector_view *bias, const gd_backend_matrix_view *up_gate, const gd_backend_matrix_view *act)
+{
+    if (be == NULL || x == NULL || w == NULL || bias == NULL || up_gate == NULL || act == NULL || bias->buffer == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = act->dtype;
+    const size_t es = gdb_dtype_size(dt);
+    if (x->dtype != dt || w->dtype != dt || bias->dtype != dt || up_gate->dtype != dt || !mv_ok(x, es) || !mv_ok(w, es) || !mv_ok(up_gate, es) ||
+        !mv_ok(act, es) || x->cols != w->cols || w->rows != 2U * act->cols || up_gate->cols != w->rows || act->rows != x->rows ||
+        up_gate->rows != x->rows || bias->length != w->rows || !gdb_range_ok(bias->buffer, bias->offset, (size_t)bias->length * es)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    cudaSetDevice(be->device);
+    if (be->gemm_mode == 0 || be->gemm_mode == 2) {
+        const gd_status st = gdb_gemm_tcgen05_pair_swiglu(be, dt, x->buffer->dptr + x->offset, x->row_bytes, w->buffer->dptr + w->offset, w->row_bytes,
+                                                          bias->buffer->dptr + bias->offset, up_gate->buffer->dptr + up_gate->offset, up_gate->row_bytes,
+                                                          act->buffer->dptr + act->offset, act->row_bytes, x->rows, act->cols, x->cols);
+        if (st != GD_ERR_UNSUPPORTED) {
+            return st;
+        }
+    }
+    gd_status st = gdb200_matmul_nt_bias(be, x, w, bias, up_gate);
+    if (st != GD_OK) {
+        return st;
+    }
+    gd_backend_tensor_view uv, av;
+    memset(&uv, 0, sizeof(uv));
+    memset(&av, 0, sizeof(av));
+    if (up_gate->row_bytes != (size_t)up_gate->cols * es || act->row_bytes != (size_t)act->cols * es) {
+        return GD_ERR_UNSUPPORTED;   // the unfused pair of calls takes contiguous tensors
+    }
+    uv.buffer = up_gate->buffer; uv.offset = up_gate->offset; uv.count = (size_t)up_gate->rows * up_gate->cols; uv.dtype = dt; uv.rank = 2;
+    uv.shape[0] = up_gate->rows; uv.shape[1] = up_gate->cols; uv.strides[0] = up_gate->cols; uv.strides[1] = 1;
+    av.buffer = act->buffer; av.offset = act->offset; av.count = (size_t)act->rows * act->cols; av.dtype = dt; av.rank = 2;
+    av.shape[0] = act->rows; av.shape[1] = act->cols; av.strides[0] = act->cols; av.strides[1] = 1;
+    return gd_backend_swiglu_split_forward(be, &uv, &av);
+}
 gd_status gdb200_matmul_tn_colsum(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_matrix_view *y,
                                   const gd_backend_vector_view *colsum)
 {

@@ -27,16 +27,16 @@ namespace {
 using namespace gdb_t5;
 
 constexpr int PBN = 256;         // tile columns of the pair
-constexpr int PSTAGES = 5;
+constexpr int P_STAGES_DEFAULT = 5;
 constexpr int P_EPI_WARPS = 8;   // two warps per tensor-memory lane quadrant, each drains half of the tile columns
 constexpr int P_THREADS = 32 * (2 + P_EPI_WARPS);
 constexpr int P_A_BYTES = BM * BK * 2;
 constexpr int P_B_BYTES = (PBN / 2) * BK * 2;
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
-constexpr int P_STAGING_PER_WARP = 2 * 4096;   // two 32-row x 128-byte buffers
-constexpr int P_STAGING_BYTES = P_EPI_WARPS * P_STAGING_PER_WARP;
-constexpr int P_SMEM_TOTAL = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 256 + 1024;
-constexpr int P_SMEM_TOTAL_COLSUM = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 1024 + 1024 + 1024;   // barriers padded to 1 KB, ones tile, alignment slack
+// default: two 32-row x 128-byte staging buffers per epilogue warp
+constexpr int P_SMEM_TOTAL = P_STAGES_DEFAULT * P_STAGE_BYTES + P_EPI_WARPS * 2 * 4096 + 256 + 1024;
+constexpr int P_SMEM_TOTAL_COLSUM = P_STAGES_DEFAULT * P_STAGE_BYTES + P_EPI_WARPS * 2 * 4096 + 1024 + 1024 + 1024;   // barriers padded to 1 KB, ones tile, alignment slack
+constexpr int P_SMEM_TOTAL_SWIGLU = (P_STAGES_DEFAULT - 1) * P_STAGE_BYTES + P_EPI_WARPS * 3 * 4096 + 256 + 1024;
 
 // COLSUM (split-K output only): the units of the first tile column also accumulate the sums of A over the
 // contraction, colsum[m] = sum_k A[m, k], by one more MMA per k-step against a tile of ones (N = 16; every output
@@ -44,14 +44,28 @@ constexpr int P_SMEM_TOTAL_COLSUM = PSTAGES * P_STAGE_BYTES + P_STAGING_BYTES + 
 // linear layer for free while its weight gradient dW = dY^T X is computed (A = dY^T). Tensor memory then holds ONE
 // accumulator (256 columns) plus the 16 column-sum columns, so units are not overlapped (split-K launches run about one
 // unit per CTA pair anyway).
-template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM>
+//
+// SWIGLU (up / gate projection of a SwiGLU block, w stored [2F, K] with the x1 rows first: reference
+// src/ops/swiglu_split_linear/core_swiglu_split_linear.c:226-301 composes matmul_nt + add + swiglu_split): a unit covers 128
+// columns j of the activation. CTA 0 of the pair fetches weight rows j (x1), CTA 1 weight rows F + j (x2), so the pair's
+// accumulator holds the x1 tile in columns 0..127 and the matching x2 tile in columns 128..255, and the epilogue forms
+// x12 = round(round(acc) + bias) and act = round(x1 * x2 * sigmoid(x2)) from one pass over tensor memory, with the rounding
+// points of the three separate calls. N is then F, tma_c maps the [M, 2F] x12 matrix (kept for the backward pass) and
+// tma_act the [M, F] activation; a warp stages its x1, x2 and act tile (32 rows x 64 columns each) and issues three TMA stores.
+template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM, bool SWIGLU = false>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const T *__restrict__ bias, uint32_t M, uint32_t N, uint32_t K,
                  uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t k_iters_per_split, int bias_mode, int *err_flag,
-                 float *__restrict__ colsum_partial)
+                 float *__restrict__ colsum_partial, const __grid_constant__ CUtensorMap tma_act)
 {
     static_assert(!COLSUM || SPLITK, "column sums ride on the split-K (FP32 partial) output path");
+    static_assert(!SWIGLU || (!SPLITK && !A_MN && !B_MN), "the SwiGLU epilogue belongs to y = x w^T with direct output");
+    // The SwiGLU epilogue stages three output tiles per warp (x1, x2, act) instead of two alternating ones: it runs with
+    // one operand stage less to make room for them.
+    constexpr int PSTAGES = SWIGLU ? P_STAGES_DEFAULT - 1 : P_STAGES_DEFAULT;
+    constexpr int P_STAGING_PER_WARP = SWIGLU ? 3 * 4096 : 2 * 4096;
+    constexpr int P_STAGING_BYTES = P_EPI_WARPS * P_STAGING_PER_WARP;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023U) & ~(uintptr_t)1023U);
     unsigned char *staging = smem + PSTAGES * P_STAGE_BYTES;
@@ -103,7 +117,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             bool ok = true;
             for (uint32_t u = cluster_id; u < units && ok; u += n_clusters) {
                 const uint32_t tn = u % tiles_n, tm = (u / tiles_n) % tiles_m, z = u / (tiles_n * tiles_m);
-                const int am = (int)(tm * 2 * BM + rank * BM), bn = (int)(tn * PBN + rank * (PBN / 2));
+                const int am = (int)(tm * 2 * BM + rank * BM), bn = SWIGLU ? (int)(tn * (PBN / 2) + rank * N) : (int)(tn * PBN + rank * (PBN / 2));
                 const uint32_t k_begin = z * k_iters_per_split;
                 const uint32_t k_end = min(total_k_iters, k_begin + k_iters_per_split);
                 for (uint32_t kb = k_begin; kb < k_end; ++kb, ++it) {
@@ -209,6 +223,72 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 const uint32_t row = row0 + lane;
                 if (row < M) colsum_partial[(size_t)z * M + row] = __uint_as_float(cs[0]);
             }
+            if (SWIGLU) {
+                // this warp: 32 rows x 64 activation columns, 32 at a time (x1 and x2 values of the same columns); the three
+                // staged tiles of the previous unit have been read by their stores long ago (a whole unit lies between)
+                if (lane == 0) bulk_wait_group_read<0>();
+                __syncwarp();
+                unsigned char *r1 = my_stage + lane * 128, *r2 = r1 + 4096, *ra = r2 + 4096;
+                const uint32_t acol = tn * (PBN / 2) + (uint32_t)(chalf * 64);    // first activation column of this warp
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    const uint32_t lc = (uint32_t)(chalf * 64 + c * 32);   // column inside the unit's 128
+                    uint32_t v1[32], v2[32];
+                    tmem_ld_32x32b_x32_nowait(tbase + lc, v1);
+                    tmem_ld_32x32b_x32_nowait(tbase + PBN / 2 + lc, v2);
+                    tmem_ld_wait();
+                    if (c == 1) {
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * buf);
+                    }
+                    const uint32_t col0 = acol + c * 32;       // activation column = x1 column; x2 column = N + col0
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint32_t o1[4], o2[4], oa[4];
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            float a0 = __uint_as_float(v1[j + e]), a1 = __uint_as_float(v1[j + e + 1]);
+                            float z0 = __uint_as_float(v2[j + e]), z1 = __uint_as_float(v2[j + e + 1]);
+                            if (bias != nullptr) {
+                                if (bias_mode == 2) {
+                                    a0 = gdb_io<T>::rnd(a0);
+                                    a1 = gdb_io<T>::rnd(a1);
+                                    z0 = gdb_io<T>::rnd(z0);
+                                    z1 = gdb_io<T>::rnd(z1);
+                                }
+                                const uint32_t cc = col0 + j + e;
+                                a0 += cc < N ? gdb_io<T>::ld(bias, cc) : 0.0f;
+                                a1 += cc + 1 < N ? gdb_io<T>::ld(bias, cc + 1) : 0.0f;
+                                z0 += cc < N ? gdb_io<T>::ld(bias, N + cc) : 0.0f;
+                                z1 += cc + 1 < N ? gdb_io<T>::ld(bias, N + cc + 1) : 0.0f;
+                            }
+                            a0 = gdb_io<T>::rnd(a0);
+                            a1 = gdb_io<T>::rnd(a1);
+                            z0 = gdb_io<T>::rnd(z0);
+                            z1 = gdb_io<T>::rnd(z1);
+                            o1[e >> 1] = half_pack<T>::pack(a0, a1);
+                            o2[e >> 1] = half_pack<T>::pack(z0, z1);
+                            oa[e >> 1] = half_pack<T>::pack(a0 * (z0 * gdb_swiglu_sigmoid(z0)), a1 * (z1 * gdb_swiglu_sigmoid(z1)));
+                        }
+                        const int chunk = ((c * 4 + (j >> 3)) ^ (lane & 7)) << 4;   // 16-byte chunk of the 128-byte swizzled row
+                        *reinterpret_cast<uint4 *>(r1 + chunk) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+                        *reinterpret_cast<uint4 *>(r2 + chunk) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+                        *reinterpret_cast<uint4 *>(ra + chunk) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (row0 < M && acol < N) {
+                        tma_store_2d(&tma_c, (int)acol, (int)row0, smem_u32(my_stage));
+                        tma_store_2d(&tma_c, (int)(N + acol), (int)row0, smem_u32(my_stage + 4096));
+                        tma_store_2d(&tma_act, (int)acol, (int)row0, smem_u32(my_stage + 8192));
+                    }
+                    bulk_commit_group();
+                }
+                continue;
+            }
             constexpr int NCH = PBN / CHUNK_COLS / 2;   // chunks per warp
 #pragma unroll 1
             for (int c = chalf * NCH; c < (chalf + 1) * NCH; ++c) {
@@ -303,13 +383,13 @@ int max_clusters(gd_backend *be, const void *kern, int smem_bytes)
     return n < be->sm_count / 2 ? n : be->sm_count / 2;
 }
 
-template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM = false>
+template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM = false, bool SWIGLU = false>
 gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const void *bias, uint32_t M,
                       uint32_t N, uint32_t K, uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t kps, int bias_mode, int *clusters_out,
-                      float *colsum_partial = nullptr)
+                      float *colsum_partial = nullptr, const CUtensorMap *tact = nullptr)
 {
-    constexpr int SMEM = COLSUM ? P_SMEM_TOTAL_COLSUM : P_SMEM_TOTAL;
-    auto kern = gemm_pair_kernel<T, A_MN, B_MN, SPLITK, COLSUM>;
+    constexpr int SMEM = SWIGLU ? P_SMEM_TOTAL_SWIGLU : (COLSUM ? P_SMEM_TOTAL_COLSUM : P_SMEM_TOTAL);
+    auto kern = gemm_pair_kernel<T, A_MN, B_MN, SPLITK, COLSUM, SWIGLU>;
     static int clusters = -1;
     if (clusters < 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -341,7 +421,8 @@ gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &
     cfg.stream = be->stream;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, (const T *)bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, be->err_flag, colsum_partial);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, (const T *)bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, be->err_flag, colsum_partial,
+                                       tact != nullptr ? *tact : tc);
     if (e != cudaSuccess) {
         be->launches += 1U;
         return gdb_fail(be, e, "gemm_tcgen05_pair");
@@ -437,4 +518,27 @@ gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype, 
         *splits_out = splits;
     }
     return st;
+}
+
+// x12[M, 2F] = round(round(x w^T) + bias) and act[M, F] = x1 * x2 * sigmoid(x2) from ONE contraction (w stored [2F, K], x1
+// rows first): the SwiGLU epilogue of the CTA-pair kernel. GD_ERR_UNSUPPORTED when the shape does not fit it (the caller
+// then issues the three separate calls, which give the same bits).
+gd_status gdb_gemm_tcgen05_pair_swiglu(gd_backend *be, uint32_t dtype, const void *x, size_t ldx_bytes, const void *w, size_t ldw_bytes,
+                                       const void *bias, void *x12, size_t ld12_bytes, void *act, size_t ldact_bytes, uint32_t M, uint32_t F,
+                                       uint32_t K)
+{
+    const uintptr_t al = (uintptr_t)x | (uintptr_t)w | (uintptr_t)x12 | (uintptr_t)act;
+    if ((dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) || M < 256U || F < 128U || (F % 128U) != 0U || K < 64U || (K % 8U) != 0U || (al % 16U) != 0U ||
+        (ldx_bytes % 16U) != 0U || (ldw_bytes % 16U) != 0U || (ld12_bytes % 16U) != 0U || (ldact_bytes % 16U) != 0U || bias == nullptr) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    CUtensorMap ma, mb, m12, mact;
+    if (!make_tmap(&ma, dtype, x, M, K, ldx_bytes, BK, BM) || !make_tmap(&mb, dtype, w, 2ULL * F, K, ldw_bytes, BK, PBN / 2) ||
+        !make_tmap(&m12, dtype, x12, M, 2ULL * F, ld12_bytes, 64, 32) || !make_tmap(&mact, dtype, act, M, F, ldact_bytes, 64, 32)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const uint32_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = F / (PBN / 2), kps = (K + BK - 1) / BK;
+    return dtype == GDB_DTYPE_F16
+               ? launch_pair<__half, false, false, false, false, true>(be, ma, mb, m12, bias, M, F, K, tiles_m, tiles_n, 1, kps, 2, nullptr, nullptr, &mact)
+               : launch_pair<__nv_bfloat16, false, false, false, false, true>(be, ma, mb, m12, bias, M, F, K, tiles_m, tiles_n, 1, kps, 2, nullptr, nullptr, &mact);
 }

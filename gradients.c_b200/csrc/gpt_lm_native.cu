@@ -384,11 +384,15 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         Ten proj = linear_t(c, sv.attn, c.param(pb + 3, {D, D}), c.param(pb + 4, {D}), T, D, D);
         memset(&sv.mask2, 0, sizeof(sv.mask2));
         residual_then_norm(x, proj, c.param(pb + 5, {D}), seed_of(SITE_ATTN, (uint64_t)i), &sv.resid, &sv.mask1, &sv.normed2, &sv.inv2);
-        sv.up_gate = linear_t(c, sv.normed2, c.param(pb + 6, {2 * F, D}), c.param(pb + 7, {2 * F}), T, D, 2 * F);
+        // up / gate projection and the SwiGLU gate: one contraction whose epilogue writes both (same bits as the three calls)
+        sv.up_gate = c.alloc(dt, {T, 2 * F});
         sv.act = c.alloc(dt, {T, F});
         {
-            gd_backend_tensor_view a = tv(sv.up_gate), o = tv(sv.act);
-            c.ok(gd_backend_swiglu_split_forward(be, &a, &o), "swiglu_split_forward");
+            const Ten w = c.param(pb + 6, {2 * F, D}), b = c.param(pb + 7, {2 * F});
+            gd_backend_matrix_view xm = mv(sv.normed2, (uint32_t)T, (uint32_t)D), wm = mv(w, (uint32_t)(2 * F), (uint32_t)D);
+            gd_backend_matrix_view um = mv(sv.up_gate, (uint32_t)T, (uint32_t)(2 * F)), am = mv(sv.act, (uint32_t)T, (uint32_t)F);
+            gd_backend_vector_view bv = vv(b, 0, (uint32_t)(2 * F));
+            c.ok(gdb200_matmul_nt_bias_swiglu_both(be, &xm, &wm, &bv, &um, &am), "matmul_nt_bias + swiglu_split");
         }
         Ten mlp = c.alloc(dt, {T, D});
         {

@@ -406,6 +406,14 @@ gd_status gdb200_matmul_nt_bias(gd_backend *backend, const gd_backend_matrix_vie
  * multiple of 128, 16-byte aligned rows); GD_ERR_UNSUPPORTED otherwise, and the caller issues the two calls. */
 gd_status gdb200_matmul_nt_bias_swiglu(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
                                        const gd_backend_vector_view *bias, const gd_backend_matrix_view *out);
+/* Training form of the same fusion: up_gate [M, 2F] = round(round(x w^T) + bias) (kept for the backward pass) AND
+ * act [M, F] = swiglu_split(up_gate) from one contraction whose epilogue reads the x1 and the x2 accumulator tile together
+ * (the reference composes matmul_nt, add and swiglu_split: src/ops/linear_transposed_weight/core_linear_transposed_weight.c:51-79,
+ * src/ops/swiglu_split_linear/core_swiglu_split_linear.c:226-301). Bit-identical to those three calls, which also run when the
+ * fused kernel does not take the shape. */
+gd_status gdb200_matmul_nt_bias_swiglu_both(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
+                                            const gd_backend_vector_view *bias, const gd_backend_matrix_view *up_gate,
+                                            const gd_backend_matrix_view *act);
 
 /* gd_backend_sdpa_varlen_backward (src/core/backend.h:699-709) for a caller that still holds the forward output `out`
  * [N, Hq, Dh] and can lend FP32 scratch `dq_accum` of q's element count: D = rowsum(grad_out o out) replaces the

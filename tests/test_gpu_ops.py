@@ -722,3 +722,28 @@ def test_batched_matmul_against_oracle(step, entry, ta, tb, case):
     close(host(yt), want, dtype, scale=math.sqrt(k) / 4, what=f"{entry} {case}")
     expect = {"plain": 1, "broadcast_w": 1, "rank2_nested": 1, "rank2_strided": 2, "small_fallback": 3}[case]
     assert n_launch == expect, (case, n_launch)
+
+
+@pytest.mark.parametrize("dtype,m,k,f", [(F16, 1024, 512, 1536), (BF16, 777, 256, 384), (F16, 300, 192, 128), (F16, 96, 128, 128)])
+def test_up_gate_projection_with_swiglu_epilogue_is_bit_identical_to_the_three_calls(step, dtype, m, k, f):
+    """gdb200_matmul_nt_bias_swiglu_both (x12 and act from one contraction, SwiGLU in the epilogue of the CTA-pair kernel; the
+    last shape is below its 256-row minimum and takes the unfused calls) against gdb200_matmul_nt_bias followed by
+    gd_backend_swiglu_split_forward bit for bit, and against the oracle."""
+    ctx, lib = step, step.lib
+    r = rng(410 + m)
+    x = rnd_np(r.standard_normal((m, k)).astype(np.float32), dtype)
+    w = rnd_np((r.standard_normal((2 * f, k)) * 0.05).astype(np.float32), dtype)
+    b = rnd_np((r.standard_normal(2 * f) * 0.1).astype(np.float32), dtype)
+    xt, wt, bt = dev(ctx, x, dtype), dev(ctx, w, dtype), dev(ctx, b, dtype)
+    ug0, act0 = ctx.scratch_empty(dtype, (m, 2 * f)), ctx.scratch_empty(dtype, (m, f))
+    ug1, act1 = ctx.scratch_empty(dtype, (m, 2 * f)), ctx.scratch_empty(dtype, (m, f))
+    xm, wm, bv = xt.mv(m, k), wt.mv(2 * f, k), bt.vv()
+    ctx.check(lib.gdb200_matmul_nt_bias(ctx.backend, byref(xm), byref(wm), byref(bv), byref(ug0.mv(m, 2 * f))), "matmul_nt_bias")
+    ctx.check(lib.gd_backend_swiglu_split_forward(ctx.backend, byref(ug0.tv()), byref(act0.tv())), "swiglu_split_forward")
+    ctx.check(lib.gdb200_matmul_nt_bias_swiglu_both(ctx.backend, byref(xm), byref(wm), byref(bv), byref(ug1.mv(m, 2 * f)), byref(act1.mv(m, f))), "fused")
+    assert np.array_equal(ug1.read().view(np.uint16), ug0.read().view(np.uint16))
+    assert np.array_equal(act1.read().view(np.uint16), act0.read().view(np.uint16))
+    sd = storage_name(dtype)
+    want_ug = O.linear_transposed_weight_forward(t32(x), t32(w), t32(b), sd)
+    close(host(ug1), want_ug, dtype, scale=math.sqrt(k) / 4, what="up_gate")
+    close(host(act1), O.swiglu_split_forward(torch.from_numpy(host(ug1)), sd), dtype, scale=2, what="act")
