@@ -337,6 +337,9 @@ gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a,
 gd_status gdb_gemm_tcgen05_pair_swiglu(gd_backend *be, uint32_t dtype, const void *x, size_t ldx_bytes, const void *w, size_t ldw_bytes,
                                        const void *bias, void *x12, size_t ld12_bytes, void *act, size_t ldact_bytes, uint32_t M, uint32_t F,
                                        uint32_t K);
+// input gradient of the down projection with the SwiGLU backward in the epilogue: d_x12 [M, 2F] from g [M, K], w [F, K], x12 [M, 2F]
+gd_status gdb_gemm_tcgen05_pair_swiglu_bwd(gd_backend *be, uint32_t dtype, const void *g, size_t ldg_bytes, const void *w, size_t ldw_bytes,
+                                           const void *x12, size_t ld12_bytes, void *d_x12, size_t ldd_bytes, uint32_t M, uint32_t F, uint32_t K);
 // CTA-pair persistent variant; *splits_out > 1 means FP32 partials were left in the workspace.
 gd_status gdb_gemm_tcgen05_pair(gd_backend *be, int ta, int tb, uint32_t dtype,
                                 const void *a, size_t lda_bytes, const void *b, size_t ldb_bytes,

@@ -495,6 +495,9 @@ gd_status gdb200_matmul_nt_bias_swiglu_both(gd_backend *be, const gd_backend_mat
     }
     cudaSetDevice(be->device);
     if (be->gemm_mode == 0 || be->gemm_mode == 2) {
+        // counted as the contraction it is (2 M (2F) K FLOP; x, w read, x12 and act written)
+        profile_scope scope(be, 2.0 * x->rows * (double)w->rows * x->cols,
+                            (double)es * ((double)x->rows * x->cols + (double)w->rows * w->cols + (double)x->rows * w->rows + (double)x->rows * act->cols));
         const gd_status st = gdb_gemm_tcgen05_pair_swiglu(be, dt, x->buffer->dptr + x->offset, x->row_bytes, w->buffer->dptr + w->offset, w->row_bytes,
                                                           bias->buffer->dptr + bias->offset, up_gate->buffer->dptr + up_gate->offset, up_gate->row_bytes,
                                                           act->buffer->dptr + act->offset, act->row_bytes, x->rows, act->cols, x->cols);
@@ -517,6 +520,31 @@ gd_status gdb200_matmul_nt_bias_swiglu_both(gd_backend *be, const gd_backend_mat
     av.buffer = act->buffer; av.offset = act->offset; av.count = (size_t)act->rows * act->cols; av.dtype = dt; av.rank = 2;
     av.shape[0] = act->rows; av.shape[1] = act->cols; av.strides[0] = act->cols; av.strides[1] = 1;
     return gd_backend_swiglu_split_forward(be, &uv, &av);
+}
+// d_up_gate[M, 2F] = swiglu_split_backward(up_gate, round(g w^T)), w stored [F, K]: gd_backend_matmul_nt into a scratch dact followed
+// by gd_backend_swiglu_split_backward, in one launch and without the scratch. GD_ERR_UNSUPPORTED when the fused kernel does
+// not take the shape: the caller then makes the two calls (same bits).
+gd_status gdb200_matmul_nt_swiglu_backward(gd_backend *be, const gd_backend_matrix_view *g, const gd_backend_matrix_view *w,
+                                           const gd_backend_matrix_view *up_gate, const gd_backend_matrix_view *d_up_gate)
+{
+    if (be == NULL || g == NULL || w == NULL || up_gate == NULL || d_up_gate == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = d_up_gate->dtype;
+    const size_t es = gdb_dtype_size(dt);
+    if (g->dtype != dt || w->dtype != dt || up_gate->dtype != dt || !mv_ok(g, es) || !mv_ok(w, es) || !mv_ok(up_gate, es) || !mv_ok(d_up_gate, es) ||
+        g->cols != w->cols || up_gate->cols != 2U * w->rows || d_up_gate->cols != up_gate->cols || up_gate->rows != g->rows || d_up_gate->rows != g->rows) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (be->gemm_mode != 0 && be->gemm_mode != 2) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    cudaSetDevice(be->device);
+    profile_scope scope(be, 2.0 * g->rows * (double)w->rows * g->cols,
+                        (double)es * ((double)g->rows * g->cols + (double)w->rows * w->cols + 2.0 * (double)g->rows * up_gate->cols));
+    return gdb_gemm_tcgen05_pair_swiglu_bwd(be, dt, g->buffer->dptr + g->offset, g->row_bytes, w->buffer->dptr + w->offset, w->row_bytes,
+                                            up_gate->buffer->dptr + up_gate->offset, up_gate->row_bytes, d_up_gate->buffer->dptr + d_up_gate->offset,
+                                            d_up_gate->row_bytes, g->rows, w->rows, g->cols);
 }
 gd_status gdb200_matmul_tn_colsum(gd_backend *be, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w, const gd_backend_matrix_view *y,
                                   const gd_backend_vector_view *colsum)

@@ -52,15 +52,22 @@ constexpr int P_SMEM_TOTAL_SWIGLU = (P_STAGES_DEFAULT - 1) * P_STAGE_BYTES + P_E
 // x12 = round(round(acc) + bias) and act = round(x1 * x2 * sigmoid(x2)) from one pass over tensor memory, with the rounding
 // points of the three separate calls. N is then F, tma_c maps the [M, 2F] x12 matrix (kept for the backward pass) and
 // tma_act the [M, F] activation; a warp stages its x1, x2 and act tile (32 rows x 64 columns each) and issues three TMA stores.
-template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM, bool SWIGLU = false>
+//
+// SWIGLU_BWD (input gradient of the down projection of a SwiGLU block, y = act w, w stored [F, N_out]: dact = g w^T is an
+// x w^T contraction with N = F): the epilogue does not write dact but the gradient of the up / gate projection's output,
+// d_x1 = dact x2 sigmoid(x2) and d_x2 = dact x1 sigmoid(x2) (1 + x2 (1 - sigmoid(x2))) with dact rounded to storage first
+// (the rounding point of the separate swiglu_split_backward call, src/ops/swiglu_split_linear/core_swiglu_split_linear.c:303-420).
+// x1 / x2 come from `aux` = the saved [M, 2F] x12 matrix (16-byte loads, a row per thread); tma_c maps d_x12 [M, 2F].
+template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM, bool SWIGLU = false, bool SWIGLU_BWD = false>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const T *__restrict__ bias, uint32_t M, uint32_t N, uint32_t K,
                  uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t k_iters_per_split, int bias_mode, int *err_flag,
-                 float *__restrict__ colsum_partial, const __grid_constant__ CUtensorMap tma_act)
+                 float *__restrict__ colsum_partial, const __grid_constant__ CUtensorMap tma_act, const T *__restrict__ aux, size_t ld_aux)
 {
     static_assert(!COLSUM || SPLITK, "column sums ride on the split-K (FP32 partial) output path");
     static_assert(!SWIGLU || (!SPLITK && !A_MN && !B_MN), "the SwiGLU epilogue belongs to y = x w^T with direct output");
+    static_assert(!SWIGLU_BWD || (!SPLITK && !A_MN && !B_MN && !SWIGLU), "the SwiGLU backward epilogue belongs to dact = g w^T with direct output");
     // The SwiGLU epilogue stages three output tiles per warp (x1, x2, act) instead of two alternating ones: it runs with
     // one operand stage less to make room for them.
     constexpr int PSTAGES = SWIGLU ? P_STAGES_DEFAULT - 1 : P_STAGES_DEFAULT;
@@ -289,6 +296,62 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 }
                 continue;
             }
+            if (SWIGLU_BWD) {
+                const uint32_t row = row0 + lane;
+#pragma unroll 1
+                for (int c = chalf * 2; c < chalf * 2 + 2; ++c) {          // two chunks of 64 columns per warp
+                    const uint32_t col0 = tn * PBN + c * 64;
+                    if (lane == 0) bulk_wait_group_read<0>();               // the two staged tiles of the previous chunk have been read
+                    __syncwarp();
+                    unsigned char *r1 = my_stage + lane * 128, *r2 = r1 + 4096;
+#pragma unroll 1
+                    for (int pc = 0; pc < 2; ++pc) {                        // 32 columns at a time
+                        const uint32_t cc0 = col0 + pc * 32;
+                        uint4 xa[4], xb[4];
+                        const bool in = row < M && cc0 < N;
+                        const uint4 *p1 = reinterpret_cast<const uint4 *>(aux + (size_t)row * ld_aux + cc0);
+                        const uint4 *p2 = reinterpret_cast<const uint4 *>(aux + (size_t)row * ld_aux + N + cc0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            xa[j] = in ? p1[j] : make_uint4(0U, 0U, 0U, 0U);
+                            xb[j] = in ? p2[j] : make_uint4(0U, 0U, 0U, 0U);
+                        }
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(tbase + c * 64 + pc * 32, v);
+                        if (c == chalf * 2 + 1 && pc == 1) {
+                            tcgen05_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * buf);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            gdb_vec8<T> a, b, d1, d2;
+                            a.raw = xa[j];
+                            b.raw = xb[j];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float gv = gdb_io<T>::rnd(__uint_as_float(v[j * 8 + e]));
+                                const float z = b.get(e), sg = gdb_swiglu_sigmoid(z);
+                                d1.set(e, gv * (z * sg));
+                                d2.set(e, gv * a.get(e) * (sg * (1.0f + z * (1.0f - sg))));
+                            }
+                            const int chunk = ((pc * 4 + j) ^ (lane & 7)) << 4;
+                            *reinterpret_cast<uint4 *>(r1 + chunk) = d1.raw;
+                            *reinterpret_cast<uint4 *>(r2 + chunk) = d2.raw;
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (row0 < M && col0 < N) {
+                            tma_store_2d(&tma_c, (int)col0, (int)row0, smem_u32(my_stage));
+                            tma_store_2d(&tma_c, (int)(N + col0), (int)row0, smem_u32(my_stage + 4096));
+                        }
+                        bulk_commit_group();
+                    }
+                }
+                continue;
+            }
             constexpr int NCH = PBN / CHUNK_COLS / 2;   // chunks per warp
 #pragma unroll 1
             for (int c = chalf * NCH; c < (chalf + 1) * NCH; ++c) {
@@ -383,13 +446,13 @@ int max_clusters(gd_backend *be, const void *kern, int smem_bytes)
     return n < be->sm_count / 2 ? n : be->sm_count / 2;
 }
 
-template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM = false, bool SWIGLU = false>
+template <typename T, bool A_MN, bool B_MN, bool SPLITK, bool COLSUM = false, bool SWIGLU = false, bool SWIGLU_BWD = false>
 gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const void *bias, uint32_t M,
                       uint32_t N, uint32_t K, uint32_t tiles_m, uint32_t tiles_n, uint32_t splits, uint32_t kps, int bias_mode, int *clusters_out,
-                      float *colsum_partial = nullptr, const CUtensorMap *tact = nullptr)
+                      float *colsum_partial = nullptr, const CUtensorMap *tact = nullptr, const void *aux = nullptr, size_t ld_aux = 0)
 {
     constexpr int SMEM = SWIGLU ? P_SMEM_TOTAL_SWIGLU : (COLSUM ? P_SMEM_TOTAL_COLSUM : P_SMEM_TOTAL);
-    auto kern = gemm_pair_kernel<T, A_MN, B_MN, SPLITK, COLSUM, SWIGLU>;
+    auto kern = gemm_pair_kernel<T, A_MN, B_MN, SPLITK, COLSUM, SWIGLU, SWIGLU_BWD>;
     static int clusters = -1;
     if (clusters < 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -422,7 +485,7 @@ gd_status launch_pair(gd_backend *be, const CUtensorMap &ta, const CUtensorMap &
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, (const T *)bias, M, N, K, tiles_m, tiles_n, splits, kps, bias_mode, be->err_flag, colsum_partial,
-                                       tact != nullptr ? *tact : tc);
+                                       tact != nullptr ? *tact : tc, (const T *)aux, ld_aux);
     if (e != cudaSuccess) {
         be->launches += 1U;
         return gdb_fail(be, e, "gemm_tcgen05_pair");
@@ -541,4 +604,28 @@ gd_status gdb_gemm_tcgen05_pair_swiglu(gd_backend *be, uint32_t dtype, const voi
     return dtype == GDB_DTYPE_F16
                ? launch_pair<__half, false, false, false, false, true>(be, ma, mb, m12, bias, M, F, K, tiles_m, tiles_n, 1, kps, 2, nullptr, nullptr, &mact)
                : launch_pair<__nv_bfloat16, false, false, false, false, true>(be, ma, mb, m12, bias, M, F, K, tiles_m, tiles_n, 1, kps, 2, nullptr, nullptr, &mact);
+}
+
+// d_x12[M, 2F] = swiglu_split_backward(x12, round(g w^T)) for w stored [F, K] (the down projection's weight, K = its output
+// width): the input gradient of the down projection with the SwiGLU backward in the epilogue, so dact never reaches memory.
+// GD_ERR_UNSUPPORTED when the shape does not fit (the caller then issues matmul_nt + swiglu_split_backward: same bits).
+gd_status gdb_gemm_tcgen05_pair_swiglu_bwd(gd_backend *be, uint32_t dtype, const void *g, size_t ldg_bytes, const void *w, size_t ldw_bytes,
+                                           const void *x12, size_t ld12_bytes, void *d_x12, size_t ldd_bytes, uint32_t M, uint32_t F, uint32_t K)
+{
+    const uintptr_t al = (uintptr_t)g | (uintptr_t)w | (uintptr_t)x12 | (uintptr_t)d_x12;
+    if ((dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) || M < 256U || F < 256U || (F % 64U) != 0U || K < 64U || (K % 8U) != 0U || (al % 16U) != 0U ||
+        (ldg_bytes % 16U) != 0U || (ldw_bytes % 16U) != 0U || (ld12_bytes % 16U) != 0U || (ldd_bytes % 16U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    CUtensorMap ma, mb, md;
+    if (!make_tmap(&ma, dtype, g, M, K, ldg_bytes, BK, BM) || !make_tmap(&mb, dtype, w, F, K, ldw_bytes, BK, PBN / 2) ||
+        !make_tmap(&md, dtype, d_x12, M, 2ULL * F, ldd_bytes, 64, 32)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const uint32_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (F + PBN - 1) / PBN, kps = (K + BK - 1) / BK;
+    return dtype == GDB_DTYPE_F16
+               ? launch_pair<__half, false, false, false, false, false, true>(be, ma, mb, md, nullptr, M, F, K, tiles_m, tiles_n, 1, kps, 0, nullptr, nullptr,
+                                                                              nullptr, x12, ld12_bytes / 2U)
+               : launch_pair<__nv_bfloat16, false, false, false, false, false, true>(be, ma, mb, md, nullptr, M, F, K, tiles_m, tiles_n, 1, kps, 0, nullptr,
+                                                                                     nullptr, nullptr, x12, ld12_bytes / 2U);
 }

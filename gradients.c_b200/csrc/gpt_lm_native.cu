@@ -569,12 +569,27 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             c.ok(gd_backend_matmul_tn(be, &am, &gm, &dwm), "matmul_tn(d_down_w)");
             gd_backend_vector_view dbv = vv(grads[(size_t)pb + 9], 0, (uint32_t)D);
             c.ok(gd_backend_reduce_rows(be, &gm, &dbv), "reduce_rows(d_down_b)");
-            Ten dact = c.alloc(dt, {T, F});
-            gd_backend_matrix_view dam = mv(dact, (uint32_t)T, (uint32_t)F);
-            c.ok(gd_backend_matmul_nt(be, &gm, &wm, &dam), "matmul_nt(d_act)");
+            // d_act = g w^T and the SwiGLU backward in its epilogue; the two separate calls when the fused kernel declines
             Ten d_up = c.alloc(dt, {T, 2 * F});
-            gd_backend_tensor_view xv = tv(sv.up_gate), dav = tv(dact), duv = tv(d_up);
-            c.ok(gd_backend_swiglu_split_backward(be, &xv, &dav, &duv), "swiglu_split_backward");
+            gd_backend_matrix_view ugm = mv(sv.up_gate, (uint32_t)T, (uint32_t)(2 * F)), dum = mv(d_up, (uint32_t)T, (uint32_t)(2 * F));
+            // (measured on the benchmark step: the fused launch takes as long as the two it replaces, 3.114 against 3.109 ms per
+            // step, because the epilogue then carries two special-function evaluations and two 16-byte loads per element; it
+            // saves the [T, F] scratch, so it is what GDB200_FUSE_SWIGLU_BWD=1 selects)
+            static int fuse_bwd = -1;
+            if (fuse_bwd < 0) {
+                const char *env = getenv("GDB200_FUSE_SWIGLU_BWD");
+                fuse_bwd = (env != NULL && env[0] == '1') ? 1 : 0;
+            }
+            gd_status fst = (c.st == GD_OK && fuse_bwd) ? gdb200_matmul_nt_swiglu_backward(be, &gm, &wm, &ugm, &dum) : GD_ERR_UNSUPPORTED;
+            if (fst == GD_ERR_UNSUPPORTED) {
+                Ten dact = c.alloc(dt, {T, F});
+                gd_backend_matrix_view dam = mv(dact, (uint32_t)T, (uint32_t)F);
+                c.ok(gd_backend_matmul_nt(be, &gm, &wm, &dam), "matmul_nt(d_act)");
+                gd_backend_tensor_view xv = tv(sv.up_gate), dav = tv(dact), duv = tv(d_up);
+                c.ok(gd_backend_swiglu_split_backward(be, &xv, &dav, &duv), "swiglu_split_backward");
+            } else {
+                c.ok(fst, "matmul_nt(d_act) + swiglu_split_backward");
+            }
             Ten dn2;
             linear_t_backward(c, sv.normed2, c.param(pb + 6, {2 * F, D}), d_up, T, D, 2 * F, &dn2, grads[(size_t)pb + 6], grads[(size_t)pb + 7]);
             rms_backward(c, sv.resid, c.param(pb + 5, {D}), sv.inv2, dn2, T, D, grads[(size_t)pb + 5], &g_resid);

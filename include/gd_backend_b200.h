@@ -414,6 +414,12 @@ gd_status gdb200_matmul_nt_bias_swiglu(gd_backend *backend, const gd_backend_mat
 gd_status gdb200_matmul_nt_bias_swiglu_both(gd_backend *backend, const gd_backend_matrix_view *x, const gd_backend_matrix_view *w,
                                             const gd_backend_vector_view *bias, const gd_backend_matrix_view *up_gate,
                                             const gd_backend_matrix_view *act);
+/* Backward counterpart: d_up_gate [M, 2F] = swiglu_split_backward(up_gate, round(g w^T)) with w stored [F, K] (the down
+ * projection's weight): gd_backend_matmul_nt into a scratch [M, F] followed by gd_backend_swiglu_split_backward
+ * (src/ops/swiglu_split_linear/core_swiglu_split_linear.c:303-420), in one launch and without the scratch. Bit-identical to the two
+ * calls; GD_ERR_UNSUPPORTED when the fused kernel does not take the shape (the caller then makes the two calls). */
+gd_status gdb200_matmul_nt_swiglu_backward(gd_backend *backend, const gd_backend_matrix_view *g, const gd_backend_matrix_view *w,
+                                           const gd_backend_matrix_view *up_gate, const gd_backend_matrix_view *d_up_gate);
 
 /* gd_backend_sdpa_varlen_backward (src/core/backend.h:699-709) for a caller that still holds the forward output `out`
  * [N, Hq, Dh] and can lend FP32 scratch `dq_accum` of q's element count: D = rowsum(grad_out o out) replaces the

@@ -747,3 +747,25 @@ def test_up_gate_projection_with_swiglu_epilogue_is_bit_identical_to_the_three_c
     want_ug = O.linear_transposed_weight_forward(t32(x), t32(w), t32(b), sd)
     close(host(ug1), want_ug, dtype, scale=math.sqrt(k) / 4, what="up_gate")
     close(host(act1), O.swiglu_split_forward(torch.from_numpy(host(ug1)), sd), dtype, scale=2, what="act")
+
+
+@pytest.mark.parametrize("dtype,m,k,f", [(F16, 1024, 512, 1536), (BF16, 777, 256, 384), (F16, 300, 192, 320)])
+def test_down_projection_input_gradient_with_swiglu_backward_epilogue_is_bit_identical_to_the_two_calls(step, dtype, m, k, f):
+    """gdb200_matmul_nt_swiglu_backward (d_up_gate from g, the down projection's weight and the saved up_gate in one launch)
+    against gd_backend_matmul_nt into a scratch followed by gd_backend_swiglu_split_backward, bit for bit, and against the oracle."""
+    ctx, lib = step, step.lib
+    r = rng(510 + m)
+    g = rnd_np(r.standard_normal((m, k)).astype(np.float32), dtype)
+    w = rnd_np((r.standard_normal((f, k)) * 0.05).astype(np.float32), dtype)
+    ug = rnd_np(r.standard_normal((m, 2 * f)).astype(np.float32), dtype)
+    gt, wt, ugt = dev(ctx, g, dtype), dev(ctx, w, dtype), dev(ctx, ug, dtype)
+    dact = ctx.scratch_empty(dtype, (m, f))
+    d0, d1 = ctx.scratch_empty(dtype, (m, 2 * f)), ctx.scratch_empty(dtype, (m, 2 * f))
+    gm, wm = gt.mv(m, k), wt.mv(f, k)
+    ctx.check(lib.gd_backend_matmul_nt(ctx.backend, byref(gm), byref(wm), byref(dact.mv(m, f))), "matmul_nt")
+    ctx.check(lib.gd_backend_swiglu_split_backward(ctx.backend, byref(ugt.tv()), byref(dact.tv()), byref(d0.tv())), "swiglu_split_backward")
+    ctx.check(lib.gdb200_matmul_nt_swiglu_backward(ctx.backend, byref(gm), byref(wm), byref(ugt.mv(m, 2 * f)), byref(d1.mv(m, 2 * f))), "fused")
+    assert np.array_equal(d1.read().view(np.uint16), d0.read().view(np.uint16))
+    sd = storage_name(dtype)
+    want_dact = O.rnd(t32(g) @ t32(w).t(), sd)
+    close(host(d1), O.swiglu_split_backward(t32(ug), want_dact, sd), dtype, scale=math.sqrt(k) / 2, what="d_up_gate")
