@@ -11,8 +11,9 @@
 //
 // With a data-parallel communicator attached (gdb200_dp_init) all parameter gradients are allocated as
 // one contiguous range and summed across ranks with ONE all-reduce after the backward pass (or, with
-// GDB200_DP_OVERLAP=1, one per block as soon as the block's backward has been enqueued); 1/world is
-// folded into the inverse loss scale used by the clip/AdamW kernels.
+// GDB200_DP_OVERLAP=1, one per block as soon as the block's backward has been enqueued). The loss is
+// normalised by the number of valid target rows of ALL ranks (counted and all-reduced at the start of
+// the step), so the summed gradients are those of the global batch without a division by the world size.
 #include "common.cuh"
 
 #include <math.h>

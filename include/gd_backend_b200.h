@@ -22,8 +22,9 @@
  *   - `offset` fields are byte offsets into `buffer`; matrix views carry `row_bytes`.
  *   - dtype codes are gd_dtype values (include/gradients/tensor.h:49-57).
  *   - all work is enqueued on one in-order CUDA stream; gd_backend_flush waits for it.
- *   - entries that are off the gpt_lm train/decode path return GD_ERR_UNSUPPORTED, as
- *     the reference's null backend does (src/backends/null/backend_null.c).
+ *   - all 109 entries of the vtable are implemented; a dtype or shape that an entry does
+ *     not take is answered with GD_ERR_UNSUPPORTED (the code the reference's null backend
+ *     gives, src/backends/null/backend_null.c), never with a silent fallback.
  */
 #ifndef GD_BACKEND_B200_H
 #define GD_BACKEND_B200_H
