@@ -11,6 +11,7 @@
 // cache capacity are dropped).
 // stats layout [N, Hq, 3] F32 = (row max of scaled scores, sum of exp, D).
 #include "common.cuh"
+#include "decode_parts.cuh"
 #include "attention.cuh"
 
 #include <stdlib.h>
@@ -19,28 +20,7 @@
 
 namespace {
 
-__device__ __forceinline__ bool mask_allowed(int i, int j, int causal, int window, int prefix)
-{
-    if (causal != 0) {
-        if (prefix > 0) {
-            if (i < prefix) {
-                if (j >= prefix) return false;
-            } else if (j > i) {
-                return false;
-            }
-        } else if (j > i) {
-            return false;
-        }
-    }
-    if (window > 0) {
-        if (prefix > 0) {
-            if (i >= prefix && j >= prefix && (i - j) >= window) return false;
-        } else if ((i - j) >= window) {
-            return false;
-        }
-    }
-    return true;
-}
+using gdb_dec::mask_allowed;
 
 // Find the segment that holds packed row `row` (cu[0] == 0, cu non-decreasing).
 __device__ __forceinline__ int find_segment(const int *cu, int batch, int row)
@@ -262,45 +242,13 @@ __global__ void varlen_dkv_kernel(const T *q, const T *k, const T *v, const T *g
 }
 
 // ------------------------------------------------------------------ decode
-struct decode_params {
-    int batch, tq, tmax, hq, hkv, dh;
-    int window, prefix;
-    int pos_mode;  // 0 scalar argument, 1 one-element tensor, 2 per-batch tensor
-    int cache_pos;
-    float scale;
-};
+using gdb_dec::decode_params;
+using gdb_dec::decode_allowed;
+using gdb_dec::decode_combine_query;
 
-__device__ __forceinline__ bool decode_allowed(int qpos, int j, int window, int prefix)
-{
-    return mask_allowed(qpos, j, 1, window, prefix);
-}
-
-// Split-K decode: grid (ceil(queries / warps), splits). Each warp owns one (b, t, hq) query and
-// the keys [split*chunk, split*chunk+chunk) of its live range. A key is handled by DH/16 adjacent
-// lanes (16 head dims = two 16-byte loads each for K and V), so a warp has 32/(DH/16) keys in
-// flight; partial (m, l, acc) per split go to the workspace and a combine kernel merges them.
-// Merge of the per-split partials of query w: out = sum_s acc_s e^(m_s - m) / sum_s l_s e^(m_s - m).
-template <typename T>
-__device__ __forceinline__ void decode_combine_query(const float *part_ml, const float *part_acc, T *out, long long w, int dh, int splits, int lane)
-{
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, __ldcg(&part_ml[((size_t)w * splits + s) * 2U]));
-    float l = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float pm = __ldcg(&part_ml[((size_t)w * splits + s) * 2U]);
-        l += pm == -INFINITY ? 0.0f : __ldcg(&part_ml[((size_t)w * splits + s) * 2U + 1U]) * __expf(pm - m);
-    }
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    for (int c = lane; c < dh; c += 32) {
-        float a = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float pm = __ldcg(&part_ml[((size_t)w * splits + s) * 2U]);
-            if (pm != -INFINITY) a += __ldcg(&part_acc[((size_t)w * splits + s) * dh + c]) * __expf(pm - m);
-        }
-        gdb_io<T>::st(out, (size_t)w * dh + c, a * inv);
-    }
-}
-
+// Split-K decode: grid (ceil(queries / warps), splits). Each warp owns one (b, t, hq) query and the keys
+// [split*chunk, split*chunk+chunk) of its live range (gdb_dec::decode_split_item); partial (m, l, acc) per split
+// go to the workspace and are merged by decode_combine_query.
 // `tickets` != NULL: the block that arrives last for its group of queries (over the splits) merges the
 // partials and writes `out`, so no combine launch follows.
 template <typename T, int DH>
@@ -308,88 +256,13 @@ __global__ void decode_split_kernel(const T *q, const T *kc, const T *vc, const 
                                     float *part_acc, decode_params p, int splits, T *out, unsigned *tickets)
 {
     gdb_pdl_sync();
-    constexpr int LPK = DH / 16, KPW = 32 / LPK;
-    const int lane = threadIdx.x & 31, sub = lane % LPK, kg = lane / LPK;
+    const int lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long total = (long long)p.batch * p.tq * p.hq;
     const bool active = w < total;
     if (active) {
-    const int split = blockIdx.y;
-    const int h = (int)(w % p.hq);
-    const int t = (int)((w / p.hq) % p.tq);
-    const int b = (int)(w / ((long long)p.hq * p.tq));
-    const int hk = h / (p.hq / p.hkv);
-    const int pos = p.pos_mode == 0 ? p.cache_pos : pos_buf[p.pos_mode == 2 ? b : 0];
-    float m = -INFINITY, l = 0.0f;
-    float acc[16], qr[16];
-#pragma unroll
-    for (int c = 0; c < 16; ++c) acc[c] = 0.0f;
-    if (pos >= 0) {
-        int live = pos + p.tq;
-        if (live > p.tmax) live = p.tmax;
-        const int qpos = pos + t;
-        int j_hi = qpos + 1;
-        if (p.prefix > 0 && qpos < p.prefix) j_hi = p.prefix;
-        if (j_hi > live) j_hi = live;
-        int j_lo = 0;
-        if (p.window > 0 && p.prefix <= 0 && qpos - p.window + 1 > 0) j_lo = qpos - p.window + 1;
-        const int span = j_hi > j_lo ? j_hi - j_lo : 0;
-        const int chunk = (span + splits - 1) / splits;
-        const int s_lo = j_lo + split * chunk;
-        int s_hi = s_lo + chunk;
-        if (s_hi > j_hi) s_hi = j_hi;
-        const size_t qb = (((size_t)b * p.tq + t) * p.hq + h) * DH + sub * 16;
-#pragma unroll
-        for (int c = 0; c < 16; ++c) qr[c] = gdb_io<T>::ld(q, qb + c) * p.scale;
-        for (int jb = s_lo; jb < s_hi; jb += KPW) {
-            const int j = jb + kg;
-            const bool valid = j < s_hi && decode_allowed(qpos, j, p.window, p.prefix);
-            const size_t kb = (((size_t)b * p.tmax + (valid ? j : 0)) * p.hkv + hk) * DH + sub * 16;
-            float s = 0.0f;
-            gdb_vec8<T> k0, k1, v0, v1;
-            if (valid) {
-                k0.raw = *reinterpret_cast<const uint4 *>(kc + kb);
-                k1.raw = *reinterpret_cast<const uint4 *>(kc + kb + 8);
-                v0.raw = *reinterpret_cast<const uint4 *>(vc + kb);
-                v1.raw = *reinterpret_cast<const uint4 *>(vc + kb + 8);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) s += qr[e] * k0.get(e) + qr[8 + e] * k1.get(e);
-            }
-#pragma unroll
-            for (int o = 1; o < LPK; o <<= 1) s += __shfl_xor_sync(0xffffffffU, s, o);
-            if (valid) {
-                const float mnew = fmaxf(s, m);
-                const float corr = __expf(m - mnew), e = __expf(s - mnew);
-                l = l * corr + e;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    acc[c] = acc[c] * corr + e * v0.get(c);
-                    acc[8 + c] = acc[8 + c] * corr + e * v1.get(c);
-                }
-                m = mnew;
-            }
-        }
-    }
-    // merge the key groups of the warp (lanes with equal `sub`)
-    float wm = m;
-#pragma unroll
-    for (int o = LPK; o < 32; o <<= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffU, wm, o));
-    const float f = (m == -INFINITY) ? 0.0f : __expf(m - wm);
-    l *= f;
-#pragma unroll
-    for (int o = LPK; o < 32; o <<= 1) l += __shfl_xor_sync(0xffffffffU, l, o);
-    float *pa = part_acc + ((size_t)w * splits + split) * DH + sub * 16;
-#pragma unroll
-    for (int c = 0; c < 16; ++c) {
-        float a = acc[c] * f;
-#pragma unroll
-        for (int o = LPK; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffU, a, o);
-        if (kg == 0) pa[c] = a;
-    }
-    if (lane == 0) {
-        part_ml[((size_t)w * splits + split) * 2U] = wm;
-        part_ml[((size_t)w * splits + split) * 2U + 1U] = l;
-    }
+        const size_t item = (size_t)w * splits + blockIdx.y;
+        gdb_dec::decode_split_item<T, DH, false>(q, kc, vc, pos_buf, part_ml + item * 2U, part_acc + item * DH, p, splits, w, (int)blockIdx.y, lane);
     }   // active
     if (tickets == nullptr) {
         return;
@@ -403,7 +276,7 @@ __global__ void decode_split_kernel(const T *q, const T *kc, const T *vc, const 
     __syncthreads();
     if (last) {
         __threadfence();
-        if (active) decode_combine_query<T>(part_ml, part_acc, out, w, DH, splits, lane);
+        if (active) decode_combine_query<T, true>(part_ml + (size_t)w * splits * 2U, part_acc + (size_t)w * splits * DH, out + (size_t)w * DH, DH, splits, lane);
         if (threadIdx.x == 0) tickets[blockIdx.x] = 0U;
     }
 }
@@ -417,7 +290,7 @@ __global__ void decode_combine_kernel(const float *part_ml, const float *part_ac
     if (w >= total) {
         return;
     }
-    decode_combine_query<T>(part_ml, part_acc, out, w, dh, splits, lane);
+    decode_combine_query<T, true>(part_ml + (size_t)w * splits * 2U, part_acc + (size_t)w * splits * dh, out + (size_t)w * dh, dh, splits, lane);
 }
 
 // General head_dim decode: one warp per query, lanes split head_dim.
@@ -652,11 +525,7 @@ gd_status decode_common(gd_backend *be, const gd_backend_tensor_view *q, const g
             const char *env = getenv("GDB200_DECODE_WARPS_PER_SM");
             wps = env != NULL && atoi(env) > 0 ? atoi(env) : 32;
         }
-        int splits = (int)(((long long)be->sm_count * wps + total - 1) / total);
-        const int max_splits = (p.tmax + 63) / 64;
-        if (splits > max_splits) splits = max_splits;
-        if (splits < 1) splits = 1;
-        if (splits > 16) splits = 16;
+        const int splits = gdb_dec::decode_choose_splits(be->sm_count, p.batch, p.tq, p.hq, p.dh, p.tmax, wps);
         const size_t need = (size_t)total * splits * (2U + (size_t)p.dh) * sizeof(float);
         if (need <= be->ws_bytes) {
             float *ml = (float *)be->ws;

@@ -1,0 +1,582 @@
+// One KV-cache decode step (gpt_block_decode_cached, examples/gpt_lm/gpt_lm_shared.c:961-1115, the logits head
+// :1204-1246 and greedy sampling :1388-1398) as ONE persistent kernel: one CTA per SM, launched cooperatively, walks
+// through the phases of a step and of the following steps, separated by grid-wide barriers instead of kernel launches.
+//
+// A decode step of the benchmark model moves 22.5 MB of weights and the live K / V (174 MB on average): 27 us at the
+// measured copy bandwidth. As 28 dependent launches it takes 183 us, nearly all of it launch and drain latency. Here a
+// step is 5 phases per layer + 2:
+//   A  [embedding | residual add] + RMSNorm as the prologue of the QKV projection, RoPE and the K / V append as its
+//      epilogue (a CTA's 16 output columns are 8 rotation pairs of one head, or 16 value columns)
+//   B  attention over the cache: the 16 warps of a CTA are heads x key ranges of one sequence, each streaming its keys
+//      through a private shared-memory ring (cp.async, three tiles of 16 keys in flight), merged in shared memory
+//   C  attention output projection
+//   D  residual add + RMSNorm as the prologue of the up / gate projection, SwiGLU as its epilogue
+//   E  down projection
+//   F  residual add + final RMSNorm as the prologue of the logits projection
+//   G  greedy sampling (soft cap, first maximum), token / position feedback for the next step
+// Every phase runs the device functions of decode_parts.cuh that the stand-alone kernels run, on the same partition
+// of the work (16-column units with K split over eight warps, the same key splits), so a step gives the same bits as
+// the 28 launches and the generated ids are identical.
+//
+// Grid barrier: a monotonically increasing counter in global memory; thread 0 of each CTA adds 1 (release) and polls
+// (acquire) until the counter reaches the phase's target. The poll is bounded: when it runs out, the CTA stores code 398
+// in the backend's error word, raises the abort bit of the counter word that every other CTA's poll also sees, and the
+// kernel returns.
+// Buffers written inside the kernel are read with plain or L2 loads after a barrier, never through the read-only path.
+#include "common.cuh"
+#include "decode_parts.cuh"
+
+#include <stdlib.h>
+
+namespace {
+
+using namespace gdb_dec;
+
+constexpr int MG_THREADS = 512, MG_WARPS = MG_THREADS / 32;
+constexpr unsigned MG_SPIN_LIMIT = 1U << 22;   // polls of the barrier word (about a microsecond each) before giving up
+constexpr int MG_ERR_BARRIER = 398;
+constexpr int MG_OT_LD = SK_COLS + 1;
+constexpr uint32_t MG_RING_BYTES = 3U * 2U * 4U * 512U;   // per warp: three tiles of two key groups, K and V halves, 16 bytes per lane
+
+struct mg_layout {
+    uint32_t stage_bytes, red_off, ot_off, total;
+};
+__host__ __device__ inline mg_layout mg_layout_for(uint32_t ch_max)
+{
+    mg_layout l;
+    l.stage_bytes = SK_ROWS * (ch_max + 8U) * 2U + ch_max * 48U;   // A tile [64][ch + 8] + the larger of the two weight tiles ([ch][24])
+    l.red_off = 2U * l.stage_bytes;
+    l.ot_off = l.red_off + (uint32_t)SK_RED_BYTES;
+    l.total = l.ot_off + (uint32_t)(SK_ROWS * MG_OT_LD * sizeof(float));
+    const uint32_t attn = MG_WARPS * MG_RING_BYTES + MG_WARPS * (2U + 64U) * (uint32_t)sizeof(float);   // the attention phase's rings and partials alias the stages
+    if (l.total < attn) l.total = attn;
+    return l;
+}
+
+struct mg_ctx {
+    unsigned char *sm;
+    mg_layout lay;
+    int tid, warp, lane;
+    unsigned target;   // barrier count this CTA waits for next
+    int *ok_flag;      // shared word: outcome of the last barrier
+    unsigned long long *timeline;
+};
+
+// sync[0]: bits 0..30 count arrivals (monotonically, never reset inside a launch), bit 31 is the abort flag; one
+// acquire load per poll sees both.
+__device__ __forceinline__ bool mg_barrier(mg_ctx &c, unsigned *sync, int *err_flag)
+{
+    __syncthreads();
+    c.target += gridDim.x;
+    if (c.tid == 0) {
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&sync[0]) : "memory");
+        int ok = 1;
+        unsigned spins = 0;
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(&sync[0]) : "memory");
+            if ((v & 0x80000000U) != 0U || ++spins > MG_SPIN_LIMIT) {
+                ok = 0;
+                break;
+            }
+            if (v >= c.target) break;
+        }
+        if (!ok) {
+            atomicOr(&sync[0], 0x80000000U);
+            atomicCAS(err_flag, 0, MG_ERR_BARRIER);
+        }
+        *c.ok_flag = ok;
+    }
+    __syncthreads();
+    if (c.timeline != nullptr && blockIdx.x == 0 && c.tid == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        *c.timeline++ = t;
+    }
+    return *c.ok_flag != 0;
+}
+
+// ---- operand staging ----
+template <typename T>
+__device__ __forceinline__ void mg_load_a(T *As, uint32_t LDA, const T *A, size_t lda, uint32_t CH, size_t k0, uint32_t M, int tid)
+{
+    const uint32_t segs = CH / 8U;
+    for (uint32_t i = tid; i < SK_ROWS * segs; i += MG_THREADS) {
+        const uint32_t r = i / segs, sgm = i % segs;
+        sk_cp16(As + r * LDA + sgm * 8U, A + (size_t)(r < M ? r : 0U) * lda + k0 + sgm * 8U, r < M);
+    }
+}
+// B_KMAJOR: the unit's 16 weight rows are rows row_lo .. row_lo + 7 and row_hi .. row_hi + 7 of B [N, K]; otherwise the
+// unit's 16 columns start at row_lo of B [K, N].
+template <typename T, bool B_KMAJOR>
+__device__ __forceinline__ void mg_load_w(T *Ws, const T *B, size_t ldb, uint32_t CH, size_t k0, uint32_t row_lo, uint32_t row_hi, int tid)
+{
+    if (B_KMAJOR) {
+        const uint32_t segs = CH / 8U, LDW = CH + 8U;
+        for (uint32_t i = tid; i < SK_COLS * segs; i += MG_THREADS) {
+            const uint32_t r = i / segs, sgm = i % segs;
+            const uint32_t wrow = r < 8U ? row_lo + r : row_hi + (r - 8U);
+            sk_cp16(Ws + r * LDW + sgm * 8U, B + (size_t)wrow * ldb + k0 + sgm * 8U, true);
+        }
+    } else {
+        for (uint32_t i = tid; i < CH * 2U; i += MG_THREADS) {
+            const uint32_t k = i >> 1, sgm = i & 1U;
+            sk_cp16(Ws + k * 24U + sgm * 8U, B + (k0 + k) * ldb + row_lo + sgm * 8U, true);
+        }
+    }
+}
+__device__ __forceinline__ void mg_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void mg_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void mg_wait_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+template <typename T> struct mg_nan_pair;
+template <> struct mg_nan_pair<__half> { static constexpr unsigned word = 0x7e007e00U; };
+template <> struct mg_nan_pair<__nv_bfloat16> { static constexpr unsigned word = 0x7fc07fc0U; };
+
+// ---- [embedding | residual add] + RMSNorm into the resident A tile ----
+// MODE 0: x = table[ids] (an id outside the table gives a NaN row, as the embedding kernel does); MODE 1: x = round(xa + ya).
+// Row r of the tile = round(x * w * rsqrt(mean(x^2) + eps)); `sum_out` (one CTA of the phase passes it) receives x.
+// mg_stage_rows puts every row of xa (and ya, into Ys) in flight at once with cp.async; after the wait, mg_norm_rows
+// normalises in place, in the per-lane order of rms_fwd_kernel / add_rms_fwd_kernel (lane takes the 8-element vectors
+// lane, lane + 32, ...), one warp per row.
+template <typename T, int MODE>
+__device__ __forceinline__ void mg_stage_rows(T *As, T *Ys, uint32_t LDA, const T *xa, const T *ya, const int32_t *ids, uint32_t vocab,
+                                              int B, int D, int tid)
+{
+    const uint32_t vecs = (uint32_t)D / 8U;
+    for (uint32_t i = tid; i < SK_ROWS * vecs; i += MG_THREADS) {
+        const uint32_t r = i / vecs, v = i % vecs;
+        T *dst = As + (size_t)r * LDA + v * 8U;
+        if (MODE == 0) {
+            const int id = (int)r < B ? ids[r] : 0;
+            if ((int)r < B && (id < 0 || (uint32_t)id >= vocab)) {
+                const unsigned nw = mg_nan_pair<T>::word;
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(nw, nw, nw, nw);
+            } else {
+                sk_cp16(dst, xa + (size_t)((int)r < B ? id : 0) * D + v * 8U, (int)r < B);
+            }
+        } else {
+            const size_t src = (size_t)((int)r < B ? r : 0U) * D + v * 8U;
+            sk_cp16(dst, xa + src, (int)r < B);
+            sk_cp16(Ys + (size_t)r * LDA + v * 8U, ya + src, (int)r < B);
+        }
+    }
+}
+template <typename T, int MODE>
+__device__ __forceinline__ void mg_norm_rows(T *As, const T *Ys, uint32_t LDA, const T *w, T *sum_out, int B, int D, float eps, int warp, int lane)
+{
+    const uint32_t vecs = (uint32_t)D / 8U;   // at most 64 (D <= 512): two vectors per lane
+    gdb_vec8<T> wv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint32_t v = (uint32_t)lane + 32U * (uint32_t)i;
+        wv[i].raw = v < vecs ? __ldg(reinterpret_cast<const uint4 *>(w) + v) : make_uint4(0U, 0U, 0U, 0U);
+    }
+    for (int r = warp; r < B; r += MG_WARPS) {
+        T *arow = As + (size_t)r * LDA;
+        float ss = 0.0f;
+        for (uint32_t v = lane; v < vecs; v += 32) {
+            gdb_vec8<T> a;
+            a.raw = *reinterpret_cast<const uint4 *>(arow + v * 8U);
+            if (MODE == 0) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float f = a.get(e);
+                    ss += f * f;
+                }
+            } else {
+                gdb_vec8<T> b;
+                b.raw = *reinterpret_cast<const uint4 *>(Ys + (size_t)r * LDA + v * 8U);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    a.set(e, a.get(e) + b.get(e));
+                    const float f = a.get(e);
+                    ss += f * f;
+                }
+                *reinterpret_cast<uint4 *>(arow + v * 8U) = a.raw;
+            }
+            if (sum_out != nullptr) reinterpret_cast<uint4 *>(sum_out + (size_t)r * D)[v] = a.raw;
+        }
+        ss = gdb_warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)(size_t)D + eps);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t v = (uint32_t)lane + 32U * (uint32_t)i;
+            if (v < vecs) {
+                gdb_vec8<T> a;
+                a.raw = *reinterpret_cast<const uint4 *>(arow + v * 8U);   // written by this lane above
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    a.set(e, a.get(e) * wv[i].get(e) * inv);
+                }
+                *reinterpret_cast<uint4 *>(arow + v * 8U) = a.raw;
+            }
+        }
+    }
+}
+
+enum { EPI_PLAIN = 0, EPI_ROPE = 1, EPI_SWIGLU = 2 };
+enum { PRO_GLOBAL = 0, PRO_EMB = 1, PRO_ADD = 2 };
+
+template <typename T> struct mg_gemm {
+    // operands
+    const T *A;            // PRO_GLOBAL: activations [B, K]
+    const T *W;            // weight: K-major [N, K] or [K, N]
+    const T *bias;
+    T *C;                  // PLAIN / SWIGLU destination [B, N]
+    uint32_t K, N, CH;
+    int bias_mode;
+    // prologue (PRO_EMB / PRO_ADD)
+    const T *xa, *ya, *norm_w;
+    T *sum_out;
+    const int32_t *ids;
+    uint32_t vocab;
+    // rope epilogue
+    T *q, *kc, *vc;
+    const int32_t *positions;
+};
+
+// One phase = one contraction [B <= 64, K] x [K, N] spread over the CTAs in units of 16 output columns.
+template <typename T, bool B_KMAJOR, int EPI, int PRO>
+__device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a, const mg_gemm<T> &g)
+{
+    uint32_t nunits;
+    if (EPI == EPI_ROPE) {
+        nunits = 2U * (uint32_t)a.H * 4U + (uint32_t)a.D / 16U;   // q and k: 8 rotation pairs of one head each; v: 16 columns
+    } else if (EPI == EPI_SWIGLU) {
+        nunits = g.N / 8U;                                         // 8 up + 8 gate columns
+    } else {
+        nunits = g.N / 16U;
+    }
+    if (blockIdx.x >= nunits) return;
+    const uint32_t CH = g.CH, LDA = CH + 8U, LDW = B_KMAJOR ? CH + 8U : 24U, a_bytes = SK_ROWS * LDA * 2U;
+    const uint32_t n_chunks = g.K / CH, kw = CH / SK_WARPS;
+    const uint32_t M = (uint32_t)a.B;
+    sk_red_t red = reinterpret_cast<sk_red_t>(c.sm + c.lay.red_off);
+    float(*ot)[MG_OT_LD] = reinterpret_cast<float(*)[MG_OT_LD]>(c.sm + c.lay.ot_off);
+    auto stage_a = [&](uint32_t st) { return reinterpret_cast<T *>(c.sm + st * c.lay.stage_bytes); };
+    auto stage_w = [&](uint32_t st) { return reinterpret_cast<T *>(c.sm + st * c.lay.stage_bytes + a_bytes); };
+    auto unit_rows = [&](uint32_t unit, uint32_t *lo, uint32_t *hi) {
+        if (EPI == EPI_ROPE) {
+            const uint32_t nrope = 2U * (uint32_t)a.H * 4U;
+            if (unit < nrope) {
+                const uint32_t region = unit / ((uint32_t)a.H * 4U), hg = unit % ((uint32_t)a.H * 4U);
+                *lo = region * (uint32_t)a.D + (hg / 4U) * 64U + (hg % 4U) * 8U;
+                *hi = *lo + 32U;
+            } else {
+                *lo = 2U * (uint32_t)a.D + (unit - nrope) * 16U;
+                *hi = *lo + 8U;
+            }
+        } else if (EPI == EPI_SWIGLU) {
+            *lo = unit * 8U;
+            *hi = g.N + unit * 8U;
+        } else {
+            *lo = unit * 16U;
+            *hi = *lo + 8U;
+        }
+    };
+    bool first = true;
+    for (uint32_t unit = blockIdx.x; unit < nunits; unit += gridDim.x) {
+        uint32_t lo, hi;
+        unit_rows(unit, &lo, &hi);
+        float acc[4][2][4];
+        sk_zero(acc);
+        if (PRO != PRO_GLOBAL) {
+            // resident A (single chunk): weights stream in while the prologue runs
+            mg_load_w<T, B_KMAJOR>(stage_w(0), g.W, B_KMAJOR ? (size_t)g.K : (size_t)g.N, CH, 0, lo, hi, c.tid);
+            mg_commit();
+            if (first) {
+                if (PRO == PRO_EMB) {
+                    mg_stage_rows<T, 0>(stage_a(0), stage_a(1), LDA, g.xa, nullptr, g.ids, g.vocab, a.B, a.D, c.tid);
+                } else {
+                    mg_stage_rows<T, 1>(stage_a(0), stage_a(1), LDA, g.xa, g.ya, nullptr, 0U, a.B, a.D, c.tid);
+                }
+                mg_commit();
+            }
+            mg_wait_all();
+            __syncthreads();
+            if (first) {
+                T *sum_out = blockIdx.x == 0U ? g.sum_out : nullptr;
+                if (PRO == PRO_EMB) {
+                    mg_norm_rows<T, 0>(stage_a(0), stage_a(1), LDA, g.norm_w, sum_out, a.B, a.D, a.eps, c.warp, c.lane);
+                } else {
+                    mg_norm_rows<T, 1>(stage_a(0), stage_a(1), LDA, g.norm_w, sum_out, a.B, a.D, a.eps, c.warp, c.lane);
+                }
+                first = false;
+                __syncthreads();
+            }
+            if (c.warp < SK_WARPS) sk_mma_chunk<T, B_KMAJOR>(acc, stage_a(0), stage_w(0), LDA, LDW, c.warp * kw, (c.warp + 1U) * kw, c.lane);
+        } else {
+            const size_t ldb = B_KMAJOR ? (size_t)g.K : (size_t)g.N;
+            auto load_chunk = [&](uint32_t ci, uint32_t st) {
+                mg_load_a<T>(stage_a(st), LDA, g.A, (size_t)g.K, CH, (size_t)ci * CH, M, c.tid);
+                mg_load_w<T, B_KMAJOR>(stage_w(st), g.W, ldb, CH, (size_t)ci * CH, lo, hi, c.tid);
+                mg_commit();
+            };
+            load_chunk(0, 0);
+            if (n_chunks > 1U) load_chunk(1, 1);
+            for (uint32_t ci = 0; ci < n_chunks; ++ci) {
+                const uint32_t st = ci & 1U;
+                if (ci + 1U < n_chunks) {
+                    mg_wait_one();
+                } else {
+                    mg_wait_all();
+                }
+                __syncthreads();
+                if (c.warp < SK_WARPS) sk_mma_chunk<T, B_KMAJOR>(acc, stage_a(st), stage_w(st), LDA, LDW, c.warp * kw, (c.warp + 1U) * kw, c.lane);
+                __syncthreads();
+                if (ci + 2U < n_chunks) load_chunk(ci + 2U, st);
+            }
+        }
+        if (c.warp < SK_WARPS) sk_store_partials(red, acc, c.warp, c.lane);
+        __syncthreads();
+        if (EPI == EPI_SWIGLU) {
+            for (int o = c.tid; o < SK_ROWS * (SK_COLS / 2); o += MG_THREADS) {
+                const int r = o / (SK_COLS / 2), cc = o % (SK_COLS / 2);
+                if ((uint32_t)r >= M) continue;
+                const float up = sk_sum(red, r, cc), gate = sk_sum(red, r, cc + 8);
+                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, sk_swiglu<T>(up, gate, g.bias, g.bias_mode, lo + cc, hi + cc));
+            }
+        } else if (EPI == EPI_PLAIN) {
+            for (int o = c.tid; o < SK_ROWS * SK_COLS; o += MG_THREADS) {
+                const int r = o / SK_COLS, cc = o % SK_COLS;
+                if ((uint32_t)r >= M) continue;
+                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, sk_bias<T>(sk_sum(red, r, cc), g.bias, g.bias_mode, lo + cc));
+            }
+        } else {
+            // the rounded linear output of the unit, then the rotation of qkv_split_rope and the append of kv_cache_append
+            for (int o = c.tid; o < SK_ROWS * SK_COLS; o += MG_THREADS) {
+                const int r = o / SK_COLS, cc = o % SK_COLS;
+                const uint32_t col = cc < 8 ? lo + cc : hi + (cc - 8);
+                ot[r][cc] = (uint32_t)r < M ? gdb_io<T>::rnd(sk_bias<T>(sk_sum(red, r, cc), g.bias, g.bias_mode, col)) : 0.0f;
+            }
+            __syncthreads();
+            const uint32_t nrope = 2U * (uint32_t)a.H * 4U, area = (uint32_t)a.D;
+            if (unit < nrope) {
+                const uint32_t region = unit / ((uint32_t)a.H * 4U), hg = unit % ((uint32_t)a.H * 4U);
+                const uint32_t hcol = (hg / 4U) * 64U + (hg % 4U) * 8U, grp = hg % 4U;
+                for (int o = c.tid; o < SK_ROWS * 8; o += MG_THREADS) {
+                    const int r = o / 8, e = o % 8;
+                    if ((uint32_t)r >= M) continue;
+                    const int pos = g.positions[r];
+                    float cs, sn;
+                    rope_cos_sin(a.rope, a.rope_table, grp * 8U + (unsigned)e, pos, &cs, &sn);
+                    const float x0 = ot[r][e], x1 = ot[r][8 + e];
+                    const float y0 = rope_lo(x0, x1, cs, sn), y1 = rope_hi(x0, x1, cs, sn);
+                    if (region == 0U) {
+                        gdb_io<T>::st(g.q, (size_t)r * area + hcol + e, y0);
+                        gdb_io<T>::st(g.q, (size_t)r * area + hcol + 32U + e, y1);
+                    } else if (pos >= 0 && pos < a.CAP) {
+                        const size_t kv = ((size_t)r * a.CAP + (size_t)pos) * area + hcol + e;
+                        gdb_io<T>::st(g.kc, kv, y0);
+                        gdb_io<T>::st(g.kc, kv + 32U, y1);
+                    }
+                }
+            } else {
+                for (int o = c.tid; o < SK_ROWS * SK_COLS; o += MG_THREADS) {
+                    const int r = o / SK_COLS, cc = o % SK_COLS;
+                    if ((uint32_t)r >= M) continue;
+                    const int pos = g.positions[r];
+                    if (pos < 0 || pos >= a.CAP) continue;
+                    gdb_io<T>::st(g.vc, ((size_t)r * a.CAP + (size_t)pos) * area + (lo - 2U * area) + cc, ot[r][cc]);
+                }
+            }
+        }
+        __syncthreads();   // the weight stage, the reduction buffer and the output tile are reused by the CTA's next unit
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid_constant__ gdb_mega_args a, const mg_layout lay)
+{
+    extern __shared__ __align__(16) unsigned char mg_sm[];
+    __shared__ int ok_flag;
+    __shared__ float am_sv[32];
+    __shared__ uint32_t am_si[32];
+    mg_ctx c;
+    c.sm = mg_sm;
+    c.lay = lay;
+    c.tid = threadIdx.x;
+    c.warp = threadIdx.x >> 5;
+    c.lane = threadIdx.x & 31;
+    c.target = 0U;
+    c.ok_flag = &ok_flag;
+    c.timeline = a.timeline;
+    const uint32_t D = (uint32_t)a.D, F = (uint32_t)a.F, V = (uint32_t)a.V;
+    const uint32_t ch_f = (F % 512U) == 0U ? 512U : ((F % 256U) == 0U ? 256U : 128U);
+    const int t0 = *a.step_counter;   // advanced once, after the last step
+    decode_params dp;
+    dp.batch = a.B;
+    dp.tq = 1;
+    dp.tmax = a.CAP;
+    dp.hq = a.H;
+    dp.hkv = a.H;
+    dp.dh = 64;
+    dp.window = a.window;
+    dp.prefix = 0;
+    dp.pos_mode = 2;
+    dp.cache_pos = 0;
+    dp.scale = a.scale;
+    for (int step = 0; step < a.n_steps; ++step) {
+        for (int layer = 0; layer < a.L; ++layer) {
+            const void *const *lw = a.lw[layer];
+            T *kc = (T *)a.kc[layer], *vc = (T *)a.vc[layer];
+            {   // A: norm + QKV + RoPE + append
+                mg_gemm<T> g = {};
+                g.W = (const T *)lw[1];
+                g.bias = (const T *)lw[2];
+                g.K = D;
+                g.N = 3U * D;
+                g.CH = D;
+                g.bias_mode = 2;
+                g.norm_w = (const T *)lw[0];
+                g.sum_out = (T *)a.xbuf;
+                g.q = (T *)a.q;
+                g.kc = kc;
+                g.vc = vc;
+                g.positions = a.positions;
+                if (layer == 0) {
+                    g.xa = (const T *)a.emb;
+                    g.ids = a.tokens;
+                    g.vocab = V;
+                    mg_gemm_phase<T, true, EPI_ROPE, PRO_EMB>(c, a, g);
+                } else {
+                    g.xa = (const T *)a.resid;
+                    g.ya = (const T *)a.mlp;
+                    mg_gemm_phase<T, true, EPI_ROPE, PRO_ADD>(c, a, g);
+                }
+            }
+            if (!mg_barrier(c, a.sync, a.err_flag)) return;
+            {   // B: attention; a CTA takes `hpc` heads x `splits` key ranges of one sequence and merges the ranges in shared memory
+                const int hpc = 16 / a.splits, groups = a.H / hpc, units = a.B * groups;
+                float *sm_ml = reinterpret_cast<float *>(c.sm + MG_WARPS * MG_RING_BYTES), *sm_acc = sm_ml + MG_WARPS * 2;
+                for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+                    const int b = unit / groups, hl = c.warp % hpc, split = c.warp / hpc;
+                    const long long w = (long long)b * a.H + (unit % groups) * hpc + hl;
+                    const int item = hl * a.splits + split;   // the query's splits side by side
+                    if (split < a.splits) {
+                        decode_split_item<T, 64, true>((const T *)a.q, kc, vc, a.positions, sm_ml + item * 2, sm_acc + item * 64, dp, a.splits, w, split,
+                                                      c.lane, c.sm + (size_t)c.warp * MG_RING_BYTES);
+                    }
+                    __syncthreads();
+                    if (c.warp < hpc) {
+                        decode_combine_query<T, false>(sm_ml + c.warp * a.splits * 2, sm_acc + c.warp * a.splits * 64,
+                                                       (T *)a.attn + (size_t)((long long)b * a.H + (unit % groups) * hpc + c.warp) * 64, 64, a.splits, c.lane);
+                    }
+                    __syncthreads();
+                }
+            }
+            if (!mg_barrier(c, a.sync, a.err_flag)) return;
+            {   // C: attention output projection
+                mg_gemm<T> g = {};
+                g.A = (const T *)a.attn;
+                g.W = (const T *)lw[3];
+                g.bias = (const T *)lw[4];
+                g.C = (T *)a.proj;
+                g.K = D;
+                g.N = D;
+                g.CH = D;
+                g.bias_mode = 2;
+                mg_gemm_phase<T, true, EPI_PLAIN, PRO_GLOBAL>(c, a, g);
+            }
+            if (!mg_barrier(c, a.sync, a.err_flag)) return;
+            {   // D: residual + norm + up / gate + SwiGLU
+                mg_gemm<T> g = {};
+                g.W = (const T *)lw[6];
+                g.bias = (const T *)lw[7];
+                g.C = (T *)a.act;
+                g.K = D;
+                g.N = F;
+                g.CH = D;
+                g.bias_mode = 2;
+                g.xa = (const T *)a.xbuf;
+                g.ya = (const T *)a.proj;
+                g.norm_w = (const T *)lw[5];
+                g.sum_out = (T *)a.resid;
+                mg_gemm_phase<T, true, EPI_SWIGLU, PRO_ADD>(c, a, g);
+            }
+            if (!mg_barrier(c, a.sync, a.err_flag)) return;
+            {   // E: down projection (weight stored [F, D])
+                mg_gemm<T> g = {};
+                g.A = (const T *)a.act;
+                g.W = (const T *)lw[8];
+                g.bias = (const T *)lw[9];
+                g.C = (T *)a.mlp;
+                g.K = F;
+                g.N = D;
+                g.CH = ch_f;
+                g.bias_mode = 1;
+                mg_gemm_phase<T, false, EPI_PLAIN, PRO_GLOBAL>(c, a, g);
+            }
+            if (!mg_barrier(c, a.sync, a.err_flag)) return;
+        }
+        {   // F: residual + final norm + logits
+            mg_gemm<T> g = {};
+            g.W = (const T *)a.w_lm;
+            g.bias = (const T *)a.b_lm;
+            g.C = (T *)a.logits;
+            g.K = D;
+            g.N = V;
+            g.CH = D;
+            g.bias_mode = 2;
+            g.xa = (const T *)a.resid;
+            g.ya = (const T *)a.mlp;
+            g.norm_w = (const T *)a.w_final;
+            mg_gemm_phase<T, true, EPI_PLAIN, PRO_ADD>(c, a, g);
+        }
+        if (!mg_barrier(c, a.sync, a.err_flag)) return;
+        // G: greedy sampling and the feedback of ids and positions
+        for (int row = blockIdx.x; row < a.B; row += gridDim.x) {
+            const int32_t id = argmax_row<T>((const T *)a.logits + (size_t)row * V, V, a.softcap, am_sv, am_si);
+            if (c.tid == 0) {
+                a.tokens[row] = id;
+                const int t = t0 + step;
+                if (t >= 0 && t < a.max_steps) a.out_tokens[(size_t)t * a.B + row] = id;
+                a.positions[row] += 1;
+            }
+            __syncthreads();
+        }
+        if (!mg_barrier(c, a.sync, a.err_flag)) return;
+    }
+    if (blockIdx.x == 0 && c.tid == 0) *a.step_counter = t0 + a.n_steps;
+}
+
+}  // namespace
+
+bool gdb_decode_mega_supported(const gd_backend *be, uint32_t dtype, int B, int D, int F, int V, int H, int Dh, int L)
+{
+    if (be == NULL || (dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) || be->gemm_mode != 0) return false;
+    if (getenv("GDB200_DECODE_MEGA") != NULL && getenv("GDB200_DECODE_MEGA")[0] == '0') return false;
+    if (getenv("GDB200_SKINNY_DIRECT") != NULL) return false;
+    if (B < 1 || B > SK_ROWS || L < 1 || L > GDB_MEGA_MAX_LAYERS || Dh != 64 || H * Dh != D) return false;
+    if (D != 128 && D != 256 && D != 512) return false;              // the normalised activations stay resident: one K chunk
+    if (sk_chunk_for((uint32_t)F) == 0U || (V % 16) != 0) return false;   // F % 128 == 0 covers the 8-column SwiGLU units
+    return true;
+}
+
+gd_status gdb_decode_mega_launch(gd_backend *be, uint32_t dtype, const gdb_mega_args *a)
+{
+    const uint32_t ch_f = sk_chunk_for((uint32_t)a->F);
+    const mg_layout lay = mg_layout_for((uint32_t)a->D > ch_f ? (uint32_t)a->D : ch_f);
+    void (*kern)(const gdb_mega_args, const mg_layout) = dtype == GDB_DTYPE_F16 ? decode_mega_kernel<__half> : decode_mega_kernel<__nv_bfloat16>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.total);
+    if (e != cudaSuccess) return gdb_fail(be, e, "decode step kernel: shared memory attribute");
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MG_THREADS, lay.total);
+    if (e != cudaSuccess || per_sm < 1) {
+        return e != cudaSuccess ? gdb_fail(be, e, "decode step kernel: occupancy") : GD_ERR_UNSUPPORTED;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.gridDim = dim3((unsigned)be->sm_count);
+    cfg.blockDim = dim3(MG_THREADS);
+    cfg.dynamicSmemBytes = lay.total;
+    cfg.stream = be->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, *a, lay);
+    if (e != cudaSuccess) return gdb_fail(be, e, "decode step kernel: launch");
+    return gdb_launched(be, "decode step kernel");
+}

@@ -8,14 +8,14 @@
 //              cos/sin table for head_dim 64, theta 10000, positions < 512).
 //   rope: same rotation applied to one tensor [..., heads, head_dim] (src/ops/rope/).
 #include "common.cuh"
+#include "decode_parts.cuh"
 
 #include <math.h>
 #include <stdlib.h>
 
 namespace {
 
-constexpr unsigned TABLE_POSITIONS = 512, TABLE_HEAD_DIM = 64, TABLE_PAIRS = 32;
-constexpr float TABLE_THETA = 10000.0f;
+using namespace gdb_dec;   // rope_params, rope_cos_sin, rope_lo / rope_hi, the cos / sin table constants
 
 // ------------------------------------------------------------------ embedding
 template <typename T>
@@ -33,7 +33,7 @@ __global__ void embedding_fwd_kernel(const T *table, const int *ids, T *out, siz
         }
     }
 }
-// 16-byte units; nan_word is the 32-bit pattern of a NaN pair (F16 0x7e007e00) or one F32 NaN.
+// 16-byte units; nan_word is the 32-bit pattern of a NaN pair (F16 0x7e007e00, BF16 0x7fc07fc0) or one F32 NaN.
 __global__ void embedding_fwd_vec_kernel(const uint4 *table, const int *ids, uint4 *out, size_t n_ids, size_t vocab,
                                          size_t row_vecs, unsigned nan_word)
 {
@@ -74,28 +74,6 @@ __global__ void cast_from_f32_kernel(const float *src, T *dst, size_t n)
 }
 
 // ------------------------------------------------------------------ rope
-struct rope_params {
-    size_t tokens;
-    unsigned heads, head_dim, n_dims, interleaved;
-    float freq_scale, sin_sign;
-    int use_table;
-};
-
-__device__ __forceinline__ void rope_cos_sin(const rope_params &p, const float *table, unsigned pair, int pos, float *c, float *s)
-{
-    if (p.use_table && pos >= 0 && (unsigned)pos < TABLE_POSITIONS && pair < TABLE_PAIRS) {
-        const float2 cs = __ldg(reinterpret_cast<const float2 *>(table) + (size_t)pos * TABLE_PAIRS + pair);
-        *c = cs.x;
-        *s = cs.y * p.sin_sign;
-        return;
-    }
-    const float angle = (float)pos * exp2f((float)pair * p.freq_scale);
-    float sv, cv;
-    sincosf(angle, &sv, &cv);
-    *c = cv;
-    *s = sv * p.sin_sign;
-}
-
 // One thread per (token, head, pair). FWD: src = qkv [N, 3*H*Dh] -> q,k,v [N,H,Dh].
 // BWD: (gq, gk, gv) -> dqkv with sin_sign = -1.
 template <typename T, bool FWD>
@@ -190,10 +168,10 @@ __global__ void qkv_split_rope_vec8_kernel(const T *a0, const T *a1, const T *a2
             float c, s;
             rope_cos_sin(p, table, grp * 8U + (unsigned)e, pos, &c, &s);
             const float q0 = qa.get(e), q1 = qb.get(e), k0 = ka.get(e), k1 = kb.get(e);
-            qa.set(e, q0 * c - q1 * s);
-            qb.set(e, q0 * s + q1 * c);
-            ka.set(e, k0 * c - k1 * s);
-            kb.set(e, k0 * s + k1 * c);
+            qa.set(e, rope_lo(q0, q1, c, s));
+            qb.set(e, rope_hi(q0, q1, c, s));
+            ka.set(e, rope_lo(k0, k1, c, s));
+            kb.set(e, rope_hi(k0, k1, c, s));
         }
         if (FWD) {
             *reinterpret_cast<uint4 *>(o0 + split) = qa.raw;
@@ -371,6 +349,37 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
 
 }  // namespace
 
+// Rotation parameters exactly as gdb_qkv_rope_append would use them (cos / sin table included), for a caller that
+// applies the rotation inside its own kernel. GD_ERR_UNSUPPORTED where that entry would not take its vector path.
+gd_status gdb_rope_params_for_decode(gd_backend *be, uint32_t n_heads, uint32_t head_dim, const gd_backend_rope_args *args, size_t tokens,
+                                     gdb_dec::rope_params *out)
+{
+    if (be == NULL || out == NULL || n_heads == 0U || head_dim == 0U || (head_dim & 1U) != 0U || !rope_args_ok(args, head_dim)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (args->n_dims != head_dim || args->interleaved != 0U || (head_dim % 16U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    rope_params p;
+    p.tokens = tokens;
+    p.heads = n_heads;
+    p.head_dim = head_dim;
+    p.n_dims = args->n_dims;
+    p.interleaved = args->interleaved;
+    p.freq_scale = -2.0f * log2f(args->theta) / (float)args->n_dims;
+    p.sin_sign = 1.0f;
+    p.use_table = (head_dim == TABLE_HEAD_DIM && args->n_dims == TABLE_HEAD_DIM && fabsf(args->theta - TABLE_THETA) <= 1.0e-3f &&
+                   getenv("GD_QKV_SPLIT_ROPE_NO_TABLE") == NULL) ? 1 : 0;
+    if (p.use_table) {
+        gd_status st = ensure_rope_table(be);
+        if (st != GD_OK) {
+            return st;
+        }
+    }
+    *out = p;
+    return GD_OK;
+}
+
 // Decode step: q = rope(split(qkv)) to `q`, and the rotated key / the value of row b straight into slot pos_ids[b] of
 // the caches [rows, tmax, heads, head_dim] (qkv_split_rope_forward + kv_cache_append_positions in one launch).
 gd_status gdb_qkv_rope_append(gd_backend *be, const gd_backend_tensor_view *qkv, const gd_backend_tensor_view *pos_ids,
@@ -454,7 +463,7 @@ gd_status gd_backend_embedding_forward(gd_backend *be, const gd_backend_tensor_v
     }
     const size_t row_bytes = a->dim * gdb_dtype_size(table->dtype);
     if ((row_bytes % 16U) == 0U && (((uintptr_t)tp | (uintptr_t)op) % 16U) == 0U && table->dtype != GDB_DTYPE_BF16) {
-        const unsigned nan_word = table->dtype == GDB_DTYPE_F16 ? 0x7e007e00U : 0x7fc00000U;
+        const unsigned nan_word = table->dtype == GDB_DTYPE_F16 ? 0x7e007e00U : (table->dtype == GDB_DTYPE_BF16 ? 0x7fc07fc0U : 0x7fc00000U);
         gdb_launch(embedding_fwd_vec_kernel, gdb_grid_for(a->ids_count * (row_bytes / 16U), 256, be, 16), 256, 0, be->stream, (const uint4 *)tp, ip, (uint4 *)op, a->ids_count, a->vocab, row_bytes / 16U, nan_word);
     } else if (table->dtype == GDB_DTYPE_F16) {
         gdb_launch(embedding_fwd_kernel<__half>, gdb_grid_for(out->count, 256, be, 16), 256, 0, be->stream, (const __half *)tp, ip, (__half *)op, a->ids_count, a->vocab, a->dim);

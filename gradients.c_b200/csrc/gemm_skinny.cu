@@ -7,30 +7,13 @@
 // trip), runs mma.sync m16n8k16 with FP32 accumulators, and the partial tiles are summed through
 // shared memory before the bias add and the single rounding.
 #include "common.cuh"
+#include "decode_parts.cuh"
 
 #include <stdlib.h>
 
 namespace {
 
-template <typename T> struct mma16816;
-template <> struct mma16816<__half> {
-    static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
-    {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-    }
-};
-template <> struct mma16816<__nv_bfloat16> {
-    static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
-    {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-    }
-};
-
-constexpr int SK_ROWS = 64, SK_COLS = 16, SK_WARPS = 8;
+using namespace gdb_dec;
 
 // B_KMAJOR: B stored [N, K] (matmul_nt); otherwise B stored [K, N] (matmul / linear).
 template <typename T, bool B_KMAJOR>
@@ -108,22 +91,8 @@ gemm_skinny_kernel(const T *__restrict__ A, size_t lda, const T *__restrict__ B,
     }
 }
 
-// ---- staged variant: operands reach shared memory with coalesced 16-byte cp.async, fragments come from ldmatrix ----
-__device__ __forceinline__ uint32_t sk_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void sk_cp16(void *dst, const void *src, bool valid)
-{
-    const int bytes = valid ? 16 : 0;   // zero-fill rows beyond M
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sk_smem(dst)), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void sk_ldm4(uint32_t (&r)[4], const void *p)
-{
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sk_smem(p)));
-}
-__device__ __forceinline__ void sk_ldm4t(uint32_t (&r)[4], const void *p)
-{
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sk_smem(p)));
-}
-
+// ---- staged variant: operands reach shared memory with coalesced 16-byte cp.async, fragments come from ldmatrix
+// (helpers and the per-chunk multiply in decode_parts.cuh) ----
 // K is walked in chunks of CH (a multiple of 128): per chunk the CTA stages A[64, CH] and its 16 columns of B, each
 // warp multiplies its CH / 8 slice, and with more than one chunk the next one is in flight (two stages).
 // SWIGLU (B K-major, i.e. a transposed weight [2N, K] = [up | gate] rows): the CTA takes 8 "up" rows and the 8 "gate"
@@ -137,7 +106,7 @@ gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restri
 {
     gdb_pdl_sync();
     extern __shared__ __align__(16) unsigned char sk_sm[];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     static_assert(!SWIGLU || B_KMAJOR, "the fused SwiGLU epilogue reads a transposed weight");
     const uint32_t n0 = blockIdx.x * (SWIGLU ? SK_COLS / 2 : SK_COLS);
     const uint32_t LDA = CH + 8U, LDW = B_KMAJOR ? CH + 8U : 24U;
@@ -167,12 +136,7 @@ gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restri
     load_chunk(0, 0);
     if (stages == 2 && n_chunks > 1U) load_chunk(1, 1);
     float acc[4][2][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
+    sk_zero(acc);
     const uint32_t kw = CH / SK_WARPS;   // k elements per warp and chunk (a multiple of 16)
     for (uint32_t ci = 0; ci < n_chunks; ++ci) {
         const uint32_t st = stages == 2 ? (ci & 1U) : 0U;
@@ -183,22 +147,7 @@ gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restri
         }
         __syncthreads();
         const T *As = reinterpret_cast<const T *>(sk_sm + st * stage_bytes), *Ws = reinterpret_cast<const T *>(sk_sm + st * stage_bytes + a_bytes);
-        for (uint32_t k = warp * kw; k < (warp + 1U) * kw; k += 16U) {
-            uint32_t a[4][4], b4[4];
-#pragma unroll
-            for (int mt = 0; mt < 4; ++mt) sk_ldm4(a[mt], As + (mt * 16 + (lane & 15)) * LDA + k + (lane >> 4) * 8);
-            if (B_KMAJOR) {
-                sk_ldm4(b4, Ws + ((lane & 7) + ((lane >> 4) << 3)) * LDW + k + ((lane >> 3) & 1) * 8);
-            } else {
-                sk_ldm4t(b4, Ws + (k + (lane & 7) + ((lane >> 3) & 1) * 8) * LDW + (lane >> 4) * 8);
-            }
-            const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
-#pragma unroll
-            for (int mt = 0; mt < 4; ++mt) {
-                mma16816<T>::run(acc[mt][0], a[mt], b0);
-                mma16816<T>::run(acc[mt][1], a[mt], b1);
-            }
-        }
+        sk_mma_chunk<T, B_KMAJOR>(acc, As, Ws, LDA, LDW, warp * kw, (warp + 1U) * kw, lane);
         __syncthreads();   // every warp is done with this stage before it is refilled (or reused for the reduction)
         if (stages == 2) {
             if (ci + 2U < n_chunks) load_chunk(ci + 2U, st);
@@ -206,53 +155,22 @@ gemm_skinny_staged_kernel(const T *__restrict__ A, size_t lda, const T *__restri
             load_chunk(ci + 1U, 0);
         }
     }
-    float(*red)[SK_ROWS][SK_COLS + 1] = reinterpret_cast<float(*)[SK_ROWS][SK_COLS + 1]>(sk_sm);
-#pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            const int r = mt * 16 + g, c = nt * 8 + 2 * t;
-            red[warp][r][c] = acc[mt][nt][0];
-            red[warp][r][c + 1] = acc[mt][nt][1];
-            red[warp][r + 8][c] = acc[mt][nt][2];
-            red[warp][r + 8][c + 1] = acc[mt][nt][3];
-        }
+    sk_red_t red = reinterpret_cast<sk_red_t>(sk_sm);
+    sk_store_partials(red, acc, warp, lane);
     __syncthreads();
     if (SWIGLU) {
         for (int o = tid; o < SK_ROWS * (SK_COLS / 2); o += SK_WARPS * 32) {
             const int r = o / (SK_COLS / 2), c = o % (SK_COLS / 2);
             if ((uint32_t)r >= M) continue;
-            float up = 0.0f, gate = 0.0f;
-#pragma unroll
-            for (int w = 0; w < SK_WARPS; ++w) {
-                up += red[w][r][c];
-                gate += red[w][r][c + 8];
-            }
-            if (bias != nullptr) {
-                if (bias_mode == 2) {
-                    up = gdb_io<T>::rnd(up);
-                    gate = gdb_io<T>::rnd(gate);
-                }
-                up += gdb_io<T>::ld(bias, n0 + c);
-                gate += gdb_io<T>::ld(bias, N + n0 + c);
-            }
-            up = gdb_io<T>::rnd(up);       // the values the separate linear call would have stored
-            gate = gdb_io<T>::rnd(gate);
-            gdb_io<T>::st(C, (size_t)r * ldc + n0 + c, up * (gate * gdb_swiglu_sigmoid(gate)));
+            const float up = sk_sum(red, r, c), gate = sk_sum(red, r, c + 8);
+            gdb_io<T>::st(C, (size_t)r * ldc + n0 + c, sk_swiglu<T>(up, gate, bias, bias_mode, n0 + c, N + n0 + c));
         }
         return;
     }
     for (int o = tid; o < SK_ROWS * SK_COLS; o += SK_WARPS * 32) {
         const int r = o / SK_COLS, c = o % SK_COLS;
         if ((uint32_t)r >= M) continue;
-        float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < SK_WARPS; ++w) v += red[w][r][c];
-        if (bias != nullptr) {
-            if (bias_mode == 2) v = gdb_io<T>::rnd(v);
-            v += gdb_io<T>::ld(bias, n0 + c);
-        }
-        gdb_io<T>::st(C, (size_t)r * ldc + n0 + c, v);
+        gdb_io<T>::st(C, (size_t)r * ldc + n0 + c, sk_bias<T>(sk_sum(red, r, c), bias, bias_mode, n0 + c));
     }
 }
 
@@ -264,7 +182,7 @@ gd_status launch_staged(gd_backend *be, const void *a, size_t lda, const void *b
     const int stages = K / ch > 1U ? 2 : 1;
     const uint32_t a_bytes = SK_ROWS * (ch + 8U) * 2U, w_bytes = B_KMAJOR ? SK_COLS * (ch + 8U) * 2U : ch * 24U * 2U;
     size_t smem = (size_t)stages * (a_bytes + w_bytes);
-    const size_t red_bytes = sizeof(float) * SK_WARPS * SK_ROWS * (SK_COLS + 1);
+    const size_t red_bytes = SK_RED_BYTES;
     if (smem < red_bytes) smem = red_bytes;
     static size_t configured = 0;
     if (smem > configured) {
@@ -288,7 +206,7 @@ gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a,
     }
     const size_t lda = lda_bytes / 2U, ldb = ldb_bytes / 2U, ldc = ldc_bytes / 2U;
     // staged variant: K in chunks of 512 / 256 / 128 and 16-byte aligned rows
-    const uint32_t ch = (K % 512U) == 0U ? 512U : ((K % 256U) == 0U ? 256U : ((K % 128U) == 0U ? 128U : 0U));
+    const uint32_t ch = sk_chunk_for(K);
     if (ch != 0U && (((uintptr_t)a | (uintptr_t)b | lda_bytes | ldb_bytes) % 16U) == 0U && getenv("GDB200_SKINNY_DIRECT") == NULL) {
         if (dtype == GDB_DTYPE_F16) {
             return tb ? launch_staged<__half, true>(be, a, lda, b, ldb, c, ldc, bias, bias_mode, M, N, K, ch)
@@ -315,7 +233,7 @@ gd_status gdb_gemm_skinny(gd_backend *be, int tb, uint32_t dtype, const void *a,
 gd_status gdb_gemm_skinny_swiglu(gd_backend *be, uint32_t dtype, const void *a, size_t lda_bytes, const void *w, size_t ldw_bytes,
                                  const void *bias, void *c, size_t ldc_bytes, uint32_t M, uint32_t N, uint32_t K)
 {
-    const uint32_t ch = (K % 512U) == 0U ? 512U : ((K % 256U) == 0U ? 256U : ((K % 128U) == 0U ? 128U : 0U));
+    const uint32_t ch = sk_chunk_for(K);
     if ((dtype != GDB_DTYPE_F16 && dtype != GDB_DTYPE_BF16) || M == 0U || M > (uint32_t)SK_ROWS || N == 0U || (N % 8U) != 0U || ch == 0U ||
         (((uintptr_t)a | (uintptr_t)w | lda_bytes | ldw_bytes) % 16U) != 0U || (ldc_bytes % 2U) != 0U || getenv("GDB200_SKINNY_DIRECT") != NULL) {
         return GD_ERR_UNSUPPORTED;

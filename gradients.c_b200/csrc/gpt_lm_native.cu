@@ -15,6 +15,7 @@
 // normalised by the number of valid target rows of ALL ranks (counted and all-reduced at the start of
 // the step), so the summed gradients are those of the global batch without a division by the world size.
 #include "common.cuh"
+#include "decode_parts.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -762,49 +763,11 @@ __global__ void argmax_rows_kernel(const T *__restrict__ logits, uint32_t classe
 {
     gdb_pdl_sync();
     const uint32_t row = blockIdx.x;
-    const T *x = logits + (size_t)row * classes;
-    float best = -INFINITY;
-    uint32_t best_i = 0xFFFFFFFFU;
-    for (uint32_t i = threadIdx.x; i < classes; i += blockDim.x) {
-        float v = gdb_io<T>::ld(x, i);
-        if (softcap > 0.0f) v = softcap * tanhf(v / softcap);
-        if (!isfinite(v)) v = -INFINITY;
-        if (v > best || best_i == 0xFFFFFFFFU) {   // strided scan visits indices in increasing order
-            best = v;
-            best_i = i;
-        }
-    }
     __shared__ float sv[32];
     __shared__ uint32_t si[32];
-    auto merge = [](float &a, uint32_t &ai, float b, uint32_t bi) {
-        if (bi != 0xFFFFFFFFU && (ai == 0xFFFFFFFFU || b > a || (b == a && bi < ai))) {
-            a = b;
-            ai = bi;
-        }
-    };
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ob = __shfl_xor_sync(0xffffffffU, best, o);
-        const uint32_t oi = __shfl_xor_sync(0xffffffffU, best_i, o);
-        merge(best, best_i, ob, oi);
-    }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    if (lane == 0) {
-        sv[warp] = best;
-        si[warp] = best_i;
-    }
-    __syncthreads();
-    if (warp == 0) {
-        best = lane < nw ? sv[lane] : -INFINITY;
-        best_i = lane < nw ? si[lane] : 0xFFFFFFFFU;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffU, best, o);
-            const uint32_t oi = __shfl_xor_sync(0xffffffffU, best_i, o);
-            merge(best, best_i, ob, oi);
-        }
-        if (lane == 0) {
-            const int32_t id = best_i == 0xFFFFFFFFU ? 0 : (int32_t)best_i;
+    const int32_t id = gdb_dec::argmax_row<T>(logits + (size_t)row * classes, classes, softcap, sv, si);
+    {
+        if (threadIdx.x == 0) {
             ids_out[row] = id;
             if (out_tokens != nullptr) {
                 const int32_t t = *step_counter;
@@ -1002,6 +965,139 @@ gd_status decode_step_body(gd_backend *be, const gdb200_gpt_spec *s, const gdb20
     return c.st;
 }
 
+// The whole run of decode steps in one persistent kernel (decode_mega.cu) where its shapes allow; GD_ERR_UNSUPPORTED
+// otherwise (the caller then enqueues one launch per operation).
+gd_status decode_steps_persistent(gd_backend *be, const gdb200_gpt_spec *s, const gdb200_gpt_decode_state *d, int32_t n_steps, size_t *scratch_used)
+{
+    const int64_t B = d->batch, D = s->d_model, F = s->mlp_hidden, V = s->vocab_size, H = s->n_heads, Dh = s->head_dim, CAP = d->capacity;
+    const int L = s->n_layers;
+    const uint32_t dt = s->dtype;
+    if (!gdb_decode_mega_supported(be, dt, (int)B, (int)D, (int)F, (int)V, (int)H, (int)Dh, L)) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if ((long long)n_steps * (5 * L + 2) * be->sm_count >= (1LL << 30)) {
+        return GD_ERR_UNSUPPORTED;   // the barrier counter of one launch has 31 bits
+    }
+    const size_t es = gdb_dtype_size(dt);
+    Step c;
+    c.be = be;
+    c.s = s;
+    c.top = 0;
+    c.st = GD_OK;
+    c.where = "";
+    gdb_mega_args a;
+    memset(&a, 0, sizeof(a));
+    bool aligned = true;
+    auto pptr = [&](int idx, size_t count) -> const void * {
+        const void *p = gdb_raw_ptr(s->params_buffer, s->param_offset[idx], count * es);
+        if (p == NULL || ((uintptr_t)p % 16U) != 0U) aligned = false;
+        return p;
+    };
+    const int P_FINAL = 1 + 10 * L, P_LMW = s->tied_lm_head ? 0 : P_FINAL + 1, P_LMB = P_FINAL + (s->tied_lm_head ? 1 : 2);
+    a.emb = pptr(0, (size_t)(V * D));
+    a.w_final = pptr(P_FINAL, (size_t)D);
+    a.w_lm = pptr(P_LMW, (size_t)(V * D));
+    a.b_lm = pptr(P_LMB, (size_t)V);
+    const size_t counts[10] = {(size_t)D, (size_t)(3 * D * D), (size_t)(3 * D), (size_t)(D * D), (size_t)D,
+                               (size_t)D, (size_t)(2 * F * D), (size_t)(2 * F), (size_t)(F * D), (size_t)D};
+    const size_t cache_bytes = (size_t)(B * CAP * H * Dh) * es;
+    for (int i = 0; i < L; ++i) {
+        for (int j = 0; j < 10; ++j) a.lw[i][j] = pptr(1 + 10 * i + j, counts[j]);
+        a.kc[i] = gdb_raw_ptr(d->cache_buffer, d->k_cache_offset[i], cache_bytes);
+        a.vc[i] = gdb_raw_ptr(d->cache_buffer, d->v_cache_offset[i], cache_bytes);
+        if (a.kc[i] == NULL || a.vc[i] == NULL || (((uintptr_t)a.kc[i] | (uintptr_t)a.vc[i]) % 16U) != 0U) aligned = false;
+    }
+    if (!aligned) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    gd_backend_rope_args rope = {s->rope_theta, (uint32_t)Dh, 0U};
+    gd_status st = gdb_rope_params_for_decode(be, (uint32_t)H, (uint32_t)Dh, &rope, (size_t)B, &a.rope);
+    if (st != GD_OK) {
+        return st;
+    }
+    a.rope_table = be->rope_table;
+    a.B = (int)B;
+    a.D = (int)D;
+    a.F = (int)F;
+    a.V = (int)V;
+    a.H = (int)H;
+    a.L = L;
+    a.CAP = (int)CAP;
+    a.window = s->sdpa_window;
+    // the key splits the stand-alone attention entry uses for this shape (the same partition gives the same bits)
+    a.splits = gdb_dec::decode_choose_splits(be->sm_count, (int)B, 1, (int)H, (int)Dh, (int)CAP, 32);
+    a.max_steps = d->max_steps;
+    a.n_steps = n_steps;
+    a.eps = s->rms_eps;
+    a.scale = (float)(1.0 / sqrt((double)Dh));
+    a.softcap = s->logits_softcap;
+    auto act = [&](int64_t cols) -> void * {
+        Ten t = c.alloc(dt, {B, cols});
+        return t.buf != NULL ? (void *)(t.buf->dptr + t.off) : NULL;
+    };
+    a.xbuf = act(D);
+    a.resid = act(D);
+    a.q = act(D);
+    a.attn = act(D);
+    a.proj = act(D);
+    a.act = act(F);
+    a.mlp = act(D);
+    a.logits = act(V);
+    Ten sync = c.alloc(GDB_DTYPE_I32, {4});
+    if (c.st != GD_OK) {
+        snprintf(be->last_error, sizeof(be->last_error), "gpt decode steps: %s", c.where);
+        return c.st;
+    }
+    a.sync = (unsigned *)(sync.buf->dptr + sync.off);
+    int32_t *io = (int32_t *)gdb_raw_ptr(d->io_buffer, 0, gd_backend_buffer_nbytes(d->io_buffer));
+    if (io == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    a.tokens = io + d->tokens_offset / 4U;
+    a.positions = io + d->positions_offset / 4U;
+    a.out_tokens = io + d->out_tokens_offset / 4U;
+    a.step_counter = io + d->step_counter_offset / 4U;
+    a.err_flag = (int *)be->err_flag;
+    st = gd_backend_fill(be, sync.buf, sync.off, sync.count(), 4U, 0U);
+    if (st != GD_OK) {
+        return st;
+    }
+    // GDB200_DECODE_TIMELINE=1 (diagnostic): time stamps after every grid barrier, printed per phase as a mean over the steps
+    const int per_step = 5 * L + 2;
+    Ten tl;
+    const bool want_tl = getenv("GDB200_DECODE_TIMELINE") != NULL;
+    if (want_tl) {
+        tl = c.alloc(GDB_DTYPE_F32, {(int64_t)n_steps * per_step * 2});
+        if (c.st == GD_OK) a.timeline = (unsigned long long *)(tl.buf->dptr + tl.off);
+    }
+    if (scratch_used != NULL) {
+        *scratch_used = c.top;
+    }
+    st = gdb_decode_mega_launch(be, dt, &a);
+    if (st == GD_OK && a.timeline != NULL && n_steps > 2) {
+        std::vector<unsigned long long> h((size_t)n_steps * per_step);
+        if (cudaStreamSynchronize(be->stream) == cudaSuccess &&
+            cudaMemcpy(h.data(), a.timeline, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess) {
+            static const char *names[5] = {"A qkv+rope", "B attention", "C proj", "D upgate", "E down"};
+            fprintf(stderr, "decode timeline, mean ns per phase over steps 1..%d (%.1f us per step)\n", n_steps - 1,
+                    (double)(h.back() - h[(size_t)per_step - 1]) / 1000.0 / (double)(n_steps - 1));
+            for (int k = 0; k < per_step; ++k) {
+                double sum = 0.0;
+                for (int stp = 1; stp < n_steps; ++stp) {
+                    const size_t i = (size_t)stp * per_step + k;
+                    sum += (double)(h[i] - h[i - 1]);
+                }
+                if (k < 5 * L) {
+                    fprintf(stderr, "  layer %d %-12s %8.0f\n", k / 5, names[k % 5], sum / (n_steps - 1));
+                } else {
+                    fprintf(stderr, "  %-20s %8.0f\n", k == 5 * L ? "F logits" : "G argmax", sum / (n_steps - 1));
+                }
+            }
+        }
+    }
+    return st;
+}
+
 }  // namespace
 
 extern "C" gd_status gdb200_argmax_rows(gd_backend *be, const gd_backend_tensor_view *logits, float softcap, const gd_backend_tensor_view *out_ids)
@@ -1031,6 +1127,12 @@ extern "C" gd_status gdb200_gpt_decode_steps(gd_backend *be, const gdb200_gpt_sp
     }
     if (n_steps == 0) {
         return GD_OK;
+    }
+    if (use_graph) {
+        gd_status pst = decode_steps_persistent(be, s, d, n_steps, scratch_used);
+        if (pst != GD_ERR_UNSUPPORTED) {
+            return pst;
+        }
     }
     int done = 0;
     // The first step runs eagerly: it performs the one-time kernel attribute set-up that must not

@@ -176,18 +176,40 @@ def test_greedy_decode_matches_oracle():
 
 
 @pytest.mark.parametrize("use_graph", [False, True])
+@pytest.mark.parametrize("mlp_hidden", [192, 256])
 @pytest.mark.parametrize("batch,window", [(4, 24), (64, 0)])
-def test_native_decode_feeds_back_on_the_device_and_matches_the_host_loop(batch, window, use_graph):
-    """gdb200_gpt_decode_steps (device argmax, ids / positions kept on the device, optional graph replay)
-    generates exactly the ids of the per-step host loop: same kernels, same logits, same tie rule."""
-    cfg = small_cfg(dropout_p=0.0, tied_lm_head=(batch == 4), sdpa_window=window)
+def test_native_decode_feeds_back_on_the_device_and_matches_the_host_loop(batch, window, mlp_hidden, use_graph):
+    """gdb200_gpt_decode_steps (device argmax, ids / positions kept on the device) generates exactly the ids of the
+    per-step host loop: same arithmetic, same logits, same tie rule. use_graph = False enqueues one launch per
+    operation; with use_graph the run is ONE persistent kernel when the shapes allow (mlp_hidden 256: 13 steps in one
+    launch after the memset of its barrier words), else a replayed CUDA graph of the per-operation launches (192)."""
+    cfg = small_cfg(dropout_p=0.0, tied_lm_head=(batch == 4), sdpa_window=window, mlp_hidden=mlp_hidden)
     hp = g.init_params(cfg, seed=12, residual_scaled=False)
     prompts = np.random.default_rng(5).integers(0, cfg.vocab_size, size=(batch, 9)).astype(np.int32)
+    timing = {}
     with pkg.runtime.Context(params_bytes=64 << 20, state_bytes=256 << 20, scratch_bytes=1 << 30) as ctx:
         model = g.GptLm(ctx, cfg, hp)
         model.training = False
         want = g.greedy_generate(model, prompts, new_tokens=14, capacity=32)
-        got = g.greedy_generate_native(model, prompts, new_tokens=14, capacity=32, use_graph=use_graph)
+        got = g.greedy_generate_native(model, prompts, new_tokens=14, capacity=32, use_graph=use_graph, timing=timing)
+    assert np.array_equal(got, want)
+    if use_graph and mlp_hidden == 256:
+        assert timing["decode_launches"] <= 2, timing
+    else:
+        assert timing["decode_launches"] >= 13, timing
+
+
+def test_persistent_decode_kernel_past_the_cache_capacity_and_bf16():
+    """The persistent decode kernel with rows whose position runs past the cache capacity (the append is dropped and
+    attention reads the live part only, as the per-operation path does), in BF16."""
+    cfg = small_cfg(dropout_p=0.0, mlp_hidden=256, dtype=abi.BF16)
+    hp = g.init_params(cfg, seed=3, residual_scaled=False)
+    prompts = np.random.default_rng(6).integers(0, cfg.vocab_size, size=(8, 9)).astype(np.int32)
+    with pkg.runtime.Context(params_bytes=64 << 20, state_bytes=256 << 20, scratch_bytes=1 << 30) as ctx:
+        model = g.GptLm(ctx, cfg, hp)
+        model.training = False
+        want = g.greedy_generate(model, prompts, new_tokens=12, capacity=16)     # positions 9 .. 19 against 16 slots
+        got = g.greedy_generate_native(model, prompts, new_tokens=12, capacity=16)
     assert np.array_equal(got, want)
 
 
