@@ -5,14 +5,14 @@
 // A decode step of the benchmark model moves 22.5 MB of weights and the live K / V (174 MB on average): 27 us at the
 // measured copy bandwidth. As 28 dependent launches it takes 183 us, nearly all of it launch and drain latency. Here a
 // step is 5 phases per layer + 2:
-//   A  [embedding | residual add] + RMSNorm as the prologue of the QKV projection, RoPE and the K / V append as its
-//      epilogue (a CTA's 16 output columns are 8 rotation pairs of one head, or 16 value columns)
+//   A  [embedding +] RMSNorm as the prologue of the QKV projection, RoPE and the K / V append as its epilogue (a CTA's
+//      16 output columns are 8 rotation pairs of one head, or 16 value columns)
 //   B  attention over the cache: the 16 warps of a CTA are heads x key ranges of one sequence, each streaming its keys
 //      through a private shared-memory ring (cp.async, three tiles of 16 keys in flight), merged in shared memory
-//   C  attention output projection
-//   D  residual add + RMSNorm as the prologue of the up / gate projection, SwiGLU as its epilogue
-//   E  down projection
-//   F  residual add + final RMSNorm as the prologue of the logits projection
+//   C  attention output projection, residual add in its epilogue
+//   D  RMSNorm as the prologue of the up / gate projection, SwiGLU as its epilogue
+//   E  down projection, residual add in its epilogue
+//   F  final RMSNorm as the prologue of the logits projection
 //   G  greedy sampling (soft cap, first maximum), token / position feedback for the next step
 // Every phase runs the device functions of decode_parts.cuh that the stand-alone kernels run, on the same partition
 // of the work (16-column units with K split over eight warps, the same key splits), so a step gives the same bits as
@@ -36,10 +36,11 @@ constexpr int MG_THREADS = 512, MG_WARPS = MG_THREADS / 32;
 constexpr unsigned MG_SPIN_LIMIT = 1U << 22;   // polls of the barrier word (about a microsecond each) before giving up
 constexpr int MG_ERR_BARRIER = 398;
 constexpr int MG_OT_LD = SK_COLS + 1;
+constexpr uint32_t MG_EPI_BYTES = 64U + SK_ROWS * SK_COLS * 2U;   // a unit's bias (two 16-byte pieces) and its residual tile [64][16]
 constexpr uint32_t MG_RING_BYTES = 3U * 2U * 4U * 512U;   // per warp: three tiles of two key groups, K and V halves, 16 bytes per lane
 
 struct mg_layout {
-    uint32_t stage_bytes, red_off, ot_off, total;
+    uint32_t stage_bytes, red_off, ot_off, epi_off, total;
 };
 __host__ __device__ inline mg_layout mg_layout_for(uint32_t ch_max)
 {
@@ -47,7 +48,8 @@ __host__ __device__ inline mg_layout mg_layout_for(uint32_t ch_max)
     l.stage_bytes = SK_ROWS * (ch_max + 8U) * 2U + ch_max * 48U;   // A tile [64][ch + 8] + the larger of the two weight tiles ([ch][24])
     l.red_off = 2U * l.stage_bytes;
     l.ot_off = l.red_off + (uint32_t)SK_RED_BYTES;
-    l.total = l.ot_off + (uint32_t)(SK_ROWS * MG_OT_LD * sizeof(float));
+    l.epi_off = l.ot_off + (uint32_t)(SK_ROWS * MG_OT_LD * sizeof(float));
+    l.total = l.epi_off + MG_EPI_BYTES;
     const uint32_t attn = MG_WARPS * MG_RING_BYTES + MG_WARPS * (2U + 64U) * (uint32_t)sizeof(float);   // the attention phase's rings and partials alias the stages
     if (l.total < attn) l.total = attn;
     return l;
@@ -133,110 +135,125 @@ template <typename T> struct mg_nan_pair;
 template <> struct mg_nan_pair<__half> { static constexpr unsigned word = 0x7e007e00U; };
 template <> struct mg_nan_pair<__nv_bfloat16> { static constexpr unsigned word = 0x7fc07fc0U; };
 
-// ---- [embedding | residual add] + RMSNorm into the resident A tile ----
-// MODE 0: x = table[ids] (an id outside the table gives a NaN row, as the embedding kernel does); MODE 1: x = round(xa + ya).
-// Row r of the tile = round(x * w * rsqrt(mean(x^2) + eps)); `sum_out` (one CTA of the phase passes it) receives x.
-// mg_stage_rows puts every row of xa (and ya, into Ys) in flight at once with cp.async; after the wait, mg_norm_rows
-// normalises in place, in the per-lane order of rms_fwd_kernel / add_rms_fwd_kernel (lane takes the 8-element vectors
-// lane, lane + 32, ...), one warp per row.
-template <typename T, int MODE>
-__device__ __forceinline__ void mg_stage_rows(T *As, T *Ys, uint32_t LDA, const T *xa, const T *ya, const int32_t *ids, uint32_t vocab,
-                                              int B, int D, int tid)
+// ---- [embedding] + RMSNorm into the resident A tile ----
+// GATHER: row r = table[ids[r]] (an id outside the table gives a NaN row, as the embedding kernel does); otherwise row r of
+// x [B, D]. mg_stage_rows puts every row in flight at once with cp.async; after the wait, mg_norm_rows replaces row r by
+// round(x * w * rsqrt(mean(x^2) + eps)) in the per-lane order of rms_fwd_kernel (lane takes the 8-element vectors lane,
+// lane + 32), one warp per row, the warp's four rows interleaved.
+template <typename T, bool GATHER>
+__device__ __forceinline__ void mg_stage_rows(T *As, uint32_t LDA, const T *x, const int32_t *ids, uint32_t vocab, int B, int D, int tid)
 {
     const uint32_t vecs = (uint32_t)D / 8U;
     for (uint32_t i = tid; i < SK_ROWS * vecs; i += MG_THREADS) {
         const uint32_t r = i / vecs, v = i % vecs;
         T *dst = As + (size_t)r * LDA + v * 8U;
-        if (MODE == 0) {
+        if (GATHER) {
             const int id = (int)r < B ? ids[r] : 0;
             if ((int)r < B && (id < 0 || (uint32_t)id >= vocab)) {
                 const unsigned nw = mg_nan_pair<T>::word;
                 *reinterpret_cast<uint4 *>(dst) = make_uint4(nw, nw, nw, nw);
             } else {
-                sk_cp16(dst, xa + (size_t)((int)r < B ? id : 0) * D + v * 8U, (int)r < B);
+                sk_cp16(dst, x + (size_t)((int)r < B ? id : 0) * D + v * 8U, (int)r < B);
             }
         } else {
-            const size_t src = (size_t)((int)r < B ? r : 0U) * D + v * 8U;
-            sk_cp16(dst, xa + src, (int)r < B);
-            sk_cp16(Ys + (size_t)r * LDA + v * 8U, ya + src, (int)r < B);
+            sk_cp16(dst, x + (size_t)((int)r < B ? r : 0U) * D + v * 8U, (int)r < B);
         }
     }
 }
-template <typename T, int MODE>
-__device__ __forceinline__ void mg_norm_rows(T *As, const T *Ys, uint32_t LDA, const T *w, T *sum_out, int B, int D, float eps, int warp, int lane)
+
+// `wraw`: the lane's two vectors of the norm weight, loaded by the caller before it waited for the rows.
+template <typename T>
+__device__ __forceinline__ void mg_norm_rows(T *As, uint32_t LDA, const uint4 (&wraw)[2], int B, int D, float eps, int warp, int lane)
 {
+    constexpr int RPW = SK_ROWS / MG_WARPS;   // rows per warp
     const uint32_t vecs = (uint32_t)D / 8U;   // at most 64 (D <= 512): two vectors per lane
-    gdb_vec8<T> wv[2];
+    float ss[RPW];
+#pragma unroll
+    for (int q = 0; q < RPW; ++q) {
+        const int r = warp + q * MG_WARPS;
+        ss[q] = 0.0f;
+        if (r < B) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint32_t v = (uint32_t)lane + 32U * (uint32_t)i;
+                if (v < vecs) {
+                    const uint4 a = *reinterpret_cast<const uint4 *>(As + (size_t)r * LDA + v * 8U);
+                    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = pack2<T>::up(aw[k]);
+                        ss[q] += f.x * f.x;
+                        ss[q] += f.y * f.y;
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int q = 0; q < RPW; ++q) ss[q] += __shfl_xor_sync(0xffffffffU, ss[q], o);
+    }
+    float wf[2][8];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const uint32_t v = (uint32_t)lane + 32U * (uint32_t)i;
-        wv[i].raw = v < vecs ? __ldg(reinterpret_cast<const uint4 *>(w) + v) : make_uint4(0U, 0U, 0U, 0U);
-    }
-    for (int r = warp; r < B; r += MG_WARPS) {
-        T *arow = As + (size_t)r * LDA;
-        float ss = 0.0f;
-        for (uint32_t v = lane; v < vecs; v += 32) {
-            gdb_vec8<T> a;
-            a.raw = *reinterpret_cast<const uint4 *>(arow + v * 8U);
-            if (MODE == 0) {
+        const uint32_t ww[4] = {wraw[i].x, wraw[i].y, wraw[i].z, wraw[i].w};
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float f = a.get(e);
-                    ss += f * f;
-                }
-            } else {
-                gdb_vec8<T> b;
-                b.raw = *reinterpret_cast<const uint4 *>(Ys + (size_t)r * LDA + v * 8U);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    a.set(e, a.get(e) + b.get(e));
-                    const float f = a.get(e);
-                    ss += f * f;
-                }
-                *reinterpret_cast<uint4 *>(arow + v * 8U) = a.raw;
-            }
-            if (sum_out != nullptr) reinterpret_cast<uint4 *>(sum_out + (size_t)r * D)[v] = a.raw;
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = pack2<T>::up(ww[k]);
+            wf[i][2 * k] = f.x;
+            wf[i][2 * k + 1] = f.y;
         }
-        ss = gdb_warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)(size_t)D + eps);
+    }
+#pragma unroll
+    for (int q = 0; q < RPW; ++q) {
+        const int r = warp + q * MG_WARPS;
+        if (r >= B) continue;
+        const float inv = rsqrtf(ss[q] / (float)(size_t)D + eps);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const uint32_t v = (uint32_t)lane + 32U * (uint32_t)i;
             if (v < vecs) {
-                gdb_vec8<T> a;
-                a.raw = *reinterpret_cast<const uint4 *>(arow + v * 8U);   // written by this lane above
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    a.set(e, a.get(e) * wv[i].get(e) * inv);
-                }
-                *reinterpret_cast<uint4 *>(arow + v * 8U) = a.raw;
+                T *p = As + (size_t)r * LDA + v * 8U;
+                const uint4 a = *reinterpret_cast<const uint4 *>(p);
+                const float2 x0 = pack2<T>::up(a.x), x1 = pack2<T>::up(a.y), x2 = pack2<T>::up(a.z), x3 = pack2<T>::up(a.w);
+                uint4 o;
+                o.x = pack2<T>::down(x0.x * wf[i][0] * inv, x0.y * wf[i][1] * inv);
+                o.y = pack2<T>::down(x1.x * wf[i][2] * inv, x1.y * wf[i][3] * inv);
+                o.z = pack2<T>::down(x2.x * wf[i][4] * inv, x2.y * wf[i][5] * inv);
+                o.w = pack2<T>::down(x3.x * wf[i][6] * inv, x3.y * wf[i][7] * inv);
+                *reinterpret_cast<uint4 *>(p) = o;
             }
         }
     }
 }
 
-enum { EPI_PLAIN = 0, EPI_ROPE = 1, EPI_SWIGLU = 2 };
-enum { PRO_GLOBAL = 0, PRO_EMB = 1, PRO_ADD = 2 };
+enum { EPI_PLAIN = 0, EPI_ROPE = 1, EPI_SWIGLU = 2, EPI_RESID = 3 };
+enum { PRO_GLOBAL = 0, PRO_EMB = 1, PRO_ROWS = 2 };
 
 template <typename T> struct mg_gemm {
     // operands
     const T *A;            // PRO_GLOBAL: activations [B, K]
     const T *W;            // weight: K-major [N, K] or [K, N]
     const T *bias;
-    T *C;                  // PLAIN / SWIGLU destination [B, N]
+    T *C;                  // PLAIN / SWIGLU / RESID destination [B, N]
     uint32_t K, N, CH;
     int bias_mode;
-    // prologue (PRO_EMB / PRO_ADD)
-    const T *xa, *ya, *norm_w;
-    T *sum_out;
+    // prologue (PRO_EMB: x = table rows of ids; PRO_ROWS: x [B, K])
+    const T *x, *norm_w;
     const int32_t *ids;
     uint32_t vocab;
+    // RESID epilogue: C = round(res + round(linear)); res [B, N], or rows res_ids of the table `res` when res_ids != NULL
+    const T *res;
+    const int32_t *res_ids;
     // rope epilogue
     T *q, *kc, *vc;
     const int32_t *positions;
 };
 
-// One phase = one contraction [B <= 64, K] x [K, N] spread over the CTAs in units of 16 output columns.
+// One phase = one contraction [B <= 64, K] x [K, N] spread over the CTAs in units of 16 output columns. Warps w and
+// w + 8 share the k range w of a chunk and take 32 of the 64 rows each, so the sum of an output over k is formed exactly
+// as in the eight-warp stand-alone kernel.
 template <typename T, bool B_KMAJOR, int EPI, int PRO>
 __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a, const mg_gemm<T> &g)
 {
@@ -252,8 +269,11 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
     const uint32_t CH = g.CH, LDA = CH + 8U, LDW = B_KMAJOR ? CH + 8U : 24U, a_bytes = SK_ROWS * LDA * 2U;
     const uint32_t n_chunks = g.K / CH, kw = CH / SK_WARPS;
     const uint32_t M = (uint32_t)a.B;
+    const uint32_t kslot = (uint32_t)c.warp & 7U;
+    const size_t ldw = B_KMAJOR ? (size_t)g.K : (size_t)g.N;
     sk_red_t red = reinterpret_cast<sk_red_t>(c.sm + c.lay.red_off);
     float(*ot)[MG_OT_LD] = reinterpret_cast<float(*)[MG_OT_LD]>(c.sm + c.lay.ot_off);
+    T *sm_bias = reinterpret_cast<T *>(c.sm + c.lay.epi_off), *sm_res = reinterpret_cast<T *>(c.sm + c.lay.epi_off + 64U);
     auto stage_a = [&](uint32_t st) { return reinterpret_cast<T *>(c.sm + st * c.lay.stage_bytes); };
     auto stage_w = [&](uint32_t st) { return reinterpret_cast<T *>(c.sm + st * c.lay.stage_bytes + a_bytes); };
     auto unit_rows = [&](uint32_t unit, uint32_t *lo, uint32_t *hi) {
@@ -275,42 +295,81 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
             *hi = *lo + 8U;
         }
     };
+    // the unit's epilogue operands ride along with its weights: bias pieces, and for RESID the residual tile
+    auto load_epi = [&](uint32_t lo, uint32_t hi) {
+        if (g.bias != nullptr && c.tid < 2) sk_cp16(sm_bias + c.tid * 8, g.bias + (c.tid == 0 ? lo : hi), true);
+        if (EPI == EPI_RESID) {
+            for (uint32_t i = c.tid; i < SK_ROWS * 2U; i += MG_THREADS) {
+                const uint32_t r = i >> 1, pc = i & 1U;
+                T *dst = sm_res + r * SK_COLS + pc * 8U;
+                if (r >= M) continue;
+                if (g.res_ids != nullptr) {
+                    const int id = g.res_ids[r];
+                    if (id < 0 || (uint32_t)id >= g.vocab) {
+                        const unsigned nw = mg_nan_pair<T>::word;
+                        *reinterpret_cast<uint4 *>(dst) = make_uint4(nw, nw, nw, nw);
+                    } else {
+                        sk_cp16(dst, g.res + (size_t)id * g.N + lo + pc * 8U, true);
+                    }
+                } else {
+                    sk_cp16(dst, g.res + (size_t)r * g.N + lo + pc * 8U, true);
+                }
+            }
+        }
+    };
     bool first = true;
+    uint32_t wst = 0U;   // weight stage of the current unit (resident-A phases)
     for (uint32_t unit = blockIdx.x; unit < nunits; unit += gridDim.x) {
         uint32_t lo, hi;
         unit_rows(unit, &lo, &hi);
-        float acc[4][2][4];
+        float acc[2][2][4];
         sk_zero(acc);
-        if (PRO != PRO_GLOBAL) {
-            // resident A (single chunk): weights stream in while the prologue runs
-            mg_load_w<T, B_KMAJOR>(stage_w(0), g.W, B_KMAJOR ? (size_t)g.K : (size_t)g.N, CH, 0, lo, hi, c.tid);
-            mg_commit();
-            if (first) {
-                if (PRO == PRO_EMB) {
-                    mg_stage_rows<T, 0>(stage_a(0), stage_a(1), LDA, g.xa, nullptr, g.ids, g.vocab, a.B, a.D, c.tid);
-                } else {
-                    mg_stage_rows<T, 1>(stage_a(0), stage_a(1), LDA, g.xa, g.ya, nullptr, 0U, a.B, a.D, c.tid);
-                }
-                mg_commit();
+        auto mma = [&](const T *As, const T *Ws) {
+            if (c.warp < SK_WARPS) {
+                sk_mma_chunk<T, B_KMAJOR, 0, 2>(acc, As, Ws, LDA, LDW, kslot * kw, (kslot + 1U) * kw, c.lane);
+            } else {
+                sk_mma_chunk<T, B_KMAJOR, 2, 2>(acc, As, Ws, LDA, LDW, kslot * kw, (kslot + 1U) * kw, c.lane);
             }
-            mg_wait_all();
+        };
+        if (PRO != PRO_GLOBAL) {
+            // resident A (single chunk): the unit's weights stream in while the prologue runs, and the weights of the CTA's
+            // next unit (the other weight stage) while this one is multiplied
+            uint4 wraw[2] = {make_uint4(0U, 0U, 0U, 0U), make_uint4(0U, 0U, 0U, 0U)};
+            if (first) {
+                mg_load_w<T, B_KMAJOR>(stage_w(0), g.W, ldw, CH, 0, lo, hi, c.tid);
+                if (PRO == PRO_EMB) {
+                    mg_stage_rows<T, true>(stage_a(0), LDA, g.x, g.ids, g.vocab, a.B, a.D, c.tid);
+                } else {
+                    mg_stage_rows<T, false>(stage_a(0), LDA, g.x, nullptr, 0U, a.B, a.D, c.tid);
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint32_t v = (uint32_t)c.lane + 32U * (uint32_t)i;
+                    if (v < (uint32_t)a.D / 8U) wraw[i] = __ldg(reinterpret_cast<const uint4 *>(g.norm_w) + v);
+                }
+            }
+            load_epi(lo, hi);
+            mg_commit();
+            if (unit + gridDim.x < nunits) {
+                uint32_t nlo, nhi;
+                unit_rows(unit + gridDim.x, &nlo, &nhi);
+                mg_load_w<T, B_KMAJOR>(stage_w(wst ^ 1U), g.W, ldw, CH, 0, nlo, nhi, c.tid);
+            }
+            mg_commit();
+            mg_wait_one();   // everything but the next unit's weights
             __syncthreads();
             if (first) {
-                T *sum_out = blockIdx.x == 0U ? g.sum_out : nullptr;
-                if (PRO == PRO_EMB) {
-                    mg_norm_rows<T, 0>(stage_a(0), stage_a(1), LDA, g.norm_w, sum_out, a.B, a.D, a.eps, c.warp, c.lane);
-                } else {
-                    mg_norm_rows<T, 1>(stage_a(0), stage_a(1), LDA, g.norm_w, sum_out, a.B, a.D, a.eps, c.warp, c.lane);
-                }
+                mg_norm_rows<T>(stage_a(0), LDA, wraw, a.B, a.D, a.eps, c.warp, c.lane);
                 first = false;
                 __syncthreads();
             }
-            if (c.warp < SK_WARPS) sk_mma_chunk<T, B_KMAJOR>(acc, stage_a(0), stage_w(0), LDA, LDW, c.warp * kw, (c.warp + 1U) * kw, c.lane);
+            mma(stage_a(0), stage_w(wst));
+            wst ^= 1U;
         } else {
-            const size_t ldb = B_KMAJOR ? (size_t)g.K : (size_t)g.N;
             auto load_chunk = [&](uint32_t ci, uint32_t st) {
                 mg_load_a<T>(stage_a(st), LDA, g.A, (size_t)g.K, CH, (size_t)ci * CH, M, c.tid);
-                mg_load_w<T, B_KMAJOR>(stage_w(st), g.W, ldb, CH, (size_t)ci * CH, lo, hi, c.tid);
+                mg_load_w<T, B_KMAJOR>(stage_w(st), g.W, ldw, CH, (size_t)ci * CH, lo, hi, c.tid);
+                if (ci == 0U) load_epi(lo, hi);
                 mg_commit();
             };
             load_chunk(0, 0);
@@ -323,32 +382,44 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
                     mg_wait_all();
                 }
                 __syncthreads();
-                if (c.warp < SK_WARPS) sk_mma_chunk<T, B_KMAJOR>(acc, stage_a(st), stage_w(st), LDA, LDW, c.warp * kw, (c.warp + 1U) * kw, c.lane);
+                mma(stage_a(st), stage_w(st));
                 __syncthreads();
                 if (ci + 2U < n_chunks) load_chunk(ci + 2U, st);
             }
         }
-        if (c.warp < SK_WARPS) sk_store_partials(red, acc, c.warp, c.lane);
+        if (c.warp < SK_WARPS) {
+            sk_store_partials<0, 2>(red, acc, (int)kslot, c.lane);
+        } else {
+            sk_store_partials<2, 2>(red, acc, (int)kslot, c.lane);
+        }
         __syncthreads();
+        const T *bias = g.bias != nullptr ? sm_bias : nullptr;   // local columns: 0..7 = lo.., 8..15 = hi..
         if (EPI == EPI_SWIGLU) {
             for (int o = c.tid; o < SK_ROWS * (SK_COLS / 2); o += MG_THREADS) {
                 const int r = o / (SK_COLS / 2), cc = o % (SK_COLS / 2);
                 if ((uint32_t)r >= M) continue;
                 const float up = sk_sum(red, r, cc), gate = sk_sum(red, r, cc + 8);
-                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, sk_swiglu<T>(up, gate, g.bias, g.bias_mode, lo + cc, hi + cc));
+                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, sk_swiglu<T>(up, gate, bias, g.bias_mode, (uint32_t)cc, (uint32_t)cc + 8U));
             }
         } else if (EPI == EPI_PLAIN) {
             for (int o = c.tid; o < SK_ROWS * SK_COLS; o += MG_THREADS) {
                 const int r = o / SK_COLS, cc = o % SK_COLS;
                 if ((uint32_t)r >= M) continue;
-                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, sk_bias<T>(sk_sum(red, r, cc), g.bias, g.bias_mode, lo + cc));
+                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, sk_bias<T>(sk_sum(red, r, cc), bias, g.bias_mode, (uint32_t)cc));
+            }
+        } else if (EPI == EPI_RESID) {
+            // the rounded linear output, then the residual add with its own rounding (gd_backend_add after the linear layer)
+            for (int o = c.tid; o < SK_ROWS * SK_COLS; o += MG_THREADS) {
+                const int r = o / SK_COLS, cc = o % SK_COLS;
+                if ((uint32_t)r >= M) continue;
+                const float y = gdb_io<T>::rnd(sk_bias<T>(sk_sum(red, r, cc), bias, g.bias_mode, (uint32_t)cc));
+                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, gdb_io<T>::ld(sm_res, (size_t)r * SK_COLS + cc) + y);
             }
         } else {
             // the rounded linear output of the unit, then the rotation of qkv_split_rope and the append of kv_cache_append
             for (int o = c.tid; o < SK_ROWS * SK_COLS; o += MG_THREADS) {
                 const int r = o / SK_COLS, cc = o % SK_COLS;
-                const uint32_t col = cc < 8 ? lo + cc : hi + (cc - 8);
-                ot[r][cc] = (uint32_t)r < M ? gdb_io<T>::rnd(sk_bias<T>(sk_sum(red, r, cc), g.bias, g.bias_mode, col)) : 0.0f;
+                ot[r][cc] = (uint32_t)r < M ? gdb_io<T>::rnd(sk_bias<T>(sk_sum(red, r, cc), bias, g.bias_mode, (uint32_t)cc)) : 0.0f;
             }
             __syncthreads();
             const uint32_t nrope = 2U * (uint32_t)a.H * 4U, area = (uint32_t)a.D;
@@ -382,7 +453,7 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
                 }
             }
         }
-        __syncthreads();   // the weight stage, the reduction buffer and the output tile are reused by the CTA's next unit
+        __syncthreads();   // the weight stage, the reduction buffer and the epilogue operands are reused by the CTA's next unit
     }
 }
 
@@ -430,20 +501,18 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 g.CH = D;
                 g.bias_mode = 2;
                 g.norm_w = (const T *)lw[0];
-                g.sum_out = (T *)a.xbuf;
                 g.q = (T *)a.q;
                 g.kc = kc;
                 g.vc = vc;
                 g.positions = a.positions;
                 if (layer == 0) {
-                    g.xa = (const T *)a.emb;
+                    g.x = (const T *)a.emb;
                     g.ids = a.tokens;
                     g.vocab = V;
                     mg_gemm_phase<T, true, EPI_ROPE, PRO_EMB>(c, a, g);
                 } else {
-                    g.xa = (const T *)a.resid;
-                    g.ya = (const T *)a.mlp;
-                    mg_gemm_phase<T, true, EPI_ROPE, PRO_ADD>(c, a, g);
+                    g.x = (const T *)a.xbuf;
+                    mg_gemm_phase<T, true, EPI_ROPE, PRO_ROWS>(c, a, g);
                 }
             }
             if (!mg_barrier(c, a.sync, a.err_flag)) return;
@@ -467,20 +536,27 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 }
             }
             if (!mg_barrier(c, a.sync, a.err_flag)) return;
-            {   // C: attention output projection
+            {   // C: attention output projection + residual: resid = x + proj (layer 0: x = the embedding rows)
                 mg_gemm<T> g = {};
                 g.A = (const T *)a.attn;
                 g.W = (const T *)lw[3];
                 g.bias = (const T *)lw[4];
-                g.C = (T *)a.proj;
+                g.C = (T *)a.resid;
                 g.K = D;
                 g.N = D;
                 g.CH = D;
                 g.bias_mode = 2;
-                mg_gemm_phase<T, true, EPI_PLAIN, PRO_GLOBAL>(c, a, g);
+                if (layer == 0) {
+                    g.res = (const T *)a.emb;
+                    g.res_ids = a.tokens;
+                    g.vocab = V;
+                } else {
+                    g.res = (const T *)a.xbuf;
+                }
+                mg_gemm_phase<T, true, EPI_RESID, PRO_GLOBAL>(c, a, g);
             }
             if (!mg_barrier(c, a.sync, a.err_flag)) return;
-            {   // D: residual + norm + up / gate + SwiGLU
+            {   // D: norm + up / gate + SwiGLU
                 mg_gemm<T> g = {};
                 g.W = (const T *)lw[6];
                 g.bias = (const T *)lw[7];
@@ -489,28 +565,27 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
                 g.N = F;
                 g.CH = D;
                 g.bias_mode = 2;
-                g.xa = (const T *)a.xbuf;
-                g.ya = (const T *)a.proj;
+                g.x = (const T *)a.resid;
                 g.norm_w = (const T *)lw[5];
-                g.sum_out = (T *)a.resid;
-                mg_gemm_phase<T, true, EPI_SWIGLU, PRO_ADD>(c, a, g);
+                mg_gemm_phase<T, true, EPI_SWIGLU, PRO_ROWS>(c, a, g);
             }
             if (!mg_barrier(c, a.sync, a.err_flag)) return;
-            {   // E: down projection (weight stored [F, D])
+            {   // E: down projection (weight stored [F, D]) + residual: x = resid + mlp
                 mg_gemm<T> g = {};
                 g.A = (const T *)a.act;
                 g.W = (const T *)lw[8];
                 g.bias = (const T *)lw[9];
-                g.C = (T *)a.mlp;
+                g.C = (T *)a.xbuf;
                 g.K = F;
                 g.N = D;
                 g.CH = ch_f;
                 g.bias_mode = 1;
-                mg_gemm_phase<T, false, EPI_PLAIN, PRO_GLOBAL>(c, a, g);
+                g.res = (const T *)a.resid;
+                mg_gemm_phase<T, false, EPI_RESID, PRO_GLOBAL>(c, a, g);
             }
             if (!mg_barrier(c, a.sync, a.err_flag)) return;
         }
-        {   // F: residual + final norm + logits
+        {   // F: final norm + logits
             mg_gemm<T> g = {};
             g.W = (const T *)a.w_lm;
             g.bias = (const T *)a.b_lm;
@@ -519,10 +594,9 @@ __global__ void __launch_bounds__(MG_THREADS, 1) decode_mega_kernel(const __grid
             g.N = V;
             g.CH = D;
             g.bias_mode = 2;
-            g.xa = (const T *)a.resid;
-            g.ya = (const T *)a.mlp;
+            g.x = (const T *)a.xbuf;
             g.norm_w = (const T *)a.w_final;
-            mg_gemm_phase<T, true, EPI_PLAIN, PRO_ADD>(c, a, g);
+            mg_gemm_phase<T, true, EPI_PLAIN, PRO_ROWS>(c, a, g);
         }
         if (!mg_barrier(c, a.sync, a.err_flag)) return;
         // G: greedy sampling and the feedback of ids and positions

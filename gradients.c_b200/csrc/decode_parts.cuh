@@ -50,10 +50,11 @@ __device__ __forceinline__ void sk_ldm4t(uint32_t (&r)[4], const void *p)
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sk_smem(p)));
 }
 
-__device__ __forceinline__ void sk_zero(float (&acc)[4][2][4])
+template <int MTN>
+__device__ __forceinline__ void sk_zero(float (&acc)[MTN][2][4])
 {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < MTN; ++i)
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -61,15 +62,16 @@ __device__ __forceinline__ void sk_zero(float (&acc)[4][2][4])
 }
 
 // One warp's share [k_begin, k_end) of a staged chunk: As [64][LDA] row-major activations, Ws either [16][LDW]
-// (B_KMAJOR: one row per output column) or [chunk][LDW = 24] (one row per k).
-template <typename T, bool B_KMAJOR>
-__device__ __forceinline__ void sk_mma_chunk(float (&acc)[4][2][4], const T *As, const T *Ws, uint32_t LDA, uint32_t LDW,
+// (B_KMAJOR: one row per output column) or [chunk][LDW = 24] (one row per k). The warp multiplies the 16-row tiles
+// MT0 .. MT0 + MTN - 1 (all four, or two when two warps share a k range); acc is indexed by tile - MT0.
+template <typename T, bool B_KMAJOR, int MT0 = 0, int MTN = 4>
+__device__ __forceinline__ void sk_mma_chunk(float (&acc)[MTN][2][4], const T *As, const T *Ws, uint32_t LDA, uint32_t LDW,
                                              uint32_t k_begin, uint32_t k_end, int lane)
 {
     for (uint32_t k = k_begin; k < k_end; k += 16U) {
-        uint32_t a[4][4], b4[4];
+        uint32_t a[MTN][4], b4[4];
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) sk_ldm4(a[mt], As + (mt * 16 + (lane & 15)) * LDA + k + (lane >> 4) * 8);
+        for (int mt = 0; mt < MTN; ++mt) sk_ldm4(a[mt], As + ((MT0 + mt) * 16 + (lane & 15)) * LDA + k + (lane >> 4) * 8);
         if (B_KMAJOR) {
             sk_ldm4(b4, Ws + ((lane & 7) + ((lane >> 4) << 3)) * LDW + k + ((lane >> 3) & 1) * 8);
         } else {
@@ -77,26 +79,27 @@ __device__ __forceinline__ void sk_mma_chunk(float (&acc)[4][2][4], const T *As,
         }
         const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
+        for (int mt = 0; mt < MTN; ++mt) {
             mma16816<T>::run(acc[mt][0], a[mt], b0);
             mma16816<T>::run(acc[mt][1], a[mt], b1);
         }
     }
 }
 
-// A warp's partial 64 x 16 tile into its slot of the reduction buffer.
-__device__ __forceinline__ void sk_store_partials(sk_red_t red, const float (&acc)[4][2][4], int warp, int lane)
+// A warp's partial tile (row tiles MT0 .. MT0 + MTN - 1 of the 64 x 16 unit) into slot `kslot` of the reduction buffer.
+template <int MT0 = 0, int MTN = 4>
+__device__ __forceinline__ void sk_store_partials(sk_red_t red, const float (&acc)[MTN][2][4], int kslot, int lane)
 {
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
+    for (int mt = 0; mt < MTN; ++mt)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-            const int r = mt * 16 + g, c = nt * 8 + 2 * t;
-            red[warp][r][c] = acc[mt][nt][0];
-            red[warp][r][c + 1] = acc[mt][nt][1];
-            red[warp][r + 8][c] = acc[mt][nt][2];
-            red[warp][r + 8][c + 1] = acc[mt][nt][3];
+            const int r = (MT0 + mt) * 16 + g, c = nt * 8 + 2 * t;
+            red[kslot][r][c] = acc[mt][nt][0];
+            red[kslot][r][c + 1] = acc[mt][nt][1];
+            red[kslot][r + 8][c] = acc[mt][nt][2];
+            red[kslot][r + 8][c + 1] = acc[mt][nt][3];
         }
 }
 
@@ -172,6 +175,45 @@ __device__ __forceinline__ void rope_cos_sin(const rope_params &p, const float *
 // The rotated pair (x0, x1) -> (x0 c - x1 s, x0 s + x1 c).
 __device__ __forceinline__ float rope_lo(float x0, float x1, float c, float s) { return x0 * c - x1 * s; }
 __device__ __forceinline__ float rope_hi(float x0, float x1, float c, float s) { return x0 * s + x1 * c; }
+
+// ------------------------------------------------------------------ packed storage pairs
+// Two storage elements in one 32-bit word. add() is the packed storage-precision add: for operands of the storage type it
+// returns round(a + b) exactly as an FP32 add followed by the rounding store does (the FP32 sum of two 11-bit or 8-bit
+// significands is rounded once more to the same result: 24 >= 2 p + 2).
+template <typename T> struct pack2;
+template <> struct pack2<__half> {
+    static __device__ __forceinline__ float2 up(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2 *>(&w)); }
+    static __device__ __forceinline__ uint32_t down(float a, float b)
+    {
+        const __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b)
+    {
+        const __half2 r = __hadd2(*reinterpret_cast<const __half2 *>(&a), *reinterpret_cast<const __half2 *>(&b));
+        return *reinterpret_cast<const uint32_t *>(&r);
+    }
+};
+template <> struct pack2<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 up(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000U)); }
+    static __device__ __forceinline__ uint32_t down(float a, float b)
+    {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b)
+    {
+        const float2 x = up(a), y = up(b);
+        return down(x.x + y.x, x.y + y.y);
+    }
+};
+// The 8 elements of a 16-byte vector as floats.
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4 &raw, float (&f)[8])
+{
+    const float2 a = pack2<T>::up(raw.x), b = pack2<T>::up(raw.y), c = pack2<T>::up(raw.z), d = pack2<T>::up(raw.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
 
 // ------------------------------------------------------------------ split-K decode attention
 struct decode_params {
@@ -266,7 +308,8 @@ __device__ __forceinline__ void decode_combine_query(const float *ml, const floa
 
 // One warp: query w = (b, t, hq) against the keys of split `split` of its live range. A key is handled by DH / 16
 // adjacent lanes (16 head dims = two 16-byte pieces each of K and V), so a warp takes 32 / (DH / 16) keys per group and
-// two groups per tile; the partial goes to ml_item [2] = (max, sum) and acc_item [DH] (global or shared memory).
+// two groups per tile, folded into the running (max, sum, acc) with one rescale per tile; the partial goes to
+// ml_item [2] = (max, sum) and acc_item [DH] (global or shared memory).
 // RING = false: a tile's loads go to registers and are consumed at once. RING = true (DH = 64): `ring` is 12 KB of
 // shared memory owned by this warp, three tiles of 16 keys deep; the warp copies a tile with cp.async, 4 keys x 128
 // contiguous bytes per instruction (full sectors), the 16-byte pieces of key k stored at piece ^ (k & 7) so that the
@@ -289,23 +332,53 @@ __device__ __forceinline__ void decode_split_item(const T *q, const T *kc, const
     float acc[16], qr[16];
 #pragma unroll
     for (int c = 0; c < 16; ++c) acc[c] = 0.0f;
-    // one group of keys: score, online-softmax update
-    auto fold = [&](bool valid, const gdb_vec8<T> &k0, const gdb_vec8<T> &k1, const gdb_vec8<T> &v0, const gdb_vec8<T> &v1) {
-        float s = 0.0f;
-        if (valid) {
+    // one tile = two groups of keys: both scores, ONE running-max update, both keys folded into (l, acc)
+    auto fold2 = [&](const bool (&valid)[2], const uint4 (&k0)[2], const uint4 (&k1)[2], const uint4 (&v0)[2], const uint4 (&v1)[2]) {
+        float s[2];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s += qr[e] * k0.get(e) + qr[8 + e] * k1.get(e);
+        for (int u = 0; u < 2; ++u) {
+            s[u] = 0.0f;
+            if (valid[u]) {
+                float ka[8], kb[8];
+                unpack8<T>(k0[u], ka);
+                unpack8<T>(k1[u], kb);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[u] = fmaf(qr[e], ka[e], s[u]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[u] = fmaf(qr[8 + e], kb[e], s[u]);
+            }
         }
 #pragma unroll
-        for (int o = 1; o < LPK; o <<= 1) s += __shfl_xor_sync(0xffffffffU, s, o);
-        if (valid) {
-            const float mnew = fmaxf(s, m);
-            const float corr = __expf(m - mnew), e = __expf(s - mnew);
-            l = l * corr + e;
+        for (int o = 1; o < LPK; o <<= 1) {
+            s[0] += __shfl_xor_sync(0xffffffffU, s[0], o);
+            s[1] += __shfl_xor_sync(0xffffffffU, s[1], o);
+        }
+        const float s0 = valid[0] ? s[0] : -INFINITY, s1 = valid[1] ? s[1] : -INFINITY;
+        const float mnew = fmaxf(m, fmaxf(s0, s1));
+        if (mnew != -INFINITY) {
+            const float corr = __expf(m - mnew), e0 = __expf(s0 - mnew), e1 = __expf(s1 - mnew);   // exp(-inf) = 0
+            l = l * corr + e0 + e1;
+            float va[8], vb[8];
+            if (valid[0]) {
+                unpack8<T>(v0[0], va);
+                unpack8<T>(v1[0], vb);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                acc[c] = acc[c] * corr + e * v0.get(c);
-                acc[8 + c] = acc[8 + c] * corr + e * v1.get(c);
+                for (int c = 0; c < 8; ++c) {
+                    acc[c] = fmaf(e0, va[c], acc[c] * corr);
+                    acc[8 + c] = fmaf(e0, vb[c], acc[8 + c] * corr);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) acc[c] *= corr;
+            }
+            if (valid[1]) {
+                unpack8<T>(v0[1], va);
+                unpack8<T>(v1[1], vb);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    acc[c] = fmaf(e1, va[c], acc[c]);
+                    acc[8 + c] = fmaf(e1, vb[c], acc[8 + c]);
+                }
             }
             m = mnew;
         }
@@ -357,22 +430,22 @@ __device__ __forceinline__ void decode_split_item(const T *q, const T *kc, const
                 __syncwarp();   // every lane's copies of this tile have landed
                 const int jb = s_lo + tile * TILE;
                 const unsigned char *base = ring + (size_t)slot * 4096U;
+                bool valid[2];
+                uint4 k0[2], k1[2], v0[2], v1[2];
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    if (u == 1 && jb + KPW >= s_hi) break;   // warp-uniform: the second group lies past the split
                     const int kl = u * KPW + kg;
-                    const bool valid = key_valid(jb + kl);
-                    gdb_vec8<T> k0, k1, v0, v1;
-                    if (valid) {
+                    valid[u] = key_valid(jb + kl);
+                    if (valid[u]) {
                         const unsigned char *row = base + kl * 128;
                         const int p0 = ((sub * 2) ^ (kl & 7)) << 4, p1 = ((sub * 2 + 1) ^ (kl & 7)) << 4;
-                        k0.raw = *reinterpret_cast<const uint4 *>(row + p0);
-                        k1.raw = *reinterpret_cast<const uint4 *>(row + p1);
-                        v0.raw = *reinterpret_cast<const uint4 *>(row + 2048 + p0);
-                        v1.raw = *reinterpret_cast<const uint4 *>(row + 2048 + p1);
+                        k0[u] = *reinterpret_cast<const uint4 *>(row + p0);
+                        k1[u] = *reinterpret_cast<const uint4 *>(row + p1);
+                        v0[u] = *reinterpret_cast<const uint4 *>(row + 2048 + p0);
+                        v1[u] = *reinterpret_cast<const uint4 *>(row + 2048 + p1);
                     }
-                    fold(valid, k0, k1, v0, v1);
                 }
+                fold2(valid, k0, k1, v0, v1);
                 __syncwarp();   // every lane is done with the slot before it is refilled
                 issue(tile + 3, slot);
                 slot = slot == 2 ? 0 : slot + 1;
@@ -383,7 +456,7 @@ __device__ __forceinline__ void decode_split_item(const T *q, const T *kc, const
 #pragma unroll
             for (int c = 0; c < 16; ++c) qr[c] = gdb_io<T>::ld(q, qb + c) * p.scale;
             for (int jb = s_lo; jb < s_hi; jb += TILE) {
-                gdb_vec8<T> k0[2], k1[2], v0[2], v1[2];
+                uint4 k0[2], k1[2], v0[2], v1[2];
                 bool valid[2];
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
@@ -391,17 +464,13 @@ __device__ __forceinline__ void decode_split_item(const T *q, const T *kc, const
                     valid[u] = key_valid(j);
                     if (valid[u]) {
                         const size_t kb = key_base(j);
-                        k0[u].raw = *reinterpret_cast<const uint4 *>(kc + kb);
-                        k1[u].raw = *reinterpret_cast<const uint4 *>(kc + kb + 8);
-                        v0[u].raw = *reinterpret_cast<const uint4 *>(vc + kb);
-                        v1[u].raw = *reinterpret_cast<const uint4 *>(vc + kb + 8);
+                        k0[u] = *reinterpret_cast<const uint4 *>(kc + kb);
+                        k1[u] = *reinterpret_cast<const uint4 *>(kc + kb + 8);
+                        v0[u] = *reinterpret_cast<const uint4 *>(vc + kb);
+                        v1[u] = *reinterpret_cast<const uint4 *>(vc + kb + 8);
                     }
                 }
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    if (u == 1 && jb + KPW >= s_hi) break;   // warp-uniform: the second group lies past the split
-                    fold(valid[u], k0[u], k1[u], v0[u], v1[u]);
-                }
+                fold2(valid, k0, k1, v0, v1);
             }
         }
     }
@@ -490,7 +559,7 @@ struct gdb_mega_args {
     float eps, scale, softcap;
     gdb_dec::rope_params rope;
     const float *rope_table;
-    void *xbuf, *resid, *q, *attn, *proj, *act, *mlp, *logits;   // activations of one step, [B, D | F | V]
+    void *xbuf, *resid, *q, *attn, *act, *logits;                // activations of one step, [B, D | F | V]
     unsigned *sync;                                               // [0] barrier counter (bit 31: abort)
     int32_t *tokens, *positions, *out_tokens, *step_counter;
     int *err_flag;

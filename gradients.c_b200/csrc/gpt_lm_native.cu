@@ -1039,9 +1039,7 @@ gd_status decode_steps_persistent(gd_backend *be, const gdb200_gpt_spec *s, cons
     a.resid = act(D);
     a.q = act(D);
     a.attn = act(D);
-    a.proj = act(D);
     a.act = act(F);
-    a.mlp = act(D);
     a.logits = act(V);
     Ten sync = c.alloc(GDB_DTYPE_I32, {4});
     if (c.st != GD_OK) {
