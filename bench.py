@@ -67,6 +67,7 @@ def parse_args():
                          "defaults (F1024, tied head, dropout 0.05, window 256); scaled = BF16 d2048 L24 H16x128 F5632 V32768 ctx2048, "
                          "32 sequences of U[256,2048] per GPU")
     ap.add_argument("--linear-shape", default="4096,512,1536", help="M,K,N of --workload linear (default: the C1 configuration)")
+    ap.add_argument("--decode-tokens", type=int, default=256, help="--workload decode: new tokens per prompt (default 256: positions 256..511; a small value makes a short run for profiling)")
     ap.add_argument("--attention-mode", type=int, default=0, help="0 auto (tcgen05 forward when the shape allows), 1 mma.sync flash kernels only")
     return ap.parse_args()
 
@@ -580,7 +581,7 @@ def measure_decode(args, with_cpu: bool = True) -> dict:
     hp = g.init_params(cfg, seed=0)
     model = g.GptLm(ctx, cfg, hp)
     model.training = False
-    batch, plen, new_tokens, cap = 64, 256, 256, 512
+    batch, plen, new_tokens, cap = 64, 256, max(4, int(getattr(args, "decode_tokens", 256))), 512
     prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(batch, plen)).astype(np.int32)
     native = args.host == "native"
     timing = {}
@@ -607,7 +608,7 @@ def measure_decode(args, with_cpu: bool = True) -> dict:
     bytes_per_step = 2.0 * n_mm + 2.0 * layers * batch * kv_rows * d * 2.0
     res = {"metric": "gpt_lm_kv_decode_tokens_per_s", "unit": "tokens/s", "higher_is_better": True, "dtype": "f16",
            "config": {"workload": f"greedy KV decode, {batch} prompts x {plen}, {new_tokens} new tokens, cache {cap}, gpt_lm baseline model",
-                      "host": "native: device argmax, ids / positions fed back on the device, decode step replayed as a CUDA graph" if native
+                      "host": "native: all decode steps in one persistent cooperative kernel (grid barriers between the phases of a step), device argmax, ids / positions fed back on the device" if native
                       else "python: host argmax and three small uploads per step"},
            "checksum": int(out.astype(np.int64).sum()), "gpu_launches": launches}
     if native and timing:
