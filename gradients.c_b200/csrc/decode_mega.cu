@@ -336,18 +336,17 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
             // next unit (the other weight stage) while this one is multiplied
             uint4 wraw[2] = {make_uint4(0U, 0U, 0U, 0U), make_uint4(0U, 0U, 0U, 0U)};
             if (first) {
-                // the norm weights first: a load issued behind the 80 KB of copies below would return behind them
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const uint32_t v = (uint32_t)c.lane + 32U * (uint32_t)i;
-                    if (v < (uint32_t)a.D / 8U) wraw[i] = __ldg(reinterpret_cast<const uint4 *>(g.norm_w) + v);
-                }
+                mg_load_w<T, B_KMAJOR>(stage_w(0), g.W, ldw, CH, 0, lo, hi, c.tid);
                 if (PRO == PRO_EMB) {
                     mg_stage_rows<T, true>(stage_a(0), LDA, g.x, g.ids, g.vocab, a.B, a.D, c.tid);
                 } else {
                     mg_stage_rows<T, false>(stage_a(0), LDA, g.x, nullptr, 0U, a.B, a.D, c.tid);
                 }
-                mg_load_w<T, B_KMAJOR>(stage_w(0), g.W, ldw, CH, 0, lo, hi, c.tid);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint32_t v = (uint32_t)c.lane + 32U * (uint32_t)i;
+                    if (v < (uint32_t)a.D / 8U) wraw[i] = __ldg(reinterpret_cast<const uint4 *>(g.norm_w) + v);
+                }
             }
             load_epi(lo, hi);
             mg_commit();
