@@ -11,6 +11,8 @@
 // begin/end scope is observed by the next read exactly as in the reference.
 #include "common.cuh"
 
+#include <atomic>
+
 #include <stdlib.h>
 #include <sys/mman.h>
 
@@ -154,6 +156,20 @@ gd_status gd_backend_create_default(gd_backend **out_backend)
                 be->device, prop.major, prop.minor);
         free(be);
         return GD_ERR_UNSUPPORTED;
+    }
+    {
+        // One device per process: the kernels' one-time set-up (dynamic shared memory limits, occupancy, cluster sizes)
+        // is cached in process-wide flags, and CUDA function attributes are per device. A backend on a second device
+        // would skip that set-up and fail at its first large launch, so it is refused here with a clear message
+        // (data parallelism runs one process per GPU).
+        static std::atomic<int> process_device(-1);
+        int expected = -1;
+        if (!process_device.compare_exchange_strong(expected, be->device) && expected != be->device) {
+            fprintf(stderr, "gd_backend_b200: this process already runs a backend on device %d; device %d needs its own process\n",
+                    expected, be->device);
+            free(be);
+            return GD_ERR_UNSUPPORTED;
+        }
     }
     be->sm_count = prop.multiProcessorCount;
     be->ws_bytes = env_size("GD_CUDA_WORKSPACE_MB", 512U) << 20;
