@@ -326,6 +326,10 @@ gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view 
 gd_status gdb_lm_ce_count_valid(gd_backend *be, const gd_backend_tensor_view *targets, int32_t ignore_index, const gd_backend_tensor_view *counts);
 gd_status gdb_lm_ce_reduce_normalize_global(gd_backend *be, const gd_backend_tensor_view *row_loss, const gd_backend_tensor_view *counts,
                                             const gd_backend_tensor_view *loss, const gd_backend_tensor_view *inv_valid_count);
+gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                                            const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
+                                            const gd_backend_tensor_view *grad_x, bool add_to_dx, const gd_backend_tensor_view *grad_weight,
+                                            const gd_backend_tensor_view *partial, const gd_backend_rms_norm_args *args);
 gd_status gdb_rms_norm_backward_accumulate(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
                                            const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
                                            const gd_backend_tensor_view *grad_accum, const gd_backend_rms_norm_args *args);

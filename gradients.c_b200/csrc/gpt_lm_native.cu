@@ -19,6 +19,7 @@
 
 #include <math.h>
 #include <stdlib.h>
+#include <algorithm>
 #include <utility>
 #include <vector>
 
@@ -210,6 +211,20 @@ Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten 
     gd_backend_rms_norm_args a = rms_args(rows, cols, c.s->rms_eps);
     Ten dx = accum != nullptr ? *accum : c.alloc(x.dt, {rows, cols});
     gd_backend_tensor_view xv = tv(x), wv = tv(w), iv = tv(inv), gv = tv(g), dxv = tv(dx), dwv = tv(dw);
+    {
+        // input and weight gradient from one pass over x and g where the fused kernel takes the shape (GDB200_RMS_BWD_SPLIT=1: two passes)
+        static const bool split = getenv("GDB200_RMS_BWD_SPLIT") != NULL;
+        if (!split && c.st == GD_OK) {
+            const int64_t prow = std::max<int64_t>((int64_t)a.row_blocks, 2 * (int64_t)c.be->sm_count);
+            Ten partial = c.alloc(GDB_DTYPE_F32, {prow, cols});
+            gd_backend_tensor_view pv = tv(partial);
+            gd_status r = gdb_rms_norm_backward_with_weight(c.be, &xv, &wv, &iv, &gv, &dxv, accum != nullptr, &dwv, &pv, &a);
+            if (r != GD_ERR_UNSUPPORTED) {
+                c.ok(r, "rms_norm_backward + weight gradient");
+                return dx;
+            }
+        }
+    }
     if (accum != nullptr) {
         c.ok(gdb_rms_norm_backward_accumulate(c.be, &xv, &wv, &iv, &gv, &dxv, &a), "rms_norm_backward_stats + accumulate");
     } else {

@@ -214,6 +214,110 @@ __global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, cons
     }
 }
 
+// Input gradient AND weight gradient of RMSNorm from one pass over x and g (rms_norm_backward_stats [+ accumulate] and
+// rms_norm_weight_backward_stats in one launch): 16-bit storage, cols <= 512 and a multiple of 8, 16-byte aligned rows.
+// A warp takes rows blockIdx.x * 16 + warp, + gridDim.x * 16, ...; a row's x and g stay in registers between the row sum and
+// the dx pass (the separate kernel reads them twice); the lane also accumulates g * x * inv of its 16 columns over its rows.
+// The warps of a block are summed through shared memory into partial[blockIdx.x, cols] (FP32), and the block that arrives
+// last (ticket) sums the blocks' partials in block order and rounds dw once, so the result does not depend on which block
+// was last. dx is computed exactly as rms_bwd_kernel does.
+constexpr int RBW_WARPS = 16, RBW_MAX_COLS = 512;   // two blocks of 16 warps per SM keep 32 rows (64 KB) in flight
+template <typename T>
+__global__ void __launch_bounds__(RBW_WARPS * 32, 2)
+rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const float *__restrict__ inv_in, const T *__restrict__ g, T *dx,
+                     T *__restrict__ dw, float *__restrict__ partial, unsigned *__restrict__ ticket, size_t rows, size_t cols, bool add_to_dx)
+{
+    gdb_pdl_sync();
+    __shared__ float sh[RBW_WARPS][RBW_MAX_COLS];
+    __shared__ bool last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t vecs = cols / 8U;
+    float dwacc[2][8];
+    gdb_vec8<T> wa[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.0f;
+        const size_t v = (size_t)lane + 32U * (size_t)i;
+        wa[i].raw = v < vecs ? __ldg(reinterpret_cast<const uint4 *>(w) + v) : make_uint4(0U, 0U, 0U, 0U);
+    }
+    for (size_t row = (size_t)blockIdx.x * RBW_WARPS + warp; row < rows; row += (size_t)gridDim.x * RBW_WARPS) {
+        const uint4 *xv = reinterpret_cast<const uint4 *>(x + row * cols), *gv = reinterpret_cast<const uint4 *>(g + row * cols);
+        uint4 *dv = reinterpret_cast<uint4 *>(dx + row * cols);
+        gdb_vec8<T> xa[2], ga[2];
+        float a = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const size_t v = (size_t)lane + 32U * (size_t)i;
+            if (v < vecs) {
+                xa[i].raw = xv[v];
+                ga[i].raw = gv[v];
+            }
+        }
+        const float inv = inv_in[row];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const size_t v = (size_t)lane + 32U * (size_t)i;
+            if (v < vecs) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float xf = xa[i].get(e), gf = ga[i].get(e);
+                    a += gf * wa[i].get(e) * xf;
+                    dwacc[i][e] += gf * xf * inv;
+                }
+            }
+        }
+        a = gdb_warp_sum(a);
+        const float k = inv * inv * inv / (float)cols;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const size_t v = (size_t)lane + 32U * (size_t)i;
+            if (v < vecs) {
+                gdb_vec8<T> o;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    o.set(e, inv * ga[i].get(e) * wa[i].get(e) - xa[i].get(e) * k * a);
+                }
+                if (add_to_dx) {
+                    gdb_vec8<T> da;
+                    da.raw = dv[v];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o.set(e, da.get(e) + o.get(e));
+                }
+                dv[v] = o.raw;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const size_t v = (size_t)lane + 32U * (size_t)i;
+        if (v < vecs) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sh[warp][v * 8U + e] = dwacc[i][e];
+        }
+    }
+    __syncthreads();
+    for (size_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        float s = 0.0f;
+#pragma unroll
+        for (int wi = 0; wi < RBW_WARPS; ++wi) s += sh[wi][c];
+        partial[(size_t)blockIdx.x * cols + c] = s;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(ticket, 1U) == gridDim.x - 1U;
+    __syncthreads();
+    if (last) {
+        __threadfence();
+        for (size_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            float s = 0.0f;
+            for (unsigned b = 0; b < gridDim.x; ++b) s += __ldcg(&partial[(size_t)b * cols + c]);
+            gdb_io<T>::st(dw, c, s);
+        }
+        if (threadIdx.x == 0) *ticket = 0U;
+    }
+}
+
 // Stage 1 of dw: block (cb, rb) sums rows [rb*chunk, rb*chunk+chunk) of columns
 // [cb*256, cb*256+256) into partial[rb, c]; thread t owns column cb*256+t, 4 rows in flight.
 template <typename T>
@@ -476,6 +580,58 @@ gd_status gdb_rms_norm_backward_accumulate(gd_backend *be, const gd_backend_tens
                                            const gd_backend_tensor_view *grad_accum, const gd_backend_rms_norm_args *args)
 {
     return bwd_dispatch<true>(be, x, weight, inv_rms, grad_out, grad_accum, args, true);
+}
+
+// rms_norm_backward_stats (+ accumulate into grad_x when add_to_dx) and rms_norm_weight_backward_stats in one launch.
+// `partial`: F32 scratch of at least row_blocks * cols elements. GD_ERR_UNSUPPORTED when the fused kernel does not take
+// the shape (the caller then issues the two entries).
+gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                                            const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
+                                            const gd_backend_tensor_view *grad_x, bool add_to_dx, const gd_backend_tensor_view *grad_weight,
+                                            const gd_backend_tensor_view *partial, const gd_backend_rms_norm_args *a)
+{
+    if (be == NULL || x == NULL || weight == NULL || inv_rms == NULL || grad_out == NULL || grad_x == NULL || grad_weight == NULL ||
+        partial == NULL || !args_ok(a) || a->row_blocks == 0U || x->count != a->rows * a->cols || grad_out->count != x->count ||
+        grad_x->count != x->count || weight->count != a->cols || grad_weight->count != a->cols || inv_rms->count != a->rows ||
+        partial->count < a->row_blocks * a->cols) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = x->dtype;
+    if ((dt != GDB_DTYPE_F16 && dt != GDB_DTYPE_BF16) || a->cols > (size_t)RBW_MAX_COLS || (a->cols % 8U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    const void *xp = gdb_tv_ptr(x, dt), *wp = gdb_tv_ptr(weight, dt), *gp = gdb_tv_ptr(grad_out, dt);
+    void *dp = gdb_tv_ptr(grad_x, dt), *dwp = gdb_tv_ptr(grad_weight, dt);
+    const float *ip = (const float *)gdb_tv_ptr(inv_rms, GDB_DTYPE_F32);
+    float *pp = (float *)gdb_tv_ptr(partial, GDB_DTYPE_F32);
+    if (xp == NULL || wp == NULL || gp == NULL || dp == NULL || dwp == NULL || ip == NULL || pp == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if ((((uintptr_t)xp | (uintptr_t)wp | (uintptr_t)gp | (uintptr_t)dp) % 16U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    size_t blocks = (size_t)be->sm_count * 2U;
+    const size_t need = (a->rows + RBW_WARPS - 1U) / RBW_WARPS, room = partial->count / a->cols;
+    if (blocks > need) blocks = need;
+    if (blocks > room) blocks = room;   // one FP32 row of partial sums per block
+    unsigned *ticket = gdb_tickets(be);
+    if (dt == GDB_DTYPE_F16) {
+        gdb_launch(rms_bwd_wgrad_kernel<__half>, (unsigned)blocks, RBW_WARPS * 32, 0, be->stream, (const __half *)xp, (const __half *)wp, ip, (const __half *)gp,
+                   (__half *)dp, (__half *)dwp, pp, ticket, a->rows, a->cols, add_to_dx);
+    } else {
+        gdb_launch(rms_bwd_wgrad_kernel<__nv_bfloat16>, (unsigned)blocks, RBW_WARPS * 32, 0, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip,
+                   (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, (__nv_bfloat16 *)dwp, pp, ticket, a->rows, a->cols, add_to_dx);
+    }
+    return gdb_launched(be, "rms_norm_backward + weight gradient");
+}
+
+extern "C" gd_status gdb200_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                                                          const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
+                                                          const gd_backend_tensor_view *grad_x, int32_t accumulate,
+                                                          const gd_backend_tensor_view *grad_weight, const gd_backend_tensor_view *partial,
+                                                          const gd_backend_rms_norm_args *args)
+{
+    return gdb_rms_norm_backward_with_weight(be, x, weight, inv_rms, grad_out, grad_x, accumulate != 0, grad_weight, partial, args);
 }
 
 gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *residual, const gd_backend_tensor_view *x,

@@ -422,6 +422,17 @@ gd_status gdb200_matmul_nt_bias_swiglu_both(gd_backend *backend, const gd_backen
 gd_status gdb200_matmul_nt_swiglu_backward(gd_backend *backend, const gd_backend_matrix_view *g, const gd_backend_matrix_view *w,
                                            const gd_backend_matrix_view *up_gate, const gd_backend_matrix_view *d_up_gate);
 
+/* gd_backend_rms_norm_backward_stats and gd_backend_rms_norm_weight_backward_stats (src/core/backend.h, the two calls of
+ * src/ops/rms_norm/core_rms_norm_bwd.c) from ONE pass over x and grad_out: grad_x exactly as the first entry computes it
+ * (with accumulate != 0 it is added into grad_x: round, add, round, as gd_backend_accumulate after the entry would), and
+ * grad_weight = sum over rows of grad_out * x * inv_rms through FP32 partials [row_blocks, cols] summed in a fixed order.
+ * 16-bit storage, cols <= 512 and a multiple of 8; GD_ERR_UNSUPPORTED otherwise (the caller then makes the two calls). */
+gd_status gdb200_rms_norm_backward_with_weight(gd_backend *backend, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                                               const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
+                                               const gd_backend_tensor_view *grad_x, int32_t accumulate,
+                                               const gd_backend_tensor_view *grad_weight, const gd_backend_tensor_view *partial,
+                                               const gd_backend_rms_norm_args *args);
+
 /* gd_backend_sdpa_varlen_backward (src/core/backend.h:699-709) for a caller that still holds the forward output `out`
  * [N, Hq, Dh] and can lend FP32 scratch `dq_accum` of q's element count: D = rowsum(grad_out o out) replaces the
  * query-stationary recomputation, and dK, dV and dQ come from one key-stationary pass (dQ accumulated in dq_accum, then

@@ -128,6 +128,48 @@ def test_rms_norm(step, dtype, rows, cols):
     close(host(dx2), wdx, dtype)
 
 
+@pytest.mark.parametrize("dtype,rows,cols,accumulate", [(F16, 18432, 512, 0), (F16, 777, 512, 1), (BF16, 130, 256, 0), (F16, 9, 24, 1)])
+def test_rms_norm_backward_with_weight_gradient_in_one_pass(step, dtype, rows, cols, accumulate):
+    """gdb200_rms_norm_backward_with_weight against the two entries it stands for: grad_x bit for bit (also when it is
+    accumulated into an existing gradient), grad_weight to FP32 summation order, both against the oracle."""
+    ctx, lib = step, step.lib
+    x = rnd_np((rng(20).standard_normal((rows, cols)) * 0.5).astype(np.float32), dtype)
+    w = rnd_np((rng(21).standard_normal(cols) * 0.25 + 1).astype(np.float32), dtype)
+    g = rnd_np((rng(22).standard_normal((rows, cols)) * 0.25).astype(np.float32), dtype)
+    base = rnd_np((rng(23).standard_normal((rows, cols)) * 0.1).astype(np.float32), dtype)
+    xt, wt, gt = dev(ctx, x, dtype), dev(ctx, w, dtype), dev(ctx, g, dtype)
+    args = ops._rms_args(rows, cols, 1e-5)
+    inv = ctx.scratch_empty(F32, (rows,))
+    ctx.check(lib.gd_backend_rms_norm_inv(ctx.backend, byref(xt.tv()), byref(inv.tv()), byref(args)), "rms_inv")
+    partial = ctx.scratch_empty(F32, (int(args.row_blocks), cols))
+    # the two entries (+ accumulate)
+    dx0, dw0 = ctx.scratch_empty(dtype, (rows, cols)), ctx.scratch_empty(dtype, (cols,))
+    ctx.check(lib.gd_backend_rms_norm_backward_stats(ctx.backend, byref(xt.tv()), byref(wt.tv()), byref(inv.tv()), byref(gt.tv()), byref(dx0.tv()), byref(args)), "bwd")
+    ctx.check(lib.gd_backend_rms_norm_weight_backward_stats(ctx.backend, byref(xt.tv()), byref(inv.tv()), byref(gt.tv()), byref(dw0.tv()), byref(partial.tv()), byref(args)), "wbwd")
+    want_dx = host(dx0)
+    if accumulate:
+        acc0 = dev(ctx, base, dtype)
+        ctx.check(lib.gd_backend_accumulate(ctx.backend, acc0.buffer, acc0.offset, dx0.buffer, dx0.offset, rows * cols, dtype), "accumulate")
+        want_dx = host(acc0)
+    # one pass
+    dx1 = dev(ctx, base, dtype) if accumulate else ctx.scratch_empty(dtype, (rows, cols))
+    dw1 = ctx.scratch_empty(dtype, (cols,))
+    st = lib.gdb200_rms_norm_backward_with_weight(ctx.backend, byref(xt.tv()), byref(wt.tv()), byref(inv.tv()), byref(gt.tv()), byref(dx1.tv()),
+                                                  accumulate, byref(dw1.tv()), byref(partial.tv()), byref(args))
+    if cols > 512 or cols % 8:
+        assert st == abi.GD_ERR_UNSUPPORTED
+        return
+    ctx.check(st, "rms backward + weight gradient")
+    bits = np.uint16 if dtype != F32 else np.uint32
+    assert np.array_equal(host(dx1).astype(np.float32).view(np.uint32), want_dx.astype(np.float32).view(np.uint32))
+    winv = O.rms_norm_forward(t32(x), t32(w), 1e-5, storage_name(dtype))[1]
+    wdx, wdw = O.rms_norm_backward(t32(x), t32(w), winv, t32(g), storage_name(dtype))
+    if not accumulate:
+        close(host(dx1), wdx, dtype)
+    close(host(dw1), wdw, dtype, scale=8 * max(1.0, math.sqrt(rows / 777)))
+    close(host(dw1), host(dw0), dtype, scale=2 * max(1.0, math.sqrt(rows / 777)))
+
+
 # ------------------------------------------------------------------ GEMM family
 GEMM_SHAPES = [(5, 3, 7), (64, 128, 96), (300, 512, 1536), (257, 520, 130),
                # decode-sized M: the K-split mma.sync kernel
