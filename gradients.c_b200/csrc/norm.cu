@@ -216,59 +216,88 @@ __global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, cons
 
 // Input gradient AND weight gradient of RMSNorm from one pass over x and g (rms_norm_backward_stats [+ accumulate] and
 // rms_norm_weight_backward_stats in one launch): 16-bit storage, cols <= 512 and a multiple of 8, 16-byte aligned rows.
-// A warp takes rows blockIdx.x * 16 + warp, + gridDim.x * 16, ...; a row's x and g stay in registers between the row sum and
-// the dx pass (the separate kernel reads them twice); the lane also accumulates g * x * inv of its 16 columns over its rows.
-// The warps of a block are summed through shared memory into partial[blockIdx.x, cols] (FP32), and the block that arrives
-// last (ticket) sums the blocks' partials in block order and rounds dw once, so the result does not depend on which block
-// was last. dx is computed exactly as rms_bwd_kernel does.
-constexpr int RBW_WARPS = 16, RBW_MAX_COLS = 512;   // two blocks of 16 warps per SM keep 32 rows (64 KB) in flight
+// One block of 16 warps per SM. A warp takes rows blockIdx.x * 16 + warp, + gridDim.x * 16, ... and streams them through
+// a private shared-memory ring three rows deep: every lane copies its own 16-byte pieces of x, g (and of dx when the
+// gradient is accumulated) with cp.async and reads them back itself, so two rows per warp (96 KB per SM) are in flight
+// while one is consumed, with no register cost and no synchronisation between lanes. The lane accumulates g * x * inv of
+// its 16 columns over its rows; the warps of a block are summed through shared memory into partial[blockIdx.x, cols]
+// (FP32), and the block that arrives last (ticket) sums the blocks' partials in block order and rounds dw once, so the
+// result does not depend on which block was last. dx is computed exactly as rms_bwd_kernel does.
+constexpr int RBW_WARPS = 16, RBW_MAX_COLS = 512, RBW_DEPTH = 3;
+constexpr int RBW_ROW_BYTES = RBW_MAX_COLS * 2;                          // one 16-bit row
+constexpr int RBW_SLOT_BYTES = 3 * RBW_ROW_BYTES;                        // x, g, dx
+constexpr int RBW_SMEM = RBW_WARPS * RBW_DEPTH * RBW_SLOT_BYTES;         // 144 KB; the block reduction reuses it
+static_assert(RBW_SMEM >= (int)sizeof(float) * RBW_WARPS * RBW_MAX_COLS, "the reduction buffer aliases the rings");
 template <typename T>
-__global__ void __launch_bounds__(RBW_WARPS * 32, 2)
+__global__ void __launch_bounds__(RBW_WARPS * 32, 1)
 rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const float *__restrict__ inv_in, const T *__restrict__ g, T *dx,
                      T *__restrict__ dw, float *__restrict__ partial, unsigned *__restrict__ ticket, size_t rows, size_t cols, bool add_to_dx)
 {
     gdb_pdl_sync();
-    __shared__ float sh[RBW_WARPS][RBW_MAX_COLS];
+    extern __shared__ __align__(16) unsigned char rbw_sm[];
     __shared__ bool last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t vecs = cols / 8U;
-    float dwacc[2][8];
-    gdb_vec8<T> wa[2];
+    unsigned char *ring = rbw_sm + (size_t)warp * RBW_DEPTH * RBW_SLOT_BYTES;
+    float dwacc[2][8], wf[2][8];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.0f;
         const size_t v = (size_t)lane + 32U * (size_t)i;
-        wa[i].raw = v < vecs ? __ldg(reinterpret_cast<const uint4 *>(w) + v) : make_uint4(0U, 0U, 0U, 0U);
-    }
-    for (size_t row = (size_t)blockIdx.x * RBW_WARPS + warp; row < rows; row += (size_t)gridDim.x * RBW_WARPS) {
-        const uint4 *xv = reinterpret_cast<const uint4 *>(x + row * cols), *gv = reinterpret_cast<const uint4 *>(g + row * cols);
-        uint4 *dv = reinterpret_cast<uint4 *>(dx + row * cols);
-        gdb_vec8<T> xa[2], ga[2];
-        float a = 0.0f;
+        gdb_vec8<T> wa;
+        wa.raw = v < vecs ? __ldg(reinterpret_cast<const uint4 *>(w) + v) : make_uint4(0U, 0U, 0U, 0U);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const size_t v = (size_t)lane + 32U * (size_t)i;
-            if (v < vecs) {
-                xa[i].raw = xv[v];
-                ga[i].raw = gv[v];
+        for (int e = 0; e < 8; ++e) wf[i][e] = wa.get(e);
+    }
+    const size_t row0 = (size_t)blockIdx.x * RBW_WARPS + warp, stride = (size_t)gridDim.x * RBW_WARPS;
+    auto cp16 = [](void *dst, const void *src) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+    };
+    auto issue = [&](size_t row, int slot) {
+        if (row < rows) {
+            unsigned char *base = ring + (size_t)slot * RBW_SLOT_BYTES;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const size_t v = (size_t)lane + 32U * (size_t)i;
+                if (v < vecs) {
+                    cp16(base + v * 16U, reinterpret_cast<const uint4 *>(x + row * cols) + v);
+                    cp16(base + RBW_ROW_BYTES + v * 16U, reinterpret_cast<const uint4 *>(g + row * cols) + v);
+                    if (add_to_dx) cp16(base + 2 * RBW_ROW_BYTES + v * 16U, reinterpret_cast<const uint4 *>(dx + row * cols) + v);
+                }
             }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    issue(row0, 0);
+    issue(row0 + stride, 1);
+    int slot = 0;
+    for (size_t row = row0; row < rows; row += stride) {
+        issue(row + 2U * stride, slot == 0 ? 2 : slot - 1);   // the slot consumed one iteration ago
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        const unsigned char *base = ring + (size_t)slot * RBW_SLOT_BYTES;
+        float xf[2][8], gf[2][8];   // x and g of the lane's 16 columns
+        float a = 0.0f;
         const float inv = inv_in[row];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const size_t v = (size_t)lane + 32U * (size_t)i;
             if (v < vecs) {
+                gdb_vec8<T> xa, ga;
+                xa.raw = *reinterpret_cast<const uint4 *>(base + v * 16U);
+                ga.raw = *reinterpret_cast<const uint4 *>(base + RBW_ROW_BYTES + v * 16U);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const float xf = xa[i].get(e), gf = ga[i].get(e);
-                    a += gf * wa[i].get(e) * xf;
-                    dwacc[i][e] += gf * xf * inv;
+                    xf[i][e] = xa.get(e);
+                    gf[i][e] = ga.get(e);
+                    a += gf[i][e] * wf[i][e] * xf[i][e];
+                    dwacc[i][e] += gf[i][e] * xf[i][e] * inv;
                 }
             }
         }
         a = gdb_warp_sum(a);
         const float k = inv * inv * inv / (float)cols;
+        uint4 *dv = reinterpret_cast<uint4 *>(dx + row * cols);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const size_t v = (size_t)lane + 32U * (size_t)i;
@@ -276,18 +305,23 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
                 gdb_vec8<T> o;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    o.set(e, inv * ga[i].get(e) * wa[i].get(e) - xa[i].get(e) * k * a);
+                    o.set(e, inv * gf[i][e] * wf[i][e] - xf[i][e] * k * a);
                 }
                 if (add_to_dx) {
+                    // dx += rounded gradient, rounded again: rms_norm_backward followed by gd_backend_accumulate, in place
                     gdb_vec8<T> da;
-                    da.raw = dv[v];
+                    da.raw = *reinterpret_cast<const uint4 *>(base + 2 * RBW_ROW_BYTES + v * 16U);
 #pragma unroll
                     for (int e = 0; e < 8; ++e) o.set(e, da.get(e) + o.get(e));
                 }
                 dv[v] = o.raw;
             }
         }
+        slot = slot == RBW_DEPTH - 1 ? 0 : slot + 1;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();   // every warp is done with its ring: the reduction buffer reuses the memory
+    float(*sh)[RBW_MAX_COLS] = reinterpret_cast<float(*)[RBW_MAX_COLS]>(rbw_sm);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const size_t v = (size_t)lane + 32U * (size_t)i;
@@ -311,7 +345,15 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
         __threadfence();
         for (size_t c = threadIdx.x; c < cols; c += blockDim.x) {
             float s = 0.0f;
-            for (unsigned b = 0; b < gridDim.x; ++b) s += __ldcg(&partial[(size_t)b * cols + c]);
+            unsigned b = 0;
+            for (; b + 8U <= gridDim.x; b += 8U) {   // eight loads in flight, summed in block order
+                float t[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) t[u] = __ldcg(&partial[(size_t)(b + u) * cols + c]);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) s += t[u];
+            }
+            for (; b < gridDim.x; ++b) s += __ldcg(&partial[(size_t)b * cols + c]);
             gdb_io<T>::st(dw, c, s);
         }
         if (threadIdx.x == 0) *ticket = 0U;
@@ -610,16 +652,25 @@ gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_ten
     if ((((uintptr_t)xp | (uintptr_t)wp | (uintptr_t)gp | (uintptr_t)dp) % 16U) != 0U) {
         return GD_ERR_UNSUPPORTED;
     }
-    size_t blocks = (size_t)be->sm_count * 2U;
+    size_t blocks = (size_t)be->sm_count;   // one block (144 KB of rings) per SM
     const size_t need = (a->rows + RBW_WARPS - 1U) / RBW_WARPS, room = partial->count / a->cols;
     if (blocks > need) blocks = need;
     if (blocks > room) blocks = room;   // one FP32 row of partial sums per block
     unsigned *ticket = gdb_tickets(be);
+    {
+        static bool configured = false;   // one device per process
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(rms_bwd_wgrad_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, RBW_SMEM);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(rms_bwd_wgrad_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, RBW_SMEM);
+            if (e != cudaSuccess) return gdb_fail(be, e, "rms_norm backward + weight gradient: shared memory attribute");
+            configured = true;
+        }
+    }
     if (dt == GDB_DTYPE_F16) {
-        gdb_launch(rms_bwd_wgrad_kernel<__half>, (unsigned)blocks, RBW_WARPS * 32, 0, be->stream, (const __half *)xp, (const __half *)wp, ip, (const __half *)gp,
+        gdb_launch(rms_bwd_wgrad_kernel<__half>, (unsigned)blocks, RBW_WARPS * 32, RBW_SMEM, be->stream, (const __half *)xp, (const __half *)wp, ip, (const __half *)gp,
                    (__half *)dp, (__half *)dwp, pp, ticket, a->rows, a->cols, add_to_dx);
     } else {
-        gdb_launch(rms_bwd_wgrad_kernel<__nv_bfloat16>, (unsigned)blocks, RBW_WARPS * 32, 0, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip,
+        gdb_launch(rms_bwd_wgrad_kernel<__nv_bfloat16>, (unsigned)blocks, RBW_WARPS * 32, RBW_SMEM, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip,
                    (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, (__nv_bfloat16 *)dwp, pp, ticket, a->rows, a->cols, add_to_dx);
     }
     return gdb_launched(be, "rms_norm_backward + weight gradient");
