@@ -25,6 +25,7 @@
 // Buffers written inside the kernel are read with plain or L2 loads after a barrier, never through the read-only path.
 #include "common.cuh"
 #include "decode_parts.cuh"
+#include "tcgen05.cuh"   // cluster rank, mapa, cluster barrier
 
 #include <stdlib.h>
 
@@ -49,7 +50,7 @@ __host__ __device__ inline mg_layout mg_layout_for(uint32_t ch_max)
     l.red_off = 2U * l.stage_bytes;
     l.ot_off = l.red_off + (uint32_t)SK_RED_BYTES;
     l.epi_off = l.ot_off + (uint32_t)(SK_ROWS * MG_OT_LD * sizeof(float));
-    l.total = l.epi_off + MG_EPI_BYTES;
+    l.total = l.epi_off + 2U * MG_EPI_BYTES;
     const uint32_t attn = MG_WARPS * MG_RING_BYTES + MG_WARPS * (2U + 64U) * (uint32_t)sizeof(float);   // the attention phase's rings and partials alias the stages
     if (l.total < attn) l.total = attn;
     return l;
@@ -141,11 +142,12 @@ template <> struct mg_nan_pair<__nv_bfloat16> { static constexpr unsigned word =
 // round(x * w * rsqrt(mean(x^2) + eps)) in the per-lane order of rms_fwd_kernel (lane takes the 8-element vectors lane,
 // lane + 32), one warp per row, the warp's four rows interleaved.
 template <typename T, bool GATHER>
-__device__ __forceinline__ void mg_stage_rows(T *As, uint32_t LDA, const T *x, const int32_t *ids, uint32_t vocab, int B, int D, int tid)
+__device__ __forceinline__ void mg_stage_rows(T *As, uint32_t LDA, const T *x, const int32_t *ids, uint32_t vocab, int B, int D, int tid,
+                                              uint32_t row0, uint32_t nrows)
 {
     const uint32_t vecs = (uint32_t)D / 8U;
-    for (uint32_t i = tid; i < SK_ROWS * vecs; i += MG_THREADS) {
-        const uint32_t r = i / vecs, v = i % vecs;
+    for (uint32_t i = tid; i < nrows * vecs; i += MG_THREADS) {
+        const uint32_t r = row0 + i / vecs, v = i % vecs;
         T *dst = As + (size_t)r * LDA + v * 8U;
         if (GATHER) {
             const int id = (int)r < B ? ids[r] : 0;
@@ -162,15 +164,20 @@ __device__ __forceinline__ void mg_stage_rows(T *As, uint32_t LDA, const T *x, c
 }
 
 // `wraw`: the lane's two vectors of the norm weight, loaded by the caller before it waited for the rows.
+// The two CTAs of a cluster share the work: this CTA normalises rows row0 .. row0 + 31 (staged in its own tile) and writes
+// the result into its own tile and, through distributed shared memory, into the same place of its peer's tile
+// (`peer_delta` = the peer's shared-memory window minus this CTA's, as a shared::cluster address difference); rows at
+// or beyond B are written as zeros. The caller's cluster barrier makes both halves visible to both CTAs.
 template <typename T>
-__device__ __forceinline__ void mg_norm_rows(T *As, uint32_t LDA, const uint4 (&wraw)[2], int B, int D, float eps, int warp, int lane)
+__device__ __forceinline__ void mg_norm_rows(T *As, uint32_t LDA, const uint4 (&wraw)[2], int B, int D, float eps, int warp, int lane,
+                                             uint32_t row0, uint32_t peer_rank)
 {
-    constexpr int RPW = SK_ROWS / MG_WARPS;   // rows per warp
-    const uint32_t vecs = (uint32_t)D / 8U;   // at most 64 (D <= 512): two vectors per lane
+    constexpr int RPW = (SK_ROWS / 2) / MG_WARPS;   // rows per warp: 32 rows per CTA of the pair
+    const uint32_t vecs = (uint32_t)D / 8U;         // at most 64 (D <= 512): two vectors per lane
     float ss[RPW];
 #pragma unroll
     for (int q = 0; q < RPW; ++q) {
-        const int r = warp + q * MG_WARPS;
+        const int r = (int)row0 + warp + q * MG_WARPS;
         ss[q] = 0.0f;
         if (r < B) {
 #pragma unroll
@@ -207,22 +214,25 @@ __device__ __forceinline__ void mg_norm_rows(T *As, uint32_t LDA, const uint4 (&
     }
 #pragma unroll
     for (int q = 0; q < RPW; ++q) {
-        const int r = warp + q * MG_WARPS;
-        if (r >= B) continue;
-        const float inv = rsqrtf(ss[q] / (float)(size_t)D + eps);
+        const int r = (int)row0 + warp + q * MG_WARPS;
+        const float inv = r < B ? rsqrtf(ss[q] / (float)(size_t)D + eps) : 0.0f;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const uint32_t v = (uint32_t)lane + 32U * (uint32_t)i;
             if (v < vecs) {
                 T *p = As + (size_t)r * LDA + v * 8U;
-                const uint4 a = *reinterpret_cast<const uint4 *>(p);
-                const float2 x0 = pack2<T>::up(a.x), x1 = pack2<T>::up(a.y), x2 = pack2<T>::up(a.z), x3 = pack2<T>::up(a.w);
-                uint4 o;
-                o.x = pack2<T>::down(x0.x * wf[i][0] * inv, x0.y * wf[i][1] * inv);
-                o.y = pack2<T>::down(x1.x * wf[i][2] * inv, x1.y * wf[i][3] * inv);
-                o.z = pack2<T>::down(x2.x * wf[i][4] * inv, x2.y * wf[i][5] * inv);
-                o.w = pack2<T>::down(x3.x * wf[i][6] * inv, x3.y * wf[i][7] * inv);
+                uint4 o = make_uint4(0U, 0U, 0U, 0U);
+                if (r < B) {
+                    const uint4 a = *reinterpret_cast<const uint4 *>(p);
+                    const float2 x0 = pack2<T>::up(a.x), x1 = pack2<T>::up(a.y), x2 = pack2<T>::up(a.z), x3 = pack2<T>::up(a.w);
+                    o.x = pack2<T>::down(x0.x * wf[i][0] * inv, x0.y * wf[i][1] * inv);
+                    o.y = pack2<T>::down(x1.x * wf[i][2] * inv, x1.y * wf[i][3] * inv);
+                    o.z = pack2<T>::down(x2.x * wf[i][4] * inv, x2.y * wf[i][5] * inv);
+                    o.w = pack2<T>::down(x3.x * wf[i][6] * inv, x3.y * wf[i][7] * inv);
+                }
                 *reinterpret_cast<uint4 *>(p) = o;
+                const uint32_t remote = gdb_t5::mapa_shared(sk_smem(p), peer_rank);
+                asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
             }
         }
     }
@@ -265,7 +275,9 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
     } else {
         nunits = g.N / 16U;
     }
-    if (blockIdx.x >= nunits) return;
+    // Resident-A phases run on CTA pairs (clusters of two): a pair takes part when either of its CTAs has a unit, because
+    // each CTA normalises half of the rows for both.
+    if (PRO == PRO_GLOBAL ? blockIdx.x >= nunits : (blockIdx.x & ~1U) >= nunits) return;
     const uint32_t CH = g.CH, LDA = CH + 8U, LDW = B_KMAJOR ? CH + 8U : 24U, a_bytes = SK_ROWS * LDA * 2U;
     const uint32_t n_chunks = g.K / CH, kw = CH / SK_WARPS;
     const uint32_t M = (uint32_t)a.B;
@@ -273,7 +285,6 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
     const size_t ldw = B_KMAJOR ? (size_t)g.K : (size_t)g.N;
     sk_red_t red = reinterpret_cast<sk_red_t>(c.sm + c.lay.red_off);
     float(*ot)[MG_OT_LD] = reinterpret_cast<float(*)[MG_OT_LD]>(c.sm + c.lay.ot_off);
-    T *sm_bias = reinterpret_cast<T *>(c.sm + c.lay.epi_off), *sm_res = reinterpret_cast<T *>(c.sm + c.lay.epi_off + 64U);
     auto stage_a = [&](uint32_t st) { return reinterpret_cast<T *>(c.sm + st * c.lay.stage_bytes); };
     auto stage_w = [&](uint32_t st) { return reinterpret_cast<T *>(c.sm + st * c.lay.stage_bytes + a_bytes); };
     auto unit_rows = [&](uint32_t unit, uint32_t *lo, uint32_t *hi) {
@@ -296,7 +307,8 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
         }
     };
     // the unit's epilogue operands ride along with its weights: bias pieces, and for RESID the residual tile
-    auto load_epi = [&](uint32_t lo, uint32_t hi) {
+    auto load_epi = [&](uint32_t lo, uint32_t hi, uint32_t eb) {
+        T *sm_bias = reinterpret_cast<T *>(c.sm + c.lay.epi_off + eb * MG_EPI_BYTES), *sm_res = sm_bias + 32;
         if (g.bias != nullptr && c.tid < 2) sk_cp16(sm_bias + c.tid * 8, g.bias + (c.tid == 0 ? lo : hi), true);
         if (EPI == EPI_RESID) {
             for (uint32_t i = c.tid; i < SK_ROWS * 2U; i += MG_THREADS) {
@@ -317,8 +329,35 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
             }
         }
     };
-    bool first = true;
-    uint32_t wst = 0U;   // weight stage of the current unit (resident-A phases)
+    uint32_t wst = 0U;   // weight stage / epilogue-operand buffer of the current unit (resident-A phases)
+    if (PRO != PRO_GLOBAL) {
+        // The first unit's weights stream in while the prologue runs. This CTA stages and normalises rows
+        // rank * 32 .. + 31 and writes them into both tiles of the pair; the cluster barrier publishes both halves.
+        const uint32_t rank = gdb_t5::cluster_ctarank() & 1U, row0 = rank * (SK_ROWS / 2);
+        uint4 wraw[2] = {make_uint4(0U, 0U, 0U, 0U), make_uint4(0U, 0U, 0U, 0U)};
+        if (blockIdx.x < nunits) {
+            uint32_t lo, hi;
+            unit_rows(blockIdx.x, &lo, &hi);
+            mg_load_w<T, B_KMAJOR>(stage_w(0), g.W, ldw, CH, 0, lo, hi, c.tid);
+            load_epi(lo, hi, 0U);
+        }
+        if (PRO == PRO_EMB) {
+            mg_stage_rows<T, true>(stage_a(0), LDA, g.x, g.ids, g.vocab, a.B, a.D, c.tid, row0, SK_ROWS / 2);
+        } else {
+            mg_stage_rows<T, false>(stage_a(0), LDA, g.x, nullptr, 0U, a.B, a.D, c.tid, row0, SK_ROWS / 2);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t v = (uint32_t)c.lane + 32U * (uint32_t)i;
+            if (v < (uint32_t)a.D / 8U) wraw[i] = __ldg(reinterpret_cast<const uint4 *>(g.norm_w) + v);
+        }
+        mg_commit();
+        mg_wait_all();
+        __syncthreads();
+        mg_norm_rows<T>(stage_a(0), LDA, wraw, a.B, a.D, a.eps, c.warp, c.lane, row0, rank ^ 1U);
+        gdb_t5::cluster_sync_all();   // every thread of both CTAs: the whole normalised tile is in both shared memories
+        if (blockIdx.x >= nunits) return;
+    }
     for (uint32_t unit = blockIdx.x; unit < nunits; unit += gridDim.x) {
         uint32_t lo, hi;
         unit_rows(unit, &lo, &hi);
@@ -332,44 +371,23 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
             }
         };
         if (PRO != PRO_GLOBAL) {
-            // resident A (single chunk): the unit's weights stream in while the prologue runs, and the weights of the CTA's
-            // next unit (the other weight stage) while this one is multiplied
-            uint4 wraw[2] = {make_uint4(0U, 0U, 0U, 0U), make_uint4(0U, 0U, 0U, 0U)};
-            if (first) {
-                mg_load_w<T, B_KMAJOR>(stage_w(0), g.W, ldw, CH, 0, lo, hi, c.tid);
-                if (PRO == PRO_EMB) {
-                    mg_stage_rows<T, true>(stage_a(0), LDA, g.x, g.ids, g.vocab, a.B, a.D, c.tid);
-                } else {
-                    mg_stage_rows<T, false>(stage_a(0), LDA, g.x, nullptr, 0U, a.B, a.D, c.tid);
-                }
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const uint32_t v = (uint32_t)c.lane + 32U * (uint32_t)i;
-                    if (v < (uint32_t)a.D / 8U) wraw[i] = __ldg(reinterpret_cast<const uint4 *>(g.norm_w) + v);
-                }
-            }
-            load_epi(lo, hi);
-            mg_commit();
+            // resident A (single chunk): this unit's weights and epilogue operands are in stage / buffer `wst` (loaded by the
+            // prologue or prefetched during the previous unit); those of the CTA's next unit go to the other one now
             if (unit + gridDim.x < nunits) {
                 uint32_t nlo, nhi;
                 unit_rows(unit + gridDim.x, &nlo, &nhi);
                 mg_load_w<T, B_KMAJOR>(stage_w(wst ^ 1U), g.W, ldw, CH, 0, nlo, nhi, c.tid);
+                load_epi(nlo, nhi, wst ^ 1U);
             }
             mg_commit();
-            mg_wait_one();   // everything but the next unit's weights
+            mg_wait_one();   // everything but the next unit's operands
             __syncthreads();
-            if (first) {
-                mg_norm_rows<T>(stage_a(0), LDA, wraw, a.B, a.D, a.eps, c.warp, c.lane);
-                first = false;
-                __syncthreads();
-            }
             mma(stage_a(0), stage_w(wst));
-            wst ^= 1U;
         } else {
             auto load_chunk = [&](uint32_t ci, uint32_t st) {
                 mg_load_a<T>(stage_a(st), LDA, g.A, (size_t)g.K, CH, (size_t)ci * CH, M, c.tid);
                 mg_load_w<T, B_KMAJOR>(stage_w(st), g.W, ldw, CH, (size_t)ci * CH, lo, hi, c.tid);
-                if (ci == 0U) load_epi(lo, hi);
+                if (ci == 0U) load_epi(lo, hi, 0U);
                 mg_commit();
             };
             load_chunk(0, 0);
@@ -393,7 +411,9 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
             sk_store_partials<2, 2>(red, acc, (int)kslot, c.lane);
         }
         __syncthreads();
-        const T *bias = g.bias != nullptr ? sm_bias : nullptr;   // local columns: 0..7 = lo.., 8..15 = hi..
+        const uint32_t eb = PRO != PRO_GLOBAL ? wst : 0U;
+        const T *sm_bias_u = reinterpret_cast<const T *>(c.sm + c.lay.epi_off + eb * MG_EPI_BYTES), *sm_res_u = sm_bias_u + 32;
+        const T *bias = g.bias != nullptr ? sm_bias_u : nullptr;   // local columns: 0..7 = lo.., 8..15 = hi..
         if (EPI == EPI_SWIGLU) {
             for (int o = c.tid; o < SK_ROWS * (SK_COLS / 2); o += MG_THREADS) {
                 const int r = o / (SK_COLS / 2), cc = o % (SK_COLS / 2);
@@ -413,7 +433,7 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
                 const int r = o / SK_COLS, cc = o % SK_COLS;
                 if ((uint32_t)r >= M) continue;
                 const float y = gdb_io<T>::rnd(sk_bias<T>(sk_sum(red, r, cc), bias, g.bias_mode, (uint32_t)cc));
-                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, gdb_io<T>::ld(sm_res, (size_t)r * SK_COLS + cc) + y);
+                gdb_io<T>::st(g.C, (size_t)r * g.N + lo + cc, gdb_io<T>::ld(sm_res_u, (size_t)r * SK_COLS + cc) + y);
             }
         } else {
             // the rounded linear output of the unit, then the rotation of qkv_split_rope and the append of kv_cache_append
@@ -454,6 +474,7 @@ __device__ __forceinline__ void mg_gemm_phase(mg_ctx &c, const gdb_mega_args &a,
             }
         }
         __syncthreads();   // the weight stage, the reduction buffer and the epilogue operands are reused by the CTA's next unit
+        wst ^= 1U;
     }
 }
 
@@ -640,19 +661,31 @@ gd_status gdb_decode_mega_launch(gd_backend *be, uint32_t dtype, const gdb_mega_
     if (e != cudaSuccess || per_sm < 1) {
         return e != cudaSuccess ? gdb_fail(be, e, "decode step kernel: occupancy") : GD_ERR_UNSUPPORTED;
     }
+    // Cooperative (every CTA resident: the grid barriers need it) and in clusters of two (the CTAs of a pair share the
+    // normalised activation tile through distributed shared memory).
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
-    cfg.gridDim = dim3((unsigned)be->sm_count);
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.gridDim = dim3((unsigned)be->sm_count & ~1U);
     cfg.blockDim = dim3(MG_THREADS);
     cfg.dynamicSmemBytes = lay.total;
     cfg.stream = be->stream;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
+    int clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg);
+    if (e != cudaSuccess || clusters * 2 < (int)cfg.gridDim.x) {
+        (void)cudaGetLastError();
+        return GD_ERR_UNSUPPORTED;   // the pairs cannot all be resident: the caller enqueues one launch per operation
+    }
     e = cudaLaunchKernelEx(&cfg, kern, *a, lay);
-    if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorNotSupported) {
-        (void)cudaGetLastError();   // the grid cannot be co-resident on this device: the caller enqueues one launch per operation
+    if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorNotSupported || e == cudaErrorInvalidValue || e == cudaErrorInvalidConfiguration) {
+        (void)cudaGetLastError();   // this device / driver does not take the launch: the caller enqueues one launch per operation
         return GD_ERR_UNSUPPORTED;
     }
     if (e != cudaSuccess) return gdb_fail(be, e, "decode step kernel: launch");
