@@ -494,7 +494,8 @@ gd_status gdb200_matmul_nt_bias_swiglu_both(gd_backend *be, const gd_backend_mat
         return GD_ERR_INVALID_ARGUMENT;
     }
     cudaSetDevice(be->device);
-    if (be->gemm_mode == 0 || be->gemm_mode == 2) {
+    static const bool unfused = getenv("GDB200_FUSE_SWIGLU_FWD") != NULL && getenv("GDB200_FUSE_SWIGLU_FWD")[0] == '0';   // A/B switch
+    if (!unfused && (be->gemm_mode == 0 || be->gemm_mode == 2)) {
         // counted as the contraction it is (2 M (2F) K FLOP; x, w read, x12 and act written)
         profile_scope scope(be, 2.0 * x->rows * (double)w->rows * x->cols,
                             (double)es * ((double)x->rows * x->cols + (double)w->rows * w->cols + (double)x->rows * w->rows + (double)x->rows * act->cols));
