@@ -213,6 +213,28 @@ def test_persistent_decode_kernel_past_the_cache_capacity_and_bf16():
     assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("d_model,n_heads,mlp_hidden,vocab,batch,window,tied", [
+    (256, 4, 512, 1024, 64, 0, False),     # 2 heads x 8 key ranges per CTA, two K chunks of 256 in the down projection
+    (256, 4, 384, 512, 7, 12, True),       # odd batch: 1 head x 16 key ranges, K chunks of 128, sliding window, tied head
+    (512, 8, 1024, 2048, 33, 0, True),     # the reference-default widths at a batch that leaves rows of the 64-row tile empty
+])
+def test_persistent_decode_kernel_shapes(d_model, n_heads, mlp_hidden, vocab, batch, window, tied):
+    """The persistent decode kernel on other partitions of its work (heads per CTA, key ranges, K chunks, unit counts above
+    and below the number of CTAs): the ids equal the per-operation host loop's, in one launch."""
+    cfg = small_cfg(dropout_p=0.0, d_model=d_model, n_heads=n_heads, mlp_hidden=mlp_hidden, vocab_size=vocab, tied_lm_head=tied,
+                    sdpa_window=window, n_layers=2)
+    hp = g.init_params(cfg, seed=21, residual_scaled=False)
+    prompts = np.random.default_rng(9).integers(0, cfg.vocab_size, size=(batch, 11)).astype(np.int32)
+    timing = {}
+    with pkg.runtime.Context(params_bytes=128 << 20, state_bytes=512 << 20, scratch_bytes=1 << 30) as ctx:
+        model = g.GptLm(ctx, cfg, hp)
+        model.training = False
+        want = g.greedy_generate(model, prompts, new_tokens=12, capacity=48)
+        got = g.greedy_generate_native(model, prompts, new_tokens=12, capacity=48, timing=timing)
+    assert np.array_equal(got, want)
+    assert timing["decode_launches"] <= 2, timing
+
+
 def test_device_argmax_first_maximum_softcap_and_non_finite():
     rng = np.random.default_rng(8)
     x = (rng.standard_normal((37, 2048)) * 3).astype(np.float16)
