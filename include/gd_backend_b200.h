@@ -565,8 +565,12 @@ typedef struct gdb200_gpt_decode_state {
     size_t tokens_offset, positions_offset, out_tokens_offset, step_counter_offset;
     int32_t batch, capacity, max_steps;
 } gdb200_gpt_decode_state;
-/* Enqueues n_steps decode steps without any host synchronisation. With use_graph != 0 the first step
- * runs eagerly, the second is recorded as a CUDA graph and the rest replay it. */
+/* Enqueues n_steps decode steps without any host synchronisation. use_graph == 0: one launch per operation, step after
+ * step. use_graph != 0: where the shapes allow (16-bit storage, at most 64 sequences, head_dim 64, d_model 128 / 256 / 512,
+ * mlp_hidden a multiple of 128, the cos / sin table of the rotation in use) ALL steps run in one persistent cooperative
+ * kernel (one CTA per SM in clusters of two, grid barriers between the phases of a step; a barrier that is not reached within
+ * its bounded wait stores code 398 in the error word and ends the kernel); otherwise the first step runs eagerly, the second is
+ * recorded as a CUDA graph and the rest replay it. The three forms generate the same ids. */
 gd_status gdb200_gpt_decode_steps(gd_backend *backend, const gdb200_gpt_spec *spec, const gdb200_gpt_decode_state *state,
                                   int32_t n_steps, int32_t use_graph, size_t *scratch_used);
 
