@@ -272,13 +272,15 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
     issue(row0, 0);
     issue(row0 + stride, 1);
     int slot = 0;
+    float inv_next = row0 < rows ? inv_in[row0] : 0.0f;   // 1 / rms of the row after this one, loaded a row ahead
     for (size_t row = row0; row < rows; row += stride) {
         issue(row + 2U * stride, slot == 0 ? 2 : slot - 1);   // the slot consumed one iteration ago
+        const float inv = inv_next;
+        if (row + stride < rows) inv_next = inv_in[row + stride];
         asm volatile("cp.async.wait_group 2;" ::: "memory");
         const unsigned char *base = ring + (size_t)slot * RBW_SLOT_BYTES;
         float xf[2][8], gf[2][8];   // x and g of the lane's 16 columns
         float a = 0.0f;
-        const float inv = inv_in[row];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const size_t v = (size_t)lane + 32U * (size_t)i;
