@@ -436,24 +436,67 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
 
     // ---- fused LM cross entropy (chunked over the vocabulary, src/ops/lm_cross_entropy/core_lm_cross_entropy.c:452-675) ----
     const Ten lm_w = c.param(P_LMW, {V, D}), lm_b = c.param(P_LMB, {V});
-    Ten row_loss = c.fill(c.alloc(GDB_DTYPE_F32, {T}), 0U);
-    Ten row_max = c.fill(c.alloc(GDB_DTYPE_F32, {T}), 0xFF800000U);
-    Ten row_inv_sum = c.fill(c.alloc(GDB_DTYPE_F32, {T}), 0U);
-    Ten row_valid = c.fill(c.alloc(GDB_DTYPE_F32, {T}), 0U);
+    Ten row_loss = c.alloc(GDB_DTYPE_F32, {T}), row_max = c.alloc(GDB_DTYPE_F32, {T});
+    Ten row_inv_sum = c.alloc(GDB_DTYPE_F32, {T}), row_valid = c.alloc(GDB_DTYPE_F32, {T});
     Ten inv_valid = c.alloc(GDB_DTYPE_F32, {});
     Ten loss = c.alloc(GDB_DTYPE_F32, {});
     const int64_t chunk = s->lm_ce_chunk > 0 && s->lm_ce_chunk < V ? s->lm_ce_chunk : V;
     const bool single = chunk >= V;
     Ten saved_logits;
     memset(&saved_logits, 0, sizeof(saved_logits));
-    const size_t ce_mark = c.top;
     gd_backend_tensor_view tgv = tv(tgt), rlv = tv(row_loss), rmv = tv(row_max), rsv = tv(row_inv_sum), rvv = tv(row_valid), ivv = tv(inv_valid), lov = tv(loss);
-    for (int64_t start = 0; start < V && c.st == GD_OK; start += chunk) {
+    // One chunk holding all classes: loss statistics and logits gradient come from ONE pass over the logits
+    // (gdb200_lm_cross_entropy_fused_rows), which needs the gradient seed (the loss scale) and the number of valid rows
+    // before the loss exists; both are known here. GDB200_LMCE_FUSED=0 keeps online update + finalize + backward chunk.
+    static int lmce_fused = -1;
+    if (lmce_fused < 0) {
+        const char *env = getenv("GDB200_LMCE_FUSED");
+        lmce_fused = (env != NULL && env[0] == '0') ? 0 : 1;
+    }
+    bool fused_ce = false;
+    Ten seed;
+    memset(&seed, 0, sizeof(seed));
+    if (single && lmce_fused != 0) {
+        if (!global_norm) {
+            counts = c.alloc(GDB_DTYPE_F32, {2});
+            gd_backend_tensor_view cv0 = tv(counts);
+            c.ok(gdb_lm_ce_count_valid(be, &tgv, s->pad_token_id, &cv0), "lm_ce_count_valid");
+        }
+        c.ok(gd_backend_amp_begin_step(be, &amp), "amp_begin_step");
+        seed = c.alloc(GDB_DTYPE_F32, {});
+        c.ok(gd_backend_amp_fill_scale(be, seed.buf, seed.off, 1, GDB_DTYPE_F32, s->state_buffer, s->amp_scale_offset), "amp_fill_scale");
+        Ten logits = c.alloc(dt, {T, V});
+        gd_backend_matrix_view hm = mv(final_norm, (uint32_t)T, (uint32_t)D), wm = mv(lm_w, (uint32_t)V, (uint32_t)D), lm = mv(logits, (uint32_t)T, (uint32_t)V);
+        c.ok(gd_backend_matmul_nt(be, &hm, &wm, &lm), "matmul_nt(logits)");
+        saved_logits = logits;
+        if (c.st == GD_OK) {
+            if (dp && !(s->global_valid_rows > 0.0f)) c.ok(gdb200_dp_join(be), "dp_join(valid rows)");
+            gd_backend_tensor_view lv = tv(logits), bv = tv(lm_b), sdv = tv(seed), cv1 = tv(counts);
+            const gd_status fst = gdb200_lm_cross_entropy_fused_rows(be, &lv, &bv, &tgv, &sdv, &cv1, &rlv, 1.0f, s->logits_softcap, s->pad_token_id);
+            if (fst == GD_OK) {
+                fused_ce = true;
+                c.ok(gdb_lm_ce_reduce_normalize_global(be, &rlv, &cv1, &lov, &ivv), "lm_ce_reduce_normalize(rows)");
+                if (dp) c.ok(gdb200_dp_all_reduce(be, loss.buf, loss.off, 1, GDB_DTYPE_F32), "dp_all_reduce(loss)");
+            } else if (fst != GD_ERR_UNSUPPORTED) {
+                c.ok(fst, "lm_ce_fused_rows");
+            }
+        }
+    }
+    const size_t ce_mark = c.top;
+    if (!fused_ce) {
+        c.fill(row_loss, 0U);
+        c.fill(row_max, 0xFF800000U);
+        c.fill(row_inv_sum, 0U);
+        c.fill(row_valid, 0U);
+    }
+    for (int64_t start = 0; start < V && c.st == GD_OK && !fused_ce; start += chunk) {
         const int64_t cc = chunk < V - start ? chunk : V - start;
         if (!single) c.top = ce_mark;
-        Ten logits = c.alloc(dt, {T, cc});
+        // (when the one-pass kernel declined, its logits are intact and are used as they are)
+        const bool have_logits = single && saved_logits.buf != NULL;
+        Ten logits = have_logits ? saved_logits : c.alloc(dt, {T, cc});
         gd_backend_matrix_view hm = mv(final_norm, (uint32_t)T, (uint32_t)D), wm = mv(lm_w, (uint32_t)cc, (uint32_t)D, (size_t)start), lm = mv(logits, (uint32_t)T, (uint32_t)cc);
-        c.ok(gd_backend_matmul_nt(be, &hm, &wm, &lm), "matmul_nt(logits)");
+        if (!have_logits) c.ok(gd_backend_matmul_nt(be, &hm, &wm, &lm), "matmul_nt(logits)");
         Ten bchunk = lm_b;
         bchunk.off += (size_t)start * gdb_dtype_size(dt);
         bchunk.shape[0] = cc;
@@ -461,6 +504,9 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         c.ok(gd_backend_lm_cross_entropy_online_update(be, &lv, &bv, &tgv, &rlv, &rmv, &rsv, (uint64_t)start, (uint64_t)V, s->logits_softcap), "lm_ce_online_update");
         if (single) saved_logits = logits;
     }
+    if (fused_ce) {
+        // loss and 1 / valid rows are already written
+    } else {
     c.ok(gd_backend_lm_cross_entropy_finalize(be, &tgv, &rlv, &rmv, &rsv, &rvv, (uint64_t)V, s->pad_token_id), "lm_ce_finalize");
     if (global_norm) {
         // loss = this rank's share of the global mean; the shares are summed below so that every rank reports the mean
@@ -471,6 +517,7 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
     } else {
         c.ok(gd_backend_lm_cross_entropy_reduce_normalize(be, &rlv, &rvv, &lov, &ivv), "lm_ce_reduce_normalize");
     }
+    }
     *loss_offset = loss.off;
     if (c.st != GD_OK) {
         snprintf(be->last_error, sizeof(be->last_error), "gpt step forward: %s", c.where);
@@ -478,9 +525,11 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
     }
 
     // ---------------------------------------------------------------- backward
-    c.ok(gd_backend_amp_begin_step(be, &amp), "amp_begin_step");
-    Ten seed = c.alloc(GDB_DTYPE_F32, {});
-    c.ok(gd_backend_amp_fill_scale(be, seed.buf, seed.off, 1, GDB_DTYPE_F32, s->state_buffer, s->amp_scale_offset), "amp_fill_scale");
+    if (seed.buf == NULL) {
+        c.ok(gd_backend_amp_begin_step(be, &amp), "amp_begin_step");
+        seed = c.alloc(GDB_DTYPE_F32, {});
+        c.ok(gd_backend_amp_fill_scale(be, seed.buf, seed.off, 1, GDB_DTYPE_F32, s->state_buffer, s->amp_scale_offset), "amp_fill_scale");
+    }
 
     std::vector<Ten> grads((size_t)n_params);
     const size_t es = gdb_dtype_size(dt);
@@ -555,8 +604,10 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         bchunk.off += (size_t)start * es;
         bchunk.shape[0] = cc;
         gd_backend_tensor_view lv = tv(logits), bv = tv(bchunk);
-        c.ok(gd_backend_lm_cross_entropy_backward_chunk(be, &lv, &bv, &tgv, &rmv, &rsv, &sdv, &ivv, &lv, (uint64_t)start, (uint64_t)V, 1.0f,
-                                                        s->logits_softcap, s->pad_token_id), "lm_ce_backward_chunk");
+        if (!fused_ce) {
+            c.ok(gd_backend_lm_cross_entropy_backward_chunk(be, &lv, &bv, &tgv, &rmv, &rsv, &sdv, &ivv, &lv, (uint64_t)start, (uint64_t)V, 1.0f,
+                                                            s->logits_softcap, s->pad_token_id), "lm_ce_backward_chunk");
+        }
         gd_backend_matrix_view lm = mv(logits, (uint32_t)T, (uint32_t)cc);
         gd_backend_matrix_view dhm = mv(single ? dh : dh_part, (uint32_t)T, (uint32_t)D);
         c.ok(gd_backend_matmul(be, &lm, &wm, &dhm), "matmul(d_hidden)");

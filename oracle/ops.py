@@ -382,11 +382,15 @@ def lm_cross_entropy_forward(hidden, weight, bias, targets, cap: float, ignore_i
     """Mean over valid rows of logsumexp(soft) - soft[target], soft = softcap(round(round(h w^T) + b))
     (metal_lm_cross_entropy.metal:89-252; tests/test_lm_cross_entropy.c:168-296). Returns a dict
     with the loss and the saved statistics."""
-    logits = rnd(hidden @ weight.t(), dtype)
+    return lm_cross_entropy_from_logits(rnd(hidden @ weight.t(), dtype), bias, targets, cap, ignore_index, dtype)
+
+
+def lm_cross_entropy_from_logits(logits, bias, targets, cap: float, ignore_index: int, dtype: str = "f16"):
+    """The statistics of lm_cross_entropy_forward from storage-precision matmul logits [rows, classes] that hold all classes."""
     raw = rnd(logits + bias, dtype) if bias is not None else logits
     soft = softcap(raw, cap)
     tg = targets.to(torch.int64)
-    v = weight.shape[0]
+    v = logits.shape[-1]
     ignored = (tg < 0) | (tg == ignore_index)
     oob = (~ignored) & (tg >= v)
     m = soft.max(dim=-1).values
@@ -399,14 +403,13 @@ def lm_cross_entropy_forward(hidden, weight, bias, targets, cap: float, ignore_i
     count = valid.sum()
     inv = (1.0 / count) if count > 0 else torch.tensor(0.0)
     loss = row_loss.sum() * inv if count > 0 else torch.tensor(float("nan"))
-    return {"loss": loss.to(torch.float32), "soft": soft, "row_max": m, "row_inv_sum": 1.0 / ssum,
+    return {"loss": loss.to(torch.float32), "soft": soft, "row_max": m, "row_inv_sum": 1.0 / ssum, "row_loss": row_loss,
             "inv_valid": torch.as_tensor(inv, dtype=torch.float32), "ignored": ignored | oob}
 
 
-def lm_cross_entropy_backward(hidden, weight, bias, targets, saved, grad_loss: float, cap: float, dtype: str = "f16"):
+def lm_cross_entropy_dlogits(targets, saved, grad_loss: float, cap: float, dtype: str = "f16"):
     """dlogits = (p - onehot) * max(0, 1 - (soft/cap)^2) * grad * inv_valid stored in the storage
-    dtype (metal :254-311), then dh = dlogits w, dW = dlogits^T h, db = sum_rows dlogits
-    (core_lm_cross_entropy.c:876-974)."""
+    dtype (metal_lm_cross_entropy.metal:254-311); zero for rows without a usable target."""
     soft = saved["soft"]
     tg = targets.to(torch.int64)
     p = torch.exp(soft - saved["row_max"][:, None]) * saved["row_inv_sum"][:, None]
@@ -420,6 +423,13 @@ def lm_cross_entropy_backward(hidden, weight, bias, targets, saved, grad_loss: f
     seed = float(np.float32(grad_loss)) * float(saved["inv_valid"])
     g = rnd(g * seed, dtype)
     g[saved["ignored"]] = 0.0
+    return g
+
+
+def lm_cross_entropy_backward(hidden, weight, bias, targets, saved, grad_loss: float, cap: float, dtype: str = "f16"):
+    """dlogits (lm_cross_entropy_dlogits), then dh = dlogits w, dW = dlogits^T h, db = sum_rows dlogits
+    (core_lm_cross_entropy.c:876-974)."""
+    g = lm_cross_entropy_dlogits(targets, saved, grad_loss, cap, dtype)
     dh = rnd(g @ weight, dtype)
     dw = rnd(g.t() @ hidden, dtype)
     db = rnd(g.sum(dim=0), dtype) if bias is not None else None

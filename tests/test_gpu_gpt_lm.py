@@ -277,7 +277,9 @@ def test_native_step_driver_matches_python_host(monkeypatch, tied, chunk_env):
             losses = [float(trainer.train_batch(b).read()[()]) for b in batches]
             results[kind] = (losses, {n: host(p) for n, p in model.params.items()}, trainer.scaler.sync(), trainer.optimizer.step_count())
     lp, ln = results["python"][0], results["native"][0]
-    assert lp[0] == ln[0]                                    # first forward: identical kernels, identical inputs
+    # first forward, identical inputs: the same kernels up to the loss, which the native driver takes from its one-pass
+    # cross entropy when one chunk holds all classes (row maximum before the exponentials instead of an online merge)
+    assert lp[0] == ln[0] if chunk_env else abs(lp[0] - ln[0]) <= 2e-6 * abs(lp[0])
     np.testing.assert_allclose(ln, lp, rtol=2e-4)
     for n in results["python"][1]:
         np.testing.assert_allclose(results["native"][1][n], results["python"][1][n], atol=2e-3, rtol=2e-2, err_msg=n)

@@ -388,6 +388,62 @@ def test_lm_cross_entropy(step, monkeypatch, rows, dim, vocab, cap, chunk_env):
     close(host(bt.grad), db, F16, scale=8)
 
 
+@pytest.mark.parametrize("rows,vocab,cap,dtype", [(18432, 2048, 30.0, F16), (203, 2048, 30.0, F16), (37, 304, 0.0, F16), (64, 1000, 0.75, BF16), (21, 8192, 30.0, F16),
+                                                  (50, 4096, 2.0, BF16), (16, 300, 30.0, F16), (9, 8200, 30.0, F16)])
+def test_lm_cross_entropy_fused_rows(step, rows, vocab, cap, dtype):
+    """gdb200_lm_cross_entropy_fused_rows (row losses and the logits gradient from one pass) against the oracle and against
+    online update + finalize + backward chunk on the same logits; rows with an ignored or out-of-range target included."""
+    ctx, lib = step, step.lib
+    name = storage_name(dtype)
+    lg = rnd_np((rng(54).standard_normal((rows, vocab)) * 3.0).astype(np.float32), dtype)
+    b = rnd_np((rng(55).standard_normal(vocab) * 0.1).astype(np.float32), dtype)
+    tg = rng(56).integers(0, vocab, size=rows).astype(np.int32)
+    tg[::7] = -1
+    tg[5] = 3                                                                 # equals ignore_index below
+    tg[8] = vocab + 2                                                         # past the classes: NaN loss, zero gradient
+    tg[2], tg[3] = 0, vocab - 1
+    valid = float(np.count_nonzero((tg >= 0) & (tg != 3)))
+    saved = O.lm_cross_entropy_from_logits(t32(lg), t32(b), torch.from_numpy(tg), cap, 3, name)
+    want_g = O.lm_cross_entropy_dlogits(torch.from_numpy(tg), saved, 64.0, cap, name).numpy()
+    assert abs(float(saved["inv_valid"]) * valid - 1.0) < 1e-6
+    bt, tt = dev(ctx, b, dtype), dev(ctx, tg, I32)
+    seed, counts = ctx.scratch_empty(F32, ()), ctx.scratch_empty(F32, (2,))
+    seed.write(np.array(64.0, dtype=np.float32))
+    counts.write(np.array([valid, valid], dtype=np.float32))
+    # the three entries
+    l0, rl0, rm0, rs0, rv0 = dev(ctx, lg, dtype), ctx.zeros(ctx.scratch, F32, (rows,)), ctx.scratch_empty(F32, (rows,)), ctx.zeros(ctx.scratch, F32, (rows,)), ctx.zeros(ctx.scratch, F32, (rows,))
+    ctx.fill(rm0, 0xFF800000)
+    inv0, loss0 = ctx.scratch_empty(F32, ()), ctx.scratch_empty(F32, ())
+    ctx.check(lib.gd_backend_lm_cross_entropy_online_update(ctx.backend, byref(l0.tv()), byref(bt.tv()), byref(tt.tv()), byref(rl0.tv()), byref(rm0.tv()), byref(rs0.tv()), 0, vocab, cap), "update")
+    ctx.check(lib.gd_backend_lm_cross_entropy_finalize(ctx.backend, byref(tt.tv()), byref(rl0.tv()), byref(rm0.tv()), byref(rs0.tv()), byref(rv0.tv()), vocab, 3), "finalize")
+    ctx.check(lib.gd_backend_lm_cross_entropy_reduce_normalize(ctx.backend, byref(rl0.tv()), byref(rv0.tv()), byref(loss0.tv()), byref(inv0.tv())), "normalize")
+    ctx.check(lib.gd_backend_lm_cross_entropy_backward_chunk(ctx.backend, byref(l0.tv()), byref(bt.tv()), byref(tt.tv()), byref(rm0.tv()), byref(rs0.tv()), byref(seed.tv()), byref(inv0.tv()),
+                                                             byref(l0.tv()), 0, vocab, 1.0, cap, 3), "backward chunk")
+    # one pass
+    l1, rl1 = dev(ctx, lg, dtype), ctx.scratch_empty(F32, (rows,))
+    st = lib.gdb200_lm_cross_entropy_fused_rows(ctx.backend, byref(l1.tv()), byref(bt.tv()), byref(tt.tv()), byref(seed.tv()), byref(counts.tv()), byref(rl1.tv()), 1.0, cap, 3)
+    if vocab % 8 or vocab > 8192:
+        assert st == abi.GD_ERR_UNSUPPORTED
+        assert np.array_equal(host(l1), lg)                                   # declined: logits untouched
+        return
+    ctx.check(st, "fused rows")
+    got_rl, want_rl = host(rl1), saved["row_loss"].numpy()
+    assert np.array_equal(np.isnan(got_rl), np.isnan(want_rl)) and np.isnan(got_rl[8])
+    ok = ~np.isnan(want_rl)
+    np.testing.assert_allclose(got_rl[ok], want_rl[ok], rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(got_rl[ok], host(rl0)[ok], rtol=2e-6, atol=2e-6)
+    assert np.all(got_rl[(tg < 0) | (tg == 3)] == 0.0)
+    close(host(l1), want_g, dtype)
+    # against the three entries: the same numbers up to the last storage bit of a few elements
+    g0, g1 = host(l0).astype(np.float32), host(l1).astype(np.float32)
+    ulp = 2.0 ** (-10 if dtype == F16 else -7)
+    assert np.all(np.abs(g1 - g0) <= ulp * np.maximum(np.abs(g0), 2.0 ** -14) + 1e-12)
+    # (a cap far below the logits saturates most classes: their slope 1 - tanh^2 is a difference of nearly equal numbers, which
+    # the one-pass kernel forms from tanh and the reference's arithmetic from soft / cap, so more last bits differ there)
+    assert np.mean(g1 != g0) < (1e-2 if cap == 0.0 or cap >= 2.0 else 0.1)
+    assert not g1[(tg < 0) | (tg == 3) | (tg >= vocab)].any()
+
+
 # ------------------------------------------------------------------ optimizer
 def test_adamw_amp_clip_steps(step):
     """Three optimizer steps incl. an overflow step: parameters, masters and the scaler state follow the oracle."""
