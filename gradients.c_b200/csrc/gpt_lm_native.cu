@@ -205,12 +205,44 @@ Ten rms_forward(Step &c, const Ten &x, const Ten &w, int64_t rows, int64_t cols,
 
 // `accum` != NULL: the input gradient is added into *accum (rounded, then added, then rounded: the two calls
 // rms_norm_backward_stats + accumulate in one launch) and *accum is returned.
+Ten dropout_mask_backward(Step &c, const Ten &mask, const Ten &g, float scale);
+
+// dx (accumulated into *accum when given) and the weight gradient of an RMSNorm; with `mask`, *dropped = the gradient of the
+// dropped branch that feeds the same residual stream, dropout_backward_mask(mask, dx, scale), from the same launch where
+// the one-pass kernel takes the shape (a separate launch otherwise).
 Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten &g, int64_t rows, int64_t cols, const Ten &dw,
-                 const Ten *accum = nullptr)
+                 const Ten *accum = nullptr, const Ten *mask = nullptr, float mask_scale = 1.0f, Ten *dropped = nullptr)
 {
     gd_backend_rms_norm_args a = rms_args(rows, cols, c.s->rms_eps);
     Ten dx = accum != nullptr ? *accum : c.alloc(x.dt, {rows, cols});
     gd_backend_tensor_view xv = tv(x), wv = tv(w), iv = tv(inv), gv = tv(g), dxv = tv(dx), dwv = tv(dw);
+    if (mask != nullptr) {
+        // GDB200_RMS_BWD_DROPOUT=0: the dropout backward stays a launch of its own
+        static const bool fuse_mask = !(getenv("GDB200_RMS_BWD_DROPOUT") != NULL && getenv("GDB200_RMS_BWD_DROPOUT")[0] == '0');
+        static const bool split = getenv("GDB200_RMS_BWD_SPLIT") != NULL;
+        if (fuse_mask && !split && c.st == GD_OK) {
+            const size_t mark = c.top;
+            Ten out = dropped->buf != NULL ? *dropped : c.alloc(x.dt, {rows, cols});   // the caller's buffer when it has one
+            const int64_t prow = std::max<int64_t>((int64_t)a.row_blocks, 2 * (int64_t)c.be->sm_count);
+            Ten partial = c.alloc(GDB_DTYPE_F32, {prow, cols});
+            gd_backend_tensor_view pv = tv(partial), mv8 = tv(*mask), ov = tv(out);
+            gd_status r = gdb_rms_norm_backward_with_weight(c.be, &xv, &wv, &iv, &gv, &dxv, accum != nullptr, &dwv, &pv, &a, &mv8, &ov, mask_scale);
+            if (r != GD_ERR_UNSUPPORTED) {
+                c.ok(r, "rms_norm_backward + weight gradient + dropout backward");
+                *dropped = out;
+                return dx;
+            }
+            c.top = mark;
+        }
+        Ten plain = rms_backward(c, x, w, inv, g, rows, cols, dw, accum);
+        if (dropped->buf != NULL) {
+            gd_backend_tensor_view mvw = tv(*mask), pv = tv(plain), dv = tv(*dropped);
+            c.ok(gd_backend_dropout_backward_mask(c.be, &mvw, &pv, &dv, mask_scale), "dropout_backward_mask");
+        } else {
+            *dropped = dropout_mask_backward(c, *mask, plain, mask_scale);
+        }
+        return plain;
+    }
     {
         // input and weight gradient from one pass over x and g where the fused kernel takes the shape (GDB200_RMS_BWD_SPLIT=1: two passes)
         static const bool split = getenv("GDB200_RMS_BWD_SPLIT") != NULL;
@@ -218,7 +250,7 @@ Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten 
             const int64_t prow = std::max<int64_t>((int64_t)a.row_blocks, 2 * (int64_t)c.be->sm_count);
             Ten partial = c.alloc(GDB_DTYPE_F32, {prow, cols});
             gd_backend_tensor_view pv = tv(partial);
-            gd_status r = gdb_rms_norm_backward_with_weight(c.be, &xv, &wv, &iv, &gv, &dxv, accum != nullptr, &dwv, &pv, &a);
+            gd_status r = gdb_rms_norm_backward_with_weight(c.be, &xv, &wv, &iv, &gv, &dxv, accum != nullptr, &dwv, &pv, &a, NULL, NULL, 1.0f);
             if (r != GD_ERR_UNSUPPORTED) {
                 c.ok(r, "rms_norm_backward + weight gradient");
                 return dx;
@@ -616,7 +648,19 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         gd_backend_vector_view dbv = vv(grads[(size_t)P_LMB], (size_t)start, (uint32_t)cc);
         c.ok(gdb200_matmul_tn_colsum(be, &lm, &hm, &dwm, &dbv), "matmul_tn_colsum(d_lm_w, d_lm_b)");
     }
-    Ten gx = rms_backward(c, x, final_w, inv_f, dh, T, D, grads[(size_t)P_FINAL]);
+    // Every RMSNorm backward below feeds the residual gradient, whose next consumer is the backward of the dropout in front of
+    // the residual add (the MLP branch, the attention branch, the embedding): that gradient comes out of the same launch.
+    // Two buffers in front of the blocks' scratch: `to_mlp` is written by the norm in front of a block boundary (final norm, norm 1)
+    // and read by the MLP branch of the block below it (or by the embedding), `to_attn` is written by norm 2 and read in its block.
+    Ten to_mlp, to_attn;
+    memset(&to_mlp, 0, sizeof(to_mlp));
+    memset(&to_attn, 0, sizeof(to_attn));
+    if (drop) {
+        to_mlp = c.alloc(dt, {T, D});
+        to_attn = c.alloc(dt, {T, D});
+    }
+    const Ten *first_mask = !drop ? nullptr : (L > 0 ? &saves[(size_t)L - 1].mask2 : &emb_mask);
+    Ten gx = rms_backward(c, x, final_w, inv_f, dh, T, D, grads[(size_t)P_FINAL], nullptr, first_mask, drop_scale, &to_mlp);
     reduce_range(head_off, head_elems);
 
     for (int i = L - 1; i >= 0 && c.st == GD_OK; --i) {
@@ -627,7 +671,7 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         // lives in the buffer that came in), so the space is reused by the next block: backward scratch is O(1) in depth.
         const size_t layer_mark = c.top;
         // out = resid + dropout(mlp)
-        Ten g_mlp = drop ? dropout_mask_backward(c, sv.mask2, gx, drop_scale) : gx;
+        Ten g_mlp = drop ? to_mlp : gx;
         Ten g_resid = gx;  // adopted: later contributions accumulate into this buffer
         // down projection y = act w + b (w stored [F, D]): dW = act^T g, db = colsum(g), dact = g w^T
         {
@@ -660,10 +704,11 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             }
             Ten dn2;
             linear_t_backward(c, sv.normed2, c.param(pb + 6, {2 * F, D}), d_up, T, D, 2 * F, &dn2, grads[(size_t)pb + 6], grads[(size_t)pb + 7]);
-            rms_backward(c, sv.resid, c.param(pb + 5, {D}), sv.inv2, dn2, T, D, grads[(size_t)pb + 5], &g_resid);
+            rms_backward(c, sv.resid, c.param(pb + 5, {D}), sv.inv2, dn2, T, D, grads[(size_t)pb + 5], &g_resid, drop ? &sv.mask1 : nullptr, drop_scale,
+                         &to_attn);
         }
         // resid = x + dropout(proj)
-        Ten g_proj = drop ? dropout_mask_backward(c, sv.mask1, g_resid, drop_scale) : g_resid;
+        Ten g_proj = drop ? to_attn : g_resid;
         Ten d_attn;
         linear_t_backward(c, sv.attn, c.param(pb + 3, {D, D}), g_proj, T, D, D, &d_attn, grads[(size_t)pb + 3], grads[(size_t)pb + 4]);
         Ten dq = c.alloc(dt, {T, H, Dh}), dk = c.alloc(dt, {T, H, Dh}), dv = c.alloc(dt, {T, H, Dh});
@@ -692,12 +737,14 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         }
         Ten dn1;
         linear_t_backward(c, sv.normed, c.param(pb + 1, {3 * D, D}), dqkv, T, D, 3 * D, &dn1, grads[(size_t)pb + 1], grads[(size_t)pb + 2]);
-        rms_backward(c, sv.x, c.param(pb + 0, {D}), sv.inv1, dn1, T, D, grads[(size_t)pb + 0], &g_resid);
+        // (this block's g_mlp in `to_mlp` is dead by now: the next reader is the block below, or the embedding after the first block)
+        const Ten *next_mask = !drop ? nullptr : (i > 0 ? &saves[(size_t)i - 1].mask2 : &emb_mask);
+        rms_backward(c, sv.x, c.param(pb + 0, {D}), sv.inv1, dn1, T, D, grads[(size_t)pb + 0], &g_resid, next_mask, drop_scale, &to_mlp);
         gx = g_resid;
         reduce_range(goff, gelems);
         c.top = layer_mark;
     }
-    if (drop) gx = dropout_mask_backward(c, emb_mask, gx, drop_scale);
+    if (drop) gx = to_mlp;
     {
         // embedding table gradient; with a tied LM head the head contribution is already in emb_grad
         Ten target = emb_grad;

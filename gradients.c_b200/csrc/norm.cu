@@ -225,14 +225,18 @@ __global__ void rms_bwd_kernel(const T *x, const T *w, const float *inv_in, cons
 // result does not depend on which block was last. dx is computed exactly as rms_bwd_kernel does.
 constexpr int RBW_WARPS = 16, RBW_MAX_COLS = 512, RBW_DEPTH = 3;
 constexpr int RBW_ROW_BYTES = RBW_MAX_COLS * 2;                          // one 16-bit row
-constexpr int RBW_SLOT_BYTES = 3 * RBW_ROW_BYTES;                        // x, g, dx
-constexpr int RBW_SMEM = RBW_WARPS * RBW_DEPTH * RBW_SLOT_BYTES;         // 144 KB; the block reduction reuses it
+constexpr int RBW_MASK_BYTES = RBW_MAX_COLS;                             // one byte per element of a dropout mask row
+constexpr int RBW_SLOT_BYTES = 3 * RBW_ROW_BYTES + RBW_MASK_BYTES;       // x, g, dx, mask
+constexpr int RBW_SMEM = RBW_WARPS * RBW_DEPTH * RBW_SLOT_BYTES;         // 168 KB; the block reduction reuses it
 static_assert(RBW_SMEM >= (int)sizeof(float) * RBW_WARPS * RBW_MAX_COLS, "the reduction buffer aliases the rings");
 template <typename T>
 __global__ void __launch_bounds__(RBW_WARPS * 32, 1)
 rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const float *__restrict__ inv_in, const T *__restrict__ g, T *dx,
-                     T *__restrict__ dw, float *__restrict__ partial, unsigned *__restrict__ ticket, size_t rows, size_t cols, bool add_to_dx)
+                     T *__restrict__ dw, float *__restrict__ partial, unsigned *__restrict__ ticket, size_t rows, size_t cols, bool add_to_dx,
+                     const unsigned char *__restrict__ mask, T *__restrict__ masked, float mask_scale)
 {
+    // mask != nullptr: masked = dropout_backward_mask(mask, dx, mask_scale) as well, i.e. the gradient that flows into the
+    // dropped branch next to the residual one, formed from the stored (rounded) dx as the separate entry would read it.
     gdb_pdl_sync();
     extern __shared__ __align__(16) unsigned char rbw_sm[];
     __shared__ bool last;
@@ -254,6 +258,9 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
     auto cp16 = [](void *dst, const void *src) {
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
     };
+    auto cp8 = [](void *dst, const void *src) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+    };
     auto issue = [&](size_t row, int slot) {
         if (row < rows) {
             unsigned char *base = ring + (size_t)slot * RBW_SLOT_BYTES;
@@ -264,6 +271,7 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
                     cp16(base + v * 16U, reinterpret_cast<const uint4 *>(x + row * cols) + v);
                     cp16(base + RBW_ROW_BYTES + v * 16U, reinterpret_cast<const uint4 *>(g + row * cols) + v);
                     if (add_to_dx) cp16(base + 2 * RBW_ROW_BYTES + v * 16U, reinterpret_cast<const uint4 *>(dx + row * cols) + v);
+                    if (mask != nullptr) cp8(base + 3 * RBW_ROW_BYTES + v * 8U, reinterpret_cast<const uint2 *>(mask + row * cols) + v);
                 }
             }
         }
@@ -317,6 +325,15 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
                     for (int e = 0; e < 8; ++e) o.set(e, da.get(e) + o.get(e));
                 }
                 dv[v] = o.raw;
+                if (mask != nullptr) {
+                    const uint2 m = *reinterpret_cast<const uint2 *>(base + 3 * RBW_ROW_BYTES + v * 8U);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const bool keep = (((e < 4 ? m.x : m.y) >> (8U * (unsigned)(e & 3))) & 255U) != 0U;
+                        o.set(e, keep ? o.get(e) * mask_scale : 0.0f);
+                    }
+                    reinterpret_cast<uint4 *>(masked + row * cols)[v] = o.raw;
+                }
             }
         }
         slot = slot == RBW_DEPTH - 1 ? 0 : slot + 1;
@@ -632,8 +649,28 @@ gd_status gdb_rms_norm_backward_accumulate(gd_backend *be, const gd_backend_tens
 gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
                                             const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
                                             const gd_backend_tensor_view *grad_x, bool add_to_dx, const gd_backend_tensor_view *grad_weight,
-                                            const gd_backend_tensor_view *partial, const gd_backend_rms_norm_args *a)
+                                            const gd_backend_tensor_view *partial, const gd_backend_rms_norm_args *a,
+                                            const gd_backend_tensor_view *mask, const gd_backend_tensor_view *masked, float mask_scale)
 {
+    // mask / masked (both or neither): masked = gd_backend_dropout_backward_mask(mask, grad_x, mask_scale) from the same launch
+    const unsigned char *mp = NULL;
+    void *mop = NULL;
+    if ((mask == NULL) != (masked == NULL)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (mask != NULL) {
+        if (x == NULL || mask->count != x->count || masked->count != x->count || masked->dtype != x->dtype || !(mask_scale > 0.0f)) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+        mp = (const unsigned char *)gdb_tv_ptr(mask, GDB_DTYPE_U8);
+        mop = gdb_tv_ptr(masked, masked->dtype);
+        if (mp == NULL || mop == NULL) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+        if (((uintptr_t)mp % 8U) != 0U || ((uintptr_t)mop % 16U) != 0U) {
+            return GD_ERR_UNSUPPORTED;
+        }
+    }
     if (be == NULL || x == NULL || weight == NULL || inv_rms == NULL || grad_out == NULL || grad_x == NULL || grad_weight == NULL ||
         partial == NULL || !args_ok(a) || a->row_blocks == 0U || x->count != a->rows * a->cols || grad_out->count != x->count ||
         grad_x->count != x->count || weight->count != a->cols || grad_weight->count != a->cols || inv_rms->count != a->rows ||
@@ -670,10 +707,10 @@ gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_ten
     }
     if (dt == GDB_DTYPE_F16) {
         gdb_launch(rms_bwd_wgrad_kernel<__half>, (unsigned)blocks, RBW_WARPS * 32, RBW_SMEM, be->stream, (const __half *)xp, (const __half *)wp, ip, (const __half *)gp,
-                   (__half *)dp, (__half *)dwp, pp, ticket, a->rows, a->cols, add_to_dx);
+                   (__half *)dp, (__half *)dwp, pp, ticket, a->rows, a->cols, add_to_dx, mp, (__half *)mop, mask_scale);
     } else {
         gdb_launch(rms_bwd_wgrad_kernel<__nv_bfloat16>, (unsigned)blocks, RBW_WARPS * 32, RBW_SMEM, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip,
-                   (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, (__nv_bfloat16 *)dwp, pp, ticket, a->rows, a->cols, add_to_dx);
+                   (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, (__nv_bfloat16 *)dwp, pp, ticket, a->rows, a->cols, add_to_dx, mp, (__nv_bfloat16 *)mop, mask_scale);
     }
     return gdb_launched(be, "rms_norm_backward + weight gradient");
 }
@@ -684,7 +721,20 @@ extern "C" gd_status gdb200_rms_norm_backward_with_weight(gd_backend *be, const 
                                                           const gd_backend_tensor_view *grad_weight, const gd_backend_tensor_view *partial,
                                                           const gd_backend_rms_norm_args *args)
 {
-    return gdb_rms_norm_backward_with_weight(be, x, weight, inv_rms, grad_out, grad_x, accumulate != 0, grad_weight, partial, args);
+    return gdb_rms_norm_backward_with_weight(be, x, weight, inv_rms, grad_out, grad_x, accumulate != 0, grad_weight, partial, args, NULL, NULL, 1.0f);
+}
+
+extern "C" gd_status gdb200_rms_norm_backward_with_weight_dropout(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
+                                                                  const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
+                                                                  const gd_backend_tensor_view *grad_x, int32_t accumulate,
+                                                                  const gd_backend_tensor_view *grad_weight, const gd_backend_tensor_view *partial,
+                                                                  const gd_backend_rms_norm_args *args, const gd_backend_tensor_view *mask,
+                                                                  const gd_backend_tensor_view *grad_dropped, float scale)
+{
+    if (mask == NULL || grad_dropped == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    return gdb_rms_norm_backward_with_weight(be, x, weight, inv_rms, grad_out, grad_x, accumulate != 0, grad_weight, partial, args, mask, grad_dropped, scale);
 }
 
 gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *residual, const gd_backend_tensor_view *x,

@@ -168,6 +168,20 @@ def test_rms_norm_backward_with_weight_gradient_in_one_pass(step, dtype, rows, c
         close(host(dx1), wdx, dtype)
     close(host(dw1), wdw, dtype, scale=8 * max(1.0, math.sqrt(rows / 777)))
     close(host(dw1), host(dw0), dtype, scale=2 * max(1.0, math.sqrt(rows / 777)))
+    # the same launch with the dropout backward of its result as a second output: all three outputs bit for bit
+    keep = (rng(24).random((rows, cols)) >= 0.1).astype(np.uint8)
+    mt = dev(ctx, keep, U8)
+    dx2 = dev(ctx, base, dtype) if accumulate else ctx.scratch_empty(dtype, (rows, cols))
+    dw2, dropped2, dropped_want = ctx.scratch_empty(dtype, (cols,)), ctx.scratch_empty(dtype, (rows, cols)), ctx.scratch_empty(dtype, (rows, cols))
+    scale = float(np.float32(1.0) / np.float32(0.9))
+    ctx.check(lib.gdb200_rms_norm_backward_with_weight_dropout(ctx.backend, byref(xt.tv()), byref(wt.tv()), byref(inv.tv()), byref(gt.tv()), byref(dx2.tv()),
+                                                               accumulate, byref(dw2.tv()), byref(partial.tv()), byref(args), byref(mt.tv()),
+                                                               byref(dropped2.tv()), scale), "rms backward + weight gradient + dropout backward")
+    ctx.check(lib.gd_backend_dropout_backward_mask(ctx.backend, byref(mt.tv()), byref(dx1.tv()), byref(dropped_want.tv()), scale), "dropout backward")
+    as_bits = lambda t: host(t).astype(np.float32).view(np.uint32)
+    assert np.array_equal(as_bits(dx2), as_bits(dx1)) and np.array_equal(as_bits(dw2), as_bits(dw1))
+    assert np.array_equal(as_bits(dropped2), as_bits(dropped_want))
+    assert np.array_equal(host(dropped2)[keep == 0], np.zeros(int((keep == 0).sum()), dtype=np.float32))
 
 
 # ------------------------------------------------------------------ GEMM family
