@@ -330,7 +330,8 @@ gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_ten
                                             const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
                                             const gd_backend_tensor_view *grad_x, bool add_to_dx, const gd_backend_tensor_view *grad_weight,
                                             const gd_backend_tensor_view *partial, const gd_backend_rms_norm_args *args,
-                                            const gd_backend_tensor_view *mask, const gd_backend_tensor_view *masked, float mask_scale);
+                                            const gd_backend_tensor_view *mask, const gd_backend_tensor_view *masked, float mask_scale,
+                                            const gd_backend_tensor_view *masked_colsum);
 gd_status gdb_rms_norm_backward_accumulate(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
                                            const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
                                            const gd_backend_tensor_view *grad_accum, const gd_backend_rms_norm_args *args);

@@ -208,10 +208,12 @@ Ten rms_forward(Step &c, const Ten &x, const Ten &w, int64_t rows, int64_t cols,
 Ten dropout_mask_backward(Step &c, const Ten &mask, const Ten &g, float scale);
 
 // dx (accumulated into *accum when given) and the weight gradient of an RMSNorm; with `mask`, *dropped = the gradient of the
-// dropped branch that feeds the same residual stream, dropout_backward_mask(mask, dx, scale), from the same launch where
-// the one-pass kernel takes the shape (a separate launch otherwise).
+// dropped branch that feeds the same residual stream, dropout_backward_mask(mask, dx, scale), and with `dropped_colsum` its
+// sum over the rows (the bias gradient of the branch's last projection), from the same launch where the one-pass kernel takes
+// the shape (separate launches otherwise).
 Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten &g, int64_t rows, int64_t cols, const Ten &dw,
-                 const Ten *accum = nullptr, const Ten *mask = nullptr, float mask_scale = 1.0f, Ten *dropped = nullptr)
+                 const Ten *accum = nullptr, const Ten *mask = nullptr, float mask_scale = 1.0f, Ten *dropped = nullptr,
+                 const Ten *dropped_colsum = nullptr)
 {
     gd_backend_rms_norm_args a = rms_args(rows, cols, c.s->rms_eps);
     Ten dx = accum != nullptr ? *accum : c.alloc(x.dt, {rows, cols});
@@ -225,8 +227,10 @@ Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten 
             Ten out = dropped->buf != NULL ? *dropped : c.alloc(x.dt, {rows, cols});   // the caller's buffer when it has one
             const int64_t prow = std::max<int64_t>((int64_t)a.row_blocks, 2 * (int64_t)c.be->sm_count);
             Ten partial = c.alloc(GDB_DTYPE_F32, {prow, cols});
-            gd_backend_tensor_view pv = tv(partial), mv8 = tv(*mask), ov = tv(out);
-            gd_status r = gdb_rms_norm_backward_with_weight(c.be, &xv, &wv, &iv, &gv, &dxv, accum != nullptr, &dwv, &pv, &a, &mv8, &ov, mask_scale);
+            gd_backend_tensor_view pv = tv(partial), mv8 = tv(*mask), ov = tv(out), csv;
+            if (dropped_colsum != nullptr) csv = tv(*dropped_colsum);
+            gd_status r = gdb_rms_norm_backward_with_weight(c.be, &xv, &wv, &iv, &gv, &dxv, accum != nullptr, &dwv, &pv, &a, &mv8, &ov, mask_scale,
+                                                            dropped_colsum != nullptr ? &csv : NULL);
             if (r != GD_ERR_UNSUPPORTED) {
                 c.ok(r, "rms_norm_backward + weight gradient + dropout backward");
                 *dropped = out;
@@ -241,6 +245,11 @@ Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten 
         } else {
             *dropped = dropout_mask_backward(c, *mask, plain, mask_scale);
         }
+        if (dropped_colsum != nullptr) {
+            gd_backend_matrix_view gm = mv(*dropped, (uint32_t)rows, (uint32_t)cols);
+            gd_backend_vector_view dbv = vv(*dropped_colsum, 0, (uint32_t)cols);
+            c.ok(gd_backend_reduce_rows(c.be, &gm, &dbv), "reduce_rows(dropped gradient)");
+        }
         return plain;
     }
     {
@@ -250,7 +259,7 @@ Ten rms_backward(Step &c, const Ten &x, const Ten &w, const Ten &inv, const Ten 
             const int64_t prow = std::max<int64_t>((int64_t)a.row_blocks, 2 * (int64_t)c.be->sm_count);
             Ten partial = c.alloc(GDB_DTYPE_F32, {prow, cols});
             gd_backend_tensor_view pv = tv(partial);
-            gd_status r = gdb_rms_norm_backward_with_weight(c.be, &xv, &wv, &iv, &gv, &dxv, accum != nullptr, &dwv, &pv, &a, NULL, NULL, 1.0f);
+            gd_status r = gdb_rms_norm_backward_with_weight(c.be, &xv, &wv, &iv, &gv, &dxv, accum != nullptr, &dwv, &pv, &a, NULL, NULL, 1.0f, NULL);
             if (r != GD_ERR_UNSUPPORTED) {
                 c.ok(r, "rms_norm_backward + weight gradient");
                 return dx;
@@ -659,8 +668,11 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         to_mlp = c.alloc(dt, {T, D});
         to_attn = c.alloc(dt, {T, D});
     }
+    // (the block below reads `to_mlp` as the gradient of its down projection's output: that projection's bias gradient, the sum of
+    // `to_mlp` over the rows, comes out of the same launch too)
     const Ten *first_mask = !drop ? nullptr : (L > 0 ? &saves[(size_t)L - 1].mask2 : &emb_mask);
-    Ten gx = rms_backward(c, x, final_w, inv_f, dh, T, D, grads[(size_t)P_FINAL], nullptr, first_mask, drop_scale, &to_mlp);
+    Ten gx = rms_backward(c, x, final_w, inv_f, dh, T, D, grads[(size_t)P_FINAL], nullptr, first_mask, drop_scale, &to_mlp,
+                          drop && L > 0 ? &grads[(size_t)(1 + 10 * (L - 1)) + 9] : nullptr);
     reduce_range(head_off, head_elems);
 
     for (int i = L - 1; i >= 0 && c.st == GD_OK; --i) {
@@ -679,8 +691,10 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             gd_backend_matrix_view am = mv(sv.act, (uint32_t)T, (uint32_t)F), gm = mv(g_mlp, (uint32_t)T, (uint32_t)D), wm = mv(w, (uint32_t)F, (uint32_t)D);
             gd_backend_matrix_view dwm = mv(grads[(size_t)pb + 8], (uint32_t)F, (uint32_t)D);
             c.ok(gd_backend_matmul_tn(be, &am, &gm, &dwm), "matmul_tn(d_down_w)");
-            gd_backend_vector_view dbv = vv(grads[(size_t)pb + 9], 0, (uint32_t)D);
-            c.ok(gd_backend_reduce_rows(be, &gm, &dbv), "reduce_rows(d_down_b)");
+            if (!drop) {   // with dropout the norm in front of this block has written it together with g_mlp
+                gd_backend_vector_view dbv = vv(grads[(size_t)pb + 9], 0, (uint32_t)D);
+                c.ok(gd_backend_reduce_rows(be, &gm, &dbv), "reduce_rows(d_down_b)");
+            }
             // d_act = g w^T and the SwiGLU backward in its epilogue; the two separate calls when the fused kernel declines
             Ten d_up = c.alloc(dt, {T, 2 * F});
             gd_backend_matrix_view ugm = mv(sv.up_gate, (uint32_t)T, (uint32_t)(2 * F)), dum = mv(d_up, (uint32_t)T, (uint32_t)(2 * F));
@@ -739,7 +753,8 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         linear_t_backward(c, sv.normed, c.param(pb + 1, {3 * D, D}), dqkv, T, D, 3 * D, &dn1, grads[(size_t)pb + 1], grads[(size_t)pb + 2]);
         // (this block's g_mlp in `to_mlp` is dead by now: the next reader is the block below, or the embedding after the first block)
         const Ten *next_mask = !drop ? nullptr : (i > 0 ? &saves[(size_t)i - 1].mask2 : &emb_mask);
-        rms_backward(c, sv.x, c.param(pb + 0, {D}), sv.inv1, dn1, T, D, grads[(size_t)pb + 0], &g_resid, next_mask, drop_scale, &to_mlp);
+        rms_backward(c, sv.x, c.param(pb + 0, {D}), sv.inv1, dn1, T, D, grads[(size_t)pb + 0], &g_resid, next_mask, drop_scale, &to_mlp,
+                     drop && i > 0 ? &grads[(size_t)(pb - 10) + 9] : nullptr);
         gx = g_resid;
         reduce_range(goff, gelems);
         c.top = layer_mark;

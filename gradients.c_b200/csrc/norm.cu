@@ -233,8 +233,10 @@ template <typename T>
 __global__ void __launch_bounds__(RBW_WARPS * 32, 1)
 rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const float *__restrict__ inv_in, const T *__restrict__ g, T *dx,
                      T *__restrict__ dw, float *__restrict__ partial, unsigned *__restrict__ ticket, size_t rows, size_t cols, bool add_to_dx,
-                     const unsigned char *__restrict__ mask, T *__restrict__ masked, float mask_scale)
+                     const unsigned char *__restrict__ mask, T *__restrict__ masked, float mask_scale, T *__restrict__ masked_colsum)
 {
+    // masked_colsum != nullptr (with mask): masked_colsum[c] = sum over rows of masked[:, c] as well, the bias gradient of the
+    // projection whose output the dropped branch is (reduce_rows of the same tensor); its partial sums use the second half of `partial`.
     // mask != nullptr: masked = dropout_backward_mask(mask, dx, mask_scale) as well, i.e. the gradient that flows into the
     // dropped branch next to the residual one, formed from the stored (rounded) dx as the separate entry would read it.
     gdb_pdl_sync();
@@ -243,11 +245,11 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t vecs = cols / 8U;
     unsigned char *ring = rbw_sm + (size_t)warp * RBW_DEPTH * RBW_SLOT_BYTES;
-    float dwacc[2][8], wf[2][8];
+    float dwacc[2][8], wf[2][8], csacc[2][8];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.0f;
+        for (int e = 0; e < 8; ++e) dwacc[i][e] = csacc[i][e] = 0.0f;
         const size_t v = (size_t)lane + 32U * (size_t)i;
         gdb_vec8<T> wa;
         wa.raw = v < vecs ? __ldg(reinterpret_cast<const uint4 *>(w) + v) : make_uint4(0U, 0U, 0U, 0U);
@@ -331,6 +333,7 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
                     for (int e = 0; e < 8; ++e) {
                         const bool keep = (((e < 4 ? m.x : m.y) >> (8U * (unsigned)(e & 3))) & 255U) != 0U;
                         o.set(e, keep ? o.get(e) * mask_scale : 0.0f);
+                        csacc[i][e] += o.get(e);
                     }
                     reinterpret_cast<uint4 *>(masked + row * cols)[v] = o.raw;
                 }
@@ -341,20 +344,28 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();   // every warp is done with its ring: the reduction buffer reuses the memory
     float(*sh)[RBW_MAX_COLS] = reinterpret_cast<float(*)[RBW_MAX_COLS]>(rbw_sm);
+    // this block's column sums of the lanes' accumulators, warps added in warp order, into row `slab_row` of partial
+    auto publish = [&](const float (&acc)[2][8], size_t slab_row) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const size_t v = (size_t)lane + 32U * (size_t)i;
-        if (v < vecs) {
+        for (int i = 0; i < 2; ++i) {
+            const size_t v = (size_t)lane + 32U * (size_t)i;
+            if (v < vecs) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) sh[warp][v * 8U + e] = dwacc[i][e];
+                for (int e = 0; e < 8; ++e) sh[warp][v * 8U + e] = acc[i][e];
+            }
         }
-    }
-    __syncthreads();
-    for (size_t c = threadIdx.x; c < cols; c += blockDim.x) {
-        float s = 0.0f;
+        __syncthreads();
+        for (size_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            float s = 0.0f;
 #pragma unroll
-        for (int wi = 0; wi < RBW_WARPS; ++wi) s += sh[wi][c];
-        partial[(size_t)blockIdx.x * cols + c] = s;
+            for (int wi = 0; wi < RBW_WARPS; ++wi) s += sh[wi][c];
+            partial[slab_row * cols + c] = s;
+        }
+    };
+    publish(dwacc, blockIdx.x);
+    if (masked_colsum != nullptr) {
+        __syncthreads();
+        publish(csacc, (size_t)gridDim.x + blockIdx.x);
     }
     __threadfence();
     __syncthreads();
@@ -362,19 +373,23 @@ rms_bwd_wgrad_kernel(const T *__restrict__ x, const T *__restrict__ w, const flo
     __syncthreads();
     if (last) {
         __threadfence();
-        for (size_t c = threadIdx.x; c < cols; c += blockDim.x) {
-            float s = 0.0f;
-            unsigned b = 0;
-            for (; b + 8U <= gridDim.x; b += 8U) {   // eight loads in flight, summed in block order
-                float t[8];
+        auto merge = [&](const float *slab, T *out) {
+            for (size_t c = threadIdx.x; c < cols; c += blockDim.x) {
+                float s = 0.0f;
+                unsigned b = 0;
+                for (; b + 8U <= gridDim.x; b += 8U) {   // eight loads in flight, summed in block order
+                    float t[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) t[u] = __ldcg(&partial[(size_t)(b + u) * cols + c]);
+                    for (int u = 0; u < 8; ++u) t[u] = __ldcg(&slab[(size_t)(b + u) * cols + c]);
 #pragma unroll
-                for (int u = 0; u < 8; ++u) s += t[u];
+                    for (int u = 0; u < 8; ++u) s += t[u];
+                }
+                for (; b < gridDim.x; ++b) s += __ldcg(&slab[(size_t)b * cols + c]);
+                gdb_io<T>::st(out, c, s);
             }
-            for (; b < gridDim.x; ++b) s += __ldcg(&partial[(size_t)b * cols + c]);
-            gdb_io<T>::st(dw, c, s);
-        }
+        };
+        merge(partial, dw);
+        if (masked_colsum != nullptr) merge(partial + (size_t)gridDim.x * cols, masked_colsum);
         if (threadIdx.x == 0) *ticket = 0U;
     }
 }
@@ -650,11 +665,19 @@ gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_ten
                                             const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
                                             const gd_backend_tensor_view *grad_x, bool add_to_dx, const gd_backend_tensor_view *grad_weight,
                                             const gd_backend_tensor_view *partial, const gd_backend_rms_norm_args *a,
-                                            const gd_backend_tensor_view *mask, const gd_backend_tensor_view *masked, float mask_scale)
+                                            const gd_backend_tensor_view *mask, const gd_backend_tensor_view *masked, float mask_scale,
+                                            const gd_backend_tensor_view *masked_colsum)
 {
-    // mask / masked (both or neither): masked = gd_backend_dropout_backward_mask(mask, grad_x, mask_scale) from the same launch
+    // mask / masked (both or neither): masked = gd_backend_dropout_backward_mask(mask, grad_x, mask_scale) from the same launch;
+    // masked_colsum (optional, with mask): [cols] = sum over rows of masked, then `partial` needs 2 * row_blocks * cols elements
     const unsigned char *mp = NULL;
-    void *mop = NULL;
+    void *mop = NULL, *mcp = NULL;
+    if (masked_colsum != NULL) {
+        if (mask == NULL || x == NULL || a == NULL || masked_colsum->count != a->cols || masked_colsum->dtype != x->dtype ||
+            (mcp = gdb_tv_ptr(masked_colsum, x->dtype)) == NULL) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+    }
     if ((mask == NULL) != (masked == NULL)) {
         return GD_ERR_INVALID_ARGUMENT;
     }
@@ -692,7 +715,10 @@ gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_ten
         return GD_ERR_UNSUPPORTED;
     }
     size_t blocks = (size_t)be->sm_count;   // one block (144 KB of rings) per SM
-    const size_t need = (a->rows + RBW_WARPS - 1U) / RBW_WARPS, room = partial->count / a->cols;
+    const size_t need = (a->rows + RBW_WARPS - 1U) / RBW_WARPS, room = partial->count / a->cols / (mcp != NULL ? 2U : 1U);
+    if (room == 0U) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
     if (blocks > need) blocks = need;
     if (blocks > room) blocks = room;   // one FP32 row of partial sums per block
     unsigned *ticket = gdb_tickets(be);
@@ -707,10 +733,10 @@ gd_status gdb_rms_norm_backward_with_weight(gd_backend *be, const gd_backend_ten
     }
     if (dt == GDB_DTYPE_F16) {
         gdb_launch(rms_bwd_wgrad_kernel<__half>, (unsigned)blocks, RBW_WARPS * 32, RBW_SMEM, be->stream, (const __half *)xp, (const __half *)wp, ip, (const __half *)gp,
-                   (__half *)dp, (__half *)dwp, pp, ticket, a->rows, a->cols, add_to_dx, mp, (__half *)mop, mask_scale);
+                   (__half *)dp, (__half *)dwp, pp, ticket, a->rows, a->cols, add_to_dx, mp, (__half *)mop, mask_scale, (__half *)mcp);
     } else {
         gdb_launch(rms_bwd_wgrad_kernel<__nv_bfloat16>, (unsigned)blocks, RBW_WARPS * 32, RBW_SMEM, be->stream, (const __nv_bfloat16 *)xp, (const __nv_bfloat16 *)wp, ip,
-                   (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, (__nv_bfloat16 *)dwp, pp, ticket, a->rows, a->cols, add_to_dx, mp, (__nv_bfloat16 *)mop, mask_scale);
+                   (const __nv_bfloat16 *)gp, (__nv_bfloat16 *)dp, (__nv_bfloat16 *)dwp, pp, ticket, a->rows, a->cols, add_to_dx, mp, (__nv_bfloat16 *)mop, mask_scale, (__nv_bfloat16 *)mcp);
     }
     return gdb_launched(be, "rms_norm_backward + weight gradient");
 }
@@ -721,7 +747,7 @@ extern "C" gd_status gdb200_rms_norm_backward_with_weight(gd_backend *be, const 
                                                           const gd_backend_tensor_view *grad_weight, const gd_backend_tensor_view *partial,
                                                           const gd_backend_rms_norm_args *args)
 {
-    return gdb_rms_norm_backward_with_weight(be, x, weight, inv_rms, grad_out, grad_x, accumulate != 0, grad_weight, partial, args, NULL, NULL, 1.0f);
+    return gdb_rms_norm_backward_with_weight(be, x, weight, inv_rms, grad_out, grad_x, accumulate != 0, grad_weight, partial, args, NULL, NULL, 1.0f, NULL);
 }
 
 extern "C" gd_status gdb200_rms_norm_backward_with_weight_dropout(gd_backend *be, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
@@ -729,12 +755,14 @@ extern "C" gd_status gdb200_rms_norm_backward_with_weight_dropout(gd_backend *be
                                                                   const gd_backend_tensor_view *grad_x, int32_t accumulate,
                                                                   const gd_backend_tensor_view *grad_weight, const gd_backend_tensor_view *partial,
                                                                   const gd_backend_rms_norm_args *args, const gd_backend_tensor_view *mask,
-                                                                  const gd_backend_tensor_view *grad_dropped, float scale)
+                                                                  const gd_backend_tensor_view *grad_dropped, float scale,
+                                                                  const gd_backend_tensor_view *grad_dropped_colsum)
 {
     if (mask == NULL || grad_dropped == NULL) {
         return GD_ERR_INVALID_ARGUMENT;
     }
-    return gdb_rms_norm_backward_with_weight(be, x, weight, inv_rms, grad_out, grad_x, accumulate != 0, grad_weight, partial, args, mask, grad_dropped, scale);
+    return gdb_rms_norm_backward_with_weight(be, x, weight, inv_rms, grad_out, grad_x, accumulate != 0, grad_weight, partial, args, mask, grad_dropped, scale,
+                                             grad_dropped_colsum);
 }
 
 gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *residual, const gd_backend_tensor_view *x,

@@ -437,13 +437,16 @@ gd_status gdb200_rms_norm_backward_with_weight(gd_backend *backend, const gd_bac
  * src/ops/dropout_add/core_dropout_add.c backward), formed from the stored grad_x after the optional accumulation, bit for bit
  * what the separate entry writes. For a residual stream whose next consumer of the gradient is the dropout in front of a
  * residual add (gpt_lm: examples/gpt_lm/gpt_lm_shared.c:602-749, every norm's input gradient meets one). mask U8 and
- * grad_dropped, both [rows, cols], are required here. */
+ * grad_dropped, both [rows, cols], are required here. grad_dropped_colsum (optional, [cols]) = sum over the rows of grad_dropped
+ * in FP32, rounded once: gd_backend_reduce_rows of it up to the order of the FP32 sum (the bias gradient of the projection whose
+ * output went through the dropout); `partial` then has to hold 2 * row_blocks * cols elements. */
 gd_status gdb200_rms_norm_backward_with_weight_dropout(gd_backend *backend, const gd_backend_tensor_view *x, const gd_backend_tensor_view *weight,
                                                        const gd_backend_tensor_view *inv_rms, const gd_backend_tensor_view *grad_out,
                                                        const gd_backend_tensor_view *grad_x, int32_t accumulate,
                                                        const gd_backend_tensor_view *grad_weight, const gd_backend_tensor_view *partial,
                                                        const gd_backend_rms_norm_args *args, const gd_backend_tensor_view *mask,
-                                                       const gd_backend_tensor_view *grad_dropped, float scale);
+                                                       const gd_backend_tensor_view *grad_dropped, float scale,
+                                                       const gd_backend_tensor_view *grad_dropped_colsum);
 
 /* Fused LM cross entropy of a logits matrix that holds ALL classes (one chunk), loss statistics and logits gradient from ONE
  * pass: gd_backend_lm_cross_entropy_online_update + _finalize + _backward_chunk (src/core/backend.h, called by

@@ -173,15 +173,28 @@ def test_rms_norm_backward_with_weight_gradient_in_one_pass(step, dtype, rows, c
     mt = dev(ctx, keep, U8)
     dx2 = dev(ctx, base, dtype) if accumulate else ctx.scratch_empty(dtype, (rows, cols))
     dw2, dropped2, dropped_want = ctx.scratch_empty(dtype, (cols,)), ctx.scratch_empty(dtype, (rows, cols)), ctx.scratch_empty(dtype, (rows, cols))
+    colsum2, partial2 = ctx.scratch_empty(dtype, (cols,)), ctx.scratch_empty(F32, (2 * int(args.row_blocks), cols))
     scale = float(np.float32(1.0) / np.float32(0.9))
     ctx.check(lib.gdb200_rms_norm_backward_with_weight_dropout(ctx.backend, byref(xt.tv()), byref(wt.tv()), byref(inv.tv()), byref(gt.tv()), byref(dx2.tv()),
-                                                               accumulate, byref(dw2.tv()), byref(partial.tv()), byref(args), byref(mt.tv()),
-                                                               byref(dropped2.tv()), scale), "rms backward + weight gradient + dropout backward")
+                                                               accumulate, byref(dw2.tv()), byref(partial2.tv()), byref(args), byref(mt.tv()),
+                                                               byref(dropped2.tv()), scale, byref(colsum2.tv())), "rms backward + weight gradient + dropout backward")
     ctx.check(lib.gd_backend_dropout_backward_mask(ctx.backend, byref(mt.tv()), byref(dx1.tv()), byref(dropped_want.tv()), scale), "dropout backward")
     as_bits = lambda t: host(t).astype(np.float32).view(np.uint32)
     assert np.array_equal(as_bits(dx2), as_bits(dx1)) and np.array_equal(as_bits(dw2), as_bits(dw1))
     assert np.array_equal(as_bits(dropped2), as_bits(dropped_want))
     assert np.array_equal(host(dropped2)[keep == 0], np.zeros(int((keep == 0).sum()), dtype=np.float32))
+    # its column sums: reduce_rows of the same tensor up to FP32 summation order, and the exact sum within the storage rounding
+    colsum_want = ctx.scratch_empty(dtype, (cols,))
+    gm, cv = dropped_want.mv(rows, cols), colsum_want.vv(0, cols)
+    ctx.check(lib.gd_backend_reduce_rows(ctx.backend, byref(gm), byref(cv)), "reduce_rows")
+    close(host(colsum2), host(colsum_want), dtype, scale=2 * max(1.0, math.sqrt(rows / 777)))
+    close(host(colsum2), host(dropped_want).astype(np.float64).sum(axis=0), dtype, scale=2 * max(1.0, math.sqrt(rows / 777)))
+    # without the column sums the same entry takes a null pointer
+    ctx.check(lib.gdb200_rms_norm_backward_with_weight_dropout(ctx.backend, byref(xt.tv()), byref(wt.tv()), byref(inv.tv()), byref(gt.tv()),
+                                                               byref((dev(ctx, base, dtype) if accumulate else ctx.scratch_empty(dtype, (rows, cols))).tv()),
+                                                               accumulate, byref(dw2.tv()), byref(partial.tv()), byref(args), byref(mt.tv()),
+                                                               byref(dropped2.tv()), scale, None), "without column sums")
+    assert np.array_equal(as_bits(dropped2), as_bits(dropped_want))
 
 
 # ------------------------------------------------------------------ GEMM family
