@@ -670,11 +670,15 @@ gd_status gd_backend_sdpa_varlen(gd_backend *be, const gd_backend_tensor_view *q
 
 // `out` (the forward output) and `dq_accum` (FP32 scratch of q's element count) are optional: with both, forward
 // statistics and head_dim 64 the backward runs as one attention pass.
-static gd_status sdpa_varlen_backward_impl(gd_backend *be, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k, const gd_backend_tensor_view *v, const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats, const gd_backend_sdpa_varlen_args *args, const gd_backend_tensor_view *out, const gd_backend_tensor_view *dq_accum)
+static gd_status sdpa_varlen_backward_impl(gd_backend *be, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k, const gd_backend_tensor_view *v, const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats, const gd_backend_sdpa_varlen_args *args, const gd_backend_tensor_view *out, const gd_backend_tensor_view *dq_accum,
+                                           int32_t *query_grad_in_accum = NULL)
 {
     varlen_params p;
     if (be == NULL || grad_out == NULL || grad_q == NULL || grad_k == NULL || grad_v == NULL) {
         return GD_ERR_INVALID_ARGUMENT;
+    }
+    if (query_grad_in_accum != NULL) {
+        *query_grad_in_accum = 0;
     }
     gd_status st = varlen_check(q, k, v, cu_seqlens, args, &p);
     if (st != GD_OK) {
@@ -717,10 +721,15 @@ static gd_status sdpa_varlen_backward_impl(gd_backend *be, const gd_backend_tens
         if (op == NULL || acc == NULL) {
             return GD_ERR_INVALID_ARGUMENT;
         }
+        fa.keep_dq32 = query_grad_in_accum != NULL ? 1 : 0;
         st = gdb_flash_varlen_backward_with_out(be, &fa, op, acc);
         if (st != GD_ERR_UNSUPPORTED) {
+            if (st == GD_OK && query_grad_in_accum != NULL) {
+                *query_grad_in_accum = 1;
+            }
             return st;
         }
+        fa.keep_dq32 = 0;
     }
     st = gdb_flash_varlen_backward(be, &fa, have_fwd_stats);
     if (st != GD_ERR_UNSUPPORTED) {
@@ -742,6 +751,14 @@ gd_status gdb200_sdpa_varlen_backward_with_output(gd_backend *be, const gd_backe
         return GD_ERR_INVALID_ARGUMENT;
     }
     return sdpa_varlen_backward_impl(be, grad_out, q, k, v, cu_seqlens, grad_q, grad_k, grad_v, stats, args, out, dq_accum);
+}
+
+gd_status gdb200_sdpa_varlen_backward_with_output_q32(gd_backend *be, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k, const gd_backend_tensor_view *v, const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *out, const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats, const gd_backend_tensor_view *dq_accum, const gd_backend_sdpa_varlen_args *args, int32_t *query_grad_in_accum)
+{
+    if (out == NULL || dq_accum == NULL || query_grad_in_accum == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    return sdpa_varlen_backward_impl(be, grad_out, q, k, v, cu_seqlens, grad_q, grad_k, grad_v, stats, args, out, dq_accum, query_grad_in_accum);
 }
 
 gd_status gd_backend_sdpa_decode(gd_backend *be, const gd_backend_tensor_view *q, const gd_backend_tensor_view *k_cache, const gd_backend_tensor_view *v_cache, const gd_backend_tensor_view *cache_pos, const gd_backend_tensor_view *out, const gd_backend_sdpa_decode_args *args)

@@ -13,6 +13,7 @@ struct gdb_flash_args {
     int causal, window, prefix, max_seqlen;
     float scale;
     uint32_t dtype;
+    int keep_dq32;     // single-pass backward: leave the query gradient unrounded in the FP32 accumulator, do not write dQ
 };
 
 // Both return GD_ERR_UNSUPPORTED when the configuration is outside the fast path; the caller

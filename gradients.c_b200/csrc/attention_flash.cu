@@ -752,6 +752,9 @@ gd_status backward_single_pass(gd_backend *be, const gdb_flash_args *a, const fl
     st = meta != nullptr ? gdb_attn5_backward(be, a, dq32, meta) : GD_ERR_UNSUPPORTED;   // tensor-memory kernel where the shape allows
     if (st == GD_ERR_UNSUPPORTED) st = launch_kv<T, 64, 64, true>(be, a, p, dq32);
     if (st != GD_OK) return st;
+    if (a->keep_dq32 != 0) {
+        return GD_OK;   // the caller's next kernel reads the accumulator and rounds on load
+    }
     gdb_launch(dq_convert_kernel<T>, gdb_grid_for(n_vec, 256, be, 8), 256, 0, be->stream, (const float4 *)dq32, (uint4 *)a->out_or_dq, n_vec);
     return gdb_launched(be, "flash_backward_dq_convert");
 }

@@ -123,8 +123,10 @@ __global__ void qkv_split_rope_kernel(const T *a0, const T *a1, const T *a2, con
 // token t go to cache slot pos_ids[t] (one new token per cache row: the decode step), skipped when the slot is out of range.
 template <typename T, bool FWD>
 __global__ void qkv_split_rope_vec8_kernel(const T *a0, const T *a1, const T *a2, const int *pos_ids, T *o0, T *o1, T *o2,
-                                           rope_params p, const float *table, unsigned tmax = 0)
+                                           rope_params p, const float *table, unsigned tmax = 0, const float *q32 = nullptr)
 {
+    // q32 != nullptr (backward only): the query gradient comes unrounded from an FP32 accumulator [tokens, heads, head_dim]
+    // and is rounded to T on load, which is what a separate conversion pass would have stored in a0.
     gdb_pdl_sync();
     const unsigned half_dims = p.head_dim >> 1, groups = half_dims >> 3;
     const size_t area = (size_t)p.heads * p.head_dim;
@@ -156,8 +158,19 @@ __global__ void qkv_split_rope_vec8_kernel(const T *a0, const T *a1, const T *a2
             va.raw = *reinterpret_cast<const uint4 *>(a0 + packed + 2U * area);
             vb.raw = *reinterpret_cast<const uint4 *>(a0 + packed + 2U * area + half_dims);
         } else {
-            qa.raw = *reinterpret_cast<const uint4 *>(a0 + split);
-            qb.raw = *reinterpret_cast<const uint4 *>(a0 + split + half_dims);
+            if (q32 != nullptr) {
+                const float4 l0 = *reinterpret_cast<const float4 *>(q32 + split), l1 = *reinterpret_cast<const float4 *>(q32 + split + 4U);
+                const float4 h0 = *reinterpret_cast<const float4 *>(q32 + split + half_dims), h1 = *reinterpret_cast<const float4 *>(q32 + split + half_dims + 4U);
+                const float lo[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w}, hi[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    qa.set(e, lo[e]);
+                    qb.set(e, hi[e]);
+                }
+            } else {
+                qa.raw = *reinterpret_cast<const uint4 *>(a0 + split);
+                qb.raw = *reinterpret_cast<const uint4 *>(a0 + split + half_dims);
+            }
             ka.raw = *reinterpret_cast<const uint4 *>(a1 + split);
             kb.raw = *reinterpret_cast<const uint4 *>(a1 + split + half_dims);
             va.raw = *reinterpret_cast<const uint4 *>(a2 + split);
@@ -274,11 +287,14 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
                        const gd_backend_tensor_view *s2, const gd_backend_tensor_view *pos_ids,
                        const gd_backend_tensor_view *d0, const gd_backend_tensor_view *d1,
                        const gd_backend_tensor_view *d2, uint32_t n_heads, uint32_t head_dim,
-                       const gd_backend_rope_args *args, uint32_t cache_tmax = 0)
+                       const gd_backend_rope_args *args, uint32_t cache_tmax = 0, const gd_backend_tensor_view *sq32 = NULL)
 {
-    // FWD: s0 = qkv, d0..d2 = q,k,v. BWD: s0..s2 = gq,gk,gv, d0 = dqkv.
+    // FWD: s0 = qkv, d0..d2 = q,k,v. BWD: s0..s2 = gq,gk,gv, d0 = dqkv; with sq32 the query gradient is that FP32 tensor and s0 is unused.
     const gd_backend_tensor_view *packed = FWD ? s0 : d0;
-    const gd_backend_tensor_view *sq = FWD ? d0 : s0, *sk = FWD ? d1 : s1, *sv = FWD ? d2 : s2;
+    const gd_backend_tensor_view *sq = FWD ? d0 : (sq32 != NULL ? s1 : s0), *sk = FWD ? d1 : s1, *sv = FWD ? d2 : s2;
+    if (sq32 != NULL && FWD) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
     if (be == NULL || packed == NULL || sq == NULL || sk == NULL || sv == NULL || pos_ids == NULL || n_heads == 0U ||
         head_dim == 0U || (head_dim & 1U) != 0U || !rope_args_ok(args, head_dim)) {
         return GD_ERR_INVALID_ARGUMENT;
@@ -321,9 +337,15 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
             return st;
         }
     }
+    const float *q32p = NULL;
+    if (sq32 != NULL) {
+        if (sq32->count != tokens * area || (q32p = (const float *)gdb_tv_ptr(sq32, GDB_DTYPE_F32)) == NULL) {
+            return GD_ERR_INVALID_ARGUMENT;
+        }
+    }
     const bool vec = args->interleaved == 0U && (head_dim % 16U) == 0U &&
-                     (((uintptr_t)pp | (uintptr_t)qp | (uintptr_t)kp | (uintptr_t)vp) % 16U) == 0U;
-    if (cache_tmax != 0U && !vec) {
+                     (((uintptr_t)pp | (uintptr_t)qp | (uintptr_t)kp | (uintptr_t)vp | (uintptr_t)q32p) % 16U) == 0U;
+    if ((cache_tmax != 0U || q32p != NULL) && !vec) {
         return GD_ERR_UNSUPPORTED;
     }
     const void *a0 = FWD ? pp : qp, *a1 = FWD ? NULL : kp, *a2 = FWD ? NULL : vp;
@@ -333,7 +355,7 @@ gd_status qkv_dispatch(gd_backend *be, const gd_backend_tensor_view *s0, const g
 #define GDB_ROPE_LAUNCH(T)                                                                                          \
     do {                                                                                                            \
         if (vec) {                                                                                                  \
-            gdb_launch(qkv_split_rope_vec8_kernel<T, FWD>, grid, 256, 0, be->stream, (const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table, (unsigned)cache_tmax); \
+            gdb_launch(qkv_split_rope_vec8_kernel<T, FWD>, grid, 256, 0, be->stream, (const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table, (unsigned)cache_tmax, q32p); \
         } else {                                                                                                    \
             gdb_launch(qkv_split_rope_kernel<T, FWD>, grid, 256, 0, be->stream, (const T *)a0, (const T *)a1, (const T *)a2, ip, (T *)o0, (T *)o1, (T *)o2, p, be->rope_table); \
         }                                                                                                           \
@@ -555,6 +577,14 @@ gd_status gd_backend_qkv_split_rope_forward(gd_backend *be, const gd_backend_ten
 gd_status gd_backend_qkv_split_rope_backward(gd_backend *be, const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *pos_ids, const gd_backend_tensor_view *grad_qkv, uint32_t n_heads, uint32_t head_dim, const gd_backend_rope_args *args)
 {
     return qkv_dispatch<false>(be, grad_q, grad_k, grad_v, pos_ids, grad_qkv, NULL, NULL, n_heads, head_dim, args);
+}
+
+gd_status gdb200_qkv_split_rope_backward_q32(gd_backend *be, const gd_backend_tensor_view *grad_q_f32, const gd_backend_tensor_view *grad_k, const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *pos_ids, const gd_backend_tensor_view *grad_qkv, uint32_t n_heads, uint32_t head_dim, const gd_backend_rope_args *args)
+{
+    if (grad_q_f32 == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    return qkv_dispatch<false>(be, NULL, grad_k, grad_v, pos_ids, grad_qkv, NULL, NULL, n_heads, head_dim, args, 0, grad_q_f32);
 }
 
 }  // extern "C"

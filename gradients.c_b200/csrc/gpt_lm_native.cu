@@ -725,7 +725,9 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         Ten g_proj = drop ? to_attn : g_resid;
         Ten d_attn;
         linear_t_backward(c, sv.attn, c.param(pb + 3, {D, D}), g_proj, T, D, D, &d_attn, grads[(size_t)pb + 3], grads[(size_t)pb + 4]);
-        Ten dq = c.alloc(dt, {T, H, Dh}), dk = c.alloc(dt, {T, H, Dh}), dv = c.alloc(dt, {T, H, Dh});
+        Ten dq = c.alloc(dt, {T, H, Dh}), dk = c.alloc(dt, {T, H, Dh}), dv = c.alloc(dt, {T, H, Dh}), acc;
+        int32_t q_in_acc = 0;
+        memset(&acc, 0, sizeof(acc));
         {
             Ten g3 = d_attn;
             g3.rank = 3;
@@ -740,14 +742,26 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             attn3.shape[0] = T;
             attn3.shape[1] = H;
             attn3.shape[2] = Dh;
-            Ten acc = c.alloc(GDB_DTYPE_F32, {T, H, Dh});
+            acc = c.alloc(GDB_DTYPE_F32, {T, H, Dh});
             gd_backend_tensor_view ov = tv(attn3), av = tv(acc);
-            c.ok(gdb200_sdpa_varlen_backward_with_output(be, &gv, &q, &k, &v, &cv, &ov, &dqv, &dkv, &dvv, &stv, &av, &sa), "sdpa_varlen_backward");
+            // the query gradient may stay in the FP32 accumulator: the RoPE backward below rounds it on load (GDB200_DQ_F32=0:
+            // a conversion pass in between, as the reference's two entries imply)
+            static const bool dq_f32 = !(getenv("GDB200_DQ_F32") != NULL && getenv("GDB200_DQ_F32")[0] == '0');
+            // (only where that RoPE backward takes its vector path: half-split rotation of the whole head, head_dim a multiple of 16)
+            if (dq_f32 && rope.interleaved == 0U && rope.n_dims == (uint32_t)Dh && (Dh % 16) == 0) {
+                c.ok(gdb200_sdpa_varlen_backward_with_output_q32(be, &gv, &q, &k, &v, &cv, &ov, &dqv, &dkv, &dvv, &stv, &av, &sa, &q_in_acc), "sdpa_varlen_backward");
+            } else {
+                c.ok(gdb200_sdpa_varlen_backward_with_output(be, &gv, &q, &k, &v, &cv, &ov, &dqv, &dkv, &dvv, &stv, &av, &sa), "sdpa_varlen_backward");
+            }
         }
         Ten dqkv = c.alloc(dt, {T, 3 * D});
         {
-            gd_backend_tensor_view a = tv(dq), b = tv(dk), v = tv(dv), p = tv(pos), o = tv(dqkv);
-            c.ok(gd_backend_qkv_split_rope_backward(be, &a, &b, &v, &p, &o, (uint32_t)H, (uint32_t)Dh, &rope), "qkv_split_rope_backward");
+            gd_backend_tensor_view a = tv(dq), a32 = tv(acc), b = tv(dk), v = tv(dv), p = tv(pos), o = tv(dqkv);
+            if (q_in_acc != 0) {
+                c.ok(gdb200_qkv_split_rope_backward_q32(be, &a32, &b, &v, &p, &o, (uint32_t)H, (uint32_t)Dh, &rope), "qkv_split_rope_backward(FP32 dq)");
+            } else {
+                c.ok(gd_backend_qkv_split_rope_backward(be, &a, &b, &v, &p, &o, (uint32_t)H, (uint32_t)Dh, &rope), "qkv_split_rope_backward");
+            }
         }
         Ten dn1;
         linear_t_backward(c, sv.normed, c.param(pb + 1, {3 * D, D}), dqkv, T, D, 3 * D, &dn1, grads[(size_t)pb + 1], grads[(size_t)pb + 2]);

@@ -295,6 +295,8 @@ PROTOTYPES = {
     "gdb200_matmul_nt_bias": (_ST, [P, MV, MV, VV, MV]),
     "gdb200_matmul_nt_bias_swiglu": (_ST, [P, MV, MV, VV, MV]),
     "gdb200_sdpa_varlen_backward_with_output": (_ST, [P] + [TV] * 11 + [C.POINTER(SdpaVarlenArgs)]),
+    "gdb200_sdpa_varlen_backward_with_output_q32": (_ST, [P] + [TV] * 11 + [C.POINTER(SdpaVarlenArgs), C.POINTER(I32_T)]),
+    "gdb200_qkv_split_rope_backward_q32": (_ST, [P, TV, TV, TV, TV, TV, U32, U32, C.POINTER(RopeArgs)]),
     "gdb200_embedding_backward_static": (_ST, [P, P, P, P, U64, U64, U64, U32]),
     "gdb200_embedding_backward_static_error": (C.c_char_p, []),
     "gdb200_embedding_backward_static_max_elems": (U64, []),

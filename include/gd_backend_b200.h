@@ -478,6 +478,24 @@ gd_status gdb200_sdpa_varlen_backward_with_output(gd_backend *backend, const gd_
                                                   const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k,
                                                   const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats,
                                                   const gd_backend_tensor_view *dq_accum, const gd_backend_sdpa_varlen_args *args);
+/* The same call for a caller whose next step reads the query gradient in FP32: where the one-pass kernel ran, the rounding
+ * pass is skipped, the unrounded gradient stays in dq_accum, grad_q is left untouched and *query_grad_in_accum is 1; in every
+ * other case grad_q is written as above and *query_grad_in_accum is 0.
+ * gdb200_qkv_split_rope_backward_q32 is gd_backend_qkv_split_rope_backward (src/core/backend.h; src/ops/qkv_split_rope) with the
+ * query gradient taken from such an FP32 tensor [N, heads, head_dim] and rounded to the storage type on load: the same bits as
+ * the rounding pass followed by the reference entry. Vector path only (half-split rotation of the whole head, head_dim a multiple
+ * of 16, 16-byte aligned tensors), GD_ERR_UNSUPPORTED otherwise. */
+gd_status gdb200_sdpa_varlen_backward_with_output_q32(gd_backend *backend, const gd_backend_tensor_view *grad_out, const gd_backend_tensor_view *q,
+                                                      const gd_backend_tensor_view *k, const gd_backend_tensor_view *v,
+                                                      const gd_backend_tensor_view *cu_seqlens, const gd_backend_tensor_view *out,
+                                                      const gd_backend_tensor_view *grad_q, const gd_backend_tensor_view *grad_k,
+                                                      const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *stats,
+                                                      const gd_backend_tensor_view *dq_accum, const gd_backend_sdpa_varlen_args *args,
+                                                      int32_t *query_grad_in_accum);
+gd_status gdb200_qkv_split_rope_backward_q32(gd_backend *backend, const gd_backend_tensor_view *grad_q_f32, const gd_backend_tensor_view *grad_k,
+                                             const gd_backend_tensor_view *grad_v, const gd_backend_tensor_view *pos_ids,
+                                             const gd_backend_tensor_view *grad_qkv, uint32_t n_heads, uint32_t head_dim,
+                                             const gd_backend_rope_args *args);
 
 /* Weight and bias gradient of a linear layer in one pass over the upstream gradient (no counterpart in the reference,
  * which calls matmul_tn and reduce_rows, src/ops/linear_transposed_weight/core_linear_transposed_weight_bwd.c:31-167):

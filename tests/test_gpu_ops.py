@@ -791,6 +791,49 @@ def test_sdpa_backward_with_forward_output_matches_the_two_pass_backward(step, d
     close(grads[True][2], grads[False][2], dtype, scale=2, what="dv single pass vs two passes")
 
 
+@pytest.mark.parametrize("dtype,dh,lengths", [(F16, 64, [300, 17, 512, 64, 131]), (BF16, 64, [257, 90]), (F16, 128, [200, 56])])
+def test_query_gradient_left_in_fp32_for_the_rope_backward(step, dtype, dh, lengths):
+    """gdb200_sdpa_varlen_backward_with_output_q32 + gdb200_qkv_split_rope_backward_q32: where the one-pass attention backward
+    runs (head_dim 64) the query gradient stays unrounded in the FP32 accumulator and the RoPE backward rounds it on load, bit
+    for bit what rounding it first and calling the reference entry gives; elsewhere grad_q is written and the flag says so."""
+    ctx, lib = step, step.lib
+    n, h = sum(lengths), 4
+    cu = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    q, k, v, go = (rnd_np(rng(140 + i).standard_normal((n, h, dh)).astype(np.float32) * s, dtype) for i, s in enumerate((0.5, 0.5, 1.0, 1.0)))
+    pos = np.concatenate([np.arange(x) for x in lengths]).astype(np.int32)
+    qt, kt, vt, got, cut, post = dev(ctx, q, dtype), dev(ctx, k, dtype), dev(ctx, v, dtype), dev(ctx, go, dtype), dev(ctx, cu, I32), dev(ctx, pos, I32)
+    scale = 1.0 / math.sqrt(dh)
+    stats, out = ctx.scratch_empty(F32, (n, h, 3)), ctx.scratch_empty(dtype, (n, h, dh))
+    fargs = abi.SdpaVarlenArgs(scale, 1, 0, 0, max(lengths), 0)
+    ctx.check(lib.gd_backend_sdpa_varlen(ctx.backend, byref(qt.tv()), byref(kt.tv()), byref(vt.tv()), byref(cut.tv()), byref(out.tv()), byref(stats.tv()), byref(fargs)), "sdpa_varlen")
+    dq, dk, dv = (ctx.scratch_empty(dtype, (n, h, dh)) for _ in range(3))
+    ctx.fill(dq, 0)
+    acc = ctx.scratch_empty(F32, (n, h, dh))
+    bargs = abi.SdpaVarlenArgs(scale, 1, 0, 0, max(lengths), 1)
+    flag = C.c_int32(-1)
+    ctx.check(lib.gdb200_sdpa_varlen_backward_with_output_q32(ctx.backend, byref(got.tv()), byref(qt.tv()), byref(kt.tv()), byref(vt.tv()), byref(cut.tv()),
+                                                              byref(out.tv()), byref(dq.tv()), byref(dk.tv()), byref(dv.tv()), byref(stats.tv()), byref(acc.tv()),
+                                                              byref(bargs), byref(flag)), "sdpa backward, query gradient in FP32")
+    wdq, wdk, wdv = O.sdpa_varlen_backward(t32(go), t32(q), t32(k), t32(v), cu, scale, True, 0, 0, storage_name(dtype))
+    close(host(dk), wdk, dtype, scale=6, what="dk")
+    close(host(dv), wdv, dtype, scale=6, what="dv")
+    rope = abi.RopeArgs(10000.0, dh, 0)
+    dqkv = ctx.scratch_empty(dtype, (n, 3 * h * dh))
+    if dh != 64:
+        assert flag.value == 0                                           # the one-pass kernel does not take this head size
+        close(host(dq), wdq, dtype, scale=4, what="dq")
+        return
+    assert flag.value == 1 and not host(dq).any()                        # grad_q untouched
+    dq_rounded = rnd_np(host(acc), dtype)
+    close(dq_rounded, wdq, dtype, scale=4, what="dq (rounded accumulator)")
+    ctx.check(lib.gdb200_qkv_split_rope_backward_q32(ctx.backend, byref(acc.tv()), byref(dk.tv()), byref(dv.tv()), byref(post.tv()), byref(dqkv.tv()), h, dh, byref(rope)),
+              "rope backward from the FP32 query gradient")
+    want = ctx.scratch_empty(dtype, (n, 3 * h * dh))
+    ctx.check(lib.gd_backend_qkv_split_rope_backward(ctx.backend, byref(dev(ctx, dq_rounded, dtype).tv()), byref(dk.tv()), byref(dv.tv()), byref(post.tv()), byref(want.tv()), h, dh,
+                                                     byref(rope)), "rope backward, reference entry")
+    assert np.array_equal(host(dqkv).view(np.uint32), host(want).view(np.uint32))
+
+
 # ------------------------------------------------------------------ batched contractions (src/ops/matmul/core_matmul.c:47,54)
 def _bview(t, batch_shape, rows, cols, strides_elems, es):
     v = abi.BatchedMatrixView()
