@@ -319,6 +319,12 @@ gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view 
                                    const gd_backend_tensor_view *weight, const gd_backend_tensor_view *sum, const gd_backend_tensor_view *mask,
                                    const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv, size_t rows, size_t cols, float eps,
                                    float p, uint64_t seed);
+// sum = dropout(embedding(table, ids)) (mask written), out = rms_norm(sum, weight), inv_rms saved: gd_backend_embedding_forward,
+// gd_backend_dropout_forward and gd_backend_rms_norm_forward_stats in one launch. GD_ERR_UNSUPPORTED when the vector path does not apply.
+gd_status gdb_embedding_dropout_rms_norm(gd_backend *be, const gd_backend_tensor_view *table, const gd_backend_tensor_view *ids,
+                                         const gd_backend_tensor_view *weight, const gd_backend_tensor_view *sum, const gd_backend_tensor_view *mask,
+                                         const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv, size_t rows, size_t cols, size_t vocab,
+                                         float eps, float p, uint64_t seed);
 // Loss normaliser of a data-parallel step: counts F32 [2] = {valid target rows of the global batch, of this rank's shard}.
 // gdb_lm_ce_count_valid writes the local count into both; the caller sums element 0 over the ranks before
 // gdb_lm_ce_reduce_normalize_global divides by it (the reference's kernel, src/ops/lm_cross_entropy/metal_lm_cross_entropy.metal:244-252,

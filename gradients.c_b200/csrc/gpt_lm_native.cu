@@ -359,19 +359,47 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
 
     // ---------------------------------------------------------------- forward
     const Ten emb_w = c.param(0, {V, D});
-    Ten x0 = c.alloc(dt, {T, D});
     gd_backend_embedding_args ea = {(uint64_t)T, (uint64_t)V, (uint64_t)D};
-    {
-        gd_backend_tensor_view a = tv(emb_w), b = tv(ids), o = tv(x0);
-        c.ok(gd_backend_embedding_forward(be, &a, &b, &o, &ea), "embedding_forward");
-    }
-    Ten x = x0, emb_mask;
+    Ten x, emb_mask, next_normed, next_inv;
+    bool have_next_norm = false;   // the norm in front of the next block came out of the launch that formed its input
     memset(&emb_mask, 0, sizeof(emb_mask));
-    if (drop) {
+    bool embedded = false;
+    if (drop && L > 0 && c.st == GD_OK) {
+        // embedding gather, its dropout and the first block's norm in one launch where the fused kernel takes the shape
+        // (GDB200_FUSE_EMBED=0: the three entries)
+        static const bool fuse_embed = !(getenv("GDB200_FUSE_EMBED") != NULL && getenv("GDB200_FUSE_EMBED")[0] == '0');
+        const size_t mark = c.top;
         x = c.alloc(dt, {T, D});
         emb_mask = c.alloc(GDB_DTYPE_U8, {T, D});
-        gd_backend_tensor_view a = tv(x0), y = tv(x), m = tv(emb_mask);
-        c.ok(gd_backend_dropout_forward(be, &a, &y, &m, s->dropout_p, splitmix64(s->dropout_seed ^ SITE_EMBED ^ step)), "dropout_forward");
+        Ten nrm = c.alloc(dt, {T, D}), iv = c.alloc(GDB_DTYPE_F32, {T});
+        const Ten w0 = c.param(1, {D});
+        gd_backend_tensor_view a = tv(emb_w), b = tv(ids), wv = tv(w0), y = tv(x), m = tv(emb_mask), nv = tv(nrm), ivv = tv(iv);
+        const gd_status st = fuse_embed ? gdb_embedding_dropout_rms_norm(be, &a, &b, &wv, &y, &m, &nv, &ivv, (size_t)T, (size_t)D, (size_t)V, s->rms_eps,
+                                                                         s->dropout_p, splitmix64(s->dropout_seed ^ SITE_EMBED ^ step))
+                                        : GD_ERR_UNSUPPORTED;
+        if (st == GD_OK) {
+            next_normed = nrm;
+            next_inv = iv;
+            have_next_norm = true;
+            embedded = true;
+        } else {
+            if (st != GD_ERR_UNSUPPORTED) c.ok(st, "embedding + dropout + rms_norm");
+            c.top = mark;
+        }
+    }
+    if (!embedded) {
+        Ten x0 = c.alloc(dt, {T, D});
+        {
+            gd_backend_tensor_view a = tv(emb_w), b = tv(ids), o = tv(x0);
+            c.ok(gd_backend_embedding_forward(be, &a, &b, &o, &ea), "embedding_forward");
+        }
+        x = x0;
+        if (drop) {
+            x = c.alloc(dt, {T, D});
+            emb_mask = c.alloc(GDB_DTYPE_U8, {T, D});
+            gd_backend_tensor_view a = tv(x0), y = tv(x), m = tv(emb_mask);
+            c.ok(gd_backend_dropout_forward(be, &a, &y, &m, s->dropout_p, splitmix64(s->dropout_seed ^ SITE_EMBED ^ step)), "dropout_forward");
+        }
     }
     std::vector<LayerSave> saves((size_t)L);
     gd_backend_rope_args rope = {s->rope_theta, (uint32_t)Dh, 0U};
@@ -407,8 +435,6 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
         }
         *normed = rms_forward(c, *sum, w, T, D, inv);
     };
-    Ten next_normed, next_inv;
-    bool have_next_norm = false;
     for (int i = 0; i < L && c.st == GD_OK; ++i) {
         LayerSave &sv = saves[(size_t)i];
         const int pb = 1 + 10 * i;

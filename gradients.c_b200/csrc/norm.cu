@@ -85,9 +85,13 @@ __global__ void rms_fwd_kernel(const T *x, const T *w, T *out, float *inv_out, s
 // (same rounding points). Warp per row, cols % 8 == 0, 16-byte aligned 16-bit tensors.
 // DROP: y goes through inverted dropout first (round(y * scale) or 0, decision per element index, mask bytes written),
 // i.e. gd_backend_dropout_add_forward; inv_out != NULL saves 1 / rms per row (rms_norm_forward_stats).
-template <typename T, bool DROP>
+// GATHER (with DROP): there is no residual; y is an embedding table [vocab, cols] and row r of the input is table row ids[r] (NaN
+// for an id outside the table), so sum = dropout(embedding(ids)): gd_backend_embedding_forward, gd_backend_dropout_forward and
+// gd_backend_rms_norm_forward_stats in one launch.
+template <typename T, bool DROP, bool GATHER = false>
 __global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *w, uint4 *sum, uint4 *out, size_t rows, size_t cols, float eps,
-                                   uint2 *mask_out, float *inv_out, float scale, uint64_t seed, unsigned threshold)
+                                   uint2 *mask_out, float *inv_out, float scale, uint64_t seed, unsigned threshold, const int *ids = nullptr,
+                                   size_t vocab = 0, unsigned nan_word = 0)
 {
     gdb_pdl_sync();
     const int lane = threadIdx.x & 31;
@@ -96,11 +100,18 @@ __global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *
         return;
     }
     const size_t vecs = cols / 8U, base = row * vecs;
+    int id = 0;
+    if (GATHER) id = __ldg(&ids[row]);
+    const bool in_table = !GATHER || (id >= 0 && (size_t)id < vocab);
     float ss = 0.0f;
     for (size_t v = lane; v < vecs; v += 32) {
         gdb_vec8<T> a, b;
-        a.raw = x[base + v];
-        b.raw = y[base + v];
+        if (GATHER) {
+            b.raw = in_table ? __ldg(&y[(size_t)id * vecs + v]) : make_uint4(nan_word, nan_word, nan_word, nan_word);
+        } else {
+            a.raw = x[base + v];
+            b.raw = y[base + v];
+        }
         uint2 m = make_uint2(0U, 0U);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -111,7 +122,7 @@ __global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *
                 *mw |= (keep ? 1U : 0U) << (8U * (unsigned)(e & 3));
                 add = keep ? gdb_io<T>::rnd(add * scale) : 0.0f;
             }
-            a.set(e, a.get(e) + add);
+            a.set(e, GATHER ? add : a.get(e) + add);
             const float f = a.get(e);
             ss += f * f;
         }
@@ -641,10 +652,10 @@ gd_status gdb_add_rms_norm(gd_backend *be, const gd_backend_tensor_view *x, cons
     const unsigned grid = (unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
     if (dt == GDB_DTYPE_F16) {
         gdb_launch(add_rms_fwd_kernel<__half, false>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps,
-                   (uint2 *)nullptr, (float *)nullptr, 1.0f, (uint64_t)0, 0U);
+                   (uint2 *)nullptr, (float *)nullptr, 1.0f, (uint64_t)0, 0U, (const int *)nullptr, (size_t)0, 0U);
     } else {
         gdb_launch(add_rms_fwd_kernel<__nv_bfloat16, false>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)xp, (const uint4 *)yp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps,
-                   (uint2 *)nullptr, (float *)nullptr, 1.0f, (uint64_t)0, 0U);
+                   (uint2 *)nullptr, (float *)nullptr, 1.0f, (uint64_t)0, 0U, (const int *)nullptr, (size_t)0, 0U);
     }
     return gdb_launched(be, "add_rms_norm");
 }
@@ -797,10 +808,66 @@ gd_status gdb_dropout_add_rms_norm(gd_backend *be, const gd_backend_tensor_view 
     const unsigned threshold = gdb_dropout_threshold(p);
     if (dt == GDB_DTYPE_F16) {
         gdb_launch(add_rms_fwd_kernel<__half, true>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)rp, (const uint4 *)xp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps,
-                   (uint2 *)mp, ip, scale, seed, threshold);
+                   (uint2 *)mp, ip, scale, seed, threshold, (const int *)nullptr, (size_t)0, 0U);
     } else {
         gdb_launch(add_rms_fwd_kernel<__nv_bfloat16, true>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)rp, (const uint4 *)xp, (const uint4 *)wp, (uint4 *)sp, (uint4 *)op, rows, cols, eps,
-                   (uint2 *)mp, ip, scale, seed, threshold);
+                   (uint2 *)mp, ip, scale, seed, threshold, (const int *)nullptr, (size_t)0, 0U);
     }
     return gdb_launched(be, "dropout_add_rms_norm");
+}
+
+// sum = dropout(embedding(table, ids)) (mask written), out = rms_norm(sum, weight), inv_rms saved: gd_backend_embedding_forward,
+// gd_backend_dropout_forward and gd_backend_rms_norm_forward_stats in one launch, same rounding points and the same keep decision
+// per element index. GD_ERR_UNSUPPORTED when the vector path does not apply.
+gd_status gdb_embedding_dropout_rms_norm(gd_backend *be, const gd_backend_tensor_view *table, const gd_backend_tensor_view *ids,
+                                         const gd_backend_tensor_view *weight, const gd_backend_tensor_view *sum, const gd_backend_tensor_view *mask,
+                                         const gd_backend_tensor_view *out, const gd_backend_tensor_view *inv, size_t rows, size_t cols, size_t vocab,
+                                         float eps, float p, uint64_t seed)
+{
+    if (be == NULL || table == NULL || ids == NULL || weight == NULL || sum == NULL || mask == NULL || out == NULL || inv == NULL || rows == 0U ||
+        cols == 0U || vocab == 0U || !(p >= 0.0f && p < 1.0f)) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const uint32_t dt = table->dtype;
+    if ((dt != GDB_DTYPE_F16 && dt != GDB_DTYPE_BF16) || (cols % 8U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    if (table->count != vocab * cols || ids->count != rows || sum->count != rows * cols || out->count != sum->count || mask->count != sum->count ||
+        weight->count != cols || inv->count != rows || sum->dtype != dt || out->dtype != dt || weight->dtype != dt) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    const void *tp = gdb_tv_ptr(table, dt), *wp = gdb_tv_ptr(weight, dt);
+    const int *ip = (const int *)gdb_tv_ptr(ids, GDB_DTYPE_I32);
+    void *sp = gdb_tv_ptr(sum, dt), *op = gdb_tv_ptr(out, dt), *mp = gdb_tv_ptr(mask, GDB_DTYPE_U8);
+    float *vp = (float *)gdb_tv_ptr(inv, GDB_DTYPE_F32);
+    if (tp == NULL || wp == NULL || ip == NULL || sp == NULL || op == NULL || mp == NULL || vp == NULL) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    if ((((uintptr_t)tp | (uintptr_t)wp | (uintptr_t)sp | (uintptr_t)op) % 16U) != 0U || ((uintptr_t)mp % 8U) != 0U) {
+        return GD_ERR_UNSUPPORTED;
+    }
+    cudaSetDevice(be->device);
+    const unsigned grid = (unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
+    const float scale = 1.0f / (1.0f - p);
+    const unsigned threshold = gdb_dropout_threshold(p);
+    if (dt == GDB_DTYPE_F16) {
+        gdb_launch(add_rms_fwd_kernel<__half, true, true>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)nullptr, (const uint4 *)tp, (const uint4 *)wp, (uint4 *)sp,
+                   (uint4 *)op, rows, cols, eps, (uint2 *)mp, vp, scale, seed, threshold, ip, vocab, 0x7e007e00U);
+    } else {
+        gdb_launch(add_rms_fwd_kernel<__nv_bfloat16, true, true>, grid, 32 * ROWS_PER_BLOCK, 0, be->stream, (const uint4 *)nullptr, (const uint4 *)tp, (const uint4 *)wp, (uint4 *)sp,
+                   (uint4 *)op, rows, cols, eps, (uint2 *)mp, vp, scale, seed, threshold, ip, vocab, 0x7fc07fc0U);
+    }
+    return gdb_launched(be, "embedding + dropout + rms_norm");
+}
+
+extern "C" gd_status gdb200_embedding_dropout_rms_norm(gd_backend *be, const gd_backend_tensor_view *table, const gd_backend_tensor_view *ids,
+                                                       const gd_backend_tensor_view *weight, const gd_backend_tensor_view *x, const gd_backend_tensor_view *mask,
+                                                       const gd_backend_tensor_view *normed, const gd_backend_tensor_view *inv_rms, float eps, float p,
+                                                       uint64_t seed)
+{
+    if (table == NULL || ids == NULL || table->rank != 2U || table->shape[0] <= 0 || table->shape[1] <= 0) {
+        return GD_ERR_INVALID_ARGUMENT;
+    }
+    return gdb_embedding_dropout_rms_norm(be, table, ids, weight, x, mask, normed, inv_rms, (size_t)ids->count, (size_t)table->shape[1],
+                                          (size_t)table->shape[0], eps, p, seed);
 }

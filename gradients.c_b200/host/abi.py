@@ -307,6 +307,7 @@ PROTOTYPES = {
     "gdb200_matmul_nt_swiglu_backward": (_ST, [P, MV, MV, MV, MV]),
     "gdb200_rms_norm_backward_with_weight": (_ST, [P, TV, TV, TV, TV, TV, I32_T, TV, TV, C.POINTER(RmsNormArgs)]),
     "gdb200_rms_norm_backward_with_weight_dropout": (_ST, [P, TV, TV, TV, TV, TV, I32_T, TV, TV, C.POINTER(RmsNormArgs), TV, TV, F, TV]),
+    "gdb200_embedding_dropout_rms_norm": (_ST, [P, TV, TV, TV, TV, TV, TV, TV, F, F, U64]),
     "gdb200_lm_cross_entropy_fused_rows": (_ST, [P, TV, TV, TV, TV, TV, TV, F, F, I32_T]),
     "gdb200_matmul_tn_colsum": (_ST, [P, MV, MV, MV, VV]),
     "gdb200_argmax_rows": (_ST, [P, TV, F, TV]),

@@ -448,6 +448,17 @@ gd_status gdb200_rms_norm_backward_with_weight_dropout(gd_backend *backend, cons
                                                        const gd_backend_tensor_view *grad_dropped, float scale,
                                                        const gd_backend_tensor_view *grad_dropped_colsum);
 
+/* The head of the gpt_lm forward pass (examples/gpt_lm/gpt_lm_shared.c:751-790) in one launch: x = dropout(embedding(table, ids))
+ * with the keep mask written, normed = rms_norm(x, weight) and inv_rms saved, i.e. gd_backend_embedding_forward,
+ * gd_backend_dropout_forward and gd_backend_rms_norm_forward_stats (src/core/backend.h) with the same rounding points, the same
+ * keep decision per element index (seed as gd_backend_dropout_forward takes it) and NaN rows for ids outside the table: bit for bit
+ * the three entries' x, mask and normed. table [vocab, cols] and x / normed [ids, cols] in F16 or BF16, cols a multiple of 8,
+ * 16-byte aligned; GD_ERR_UNSUPPORTED otherwise (the caller then makes the three calls). */
+gd_status gdb200_embedding_dropout_rms_norm(gd_backend *backend, const gd_backend_tensor_view *table, const gd_backend_tensor_view *ids,
+                                            const gd_backend_tensor_view *weight, const gd_backend_tensor_view *x, const gd_backend_tensor_view *mask,
+                                            const gd_backend_tensor_view *normed, const gd_backend_tensor_view *inv_rms, float eps, float p,
+                                            uint64_t seed);
+
 /* Fused LM cross entropy of a logits matrix that holds ALL classes (one chunk), loss statistics and logits gradient from ONE
  * pass: gd_backend_lm_cross_entropy_online_update + _finalize + _backward_chunk (src/core/backend.h, called by
  * src/ops/lm_cross_entropy/core_lm_cross_entropy.c:452-675 and :876-890) for a caller that knows the gradient seed and the

@@ -75,6 +75,42 @@ def test_embedding_forward_backward(step, dtype, dim):
     close(host(tt.grad), O.embedding_backward(t32(g), torch.from_numpy(ids), vocab, storage_name(dtype)), dtype, scale=4)
 
 
+@pytest.mark.parametrize("dtype,dim,p", [(F16, 512, 0.1), (BF16, 64, 0.25), (F16, 24, 0.0), (F16, 12, 0.1)])
+def test_embedding_dropout_and_first_norm_in_one_launch(step, dtype, dim, p):
+    """gdb200_embedding_dropout_rms_norm against the three entries it stands for (embedding_forward, dropout_forward,
+    rms_norm_forward_stats): x, mask and normed bit for bit, 1 / rms to FP32 rounding; ids outside the table give NaN rows."""
+    ctx, lib = step, step.lib
+    vocab, n, seed, eps = 97, 301, 0x0123456789ABCDEF, 1e-5
+    table = rnd_np(rng(4).standard_normal((vocab, dim)).astype(np.float32), dtype)
+    w = rnd_np((rng(5).standard_normal(dim) * 0.25 + 1).astype(np.float32), dtype)
+    ids = rng(6).integers(0, vocab, size=n).astype(np.int32)
+    ids[[3, 50]] = [-1, vocab]
+    tt, it, wt = dev(ctx, table, dtype), dev(ctx, ids, I32), dev(ctx, w, dtype)
+    x1, m1, y1, inv1 = ctx.scratch_empty(dtype, (n, dim)), ctx.scratch_empty(U8, (n, dim)), ctx.scratch_empty(dtype, (n, dim)), ctx.scratch_empty(F32, (n,))
+    st = lib.gdb200_embedding_dropout_rms_norm(ctx.backend, byref(tt.tv()), byref(it.tv()), byref(wt.tv()), byref(x1.tv()), byref(m1.tv()), byref(y1.tv()),
+                                               byref(inv1.tv()), eps, p, seed)
+    if dim % 8:
+        assert st == abi.GD_ERR_UNSUPPORTED
+        return
+    ctx.check(st, "embedding + dropout + rms_norm")
+    e0, x0, m0, y0, inv0 = (ctx.scratch_empty(dtype, (n, dim)), ctx.scratch_empty(dtype, (n, dim)), ctx.scratch_empty(U8, (n, dim)),
+                            ctx.scratch_empty(dtype, (n, dim)), ctx.scratch_empty(F32, (n,)))
+    ea = abi.EmbeddingArgs(n, vocab, dim)
+    ctx.check(lib.gd_backend_embedding_forward(ctx.backend, byref(tt.tv()), byref(it.tv()), byref(e0.tv()), byref(ea)), "embedding_forward")
+    ctx.check(lib.gd_backend_dropout_forward(ctx.backend, byref(e0.tv()), byref(x0.tv()), byref(m0.tv()), p, seed), "dropout_forward")
+    args = ops._rms_args(n, dim, eps)
+    ctx.check(lib.gd_backend_rms_norm_forward_stats(ctx.backend, byref(x0.tv()), byref(wt.tv()), byref(y0.tv()), byref(inv0.tv()), byref(args)), "rms_norm_forward_stats")
+    bits = lambda t: host(t).astype(np.float32).view(np.uint32)
+    assert np.array_equal(host(m1), host(m0))
+    assert np.array_equal(bits(x1), bits(x0)) and np.array_equal(bits(y1), bits(y0))
+    ok = ~np.isnan(host(inv0))
+    np.testing.assert_allclose(host(inv1)[ok], host(inv0)[ok], rtol=1e-6)
+    assert np.isnan(host(x1)[3]).sum() + np.isnan(host(x1)[50]).sum() >= 1 and not np.isnan(host(x1)[4]).any()
+    want = O.embedding_forward(t32(table), torch.from_numpy(ids))
+    want_x, _ = O.dropout_forward(want.reshape(-1), p, seed, storage_name(dtype))
+    assert np.array_equal(np.nan_to_num(host(x1).reshape(-1)), np.nan_to_num(want_x.numpy()))
+
+
 # ------------------------------------------------------------------ dropout
 @pytest.mark.parametrize("dtype,n,p,seed", [(F16, 4096 * 16, 0.1, 0x1234567890ABCDEF), (F16, 513, 0.2, 2**64 - 5), (F32, 1000, 0.35, 42)])
 def test_dropout_family(step, dtype, n, p, seed):
