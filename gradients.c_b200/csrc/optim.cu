@@ -219,31 +219,31 @@ struct adamw_item {
     float lr, beta1, beta2, eps, weight_decay;
     float host_step_scale, host_decay_scale, host_eps_scaled;
 };
+// One launch takes up to ADAMW_BATCH tensors (the struct travels as a kernel parameter: 8.3 KB of the 32 KB sm_100 allows), which
+// covers every parameter of a gpt_lm of up to four blocks in one update launch.
+constexpr int ADAMW_BATCH = 48;
 struct adamw_batch {
-    adamw_item it[16];
-    unsigned block_start[17];
+    adamw_item it[ADAMW_BATCH];
+    unsigned block_start[ADAMW_BATCH + 1];
     int n;
 };
-
-__global__ void adamw_prepare_kernel(adamw_batch b)
+// The per-tensor step scalars (metal_adamw.metal:59-88, src/optim/adamw.c:1570-1640): bias corrections from the running beta
+// powers, which adamw_commit_kernel advances after the update.
+struct adamw_scalars {
+    float step_scale, decay_scale, eps_scaled;
+};
+__device__ __forceinline__ adamw_scalars adamw_step_scalars(const adamw_item &a)
 {
-    gdb_pdl_sync();
-    const int t = threadIdx.x;
-    if (t >= b.n) {
-        return;
-    }
-    const adamw_item &a = b.it[t];
-    if (a.beta1_power == nullptr || (a.found_inf != nullptr && *a.found_inf != 0)) {
-        return;
-    }
     const float b1p = __fmul_rn(a.beta1_power[0], a.beta1);
     const float b2p = __fmul_rn(a.beta2_power[0], a.beta2);
     const float bc1 = a.bias_correction ? __fsub_rn(1.0f, b1p) : 1.0f;
     const float bc2 = a.bias_correction ? __fsub_rn(1.0f, b2p) : 1.0f;
     const float bc2s = sqrtf(bc2);
-    a.step_scale[0] = __fdiv_rn(__fmul_rn(a.lr, bc2s), bc1);
-    a.decay_scale[0] = __fmul_rn(a.lr, a.weight_decay);
-    a.eps_scaled[0] = __fmul_rn(a.eps, bc2s);
+    adamw_scalars r;
+    r.step_scale = __fdiv_rn(__fmul_rn(a.lr, bc2s), bc1);
+    r.decay_scale = __fmul_rn(a.lr, a.weight_decay);
+    r.eps_scaled = __fmul_rn(a.eps, bc2s);
+    return r;
 }
 
 __global__ void adamw_commit_kernel(adamw_batch b)
@@ -279,9 +279,24 @@ __global__ void adamw_update_kernel(adamw_batch b)
         return;  // overflow: the whole update is skipped (metal_adamw.metal:117)
     }
     const float gs = a.grad_scale != nullptr ? a.grad_scale[0] : 1.0f;
-    const float step_scale = a.step_scale != nullptr ? a.step_scale[0] : a.host_step_scale;
-    const float decay_scale = a.decay_scale != nullptr ? a.decay_scale[0] : a.host_decay_scale;
-    const float eps_scaled = a.eps_scaled != nullptr ? a.eps_scaled[0] : a.host_eps_scaled;
+    float step_scale = a.host_step_scale, decay_scale = a.host_decay_scale, eps_scaled = a.host_eps_scaled;
+    if (a.beta1_power != nullptr) {
+        // device-side state: every block forms the tensor's step scalars itself (a dozen operations; the beta powers do not
+        // change before adamw_commit_kernel), and the tensor's first block leaves them in the state where the reference keeps them
+        const adamw_scalars sc = adamw_step_scalars(a);
+        step_scale = sc.step_scale;
+        decay_scale = sc.decay_scale;
+        eps_scaled = sc.eps_scaled;
+        if (blockIdx.x == b.block_start[t] && threadIdx.x == 0) {
+            a.step_scale[0] = sc.step_scale;
+            a.decay_scale[0] = sc.decay_scale;
+            a.eps_scaled[0] = sc.eps_scaled;
+        }
+    } else if (a.step_scale != nullptr) {
+        step_scale = a.step_scale[0];
+        decay_scale = a.decay_scale[0];
+        eps_scaled = a.eps_scaled[0];
+    }
     const float omb1 = __fsub_rn(1.0f, a.beta1), omb2 = __fsub_rn(1.0f, a.beta2);
     const size_t base = (size_t)(blockIdx.x - b.block_start[t]) * ADAMW_BLOCK_ELEMS;
     // Full block of 16-bit parameters / gradients with FP32 masters: every thread owns 8 consecutive elements and moves
@@ -611,12 +626,12 @@ gd_status gd_backend_adamw_batch(gd_backend *be, const gd_backend_adamw_desc *de
             }
         }
     }
-    for (uint32_t start = 0; start < desc_count; start += 16U) {
+    for (uint32_t start = 0; start < desc_count; start += (uint32_t)ADAMW_BATCH) {
         adamw_batch b;
         memset(&b, 0, sizeof(b));
         unsigned blocks = 0;
         bool any_state = false;
-        for (uint32_t i = start; i < desc_count && i < start + 16U; ++i) {
+        for (uint32_t i = start; i < desc_count && i < start + (uint32_t)ADAMW_BATCH; ++i) {
             (void)fill_adamw_item(&descs[i], &b.it[b.n]);
             any_state = any_state || b.it[b.n].beta1_power != NULL;
             b.block_start[b.n] = blocks;
@@ -625,20 +640,14 @@ gd_status gd_backend_adamw_batch(gd_backend *be, const gd_backend_adamw_desc *de
         }
         b.block_start[b.n] = blocks;
         gd_status st;
-        if (any_state) {
-            gdb_launch(adamw_prepare_kernel, 1, 32, 0, be->stream, b);
-            st = gdb_launched(be, "adamw_prepare");
-            if (st != GD_OK) {
-                return st;
-            }
-        }
+        // (the step scalars of tensors with device-side state are formed inside the update kernel)
         gdb_launch(adamw_update_kernel, blocks, 256, 0, be->stream, b);
         st = gdb_launched(be, "adamw_update");
         if (st != GD_OK) {
             return st;
         }
         if (any_state) {
-            gdb_launch(adamw_commit_kernel, 1, 32, 0, be->stream, b);
+            gdb_launch(adamw_commit_kernel, 1, 64, 0, be->stream, b);
             st = gdb_launched(be, "adamw_commit");
             if (st != GD_OK) {
                 return st;
