@@ -613,8 +613,6 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
             grads[(size_t)p] = g;
             cursor += (s->param_count[p] + 7U) & ~(size_t)7U;
         }
-        // padding elements between pieces take part in the all-reduce: keep them finite
-        c.ok(gd_backend_fill(be, block.buf, block.off, total, es, 0U), "grad block clear");
         *range_off = block.off;
         *range_elems = total;
     };
@@ -650,6 +648,8 @@ extern "C" gd_status gdb200_gpt_train_step(gd_backend *be, const gdb200_gpt_spec
     std::vector<size_t> blk_off((size_t)L), blk_elems((size_t)L);
     for (int i = L - 1; i >= 0; --i) alloc_grads(1 + 10 * i, 10, &blk_off[(size_t)i], &blk_elems[(size_t)i]);
     const size_t all_grads_end = c.top;
+    // padding elements between the pieces take part in the all-reduce: keep them finite (one clear over the whole range)
+    c.ok(gd_backend_fill(be, s->scratch_buffer, head_off, (all_grads_end - head_off) / es, es, 0U), "gradient range clear");
     Ten dh = c.alloc(dt, {T, D});
     if (!single) c.fill(dh, 0U);
     Ten dh_part;
