@@ -104,6 +104,61 @@ __global__ void add_rms_fwd_kernel(const uint4 *x, const uint4 *y, const uint4 *
     if (GATHER) id = __ldg(&ids[row]);
     const bool in_table = !GATHER || (id >= 0 && (size_t)id < vocab);
     float ss = 0.0f;
+    if (vecs <= 64U) {
+        // rows of up to 512 elements: the lane's two vectors of the sum stay in registers between the two passes and all four
+        // loads are in flight together (same arithmetic, element for element, as the general loop below)
+        gdb_vec8<T> a[2], b[2], wv[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const size_t v = (size_t)lane + 32U * (size_t)i;
+            if (v < vecs) {
+                if (GATHER) {
+                    b[i].raw = in_table ? __ldg(&y[(size_t)id * vecs + v]) : make_uint4(nan_word, nan_word, nan_word, nan_word);
+                } else {
+                    a[i].raw = x[base + v];
+                    b[i].raw = y[base + v];
+                }
+                wv[i].raw = __ldg(&w[v]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const size_t v = (size_t)lane + 32U * (size_t)i;
+            if (v < vecs) {
+                uint2 m = make_uint2(0U, 0U);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float add = b[i].get(e);
+                    if (DROP) {
+                        const bool keep = gdb_dropout_keep(seed, (uint64_t)(base + v) * 8U + (uint64_t)e, threshold);
+                        unsigned *mw = e < 4 ? &m.x : &m.y;
+                        *mw |= (keep ? 1U : 0U) << (8U * (unsigned)(e & 3));
+                        add = keep ? gdb_io<T>::rnd(add * scale) : 0.0f;
+                    }
+                    a[i].set(e, GATHER ? add : a[i].get(e) + add);
+                    const float f = a[i].get(e);
+                    ss += f * f;
+                }
+                sum[base + v] = a[i].raw;
+                if (DROP) mask_out[base + v] = m;
+            }
+        }
+        ss = gdb_warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)cols + eps);
+        if (inv_out != nullptr && lane == 0) inv_out[row] = inv;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const size_t v = (size_t)lane + 32U * (size_t)i;
+            if (v < vecs) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    a[i].set(e, a[i].get(e) * wv[i].get(e) * inv);
+                }
+                out[base + v] = a[i].raw;
+            }
+        }
+        return;
+    }
     for (size_t v = lane; v < vecs; v += 32) {
         gdb_vec8<T> a, b;
         if (GATHER) {
