@@ -259,13 +259,16 @@ def test_device_argmax_first_maximum_softcap_and_non_finite():
             assert got[0] == 5 and got[1] == 0 and got[4] == 0 and got[2] != 7 and (got[2] == 8) == (cap > 0.0)
 
 
-@pytest.mark.parametrize("tied,chunk_env", [(False, None), (True, None), (False, "128")])
-def test_native_step_driver_matches_python_host(monkeypatch, tied, chunk_env):
-    """The library's native per-step driver and the Python op capsules enqueue the same calls: losses
-    and updated parameters agree to within atomics noise (embedding scatter), and both track the oracle."""
+@pytest.mark.parametrize("tied,chunk_env,extra", [(False, None, {}), (True, None, {}), (False, "128", {}),
+                                                  (False, None, {"vocab_size": 324}),      # the one-pass cross entropy declines: three entries
+                                                  (False, None, {"dropout_p": 0.0})])      # no dropout: none of the fused dropout outputs
+def test_native_step_driver_matches_python_host(monkeypatch, tied, chunk_env, extra):
+    """The library's native per-step driver and the Python op capsules enqueue the same calls (the driver through its fused
+    entries where they take the shape): losses and updated parameters agree to within atomics noise (embedding scatter),
+    and both track the oracle."""
     if chunk_env:
         monkeypatch.setenv("GD_LM_CE_CHUNK_SIZE", chunk_env)
-    cfg = small_cfg(tied_lm_head=tied, sdpa_window=0 if not tied else 16)
+    cfg = small_cfg(tied_lm_head=tied, sdpa_window=0 if not tied else 16, **extra)
     tc = g.TrainConfig.baseline()
     hp = g.init_params(cfg, seed=21)
     batches = [g.synthetic_batch(cfg, n_seqs=5, min_len=4, max_len=64, seed=300 + s, pad_to=64) for s in range(3)]
