@@ -6,6 +6,7 @@
 // (broadcast rule), src/ops/dropout/metal_dropout.metal:6-140 + metal_dropout.m:145-155
 // (keep rule and threshold), src/ops/swiglu/metal_swiglu.metal:6-151.
 #include "common.cuh"
+#include "decode_parts.cuh"
 
 #include <math.h>
 
@@ -324,18 +325,20 @@ __global__ void swiglu_bwd_vec8_kernel(const uint4 *x1, const uint4 *x2, const u
     const unsigned n = rows * hv, stride = gridDim.x * blockDim.x;   // 32-bit index arithmetic, see the forward kernel
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const unsigned r = i / hv, c = i - r * hv;
-        gdb_vec8<T> a, b, g, d1, d2;
-        a.raw = x1[(size_t)r * in_ldv + c];
-        b.raw = x2[(size_t)r * in_ldv + c];
-        g.raw = go[i];
+        // packed conversions (two elements per instruction both ways); the arithmetic per element is unchanged
+        float a[8], b[8], g[8], d1[8], d2[8];
+        gdb_dec::unpack8<T>(x1[(size_t)r * in_ldv + c], a);
+        gdb_dec::unpack8<T>(x2[(size_t)r * in_ldv + c], b);
+        gdb_dec::unpack8<T>(go[i], g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            const float z = b.get(e), s = swiglu_sigmoid(z), gv = g.get(e);
-            d1.set(e, gv * (z * s));
-            d2.set(e, gv * a.get(e) * (s * (1.0f + z * (1.0f - s))));
+            const float z = b[e], s = swiglu_sigmoid(z), gv = g[e];
+            d1[e] = gv * (z * s);
+            d2[e] = gv * a[e] * (s * (1.0f + z * (1.0f - s)));
         }
-        dx1[(size_t)r * out_ldv + c] = d1.raw;
-        dx2[(size_t)r * out_ldv + c] = d2.raw;
+        using pk = gdb_dec::pack2<T>;
+        dx1[(size_t)r * out_ldv + c] = make_uint4(pk::down(d1[0], d1[1]), pk::down(d1[2], d1[3]), pk::down(d1[4], d1[5]), pk::down(d1[6], d1[7]));
+        dx2[(size_t)r * out_ldv + c] = make_uint4(pk::down(d2[0], d2[1]), pk::down(d2[2], d2[3]), pk::down(d2[4], d2[5]), pk::down(d2[6], d2[7]));
     }
 }
 
